@@ -1,0 +1,472 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:  D = epilogue(alpha * op(A) * op(B)).
+//
+//   * operands are staged global -> shared by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a
+//     4-deep mbarrier ring; one producer thread issues the copies;
+//   * one thread issues tcgen05.mma (128 x 256 x 16 per instruction, cta_group::1), accumulating in
+//     tensor memory; two 256-column accumulators are double-buffered so that the epilogue of tile i
+//     overlaps the main loop of tile i+1;
+//   * four epilogue warps read the accumulator with tcgen05.ld and apply the fused epilogue
+//     (alpha, bias, optional store of the pre-activation, GeLU / GeLU', residual or gradient
+//     accumulate, bf16 or fp32 output).
+//
+// Both operands may be K-major (the contraction index is contiguous in memory) or MN-major (the
+// output index is contiguous); the four combinations cover forward (X·Wᵀ), dgrad (dY·W) and wgrad
+// (dYᵀ·X) of a linear layer without any transposition pass.  This replaces the cuBLAS calls behind
+// F.linear in megatron/mpu/layers.py:578,777 of the reference.
+//
+// All barrier waits are bounded (see sm100_ptx.cuh); on a time-out the kernel records a code in the
+// status word, leaves its loops, frees its tensor memory and returns.
+#include "sm100_ptx.cuh"
+#include "neox_b200.h"
+#include <mutex>
+#include <unordered_map>
+#include <string.h>
+#include <stdio.h>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 1024;
+
+struct GemmParams {
+    int M, N, K;
+    int a_mn, b_mn;
+    void* D;
+    long long ldd;
+    int d_fp32;
+    const __nv_bfloat16* bias;
+    const void* add;
+    long long ldadd;
+    int add_fp32;
+    __nv_bfloat16* preact;
+    long long ldpre;
+    const __nv_bfloat16* aux;
+    long long ldaux;
+    int act;
+    float alpha;
+    int vec_ok;
+    int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
+    const int per_group = GROUP_M * num_n;
+    const int group = tile / per_group;
+    const int first_m = group * GROUP_M;
+    const int gsize = min(num_m - first_m, GROUP_M);
+    const int in_group = tile - group * per_group;
+    m_blk = first_m + in_group % gsize;
+    n_blk = in_group / gsize;
+}
+
+// Apply the fused epilogue to 32 consecutive columns of one output row.
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row, int col0, const GemmParams& p) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+    const bool full = p.vec_ok && (col0 + 32 <= p.N);
+    if (full) {
+        if (p.bias) {
+            const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 b = __ldg(b4 + j);
+                uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    v[j * 8 + t * 2] += bf16_lo(w[t]);
+                    v[j * 8 + t * 2 + 1] += bf16_hi(w[t]);
+                }
+            }
+        }
+        if (p.preact) {
+            uint4* o = reinterpret_cast<uint4*>(p.preact + (long long)row * p.ldpre + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 q;
+                q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+                q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+                q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+                q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+                o[j] = q;
+            }
+        }
+        if (p.act == 1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        } else if (p.act == 2) {
+            const uint4* a4 = reinterpret_cast<const uint4*>(p.aux + (long long)row * p.ldaux + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 a = __ldg(a4 + j);
+                uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    v[j * 8 + t * 2] *= dgelu_tanh(bf16_lo(w[t]));
+                    v[j * 8 + t * 2 + 1] *= dgelu_tanh(bf16_hi(w[t]));
+                }
+            }
+        }
+        if (p.add) {
+            if (p.add_fp32) {
+                const float4* a4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.add) +
+                                                                   (long long)row * p.ldadd + col0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float4 a = a4[j];
+                    v[j * 4 + 0] += a.x;
+                    v[j * 4 + 1] += a.y;
+                    v[j * 4 + 2] += a.z;
+                    v[j * 4 + 3] += a.w;
+                }
+            } else {
+                const uint4* a4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.add) +
+                                                                 (long long)row * p.ldadd + col0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 a = a4[j];
+                    uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        v[j * 8 + t * 2] += bf16_lo(w[t]);
+                        v[j * 8 + t * 2 + 1] += bf16_hi(w[t]);
+                    }
+                }
+            }
+        }
+        if (p.d_fp32) {
+            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        } else {
+            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 q;
+                q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+                q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+                q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+                q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+                o[j] = q;
+            }
+        }
+    } else {
+        // ragged / unaligned edge: element-wise with bounds checks
+        for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            if (col >= p.N) break;
+            float x = v[i];
+            if (p.bias) x += __bfloat162float(p.bias[col]);
+            if (p.preact) p.preact[(long long)row * p.ldpre + col] = __float2bfloat16(x);
+            if (p.act == 1) x = gelu_tanh(x);
+            else if (p.act == 2) x *= dgelu_tanh(__bfloat162float(p.aux[(long long)row * p.ldaux + col]));
+            if (p.add) {
+                if (p.add_fp32) x += reinterpret_cast<const float*>(p.add)[(long long)row * p.ldadd + col];
+                else x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.add)[(long long)row * p.ldadd + col]);
+            }
+            if (p.d_fp32) reinterpret_cast<float*>(p.D)[(long long)row * p.ldd + col] = x;
+            else reinterpret_cast<__nv_bfloat16*>(p.D)[(long long)row * p.ldd + col] = __float2bfloat16(x);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* tfull = empty + STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 4);
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (p.M + BM - 1) / BM;
+    const int num_n = (p.N + BN - 1) / BN;
+    const int ntiles = num_m * num_n;
+    const int nk = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                int m_blk, n_blk;
+                tile_coords(tile, num_m, num_n, m_blk, n_blk);
+                for (int kb = 0; kb < nk; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1)) {
+                        atomicExch(p.status, 101);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+                    uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+                    uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+                    if (!p.a_mn) {
+                        tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m_blk * BM);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_2d(a_dst + j * (64 * BK * 2), &tmA, &full[stage], m_blk * BM + j * 64, kb * BK);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n_blk * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(b_dst + j * (64 * BK * 2), &tmB, &full[stage], n_blk * BN + j * 64, kb * BK);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+            int stage = 0;
+            uint32_t phase = 0;
+            int buf = 0;
+            uint32_t bphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(&tempty[buf], bphase ^ 1)) {
+                    atomicExch(p.status, 102);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < nk; ++kb) {
+                    if (!mbar_wait(&full[stage], phase)) {
+                        atomicExch(p.status, 103);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
+                    const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(a_base + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                      : make_smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_base + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                      : make_smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
+                        umma_bf16_ss(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&tfull[buf]);
+                buf ^= 1;
+                if (buf == 0) bphase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps (2..5)
+        const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+        int buf = 0;
+        uint32_t bphase = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            int m_blk, n_blk;
+            tile_coords(tile, num_m, num_n, m_blk, n_blk);
+            if (!mbar_wait(&tfull[buf], bphase)) {
+                if (lane == 0) atomicExch(p.status, 104);
+                break;
+            }
+            tc_fence_after();
+            const int row = m_blk * BM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = n_blk * BN + c * 32;
+                if (col0 >= p.N) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c * 32, r);
+                tmem_wait_ld();
+                if (row < p.M) epilogue_chunk(r, row, col0, p);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[buf]);
+            buf ^= 1;
+            if (buf == 0) bphase ^= 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    unsigned long long d0, d1, ld;
+    unsigned b0, b1;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        h = h * 1000003u ^ k.d0;
+        h = h * 1000003u ^ k.d1;
+        h = h * 1000003u ^ k.ld;
+        h = h * 1000003u ^ (size_t(k.b0) << 16 | k.b1);
+        return h;
+    }
+};
+
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+}  // namespace
+
+// Build (or fetch from a cache) the 2-D bf16 tensor map of a row-major [d1, d0] view with a row
+// pitch of `ld` elements and a [b1, b0] box, 128-byte swizzled.
+int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                           unsigned long long ld, unsigned b0, unsigned b1) {
+    MapKey key{ptr, d0, d1, ld, b0, b1};
+    {
+        std::lock_guard<std::mutex> g(g_map_mu);
+        auto it = g_maps.find(key);
+        if (it != g_maps.end()) {
+            *out = it->second;
+            return 0;
+        }
+    }
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return NEOX_ERR_DRIVER;
+    cuuint64_t dims[2] = {d0, d1};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {b0, b1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return NEOX_ERR_TMAP;
+    std::lock_guard<std::mutex> g(g_map_mu);
+    if (g_maps.size() > 8192) g_maps.clear();
+    g_maps.emplace(key, *out);
+    return 0;
+}
+
+extern "C" int neox_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                              long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
+                              const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
+                              const void* aux, long long ldaux, int act, float alpha, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes.
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8))
+        return NEOX_ERR_ALIGN;
+    int* status = neox_status_word();
+    if (!status) return NEOX_ERR_DRIVER;
+
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (!a_mn) rc = neox_make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
+    else rc = neox_make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+    if (rc) return rc;
+    if (!b_mn) rc = neox_make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, BN);
+    else rc = neox_make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+    if (rc) return rc;
+
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K;
+    p.a_mn = a_mn; p.b_mn = b_mn;
+    p.D = D; p.ldd = ldd; p.d_fp32 = d_fp32;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.add = add; p.ldadd = ldadd; p.add_fp32 = add_fp32;
+    p.preact = static_cast<__nv_bfloat16*>(preact); p.ldpre = ldpre;
+    p.aux = static_cast<const __nv_bfloat16*>(aux); p.ldaux = ldaux;
+    p.act = act; p.alpha = alpha;
+    p.status = status;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    bool vec = al16(D) && (ldd % 8 == 0);
+    if (bias) vec = vec && al16(bias);
+    if (add) vec = vec && al16(add) && (ldadd % 8 == 0);
+    if (preact) vec = vec && al16(preact) && (ldpre % 8 == 0);
+    if (aux) vec = vec && al16(aux) && (ldaux % 8 == 0);
+    p.vec_ok = vec ? 1 : 0;
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_BYTES);
+        if (e != cudaSuccess) return NEOX_ERR_LAUNCH;
+        attr_set = true;
+    }
+    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    int grid = num_m * num_n;
+    const int sms = neox_sm_count();
+    if (grid > sms) grid = sms;
+    gemm_bf16_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}

@@ -1,0 +1,101 @@
+"""bf16 GEMM front-end for the tcgen05 kernel in ``csrc/gemm_sm100.cu``.
+
+``gemm(a, b, ...)`` computes ``epilogue(alpha * op(a) @ op(b))`` where each operand is given as a
+2-D tensor and a flag telling whether it is stored "K-major" (contraction index contiguous) or
+"MN-major".  The three GEMMs of a linear layer map onto it without any transposition copy:
+
+=========  =======================  ==================  ==================
+pass       math                     A (stored)          B (stored)
+=========  =======================  ==================  ==================
+forward    Y[M,N] = X W^T           X[M,K]  K-major     W[N,K]  K-major
+dgrad      dX[M,K] = dY W           dY[M,N] K-major     W[N,K]  MN-major
+wgrad      dW[N,K] = dY^T X         dY[M,N] MN-major    X[M,K]  MN-major
+=========  =======================  ==================  ==================
+
+On CPU (no device) the same function evaluates the identical math with torch ops in fp32, which is
+the oracle the GPU tests compare against.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+
+ACT_NONE, ACT_GELU, ACT_DGELU = 0, 1, 2
+
+
+def gelu_tanh_ref(x):
+    return F.gelu(x, approximate="tanh")
+
+
+def dgelu_tanh_ref(x):
+    k0, k1 = 0.7978845608028654, 0.044715
+    t = torch.tanh(k0 * x * (1 + k1 * x * x))
+    return 0.5 * x * ((1 - t * t) * (k0 + 3 * k0 * k1 * x * x)) + 0.5 * (1 + t)
+
+
+def gemm_ref(a, b, a_mn=False, b_mn=False, out_dtype=torch.bfloat16, bias=None, add=None, act=ACT_NONE, aux=None,
+             alpha=1.0, want_preact=False):
+    """fp32 eager statement of the kernel's math (oracle and CPU path)."""
+    A = a.float().t() if a_mn else a.float()          # [M, K]
+    B = b.float() if b_mn else b.float().t()          # [K, N]
+    v = alpha * (A @ B)
+    if bias is not None:
+        v = v + bias.float()
+    pre = v.to(torch.bfloat16) if want_preact else None
+    if act == ACT_GELU:
+        v = gelu_tanh_ref(v)
+    elif act == ACT_DGELU:
+        v = v * dgelu_tanh_ref(aux.float())
+    if add is not None:
+        v = v + add.float()
+    v = v.to(out_dtype)
+    return (v, pre) if want_preact else v
+
+
+def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=None, add=None, act=ACT_NONE,
+         aux=None, alpha=1.0, want_preact=False):
+    """See module docstring.  ``add`` may alias ``out`` (in-place accumulate, e.g. wgrad into main_grad)."""
+    if not a.is_cuda:
+        r = gemm_ref(a, b, a_mn, b_mn, out_dtype if out is None else out.dtype, bias, add, act, aux, alpha, want_preact)
+        if out is not None:
+            if want_preact:
+                out.copy_(r[0]); return out, r[1]
+            out.copy_(r); return out
+        return r
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=out_dtype)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    pre = torch.empty(M, N, device=a.device, dtype=torch.bfloat16) if want_preact else None
+    if add is not None:
+        assert add.shape == (M, N) and add.stride(1) == 1 and add.dtype in (torch.bfloat16, torch.float32)
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+    if act == ACT_DGELU:
+        assert aux is not None and aux.shape == (M, N) and aux.dtype == torch.bfloat16 and aux.stride(1) == 1
+    L = native.lib()
+    rc = L.neox_gemm_bf16(
+        native.ptr(a), native.ptr(b), native.ptr(out), M, N, K,
+        ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(out.stride(0)),
+        int(a_mn), int(b_mn), int(out.dtype == torch.float32),
+        native.ptr(bias), native.ptr(add), ctypes.c_longlong(add.stride(0) if add is not None else 0),
+        int(add is not None and add.dtype == torch.float32),
+        native.ptr(pre), ctypes.c_longlong(pre.stride(0) if pre is not None else 0),
+        native.ptr(aux), ctypes.c_longlong(aux.stride(0) if aux is not None else 0),
+        int(act), ctypes.c_float(alpha), ctypes.c_void_p(native.stream_ptr()))
+    native.check(rc, "neox_gemm_bf16")
+    return (out, pre) if want_preact else out
