@@ -381,7 +381,9 @@ class Field:
     def accepts(self, value) -> bool:
         if value is None or not self.types and not self.choices:
             return True
-        if self.choices and isinstance(value, str) and value in self.choices:
+        if self.choices and isinstance(value, str) and value.lower() in {c.lower() for c in self.choices}:
+            return True
+        if value == "auto":   # autotuning placeholder
             return True
         for t in self.types:
             if t is Any:

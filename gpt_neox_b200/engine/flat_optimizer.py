@@ -1,0 +1,297 @@
+"""Mixed-precision optimizer over contiguous flat buffers with ZeRO-1 style sharding.
+
+What DeepSpeed's ``BF16_Optimizer`` / ``FP16_Optimizer`` / ``DeepSpeedZeroOptimizer`` stage 1-2 provide
+to the reference (``megatron/training.py:1278-1288``, config block ``zero_optimization``), re-designed
+around three flat buffers per parameter bucket:
+
+* ``flat_param``  (model dtype)  -- every parameter is a *view* into it;
+* ``flat_grad``   (fp32)         -- every ``param.main_grad`` is a view into it; weight-gradient GEMMs
+  accumulate into it from their epilogue, other gradients are added by a post-accumulate hook;
+* per data-parallel rank a *shard* ``[lo, hi)`` of the bucket with fp32 master weights and the inner
+  optimizer's state (e.g. Adam ``m``/``v``).
+
+One step at a gradient-accumulation boundary:
+
+1. ``reduce``: ZeRO >= 1 reduce-scatters ``flat_grad`` over the data-parallel group so each rank owns the
+   summed gradient of its shard (stage 0 all-reduces);
+2. the global gradient norm is the root of (sum of squares of every shard), all-reduced over the DP,
+   TP and PP groups, counting tensor-parallel-replicated parameters once; it doubles as the fp16
+   overflow test;
+3. the inner optimizer updates the fp32 shard; un-scaling (loss scale, clip factor) is a scalar
+   multiplier consumed by the update kernel, and the fused Adam kernel also writes the model-dtype
+   copy straight into ``flat_param``;
+4. ZeRO >= 1 all-gathers ``flat_param`` in place.
+
+A bucket is keyed by (optimizer param group, communication group) so MoE expert parameters, which
+are data-parallel only over the expert-data-parallel group, live in their own bucket.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..parallel import mpu
+from .loss_scaler import DynamicLossScaler, StaticLossScaler
+
+_ALIGN = 128  # elements; keeps every shard boundary 256-byte aligned for bf16 and 512 for fp32
+
+
+def _pad_to(n, m):
+    return (n + m - 1) // m * m
+
+
+class Bucket:
+    """One contiguous (param, grad, master-shard) triple."""
+
+    def __init__(self, params, group_opts, comm_group, comm_world, comm_rank, model_dtype, device, sharded,
+                 grad_dtype=torch.float32):
+        # tensor-parallel-replicated parameters first: their squared norm is counted on TP rank 0 only
+        rep = [p for p in params if not getattr(p, "model_parallel", False)]
+        shd = [p for p in params if getattr(p, "model_parallel", False)]
+        self.params = rep + shd
+        self.opts = group_opts
+        self.comm_group, self.world, self.rank = comm_group, comm_world, comm_rank
+        self.sharded = sharded and comm_world > 1
+        offs, off = [], 0
+        for p in self.params:
+            offs.append(off)
+            off += _pad_to(p.numel(), 8)
+        self.rep_end = offs[len(rep)] if shd else off
+        if not shd:
+            self.rep_end = off
+        self.numel = off
+        self.padded = _pad_to(max(off, 1), _ALIGN * max(comm_world, 1))
+        self.offsets = offs
+        self.flat_param = torch.zeros(self.padded, dtype=model_dtype, device=device)
+        self.flat_grad = torch.zeros(self.padded, dtype=grad_dtype, device=device)
+        for p, o in zip(self.params, offs):
+            view = self.flat_param[o:o + p.numel()].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
+            p.grad_in_main = False
+        shard = self.padded // self.world if self.sharded else self.padded
+        self.lo = shard * self.rank if self.sharded else 0
+        self.hi = self.lo + shard
+        self.mixed = model_dtype != torch.float32
+        if self.mixed:
+            self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi].float().clone())
+        else:
+            self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi])   # a view: updated in place
+        self.master.model_out = self.flat_param[self.lo:self.hi] if self.mixed else None
+        self.grad_shard = self.flat_grad[self.lo:self.hi] if grad_dtype == torch.float32 else None
+
+    # ---- gradients
+    def reduce_grads(self, average_factor):
+        """Sum gradients over the communication group (and divide by ``average_factor``)."""
+        if self.world > 1:
+            if average_factor != 1.0:
+                self.flat_grad.div_(average_factor)
+            if self.sharded:
+                dist.reduce_scatter_tensor(self.flat_grad[self.lo:self.hi], self.flat_grad, group=self.comm_group)
+            else:
+                dist.all_reduce(self.flat_grad, group=self.comm_group)
+
+    def shard_sq_norm(self, tp_rank):
+        """Squared L2 norm of this rank's gradient shard, counting TP-replicated entries on TP rank 0 only."""
+        g = self.flat_grad[self.lo:self.hi]
+        rep_hi = min(max(self.rep_end, self.lo), self.hi) - self.lo
+        total = g.new_zeros((), dtype=torch.float32)
+        if rep_hi > 0 and tp_rank == 0:
+            total = total + g[:rep_hi].float().pow(2).sum()
+        if rep_hi < g.numel():
+            total = total + g[rep_hi:].float().pow(2).sum()
+        return total
+
+    def gather_params(self):
+        if self.sharded:
+            src = self.flat_param[self.lo:self.hi]
+            if not src.is_cuda:
+                src = src.clone()      # gloo does not define the aliased (in-place) form
+            dist.all_gather_into_tensor(self.flat_param, src, group=self.comm_group)
+
+    def zero_grad(self):
+        self.flat_grad.zero_()
+        for p in self.params:
+            p.grad = None
+            p.grad_in_main = False
+
+
+class FlatMixedPrecisionOptimizer:
+    """See module docstring.  ``inner_cls(param_groups, **defaults)`` is any element-wise
+    ``torch.optim.Optimizer`` (fused Adam, Lion, SGD, MADGRAD ...): it sees one flat fp32 parameter per
+    bucket whose ``.grad`` is the reduced gradient shard."""
+
+    def __init__(self, param_groups, inner_cls, inner_defaults, model_dtype, zero_stage=0, clip_grad=0.0,
+                 fp16_cfg=None, gradient_predivide_factor=1.0, prescale_gradients=False, device=None):
+        self.zero_stage = int(zero_stage or 0)
+        self.clip_grad = float(clip_grad or 0.0)
+        self.model_dtype = model_dtype
+        self.overflow = False
+        self.skipped_steps = 0
+        self._global_grad_norm = 0.0
+        self.buckets: list[Bucket] = []
+        dp_group, dp_world, dp_rank = mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(), \
+            mpu.get_data_parallel_rank()
+        inner_groups = []
+        for gi, grp in enumerate(param_groups):
+            params = [p for p in grp["params"] if p.requires_grad]
+            if not params:
+                continue
+            opts = {k: v for k, v in grp.items() if k != "params"}
+            dense = [p for p in params if not getattr(p, "expert_parallel", False)]
+            expert = [p for p in params if getattr(p, "expert_parallel", False)]
+            for plist, (cg, cw, cr) in ((dense, (dp_group, dp_world, dp_rank)),
+                                        (expert, (mpu.get_expert_data_parallel_group(),
+                                                  mpu.get_expert_data_parallel_world_size(),
+                                                  _rank_in(mpu.get_expert_data_parallel_group())))):
+                if not plist:
+                    continue
+                dev = device or plist[0].device
+                b = Bucket(plist, opts, cg, cw, cr, model_dtype, dev, sharded=self.zero_stage >= 1)
+                self.buckets.append(b)
+                inner_groups.append({"params": [b.master], **opts})
+        self.optimizer = inner_cls(inner_groups, **inner_defaults)
+        self.param_groups = self.optimizer.param_groups
+        self.dp_world = dp_world
+        if model_dtype == torch.float16:
+            cfg = fp16_cfg or {}
+            if cfg.get("loss_scale", 0) in (0, None):
+                self.loss_scaler = DynamicLossScaler(init_scale=2 ** cfg.get("initial_scale_power", 16),
+                                                     scale_window=cfg.get("loss_scale_window", 1000),
+                                                     min_scale=cfg.get("min_loss_scale", 1),
+                                                     hysteresis=cfg.get("hysteresis", 2))
+            else:
+                self.loss_scaler = StaticLossScaler(cfg["loss_scale"])
+        else:
+            self.loss_scaler = StaticLossScaler(1.0)
+        self._install_grad_hooks()
+
+    # ------------------------------------------------------------------ hooks
+    def _install_grad_hooks(self):
+        """Fold autograd-produced ``.grad`` tensors (biases, norms, embeddings ...) into ``main_grad``."""
+        def make(p):
+            def hook(param):
+                if param.grad is not None:
+                    param.main_grad.add_(param.grad.to(param.main_grad.dtype))
+                    param.grad = None
+            return hook
+        self._hooks = []
+        for b in self.buckets:
+            for p in b.params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(make(p)))
+
+    # ------------------------------------------------------------------ properties the training loop reads
+    @property
+    def cur_scale(self):
+        return self.loss_scaler.cur_scale
+
+    @property
+    def loss_scale(self):
+        return self.loss_scaler.cur_scale
+
+    def scale_loss(self, loss):
+        s = self.loss_scaler.cur_scale
+        return loss * s if s != 1.0 else loss
+
+    def zero_grad(self, set_to_none=True):
+        for b in self.buckets:
+            b.zero_grad()
+
+    # ------------------------------------------------------------------ the step
+    def global_grad_norm(self):
+        tp_rank = mpu.get_model_parallel_rank()
+        dev = self.buckets[0].flat_grad.device if self.buckets else torch.device("cpu")
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        for b in self.buckets:
+            sq = b.shard_sq_norm(tp_rank)
+            if b.world > 1 and not b.sharded:
+                pass  # replicated over DP: every rank already holds the full sum
+            total = total + sq
+            b._sq = sq
+        if dist.is_available() and dist.is_initialized():
+            # shards partition the bucket over DP; TP shards and PP stages partition the model
+            if any(b.sharded for b in self.buckets):
+                # sum over data-parallel ranks (expert buckets use a sub-group of it; summing their shards
+                # over the full DP group counts each expert shard exactly once as well)
+                dist.all_reduce(total, group=mpu.get_data_parallel_group())
+            if mpu.get_model_parallel_world_size() > 1:
+                dist.all_reduce(total, group=mpu.get_model_parallel_group())
+            if mpu.get_pipe_parallel_world_size() > 1:
+                dist.all_reduce(total, group=mpu.get_pipe_parallel_group())
+        return total.sqrt()
+
+    def step(self, grad_divisor=1.0):
+        """Reduce, check, clip, update, gather.  ``grad_divisor``: value the summed gradients must be
+        divided by in total (micro-batches x data-parallel size)."""
+        for b in self.buckets:
+            b.reduce_grads(1.0)
+        norm_t = self.global_grad_norm()
+        scale = self.loss_scaler.cur_scale * grad_divisor
+        norm = float(norm_t) / scale
+        self._global_grad_norm = norm
+        overflow = not math.isfinite(norm)
+        self.overflow = overflow
+        self.loss_scaler.update_scale(overflow)
+        if overflow:
+            self.skipped_steps += 1
+            self.zero_grad()
+            return False
+        combined = scale
+        if self.clip_grad > 0.0:
+            clip = norm / self.clip_grad
+            if clip > 1.0:
+                combined = scale * clip
+        inv = 1.0 / combined
+        for b, g in zip(self.buckets, self.optimizer.param_groups):
+            b.master.grad = b.flat_grad[b.lo:b.hi]
+            g["grad_scale"] = inv
+        if getattr(self.optimizer, "supports_grad_scale", False):
+            self.optimizer.step()
+        else:
+            if inv != 1.0:
+                for b in self.buckets:
+                    b.master.grad.mul_(inv)
+            self.optimizer.step()
+        for b in self.buckets:
+            if b.mixed and not getattr(self.optimizer, "writes_model_out", False):
+                b.flat_param[b.lo:b.hi].copy_(b.master.data)
+            b.master.grad = None
+            b.gather_params()
+        self.zero_grad()
+        return True
+
+    # ------------------------------------------------------------------ checkpointing
+    def state_dict(self):
+        return {
+            "loss_scaler": self.loss_scaler.state_dict(),
+            "skipped_steps": self.skipped_steps,
+            "zero_stage": self.zero_stage,
+            "partition_count": [b.world if b.sharded else 1 for b in self.buckets],
+            "optimizer_state_dict": self.optimizer.state_dict(),
+            "single_partition_of_fp32_groups": [b.master.data.detach().clone().cpu() for b in self.buckets],
+            "bucket_numel": [b.numel for b in self.buckets],
+        }
+
+    def load_state_dict(self, sd, load_optimizer_states=True):
+        self.loss_scaler.load_state_dict(sd.get("loss_scaler", {}))
+        self.skipped_steps = sd.get("skipped_steps", 0)
+        if load_optimizer_states and "optimizer_state_dict" in sd:
+            self.optimizer.load_state_dict(sd["optimizer_state_dict"])
+        for b, m in zip(self.buckets, sd.get("single_partition_of_fp32_groups", [])):
+            if m.numel() == b.master.numel():
+                b.master.data.copy_(m.to(b.master.device))
+
+    def refresh_master_from_params(self):
+        """After loading module weights: re-derive the fp32 master shards from ``flat_param``."""
+        for b in self.buckets:
+            if b.mixed:
+                b.master.data.copy_(b.flat_param[b.lo:b.hi].float())
+
+
+def _rank_in(group):
+    if group is None or not (dist.is_available() and dist.is_initialized()):
+        return 0
+    return dist.get_rank(group)

@@ -1,0 +1,121 @@
+"""Fused multi-head attention (flash attention) front-end.
+
+``flash_attention(q, k, v)`` takes the ``[s, b, heads, d]`` views the transformer layer slices out of
+the fused QKV projection -- without making them contiguous -- and returns ``[sq, b, heads, d]``.
+Supported: causal masking (bottom-right aligned when ``sq < sk``, as needed for kv-cache decoding),
+sliding windows, ALiBi slopes, grouped-query attention (``heads_q % heads_kv == 0``), head sizes
+64 / 96 / 128 on the sm_100a kernel (``csrc/flash_attn_sm100.cu``: QK^T and PV on tcgen05 with S and
+O accumulators in tensor memory).  Reference: the flash-attn 2 calls in
+``megatron/model/transformer.py:627-744``.
+
+``attention_ref`` is the fp32 statement of the same math (CPU path and test oracle).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import native
+from .functional import _DT, _s
+
+
+def attention_ref(q, k, v, causal=True, softmax_scale=None, window=None, alibi_slopes=None, bias=None,
+                  return_lse=False):
+    sq, b, hq, d = q.shape
+    sk, _, hkv, _ = k.shape
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    qf = q.float().permute(1, 2, 0, 3)                       # [b, hq, sq, d]
+    kf = k.float().permute(1, 2, 0, 3)
+    vf = v.float().permute(1, 2, 0, 3)
+    if hkv != hq:
+        rep = hq // hkv
+        kf = kf.repeat_interleave(rep, dim=1)
+        vf = vf.repeat_interleave(rep, dim=1)
+    scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale  # [b, hq, sq, sk]
+    qi = torch.arange(sq, device=q.device)[:, None] + (sk - sq)
+    ki = torch.arange(sk, device=q.device)[None, :]
+    if alibi_slopes is not None:
+        scores = scores + (-(qi - ki).abs().float())[None, None] * alibi_slopes.float().view(1, -1, 1, 1)
+    if bias is not None:
+        scores = scores + bias.float()
+    mask = torch.zeros(sq, sk, dtype=torch.bool, device=q.device)
+    if causal:
+        mask |= ki > qi
+    if window is not None:
+        mask |= ki < qi - window
+    scores = scores.masked_fill(mask[None, None], float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    p = torch.softmax(scores, dim=-1)
+    out = torch.matmul(p, vf).permute(2, 0, 1, 3).contiguous().to(q.dtype)
+    return (out, lse) if return_lse else out
+
+
+def kernel_ok(q, k, v, bias=None) -> bool:
+    return (q.is_cuda and native.available() and q.dtype == torch.bfloat16 and bias is None
+            and q.shape[-1] in (64, 96, 128) and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+            and q.shape[0] >= 1)
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale, window, slopes):
+        sq, b, hq, d = q.shape
+        sk, _, hkv, _ = k.shape
+        out = torch.empty(sq, b, hq, d, dtype=q.dtype, device=q.device)
+        lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
+        L = native.lib()
+        ll = ctypes.c_longlong
+        rc = L.neox_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse),
+                              sq, sk, b, hq, hkv, d,
+                              ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
+                              ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+                              ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)),
+                              ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
+                              native.ptr(slopes), _s())
+        native.check(rc, "neox_flash_fwd")
+        ctx.save_for_backward(q, k, v, out, lse, slopes if slopes is not None else torch.empty(0, device=q.device))
+        ctx.cfg = (causal, scale, window, slopes is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse, slopes = ctx.saved_tensors
+        causal, scale, window, has_slopes = ctx.cfg
+        sq, b, hq, d = q.shape
+        sk, _, hkv, _ = k.shape
+        do = do.contiguous()
+        dq = torch.empty(sq, b, hq, d, dtype=q.dtype, device=q.device)
+        dk = torch.empty(sk, b, hkv, d, dtype=q.dtype, device=q.device)
+        dv = torch.empty(sk, b, hkv, d, dtype=q.dtype, device=q.device)
+        L = native.lib()
+        ll = ctypes.c_longlong
+        rc = L.neox_flash_bwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(do),
+                              native.ptr(lse), native.ptr(dq), native.ptr(dk), native.ptr(dv),
+                              sq, sk, b, hq, hkv, d,
+                              ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
+                              ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+                              ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)),
+                              ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
+                              native.ptr(slopes) if has_slopes else None, _s())
+        native.check(rc, "neox_flash_bwd")
+        return dq, dk, dv, None, None, None, None
+
+
+_FLASH_IMPL = {"fwd": None}
+
+
+def have_flash_kernel() -> bool:
+    if _FLASH_IMPL["fwd"] is None:
+        _FLASH_IMPL["fwd"] = hasattr(native.lib(), "neox_flash_fwd") if native.available() else False
+    return _FLASH_IMPL["fwd"]
+
+
+def flash_attention(q, k, v, causal=True, softmax_scale=None, window=None, alibi_slopes=None, bias=None):
+    d = q.shape[-1]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    if kernel_ok(q, k, v, bias) and have_flash_kernel():
+        slopes = alibi_slopes.float().contiguous() if alibi_slopes is not None else None
+        return _FlashFn.apply(q, k, v, causal, scale, window, slopes)
+    return attention_ref(q, k, v, causal, scale, window, alibi_slopes, bias)

@@ -1,0 +1,428 @@
+"""Fused element-wise, normalisation, softmax, rotary and loss operators.
+
+Every operator has two bodies that compute the same math:
+
+* ``*_ref``  -- plain PyTorch (fp32 internally).  It is the CPU path and the oracle of the GPU tests.
+* the CUDA kernel in ``csrc/`` reached through ctypes, used whenever the input lives on a GPU and
+  has a supported dtype.  There is no silent fallback on a GPU for supported dtypes: if the library
+  cannot be loaded the call raises.
+
+Reference call sites these replace: apex/TorchScript fused ops in ``megatron/model/fused_layer_norm.py``,
+``norms.py``, ``activations.py:78-112``, ``fused_bias_dropout.py:28-55``, ``fused_softmax.py:24-205``,
+``fused_rope.py`` and ``megatron/mpu/cross_entropy.py:27-117``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+
+_DT = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
+
+
+def _k(*ts) -> bool:
+    """Kernel path usable for these tensors?"""
+    t0 = ts[0]
+    return t0.is_cuda and native.available() and t0.dtype in _DT
+
+
+def _s():
+    return ctypes.c_void_p(native.stream_ptr())
+
+
+_workspaces = {}
+
+
+def workspace(nbytes: int, device, tag="ws") -> torch.Tensor:
+    """A cached per-device scratch buffer of at least ``nbytes`` (grown geometrically, never shrunk)."""
+    key = (device, tag)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+# ------------------------------------------------------------------------------------ LayerNorm
+def layer_norm_ref(x, weight, bias, eps):
+    xf = x.float()
+    mean = xf.mean(-1, keepdim=True)
+    var = xf.var(-1, unbiased=False, keepdim=True)
+    y = (xf - mean) * torch.rsqrt(var + eps)
+    if weight is not None:
+        y = y * weight.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        cols = x.shape[-1]
+        x2 = x.reshape(-1, cols)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rc = native.lib().neox_layernorm_fwd(native.ptr(x2), native.ptr(weight), native.ptr(bias), native.ptr(y),
+                                             native.ptr(mean), native.ptr(rstd), rows, cols, ctypes.c_float(eps),
+                                             _DT[x.dtype], _s())
+        native.check(rc, "neox_layernorm_fwd")
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.has_bias = bias is not None
+        ctx.shape = x.shape
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, weight, mean, rstd = ctx.saved_tensors
+        rows, cols = x2.shape
+        g2 = g.reshape(rows, cols)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        dx = torch.empty_like(x2)
+        nblk = int(native.lib().neox_norm_bwd_blocks(rows))
+        ws = workspace(2 * nblk * cols * 4, x2.device, "ln_bwd")
+        dgamma = torch.empty(cols, dtype=torch.float32, device=x2.device)
+        dbeta = torch.empty(cols, dtype=torch.float32, device=x2.device)
+        rc = native.lib().neox_layernorm_bwd(native.ptr(g2), native.ptr(x2), native.ptr(weight), native.ptr(mean),
+                                             native.ptr(rstd), native.ptr(dx), native.ptr(dgamma), native.ptr(dbeta),
+                                             native.ptr(ws), rows, cols, _DT[x2.dtype], _s())
+        native.check(rc, "neox_layernorm_bwd")
+        return (dx.reshape(ctx.shape), dgamma.to(weight.dtype), dbeta.to(weight.dtype) if ctx.has_bias else None,
+                None)
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    if _k(x) and weight is not None and weight.dtype == x.dtype and x.shape[-1] % 8 == 0:
+        return _LayerNormFn.apply(x, weight, bias, eps)
+    return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+# ------------------------------------------------------------------------------------ RMSNorm
+def rms_norm_ref(x, scale, bias, eps):
+    """``x / (||x||_2 * d^-1/2 + eps) * scale (+ bias)``: eps is added to the RMS, not under the root
+    (reference ``megatron/model/norms.py:81-96``)."""
+    xf = x.float()
+    rms = xf.norm(2, dim=-1, keepdim=True) * (x.shape[-1] ** -0.5)
+    y = xf / (rms + eps) * scale.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, bias, eps):
+        cols = x.shape[-1]
+        x2 = x.reshape(-1, cols)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rinv = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rc = native.lib().neox_rmsnorm_fwd(native.ptr(x2), native.ptr(scale), native.ptr(bias), native.ptr(y),
+                                           native.ptr(rinv), rows, cols, ctypes.c_float(eps), _DT[x.dtype], _s())
+        native.check(rc, "neox_rmsnorm_fwd")
+        ctx.save_for_backward(x2, scale, rinv)
+        ctx.has_bias = bias is not None
+        ctx.eps = eps
+        ctx.shape = x.shape
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, scale, rinv = ctx.saved_tensors
+        rows, cols = x2.shape
+        g2 = g.reshape(rows, cols)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        dx = torch.empty_like(x2)
+        nblk = int(native.lib().neox_norm_bwd_blocks(rows))
+        ws = workspace(2 * nblk * cols * 4, x2.device, "ln_bwd")
+        dscale = torch.empty(cols, dtype=torch.float32, device=x2.device)
+        dbias = torch.empty(cols, dtype=torch.float32, device=x2.device)
+        rc = native.lib().neox_rmsnorm_bwd(native.ptr(g2), native.ptr(x2), native.ptr(scale), native.ptr(rinv),
+                                           native.ptr(dx), native.ptr(dscale), native.ptr(dbias), native.ptr(ws),
+                                           rows, cols, ctypes.c_float(ctx.eps), _DT[x2.dtype], _s())
+        native.check(rc, "neox_rmsnorm_bwd")
+        return dx.reshape(ctx.shape), dscale.to(scale.dtype), dbias.to(scale.dtype) if ctx.has_bias else None, None
+
+
+def rms_norm(x, scale, bias=None, eps=1e-8):
+    if _k(x) and scale.dtype == x.dtype and x.shape[-1] % 8 == 0:
+        return _RMSNormFn.apply(x, scale, bias, eps)
+    return rms_norm_ref(x, scale, bias, eps)
+
+
+# ------------------------------------------------------------------------------------ activations
+def gelu_ref(x):
+    return F.gelu(x.float(), approximate="tanh").to(x.dtype)
+
+
+def _dgelu(xf):
+    k0, k1 = 0.7978845608028654, 0.044715
+    t = torch.tanh(k0 * xf * (1 + k1 * xf * xf))
+    return 0.5 * xf * ((1 - t * t) * (k0 + 3 * k0 * k1 * xf * xf)) + 0.5 * (1 + t)
+
+
+def dgelu_mul(g, pre):
+    """``g * gelu'(pre)`` (tanh approximation)."""
+    if _k(g) and g.dtype == pre.dtype and g.is_contiguous() and pre.is_contiguous():
+        out = torch.empty_like(g)
+        rc = native.lib().neox_dgelu_mul(native.ptr(g), native.ptr(pre), native.ptr(out),
+                                         ctypes.c_longlong(g.numel()), _DT[g.dtype], _s())
+        native.check(rc, "neox_dgelu_mul")
+        return out
+    return (g.float() * _dgelu(pre.float())).to(g.dtype)
+
+
+class _BiasGeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias):
+        x2 = x.contiguous()
+        out = torch.empty_like(x2)
+        cols = x.shape[-1]
+        rc = native.lib().neox_bias_gelu_fwd(native.ptr(x2), native.ptr(bias), native.ptr(out),
+                                             ctypes.c_longlong(x2.numel() // cols), cols, _DT[x.dtype], _s())
+        native.check(rc, "neox_bias_gelu_fwd")
+        ctx.save_for_backward(x2, bias)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, bias = ctx.saved_tensors
+        cols = x2.shape[-1]
+        g2 = g.contiguous()
+        dx = torch.empty_like(x2)
+        rc = native.lib().neox_bias_gelu_bwd(native.ptr(g2), native.ptr(x2), native.ptr(bias), native.ptr(dx),
+                                             ctypes.c_longlong(x2.numel() // cols), cols, _DT[x2.dtype], _s())
+        native.check(rc, "neox_bias_gelu_bwd")
+        db = dx.reshape(-1, cols).sum(0) if bias is not None else None
+        return dx, db
+
+
+def bias_gelu(x, bias=None):
+    """``gelu(x + bias)`` with the tanh approximation (reference ``activations.py:78-112``)."""
+    if _k(x) and x.shape[-1] % 8 == 0 and (bias is None or bias.dtype == x.dtype):
+        return _BiasGeluFn.apply(x, bias)
+    y = x if bias is None else x + bias
+    return F.gelu(y, approximate="tanh")
+
+
+_GATED = {"geglu": 0, "swiglu": 1, "reglu": 2, "bilinear": 3, "glu": 4}
+
+
+def _gate_fn(kind, gate):
+    return {"geglu": lambda t: F.gelu(t, approximate="tanh"), "swiglu": F.silu, "reglu": F.relu,
+            "bilinear": lambda t: t, "glu": torch.sigmoid}[kind](gate)
+
+
+def gated_act_ref(x, kind, bias=None):
+    """``x, gate = chunk(2); out = act(gate) * x`` (reference ``transformer.py:190-206``)."""
+    if bias is not None:
+        x = x + bias
+    a, gate = x.float().chunk(2, dim=-1)
+    return (_gate_fn(kind, gate) * a).to(x.dtype)
+
+
+class _GatedActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, kind):
+        x2 = x.contiguous()
+        cols = x.shape[-1] // 2
+        rows = x2.numel() // (2 * cols)
+        out = torch.empty(*x.shape[:-1], cols, dtype=x.dtype, device=x.device)
+        rc = native.lib().neox_gated_act_fwd(native.ptr(x2), native.ptr(out), ctypes.c_longlong(rows), cols,
+                                             _GATED[kind], _DT[x.dtype], _s())
+        native.check(rc, "neox_gated_act_fwd")
+        ctx.save_for_backward(x2)
+        ctx.kind = kind
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (x2,) = ctx.saved_tensors
+        cols = x2.shape[-1] // 2
+        rows = x2.numel() // (2 * cols)
+        g2 = g.contiguous()
+        dx = torch.empty_like(x2)
+        rc = native.lib().neox_gated_act_bwd(native.ptr(g2), native.ptr(x2), native.ptr(dx), ctypes.c_longlong(rows),
+                                             cols, _GATED[ctx.kind], _DT[x2.dtype], _s())
+        native.check(rc, "neox_gated_act_bwd")
+        return dx, None
+
+
+def gated_act(x, kind, bias=None):
+    if bias is not None:
+        x = x + bias
+    if _k(x) and (x.shape[-1] // 2) % 8 == 0:
+        return _GatedActFn.apply(x, kind)
+    return gated_act_ref(x, kind)
+
+
+def get_activation(name):
+    """Non-gated activations by config name (reference ``activations.py:27-66``)."""
+    table = {
+        "gelu": lambda x: F.gelu(x, approximate="tanh"),
+        "relu": F.relu,
+        "softsign": F.softsign,
+        "swish": F.silu,
+        "silu": F.silu,
+        "mish": F.mish,
+    }
+    if name not in table:
+        raise ValueError(f"Activation function {name} not recognized")
+    return table[name]
+
+
+# ------------------------------------------------------------------------------------ bias + dropout + add
+def bias_dropout_add(x, bias, residual, prob, training):
+    """``residual + dropout(x + bias)`` (reference ``fused_bias_dropout.py:28-55``)."""
+    if prob == 0.0 or not training:
+        if _k(x) and x.is_contiguous() and residual.is_contiguous() and x.dtype == residual.dtype \
+                and not (torch.is_grad_enabled() and (x.requires_grad or residual.requires_grad)) \
+                and x.shape[-1] % 8 == 0 and (bias is None or bias.dtype == x.dtype):
+            out = torch.empty_like(x)
+            cols = x.shape[-1]
+            rc = native.lib().neox_bias_residual_add(native.ptr(x), native.ptr(bias), native.ptr(residual),
+                                                     native.ptr(out), ctypes.c_longlong(x.numel() // cols), cols,
+                                                     _DT[x.dtype], _s())
+            native.check(rc, "neox_bias_residual_add")
+            return out
+        if bias is not None:
+            x = x + bias
+        return residual + x
+    if bias is not None:
+        x = x + bias
+    return residual + F.dropout(x, p=prob, training=training)
+
+
+# ------------------------------------------------------------------------------------ softmax
+def scaled_masked_softmax_ref(x, mask, scale, fill=-10000.0):
+    """softmax(mask ? fill : x*scale) over the last dim; ``mask`` is True/1 where attention is NOT allowed."""
+    xf = x.float() * scale
+    if mask is not None:
+        xf = xf.masked_fill(mask.bool(), fill)
+    return torch.softmax(xf, dim=-1).to(x.dtype)
+
+
+def scaled_causal_softmax_ref(x, scale):
+    """Causal softmax over square [..., s, s] scores; entries above the diagonal are exactly 0."""
+    s = x.shape[-1]
+    xf = x.float() * scale
+    m = torch.ones(s, s, dtype=torch.bool, device=x.device).triu(1)
+    xf = xf.masked_fill(m, float("-inf"))
+    return torch.softmax(xf, dim=-1).to(x.dtype)
+
+
+class _SoftmaxFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mask, scale, causal):
+        x2 = x.contiguous()
+        sk = x.shape[-1]
+        sq = x.shape[-2]
+        rows = x2.numel() // sk
+        y = torch.empty_like(x2)
+        mask_rows_mod = 0
+        mptr = None
+        if mask is not None:
+            m = mask.to(torch.uint8).contiguous()
+            # mask is [b or 1, 1, sq, sk]; heads share it
+            assert m.dim() == 4 and m.shape[1] == 1 and m.shape[-1] == sk and m.shape[-2] == sq
+            ctx.mask_keep = m
+            mptr = native.ptr(m)
+            mask_rows_mod = m.shape[0]
+        heads = x.shape[1] if x.dim() == 4 else 1
+        rc = native.lib().neox_softmax_fwd(native.ptr(x2), mptr, native.ptr(y), ctypes.c_longlong(rows), sq, sk,
+                                           heads, mask_rows_mod, ctypes.c_float(scale), int(causal), _DT[x.dtype],
+                                           _s())
+        native.check(rc, "neox_softmax_fwd")
+        ctx.save_for_backward(y)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        g2 = g.contiguous()
+        sk = y.shape[-1]
+        dx = torch.empty_like(y)
+        rc = native.lib().neox_softmax_bwd(native.ptr(g2), native.ptr(y), native.ptr(dx),
+                                           ctypes.c_longlong(y.numel() // sk), sk, ctypes.c_float(ctx.scale),
+                                           _DT[y.dtype], _s())
+        native.check(rc, "neox_softmax_bwd")
+        return dx, None, None, None
+
+
+def scaled_masked_softmax(x, mask, scale):
+    """x: [b, np, sq, sk]; mask: [b|1, 1, sq, sk] (nonzero = masked).  Any sk (reference kernel: sk <= 2048)."""
+    if _k(x):
+        return _SoftmaxFn.apply(x, mask, scale, False)
+    return scaled_masked_softmax_ref(x, mask, scale)
+
+
+def scaled_upper_triang_masked_softmax(x, scale):
+    """x: [attn_batches, s, s] causal softmax."""
+    if _k(x):
+        return _SoftmaxFn.apply(x, None, scale, True)
+    return scaled_causal_softmax_ref(x, scale)
+
+
+# ------------------------------------------------------------------------------------ rotary
+def rotate_half(x):
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def rope_ref(x, cos, sin):
+    """x: [s, b, h, d]; cos/sin: [s, 1, 1, rot]; rotates the first ``rot`` dims of every head."""
+    rot = cos.shape[-1]
+    xr, xp = x[..., :rot], x[..., rot:]
+    xr = (xr.float() * cos.float() + rotate_half(xr.float()) * sin.float()).to(x.dtype)
+    return torch.cat((xr, xp), dim=-1) if xp.shape[-1] else xr
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, inverse):
+        s, b, h, d = x.shape
+        rot = cos.shape[-1]
+        xs = x if x.stride(-1) == 1 else x.contiguous()
+        out = torch.empty((s, b, h, d), dtype=x.dtype, device=x.device)
+        c = cos.reshape(-1, rot)[:s].float().contiguous()
+        sn = sin.reshape(-1, rot)[:s].float().contiguous()
+        rc = native.lib().neox_rope(native.ptr(xs), native.ptr(out), native.ptr(c), native.ptr(sn), s, b, h, d, rot,
+                                    ctypes.c_longlong(xs.stride(0)), ctypes.c_longlong(xs.stride(1)),
+                                    ctypes.c_longlong(xs.stride(2)), int(inverse), _DT[x.dtype], _s())
+        native.check(rc, "neox_rope")
+        ctx.save_for_backward(c, sn)
+        ctx.inverse = inverse
+        ctx.rot = rot
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        c, sn = ctx.saved_tensors
+        return _RopeFn.apply(g, c.reshape(-1, 1, 1, ctx.rot), sn.reshape(-1, 1, 1, ctx.rot), not ctx.inverse), None, None, None
+
+
+def rope(x, cos, sin):
+    """Apply (partial) rotary position embedding to [s, b, h, d]; strided inputs are read in place."""
+    if _k(x):
+        return _RopeFn.apply(x, cos, sin, False)
+    return rope_ref(x, cos, sin)
+
+
+# ------------------------------------------------------------------------------------ cross entropy
+def cross_entropy_ref(logits, target):
+    """Per-token CE on fp32-cast logits: [..., V], [...] -> [...]."""
+    return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), target.reshape(-1),
+                           reduction="none").reshape(target.shape)

@@ -1,0 +1,98 @@
+"""Linear layer autograd function on top of the tcgen05 GEMM.
+
+forward   ``y = act(x W^T + b) (+ residual)``           -> one GEMM, bias / GeLU / residual in the epilogue
+backward  ``dx = dy W``  and  ``dW = dy^T x``           -> two GEMMs reading the *same* row-major tensors
+                                                          (MN-major operand descriptors, no transposes)
+
+When the weight carries a ``main_grad`` attribute (an fp32 view into the engine's contiguous gradient
+buffer) the weight-gradient GEMM accumulates straight into it from its epilogue and autograd sees no
+``.grad`` for that parameter; this replaces both the separate accumulation kernel and the
+bf16 -> fp32 copy of a DeepSpeed-style bf16 optimizer.
+
+On CPU, or for dtypes the kernel does not take, the same math runs through ``torch`` ops.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import gemm as G
+from . import native
+
+
+def kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.is_cuda and native.available() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous())
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, act):
+        ctx.act = act
+        ctx.x_shape = x.shape
+        N, K = weight.shape
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        res2 = residual.reshape(-1, N) if residual is not None else None
+        need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
+        use_k = kernel_ok(x2, weight) and (bias is None or bias.dtype == torch.bfloat16)
+        ctx.use_k = use_k
+        pre = None
+        if use_k:
+            r = G.gemm(x2, weight, bias=bias, add=res2, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE,
+                       want_preact=need_pre)
+            out, pre = r if need_pre else (r, None)
+        else:
+            out = F.linear(x2, weight, bias)
+            if act == "gelu":
+                pre = out if need_pre else None
+                out = F.gelu(out, approximate="tanh")
+            if res2 is not None:
+                out = out + res2
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.save_for_backward(x2, weight, pre)
+        return out.reshape(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, weight, pre = ctx.saved_tensors
+        N, K = weight.shape
+        g_in = g
+        g2 = g.reshape(-1, N)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        g_res = g_in if ctx.has_res else None
+        if ctx.act == "gelu":
+            from .functional import dgelu_mul
+            g2 = dgelu_mul(g2, pre)
+        gx = gw = gb = None
+        if ctx.use_k and g2.dtype == torch.bfloat16:
+            if ctx.needs_input_grad[0]:
+                gx = G.gemm(g2, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
+            if ctx.needs_input_grad[1]:
+                mg = getattr(weight, "main_grad", None)
+                if mg is not None:
+                    G.gemm(g2, x2, a_mn=True, b_mn=True, out=mg, add=mg)
+                    weight.grad_in_main = True
+                else:
+                    gw = G.gemm(g2, x2, a_mn=True, b_mn=True)
+        else:
+            if ctx.needs_input_grad[0]:
+                gx = (g2 @ weight).reshape(ctx.x_shape)
+            if ctx.needs_input_grad[1]:
+                gw = g2.t() @ x2
+                mg = getattr(weight, "main_grad", None)
+                if mg is not None:
+                    mg.add_(gw)
+                    weight.grad_in_main = True
+                    gw = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g2.sum(0)
+        return gx, gw, gb, g_res, None
+
+
+def linear(x, weight, bias=None, residual=None, act=None):
+    """``act(x @ weight.T + bias) + residual`` with the epilogue fused into the GEMM."""
+    return _LinearFn.apply(x, weight, bias, residual, act)

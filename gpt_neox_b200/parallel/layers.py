@@ -1,0 +1,241 @@
+"""Tensor-parallel layers: vocabulary-sharded embedding, column- and row-sharded linears and a
+head-sharded T5 relative position bias (API of ``megatron/mpu/layers.py:98-794``).
+
+Sharding rules:
+
+* ``ColumnParallelLinear``  W is ``[out/tp, in]``; with sequence parallelism the input arrives sharded
+  along ``seq_dim`` and is all-gathered before the GEMM, otherwise it is an identity whose backward
+  all-reduces.  ``gather_output`` all-gathers the last dim.  ``skip_bias_add`` returns the bias to the
+  caller so it can be fused into the next op.
+* ``RowParallelLinear``  W is ``[out, in/tp]``; the partial products are reduce-scattered (sequence
+  parallel) or all-reduced, unless ``parallel_output`` defers the reduction to the caller (GPT-J
+  residual sums attention and MLP partials first).
+
+The GEMMs run through ``ops.linear`` (tcgen05 kernel, fused epilogue).  When the fused peer-memory
+collectives are enabled (``parallel/fused_comm.py``) the all-gather / reduce-scatter around the
+GEMM is replaced by the fused kernel.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.nn import init
+from torch.nn.parameter import Parameter
+
+from ..ops.linear import linear as fused_linear
+from . import mappings as M
+from . import mpu
+from .rng import get_cuda_rng_tracker
+
+
+def _device(neox_args=None):
+    if torch.cuda.is_available() and not (neox_args is not None and getattr(neox_args, "use_cpu_initialization", False)
+                                          and False):
+        return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cpu")
+
+
+def _mark(weight, partition_dim, stride=1):
+    weight.model_parallel = True
+    weight.partition_dim = partition_dim
+    weight.partition_stride = stride
+
+
+def init_sharded_weight(neox_args, weight, full_rows, full_cols, partition_dim, init_method, stride=1):
+    """Initialise a sharded weight.
+
+    Device path: draw under the tensor-parallel RNG stream so every shard differs.  Host path
+    (``use_cpu_initialization``): draw the full fp32 matrix with the default stream (identical on all
+    ranks) and keep this rank's slice, which makes the result independent of the TP degree.
+    """
+    _mark(weight, partition_dim, stride)
+    if getattr(neox_args, "use_cpu_initialization", False):
+        master = torch.empty(full_rows, full_cols, dtype=torch.float)
+        init_method(master)
+        tp, r = mpu.get_model_parallel_world_size(), mpu.get_model_parallel_rank()
+        per = weight.shape[partition_dim] // stride
+        pieces = torch.split(master, per, dim=partition_dim)[r::tp]
+        with torch.no_grad():
+            weight.copy_(torch.cat(pieces, dim=partition_dim).to(weight.dtype))
+        return
+    with get_cuda_rng_tracker().fork():
+        if weight.dtype in (torch.bfloat16, torch.float16) and not weight.is_cuda:
+            tmp = torch.empty(weight.shape, dtype=torch.float)
+            init_method(tmp)
+            with torch.no_grad():
+                weight.copy_(tmp.to(weight.dtype))
+        else:
+            init_method(weight)
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Embedding sharded along the vocabulary; out-of-range ids contribute zeros, then all-reduce."""
+
+    def __init__(self, neox_args, num_embeddings, embedding_dim, init_method=init.xavier_normal_):
+        super().__init__()
+        self.num_embeddings = num_embeddings
+        self.embedding_dim = embedding_dim
+        self.model_parallel_size = mpu.get_model_parallel_world_size()
+        self.vocab_start_index, self.vocab_end_index = mpu.VocabUtility.vocab_range_from_global_vocab_size(
+            num_embeddings, mpu.get_model_parallel_rank(), self.model_parallel_size)
+        self.num_embeddings_per_partition = self.vocab_end_index - self.vocab_start_index
+        self.init_method = init_method
+        self.weight = Parameter(torch.empty(self.num_embeddings_per_partition, embedding_dim, device=_device(neox_args),
+                                            dtype=neox_args.params_dtype))
+        init_sharded_weight(neox_args, self.weight, num_embeddings, embedding_dim, 0, init_method)
+
+    def forward(self, input_):
+        if self.model_parallel_size > 1:
+            mask = (input_ < self.vocab_start_index) | (input_ >= self.vocab_end_index)
+            local = (input_ - self.vocab_start_index).masked_fill(mask, 0)
+        else:
+            mask, local = None, input_
+        out = F.embedding(local, self.weight)
+        if mask is not None:
+            out = out.masked_fill(mask.unsqueeze(-1), 0.0)
+        return M.reduce_from_model_parallel_region(out)
+
+
+class ParallelRelativePositionBias(nn.Module):
+    """T5 bucketed relative position bias with heads sharded over tensor-parallel ranks."""
+
+    def __init__(self, neox_args, scale, causal=True, num_buckets=32, max_distance=128, heads=8,
+                 init_method=init.xavier_normal_):
+        super().__init__()
+        self.scale, self.causal, self.num_buckets, self.max_distance, self.heads = scale, causal, num_buckets, \
+            max_distance, heads
+        tp, r = mpu.get_model_parallel_world_size(), mpu.get_model_parallel_rank()
+        self.num_heads_per_partition = mpu.divide(heads, tp)
+        self.head_start_index = r * self.num_heads_per_partition
+        self.head_end_index = self.head_start_index + self.num_heads_per_partition
+        self.weight = Parameter(torch.empty(num_buckets, self.num_heads_per_partition, device=_device(neox_args),
+                                            dtype=neox_args.params_dtype))
+        init_sharded_weight(neox_args, self.weight, num_buckets, heads, 1, init_method)
+        self._cache = None
+
+    def _bucket(self, rel):
+        nb = self.num_buckets
+        ret = torch.zeros_like(rel)
+        n = -rel
+        if not self.causal:
+            nb //= 2
+            ret = ret + (n < 0).long() * nb
+            n = n.abs()
+        else:
+            n = n.clamp(min=0)
+        max_exact = nb // 2
+        small = n < max_exact
+        large = max_exact + (torch.log(n.float().clamp(min=1) / max_exact) / math.log(self.max_distance / max_exact)
+                             * (nb - max_exact)).long()
+        large = large.clamp(max=nb - 1)
+        return ret + torch.where(small, n, large)
+
+    def forward(self, q_len, k_len):
+        if self._cache is None or self._cache[0] != (q_len, k_len) or self._cache[1].device != self.weight.device:
+            q = torch.arange(q_len, dtype=torch.long, device=self.weight.device)
+            k = torch.arange(k_len, dtype=torch.long, device=self.weight.device)
+            self._cache = ((q_len, k_len), self._bucket(k[None, :] - q[:, None]))
+        values = F.embedding(self._cache[1], self.weight)        # [q, k, heads/tp]
+        return values.movedim(2, 0).unsqueeze(0) * self.scale     # [1, heads/tp, q, k]
+
+
+class ColumnParallelLinear(nn.Module):
+    """``Y = X A + b`` with ``A`` split along its output (column) dimension."""
+
+    def __init__(self, neox_args, input_size, output_size, bias=True, gather_output=True,
+                 init_method=init.xavier_normal_, stride=1, keep_master_weight_for_test=False, skip_bias_add=False,
+                 MOE=False, MoE_mp_size=1, mup_rescale_parameters=False, seq_dim=0):
+        super().__init__()
+        self.input_size, self.output_size, self.gather_output = input_size, output_size, gather_output
+        world = MoE_mp_size if MOE else mpu.get_model_parallel_world_size()
+        self.tp = world
+        self.output_size_per_partition = mpu.divide(output_size, world)
+        self.skip_bias_add = skip_bias_add
+        self.sequence_parallel = bool(getattr(neox_args, "sequence_parallel", False)) and world > 1
+        self.seq_dim = seq_dim
+        self.init_method, self.stride = init_method, stride
+        self.mup_rescale_parameters = mup_rescale_parameters
+        self.use_mup = getattr(neox_args, "use_mup", False)
+        self.width_mult_val = 1.0
+        dev = _device(neox_args)
+        self.weight = Parameter(torch.empty(self.output_size_per_partition, input_size, device=dev,
+                                            dtype=neox_args.params_dtype))
+        init_sharded_weight(neox_args, self.weight, output_size, input_size, 0, init_method, stride)
+        if bias:
+            self.bias = Parameter(torch.zeros(self.output_size_per_partition, device=dev, dtype=neox_args.params_dtype))
+            _mark(self.bias, 0, stride)
+        else:
+            self.register_parameter("bias", None)
+
+    def set_parallel_output(self, value: bool):
+        self.gather_output = not value
+
+    def width_mult(self):
+        return self.width_mult_val
+
+    def forward(self, input_, act=None):
+        if self.use_mup and self.mup_rescale_parameters:
+            input_ = input_ / self.width_mult()
+        if self.sequence_parallel:
+            x = M.gather_from_sequence_parallel_region(input_, self.seq_dim)
+        else:
+            x = M.copy_to_model_parallel_region(input_)
+        bias = None if self.skip_bias_add else self.bias
+        out = fused_linear(x, self.weight, bias, act=act)
+        if self.gather_output:
+            assert not self.sequence_parallel, "sequence_parallel is incompatible with gather_output"
+            out = M.gather_from_model_parallel_region(out)
+        return out, (self.bias if self.skip_bias_add else None)
+
+
+class RowParallelLinear(nn.Module):
+    """``Y = X A + b`` with ``A`` split along its input (row) dimension and ``X`` along its last dim."""
+
+    def __init__(self, neox_args, input_size, output_size, bias=True, input_is_parallel=False,
+                 init_method=init.xavier_normal_, stride=1, keep_master_weight_for_test=False, skip_bias_add=False,
+                 MOE=False, MoE_mp_size=1, parallel_output=False, mup_rescale_parameters=False):
+        super().__init__()
+        self.input_size, self.output_size, self.input_is_parallel = input_size, output_size, input_is_parallel
+        world = MoE_mp_size if MOE else mpu.get_model_parallel_world_size()
+        self.tp = world
+        self.input_size_per_partition = mpu.divide(input_size, world)
+        self.skip_bias_add = skip_bias_add
+        self.parallel_output = parallel_output
+        self.sequence_parallel = bool(getattr(neox_args, "sequence_parallel", False)) and world > 1
+        assert not (self.sequence_parallel and not input_is_parallel), \
+            "Cannot have self.input_is_parallel=False and self.sequence_parallel=True."
+        self.init_method, self.stride = init_method, stride
+        self.mup_rescale_parameters = mup_rescale_parameters
+        self.use_mup = getattr(neox_args, "use_mup", False)
+        dev = _device(neox_args)
+        self.weight = Parameter(torch.empty(output_size, self.input_size_per_partition, device=dev,
+                                            dtype=neox_args.params_dtype))
+        init_sharded_weight(neox_args, self.weight, output_size, input_size, 1, init_method, stride)
+        if bias:
+            self.bias = Parameter(torch.zeros(output_size, device=dev, dtype=neox_args.params_dtype))
+        else:
+            self.register_parameter("bias", None)
+
+    def set_parallel_output(self, value: bool):
+        self.parallel_output = value
+
+    def forward(self, input_, residual=None):
+        """``residual`` (optional) is added in the GEMM epilogue; only legal when no cross-rank
+        reduction follows (tp == 1) or the caller defers it (``parallel_output``) and accounts for it."""
+        x = input_ if self.input_is_parallel else M.scatter_to_model_parallel_region(input_)
+        local_bias = None
+        if self.bias is not None and not self.skip_bias_add and (self.tp == 1):
+            local_bias = self.bias      # no reduction follows: fold the bias into the epilogue
+        out = fused_linear(x, self.weight, local_bias, residual=residual)
+        if self.sequence_parallel and not self.parallel_output:
+            out = M.reduce_scatter_to_sequence_parallel_region(out)
+        elif not self.parallel_output:
+            out = M.reduce_from_model_parallel_region(out)
+        if self.skip_bias_add:
+            return out, self.bias
+        if self.bias is not None and local_bias is None:
+            out = out + self.bias
+        return out, None
