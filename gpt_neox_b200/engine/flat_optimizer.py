@@ -95,14 +95,25 @@ class Bucket:
                 dist.all_reduce(self.flat_grad, group=self.comm_group)
 
     def shard_sq_norm(self, tp_rank):
-        """Squared L2 norm of this rank's gradient shard, counting TP-replicated entries on TP rank 0 only."""
+        """Squared L2 norm of this rank's gradient shard, counting TP-replicated entries on TP rank 0 only.
+        On CUDA one reduction kernel per segment accumulates into a scalar (no temporaries)."""
         g = self.flat_grad[self.lo:self.hi]
         rep_hi = min(max(self.rep_end, self.lo), self.hi) - self.lo
-        total = g.new_zeros((), dtype=torch.float32)
+        segs = []
         if rep_hi > 0 and tp_rank == 0:
-            total = total + g[:rep_hi].float().pow(2).sum()
+            segs.append(g[:rep_hi])
         if rep_hi < g.numel():
-            total = total + g[rep_hi:].float().pow(2).sum()
+            segs.append(g[rep_hi:])
+        total = torch.zeros((), dtype=torch.float32, device=g.device)
+        for seg in segs:
+            if seg.is_cuda and seg.dtype == torch.float32:
+                from ..ops import native
+                import ctypes
+                rc = native.lib().neox_sumsq_f32(native.ptr(seg), ctypes.c_longlong(seg.numel()), native.ptr(total),
+                                                 ctypes.c_void_p(native.stream_ptr()))
+                native.check(rc, "neox_sumsq_f32")
+            else:
+                total = total + torch.linalg.vector_norm(seg.float()) ** 2
         return total
 
     def gather_params(self):

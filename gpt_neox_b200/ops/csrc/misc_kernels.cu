@@ -1,0 +1,370 @@
+// Softmax (masked / causal), rotary embedding, vocabulary-parallel cross-entropy pieces, fused
+// Adam / Lion updates and the squared-norm reduction.  All bandwidth-bound; fp32 arithmetic.
+//
+// Reference counterparts: scaled_masked_softmax.h / scaled_upper_triang_masked_softmax.h (one warp per
+// row, sk <= 2048) and fused_rotary_positional_embedding.h of megatron/fused_kernels, the eager
+// megatron/mpu/cross_entropy.py, and apex multi_tensor_adam / DeepSpeed FusedLion.  These versions take
+// any row length, any of bf16/fp16/fp32, and strided rotary inputs.
+#include "neox_b200.h"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <float.h>
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+template <bool MAX>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = MAX ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nw) ? red[threadIdx.x] : (MAX ? -FLT_MAX : 0.f);
+    if (warp == 0) {
+        t = MAX ? warp_max(t) : warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// ------------------------------------------------------------------ softmax
+constexpr int SM_CACHE = 16;  // elements cached per thread (256 threads -> rows up to 4096 stay in registers)
+
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ x, const uint8_t* __restrict__ mask,
+                                                          T* __restrict__ y, long long rows, int sq, int sk,
+                                                          int heads, int mask_batches, float scale, int causal) {
+    __shared__ float red[33];
+    const bool cached = sk <= SM_CACHE * (int)blockDim.x;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * sk;
+        T* yr = y + row * sk;
+        const int q = (int)(row % sq);
+        const uint8_t* mr = nullptr;
+        if (mask) {
+            const long long b = row / ((long long)heads * sq);
+            mr = mask + ((mask_batches == 1 ? 0 : b) * sq + q) * (long long)sk;
+        }
+        const int limit = causal ? q + 1 : sk;  // columns >= limit are excluded (output exactly 0)
+        float v[SM_CACHE];
+        float mx = -FLT_MAX;
+        auto fetch = [&](int c) -> float {
+            float t = to_f<T>(xr[c]) * scale;
+            if (mr && mr[c]) t = -10000.0f;
+            return t;
+        };
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < SM_CACHE; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                v[j] = (c < limit) ? fetch(c) : -FLT_MAX;
+                mx = fmaxf(mx, v[j]);
+            }
+        } else {
+            for (int c = threadIdx.x; c < limit; c += blockDim.x) mx = fmaxf(mx, fetch(c));
+        }
+        mx = block_reduce<true>(mx, red);
+        float s = 0.f;
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < SM_CACHE; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                v[j] = (c < limit) ? __expf(v[j] - mx) : 0.f;
+                s += v[j];
+            }
+        } else {
+            for (int c = threadIdx.x; c < limit; c += blockDim.x) s += __expf(fetch(c) - mx);
+        }
+        s = block_reduce<false>(s, red);
+        const float inv = 1.0f / s;
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < SM_CACHE; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                if (c < sk) yr[c] = from_f<T>(v[j] * inv);
+            }
+        } else {
+            for (int c = threadIdx.x; c < sk; c += blockDim.x)
+                yr[c] = from_f<T>(c < limit ? __expf(fetch(c) - mx) * inv : 0.f);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(const T* __restrict__ g, const T* __restrict__ y,
+                                                          T* __restrict__ dx, long long rows, int sk, float scale) {
+    __shared__ float red[33];
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* gr = g + row * sk;
+        const T* yr = y + row * sk;
+        T* dr = dx + row * sk;
+        float s = 0.f;
+        for (int c = threadIdx.x; c < sk; c += blockDim.x) s += to_f<T>(gr[c]) * to_f<T>(yr[c]);
+        s = block_reduce<false>(s, red);
+        for (int c = threadIdx.x; c < sk; c += blockDim.x) {
+            const float yv = to_f<T>(yr[c]);
+            dr[c] = from_f<T>(scale * yv * (to_f<T>(gr[c]) - s));
+        }
+    }
+}
+
+// ------------------------------------------------------------------ rotary
+// x: [s, b, h, d] with element strides (ss, sb, sh) and unit stride on d; out: contiguous [s, b, h, d].
+// First `rot` dims rotated with cos/sin [s, rot] (fp32), remaining dims copied.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                   const float* __restrict__ cs, const float* __restrict__ sn, int s,
+                                                   int b, int h, int d, int rot, long long ss, long long sb,
+                                                   long long sh, int inverse) {
+    const long long total = (long long)s * b * h * d;
+    const int half = rot >> 1;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int e = (int)(i % d);
+        long long r = i / d;
+        const int hh = (int)(r % h);
+        r /= h;
+        const int bb = (int)(r % b);
+        const int sI = (int)(r / b);
+        const T* xp = x + sI * ss + bb * sb + hh * sh;
+        float v = to_f<T>(xp[e]);
+        if (e < rot) {
+            const float c = cs[(long long)sI * rot + e];
+            float sv = sn[(long long)sI * rot + e];
+            if (inverse) sv = -sv;
+            const float other = (e < half) ? -to_f<T>(xp[e + half]) : to_f<T>(xp[e - half]);
+            v = v * c + other * sv;
+        }
+        out[i] = from_f<T>(v);
+    }
+}
+
+// ------------------------------------------------------------------ cross entropy
+template <typename T>
+__global__ void __launch_bounds__(256) row_max_kernel(const T* __restrict__ x, float* __restrict__ out, int rows,
+                                                      int cols) {
+    __shared__ float red[33];
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + (size_t)row * cols;
+        float m = -FLT_MAX;
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, to_f<T>(xr[c]));
+        m = block_reduce<true>(m, red);
+        if (threadIdx.x == 0) out[row] = m;
+    }
+}
+
+// stats[row] = (sum_c exp(x - max), x[target - v0] - max if this shard owns the target else 0)
+template <typename T>
+__global__ void __launch_bounds__(256) ce_stats_kernel(const T* __restrict__ x, const long long* __restrict__ target,
+                                                       const float* __restrict__ row_max, float* __restrict__ stats,
+                                                       int rows, int cols, int v0) {
+    __shared__ float red[33];
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + (size_t)row * cols;
+        const float m = row_max[row];
+        float s = 0.f;
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) s += __expf(to_f<T>(xr[c]) - m);
+        s = block_reduce<false>(s, red);
+        if (threadIdx.x == 0) {
+            const long long t = target[row] - v0;
+            stats[2 * row] = s;
+            stats[2 * row + 1] = (t >= 0 && t < cols) ? to_f<T>(xr[t]) - m : 0.f;
+        }
+    }
+}
+
+// grad = (exp(x - max) / sum_exp - [c == target - v0]) * g[row]
+template <typename T>
+__global__ void __launch_bounds__(256) ce_bwd_kernel(const T* __restrict__ x, const long long* __restrict__ target,
+                                                     const float* __restrict__ row_max, const float* __restrict__ stats,
+                                                     const float* __restrict__ g, T* __restrict__ grad, int rows,
+                                                     int cols, int v0) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + (size_t)row * cols;
+        T* gr = grad + (size_t)row * cols;
+        const float m = row_max[row], inv = 1.0f / stats[2 * row], gv = g[row];
+        const long long t = target[row] - v0;
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            float p = __expf(to_f<T>(xr[c]) - m) * inv;
+            if (c == t) p -= 1.0f;
+            gr[c] = from_f<T>(p * gv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ optimizers
+template <typename OUT>
+__global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                                                   const float* __restrict__ g, OUT* __restrict__ out, long long n,
+                                                   float lr, float b1, float b2, float eps, float wd, float bc1,
+                                                   float bc2, float gs, int adamw) {
+    const float step = lr / bc1;
+    const float isb2 = rsqrtf(bc2);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float gi = g[i] * gs;
+        float pi = p[i];
+        if (!adamw && wd != 0.f) gi += wd * pi;
+        const float mi = b1 * m[i] + (1.f - b1) * gi;
+        const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        float upd = step * (mi / (sqrtf(vi) * isb2 + eps));
+        if (adamw && wd != 0.f) upd += lr * wd * pi;
+        pi -= upd;
+        p[i] = pi;
+        if (out) out[i] = from_f<OUT>(pi);
+    }
+}
+
+template <typename OUT>
+__global__ void __launch_bounds__(256) lion_kernel(float* __restrict__ p, float* __restrict__ m,
+                                                   const float* __restrict__ g, OUT* __restrict__ out, long long n,
+                                                   float lr, float b1, float b2, float wd, float gs) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float gi = g[i] * gs;
+        float pi = p[i] * (1.f - lr * wd);
+        const float mi = m[i];
+        const float c = mi * b1 + gi * (1.f - b1);
+        pi -= lr * ((c > 0.f) ? 1.f : (c < 0.f ? -1.f : 0.f));
+        m[i] = mi * b2 + gi * (1.f - b2);
+        p[i] = pi;
+        if (out) out[i] = from_f<OUT>(pi);
+    }
+}
+
+__global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+    __shared__ float red[33];
+    float s = 0.f;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        s += v * v;
+    }
+    s = block_reduce<false>(s, red);
+    if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+int grid_for(long long n, int per_sm = 8) {
+    long long b = (n + 255) / 256;
+    const long long cap = (long long)neox_sm_count() * per_sm;
+    return (int)(b < cap ? (b > 0 ? b : 1) : cap);
+}
+int row_grid(long long rows) {
+    const long long cap = (long long)neox_sm_count() * 8;
+    return (int)(rows < cap ? (rows > 0 ? rows : 1) : cap);
+}
+
+#define DISPATCH(dtype, CALL)                          \
+    do {                                               \
+        if (dtype == 0) { using T = __nv_bfloat16; CALL; } \
+        else if (dtype == 1) { using T = float; CALL; }    \
+        else { using T = __half; CALL; }                   \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int neox_softmax_fwd(const void* x, const void* mask, void* y, long long rows, int sq, int sk, int heads,
+                     int mask_batches, float scale, int causal, int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = sk <= 512 ? 64 : 256;
+    DISPATCH(dtype, (softmax_fwd_kernel<T><<<row_grid(rows), threads, 0, st>>>(
+                        (const T*)x, (const uint8_t*)mask, (T*)y, rows, sq, sk, heads, mask_batches, scale, causal)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_softmax_bwd(const void* g, const void* y, void* dx, long long rows, int sk, float scale, int dtype,
+                     void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = sk <= 512 ? 64 : 256;
+    DISPATCH(dtype, (softmax_bwd_kernel<T><<<row_grid(rows), threads, 0, st>>>((const T*)g, (const T*)y, (T*)dx, rows,
+                                                                              sk, scale)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_rope(const void* x, void* out, const float* cs, const float* sn, int s, int b, int h, int d, int rot,
+              long long ss, long long sb, long long sh, int inverse, int dtype, void* stream) {
+    const long long total = (long long)s * b * h * d;
+    if (total <= 0) return 0;
+    if (rot % 2 || rot > d) return NEOX_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dtype, (rope_kernel<T><<<grid_for(total, 16), 256, 0, st>>>((const T*)x, (T*)out, cs, sn, s, b, h, d, rot,
+                                                                         ss, sb, sh, inverse)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_row_max(const void* x, float* out, int rows, int cols, int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dtype, (row_max_kernel<T><<<row_grid(rows), 256, 0, st>>>((const T*)x, out, rows, cols)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_ce_stats(const void* x, const long long* target, const float* row_max, float* stats, int rows, int cols,
+                  int v0, int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dtype, (ce_stats_kernel<T><<<row_grid(rows), 256, 0, st>>>((const T*)x, target, row_max, stats, rows,
+                                                                       cols, v0)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_ce_bwd(const void* x, const long long* target, const float* row_max, const float* stats, const float* g,
+                void* grad, int rows, int cols, int v0, int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dtype, (ce_bwd_kernel<T><<<row_grid(rows), 256, 0, st>>>((const T*)x, target, row_max, stats, g, (T*)grad,
+                                                                     rows, cols, v0)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_adam_step(float* p, float* m, float* v, const float* g, void* out, int out_dtype, long long n, float lr,
+                   float b1, float b2, float eps, float wd, float bc1, float bc2, float gs, int adamw, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid = grid_for(n, 16);
+    if (!out || out_dtype == 1)
+        adam_kernel<float><<<grid, 256, 0, st>>>(p, m, v, g, (float*)out, n, lr, b1, b2, eps, wd, bc1, bc2, gs, adamw);
+    else if (out_dtype == 0)
+        adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, m, v, g, (__nv_bfloat16*)out, n, lr, b1, b2, eps, wd, bc1,
+                                                          bc2, gs, adamw);
+    else
+        adam_kernel<__half><<<grid, 256, 0, st>>>(p, m, v, g, (__half*)out, n, lr, b1, b2, eps, wd, bc1, bc2, gs, adamw);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_lion_step(float* p, float* m, const float* g, void* out, int out_dtype, long long n, float lr, float b1,
+                   float b2, float wd, float gs, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid = grid_for(n, 16);
+    if (!out || out_dtype == 1) lion_kernel<float><<<grid, 256, 0, st>>>(p, m, g, (float*)out, n, lr, b1, b2, wd, gs);
+    else if (out_dtype == 0)
+        lion_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, m, g, (__nv_bfloat16*)out, n, lr, b1, b2, wd, gs);
+    else lion_kernel<__half><<<grid, 256, 0, st>>>(p, m, g, (__half*)out, n, lr, b1, b2, wd, gs);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+// out += sum(x^2); the caller zeroes `out` first.
+int neox_sumsq_f32(const float* x, long long n, float* out, void* stream) {
+    if (n <= 0) return 0;
+    sumsq_kernel<<<grid_for(n, 4), 256, 0, (cudaStream_t)stream>>>(x, n, out);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+}  // extern "C"

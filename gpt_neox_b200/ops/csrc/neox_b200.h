@@ -22,4 +22,5 @@ int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long
 
 extern "C" {
 int neox_read_status();  // synchronises the device; returns and clears the status word
+int neox_norm_bwd_blocks(int rows);  // CTAs (= partial rows of scratch) the norm backward kernels use
 }

@@ -1,0 +1,577 @@
+// Bandwidth-bound row kernels: LayerNorm / RMSNorm forward+backward and the fused bias / activation /
+// residual element-wise ops.  One CTA per row (grid-stride over rows), 16-byte vector accesses, the
+// row is held in registers between the statistics pass and the normalisation pass so every input
+// byte is read from HBM exactly once.  fp32 statistics for all storage dtypes (bf16 / fp16 / fp32).
+//
+// Replaces apex fused_layer_norm_cuda / FastLayerNormFN (megatron/model/fused_layer_norm.py:123-153),
+// the TorchScript bias_gelu (activations.py:78-112), the gated-activation glue (transformer.py:190-206)
+// and bias_dropout_add (fused_bias_dropout.py:28-55) of the reference.
+#include "neox_b200.h"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int MAXV = 4;  // vectors of 8 elements cached per thread
+
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        uint4 u = *reinterpret_cast<const uint4*>(p);
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <>
+struct Vec8<__half> {
+    static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+        uint4 u = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+        uint4 u;
+        __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = u;
+    }
+};
+template <>
+struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum over the CTA; every thread receives the result.  `red` is a 33-float shared scratch.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+    if (warp == 0) {
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) {
+        red[warp] = a;
+        red[33 + warp] = b;
+    }
+    __syncthreads();
+    float ta = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+    float tb = (threadIdx.x < nw) ? red[33 + threadIdx.x] : 0.f;
+    if (warp == 0) {
+        ta = warp_sum(ta);
+        tb = warp_sum(tb);
+        if (lane == 0) {
+            red[32] = ta;
+            red[65] = tb;
+        }
+    }
+    __syncthreads();
+    a = red[32];
+    b = red[65];
+}
+
+// ------------------------------------------------------------------ LayerNorm
+// RMS == false: y = (x - mean) * rstd * gamma + beta,   stat0 = mean, stat1 = rstd
+// RMS == true : y = x * rinv * gamma + beta with rinv = 1 / (sqrt(mean(x^2)) + eps),  stat1 = rinv
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                       const T* __restrict__ beta, T* __restrict__ y,
+                                                       float* __restrict__ stat0, float* __restrict__ stat1,
+                                                       int rows, int cols, float eps) {
+    __shared__ float red[66];
+    const int nvec = cols >> 3;
+    const bool cached = nvec <= MAXV * (int)blockDim.x;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + (size_t)row * cols;
+        T* yr = y + (size_t)row * cols;
+        float v[MAXV][8];
+        float s = 0.f;
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                if (c < nvec) {
+                    Vec8<T>::load(xr + c * 8, v[j]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) s += RMS ? v[j][i] * v[j][i] : v[j][i];
+                }
+            }
+        } else {
+            for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+                float t[8];
+                Vec8<T>::load(xr + c * 8, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += RMS ? t[i] * t[i] : t[i];
+            }
+        }
+        s = block_sum(s, red);
+        float mean = 0.f, scale;
+        if (RMS) {
+            scale = 1.0f / (sqrtf(s / cols) + eps);
+        } else {
+            mean = s / cols;
+            float q = 0.f;
+            if (cached) {
+#pragma unroll
+                for (int j = 0; j < MAXV; ++j) {
+                    const int c = threadIdx.x + j * blockDim.x;
+                    if (c < nvec) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float d = v[j][i] - mean;
+                            q += d * d;
+                        }
+                    }
+                }
+            } else {
+                for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+                    float t[8];
+                    Vec8<T>::load(xr + c * 8, t);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float d = t[i] - mean;
+                        q += d * d;
+                    }
+                }
+            }
+            q = block_sum(q, red);
+            scale = rsqrtf(q / cols + eps);
+        }
+        if (threadIdx.x == 0) {
+            if (stat0) stat0[row] = mean;
+            stat1[row] = scale;
+        }
+        auto emit = [&](int c, float (&t)[8]) {
+            float g[8], b[8], o[8];
+            Vec8<T>::load(gamma + c * 8, g);
+            if (beta) Vec8<T>::load(beta + c * 8, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = (t[i] - mean) * scale * g[i] + (beta ? b[i] : 0.f);
+            Vec8<T>::store(yr + c * 8, o);
+        };
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                if (c < nvec) emit(c, v[j]);
+            }
+        } else {
+            for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+                float t[8];
+                Vec8<T>::load(xr + c * 8, t);
+                emit(c, t);
+            }
+        }
+    }
+}
+
+// Backward.  Column sums (dgamma, dbeta) are accumulated per CTA in registers (cached path) or in
+// global partial rows (generic path) and written to partial[blockIdx.x][cols]; a second kernel
+// reduces the partial rows.  partial layout: [2][nblk][cols] fp32.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256) norm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x,
+                                                       const T* __restrict__ gamma, const float* __restrict__ stat0,
+                                                       const float* __restrict__ stat1, T* __restrict__ dx,
+                                                       float* __restrict__ partial, int rows, int cols, float eps) {
+    __shared__ float red[66];
+    const int nvec = cols >> 3;
+    const bool cached = nvec <= MAXV * (int)blockDim.x;
+    float* pg = partial + (size_t)blockIdx.x * cols;
+    float* pb = partial + ((size_t)gridDim.x + blockIdx.x) * cols;
+    float ag[MAXV][8], ab[MAXV][8];
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ag[j][i] = ab[j][i] = 0.f;
+    } else {
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) pg[c] = pb[c] = 0.f;
+    }
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + (size_t)row * cols;
+        const T* gr = g + (size_t)row * cols;
+        T* dr = dx + (size_t)row * cols;
+        const float mean = RMS ? 0.f : stat0[row];
+        const float sc = stat1[row];
+        float s1 = 0.f, s2 = 0.f;
+        float xv[MAXV][8], gv[MAXV][8];
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                if (c < nvec) {
+                    float gm[8];
+                    Vec8<T>::load(xr + c * 8, xv[j]);
+                    Vec8<T>::load(gr + c * 8, gv[j]);
+                    Vec8<T>::load(gamma + c * 8, gm);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float xh = RMS ? xv[j][i] : (xv[j][i] - mean) * sc;
+                        const float gg = gv[j][i] * gm[i];
+                        s1 += gg;
+                        s2 += gg * xh;
+                        ag[j][i] += gv[j][i] * (RMS ? xv[j][i] * sc : xh);
+                        ab[j][i] += gv[j][i];
+                        gv[j][i] = gg;   // keep g*gamma
+                        xv[j][i] = xh;   // keep xhat (LN) or x (RMS)
+                    }
+                }
+            }
+        } else {
+            for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+                float xt[8], gt[8], gm[8];
+                Vec8<T>::load(xr + c * 8, xt);
+                Vec8<T>::load(gr + c * 8, gt);
+                Vec8<T>::load(gamma + c * 8, gm);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float xh = RMS ? xt[i] : (xt[i] - mean) * sc;
+                    const float gg = gt[i] * gm[i];
+                    s1 += gg;
+                    s2 += gg * xh;
+                    pg[c * 8 + i] += gt[i] * (RMS ? xt[i] * sc : xh);
+                    pb[c * 8 + i] += gt[i];
+                }
+            }
+        }
+        block_sum2(s1, s2, red);
+        // LN : dx = sc * (gg - s1/n - xhat * s2/n)
+        // RMS: y = x*sc*gamma, sc = 1/(r+eps), r = sqrt(mean x^2) -> dx = gg*sc - x * s2 * sc^2 / (n * r)
+        float k1, k2;
+        if (RMS) {
+            const float r = 1.0f / sc - eps;
+            k1 = 0.f;
+            k2 = (r > 0.f) ? s2 * sc * sc / (cols * r) : 0.f;
+        } else {
+            k1 = s1 / cols;
+            k2 = s2 / cols;
+        }
+        auto emit = [&](int c, const float (&xh)[8], const float (&gg)[8]) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = RMS ? gg[i] * sc - xh[i] * k2 : sc * (gg[i] - k1 - xh[i] * k2);
+            Vec8<T>::store(dr + c * 8, o);
+        };
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                if (c < nvec) emit(c, xv[j], gv[j]);
+            }
+        } else {
+            for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+                float xt[8], gt[8], gm[8], xh[8], gg[8];
+                Vec8<T>::load(xr + c * 8, xt);
+                Vec8<T>::load(gr + c * 8, gt);
+                Vec8<T>::load(gamma + c * 8, gm);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    xh[i] = RMS ? xt[i] : (xt[i] - mean) * sc;
+                    gg[i] = gt[i] * gm[i];
+                }
+                emit(c, xh, gg);
+            }
+        }
+    }
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int c = threadIdx.x + j * blockDim.x;
+            if (c < nvec) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    pg[c * 8 + i] = ag[j][i];
+                    pb[c * 8 + i] = ab[j][i];
+                }
+            }
+        }
+    }
+}
+
+__global__ void colreduce_kernel(const float* __restrict__ partial, float* __restrict__ out0,
+                                 float* __restrict__ out1, int nblk, int cols) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float a = 0.f, b = 0.f;
+    for (int r = 0; r < nblk; ++r) {
+        a += partial[(size_t)r * cols + c];
+        b += partial[((size_t)nblk + r) * cols + c];
+    }
+    out0[c] = a;
+    if (out1) out1[c] = b;
+}
+
+int pick_threads(int cols) {
+    int t = 32;
+    while (t < 256 && t * 8 < cols) t <<= 1;
+    return t;
+}
+
+template <bool RMS>
+int launch_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* s0, float* s1, int rows,
+                    int cols, float eps, int dtype, cudaStream_t st) {
+    if (cols % 8) return NEOX_ERR_SHAPE;
+    if (rows <= 0) return 0;
+    const int threads = pick_threads(cols);
+    const int grid = rows < neox_sm_count() * 8 ? rows : neox_sm_count() * 8;
+#define LAUNCH(T)                                                                                                   \
+    norm_fwd_kernel<T, RMS><<<grid, threads, 0, st>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y, s0, s1, \
+                                                      rows, cols, eps)
+    if (dtype == 0) LAUNCH(__nv_bfloat16);
+    else if (dtype == 1) LAUNCH(float);
+    else LAUNCH(__half);
+#undef LAUNCH
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+template <bool RMS>
+int launch_norm_bwd(const void* g, const void* x, const void* gamma, const float* s0, const float* s1, void* dx,
+                    float* d0, float* d1, float* ws, int rows, int cols, float eps, int dtype, cudaStream_t st) {
+    if (cols % 8) return NEOX_ERR_SHAPE;
+    if (rows <= 0) return 0;
+    const int threads = pick_threads(cols);
+    const int nblk = neox_norm_bwd_blocks(rows);
+#define LAUNCH(T)                                                                                                    \
+    norm_bwd_kernel<T, RMS><<<nblk, threads, 0, st>>>((const T*)g, (const T*)x, (const T*)gamma, s0, s1, (T*)dx, ws, \
+                                                      rows, cols, eps)
+    if (dtype == 0) LAUNCH(__nv_bfloat16);
+    else if (dtype == 1) LAUNCH(float);
+    else LAUNCH(__half);
+#undef LAUNCH
+    colreduce_kernel<<<(cols + 255) / 256, 256, 0, st>>>(ws, d0, d1, nblk, cols);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+// ------------------------------------------------------------------ element-wise
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+    return 0.5f * x * (1.0f + tanh_fast(0.7978845608028654f * x * (1.0f + 0.044715f * x * x)));
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    const float t = tanh_fast(k0 * x * (1.0f + k1 * x * x));
+    return 0.5f * x * ((1.0f - t * t) * (k0 + 3.0f * k0 * k1 * x * x)) + 0.5f * (1.0f + t);
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// mode 0: out = g * gelu'(a)                    (a = pre-activation)
+// mode 1: out = gelu(a + bias)                  (bias per column, may be null)
+// mode 2: out = g * gelu'(a + bias)
+// mode 3: out = a + bias + r                    (bias + residual add)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) ew_kernel(const T* __restrict__ a, const T* __restrict__ b2,
+                                                 const T* __restrict__ bias, T* __restrict__ out, long long nvec,
+                                                 int colvec) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        float va[8], vb[8], bb[8], o[8];
+        Vec8<T>::load(a + i * 8, va);
+        if (MODE == 0 || MODE == 2 || MODE == 3) Vec8<T>::load(b2 + i * 8, vb);
+        const bool hb = (MODE != 0) && bias != nullptr;
+        if (hb) Vec8<T>::load(bias + (i % colvec) * 8, bb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float xa = va[k] + (hb ? bb[k] : 0.f);
+            if (MODE == 0) o[k] = vb[k] * dgelu_f(va[k]);
+            else if (MODE == 1) o[k] = gelu_f(xa);
+            else if (MODE == 2) o[k] = vb[k] * dgelu_f(xa);
+            else o[k] = xa + vb[k];
+        }
+        Vec8<T>::store(out + i * 8, o);
+    }
+}
+
+// gated activations: x = [up | gate] halves of the last dim; out = act(gate) * up
+// kind 0 geglu, 1 swiglu, 2 reglu, 3 bilinear, 4 glu(sigmoid)
+__device__ __forceinline__ float gate_act(int kind, float t) {
+    switch (kind) {
+        case 0: return gelu_f(t);
+        case 1: return t * sigmoid_f(t);
+        case 2: return fmaxf(t, 0.f);
+        case 3: return t;
+        default: return sigmoid_f(t);
+    }
+}
+__device__ __forceinline__ float gate_dact(int kind, float t) {
+    switch (kind) {
+        case 0: return dgelu_f(t);
+        case 1: { const float s = sigmoid_f(t); return s * (1.0f + t * (1.0f - s)); }
+        case 2: return t > 0.f ? 1.f : 0.f;
+        case 3: return 1.f;
+        default: { const float s = sigmoid_f(t); return s * (1.0f - s); }
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) gated_fwd_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows,
+                                                        int cols, int kind) {
+    const int cv = cols >> 3;
+    const long long n = rows * cv;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cv;
+        const int c = (int)(i % cv) * 8;
+        float up[8], gt[8], o[8];
+        Vec8<T>::load(x + r * 2 * cols + c, up);
+        Vec8<T>::load(x + r * 2 * cols + cols + c, gt);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = gate_act(kind, gt[k]) * up[k];
+        Vec8<T>::store(out + r * cols + c, o);
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) gated_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x,
+                                                        T* __restrict__ dx, long long rows, int cols, int kind) {
+    const int cv = cols >> 3;
+    const long long n = rows * cv;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cv;
+        const int c = (int)(i % cv) * 8;
+        float up[8], gt[8], gg[8], du[8], dg[8];
+        Vec8<T>::load(x + r * 2 * cols + c, up);
+        Vec8<T>::load(x + r * 2 * cols + cols + c, gt);
+        Vec8<T>::load(g + r * cols + c, gg);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            du[k] = gg[k] * gate_act(kind, gt[k]);
+            dg[k] = gg[k] * up[k] * gate_dact(kind, gt[k]);
+        }
+        Vec8<T>::store(dx + r * 2 * cols + c, du);
+        Vec8<T>::store(dx + r * 2 * cols + cols + c, dg);
+    }
+}
+
+int ew_grid(long long nvec) {
+    long long b = (nvec + 255) / 256;
+    const long long cap = (long long)neox_sm_count() * 16;
+    return (int)(b < cap ? (b > 0 ? b : 1) : cap);
+}
+
+template <int MODE>
+int launch_ew(const void* a, const void* b, const void* bias, void* out, long long n, int cols, int dtype,
+              cudaStream_t st) {
+    if (n % 8 || (cols % 8)) return NEOX_ERR_SHAPE;
+    if (n == 0) return 0;
+    const long long nvec = n / 8;
+    const int grid = ew_grid(nvec);
+#define LAUNCH(T) ew_kernel<T, MODE><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (const T*)bias, (T*)out, nvec, cols / 8)
+    if (dtype == 0) LAUNCH(__nv_bfloat16);
+    else if (dtype == 1) LAUNCH(float);
+    else LAUNCH(__half);
+#undef LAUNCH
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+}  // namespace
+
+extern "C" {
+
+int neox_norm_bwd_blocks(int rows) {
+    const int cap = neox_sm_count() * 2;
+    return rows < cap ? (rows > 0 ? rows : 1) : cap;
+}
+
+int neox_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                       int rows, int cols, float eps, int dtype, void* stream) {
+    return launch_norm_fwd<false>(x, gamma, beta, y, mean, rstd, rows, cols, eps, dtype, (cudaStream_t)stream);
+}
+int neox_layernorm_bwd(const void* g, const void* x, const void* gamma, const float* mean, const float* rstd,
+                       void* dx, float* dgamma, float* dbeta, float* ws, int rows, int cols, int dtype, void* stream) {
+    return launch_norm_bwd<false>(g, x, gamma, mean, rstd, dx, dgamma, dbeta, ws, rows, cols, 0.f, dtype,
+                                  (cudaStream_t)stream);
+}
+int neox_rmsnorm_fwd(const void* x, const void* scale, const void* bias, void* y, float* rinv, int rows, int cols,
+                     float eps, int dtype, void* stream) {
+    return launch_norm_fwd<true>(x, scale, bias, y, nullptr, rinv, rows, cols, eps, dtype, (cudaStream_t)stream);
+}
+int neox_rmsnorm_bwd(const void* g, const void* x, const void* scale, const float* rinv, void* dx, float* dscale,
+                     float* dbias, float* ws, int rows, int cols, float eps, int dtype, void* stream) {
+    return launch_norm_bwd<true>(g, x, scale, nullptr, rinv, dx, dscale, dbias, ws, rows, cols, eps, dtype,
+                                 (cudaStream_t)stream);
+}
+int neox_dgelu_mul(const void* g, const void* pre, void* out, long long n, int dtype, void* stream) {
+    return launch_ew<0>(pre, g, nullptr, out, n, 8, dtype, (cudaStream_t)stream);
+}
+int neox_bias_gelu_fwd(const void* x, const void* bias, void* out, long long rows, int cols, int dtype, void* stream) {
+    return launch_ew<1>(x, nullptr, bias, out, rows * cols, cols, dtype, (cudaStream_t)stream);
+}
+int neox_bias_gelu_bwd(const void* g, const void* x, const void* bias, void* dx, long long rows, int cols, int dtype,
+                       void* stream) {
+    return launch_ew<2>(x, g, bias, dx, rows * cols, cols, dtype, (cudaStream_t)stream);
+}
+int neox_bias_residual_add(const void* x, const void* bias, const void* residual, void* out, long long rows, int cols,
+                           int dtype, void* stream) {
+    return launch_ew<3>(x, residual, bias, out, rows * cols, cols, dtype, (cudaStream_t)stream);
+}
+int neox_gated_act_fwd(const void* x, void* out, long long rows, int cols, int kind, int dtype, void* stream) {
+    if (cols % 8) return NEOX_ERR_SHAPE;
+    if (rows == 0) return 0;
+    const int grid = ew_grid(rows * (cols / 8));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == 0) gated_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, kind);
+    else if (dtype == 1) gated_fwd_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (float*)out, rows, cols, kind);
+    else gated_fwd_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, (__half*)out, rows, cols, kind);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_gated_act_bwd(const void* g, const void* x, void* dx, long long rows, int cols, int kind, int dtype,
+                       void* stream) {
+    if (cols % 8) return NEOX_ERR_SHAPE;
+    if (rows == 0) return 0;
+    const int grid = ew_grid(rows * (cols / 8));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == 0) gated_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (__nv_bfloat16*)dx, rows, cols, kind);
+    else if (dtype == 1) gated_bwd_kernel<float><<<grid, 256, 0, st>>>((const float*)g, (const float*)x, (float*)dx, rows, cols, kind);
+    else gated_bwd_kernel<__half><<<grid, 256, 0, st>>>((const __half*)g, (const __half*)x, (__half*)dx, rows, cols, kind);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+}  // extern "C"

@@ -1,0 +1,215 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from gpt_neox_b200.ops import functional as OF
+from gpt_neox_b200.ops import gemm as G
+from gpt_neox_b200.ops import native
+
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol=1e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (tol {atol}, {rtol})"
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(128, 256, 64, 0, 0), (256, 512, 256, 0, 1), (256, 512, 256, 1, 0),
+                                             (384, 264, 136, 1, 1), (1000, 840, 328, 0, 0), (77, 96, 200, 0, 1)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    out = G.gemm(a, b, a_mn, b_mn)
+    ref = G.gemm_ref(a, b, a_mn, b_mn, out_dtype=torch.float32)
+    assert native.read_status() == 0
+    _close(out, ref, atol=0.02 * ref.abs().max().item(), rtol=1e-2)
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    M, N, K = 512, 1024, 512
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    out, pre = G.gemm(a, b, bias=bias, act=G.ACT_GELU, add=res, want_preact=True)
+    ro, rp = G.gemm_ref(a, b, bias=bias, act=G.ACT_GELU, add=res, want_preact=True, out_dtype=torch.float32)
+    _close(out, ro, atol=0.05)
+    _close(pre, rp, atol=0.05)
+    aux = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    out = G.gemm(a, b, act=G.ACT_DGELU, aux=aux)
+    _close(out, G.gemm_ref(a, b, act=G.ACT_DGELU, aux=aux, out_dtype=torch.float32), atol=0.05)
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    want = G.gemm_ref(a, b, add=acc, out_dtype=torch.float32)
+    G.gemm(a, b, out=acc, add=acc)
+    _close(acc, want, atol=0.02)
+    assert native.read_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("rows,cols", [(33, 64), (128, 2048), (17, 6144), (5, 16384)])
+def test_layernorm(dtype, rows, cols):
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device=DEV, dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(dtype).requires_grad_()
+    b = (0.1 * torch.randn(cols, device=DEV)).to(dtype).requires_grad_()
+    y = OF.layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (cols,), wr, br, 1e-5)
+    yr.backward(g.float())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    _close(y, yr, tol)
+    _close(x.grad, xr.grad, tol)
+    _close(w.grad, wr.grad, tol * math.sqrt(rows), rtol=2e-2)
+    _close(b.grad, br.grad, tol * math.sqrt(rows), rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(33, 64), (64, 4096)])
+def test_rmsnorm(dtype, rows, cols):
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device=DEV, dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(dtype).requires_grad_()
+    y = OF.rms_norm(x, w, None, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = (t.detach().float().requires_grad_() for t in (x, w))
+    yr = OF.rms_norm_ref(xr, wr, None, 1e-5)
+    yr.backward(g.float())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    _close(y, yr, tol)
+    _close(x.grad, xr.grad, tol)
+    _close(w.grad, wr.grad, tol * math.sqrt(rows), rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bias_gelu_and_gated(dtype):
+    torch.manual_seed(0)
+    x = torch.randn(37, 512, device=DEV, dtype=dtype, requires_grad=True)
+    bias = torch.randn(512, device=DEV, dtype=dtype, requires_grad=True)
+    y = OF.bias_gelu(x, bias)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, br = x.detach().float().requires_grad_(), bias.detach().float().requires_grad_()
+    yr = torch.nn.functional.gelu(xr + br, approximate="tanh")
+    yr.backward(g.float())
+    tol = 2e-3 if dtype == torch.float32 else 3e-2
+    _close(y, yr, tol)
+    _close(x.grad, xr.grad, tol)
+    for kind in ("geglu", "swiglu", "reglu", "bilinear", "glu"):
+        x2 = torch.randn(19, 256, device=DEV, dtype=dtype, requires_grad=True)
+        y2 = OF.gated_act(x2, kind)
+        g2 = torch.randn_like(y2)
+        y2.backward(g2)
+        x2r = x2.detach().float().requires_grad_()
+        y2r = OF.gated_act_ref(x2r, kind)
+        y2r.backward(g2.float())
+        _close(y2, y2r, tol)
+        _close(x2.grad, x2r.grad, tol)
+
+
+@pytest.mark.parametrize("sk", [17, 128, 1000, 2048, 5000])
+def test_softmax(sk):
+    torch.manual_seed(0)
+    b, h, sq = 2, 3, 8
+    x = torch.randn(b, h, sq, sk, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    mask = torch.rand(b, 1, sq, sk, device=DEV) < 0.3
+    y = OF.scaled_masked_softmax(x, mask, 0.7)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = OF.scaled_masked_softmax_ref(xr, mask, 0.7)
+    yr.backward(g.float())
+    # the reference bar for this kernel is a mean absolute difference <= 1e-3
+    assert (y.float() - yr).abs().mean().item() <= 1e-3
+    _close(y, yr, 1e-2)
+    _close(x.grad, xr.grad, 2e-2)
+
+
+@pytest.mark.parametrize("s", [16, 129, 2048])
+def test_causal_softmax(s):
+    torch.manual_seed(0)
+    x = torch.randn(4, s, s, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = OF.scaled_upper_triang_masked_softmax(x, 0.5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = OF.scaled_causal_softmax_ref(xr, 0.5)
+    yr.backward(g.float())
+    assert (y.float() - yr).abs().mean().item() <= 1e-3
+    assert bool((y.float().triu(1) == 0).all())
+    _close(x.grad, xr.grad, 2e-2)
+
+
+@pytest.mark.parametrize("d,rot", [(64, 16), (96, 24), (128, 128)])
+def test_rope_strided(d, rot):
+    torch.manual_seed(0)
+    s, b, h = 33, 2, 4
+    qkv = torch.randn(s, b, h, 3 * d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    q = qkv[..., d:2 * d]                    # a strided view, as sliced from the fused projection
+    t = torch.arange(s, device=DEV).float()
+    inv = 1.0 / (10000 ** (torch.arange(0, rot, 2, device=DEV).float() / rot))
+    emb = torch.cat([torch.outer(t, inv)] * 2, dim=-1)
+    cos, sin = emb.cos()[:, None, None, :], emb.sin()[:, None, None, :]
+    y = OF.rope(q, cos, sin)
+    g = torch.randn_like(y)
+    y.backward(g)
+    qr = qkv.detach().float().requires_grad_()
+    yr = OF.rope_ref(qr[..., d:2 * d], cos, sin)
+    yr.backward(g.float())
+    _close(y, yr, 3e-2)
+    _close(qkv.grad, qr.grad, 3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy(dtype):
+    from gpt_neox_b200.parallel.cross_entropy import vocab_parallel_cross_entropy
+    torch.manual_seed(0)
+    logits = (torch.randn(4, 9, 1000, device=DEV) * 3).to(dtype).requires_grad_()
+    tgt = torch.randint(0, 1000, (4, 9), device=DEV)
+    loss = vocab_parallel_cross_entropy(logits, tgt)
+    w = torch.rand_like(loss)
+    (loss * w).sum().backward()
+    lr = logits.detach().float().requires_grad_()
+    ref = OF.cross_entropy_ref(lr, tgt)
+    (ref * w).sum().backward()
+    _close(loss, ref, 2e-3 if dtype == torch.float32 else 2e-2)
+    _close(logits.grad, lr.grad, 1e-4 if dtype == torch.float32 else 1e-2)
+
+
+def test_fused_adam_matches_torch():
+    from gpt_neox_b200.optim.fused_adam import FusedAdam
+    torch.manual_seed(0)
+    p0 = torch.randn(10007, device=DEV)
+    p1 = torch.nn.Parameter(p0.clone())
+    p2 = torch.nn.Parameter(p0.clone())
+    out = torch.empty(10007, device=DEV, dtype=torch.bfloat16)
+    p1.model_out = out
+    o1 = FusedAdam([p1], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    o2 = torch.optim.AdamW([p2], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for _ in range(5):
+        g = torch.randn(10007, device=DEV)
+        p1.grad, p2.grad = g.clone(), g.clone()
+        o1.step()
+        o2.step()
+    _close(p1, p2, 1e-5, rtol=1e-5)
+    _close(out, p2, 1e-2)
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """Status word plumbing: a clean run leaves the status at 0 and reading it does not disturb later launches."""
+    a = torch.randn(128, 64, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(256, 64, device=DEV, dtype=torch.bfloat16)
+    G.gemm(a, b)
+    assert native.read_status() == 0
+    G.gemm(a, b)
+    assert native.read_status() == 0
