@@ -1,0 +1,270 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput of a GPT-NeoX-20B-shaped model.
+
+    python bench.py --gpus N --steps K --warmup W              (N = 1)
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+
+Metric: tokens/s over the whole job (and TFLOPS/GPU from the reference FLOPs formula) for the
+layer shape of GPT-NeoX-20B: hidden 6144, 64 heads (head size 96), rotary on 25 % of each head,
+parallel attention+MLP residual, LayerNorm, GeLU MLP 24576, vocab 50432, sequence 2048, micro-batch 4,
+activation checkpointing on, bf16 parameters with fp32 master weights and Adam (ZeRO-1 layout).
+
+The full 44-layer model needs 8 GPUs (it is ~330 GB of parameter + optimizer state), so the depth
+scales with the GPU count -- 5.5 layers per GPU, as in the 8-GPU run -- and so does the global batch
+(192 sequences per GPU; 1536 at N = 8): work per GPU is constant (weak scaling).
+
+    N = 1: 6 layers            N = 2: 11 layers, TP 2 (sequence parallel)
+    N = 4: 22 layers, TP 4     N = 8: 44 layers, TP 4 x PP 2 (1F1B)   <- the named configuration
+
+Two timed regions of K optimizer steps each, both through the public API
+(``gpt_neox_b200.training.train_step``):
+  * device: inputs already resident on the GPU; CUDA events, max over ranks  -> ``value``
+  * end-to-end: every micro-batch is copied from pinned host memory and the loss is read back
+    every step; timed the same way                                           -> ``e2e``
+Inputs (uniform-random token ids) total far more than L2 per step, so no explicit L2 flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = {1: 6, 2: 11, 4: 22, 8: 44}
+PARALLEL = {1: (1, 0), 2: (2, 0), 4: (4, 0), 8: (4, 2)}      # (tensor parallel, pipeline stages)
+SEQ_PER_GPU = 192
+PAPER_TFLOPS_PER_GPU_A100 = 117.0
+
+
+def model_config(n_gpus, layers=None, micro_batch=4, seq=2048, seq_per_gpu=SEQ_PER_GPU, ckpt=True):
+    tp, pp = PARALLEL[n_gpus]
+    L = layers or LAYERS[n_gpus]
+    return {
+        "num_layers": L, "hidden_size": 6144, "num_attention_heads": 64, "seq_length": seq,
+        "max_position_embeddings": seq, "pos_emb": "rotary", "rotary_pct": 0.25, "no_weight_tying": True,
+        "gpt_j_residual": True, "output_layer_parallelism": "column", "norm": "layernorm",
+        "attention_config": [[["flash"], "all"]],
+        "scaled_upper_triang_masked_softmax_fusion": True, "bias_gelu_fusion": True,
+        "init_method": "small_init", "output_layer_init_method": "wang_init",
+        "optimizer": {"type": "Adam", "params": {"lr": 0.97e-4, "betas": [0.9, 0.95], "eps": 1.0e-8}},
+        "min_lr": 0.97e-5,
+        "zero_optimization": {"stage": 1, "allgather_partitions": True, "allgather_bucket_size": 1260000000,
+                              "overlap_comm": True, "reduce_scatter": True, "reduce_bucket_size": 1260000000,
+                              "contiguous_gradients": True},
+        "train_micro_batch_size_per_gpu": micro_batch, "train_batch_size": seq_per_gpu * n_gpus,
+        "gradient_accumulation_steps": None,
+        "checkpoint_activations": ckpt, "checkpoint_num_layers": 1, "partition_activations": False,
+        "synchronize_each_layer": True, "gradient_clipping": 1.0, "weight_decay": 0.01, "hidden_dropout": 0,
+        "attention_dropout": 0, "precision": "bfloat16", "model_parallel_size": tp, "pipe_parallel_size": pp,
+        "sequence_parallel": tp > 1, "train_iters": 1000, "lr_decay_iters": 1000, "lr_decay_style": "cosine",
+        "warmup": 0.01, "data_path": "synthetic", "tokenizer_type": "CharLevelTokenizer",
+        "make_vocab_size_divisible_by": 128, "log_interval": 10 ** 9,
+        "eval_interval": 10 ** 9, "eval_iters": 1, "num_workers": 0, "seed": 1234, "global_num_gpus": n_gpus,
+        "checkpoint_factor": 10 ** 9, "distributed_backend": "nccl",
+    }
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                clk, mclk = float(r[1]), float(r[2])
+            except (ValueError, IndexError):
+                continue
+            if len(r) > 3:
+                try:
+                    if float(r[3]) < 300.0:      # idle sample (W): not "under load"
+                        continue
+                except ValueError:
+                    pass
+            sm.append(clk)
+            mx.append(mclk)
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The unmodified reference needs DeeperSpeed (imported at module scope by deepy.py, training.py and
+    the model files), which is not installable offline; see DESIGN.md for the recorded attempt."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref_dir, "megatron")):
+        why = "baseline/_ref is not installed (pip install of /root/reference was not possible offline)"
+    else:
+        sys.path.insert(0, ref_dir)
+        try:
+            import deepspeed  # noqa: F401
+        except Exception as exc:
+            why = f"reference imports deepspeed at module scope and it is not installed ({type(exc).__name__})"
+    if why is None:
+        why = "reference runner not wired: no deepspeed-compatible engine available on this image"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="override depth (debugging)")
+    ap.add_argument("--seq-per-gpu", type=int, default=SEQ_PER_GPU, help="sequences per GPU per step")
+    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--no-act-ckpt", action="store_true", help="secondary number: activation checkpointing off")
+    ap.add_argument("--skip-e2e", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm(a)
+
+    import torch
+    import torch.distributed as dist
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.logging import flops_per_iteration
+    from gpt_neox_b200.ops import native
+    from gpt_neox_b200.parallel import mpu
+    from gpt_neox_b200.training import setup_model_and_optimizer, train_step
+    from gpt_neox_b200.utils import Timers
+
+    n = a.gpus
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == n, f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}"
+    assert n in LAYERS, "supported GPU counts: 1, 2, 4, 8"
+    warm = max(a.warmup, 3)
+    cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch, seq_per_gpu=a.seq_per_gpu,
+                       ckpt=not a.no_act_ckpt)
+    neox_args = NeoXArgs.from_dict(cfg)
+    neox_args.configure_distributed_args()
+    neox_args.build_tokenizer()
+    neox_args.padded_vocab_size = 50432
+    initialize_megatron(neox_args)
+    rank = neox_args.rank
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model, optimizer, lr_scheduler, _ = setup_model_and_optimizer(neox_args)
+    timers = Timers()
+    gas, mb, seq = neox_args.gradient_accumulation_steps, neox_args.train_micro_batch_size_per_gpu, neox_args.seq_length
+    vocab = neox_args.padded_vocab_size
+
+    # ---- synthetic data: a pool of distinct micro-batches, on the device and in pinned host memory
+    g = torch.Generator().manual_seed(1234 + mpu.get_data_parallel_rank())
+    pool = max(gas, 8)
+    host = [torch.randint(0, vocab, (mb, seq + 1), generator=g, dtype=torch.int64).pin_memory() for _ in range(pool)]
+    on_dev = [t.to(dev) for t in host]
+    needs_data = (not neox_args.is_pipe_parallel) or mpu.is_pipeline_first_stage() or mpu.is_pipeline_last_stage()
+
+    def stream(tensors):
+        i = 0
+        while True:
+            yield {"text": tensors[i % len(tensors)]}
+            i += 1
+
+    def run_steps(k, it, read_loss):
+        last = None
+        for _ in range(k):
+            d, _ = train_step(neox_args, timers, it if needs_data else None, model, optimizer, lr_scheduler)
+            if read_loss:
+                last = float(d["lm_loss"])          # device -> host read of the step's result
+        return last
+
+    def timed(k, it, read_loss):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = native.launch_count
+        e0.record()
+        loss = run_steps(k, it, read_loss)
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / k, native.launch_count - before, loss
+
+    run_steps(warm, stream(on_dev), True)                    # untimed warm-up
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    ms_dev, launches, _ = timed(a.steps, stream(on_dev), False)
+    ms_e2e, _, loss = (None, 0, None) if a.skip_e2e else timed(a.steps, stream(host), True)
+    clocks = sampler.stop() if rank == 0 else None
+    status = native.read_status()
+
+    tokens = neox_args.train_batch_size * seq
+    tps = tokens / (ms_dev / 1e3)
+    mfu_flops = flops_per_iteration(neox_args, 3) / (ms_dev / 1e3) / n / 1e12
+    hfu_flops = flops_per_iteration(neox_args, 4 if neox_args.checkpoint_activations else 3) / (ms_dev / 1e3) / n / 1e12
+    tp, pp = PARALLEL[n]
+    if rank == 0:
+        out = {
+            "metric": "tokens_per_sec (20B-shape 3D-parallel training; TFLOPS/GPU in tflops_per_gpu)",
+            "value": round(tps, 1), "unit": "tokens/s", "n_gpus": n, "steps": a.steps, "warmup": warm,
+            "ms_per_step": round(ms_dev, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights (small_init / wang_init)",
+            "tflops_per_gpu": {"model_c3": round(mfu_flops, 1), "hardware_c4": round(hfu_flops, 1),
+                               "formula": "24*c*B*s*L*h^2*(1+s/6h+V/16Lh) / (t*gpus)"},
+            "vs_paper_a100_tflops_per_gpu": round(hfu_flops / PAPER_TFLOPS_PER_GPU_A100, 2),
+            "config": {"model": f"GPT-NeoX-20B layer shape (h6144, 64 heads, ffn 24576, vocab 50432), "
+                                f"{neox_args.num_layers} of 44 layers" + (" = full model" if neox_args.num_layers == 44 else
+                                                                          " (depth scales with GPUs: 5.5 layers/GPU)"),
+                       "global_batch": neox_args.train_batch_size, "seq_len": seq, "micro_batch": mb,
+                       "grad_accum": gas, "activation_checkpointing": bool(neox_args.checkpoint_activations),
+                       "parallelism": f"tp{tp}" + (f"pp{pp}" if pp else "") + f"dp{world // (tp * max(pp, 1))}"
+                                      + ("+sp" if tp > 1 else "") + " zero1",
+                       "l2": "inputs larger than L2 (no flush needed)"},
+            "clocks": clocks,
+            "e2e": None if ms_e2e is None else {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
+                                                "ms_per_step": round(ms_e2e, 2),
+                                                "h2d_bytes_per_step": gas * mb * (seq + 1) * 8,
+                                                "d2h_bytes_per_step": 4, "final_loss": loss},
+            "gpu_launches": launches, "kernel_status": status,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

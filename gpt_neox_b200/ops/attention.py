@@ -108,7 +108,7 @@ _FLASH_IMPL = {"fwd": None}
 
 def have_flash_kernel() -> bool:
     if _FLASH_IMPL["fwd"] is None:
-        _FLASH_IMPL["fwd"] = hasattr(native.lib(), "neox_flash_fwd") if native.available() else False
+        _FLASH_IMPL["fwd"] = native.lib().has("neox_flash_fwd") if native.available() else False
     return _FLASH_IMPL["fwd"]
 
 

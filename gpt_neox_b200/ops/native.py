@@ -35,11 +35,41 @@ def _load(name: str, builder: str):
     return ctypes.CDLL(str(path))
 
 
+launch_count = 0   # number of kernel-launching library calls made by this process (see bench.py)
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts calls into kernel launchers (``neox_*`` entry points that take a
+    stream); pure queries such as ``neox_read_status`` are not counted."""
+    _NOT_LAUNCHES = {"neox_read_status", "neox_norm_bwd_blocks", "neox_sm_count_c"}
+
+    def __init__(self, cdll):
+        self._cdll = cdll
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            if name in self._NOT_LAUNCHES:
+                fn = raw
+            else:
+                def fn(*args, _raw=raw):
+                    global launch_count
+                    launch_count += 1
+                    return _raw(*args)
+            self._cache[name] = fn
+        return fn
+
+    def has(self, name):
+        return hasattr(self._cdll, name)
+
+
 def lib():
     """The CUDA kernel library (loaded once)."""
     global _cuda_lib
     if _cuda_lib is None:
-        _cuda_lib = _load("libneox_b200.so", "build_cuda")
+        _cuda_lib = _CountingLib(_load("libneox_b200.so", "build_cuda"))
     return _cuda_lib
 
 
