@@ -89,10 +89,11 @@ class _FlashFn(torch.autograd.Function):
         dq = torch.empty(sq, b, hq, d, dtype=q.dtype, device=q.device)
         dk = torch.empty(sk, b, hkv, d, dtype=q.dtype, device=q.device)
         dv = torch.empty(sk, b, hkv, d, dtype=q.dtype, device=q.device)
+        delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
         L = native.lib()
         ll = ctypes.c_longlong
         rc = L.neox_flash_bwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(do),
-                              native.ptr(lse), native.ptr(dq), native.ptr(dk), native.ptr(dv),
+                              native.ptr(lse), native.ptr(dq), native.ptr(dk), native.ptr(dv), native.ptr(delta),
                               sq, sk, b, hq, hkv, d,
                               ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
                               ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),

@@ -417,6 +417,27 @@ int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long
     return 0;
 }
 
+// 4-D bf16 tensor map over a strided [d3, d2, d1, d0] view (d0 contiguous; strides in elements), box
+// [b3, 1, 1, b0], 128-byte swizzled.  Used by the attention kernels to read [s, b, h, d] views in place.
+int neox_make_tmap_bf16_4d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                           unsigned long long d2, unsigned long long d3, long long s1, long long s2, long long s3,
+                           unsigned b0, unsigned b3) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return NEOX_ERR_DRIVER;
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (s1 % 8) || (s2 % 8) || (s3 % 8)) return NEOX_ERR_ALIGN;
+    cuuint64_t dims[4] = {d0, d1, d2, d3};
+    cuuint64_t strides[3] = {(cuuint64_t)s1 * 2, (cuuint64_t)s2 * 2, (cuuint64_t)s3 * 2};
+    cuuint32_t box[4] = {b0, 1, 1, b3};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    // a size-1 dimension may carry any stride; the encoder wants strides that are positive multiples of 16
+    for (int i = 0; i < 3; ++i)
+        if (strides[i] == 0) strides[i] = 16;
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : NEOX_ERR_TMAP;
+}
+
 extern "C" int neox_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
                               long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
                               const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
