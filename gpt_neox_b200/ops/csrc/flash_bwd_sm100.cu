@@ -257,7 +257,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 my_dl[half * 32 + lane] = (q < p.sq) ? p.delta[idx] : 0.f;
             }
             __syncwarp();
-            if (!mbar_wait(sdp_full, it & 1)) {
+            if (!mbar_wait_warp(sdp_full, it & 1)) {
                 if (lane == 0) atomicExch(p.status, 306);
                 ok = false;
                 break;
@@ -292,7 +292,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 pt[c] = pv;
                 ds[c] = pv * (ds[c] - my_dl[c]) * p.scale;
             }
-            if (!mbar_wait(pds_empty, (it & 1) ^ 1)) {
+            if (!mbar_wait_warp(pds_empty, (it & 1) ^ 1)) {
                 if (lane == 0) atomicExch(p.status, 307);
                 ok = false;
                 break;
@@ -304,15 +304,19 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (lane == 0) mbar_arrive(pds_full);
         }
         if (niter > 0 && ok) {
-            if (!mbar_wait(acc_full, 0)) {
+            if (!mbar_wait_warp(acc_full, 0)) {
                 if (lane == 0) atomicExch(p.status, 308);
                 ok = false;
             }
             tc_fence_after();
         }
-        if (ok && kv < p.sk) {
-            __nv_bfloat16* dkp = p.dk + (((size_t)kv * p.b + bb) * p.hkv + hk) * D;
-            __nv_bfloat16* dvp = p.dv + (((size_t)kv * p.b + bb) * p.hkv + hk) * D;
+        // tcgen05.ld is warp-collective (.sync.aligned): every lane of the warp must execute it, so the loads are
+        // guarded by warp-uniform conditions only and the per-row bound check applies to the stores.
+        ok = __all_sync(0xffffffffu, ok);
+        const bool live = kv < p.sk;
+        if (ok) {
+            __nv_bfloat16* dkp = p.dk + (((size_t)(live ? kv : 0) * p.b + bb) * p.hkv + hk) * D;
+            __nv_bfloat16* dvp = p.dv + (((size_t)(live ? kv : 0) * p.b + bb) * p.hkv + hk) * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
@@ -330,7 +334,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     q.y = pack_bf16x2(__uint_as_float(r[u * 8 + 2]), __uint_as_float(r[u * 8 + 3]));
                     q.z = pack_bf16x2(__uint_as_float(r[u * 8 + 4]), __uint_as_float(r[u * 8 + 5]));
                     q.w = pack_bf16x2(__uint_as_float(r[u * 8 + 6]), __uint_as_float(r[u * 8 + 7]));
-                    reinterpret_cast<uint4*>(dvp + c * 32)[u] = q;
+                    if (live) reinterpret_cast<uint4*>(dvp + c * 32)[u] = q;
                 }
                 if (niter > 0) {
                     tmem_ld_32x32(TM_DK + lane_base + c * 32, r);
@@ -342,7 +346,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     q.y = pack_bf16x2(__uint_as_float(r[u * 8 + 2]), __uint_as_float(r[u * 8 + 3]));
                     q.z = pack_bf16x2(__uint_as_float(r[u * 8 + 4]), __uint_as_float(r[u * 8 + 5]));
                     q.w = pack_bf16x2(__uint_as_float(r[u * 8 + 6]), __uint_as_float(r[u * 8 + 7]));
-                    reinterpret_cast<uint4*>(dkp + c * 32)[u] = q;
+                    if (live) reinterpret_cast<uint4*>(dkp + c * 32)[u] = q;
                 }
             }
         }
@@ -509,7 +513,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bool ok = true;
         for (int it = 0; it < niter; ++it) {
             const int kvj = (jb + it) * 64;
-            if (!mbar_wait(sdp_full, it & 1)) {
+            if (!mbar_wait_warp(sdp_full, it & 1)) {
                 if (lane == 0) atomicExch(p.status, 316);
                 ok = false;
                 break;
@@ -541,7 +545,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const float pv = dead ? 0.f : exp2f(t - lse2);
                 ds[c] = pv * (ds[c] - dl) * p.scale;
             }
-            if (!mbar_wait(ds_empty, (it & 1) ^ 1)) {
+            if (!mbar_wait_warp(ds_empty, (it & 1) ^ 1)) {
                 if (lane == 0) atomicExch(p.status, 317);
                 ok = false;
                 break;
@@ -552,14 +556,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (lane == 0) mbar_arrive(ds_full);
         }
         if (niter > 0 && ok) {
-            if (!mbar_wait(acc_full, 0)) {
+            if (!mbar_wait_warp(acc_full, 0)) {
                 if (lane == 0) atomicExch(p.status, 318);
                 ok = false;
             }
             tc_fence_after();
         }
-        if (ok && q < p.sq) {
-            __nv_bfloat16* dqp = p.dq + (((size_t)q * p.b + bb) * p.hq + h) * D;
+        ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
+        const bool live = q < p.sq;
+        if (ok) {
+            __nv_bfloat16* dqp = p.dq + (((size_t)(live ? q : 0) * p.b + bb) * p.hq + h) * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
@@ -577,7 +583,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     qv.y = pack_bf16x2(__uint_as_float(r[u * 8 + 2]), __uint_as_float(r[u * 8 + 3]));
                     qv.z = pack_bf16x2(__uint_as_float(r[u * 8 + 4]), __uint_as_float(r[u * 8 + 5]));
                     qv.w = pack_bf16x2(__uint_as_float(r[u * 8 + 6]), __uint_as_float(r[u * 8 + 7]));
-                    reinterpret_cast<uint4*>(dqp + c * 32)[u] = qv;
+                    if (live) reinterpret_cast<uint4*>(dqp + c * 32)[u] = qv;
                 }
             }
         }

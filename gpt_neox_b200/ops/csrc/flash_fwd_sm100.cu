@@ -203,7 +203,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float m = -INFINITY, l = 0.f;
         for (int i = 0; i < nblk; ++i) {
             const int st = i & 1;
-            if (!mbar_wait(&s_full[st], (i >> 1) & 1)) {
+            if (!mbar_wait_warp(&s_full[st], (i >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.status, 206);
                 break;
             }
@@ -248,7 +248,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             l = l * alpha + sum;
             m = mx;
-            if (!mbar_wait(p_empty, (i & 1) ^ 1)) {
+            if (!mbar_wait_warp(p_empty, (i & 1) ^ 1)) {
                 if (lane == 0) atomicExch(p.status, 207);
                 break;
             }
@@ -286,7 +286,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         bool ok = true;
         for (int i = 0; i < nblk; ++i) {
             const int st = i & 1;
-            if (!mbar_wait(&o_full[st], (i >> 1) & 1)) {
+            if (!mbar_wait_warp(&o_full[st], (i >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.status, 208);
                 ok = false;
                 break;
@@ -305,7 +305,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(&o_empty[st]);
         }
-        if (ok && !mbar_wait(l_full, 0)) {
+        if (ok && !mbar_wait_warp(l_full, 0)) {
             if (lane == 0) atomicExch(p.status, 209);
             ok = false;
         }

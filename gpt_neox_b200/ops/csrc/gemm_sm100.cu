@@ -314,7 +314,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             int m_blk, n_blk;
             tile_coords(tile, num_m, num_n, m_blk, n_blk);
-            if (!mbar_wait(&tfull[buf], bphase)) {
+            if (!mbar_wait_warp(&tfull[buf], bphase)) {
                 if (lane == 0) atomicExch(p.status, 104);
                 break;
             }

@@ -62,6 +62,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return true;
 }
 
+// Warp-wide bounded wait: every lane gets the same answer, so that the warp-collective tcgen05.ld / st that
+// usually follow are never executed by a partial warp, even on the time-out path.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -213,3 +213,60 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert native.read_status() == 0
     G.gemm(a, b)
     assert native.read_status() == 0
+
+
+@pytest.mark.parametrize("sq,sk,b,hq,hkv,d,causal,window,alibi,fused", [
+    (128, 128, 1, 1, 1, 64, True, None, False, False),
+    (256, 256, 2, 4, 4, 96, True, None, False, True),
+    (300, 300, 2, 4, 2, 64, True, None, False, False),      # GQA + ragged tiles
+    (200, 200, 1, 2, 2, 128, False, None, False, False),
+    (77, 500, 1, 2, 1, 96, True, None, False, False),       # sq < sk: bottom-right aligned causal mask
+    (512, 512, 1, 2, 2, 64, True, 100, False, False),       # sliding window
+    (512, 512, 1, 2, 2, 64, True, None, True, False),       # ALiBi
+    (1024, 1024, 1, 4, 4, 96, True, None, False, True),
+])
+def test_flash_attention_fwd_bwd(sq, sk, b, hq, hkv, d, causal, window, alibi, fused):
+    from gpt_neox_b200.ops import attention as A
+    torch.manual_seed(0)
+    if fused and hq == hkv:
+        qkv = torch.randn(sq, b, hq, 3 * d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        q, k, v = qkv[..., :d], qkv[..., d:2 * d], qkv[..., 2 * d:]
+        leaves = [qkv]
+    else:
+        q = torch.randn(sq, b, hq, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        k = torch.randn(sk, b, hkv, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        v = torch.randn(sk, b, hkv, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        leaves = [q, k, v]
+    slopes = (torch.rand(hq, device=DEV) * 0.1) if alibi else None
+    assert A.have_flash_kernel()
+    out = A.flash_attention(q, k, v, causal=causal, window=window, alibi_slopes=slopes)
+    g = torch.randn_like(out)
+    out.backward(g)
+    assert native.read_status() == 0
+    refl = [l.detach().float().requires_grad_() for l in leaves]
+    if len(refl) == 1:
+        rq, rk, rv = refl[0][..., :d], refl[0][..., d:2 * d], refl[0][..., 2 * d:]
+    else:
+        rq, rk, rv = refl
+    ref = A.attention_ref(rq, rk, rv, causal, None, window, slopes)
+    ref.backward(g.float())
+    _close(out, ref, 3e-2)
+    for got, want in zip(leaves, refl):
+        _close(got.grad, want.grad, 0.02 + 0.02 * want.grad.abs().max().item(), rtol=3e-2)
+
+
+def test_flash_attention_is_deterministic():
+    from gpt_neox_b200.ops import attention as A
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(512, 2, 4, 96, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    outs, grads = [], []
+    for _ in range(2):
+        for t in (q, k, v):
+            t.grad = None
+        o = A.flash_attention(q, k, v)
+        o.backward(torch.ones_like(o))
+        outs.append(o.detach().clone())
+        grads.append([t.grad.clone() for t in (q, k, v)])
+    assert torch.equal(outs[0], outs[1])
+    for a, b_ in zip(grads[0], grads[1]):
+        assert torch.equal(a, b_)      # no atomics anywhere: bitwise repeatable
