@@ -186,7 +186,8 @@ class ColumnParallelLinear(nn.Module):
         bias = None if self.skip_bias_add else self.bias
         out = fused_linear(x, self.weight, bias, act=act)
         if self.gather_output:
-            assert not self.sequence_parallel, "sequence_parallel is incompatible with gather_output"
+            # after the sequence all-gather every rank holds the full sequence, so gathering the output
+            # features is well defined (the reference asserts here, which rules out inference under SP)
             out = M.gather_from_model_parallel_region(out)
         return out, (self.bias if self.skip_bias_add else None)
 
