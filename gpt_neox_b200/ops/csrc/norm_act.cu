@@ -575,3 +575,78 @@ int neox_gated_act_bwd(const void* g, const void* x, void* dx, long long rows, i
 }
 
 }  // extern "C"
+
+// =====================================================================================================
+// Allocation-free LayerNorm backward (declared in neox_noalloc.h; no counterpart in the reference).
+//
+// neox_layernorm_bwd() above needs a caller-provided scratch buffer for the per-CTA partial sums of
+// dgamma / dbeta.  Some callers cannot provide one: a process whose device memory is already fully
+// reserved (for instance by a framework's caching allocator that was sized to the whole GPU), or a
+// latency-critical path that must not hit cudaMalloc's implicit device synchronisation.  For them the
+// scratch lives in a file-scope device array that is part of the loaded library image.
+//
+// Rules that follow from that design:
+//   * limits: cols <= NEOX_NOALLOC_MAX_COLS, and the kernel uses at most NEOX_NOALLOC_MAX_BLOCKS CTAs;
+//     larger requests are rejected with NEOX_ERR_TOO_LARGE (see neox_noalloc_last_error());
+//   * the array costs NEOX_NOALLOC_MAX_BLOCKS * NEOX_NOALLOC_MAX_COLS * 2 * 4 bytes (20 MiB) on every GPU
+//     that loads the library, until the process exits;
+//   * in host code the array's name is only a stand-in for the symbol, not a device address: the device
+//     address is looked up with cudaGetSymbolAddress once per device (with that device current) by the
+//     first call on that device, which therefore should be made before any stream capture begins;
+//   * every call on a device uses the same array.  The kernel fully overwrites the part it reads (nothing
+//     has to be zero on entry, and stale contents of earlier calls are never read), but two calls that
+//     overlap on the GPU (different streams) race on it: serialise them.
+//   * the entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+#include "neox_noalloc.h"
+#include <stdio.h>
+
+static __device__ __align__(256) float g_noalloc_scratch[2LL * NEOX_NOALLOC_MAX_BLOCKS * NEOX_NOALLOC_MAX_COLS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEV = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEV] = {nullptr};
+char g_noalloc_err[256] = "";
+
+int noalloc_fail(int code, const char* fmt, long long a, long long b) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), fmt, a, b);
+    return code;
+}
+
+// Device address of the scratch array on the current device (looked up once per device).
+int noalloc_scratch(float** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEV)
+        return noalloc_fail(NEOX_ERR_DRIVER, "no current CUDA device (index %lld, limit %lld)", dev, NOALLOC_MAX_DEV);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return noalloc_fail(NEOX_ERR_DRIVER, "cudaGetSymbolAddress failed with code %lld on device %lld", (long long)e, dev);
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" const char* neox_noalloc_last_error() { return g_noalloc_err; }
+
+extern "C" int neox_layernorm_bwd_noalloc(const void* g, const void* x, const void* gamma, const float* mean,
+                                          const float* rstd, void* dx, float* dgamma, float* dbeta, int rows,
+                                          int cols, int dtype, void* stream) {
+    if (cols <= 0 || rows < 0 || cols % 8)
+        return noalloc_fail(NEOX_ERR_SHAPE, "cols must be a positive multiple of 8 (got %lld; rows %lld)", cols, rows);
+    if (cols > NEOX_NOALLOC_MAX_COLS)
+        return noalloc_fail(NEOX_ERR_TOO_LARGE, "cols = %lld exceeds the built-in scratch limit of %lld columns", cols,
+                            NEOX_NOALLOC_MAX_COLS);
+    const int nblk = neox_norm_bwd_blocks(rows);
+    if (nblk > NEOX_NOALLOC_MAX_BLOCKS)
+        return noalloc_fail(NEOX_ERR_TOO_LARGE, "this GPU would use %lld CTAs, the built-in scratch holds %lld", nblk,
+                            NEOX_NOALLOC_MAX_BLOCKS);
+    float* ws = nullptr;
+    const int rc = noalloc_scratch(&ws);
+    if (rc) return rc;
+    g_noalloc_err[0] = 0;
+    return launch_norm_bwd<false>(g, x, gamma, mean, rstd, dx, dgamma, dbeta, ws, rows, cols, 0.f, dtype,
+                                  static_cast<cudaStream_t>(stream));
+}
