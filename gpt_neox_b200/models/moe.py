@@ -1,0 +1,201 @@
+"""Mixture-of-experts MLP block with expert parallelism.
+
+Capabilities of the two MoE back-ends the reference can be configured with
+(``megatron/model/transformer.py:1076-1164``): DeepSpeed-style top-k gating with a capacity factor
+(token dropping, ``moe_min_capacity``) and MegaBlocks-style dropless routing (``moe_token_dropping:
+false``), optional GLU experts (``moe_glu``), router jitter, fp32 load-balancing statistics, and expert
+parallelism over ``moe_expert_parallel_size`` ranks of the data-parallel group.
+
+Data flow for T local tokens, E experts, top-k::
+
+    probs = softmax(router(x))                       [T, E]
+    (w, e) = topk(probs)                             [T, k]      (weights renormalised when k > 1)
+    sort the T*k assignments by expert -> contiguous per-expert segments (capacity applied here)
+    all-to-all over the expert-parallel group: every rank receives the segments of ITS experts
+    per local expert: h = act(seg W1^T) W2^T         tcgen05 GEMMs on the variable-length segments
+    all-to-all back, un-sort, y[token] += w * out
+
+The auxiliary load-balancing loss returned with the output is ``E * sum_e f_e * P_e`` (``f_e`` fraction of
+assignments routed to expert e, ``P_e`` mean router probability); ``training.py`` scales it by
+``moe_loss_coeff``.  Expert weights are tagged ``expert_parallel`` so the optimizer reduces their gradients
+over the expert-data-parallel group only.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import functional as OF
+from ..ops.linear import linear as fused_linear
+from ..parallel import mpu
+from ..parallel.rng import get_cuda_rng_tracker
+
+
+class _AllToAll(torch.autograd.Function):
+    """Variable-split all-to-all over the expert-parallel group; backward swaps the split lists."""
+
+    @staticmethod
+    def forward(ctx, x, out_splits, in_splits, group):
+        ctx.group, ctx.out_splits, ctx.in_splits = group, out_splits, in_splits
+        out = x.new_empty((sum(out_splits), *x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=out_splits, input_split_sizes=in_splits,
+                               group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        out = g.new_empty((sum(ctx.in_splits), *g.shape[1:]))
+        dist.all_to_all_single(out, g.contiguous(), output_split_sizes=ctx.in_splits,
+                               input_split_sizes=ctx.out_splits, group=ctx.group)
+        return out, None, None, None
+
+
+class Router(nn.Module):
+    def __init__(self, neox_args, num_experts):
+        super().__init__()
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
+        self.layer = nn.Linear(neox_args.hidden_size, num_experts, bias=False, device=dev,
+                               dtype=neox_args.params_dtype)
+        nn.init.normal_(self.layer.weight, mean=0.0, std=neox_args.init_method_std)
+        self.top_k = neox_args.moe_top_k
+        self.jitter_eps = neox_args.moe_jitter_eps
+        self.fp32 = neox_args.moe_lbl_in_fp32
+
+    def forward(self, x):
+        if self.training and self.jitter_eps:
+            noise = torch.empty_like(x).uniform_(1.0 - self.jitter_eps, 1.0 + self.jitter_eps)
+            x = x * noise
+        logits = self.layer(x)
+        probs = F.softmax(logits.float() if self.fp32 or True else logits, dim=-1)
+        w, idx = torch.topk(probs, self.top_k, dim=-1)
+        if self.top_k > 1:
+            w = w / w.sum(dim=-1, keepdim=True)
+        return probs, w, idx
+
+
+class ParallelMoE(nn.Module):
+    def __init__(self, neox_args, init_method, output_layer_init_method, num_experts):
+        super().__init__()
+        self.num_experts = num_experts
+        self.ep = mpu.get_expert_parallel_world_size()
+        assert num_experts % self.ep == 0, f"{num_experts} experts not divisible by expert-parallel size {self.ep}"
+        self.local_experts = num_experts // self.ep
+        self.top_k = neox_args.moe_top_k
+        self.token_dropping = neox_args.moe_token_dropping
+        self.train_cf = neox_args.moe_train_capacity_factor
+        self.eval_cf = neox_args.moe_eval_capacity_factor
+        self.min_capacity = neox_args.moe_min_capacity
+        self.glu = neox_args.moe_glu
+        self.activation = neox_args.activation
+        h = neox_args.hidden_size
+        ffn = neox_args.intermediate_size or int((neox_args.expansion_factor or 4) * h)
+        self.ffn = ffn
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
+        dt = neox_args.params_dtype
+        self.router = Router(neox_args, num_experts)
+        n_in = ffn * (2 if self.glu else 1)
+        self.w1 = nn.Parameter(torch.empty(self.local_experts, n_in, h, device=dev, dtype=dt))
+        self.w2 = nn.Parameter(torch.empty(self.local_experts, h, ffn, device=dev, dtype=dt))
+        # Every expert is initialised from its own seed (a function of the GLOBAL expert id), so the weights do
+        # not depend on how experts are spread over expert-parallel ranks.
+        ep_rank = mpu.get_expert_parallel_rank()
+        for e in range(self.local_experts):
+            gid = ep_rank * self.local_experts + e
+            with torch.random.fork_rng(devices=[]):
+                torch.manual_seed(neox_args.seed + 7919 * (gid + 1))
+                tmp1 = torch.empty(n_in, h, dtype=torch.float)
+                tmp2 = torch.empty(h, ffn, dtype=torch.float)
+                init_method(tmp1)
+                output_layer_init_method(tmp2)
+            with torch.no_grad():
+                self.w1[e].copy_(tmp1)
+                self.w2[e].copy_(tmp2)
+        if self.ep > 1:
+            self.w1.expert_parallel = True
+            self.w2.expert_parallel = True
+        self.w1.moe_expert = self.w2.moe_expert = True
+
+    # ------------------------------------------------------------------ expert compute
+    def _expert(self, e, seg):
+        if seg.shape[0] == 0:
+            return seg.new_zeros((0, self.w2.shape[1]))
+        w1, w2 = self.w1[e], self.w2[e]
+        if self.glu:
+            hdn = OF.gated_act(fused_linear(seg, w1), "swiglu" if self.activation in ("swiglu", "silu") else "geglu")
+        elif self.activation == "gelu":
+            hdn = fused_linear(seg, w1, act="gelu")
+        else:
+            hdn = OF.get_activation(self.activation)(fused_linear(seg, w1))
+        return fused_linear(hdn, w2)
+
+    def _capacity(self, tokens):
+        cf = self.train_cf if self.training else self.eval_cf
+        return max(self.min_capacity, int(math.ceil(cf * tokens * self.top_k / self.num_experts)))
+
+    def forward(self, hidden_states):
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, shape[-1])
+        T, E, k = x.shape[0], self.num_experts, self.top_k
+        probs, w, idx = self.router(x)
+        # ---- load-balancing statistics
+        flat_e = idx.reshape(-1)
+        counts = torch.bincount(flat_e, minlength=E)
+        f = counts.float() / float(T * k)
+        P = probs.mean(dim=0)
+        lbl = E * torch.sum(f.detach() * P)
+        # ---- sort assignments by expert (stable: token order preserved inside an expert)
+        order = torch.argsort(flat_e, stable=True)
+        sorted_e = flat_e[order]
+        token_of = order // k
+        keep = torch.ones_like(sorted_e, dtype=torch.bool)
+        if self.token_dropping:
+            cap = self._capacity(T)
+            starts = torch.cumsum(counts, 0) - counts
+            pos = torch.arange(T * k, device=x.device) - starts[sorted_e]
+            keep = pos < cap
+            counts = torch.clamp(counts, max=cap)
+        sel = order[keep]
+        tok = token_of[keep]
+        xs = x[tok]                                              # [A, h] grouped by expert
+        gate = w.reshape(-1)[sel].to(x.dtype)
+        if self.ep > 1:
+            grp = mpu.get_expert_parallel_group()
+            send = counts.view(self.ep, self.local_experts)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send.contiguous(), group=grp)
+            in_splits = send.sum(1).tolist()
+            out_splits = recv.sum(1).tolist()
+            recv_l = recv.tolist()
+            xr = _AllToAll.apply(xs, out_splits, in_splits, grp)
+            # received layout: for each source rank, its segments for local experts 0..L-1
+            outs = torch.empty((xr.shape[0], shape[-1]), dtype=x.dtype, device=x.device)
+            pieces, off = [[] for _ in range(self.local_experts)], 0
+            for r in range(self.ep):
+                for e in range(self.local_experts):
+                    n = recv_l[r][e]
+                    pieces[e].append((off, n))
+                    off += n
+            res_parts = {}
+            for e in range(self.local_experts):
+                seg = torch.cat([xr[o:o + n] for o, n in pieces[e]]) if pieces[e] else xr[:0]
+                out_e = self._expert(e, seg)
+                o2 = 0
+                for o, n in pieces[e]:
+                    res_parts[o] = out_e[o2:o2 + n]
+                    o2 += n
+            outs = torch.cat([res_parts[o] for o in sorted(res_parts)]) if res_parts else xr
+            ys = _AllToAll.apply(outs, in_splits, out_splits, grp)
+        else:
+            cl = counts.tolist()
+            parts, off = [], 0
+            for e in range(E):
+                parts.append(self._expert(e, xs[off:off + cl[e]]))
+                off += cl[e]
+            ys = torch.cat(parts) if parts else xs
+        y = torch.zeros_like(x)
+        y.index_add_(0, tok, ys * gate[:, None])
+        return y.reshape(shape), lbl.to(hidden_states.dtype)
