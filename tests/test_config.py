@@ -133,7 +133,7 @@ def test_every_shipped_config_loads(path):
     files = [path]
     if "num_layers" not in keys:
         pytest.skip("overlay file")
-    if "data_path" not in keys and "train_data_paths" not in keys:
+    if not keys & {"data_path", "train_data_paths", "vocab_file", "save", "load"}:
         files.append(os.path.join(CONFIGS, "local_setup.yml"))
     over = {} if "global_num_gpus" in keys else {"global_num_gpus": 8}
     a = NeoXArgs.from_ymls(files, overwrite_values=over)
