@@ -28,7 +28,7 @@ NVCC_FLAGS = [
     "-O3", "-lineinfo", "-std=c++17", "--use_fast_math",
     "-Xcompiler", "-fPIC",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v3", "-fopenmp"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v3", "-fopenmp", "-ffp-contract=off"]
 
 
 def _nvcc() -> str | None:

@@ -53,7 +53,8 @@ def load_config(path):
 
 
 def get_key(cfg, key, default=None):
-    return cfg.get(key, cfg.get(key.replace("_", "-"), default))
+    v = cfg.get(key, cfg.get(key.replace("_", "-"), None))
+    return default if v is None else v
 
 
 def load_partitions(input_dir, mp, layer_idx, sequential):

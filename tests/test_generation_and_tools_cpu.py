@@ -1,0 +1,158 @@
+"""Generation (kv cache vs recompute, sampling filters), Hugging Face conversion in both directions, LR schedule,
+objectives."""
+import math
+import os
+
+import pytest
+import torch
+
+from common import make_args, run_distributed
+
+
+def _native_model(cfg):
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.training import setup_model_and_optimizer
+    args = make_args(**cfg)
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    model, _, _, _ = setup_model_and_optimizer(args, use_cache=True)
+    return args, model
+
+
+def _generation(rank, world):
+    from gpt_neox_b200.text_generation import filter_logits, stream_tokens
+    args, model = _native_model({"optimizer": None, "no_load_optim": True, "seq_length": 48,
+                                 "max_position_embeddings": 48})
+    model.module.inference_mode(use_cache=True)
+    prompts = [[5, 6, 7, 8], [9, 10]]
+    outs = {}
+    for recompute in (False, True):
+        model.module.inference_mode(use_cache=not recompute)
+        last = None
+        for last in stream_tokens(args, model, prompts, eos_token_id=-1, maximum_tokens=8, recompute=recompute):
+            pass
+        outs[recompute] = last[0].clone()
+    assert torch.equal(outs[False], outs[True]), (outs[False], outs[True])
+    assert outs[False].shape[1] == 12
+    # nucleus / top-k filters
+    logits = torch.tensor([[2.0, 1.0, 0.5, -1.0], [0.0, 3.0, 0.0, 0.0]])
+    k = filter_logits(logits.clone(), top_k=2)
+    assert torch.isinf(k[0, 2:]).all() and torch.isfinite(k[0, :2]).all()
+    p = filter_logits(logits.clone(), top_p=0.5)
+    assert torch.isfinite(p[1, 1]) and torch.isinf(p[1, 0])
+
+
+def test_generation_cache_matches_recompute():
+    run_distributed(_generation, 1)
+
+
+def _hf_round_trip(rank, world, arch, tmp):
+    from gpt_neox_b200.checkpointing import save_checkpoint
+    from gpt_neox_b200.tools.ckpts import convert_hf_to_sequential, convert_neox_to_hf
+    cfg = {"save": tmp, "optimizer": None, "no_load_optim": True}
+    if arch == "llama":
+        cfg.update({"gpt_j_residual": False, "norm": "rmsnorm", "rms_norm_epsilon": 1e-5, "activation": "swiglu",
+                    "use_bias_in_mlp": False, "use_bias_in_attn_linear": False, "use_bias_in_norms": False,
+                    "rotary_pct": 1.0, "intermediate_size": 192, "num_kv_heads": 2, "make_vocab_size_divisible_by": 64})
+    args, model = _native_model(cfg)
+    model.module.train_mode()
+    save_checkpoint(args, 1, model, None, None)
+    tokens = torch.randint(0, args.padded_vocab_size, (2, args.seq_length))
+    pos = torch.arange(args.seq_length).unsqueeze(0).expand_as(tokens)
+    with torch.no_grad():
+        out = model.module((tokens, pos, None))
+        native_logits = out[0] if isinstance(out, tuple) else out
+    conf = {k: getattr(args, k) for k in ("num_layers", "hidden_size", "num_attention_heads", "max_position_embeddings",
+                                          "rotary_pct", "rotary_emb_base", "layernorm_epsilon", "rms_norm_epsilon",
+                                          "gpt_j_residual", "no_weight_tying", "padded_vocab_size", "model_parallel_size",
+                                          "intermediate_size", "expansion_factor", "activation", "mlp_multiple_of",
+                                          "num_kv_heads", "use_bias_in_attn_linear", "init_method_std")}
+    hf = convert_neox_to_hf.convert(os.path.join(tmp, "global_step1"), conf, architecture=arch)
+    hf.eval()
+    with torch.no_grad():
+        hf_logits = hf(tokens).logits
+    # RMSNorm here keeps the reference's form x / (rms + eps); Hugging Face uses x * rsqrt(mean(x^2) + eps).  With
+    # eps = 1e-5 and small activations the two differ at the 1e-3 level, hence the looser bound for llama.
+    atol = 2e-4 if arch == "neox" else 5e-3
+    assert torch.allclose(hf_logits, native_logits, atol=atol, rtol=1e-3), (hf_logits - native_logits).abs().max()
+    # and back: HF -> native sequential shards (tensor-parallel degree 2) -> merged again equals the original
+    shards = convert_hf_to_sequential.convert(hf, mp=2, architecture=arch)
+    native_sd = model.module.state_dict()
+    for key, val in native_sd.items():
+        if "inv_freq" in key or key not in shards[0]:
+            continue
+        a, b = shards[0][key], shards[1][key]
+        if a.shape == val.shape:           # replicated (norms) or divided biases
+            merged = a + b if key.endswith(("dense.bias", "linear2.bias")) else a
+        elif key.endswith(("attention.dense.weight", "mlp.linear2.weight")):
+            merged = torch.cat([a, b], dim=1)
+        elif key.endswith("mlp.linear1.weight") and arch == "llama":
+            ua, ga = a.chunk(2, 0)
+            ub, gb = b.chunk(2, 0)
+            merged = torch.cat([ua, ub, ga, gb], 0)
+        elif key.endswith("query_key_value.weight") and arch == "llama":
+            continue                        # GQA shards are [Q|K|V] per rank; covered by the logits check above
+        else:
+            merged = torch.cat([a, b], dim=0)
+        assert torch.allclose(merged, val, atol=1e-6), key
+
+
+@pytest.mark.parametrize("arch", ["neox", "llama"])
+def test_hf_conversion_round_trip(arch, tmp_path):
+    run_distributed(_hf_round_trip, 1, arch, str(tmp_path))
+
+
+def test_annealing_lr_shapes():
+    from gpt_neox_b200.learning_rates import AnnealingLR
+
+    class Opt:
+        param_groups = [{"lr": 0.0}]
+    for style in ("linear", "cosine", "exponential", "constant"):
+        o = Opt()
+        s = AnnealingLR(o, start_lr=1.0, warmup_iter=10, total_iters=110, decay_style=style, last_iter=0, min_lr=0.1)
+        lrs = []
+        for _ in range(120):
+            s.step()
+            lrs.append(o.param_groups[0]["lr"])
+        assert abs(lrs[4] - 0.5) < 1e-9 and abs(lrs[9] - 1.0) < 1e-9          # linear warm-up
+        assert min(lrs[10:]) >= 0.1 - 1e-12
+        if style == "cosine":
+            assert abs(lrs[59] - (0.1 + 0.9 / 2 * (math.cos(math.pi * 0.5) + 1))) < 1e-9
+        if style != "constant":
+            assert lrs[109] <= lrs[20]
+    sd = s.state_dict()
+    s2 = AnnealingLR(Opt(), 1.0, 10, 110, "constant", 0, 0.1)
+    s2.load_state_dict(sd)
+    assert s2.num_iters == s.num_iters
+
+
+def test_objectives_match_dense_formulas():
+    from gpt_neox_b200 import objectives as O
+    torch.manual_seed(0)
+    B, S, V = 4, 6, 32
+    logits = torch.randn(B, S, V, requires_grad=True)
+    ref_logits = torch.randn(B, S, V)
+    labels = torch.randint(0, V, (B, S))
+    mask = (torch.rand(B, S) > 0.3).float()
+    lp = torch.gather(logits.log_softmax(-1), 2, labels[..., None]).squeeze(2)
+    assert torch.allclose(O.get_logp(logits, labels), lp, atol=1e-5)
+    loss, m = O.dpo_loss(logits, labels, mask, beta=0.1, ref_logits=ref_logits)
+    rl = torch.gather(ref_logits.log_softmax(-1), 2, labels[..., None]).squeeze(2)
+    pm, nm = mask.chunk(2, 0)
+    pol = (lp * mask).sum(-1)
+    ref = (rl * mask).sum(-1)
+    want = -torch.nn.functional.logsigmoid(0.1 * ((pol[:2] - pol[2:]) - (ref[:2] - ref[2:]))).mean()
+    assert torch.allclose(loss, want, atol=1e-5)
+    loss.backward()
+    assert logits.grad is not None and torch.isfinite(logits.grad).all()
+    rewards = torch.randn(B, S)
+    l2, _ = O.reinforce_loss(logits.detach(), labels, mask, rewards, rewards[:, 0], kl_impl="mse", kl_beta=0.1,
+                             ref_logits=ref_logits)
+    want2 = (((-lp.detach() * rewards) + 0.1 * 0.5 * (lp.detach() - rl) ** 2) * mask).sum(-1).div(mask.sum()).mean()
+    assert torch.allclose(l2, want2, atol=1e-5)
+    vals = torch.randn(B, S, 1)
+    one = torch.zeros(B, S)
+    one[:, -1] = 1
+    l3, m3 = O.reward_model_loss(vals, one)
+    want3 = -torch.nn.functional.logsigmoid(vals[:2, -1, 0] - vals[2:, -1, 0]).mean()
+    assert torch.allclose(l3, want3, atol=1e-6)
