@@ -72,22 +72,21 @@ class ParallelMLP(nn.Module):
         if not self.is_gated and self.activation_type != "gelu":
             self.act = OF.get_activation(self.activation_type)
 
-    def forward(self, hidden_states, residual=None):
-        """Returns ``(output, output_bias)``.  ``residual`` is folded into linear2's epilogue when legal."""
+    def forward(self, hidden_states, residual=None, partial_add=None, post_residual=None):
+        """Returns ``(output, output_bias)``; ``residual`` is added by linear2 (see ``RowParallelLinear.forward``).
+        With ``post_residual`` it returns ``reduce(mlp + bias + partial_add) + post_residual`` as one tensor."""
         l1 = self.linear1
         if self.activation_type == "gelu":
             # bias + GeLU in the GEMM epilogue
-            if l1.sequence_parallel:
-                x = M.gather_from_sequence_parallel_region(hidden_states, l1.seq_dim)
-            else:
-                x = M.copy_to_model_parallel_region(hidden_states)
-            inter = fused_linear(x, l1.weight, l1.bias, act="gelu")
+            inter = l1.matmul(hidden_states, l1.bias, act="gelu")
         else:
             inter, bias = l1(hidden_states)
             if self.is_gated:
                 inter = OF.gated_act(inter, self.activation_type, bias)
             else:
                 inter = self.act(inter + bias if bias is not None else inter)
+        if post_residual is not None:
+            return self.linear2.forward_reduced(inter, partial_add, post_residual)
         return self.linear2(inter, residual=residual)
 
 
@@ -370,12 +369,13 @@ class ParallelTransformerLayer(nn.Module):
                 a_out, a_bias = self.attention(x1, attention_mask, layer_past=layer_past, residual=attn_res)
                 if a_bias is not None:
                     a_out = a_out + a_bias
-                m_out, m_bias = self.mlp(x2, residual=a_out)
-                if m_bias is not None:
-                    m_out = m_out + m_bias
                 if self.tp == 1:
+                    m_out, m_bias = self.mlp(x2, residual=a_out)
+                    if m_bias is not None:
+                        m_out = m_out + m_bias
                     return m_out, moe_loss
-                return residual + self._reduce(m_out), moe_loss
+                # one reduction for both partial sums, fused with the last GEMM:  reduce(mlp + b_m + attn + b_a) + x
+                return self.mlp(x2, partial_add=a_out, post_residual=residual), moe_loss
             a_out, a_bias = self.attention(x1, attention_mask, layer_past=layer_past)
             if self.use_cache:
                 a_out, presents = a_out
@@ -392,7 +392,7 @@ class ParallelTransformerLayer(nn.Module):
 
         # sequential residual
         residual = x
-        can_fuse_res = fuse and self.tp == 1 and not self.use_cache
+        can_fuse_res = fuse and not self.use_cache
         a_out, a_bias = self.attention(self.input_layernorm(x), attention_mask, layer_past=layer_past,
                                        residual=residual if (can_fuse_res and self.attention.dense.bias is None) else None)
         if self.use_cache:

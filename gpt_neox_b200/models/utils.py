@@ -36,7 +36,7 @@ def norm_parameters(module):
     sequence shard only (all norm gains / biases, incl. per-head qk norms)."""
     out = []
     for name, p in module.named_parameters():
-        if "norm" in name.lower() and p.requires_grad:
+        if p.requires_grad and ("norm" in name.lower() or getattr(p, "sequence_parallel_grad_sync", False)):
             out.append(p)
     return out
 

@@ -16,7 +16,7 @@
 //
 // All barrier waits are bounded (see sm100_ptx.cuh); on a time-out the kernel records a code in the
 // status word, leaves its loops, frees its tensor memory and returns.
-#include "sm100_ptx.cuh"
+#include "gemm_common.cuh"
 #include "neox_b200.h"
 #include <mutex>
 #include <unordered_map>
@@ -25,159 +25,9 @@
 
 using namespace sm100;
 
+using namespace gemm;
+
 namespace {
-
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;
-constexpr int STAGES = 4;
-constexpr int UMMA_K = 16;
-constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int B_STAGE_BYTES = BN * BK * 2;
-constexpr int NUM_THREADS = 192;
-constexpr int GROUP_M = 16;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 1024;
-
-struct GemmParams {
-    int M, N, K;
-    int a_mn, b_mn;
-    void* D;
-    long long ldd;
-    int d_fp32;
-    const __nv_bfloat16* bias;
-    const void* add;
-    long long ldadd;
-    int add_fp32;
-    __nv_bfloat16* preact;
-    long long ldpre;
-    const __nv_bfloat16* aux;
-    long long ldaux;
-    int act;
-    float alpha;
-    int vec_ok;
-    int* status;
-};
-
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-    const int per_group = GROUP_M * num_n;
-    const int group = tile / per_group;
-    const int first_m = group * GROUP_M;
-    const int gsize = min(num_m - first_m, GROUP_M);
-    const int in_group = tile - group * per_group;
-    m_blk = first_m + in_group % gsize;
-    n_blk = in_group / gsize;
-}
-
-// Apply the fused epilogue to 32 consecutive columns of one output row.
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row, int col0, const GemmParams& p) {
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-    const bool full = p.vec_ok && (col0 + 32 <= p.N);
-    if (full) {
-        if (p.bias) {
-            const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 b = __ldg(b4 + j);
-                uint32_t w[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    v[j * 8 + t * 2] += bf16_lo(w[t]);
-                    v[j * 8 + t * 2 + 1] += bf16_hi(w[t]);
-                }
-            }
-        }
-        if (p.preact) {
-            uint4* o = reinterpret_cast<uint4*>(p.preact + (long long)row * p.ldpre + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 q;
-                q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-                q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-                q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-                q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-                o[j] = q;
-            }
-        }
-        if (p.act == 1) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-        } else if (p.act == 2) {
-            const uint4* a4 = reinterpret_cast<const uint4*>(p.aux + (long long)row * p.ldaux + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 a = __ldg(a4 + j);
-                uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    v[j * 8 + t * 2] *= dgelu_tanh(bf16_lo(w[t]));
-                    v[j * 8 + t * 2 + 1] *= dgelu_tanh(bf16_hi(w[t]));
-                }
-            }
-        }
-        if (p.add) {
-            if (p.add_fp32) {
-                const float4* a4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.add) +
-                                                                   (long long)row * p.ldadd + col0);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float4 a = a4[j];
-                    v[j * 4 + 0] += a.x;
-                    v[j * 4 + 1] += a.y;
-                    v[j * 4 + 2] += a.z;
-                    v[j * 4 + 3] += a.w;
-                }
-            } else {
-                const uint4* a4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.add) +
-                                                                 (long long)row * p.ldadd + col0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint4 a = a4[j];
-                    uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        v[j * 8 + t * 2] += bf16_lo(w[t]);
-                        v[j * 8 + t * 2 + 1] += bf16_hi(w[t]);
-                    }
-                }
-            }
-        }
-        if (p.d_fp32) {
-            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-        } else {
-            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 q;
-                q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-                q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-                q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-                q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-                o[j] = q;
-            }
-        }
-    } else {
-        // ragged / unaligned edge: element-wise with bounds checks
-        for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            if (col >= p.N) break;
-            float x = v[i];
-            if (p.bias) x += __bfloat162float(p.bias[col]);
-            if (p.preact) p.preact[(long long)row * p.ldpre + col] = __float2bfloat16(x);
-            if (p.act == 1) x = gelu_tanh(x);
-            else if (p.act == 2) x *= dgelu_tanh(__bfloat162float(p.aux[(long long)row * p.ldaux + col]));
-            if (p.add) {
-                if (p.add_fp32) x += reinterpret_cast<const float*>(p.add)[(long long)row * p.ldadd + col];
-                else x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.add)[(long long)row * p.ldadd + col]);
-            }
-            if (p.d_fp32) reinterpret_cast<float*>(p.D)[(long long)row * p.ldd + col] = x;
-            else reinterpret_cast<__nv_bfloat16*>(p.D)[(long long)row * p.ldd + col] = __float2bfloat16(x);
-        }
-    }
-}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,

@@ -1,0 +1,397 @@
+"""Tensor-parallel linear layers whose collective runs INSIDE the tcgen05 GEMM kernel.
+
+The NCCL formulation of a Megatron layer (``megatron/mpu/layers.py:560-590,760-794`` and the mappings in
+``megatron/mpu/mappings.py``) serialises "all-gather, then GEMM" and "GEMM, then reduce-scatter / all-reduce".
+Here the GEMM kernel (``ops/csrc/comm_gemm_sm100.cu``) reads gathered operands tile by tile straight from the peers'
+symmetric memory with TMA and pushes scattered outputs tile by tile into the owner's receive buffer, so NVLink
+traffic overlaps the tensor-core work:
+
+====================  =========================================  ==========================================
+layer, pass           NCCL form                                  fused form
+====================  =========================================  ==========================================
+column, fwd (SP)      all-gather(x) ; y = x W^T                  publish(x) ; GEMM reading A from all ranks
+column, dgrad (SP)    dx = dy W ; reduce-scatter                 GEMM pushing row blocks ; owner-side reduce
+column, wgrad (SP)    all-gather(x) ; dW = dy^T x                publish(x) ; GEMM reading B from all ranks
+row, fwd (SP)         y = x W^T ; reduce-scatter                 GEMM pushing row blocks ; reduce (+bias, +res)
+row, dgrad+wgrad(SP)  all-gather(dy) ; two GEMMs                 publish(dy) ; two GEMMs reading A remotely
+row, fwd (no SP)      y = x W^T ; all-reduce                     push ; reduce ; broadcast-store ; copy
+column, dgrad(no SP)  dx = dy W ; all-reduce                     same
+====================  =========================================  ==========================================
+
+Buffers are double-buffered by epoch parity and guarded by "done" flags, so any interleaving of these ops that is
+identical on all ranks of the group is safe.  Shapes the kernels do not take (row shard not a multiple of 128,
+groups larger than 8, CPU tensors) fall back to the NCCL mappings; ``NEOX_FUSED_TP_COMM=0`` disables the fused path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import gemm as G
+from ..ops import native
+from . import mpu
+from . import symm_mem as S
+
+_workspaces = {}
+_disabled_reason = None
+
+
+def enabled() -> bool:
+    return os.environ.get("NEOX_FUSED_TP_COMM", "1") != "0" and torch.cuda.is_available()
+
+
+class Workspace:
+    """Per-process-group symmetric buffers + epoch counters."""
+
+    def __init__(self, group):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.pad = S.SignalPad(group)
+        self.bufs = {"ag": [None, None], "recv": [None, None], "gath": [None, None]}
+        self.ag_epoch = 0
+        self.rs_epoch = 0
+        self._gath_last = [0, 0]
+        self.dev_null = ctypes.c_void_p(0)
+
+    def _buf(self, kind, parity, nbytes):
+        b = self.bufs[kind][parity]
+        if b is None or b.nbytes < nbytes:
+            # collective growth: shapes are identical on all ranks, so every rank gets here at the same op
+            if b is not None:
+                b.close()
+            size = (int(nbytes * 1.0) + (1 << 21) - 1) // (1 << 21) * (1 << 21)
+            b = S.SymmBuffer(size, self.group)
+            self.bufs[kind][parity] = b
+        return b
+
+    # ------------------------------------------------------------------ all-gather side
+    def publish(self, x2):
+        """Stage this rank's shard ``x2`` ([rows, cols] bf16, contiguous) for the peers; returns the epoch."""
+        assert x2.is_contiguous() and x2.dtype == torch.bfloat16
+        self.ag_epoch += 1
+        e = self.ag_epoch
+        nbytes = x2.numel() * 2
+        buf = self._buf("ag", e & 1, nbytes)
+        L = native.lib()
+        rc = L.neox_symm_publish(native.ptr(x2), ctypes.c_void_p(buf.local), ctypes.c_ulonglong(nbytes),
+                                 self.pad.word(S.AG_DONE), ctypes.c_uint((e - 2) & 0xFFFFFFFF), self.pad.c_ptrs,
+                                 self.world, self.rank, S.AG_READY, ctypes.c_uint(e), self.pad.word(S.CTR_PUBLISH),
+                                 ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_symm_publish")
+        return e
+
+    def _comm_gemm(self, a_ptrs, b_ptrs, out, M, N, K, lda, ldb, a_mn, b_mn, bias=None, add=None, preact=None, act=0,
+                   a_split=0, b_split=0, gather_epoch=0, scatter=False, recv=None, free_epoch=0, sig_offset=-1,
+                   sig_value=0):
+        L = native.lib()
+        rc = L.neox_comm_gemm(
+            a_ptrs, b_ptrs, native.ptr(out), M, N, K, ctypes.c_longlong(lda), ctypes.c_longlong(ldb),
+            ctypes.c_longlong(out.stride(0) if out is not None else N), int(a_mn), int(b_mn),
+            int(out is not None and out.dtype == torch.float32), native.ptr(bias), native.ptr(add),
+            ctypes.c_longlong(add.stride(0) if add is not None else 0),
+            int(add is not None and add.dtype == torch.float32), native.ptr(preact),
+            ctypes.c_longlong(preact.stride(0) if preact is not None else 0), int(act), self.world, self.rank,
+            int(a_split), int(b_split), self.pad.word(S.AG_READY), ctypes.c_uint(gather_epoch & 0xFFFFFFFF),
+            int(scatter), int(M // self.world if scatter else 0), recv.c_ptrs if recv is not None else None,
+            self.pad.word(S.RS_DONE), ctypes.c_uint(free_epoch & 0xFFFFFFFF), self.pad.c_ptrs, int(sig_offset),
+            ctypes.c_uint(sig_value & 0xFFFFFFFF), self.pad.word(S.CTR_GEMM), ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_comm_gemm")
+
+    def gemm_a_gathered(self, epoch, rows, b, b_mn, out_dtype=torch.bfloat16, bias=None, act=G.ACT_NONE,
+                        want_preact=False, last_reader=True):
+        """``op(A_full) @ op(B)`` with A = concat over ranks of the published [rows, K] shards (K-major)."""
+        if b_mn:
+            K, N = b.shape
+        else:
+            N, K = b.shape
+        M = rows * self.world
+        out = torch.empty(M, N, device=b.device, dtype=out_dtype)
+        pre = torch.empty(M, N, device=b.device, dtype=torch.bfloat16) if want_preact else None
+        buf = self.bufs["ag"][epoch & 1]
+        self._comm_gemm(buf.c_ptrs, S._ull_array([b.data_ptr()]), out, M, N, K, K, b.stride(0), False, b_mn,
+                        bias=bias, preact=pre, act=act, a_split=rows, gather_epoch=epoch,
+                        sig_offset=S.AG_DONE if last_reader else -1, sig_value=epoch)
+        return (out, pre) if want_preact else out
+
+    def wgrad_a_gathered(self, epoch, rows, cols_a, b, out=None, add=None, last_reader=True):
+        """``dW[cols_a, N] = A_full^T @ B`` where A_full = concat of published [rows, cols_a] shards (token-major)
+        and ``b`` = local [rows * world, N]."""
+        Kt, N = b.shape
+        assert Kt == rows * self.world
+        if out is None:
+            out = torch.empty(cols_a, N, device=b.device, dtype=torch.bfloat16)
+        buf = self.bufs["ag"][epoch & 1]
+        self._comm_gemm(buf.c_ptrs, S._ull_array([b.data_ptr()]), out, cols_a, N, Kt, cols_a, b.stride(0), True, True,
+                        add=add, a_split=rows, gather_epoch=epoch, sig_offset=S.AG_DONE if last_reader else -1,
+                        sig_value=epoch)
+        return out
+
+    def wgrad_b_gathered(self, a, epoch, rows, cols_b, out=None, add=None, last_reader=True):
+        """``dW[M, cols_b] = a^T @ B_full`` where ``a`` = local [rows * world, M] and B_full = concat of the published
+        [rows, cols_b] shards."""
+        Kt, M = a.shape
+        assert Kt == rows * self.world
+        if out is None:
+            out = torch.empty(M, cols_b, device=a.device, dtype=torch.bfloat16)
+        buf = self.bufs["ag"][epoch & 1]
+        self._comm_gemm(S._ull_array([a.data_ptr()]), buf.c_ptrs, out, M, cols_b, Kt, a.stride(0), cols_b, True, True,
+                        add=add, b_split=rows, gather_epoch=epoch, sig_offset=S.AG_DONE if last_reader else -1,
+                        sig_value=epoch)
+        return out
+
+    # ------------------------------------------------------------------ reduce-scatter / all-reduce side
+    def gather(self, epoch, rows, cols, last_reader=True):
+        """Materialise the concatenation of the published [rows, cols] shards as a local tensor."""
+        out = torch.empty(rows * self.world, cols, device=torch.device("cuda", torch.cuda.current_device()),
+                          dtype=torch.bfloat16)
+        buf = self.bufs["ag"][epoch & 1]
+        rc = native.lib().neox_symm_gather(buf.c_ptrs, native.ptr(out), ctypes.c_ulonglong(rows * cols * 2),
+                                           self.pad.word(S.AG_READY), ctypes.c_uint(epoch & 0xFFFFFFFF),
+                                           self.pad.c_ptrs, self.world, self.rank,
+                                           S.AG_DONE if last_reader else -1, self.pad.word(S.CTR_GCOPY),
+                                           ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_symm_gather")
+        return out
+
+    def gemm_reduce(self, a, b, b_mn, bias=None, residual=None, all_reduce=False, partial_bias=None,
+                    partial_add=None):
+        """``reduce_over_ranks(a @ op(b) + partial_bias + partial_add) + bias + residual``: returns this rank's
+        [M / world, N] row block (reduce-scatter) or the whole [M, N] result (``all_reduce``).  The ``partial_*``
+        terms are added to this rank's product before the reduction (in the GEMM epilogue), ``bias`` / ``residual``
+        once after it (``residual`` has the shape of the result)."""
+        M, K = a.shape
+        N = b.shape[1] if b_mn else b.shape[0]
+        rows = M // self.world
+        self.rs_epoch += 1
+        e = self.rs_epoch
+        recv = self._buf("recv", e & 1, M * N * 2)
+        gath = self._buf("gath", e & 1, M * N * 2) if all_reduce else None
+        self._comm_gemm(S._ull_array([a.data_ptr()]), S._ull_array([b.data_ptr()]), None, M, N, K, a.stride(0),
+                        b.stride(0), False, b_mn, bias=partial_bias, add=partial_add, scatter=True, recv=recv,
+                        free_epoch=e - 2, sig_offset=S.RS_READY, sig_value=e)
+        L = native.lib()
+        out = torch.empty(M if all_reduce else rows, N, device=a.device, dtype=torch.bfloat16)
+        if residual is not None:
+            assert residual.is_contiguous() and residual.dtype == torch.bfloat16
+        res_ptr = native.ptr(residual)
+        if all_reduce and residual is not None:
+            # the owner adds the residual rows it owns
+            res_ptr = ctypes.c_void_p(residual.data_ptr() + self.rank * rows * N * 2)
+        rc = L.neox_rs_reduce(ctypes.c_void_p(recv.local), native.ptr(out) if not all_reduce else None,
+                              native.ptr(bias), res_ptr, self.world, self.rank, rows, N, self.pad.word(S.RS_READY),
+                              ctypes.c_uint(e), self.pad.c_ptrs, S.RS_DONE, self.pad.word(S.CTR_REDUCE),
+                              gath.c_ptrs if all_reduce else None, self.pad.word(S.AR_DONE),
+                              ctypes.c_uint(self._gath_last[e & 1]), S.AR_READY,
+                              ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_rs_reduce")
+        if all_reduce:
+            self._gath_last[e & 1] = e
+            rc = L.neox_gathered_copy(ctypes.c_void_p(gath.local), native.ptr(out), ctypes.c_ulonglong(M * N * 2),
+                                      self.pad.word(S.AR_READY), ctypes.c_uint(e), self.pad.c_ptrs, self.world,
+                                      self.rank, S.AR_DONE, self.pad.word(S.CTR_GCOPY),
+                                      ctypes.c_void_p(native.stream_ptr()))
+            native.check(rc, "neox_gathered_copy")
+        return out
+
+
+def workspace(group=None) -> Workspace:
+    group = group if group is not None else mpu.get_model_parallel_group()
+    key = id(group)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = Workspace(group)
+        _workspaces[key] = ws
+    return ws
+
+
+def reset():
+    """Drop all workspaces (collective).  Call before destroying the process groups."""
+    for ws in _workspaces.values():
+        for pair in ws.bufs.values():
+            for b in pair:
+                if b is not None:
+                    b.close()
+        ws.pad.close()
+    _workspaces.clear()
+
+
+def eligible(x2, weight, world, sharded_rows=None) -> bool:
+    """Shapes / dtypes the fused kernels accept.  ``sharded_rows``: rows of the per-rank row block."""
+    if not enabled() or world < 2 or world > S.MAX_RANKS:
+        return False
+    if not (x2.is_cuda and x2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()):
+        return False
+    if sharded_rows is None or sharded_rows % 128 or sharded_rows == 0:
+        return False
+    return x2.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+
+
+def _accumulate_wgrad(weight, fn):
+    """Run the weight-gradient GEMM ``fn(out, add)``: into ``weight.main_grad`` when the engine provides it."""
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        fn(mg, mg)
+        weight.grad_in_main = True
+        return None
+    return fn(None, None)
+
+
+class _ColumnSP(torch.autograd.Function):
+    """Column-parallel linear under sequence parallelism: input [rows, K] is this rank's sequence shard."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        ws = workspace()
+        N, K = weight.shape
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
+        e = ws.publish(x2)
+        r = ws.gemm_a_gathered(e, rows, weight, False, bias=bias, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE,
+                               want_preact=need_pre)
+        out, pre = r if need_pre else (r, None)
+        ctx.act, ctx.rows, ctx.x_shape, ctx.has_bias = act, rows, x.shape, bias is not None
+        ctx.save_for_backward(x2, weight, pre)
+        return out.reshape(x.shape[0] * ws.world, *x.shape[1:-1], N)
+
+    @staticmethod
+    def backward(ctx, g):
+        ws = workspace()
+        x2, weight, pre = ctx.saved_tensors
+        N, K = weight.shape
+        g2 = g.reshape(-1, N)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        if ctx.act == "gelu":
+            from ..ops.functional import dgelu_mul
+            g2 = dgelu_mul(g2, pre)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = ws.gemm_reduce(g2, weight, True).reshape(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            e = ws.publish(x2)
+            gw = _accumulate_wgrad(weight, lambda out, add: ws.wgrad_b_gathered(g2, e, ctx.rows, K, out=out, add=add))
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g2.sum(0)
+        return gx, gw, gb, None
+
+
+class _Row(torch.autograd.Function):
+    """Row-parallel linear with its reduction: ``reduce(x W^T [+ bias] [+ partial_add]) [+ bias] + residual``.
+
+    ``sp``: the reduction is a reduce-scatter along dim 0 (sequence parallelism) and ``residual`` / the result are
+    this rank's sequence shard; otherwise an all-reduce.  ``bias_partial`` selects whether the bias is added to this
+    rank's partial product (every rank then contributes its own bias) or once after the reduction.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, partial_add, sp, bias_partial):
+        ws = workspace()
+        N, K = weight.shape
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        res2 = residual.reshape(-1, N).contiguous() if residual is not None else None
+        add2 = partial_add.reshape(-1, N) if partial_add is not None else None
+        if add2 is not None and not add2.is_contiguous():
+            add2 = add2.contiguous()
+        out = ws.gemm_reduce(x2, weight, False, bias=None if bias_partial else bias, residual=res2, all_reduce=not sp,
+                             partial_bias=bias if bias_partial else None, partial_add=add2)
+        ctx.x_shape, ctx.sp, ctx.bias_partial = x.shape, sp, bias_partial
+        ctx.has_bias, ctx.has_res, ctx.has_add = bias is not None, residual is not None, partial_add is not None
+        ctx.add_shape = partial_add.shape if partial_add is not None else None
+        ctx.save_for_backward(x2, weight)
+        lead = x.shape[0] // ws.world if sp else x.shape[0]
+        return out.reshape(lead, *x.shape[1:-1], N)
+
+    @staticmethod
+    def backward(ctx, g):
+        ws = workspace()
+        x2, weight = ctx.saved_tensors
+        N, K = weight.shape
+        g2 = g.reshape(-1, N)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        gx = gw = gb = g_add = None
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_add = ctx.has_add and ctx.needs_input_grad[4]
+        need_full_bias = ctx.has_bias and ctx.bias_partial and ctx.needs_input_grad[2]
+        if not ctx.sp:
+            g_full = g2                                   # backward of an all-reduce is the identity
+        elif need_add or need_full_bias:
+            e = ws.publish(g2)
+            g_full = ws.gather(e, g2.shape[0], N)        # the addend's gradient is the gathered tensor itself
+        else:
+            g_full = None
+        if g_full is not None:
+            if need_x:
+                gx = G.gemm(g_full, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
+            if need_w:
+                gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g_full, x2, a_mn=True, b_mn=True, out=out,
+                                                                       add=add))
+            if need_add:
+                g_add = g_full.reshape(ctx.add_shape)
+        else:
+            rows = g2.shape[0]
+            e = ws.publish(g2)
+            if need_x:
+                gx = ws.gemm_a_gathered(e, rows, weight, True, last_reader=not need_w).reshape(ctx.x_shape)
+            if need_w:
+                gw = _accumulate_wgrad(weight, lambda out, add: ws.wgrad_a_gathered(e, rows, N, x2, out=out, add=add))
+            if not (need_x or need_w):
+                ws.gather(e, rows, N)                     # keeps the epoch protocol balanced (never hit in training)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            # post-reduction bias under SP: partial over this rank's shard, summed with the other replicated grads
+            gb = (g_full if (ctx.bias_partial or not ctx.sp) else g2).sum(0)
+        return gx, gw, gb, (g if ctx.has_res else None), g_add, None, None
+
+
+class _ColumnAR(torch.autograd.Function):
+    """Column-parallel linear without sequence parallelism: forward is local, the data gradient is all-reduced."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        N, K = weight.shape
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
+        r = G.gemm(x2, weight, bias=bias, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE, want_preact=need_pre)
+        out, pre = r if need_pre else (r, None)
+        ctx.act, ctx.x_shape, ctx.has_bias = act, x.shape, bias is not None
+        ctx.save_for_backward(x2, weight, pre)
+        return out.reshape(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, g):
+        ws = workspace()
+        x2, weight, pre = ctx.saved_tensors
+        N, K = weight.shape
+        g2 = g.reshape(-1, N)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        if ctx.act == "gelu":
+            from ..ops.functional import dgelu_mul
+            g2 = dgelu_mul(g2, pre)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = ws.gemm_reduce(g2, weight, True, all_reduce=True).reshape(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g2, x2, a_mn=True, b_mn=True, out=out, add=add))
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g2.sum(0)
+        return gx, gw, gb, None
+
+
+def column_linear(x, weight, bias, act, sequence_parallel):
+    return (_ColumnSP if sequence_parallel else _ColumnAR).apply(x, weight, bias, act)
+
+
+def row_linear(x, weight, bias, residual, sequence_parallel, partial_add=None, bias_partial=False):
+    return _Row.apply(x, weight, bias, residual, partial_add, bool(sequence_parallel), bool(bias_partial))

@@ -26,6 +26,7 @@ from torch.nn import init
 from torch.nn.parameter import Parameter
 
 from ..ops.linear import linear as fused_linear
+from . import fused_comm
 from . import mappings as M
 from . import mpu
 from .rng import get_cuda_rng_tracker
@@ -176,15 +177,32 @@ class ColumnParallelLinear(nn.Module):
     def width_mult(self):
         return self.width_mult_val
 
-    def forward(self, input_, act=None):
-        if self.use_mup and self.mup_rescale_parameters:
-            input_ = input_ / self.width_mult()
+    def matmul(self, input_, bias, act=None):
+        """Region mapping + GEMM: ``act(gather_or_copy(input_) W^T + bias)``.  Uses the kernel that overlaps the
+        collective with the GEMM when the shapes allow it, the NCCL mapping otherwise."""
+        K = input_.shape[-1]
+        if self.tp > 1 and self.tp == mpu.get_model_parallel_world_size() and not mpu.get_fp32_allreduce():
+            tokens = input_.numel() // K
+            rows = tokens if self.sequence_parallel else tokens // self.tp
+            ok = (self.seq_dim == 0 or input_.shape[0] == 1 or not self.sequence_parallel) and \
+                (self.sequence_parallel or tokens % self.tp == 0)
+            if ok and (bias is None or bias.dtype == torch.bfloat16) and \
+                    fused_comm.eligible(input_, self.weight, self.tp, rows):
+                if self.sequence_parallel and self.seq_dim != 0:
+                    out = fused_comm.column_linear(input_[0], self.weight, bias, act, True)
+                    return out.unsqueeze(0)
+                return fused_comm.column_linear(input_, self.weight, bias, act, self.sequence_parallel)
         if self.sequence_parallel:
             x = M.gather_from_sequence_parallel_region(input_, self.seq_dim)
         else:
             x = M.copy_to_model_parallel_region(input_)
+        return fused_linear(x, self.weight, bias, act=act)
+
+    def forward(self, input_, act=None):
+        if self.use_mup and self.mup_rescale_parameters:
+            input_ = input_ / self.width_mult()
         bias = None if self.skip_bias_add else self.bias
-        out = fused_linear(x, self.weight, bias, act=act)
+        out = self.matmul(input_, bias, act)
         if self.gather_output:
             # after the sequence all-gather every rank holds the full sequence, so gathering the output
             # features is well defined (the reference asserts here, which rules out inference under SP)
@@ -217,26 +235,57 @@ class RowParallelLinear(nn.Module):
         init_sharded_weight(neox_args, self.weight, output_size, input_size, 1, init_method, stride)
         if bias:
             self.bias = Parameter(torch.zeros(output_size, device=dev, dtype=neox_args.params_dtype))
+            if self.sequence_parallel and not parallel_output:
+                # replicated parameter whose gradient is computed from this rank's sequence shard only
+                self.bias.sequence_parallel_grad_sync = True
         else:
             self.register_parameter("bias", None)
 
     def set_parallel_output(self, value: bool):
         self.parallel_output = value
 
+    def _fusable(self, x):
+        if self.tp == 1 or self.tp != mpu.get_model_parallel_world_size() or mpu.get_fp32_allreduce():
+            return False
+        tokens = x.numel() // x.shape[-1]
+        return tokens % self.tp == 0 and fused_comm.eligible(x, self.weight, self.tp, tokens // self.tp) and \
+            (self.bias is None or self.bias.dtype == torch.bfloat16)
+
     def forward(self, input_, residual=None):
-        """``residual`` (optional) is added in the GEMM epilogue; only legal when no cross-rank
-        reduction follows (tp == 1) or the caller defers it (``parallel_output``) and accounts for it."""
+        """``residual`` (optional) is added to the layer's output: after the cross-rank reduction when this layer
+        performs it, to this rank's partial product when the caller defers it (``parallel_output``)."""
         x = input_ if self.input_is_parallel else M.scatter_to_model_parallel_region(input_)
-        local_bias = None
-        if self.bias is not None and not self.skip_bias_add and (self.tp == 1):
-            local_bias = self.bias      # no reduction follows: fold the bias into the epilogue
-        out = fused_linear(x, self.weight, local_bias, residual=residual)
-        if self.sequence_parallel and not self.parallel_output:
-            out = M.reduce_scatter_to_sequence_parallel_region(out)
-        elif not self.parallel_output:
-            out = M.reduce_from_model_parallel_region(out)
-        if self.skip_bias_add:
-            return out, self.bias
-        if self.bias is not None and local_bias is None:
-            out = out + self.bias
-        return out, None
+        bias = None if self.skip_bias_add else self.bias
+        if not self.parallel_output and self._fusable(x):
+            # GEMM -> reduce-scatter / all-reduce in one pass; bias and residual are added after the reduction
+            out = fused_comm.row_linear(x, self.weight, bias, residual, self.sequence_parallel)
+            return out, (self.bias if self.skip_bias_add else None)
+        local = self.tp == 1 or self.parallel_output
+        out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None)
+        if not local:
+            if self.sequence_parallel:
+                out = M.reduce_scatter_to_sequence_parallel_region(out)
+            else:
+                out = M.reduce_from_model_parallel_region(out)
+            if bias is not None:
+                out = out + bias
+            if residual is not None:
+                out = out + residual
+        return out, (self.bias if self.skip_bias_add else None)
+
+    def forward_reduced(self, input_, partial_add, post_residual):
+        """``reduce_over_tp(input_ W^T + bias + partial_add) + post_residual`` regardless of ``parallel_output``:
+        the GPT-J style residual, where attention and MLP partial sums share one reduction.  Every rank's bias is
+        added to its own partial product (they are distinct parameters, as in the reference's
+        ``megatron/model/transformer.py:1283-1331``)."""
+        x = input_ if self.input_is_parallel else M.scatter_to_model_parallel_region(input_)
+        if self._fusable(x):
+            return fused_comm.row_linear(x, self.weight, self.bias, post_residual, self.sequence_parallel,
+                                         partial_add=partial_add, bias_partial=True)
+        out = fused_linear(x, self.weight, self.bias, residual=partial_add)
+        if self.tp > 1:
+            if self.sequence_parallel:
+                out = M.reduce_scatter_to_sequence_parallel_region(out)
+            else:
+                out = M.reduce_from_model_parallel_region(out)
+        return out + post_residual
