@@ -1,0 +1,30 @@
+"""Fused GEMM + collective kernels over peer memory, on 2 GPUs (or more) of one node.
+
+The checks live in ``tests/workers/fused_comm_worker.py`` (one process per GPU under torchrun): every fused op is
+compared with the NCCL collective + fp32 matmul statement of the same math, over several iterations so both buffer
+parities are reused, then a column->row parallel layer pair is run forward and backward both ways, and finally a wait
+on an epoch nobody publishes must time out with a status code and leave the context usable.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from common import ROOT, free_port
+
+
+@pytest.mark.gpu
+def test_fused_comm_two_gpus():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(ROOT, "tests", "workers", "fused_comm_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and "FUSED_COMM_OK" in out, out[-4000:]

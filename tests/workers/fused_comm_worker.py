@@ -1,0 +1,153 @@
+"""Multi-GPU worker for the fused tensor-parallel GEMM tests (launched by torchrun from test_fused_comm_gpu.py).
+
+Every check compares a fused peer-memory op with the NCCL collective + fp32 matmul statement of the same math.
+Prints ``FUSED_COMM_OK`` on rank 0 when all checks pass on all ranks.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from gpt_neox_b200.ops import native  # noqa: E402
+from gpt_neox_b200.parallel import fused_comm, mpu  # noqa: E402
+
+
+def close(a, b, tol, what):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item() + 1e-6
+    ok = err <= tol * ref
+    if not ok:
+        print(f"[rank {dist.get_rank()}] MISMATCH {what}: max err {err:.4g} vs ref max {ref:.4g}", flush=True)
+    return ok
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl")
+    mpu.initialize_model_parallel(world)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ws = fused_comm.workspace()
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    ok = True
+    rows, K, N = 256, 512, 768                     # per-rank rows; small enough for seconds, > 1 tile each way
+    grp = mpu.get_model_parallel_group()
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, device=dev, generator=g) * scale).to(torch.bfloat16)
+
+    for it in range(5):                            # > 2 iterations: both buffer parities get reused
+        # ---- all-gather -> GEMM (A gathered along M), K-major B and MN-major B
+        x = rnd(rows, K)
+        w = rnd(N, K, scale=0.05)
+        full = torch.empty(rows * world, K, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, x, group=grp)
+        e = ws.publish(x)
+        y = ws.gemm_a_gathered(e, rows, w, False, last_reader=False)
+        ok &= close(y, full.float() @ w.float().t(), 2e-2, f"ag_gemm it{it}")
+        w2 = rnd(K, N, scale=0.05)
+        y2 = ws.gemm_a_gathered(e, rows, w2, True, last_reader=False)
+        ok &= close(y2, full.float() @ w2.float(), 2e-2, f"ag_gemm(b_mn) it{it}")
+        # ---- wgrad with the gathered operand on the A side:  dW[K, N2] = full^T @ b
+        b = rnd(rows * world, 384)
+        dw = ws.wgrad_a_gathered(e, rows, K, b, last_reader=False)
+        ok &= close(dw, full.float().t() @ b.float(), 2e-2, f"wgrad_a it{it}")
+        # ---- ... and on the B side, accumulating into fp32:  dW[M2, K] += a^T @ full
+        a = rnd(rows * world, 256)
+        acc = torch.ones(256, K, device=dev, dtype=torch.float32)
+        ws.wgrad_b_gathered(a, e, rows, K, out=acc, add=acc, last_reader=False)
+        ok &= close(acc, 1.0 + a.float().t() @ full.float(), 2e-2, f"wgrad_b it{it}")
+        # ---- plain gather (last reader: releases the staging buffer)
+        gat = ws.gather(e, rows, K)
+        ok &= bool(torch.equal(gat, full))
+
+        # ---- GEMM -> reduce-scatter, with post-reduction bias and residual
+        xa = rnd(rows * world, K)
+        wr = rnd(N, K, scale=0.05)
+        bias = rnd(N)
+        res = rnd(rows, N)
+        part = (xa.float() @ wr.float().t()).to(torch.bfloat16).float()
+        ref = torch.empty(rows, N, device=dev, dtype=torch.float32)
+        dist.reduce_scatter_tensor(ref, part.contiguous(), group=grp)
+        out = ws.gemm_reduce(xa, wr, False, bias=bias, residual=res)
+        ok &= close(out, ref + bias.float() + res.float(), 2e-2, f"gemm_rs it{it}")
+        # ---- GEMM -> all-reduce with per-rank (pre-reduction) bias and addend
+        padd = rnd(rows * world, N)
+        part2 = (xa.float() @ wr.float().t() + bias.float() + padd.float()).to(torch.bfloat16).float()
+        dist.all_reduce(part2, group=grp)
+        out2 = ws.gemm_reduce(xa, wr, False, all_reduce=True, partial_bias=bias, partial_add=padd)
+        ok &= close(out2, part2, 2e-2, f"gemm_ar it{it}")
+        # ---- dgrad form (MN-major B) -> reduce-scatter
+        dy = rnd(rows * world, N)
+        part3 = (dy.float() @ wr.float()).to(torch.bfloat16).float()
+        ref3 = torch.empty(rows, K, device=dev, dtype=torch.float32)
+        dist.reduce_scatter_tensor(ref3, part3.contiguous(), group=grp)
+        out3 = ws.gemm_reduce(dy, wr, True)
+        ok &= close(out3, ref3, 2e-2, f"gemm_rs(b_mn) it{it}")
+
+    st = native.read_status()
+    if st != 0:
+        print(f"[rank {rank}] device status {st}", flush=True)
+        ok = False
+
+    # ---- layer level: fused vs NCCL formulation of column -> row parallel linears, forward and backward
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from common import make_args
+    from gpt_neox_b200.parallel.layers import ColumnParallelLinear, RowParallelLinear
+    from gpt_neox_b200.parallel.rng import model_parallel_cuda_manual_seed
+    model_parallel_cuda_manual_seed(4321)
+    for sp in (True, False):
+        args = make_args(hidden_size=512, num_attention_heads=8, seq_length=128 * world,
+                         max_position_embeddings=128 * world, precision="bfloat16", model_parallel_size=world,
+                         sequence_parallel=sp, train_micro_batch_size_per_gpu=4, global_num_gpus=world,
+                         distributed_backend="nccl")
+        torch.manual_seed(7)
+        col = ColumnParallelLinear(args, 512, 2048, gather_output=False, skip_bias_add=False)
+        row = RowParallelLinear(args, 2048, 512, input_is_parallel=True, skip_bias_add=False)
+        s, b = 128 * world, 4
+        xs = rnd(s // world if sp else s, b, 512)
+        if not sp:
+            dist.broadcast(xs, 0)
+        results = {}
+        for mode in ("1", "0"):
+            os.environ["NEOX_FUSED_TP_COMM"] = mode
+            for p in list(col.parameters()) + list(row.parameters()):
+                p.grad = None
+            xin = xs.clone().requires_grad_(True)
+            h, _ = col(xin, act=None)
+            o, _ = row(h)
+            (o.float() * 0.01).sum().backward()
+            results[mode] = [o.detach(), xin.grad] + [p.grad for p in list(col.parameters()) + list(row.parameters())]
+        os.environ["NEOX_FUSED_TP_COMM"] = "1"
+        for i, (fa, fb) in enumerate(zip(results["1"], results["0"])):
+            ok &= close(fa, fb, 3e-2, f"layer sp={sp} tensor{i}")
+    st = native.read_status()
+    if st != 0:
+        print(f"[rank {rank}] device status {st} after layer test", flush=True)
+        ok = False
+
+    # ---- bounded wait: nobody publishes this epoch, the gather must give up, report, and leave the context usable
+    if os.environ.get("NEOX_TEST_TIMEOUT_PATH", "1") == "1":
+        ws.gather(ws.ag_epoch + 1000, rows, K, last_reader=False)
+        st = native.read_status()
+        ok &= (520 <= st < 528)
+        z = torch.ones(4, device=dev).sum().item()
+        ok &= (z == 4.0)
+
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0 and flag.item() == 1:
+        print("FUSED_COMM_OK", flush=True)
+    dist.barrier()
+    fused_comm.reset()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
