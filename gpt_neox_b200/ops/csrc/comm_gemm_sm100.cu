@@ -3,20 +3,23 @@
 // One kernel, same pipeline as gemm_sm100.cu (TMA ring -> tcgen05.mma -> TMEM -> epilogue warps), with two
 // extensions that replace the NCCL calls around a column- / row-parallel linear layer:
 //
-//   * GATHERED OPERANDS (all-gather -> GEMM).  An operand whose rows are sharded over the tensor-parallel ranks is
-//     described by one tensor map PER RANK, each over that rank's shard in peer-mapped ("symmetric") memory.  The
-//     producer picks the map from the row coordinate, so every CTA fetches the remote tile it needs straight into its
-//     own shared memory with a plain (non-multicast) TMA load: no gathered copy of the activation is ever written.
-//     Before the first load from a peer the producer waits -- bounded -- for that peer's "shard is ready" flag; tiles
-//     are visited local-shard-first so the wait overlaps useful work.  This covers the forward of a column-parallel
-//     layer (A gathered along M), the data gradient of a row-parallel layer, and both weight gradients (the gathered
-//     tensor is then the operand that is sharded along the contraction dimension).
+//   * BROADCAST (all-gather -> GEMM).  A few CTAs of the grid do no math: they copy this rank's shard of a
+//     row-sharded tensor into slot [rank] of EVERY rank's full-size symmetric buffer with posted peer stores (NVLink
+//     writes need no round trip; copy warps inside the GEMM CTAs were measured 10x slower because their loads queue
+//     behind the TMA operand traffic), 32 KB pieces at a time in the order the receivers will need them, and bump a
+//     per-128-row-block counter in the receiver's memory after each piece.  When an operand of the GEMM is the
+//     gathered buffer, a watcher warp in every GEMM CTA turns the counters into a "blocks complete so far" watermark
+//     in shared memory and the TMA producer waits -- bounded -- on that before its first load from a block; tiles
+//     (or k-steps) are visited local-shard-first, so the arrival of block i+1 overlaps the tensor-core work on
+//     block i and every byte crosses NVLink exactly once.  The broadcast may also ride on a GEMM
+//     that does not read the tensor (a prefetch: the weight-gradient GEMM of a column-parallel layer then finds the
+//     gathered activations complete).
 //
-//   * SCATTERED OUTPUT (GEMM -> reduce-scatter).  Row block m of the partial product belongs to rank m / rows_per_rank;
-//     the epilogue stores each finished tile directly into the OWNER's receive buffer, slot [source rank], with
-//     peer stores, so the transfer of tile i overlaps the math of tile i+1 (remote owners are served first).  A small
-//     second kernel on the owner waits for every source's "all tiles pushed" flag and adds the slots in rank order in
-//     fp32 (deterministic), fusing bias and residual.
+//   * PUSH (GEMM -> reduce-scatter).  Row block m of the partial product belongs to rank m / rows_per_rank; the
+//     epilogue warps stage each finished 32x64 sub-tile in shared memory and TMA-store it straight into the OWNER's
+//     receive buffer, slot [source rank] (128-byte rows, no multicast), so the transfer of tile i overlaps the math
+//     of tile i+1; remote owners are served first.  A small second kernel on the owner waits for every source's
+//     "all tiles pushed" flag and adds the slots in rank order in fp32 (deterministic), fusing bias and residual.
 //
 // Flags are 32-bit epochs in the receiver's signal pad, written with st.release.sys after a system fence and read
 // with ld.acquire.sys in a loop that gives up after ~2 s, records a status code and lets the kernel drain.
@@ -30,26 +33,47 @@ using namespace gemm;
 namespace {
 
 constexpr int MAX_RANKS = 8;
+constexpr int COMM_THREADS = 256;                  // GEMM CTA: warp 0 TMA, 1 MMA, 2-5 epilogue, 6 watcher
+constexpr int COPY_WARPS = COMM_THREADS / 32;       // copy CTA: every warp copies
+constexpr int PIECE_BYTES = 32768;
+constexpr int STG_BYTES = 32 * 128;                // one 32-row x 64-column bf16 sub-tile
+constexpr int COMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 8 * STG_BYTES + 256 + 1024;
 
-struct CommMaps {
-    CUtensorMap a[MAX_RANKS];
-    CUtensorMap b[MAX_RANKS];
+struct OutMaps {
+    CUtensorMap m[MAX_RANKS];
 };
 
 struct CommParams {
     GemmParams g;
     int world, rank;
-    int a_split, b_split;            // rows of the operand's 2-D view owned by each rank (0 = operand is local)
-    const uint32_t* gather_flags;     // local pad: gather_flags[src] >= gather_epoch  <=>  src's shard is published
-    uint32_t gather_epoch;
+    // ---- broadcast job: this rank's shard -> slot [rank] of every rank's gathered buffer
+    int bcast;
+    int n_copy;                       // CTAs at the end of the grid that only copy
+    const uint4* bc_src;              // local shard [rows_per_shard][row_bytes]
+    uint4* bc_dst[MAX_RANKS];         // every rank's gathered buffer (peer-mapped)
+    unsigned* bc_cnt[MAX_RANKS];      // every rank's per-block arrival flags (peer-mapped)
+    unsigned* bc_local_cnt;           // local scratch [world * blocks_per_rank]: pieces sent per block (zero at rest)
+    const uint32_t* bc_free_flags;    // local pad: bc_free_flags[dst] >= bc_free_epoch  <=>  dst released its buffer
+    uint32_t bc_free_epoch;
+    long long shard_bytes;            // bytes of one shard
+    long long block_bytes;            // bytes of 128 rows
+    int blocks_per_rank;              // 128-row blocks per shard
+    int pieces_per_block;
+    // ---- dependency of an operand on a gathered buffer
+    int a_dep, b_dep;                 // operand A / B is the local gathered buffer: wait for a block before loading
+    const unsigned* dep_cnt;          // local arrival flags [world * blocks_per_rank]
+    int rows_per_shard;               // rows of the gathered tensor per rank (multiple of 128)
+    // ---- push job
     int scatter;                      // 1: epilogue pushes row blocks to their owner's receive buffer
-    int rows_per_rank;                // scatter: output rows owned by each rank
-    __nv_bfloat16* recv[MAX_RANKS];   // scatter: every rank's receive buffer [world][rows_per_rank][N]
-    const uint32_t* free_flags;       // local pad: free_flags[owner] >= free_epoch  <=>  owner's buffer may be rewritten
+    int rows_per_rank;                // output rows owned by each rank
+    const uint32_t* free_flags;       // local pad: free_flags[owner] >= free_epoch  <=>  owner's buffer is reusable
     uint32_t free_epoch;
+    // ---- end-of-grid signal
     uint32_t* peer_pad[MAX_RANKS];    // every rank's signal pad (peer-mapped)
-    int sig_offset;                   // >= 0: when the whole grid is done, peer_pad[dst][sig_offset + rank] = sig_value
+    int sig_offset;                   // >= 0: peer_pad[dst][sig_offset + rank] = sig_value when the grid is done
     uint32_t sig_value;
+    int sig2_offset;                  // second, independent signal (unused slot for callers that need two)
+    uint32_t sig2_value;
     unsigned* counter;                // local CTA-completion counter for the end-of-grid signal
 };
 
@@ -61,6 +85,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -75,15 +102,31 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch) {
     }
     return true;
 }
+// Called by one thread per CTA after the CTA's last global / peer store (and a __syncthreads()).  The CTA that
+// arrives last publishes the value(s) in slot [offset + rank] of every rank's signal pad.
+__device__ __forceinline__ void grid_done_signal(unsigned* counter, uint32_t* const* pads, int world, int rank,
+                                                 int offset, uint32_t value, int offset2 = -1, uint32_t value2 = 0) {
+    __threadfence_system();
+    const unsigned old = atomicAdd(counter, 1u);
+    if (old == gridDim.x - 1) {
+        atomicExch(counter, 0u);
+        __threadfence_system();
+        for (int dst = 0; dst < world; ++dst) {
+            if (offset >= 0) st_release_sys(pads[dst] + offset + rank, value);
+            if (offset2 >= 0) st_release_sys(pads[dst] + offset2 + rank, value2);
+        }
+    }
+}
 
-// Scatter epilogue for 32 columns of one row: partial = acc (+ bias) (+ local bf16 addend), stored as bf16 into the
-// owner's receive slot (`dst` = start of this row in that slot).
-__device__ __forceinline__ void push_chunk(const uint32_t (&r)[32], int row, int col0, const GemmParams& p,
-                                           __nv_bfloat16* dst) {
+// Scatter epilogue for 32 columns of one row: partial = acc (+ bias) (+ local bf16 addend) as 4 x 16 bytes of bf16.
+// Columns beyond N are produced as zeros-or-garbage and clipped by the TMA store.
+__device__ __forceinline__ void pack_partial(const uint32_t (&r)[32], int row, int col0, const GemmParams& p,
+                                             uint4* out) {
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    if (p.vec_ok && col0 + 32 <= p.N) {
+    const bool inb = (row < p.M) && (col0 + 32 <= p.N);
+    if (inb) {
         if (p.bias) {
             const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col0);
 #pragma unroll
@@ -111,54 +154,43 @@ __device__ __forceinline__ void push_chunk(const uint32_t (&r)[32], int row, int
                 }
             }
         }
-        uint4* o = reinterpret_cast<uint4*>(dst + col0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint4 q;
-            q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-            q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-            q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-            q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-            o[j] = q;
-        }
-    } else {
+    } else if (row < p.M) {
         for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-            float x = v[i];
-            if (p.bias) x += __bfloat162float(p.bias[col0 + i]);
-            if (p.add) x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.add)[(long long)row * p.ldadd + col0 + i]);
-            dst[col0 + i] = __float2bfloat16(x);
+            if (p.bias) v[i] += __bfloat162float(p.bias[col0 + i]);
+            if (p.add) v[i] += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.add)[(long long)row * p.ldadd + col0 + i]);
         }
     }
-}
-
-// Called by one thread per CTA after the CTA's last global / peer store (and a __syncthreads()).  The CTA that
-// arrives last publishes `value` in slot [offset + rank] of every rank's signal pad.
-__device__ __forceinline__ void grid_done_signal(unsigned* counter, uint32_t* const* pads, int world, int rank,
-                                                 int offset, uint32_t value) {
-    __threadfence_system();
-    const unsigned old = atomicAdd(counter, 1u);
-    if (old == gridDim.x - 1) {
-        atomicExch(counter, 0u);
-        __threadfence_system();
-        for (int dst = 0; dst < world; ++dst) st_release_sys(pads[dst] + offset + rank, value);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint4 q;
+        q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+        q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+        q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+        q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+        out[j] = q;
     }
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
+__global__ void __launch_bounds__(COMM_THREADS, 1)
+comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ OutMaps outm, const CommParams cp) {
     const GemmParams& p = cp.g;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+    uint8_t* sStg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(sStg + 8 * STG_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* tfull = empty + STAGES;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* watermark = reinterpret_cast<volatile int*>(tmem_slot + 1);   // gathered blocks complete so far
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int n_gemm = gridDim.x - cp.n_copy;            // GEMM CTAs come first, copy CTAs last
+    const bool copy_cta = (int)blockIdx.x >= n_gemm;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -169,25 +201,28 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
             mbar_init(&tfull[b], 1);
             mbar_init(&tempty[b], 4);
         }
+        *watermark = 0;
         fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
     }
-    if (warp == 1) {
+    if (warp == 1 && !copy_cta) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = copy_cta ? 0u : *tmem_slot;
 
     const int num_m = (p.M + BM - 1) / BM;
     const int num_n = (p.N + BN - 1) / BN;
     const int ntiles = num_m * num_n;
     const int nk = (p.K + BK - 1) / BK;
-    // Rotation of the row-block order: gathered-A kernels start on the local shard, scattering kernels start on the
-    // block of the next rank (remote owners first, own block last).
-    int m_rot = 0;
-    if (cp.a_split > 0 && !p.a_mn) m_rot = (cp.rank * cp.a_split) / BM;
+    // Rotations: start on the local shard when an operand is being gathered, on the next rank's rows when pushing.
+    int m_rot = 0, k_rot = 0;
+    if (cp.a_dep && !p.a_mn) m_rot = (cp.rank * cp.rows_per_shard) / BM;
+    if ((cp.a_dep && p.a_mn) || (cp.b_dep && p.b_mn)) k_rot = (cp.rank * cp.rows_per_shard) / BK;
     if (cp.scatter) m_rot = (((cp.rank + 1) % cp.world) * cp.rows_per_rank) / BM;
 
     auto coords = [&](int tile, int& m_blk, int& n_blk) {
@@ -195,68 +230,130 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
         m_blk = (m_blk + m_rot) % num_m;
     };
 
-    if (warp == 0) {
+    const int dep_total = cp.world * cp.blocks_per_rank;          // gathered blocks, consumed starting at the local shard
+    const int dep_rot = cp.rank * cp.blocks_per_rank;
+
+    if (copy_cta) {
+        // ------------------------------------------------------------ copy CTA: broadcast the local shard
+        // Phase i sends to rank - i: every rank then receives, in phase i, the shard of rank + i, which is the order
+        // in which its own GEMM consumes them, and each phase is a permutation (balanced through the switch).
+        const int gw = ((int)blockIdx.x - n_gemm) * COPY_WARPS + warp;
+        const int GW = cp.n_copy * COPY_WARPS;
+        const int per_dst = cp.blocks_per_rank * cp.pieces_per_block;
+        const long long units = (long long)cp.world * per_dst;
+        uint32_t freed = 1u << cp.rank;
+        for (long long u = gw; u < units; u += GW) {
+            const int i = (int)(u / per_dst);
+            const int dst = (cp.rank - i + cp.world) % cp.world;
+            const int rem = (int)(u - (long long)i * per_dst);
+            const int rb = rem / cp.pieces_per_block;
+            const int piece = rem - rb * cp.pieces_per_block;
+            if (!(freed & (1u << dst))) {
+                int okf = 1;
+                if (lane == 0) okf = wait_flag(cp.bc_free_flags + dst, cp.bc_free_epoch) ? 1 : 0;
+                okf = __shfl_sync(0xffffffffu, okf, 0);
+                if (!okf) {
+                    if (lane == 0) atomicExch(p.status, 460 + dst);
+                    break;
+                }
+                freed |= 1u << dst;
+                __syncwarp();
+            }
+            const long long off = (long long)rb * cp.block_bytes + (long long)piece * PIECE_BYTES;
+            long long len = cp.block_bytes - (long long)piece * PIECE_BYTES;
+            if (len > PIECE_BYTES) len = PIECE_BYTES;
+            const int nvec = (int)(len >> 4);
+            const uint4* __restrict__ s4 = cp.bc_src + (off >> 4);
+            uint4* __restrict__ d4 = cp.bc_dst[dst] + (((long long)cp.rank * cp.shard_bytes + off) >> 4);
+            int v = lane;
+            for (; v + 15 * 32 < nvec; v += 32 * 16) {    // 16 independent 16-byte loads in flight per lane
+                uint4 t[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) t[j] = __ldg(s4 + v + j * 32);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) d4[v + j * 32] = t[j];
+            }
+            for (; v < nvec; v += 32) d4[v] = __ldg(s4 + v);
+            __syncwarp();
+            // System-scope releases are serialised GPU-wide (measured: ~0.5 us each, 3000 of them dominated the
+            // kernel), so pieces are counted locally at GPU scope and only the warp that completes a 128-row block
+            // publishes it to the receiver: one system-scope release per block and destination.
+            if (lane == 0) {
+                __threadfence();
+                unsigned* lc = cp.bc_local_cnt + dst * cp.blocks_per_rank + rb;
+                if (atomicAdd(lc, 1u) == (unsigned)cp.pieces_per_block - 1u) {
+                    atomicExch(lc, 0u);                     // ready for the next launch
+                    __threadfence();
+                    red_release_sys_add(cp.bc_cnt[dst] + cp.rank * cp.blocks_per_rank + rb, 1u);
+                }
+            }
+        }
+    } else if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            uint32_t ready = 1u << cp.rank;      // bit r: rank r's shard is known to be ready
-            auto need = [&](int src) -> bool {
-                if (ready & (1u << src)) return true;
-                if (!wait_flag(cp.gather_flags + src, cp.gather_epoch)) {
-                    atomicExch(p.status, 400 + src);
-                    return false;
+            int known = 0;                        // watermark value last read
+            // Wait until the gathered block holding `row` has arrived (the watcher warp maintains the watermark).
+            auto block_ready = [&](int row) -> bool {
+                int o = (row >> 7) - dep_rot;
+                if (o < 0) o += dep_total;
+                if (o < known) return true;
+                const long long t0 = clock64();
+                for (;;) {
+                    known = *watermark;
+                    if (known < 0) return false;           // the watcher gave up and reported
+                    if (o < known) break;
+                    if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
+                        atomicExch(p.status, 400 + row / cp.rows_per_shard);
+                        return false;
+                    }
+                    __nanosleep(100);
                 }
-                // the shard was written through the generic proxy; TMA reads through the async proxy
+                __threadfence();
+                // the block was written through the generic proxy; TMA reads it through the async proxy
                 asm volatile("fence.proxy.async.global;" ::: "memory");
-                ready |= 1u << src;
                 return true;
             };
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += n_gemm) {
                 int m_blk, n_blk;
                 coords(tile, m_blk, n_blk);
-                for (int kb = 0; kb < nk && ok; ++kb) {
+                for (int kk = 0; kk < nk && ok; ++kk) {
+                    const int kb = (kk + k_rot) % nk;
                     if (!mbar_wait(&empty[stage], phase ^ 1)) {
                         atomicExch(p.status, 101);
                         ok = false;
                         break;
                     }
-                    // y coordinate (row of the operand's 2-D view) decides which rank holds the tile
-                    int ay = p.a_mn ? kb * BK : m_blk * BM;
-                    int by = p.b_mn ? kb * BK : n_blk * BN;
-                    int asrc = cp.rank, bsrc = cp.rank;
-                    if (cp.a_split > 0) {
-                        asrc = ay / cp.a_split;
-                        ay -= asrc * cp.a_split;
-                        if (asrc >= cp.world) asrc = cp.world - 1;
+                    // y coordinate = row of the operand's 2-D view
+                    const int ay = p.a_mn ? kb * BK : m_blk * BM;
+                    const int by = p.b_mn ? kb * BK : n_blk * BN;
+                    if (cp.a_dep && !block_ready(ay)) { ok = false; break; }
+                    if (cp.b_dep) {
+                        // an N-side K-major tile spans two 128-row blocks
+                        if (!block_ready(by)) { ok = false; break; }
+                        if (!p.b_mn && by + 128 < cp.rows_per_shard * cp.world && !block_ready(by + 128)) {
+                            ok = false;
+                            break;
+                        }
                     }
-                    if (cp.b_split > 0) {
-                        bsrc = by / cp.b_split;
-                        by -= bsrc * cp.b_split;
-                        if (bsrc >= cp.world) bsrc = cp.world - 1;
-                    }
-                    if (!need(asrc) || !need(bsrc)) {
-                        ok = false;
-                        break;
-                    }
-                    const CUtensorMap* ma = &maps.a[cp.a_split > 0 ? asrc : 0];
-                    const CUtensorMap* mb = &maps.b[cp.b_split > 0 ? bsrc : 0];
                     mbar_expect_tx(&full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
                     uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
                     uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
                     if (!p.a_mn) {
-                        tma_load_2d(a_dst, ma, &full[stage], kb * BK, ay);
+                        tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, ay);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j)
-                            tma_load_2d(a_dst + j * (64 * BK * 2), ma, &full[stage], m_blk * BM + j * 64, ay);
+                            tma_load_2d(a_dst + j * (64 * BK * 2), &tmA, &full[stage], m_blk * BM + j * 64, ay);
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(b_dst, mb, &full[stage], kb * BK, by);
+                        tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, by);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(b_dst + j * (64 * BK * 2), mb, &full[stage], n_blk * BN + j * 64, by);
+                            tma_load_2d(b_dst + j * (64 * BK * 2), &tmB, &full[stage], n_blk * BN + j * 64, by);
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -266,6 +363,7 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
             }
         }
     } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
             int stage = 0;
@@ -273,7 +371,7 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
             int buf = 0;
             uint32_t bphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += n_gemm) {
                 if (!mbar_wait(&tempty[buf], bphase ^ 1)) {
                     atomicExch(p.status, 102);
                     break;
@@ -309,12 +407,15 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
                 if (buf == 0) bphase ^= 1;
             }
         }
-    } else {
-        const int q = warp & 3;
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue warps (2..5)
+        const int q = warp & 3;  // tensor-memory lane quarter this warp may read
         int buf = 0;
         uint32_t bphase = 0;
         uint32_t freed = 1u << cp.rank;   // bit o: owner o's receive buffer is known to be reusable
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        uint8_t* stg = sStg + q * 2 * STG_BYTES;
+        int sbuf = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += n_gemm) {
             int m_blk, n_blk;
             coords(tile, m_blk, n_blk);
             if (!mbar_wait_warp(&tfull[buf], bphase)) {
@@ -324,36 +425,53 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
             tc_fence_after();
             const int row = m_blk * BM + q * 32 + lane;
             const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
-            // scatter mode: this row lives in the receive buffer of its owner, slot = my rank
-            __nv_bfloat16* push = nullptr;
-            if (cp.scatter) {
+            if (!cp.scatter) {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int col0 = n_blk * BN + c * 32;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c * 32, r);
+                    tmem_wait_ld();
+                    if (row < p.M) epilogue_chunk(r, row, col0, p);
+                }
+            } else {
                 const int owner = min((m_blk * BM) / cp.rows_per_rank, cp.world - 1);   // warp-uniform
                 if (!(freed & (1u << owner))) {
-                    int ok = 1;
-                    if (lane == 0) ok = wait_flag(cp.free_flags + owner, cp.free_epoch) ? 1 : 0;
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) {
+                    int okf = 1;
+                    if (lane == 0) okf = wait_flag(cp.free_flags + owner, cp.free_epoch) ? 1 : 0;
+                    okf = __shfl_sync(0xffffffffu, okf, 0);
+                    if (!okf) {
                         if (lane == 0) atomicExch(p.status, 440 + owner);
                         break;
                     }
                     freed |= 1u << owner;
                 }
-                const int lrow = row - owner * cp.rows_per_rank;
-                push = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + lrow) * (size_t)p.N;
-            }
+                const int lrow0 = m_blk * BM + q * 32 - owner * cp.rows_per_rank;   // first row of this warp in the slot
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int col0 = n_blk * BN + c * 32;
-                if (col0 >= p.N) break;
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c * 32, r);
-                tmem_wait_ld();
-                if (row < p.M) {
-                    if (!cp.scatter) {
-                        epilogue_chunk(r, row, col0, p);
-                    } else {
-                        push_chunk(r, row, col0, p, push);
+                for (int c = 0; c < BN / 64; ++c) {
+                    const int col0 = n_blk * BN + c * 64;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(taddr + c * 64, r0);
+                    tmem_ld_32x32(taddr + c * 64 + 32, r1);
+                    tmem_wait_ld();
+                    uint4 pk[8];
+                    pack_partial(r0, row, col0, p, pk);
+                    pack_partial(r1, row, col0 + 32, p, pk + 4);
+                    // the store issued two chunks ago has finished reading this staging buffer
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    uint8_t* sb = stg + sbuf * STG_BYTES + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(sb + ((j ^ (lane & 7)) << 4)) = pk[j];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&outm.m[owner], stg + sbuf * STG_BYTES, col0, lrow0);
+                        tma_store_commit();
                     }
+                    sbuf ^= 1;
                 }
             }
             tc_fence_before();
@@ -362,22 +480,64 @@ comm_gemm_kernel(const __grid_constant__ CommMaps maps, const CommParams cp) {
             buf ^= 1;
             if (buf == 0) bphase ^= 1;
         }
+        if (cp.scatter && lane == 0) {
+            tma_store_wait<0>();                                   // all pushed tiles are written
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+    } else if (warp == 6 && (cp.a_dep || cp.b_dep)) {
+        // ------------------------------------------------------------ watcher: counters -> watermark
+        int W = 0;
+        long long t0 = clock64();
+        while (W < dep_total) {
+            const int o = W + lane;
+            bool c = false;
+            if (o < dep_total) {
+                int blk = o + dep_rot;
+                if (blk >= dep_total) blk -= dep_total;
+                c = ld_acquire_sys(cp.dep_cnt + blk) != 0u;
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, c);
+            const int n = (m == 0xffffffffu) ? 32 : (__ffs(~m) - 1);      // leading complete blocks
+            if (n > 0) {
+                W = min(W + n, dep_total);
+                if (lane == 0) {
+                    __threadfence();
+                    *watermark = W;
+                }
+                t0 = clock64();
+            } else {
+                if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
+                    if (lane == 0) {
+                        int blk = W + dep_rot;
+                        if (blk >= dep_total) blk -= dep_total;
+                        atomicExch(p.status, 400 + blk / cp.blocks_per_rank);
+                        *watermark = -1;
+                    }
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 1 && !copy_cta) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
-    if (threadIdx.x == 0 && cp.sig_offset >= 0) grid_done_signal(cp.counter, cp.peer_pad, cp.world, cp.rank, cp.sig_offset, cp.sig_value);
+    if (threadIdx.x == 0 && (cp.sig_offset >= 0 || cp.sig2_offset >= 0))
+        grid_done_signal(cp.counter, cp.peer_pad, cp.world, cp.rank, cp.sig_offset, cp.sig_value, cp.sig2_offset,
+                         cp.sig2_value);
 }
 
-// Copy this rank's shard into its symmetric staging buffer and tell every rank it is there.
+// Copy this rank's shard into its symmetric staging buffer (and, optionally, into its slot of the local gathered
+// tensor) and tell every rank it is there.
 //   wait  : the buffer was last read by the peers' GEMMs of epoch `need`; done_flags[peer] >= need says they finished
 //   copy  : 16-byte vectors, grid-stride
 //   signal: last CTA writes `epoch` into slot [sig_offset + rank] of every pad
-__global__ void __launch_bounds__(256) publish_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t nvec,
+__global__ void __launch_bounds__(256) publish_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                      uint4* __restrict__ dst2, size_t nvec,
                                                       const uint32_t* done_flags, uint32_t need, PeerPads pads, int world,
                                                       int rank, int sig_offset, uint32_t epoch, unsigned* counter,
                                                       int* status) {
@@ -393,8 +553,11 @@ __global__ void __launch_bounds__(256) publish_kernel(const uint4* __restrict__ 
     }
     __syncthreads();
     if (!s_ok) return;     // nothing published: the readers' own bounded waits will report it
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x)
-        dst[i] = src[i];
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = src[i];
+        dst[i] = v;
+        if (dst2) dst2[i] = v;
+    }
     __syncthreads();
     if (threadIdx.x == 0) grid_done_signal(counter, pads.p, world, rank, sig_offset, epoch);
 }
@@ -537,6 +700,18 @@ __global__ void __launch_bounds__(256) symm_gather_kernel(PeerPads srcs, uint4* 
     if (threadIdx.x == 0 && sig_offset >= 0) grid_done_signal(counter, pads.p, world, rank, sig_offset, epoch);
 }
 
+// Release a gathered buffer: clear its block counters, then tell every rank (AG_DONE-style flag) that it may be
+// overwritten.  Runs after the last local reader of the buffer, in stream order.
+__global__ void __launch_bounds__(256) release_kernel(unsigned* cnt, int n, PeerPads pads, int world, int rank,
+                                                      int sig_offset, uint32_t epoch) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) cnt[i] = 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int dst = 0; dst < world; ++dst) st_release_sys(pads.p[dst] + sig_offset + rank, epoch);
+    }
+}
+
 int copy_grid(size_t nvec) {
     size_t g = (nvec + 255) / 256;
     const size_t cap = (size_t)neox_sm_count() * 8;
@@ -575,11 +750,12 @@ extern "C" int neox_ipc_open(const void* handle64, void** out) {
 }
 extern "C" int neox_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : NEOX_ERR_DRIVER; }
 
-extern "C" int neox_symm_publish(const void* src, void* dst, unsigned long long bytes, const void* done_flags,
-                                 unsigned need, const unsigned long long* pad_ptrs, int world, int rank,
-                                 int sig_offset, unsigned epoch, void* counter, void* stream) {
+extern "C" int neox_symm_publish(const void* src, void* dst, void* dst2, unsigned long long bytes,
+                                 const void* done_flags, unsigned need, const unsigned long long* pad_ptrs, int world,
+                                 int rank, int sig_offset, unsigned epoch, void* counter, void* stream) {
     if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
-    if ((bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    if ((bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) ||
+        (reinterpret_cast<uintptr_t>(dst2) & 15))
         return NEOX_ERR_ALIGN;
     int* status = neox_status_word();
     if (!status) return NEOX_ERR_DRIVER;
@@ -588,47 +764,63 @@ extern "C" int neox_symm_publish(const void* src, void* dst, unsigned long long 
     for (int i = 0; i < world; ++i) pads.p[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
     const size_t nvec = bytes / 16;
     publish_kernel<<<copy_grid(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), static_cast<uint4*>(dst), nvec, static_cast<const uint32_t*>(done_flags), need,
-        pads, world, rank, sig_offset, epoch, static_cast<unsigned*>(counter), status);
+        static_cast<const uint4*>(src), static_cast<uint4*>(dst), static_cast<uint4*>(dst2), nvec,
+        static_cast<const uint32_t*>(done_flags), need, pads, world, rank, sig_offset, epoch,
+        static_cast<unsigned*>(counter), status);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
-// a_ptrs / b_ptrs: per-rank base pointers of the operand (only index 0 is read when the operand is local).
-// a_split / b_split: rows of the operand's 2-D view held by EACH rank (0 = local operand).
-extern "C" int neox_comm_gemm(const unsigned long long* a_ptrs, const unsigned long long* b_ptrs, void* D, int M,
-                              int N, int K, long long lda, long long ldb, long long ldd, int a_mn, int b_mn,
-                              int d_fp32, const void* bias, const void* add, long long ldadd, int add_fp32,
-                              void* preact, long long ldpre, int act, int world, int rank, int a_split, int b_split,
-                              const void* gather_flags, unsigned gather_epoch, int scatter, int rows_per_rank,
-                              const unsigned long long* recv_ptrs, const void* free_flags, unsigned free_epoch,
-                              const unsigned long long* pad_ptrs, int sig_offset, unsigned sig_value, void* counter,
-                              void* stream) {
+// The GEMM D = epilogue(op(A) op(B)) with an optional BROADCAST job and an optional PUSH of its output.
+//   bc_src != NULL: this rank's shard ([rows_per_shard, row_bytes]) is copied into slot [rank] of every rank's
+//       gathered buffer bc_dst_ptrs[dst], flagging finished 128-row blocks in bc_cnt_ptrs[dst] (bc_local_cnt: local
+//       scratch of world * rows_per_shard / 128 zeroed words); the first store to dst waits for
+//       bc_free_flags[dst] >= bc_free_epoch (dst has released the buffer).
+//   a_dep / b_dep: A / B IS the local gathered buffer; loads wait for dep_cnt[block] != 0.
+//   scatter: the output goes to recv_ptrs[owner] (slot = this rank) instead of D; bias / add (bf16) are added first.
+//   sig*/sig2*: end-of-grid signals written into every rank's pad (offset < 0: none).
+extern "C" int neox_comm_gemm(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                              long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias, const void* add,
+                              long long ldadd, int add_fp32, void* preact, long long ldpre, int act, int world, int rank,
+                              const void* bc_src, const unsigned long long* bc_dst_ptrs,
+                              const unsigned long long* bc_cnt_ptrs, void* bc_local_cnt, const void* bc_free_flags,
+                              unsigned bc_free_epoch,
+                              int rows_per_shard, long long row_bytes, const void* dep_cnt, int a_dep, int b_dep,
+                              int scatter, int rows_per_rank, const unsigned long long* recv_ptrs,
+                              const void* free_flags, unsigned free_epoch, const unsigned long long* pad_ptrs,
+                              int sig_offset, unsigned sig_value, int sig2_offset, unsigned sig2_value, void* counter,
+                              int n_copy, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
-    if ((lda % 8) || (ldb % 8)) return NEOX_ERR_ALIGN;
-    if (a_split > 0 && (a_split % (a_mn ? BK : BM))) return NEOX_ERR_SHAPE;
-    if (b_split > 0 && (b_split % (b_mn ? BK : BN))) return NEOX_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8))
+        return NEOX_ERR_ALIGN;
+    const bool bcast = bc_src != nullptr;
+    const bool dep = a_dep || b_dep;
+    if ((bcast || dep) && ((rows_per_shard % 128) || rows_per_shard <= 0 || (row_bytes % 16))) return NEOX_ERR_SHAPE;
+    if (bcast && ((reinterpret_cast<uintptr_t>(bc_src) & 15) || !bc_local_cnt)) return NEOX_ERR_ALIGN;
+    if (dep && !dep_cnt) return NEOX_ERR_SHAPE;
     if (scatter && ((rows_per_rank % BM) || (N % 8) || rows_per_rank * world != M || (add && add_fp32)))
         return NEOX_ERR_SHAPE;
     int* status = neox_status_word();
     if (!status) return NEOX_ERR_DRIVER;
-    CommMaps maps;
-    memset(&maps, 0, sizeof(maps));
-    const int na = a_split > 0 ? world : 1, nb = b_split > 0 ? world : 1;
-    for (int r = 0; r < na; ++r) {
-        const void* ptr = reinterpret_cast<const void*>(a_ptrs[r]);
-        // K-major: dims {K, rows}, box {BK, BM};  MN-major: dims {M, k-rows}, box {64, BK}
-        const unsigned long long rows = a_split > 0 ? (unsigned long long)a_split : (unsigned long long)(a_mn ? K : M);
-        int rc = a_mn ? neox_make_tmap_bf16_2d(&maps.a[r], ptr, M, rows, lda, 64, BK)
-                      : neox_make_tmap_bf16_2d(&maps.a[r], ptr, K, rows, lda, BK, BM);
-        if (rc) return rc;
+
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (!a_mn) rc = neox_make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
+    else rc = neox_make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+    if (rc) return rc;
+    if (!b_mn) rc = neox_make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, BN);
+    else rc = neox_make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+    if (rc) return rc;
+    OutMaps outm;
+    memset(&outm, 0, sizeof(outm));
+    if (scatter) {
+        for (int r = 0; r < world; ++r) {
+            const char* base = reinterpret_cast<const char*>(recv_ptrs[r]) + (size_t)rank * rows_per_rank * N * 2;
+            rc = neox_make_tmap_bf16_2d(&outm.m[r], base, N, rows_per_rank, N, 64, 32);
+            if (rc) return rc;
+        }
     }
-    for (int r = 0; r < nb; ++r) {
-        const void* ptr = reinterpret_cast<const void*>(b_ptrs[r]);
-        const unsigned long long rows = b_split > 0 ? (unsigned long long)b_split : (unsigned long long)(b_mn ? K : N);
-        int rc = b_mn ? neox_make_tmap_bf16_2d(&maps.b[r], ptr, N, rows, ldb, 64, BK)
-                      : neox_make_tmap_bf16_2d(&maps.b[r], ptr, K, rows, ldb, BK, BN);
-        if (rc) return rc;
-    }
+
     CommParams cp;
     memset(&cp, 0, sizeof(cp));
     GemmParams& p = cp.g;
@@ -643,19 +835,40 @@ extern "C" int neox_comm_gemm(const unsigned long long* a_ptrs, const unsigned l
     if (bias) vec = vec && al16(bias);
     if (add) vec = vec && al16(add) && (ldadd % 8 == 0);
     if (preact) vec = vec && al16(preact) && (ldpre % 8 == 0);
+    if (scatter && !vec) return NEOX_ERR_ALIGN;
     p.vec_ok = vec ? 1 : 0;
-    cp.world = world; cp.rank = rank; cp.a_split = a_split; cp.b_split = b_split;
-    cp.gather_flags = static_cast<const uint32_t*>(gather_flags); cp.gather_epoch = gather_epoch;
+    cp.world = world; cp.rank = rank;
+    cp.bcast = bcast ? 1 : 0;
+    if (bcast || dep) {
+        cp.shard_bytes = (long long)rows_per_shard * row_bytes;
+        cp.block_bytes = 128LL * row_bytes;
+        cp.blocks_per_rank = rows_per_shard / 128;
+        cp.pieces_per_block = (int)((cp.block_bytes + PIECE_BYTES - 1) / PIECE_BYTES);
+        cp.rows_per_shard = rows_per_shard;
+        cp.a_dep = a_dep; cp.b_dep = b_dep;
+        cp.dep_cnt = static_cast<const unsigned*>(dep_cnt);
+    }
+    if (bcast) {
+        cp.bc_src = static_cast<const uint4*>(bc_src);
+        for (int r = 0; r < world; ++r) {
+            cp.bc_dst[r] = reinterpret_cast<uint4*>(bc_dst_ptrs[r]);
+            cp.bc_cnt[r] = reinterpret_cast<unsigned*>(bc_cnt_ptrs[r]);
+        }
+        cp.bc_local_cnt = static_cast<unsigned*>(bc_local_cnt);
+        cp.bc_free_flags = static_cast<const uint32_t*>(bc_free_flags);
+        cp.bc_free_epoch = bc_free_epoch;
+    }
     cp.scatter = scatter; cp.rows_per_rank = rows_per_rank;
     cp.free_flags = static_cast<const uint32_t*>(free_flags); cp.free_epoch = free_epoch;
-    if (scatter)
-        for (int r = 0; r < world; ++r) cp.recv[r] = reinterpret_cast<__nv_bfloat16*>(recv_ptrs[r]);
-    cp.sig_offset = sig_offset; cp.sig_value = sig_value; cp.counter = static_cast<unsigned*>(counter);
-    if (sig_offset >= 0)
+    cp.sig_offset = sig_offset; cp.sig_value = sig_value;
+    cp.sig2_offset = sig2_offset; cp.sig2_value = sig2_value;
+    cp.counter = static_cast<unsigned*>(counter);
+    if (sig_offset >= 0 || sig2_offset >= 0)
         for (int r = 0; r < world; ++r) cp.peer_pad[r] = reinterpret_cast<uint32_t*>(pad_ptrs[r]);
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(comm_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(comm_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, COMM_SMEM_BYTES) !=
+            cudaSuccess)
             return NEOX_ERR_LAUNCH;
         attr_set = true;
     }
@@ -663,7 +876,15 @@ extern "C" int neox_comm_gemm(const unsigned long long* a_ptrs, const unsigned l
     int grid = num_m * num_n;
     const int sms = neox_sm_count();
     if (grid > sms) grid = sms;
-    comm_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(maps, cp);
+    if (bcast) {
+        // the last n_copy CTAs of the grid copy instead of computing; all CTAs must be co-resident (one per SM)
+        if (n_copy < 1) n_copy = 8;
+        if (n_copy > sms / 2) n_copy = sms / 2;
+        if (grid + n_copy > sms) grid = sms - n_copy;
+        cp.n_copy = n_copy;
+        grid += n_copy;
+    }
+    comm_gemm_kernel<<<grid, COMM_THREADS, COMM_SMEM_BYTES, stream>>>(tmA, tmB, outm, cp);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
@@ -730,5 +951,16 @@ extern "C" int neox_symm_gather(const unsigned long long* src_ptrs, void* dst, u
     symm_gather_kernel<<<copy_grid(per * world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         srcs, static_cast<uint4*>(dst), per, static_cast<const uint32_t*>(ready_flags), epoch, pads, world, rank,
         sig_offset, static_cast<unsigned*>(counter), status);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+extern "C" int neox_symm_release(void* cnt, int n, const unsigned long long* pad_ptrs, int world, int rank,
+                                 int sig_offset, unsigned epoch, void* stream) {
+    if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
+    PeerPads pads;
+    memset(&pads, 0, sizeof(pads));
+    for (int i = 0; i < world; ++i) pads.p[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
+    release_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned*>(cnt), n, pads, world, rank,
+                                                                      sig_offset, epoch);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }

@@ -36,11 +36,32 @@ from . import mpu
 from . import symm_mem as S
 
 _workspaces = {}
-_disabled_reason = None
+# CTAs of a broadcasting GEMM's grid that copy instead of computing (each moves roughly 40-60 GB/s)
+COPY_CTAS = int(os.environ.get("NEOX_COPY_CTAS", "16"))
+
+
+def fused_all_gather() -> bool:
+    """Whether gathered operands arrive by the in-GEMM broadcast (``NEOX_FUSED_AG=1``) or by an NCCL all-gather
+    before a plain GEMM (default).  Measured on 2 B200s at h=6144, 8192 tokens: the broadcast shares the L2 ports
+    with the GEMM's operand traffic and ends up 5-10% slower than "NCCL all-gather, then GEMM", while the pushed
+    reduce-scatter / all-reduce is 5-45% faster than its NCCL form and is always on."""
+    return os.environ.get("NEOX_FUSED_AG", "0") == "1"
+
+
+def _nccl_gather_rows(x2):
+    ws = workspace()
+    full = torch.empty(x2.shape[0] * ws.world, x2.shape[1], device=x2.device, dtype=x2.dtype)
+    dist.all_gather_into_tensor(full, x2, group=ws.group)
+    return full
 
 
 def enabled() -> bool:
     return os.environ.get("NEOX_FUSED_TP_COMM", "1") != "0" and torch.cuda.is_available()
+
+
+class _Gather:
+    """Handle of one gathered tensor (see ``Workspace.begin_gather``)."""
+    __slots__ = ("epoch", "shard", "rows", "cols", "buf", "full")
 
 
 class Workspace:
@@ -51,17 +72,21 @@ class Workspace:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.pad = S.SignalPad(group)
-        self.bufs = {"ag": [None, None], "recv": [None, None], "gath": [None, None]}
+        self.bufs = {"ag": [None, None], "recv": [None, None], "gath": [None, None], "full": [None, None]}
+        self.cnt = None
+        self._send_cnt = None
+        self._views = {}
         self.ag_epoch = 0
+        self.bc_epoch = 0
         self.rs_epoch = 0
         self._gath_last = [0, 0]
-        self.dev_null = ctypes.c_void_p(0)
 
     def _buf(self, kind, parity, nbytes):
         b = self.bufs[kind][parity]
         if b is None or b.nbytes < nbytes:
             # collective growth: shapes are identical on all ranks, so every rank gets here at the same op
             if b is not None:
+                self._views = {k: v for k, v in self._views.items() if k[0] != id(b)}
                 b.close()
             size = (int(nbytes * 1.0) + (1 << 21) - 1) // (1 << 21) * (1 << 21)
             b = S.SymmBuffer(size, self.group)
@@ -70,80 +95,117 @@ class Workspace:
 
     # ------------------------------------------------------------------ all-gather side
     def publish(self, x2):
-        """Stage this rank's shard ``x2`` ([rows, cols] bf16, contiguous) for the peers; returns the epoch."""
+        """Stage this rank's shard ``x2`` ([rows, cols] bf16, contiguous) for a stand-alone ``gather``."""
         assert x2.is_contiguous() and x2.dtype == torch.bfloat16
         self.ag_epoch += 1
         e = self.ag_epoch
         nbytes = x2.numel() * 2
         buf = self._buf("ag", e & 1, nbytes)
         L = native.lib()
-        rc = L.neox_symm_publish(native.ptr(x2), ctypes.c_void_p(buf.local), ctypes.c_ulonglong(nbytes),
+        rc = L.neox_symm_publish(native.ptr(x2), ctypes.c_void_p(buf.local), None, ctypes.c_ulonglong(nbytes),
                                  self.pad.word(S.AG_DONE), ctypes.c_uint((e - 2) & 0xFFFFFFFF), self.pad.c_ptrs,
                                  self.world, self.rank, S.AG_READY, ctypes.c_uint(e), self.pad.word(S.CTR_PUBLISH),
                                  ctypes.c_void_p(native.stream_ptr()))
         native.check(rc, "neox_symm_publish")
         return e
 
-    def _comm_gemm(self, a_ptrs, b_ptrs, out, M, N, K, lda, ldb, a_mn, b_mn, bias=None, add=None, preact=None, act=0,
-                   a_split=0, b_split=0, gather_epoch=0, scatter=False, recv=None, free_epoch=0, sig_offset=-1,
-                   sig_value=0):
+    def all_gather(self, x2):
+        """Stand-alone all-gather along dim 0 by peer loads (no GEMM to hide it behind)."""
+        e = self.publish(x2)
+        return self.gather(e, x2.shape[0], x2.shape[1])
+
+    def begin_gather(self, x2):
+        """Open a gathered view of the row-sharded tensor whose local shard is ``x2`` ([rows, cols] bf16).
+
+        Returns a handle ``h``; ``h.full`` is a [rows * world, cols] tensor over this rank's symmetric gathered
+        buffer.  Its contents arrive while a ``gemm(..., gather=h, bcast=True)`` runs on every rank of the group
+        (each rank broadcasts its own shard); a GEMM given ``dep="a"`` / ``"b"`` may read ``h.full`` as that operand
+        and waits block by block.  ``h.full`` may be read by any later kernel once such a dependent GEMM has finished,
+        until ``release(h)``; a tensor that must outlive that has to be cloned.
+        """
+        assert x2.is_contiguous() and x2.dtype == torch.bfloat16 and x2.shape[0] % 128 == 0
+        self.bc_epoch += 1
+        e = self.bc_epoch
+        rows, cols = x2.shape
+        assert rows * self.world // 128 <= S.CNT_WORDS
+        F = self._buf("full", e & 1, rows * self.world * cols * 2)
+        if self.cnt is None:
+            self.cnt = S.SymmBuffer(2 * S.CNT_WORDS * 4, self.group)
+        h = _Gather()
+        h.epoch, h.shard, h.rows, h.cols, h.buf = e, x2, rows, cols, F
+        # building a tensor over foreign memory costs ~1 ms of host time: keep one view per buffer and shape
+        key = (id(F), rows, cols)
+        view = self._views.get(key)
+        if view is None:
+            view = F.tensor((rows * self.world, cols))
+            self._views[key] = view
+        h.full = view
+        return h
+
+    def release(self, h):
+        """All local reads of ``h.full`` have been launched: let the peers overwrite the buffer (two epochs on)."""
+        par = h.epoch & 1
+        rc = native.lib().neox_symm_release(ctypes.c_void_p(self.cnt.local + par * S.CNT_WORDS * 4),
+                                            int(self.world * h.rows // 128), self.pad.c_ptrs, self.world, self.rank,
+                                            S.BC_DONE, ctypes.c_uint(h.epoch & 0xFFFFFFFF),
+                                            ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_symm_release")
+        h.full = None
+
+    def gemm(self, a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=None, add=None,
+             act=G.ACT_NONE, want_preact=False, gather=None, bcast=False, dep=None, scatter=None):
+        """The tcgen05 GEMM with an optional broadcast job and an optional pushed output.
+
+        ``gather``: handle from ``begin_gather``.  ``bcast``: this kernel sends the local shard to every rank's
+        gathered buffer while it computes.  ``dep`` ("a" / "b" / None): that operand is ``gather.full``; its loads
+        wait for the blocks to arrive.  ``scatter = (recv, epoch)``: push the output row blocks to their owners
+        instead of writing ``out``.
+        """
+        if a_mn:
+            K, M = a.shape
+        else:
+            M, K = a.shape
+        N = b.shape[1] if b_mn else b.shape[0]
+        pre = None
+        if scatter is None:
+            if out is None:
+                out = torch.empty(M, N, device=a.device, dtype=out_dtype)
+            if want_preact:
+                pre = torch.empty(M, N, device=a.device, dtype=torch.bfloat16)
+        if gather is not None:
+            h = gather
+            par = h.epoch & 1
+            cnt_off = par * S.CNT_WORDS * 4
+            if self._send_cnt is None:
+                self._send_cnt = torch.zeros(S.CNT_WORDS, device=a.device, dtype=torch.int32)
+            g_args = (native.ptr(h.shard) if bcast else None, h.buf.c_ptrs, self.cnt.offset_ptrs(cnt_off),
+                      native.ptr(self._send_cnt), self.pad.word(S.BC_DONE), ctypes.c_uint((h.epoch - 2) & 0xFFFFFFFF), int(h.rows),
+                      ctypes.c_longlong(h.cols * 2), ctypes.c_void_p(self.cnt.local + cnt_off), int(dep == "a"),
+                      int(dep == "b"))
+        else:
+            assert not bcast and dep is None
+            g_args = (None, None, None, None, None, ctypes.c_uint(0), 0, ctypes.c_longlong(0), None, 0, 0)
+        if scatter is not None:
+            recv, e = scatter
+            sc_args = (1, int(M // self.world), recv.c_ptrs, self.pad.word(S.RS_DONE),
+                       ctypes.c_uint((e - 2) & 0xFFFFFFFF))
+            sig = (S.RS_READY, ctypes.c_uint(e & 0xFFFFFFFF))
+        else:
+            sc_args = (0, 0, None, None, ctypes.c_uint(0))
+            sig = (-1, ctypes.c_uint(0))
         L = native.lib()
         rc = L.neox_comm_gemm(
-            a_ptrs, b_ptrs, native.ptr(out), M, N, K, ctypes.c_longlong(lda), ctypes.c_longlong(ldb),
-            ctypes.c_longlong(out.stride(0) if out is not None else N), int(a_mn), int(b_mn),
-            int(out is not None and out.dtype == torch.float32), native.ptr(bias), native.ptr(add),
+            native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, ctypes.c_longlong(a.stride(0)),
+            ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(out.stride(0) if out is not None else N), int(a_mn),
+            int(b_mn), int(out is not None and out.dtype == torch.float32), native.ptr(bias), native.ptr(add),
             ctypes.c_longlong(add.stride(0) if add is not None else 0),
-            int(add is not None and add.dtype == torch.float32), native.ptr(preact),
-            ctypes.c_longlong(preact.stride(0) if preact is not None else 0), int(act), self.world, self.rank,
-            int(a_split), int(b_split), self.pad.word(S.AG_READY), ctypes.c_uint(gather_epoch & 0xFFFFFFFF),
-            int(scatter), int(M // self.world if scatter else 0), recv.c_ptrs if recv is not None else None,
-            self.pad.word(S.RS_DONE), ctypes.c_uint(free_epoch & 0xFFFFFFFF), self.pad.c_ptrs, int(sig_offset),
-            ctypes.c_uint(sig_value & 0xFFFFFFFF), self.pad.word(S.CTR_GEMM), ctypes.c_void_p(native.stream_ptr()))
+            int(add is not None and add.dtype == torch.float32), native.ptr(pre),
+            ctypes.c_longlong(pre.stride(0) if pre is not None else 0), int(act), self.world, self.rank,
+            *g_args, *sc_args, self.pad.c_ptrs, sig[0], sig[1], -1, ctypes.c_uint(0), self.pad.word(S.CTR_GEMM),
+            int(COPY_CTAS), ctypes.c_void_p(native.stream_ptr()))
         native.check(rc, "neox_comm_gemm")
-
-    def gemm_a_gathered(self, epoch, rows, b, b_mn, out_dtype=torch.bfloat16, bias=None, act=G.ACT_NONE,
-                        want_preact=False, last_reader=True):
-        """``op(A_full) @ op(B)`` with A = concat over ranks of the published [rows, K] shards (K-major)."""
-        if b_mn:
-            K, N = b.shape
-        else:
-            N, K = b.shape
-        M = rows * self.world
-        out = torch.empty(M, N, device=b.device, dtype=out_dtype)
-        pre = torch.empty(M, N, device=b.device, dtype=torch.bfloat16) if want_preact else None
-        buf = self.bufs["ag"][epoch & 1]
-        self._comm_gemm(buf.c_ptrs, S._ull_array([b.data_ptr()]), out, M, N, K, K, b.stride(0), False, b_mn,
-                        bias=bias, preact=pre, act=act, a_split=rows, gather_epoch=epoch,
-                        sig_offset=S.AG_DONE if last_reader else -1, sig_value=epoch)
         return (out, pre) if want_preact else out
 
-    def wgrad_a_gathered(self, epoch, rows, cols_a, b, out=None, add=None, last_reader=True):
-        """``dW[cols_a, N] = A_full^T @ B`` where A_full = concat of published [rows, cols_a] shards (token-major)
-        and ``b`` = local [rows * world, N]."""
-        Kt, N = b.shape
-        assert Kt == rows * self.world
-        if out is None:
-            out = torch.empty(cols_a, N, device=b.device, dtype=torch.bfloat16)
-        buf = self.bufs["ag"][epoch & 1]
-        self._comm_gemm(buf.c_ptrs, S._ull_array([b.data_ptr()]), out, cols_a, N, Kt, cols_a, b.stride(0), True, True,
-                        add=add, a_split=rows, gather_epoch=epoch, sig_offset=S.AG_DONE if last_reader else -1,
-                        sig_value=epoch)
-        return out
-
-    def wgrad_b_gathered(self, a, epoch, rows, cols_b, out=None, add=None, last_reader=True):
-        """``dW[M, cols_b] = a^T @ B_full`` where ``a`` = local [rows * world, M] and B_full = concat of the published
-        [rows, cols_b] shards."""
-        Kt, M = a.shape
-        assert Kt == rows * self.world
-        if out is None:
-            out = torch.empty(M, cols_b, device=a.device, dtype=torch.bfloat16)
-        buf = self.bufs["ag"][epoch & 1]
-        self._comm_gemm(S._ull_array([a.data_ptr()]), buf.c_ptrs, out, M, cols_b, Kt, a.stride(0), cols_b, True, True,
-                        add=add, b_split=rows, gather_epoch=epoch, sig_offset=S.AG_DONE if last_reader else -1,
-                        sig_value=epoch)
-        return out
-
-    # ------------------------------------------------------------------ reduce-scatter / all-reduce side
     def gather(self, epoch, rows, cols, last_reader=True):
         """Materialise the concatenation of the published [rows, cols] shards as a local tensor."""
         out = torch.empty(rows * self.world, cols, device=torch.device("cuda", torch.cuda.current_device()),
@@ -158,11 +220,12 @@ class Workspace:
         return out
 
     def gemm_reduce(self, a, b, b_mn, bias=None, residual=None, all_reduce=False, partial_bias=None,
-                    partial_add=None):
+                    partial_add=None, gather=None):
         """``reduce_over_ranks(a @ op(b) + partial_bias + partial_add) + bias + residual``: returns this rank's
         [M / world, N] row block (reduce-scatter) or the whole [M, N] result (``all_reduce``).  The ``partial_*``
         terms are added to this rank's product before the reduction (in the GEMM epilogue), ``bias`` / ``residual``
-        once after it (``residual`` has the shape of the result)."""
+        once after it (``residual`` has the shape of the result).  ``gather``: a handle whose broadcast rides on this
+        GEMM as a prefetch for a later op (see ``gemm``)."""
         M, K = a.shape
         N = b.shape[1] if b_mn else b.shape[0]
         rows = M // self.world
@@ -170,9 +233,8 @@ class Workspace:
         e = self.rs_epoch
         recv = self._buf("recv", e & 1, M * N * 2)
         gath = self._buf("gath", e & 1, M * N * 2) if all_reduce else None
-        self._comm_gemm(S._ull_array([a.data_ptr()]), S._ull_array([b.data_ptr()]), None, M, N, K, a.stride(0),
-                        b.stride(0), False, b_mn, bias=partial_bias, add=partial_add, scatter=True, recv=recv,
-                        free_epoch=e - 2, sig_offset=S.RS_READY, sig_value=e)
+        self.gemm(a, b, False, b_mn, bias=partial_bias, add=partial_add, gather=gather, bcast=gather is not None,
+                  scatter=(recv, e))
         L = native.lib()
         out = torch.empty(M if all_reduce else rows, N, device=a.device, dtype=torch.bfloat16)
         if residual is not None:
@@ -215,6 +277,8 @@ def reset():
             for b in pair:
                 if b is not None:
                     b.close()
+        if ws.cnt is not None:
+            ws.cnt.close()
         ws.pad.close()
     _workspaces.clear()
 
@@ -252,9 +316,13 @@ class _ColumnSP(torch.autograd.Function):
             x2 = x2.contiguous()
         rows = x2.shape[0]
         need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
-        e = ws.publish(x2)
-        r = ws.gemm_a_gathered(e, rows, weight, False, bias=bias, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE,
-                               want_preact=need_pre)
+        act_id = G.ACT_GELU if act == "gelu" else G.ACT_NONE
+        if fused_all_gather():
+            h = ws.begin_gather(x2)
+            r = ws.gemm(h.full, weight, bias=bias, act=act_id, want_preact=need_pre, gather=h, bcast=True, dep="a")
+            ws.release(h)
+        else:
+            r = G.gemm(_nccl_gather_rows(x2), weight, bias=bias, act=act_id, want_preact=need_pre)
         out, pre = r if need_pre else (r, None)
         ctx.act, ctx.rows, ctx.x_shape, ctx.has_bias = act, rows, x.shape, bias is not None
         ctx.save_for_backward(x2, weight, pre)
@@ -272,11 +340,23 @@ class _ColumnSP(torch.autograd.Function):
             from ..ops.functional import dgelu_mul
             g2 = dgelu_mul(g2, pre)
         gx = gw = gb = None
-        if ctx.needs_input_grad[0]:
-            gx = ws.gemm_reduce(g2, weight, True).reshape(ctx.x_shape)
-        if ctx.needs_input_grad[1]:
-            e = ws.publish(x2)
-            gw = _accumulate_wgrad(weight, lambda out, add: ws.wgrad_b_gathered(g2, e, ctx.rows, K, out=out, add=add))
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if fused_all_gather():
+            h = ws.begin_gather(x2) if need_w else None
+            if need_x:
+                # the data-gradient GEMM carries the broadcast of x as a prefetch for the weight-gradient GEMM
+                gx = ws.gemm_reduce(g2, weight, True, gather=h).reshape(ctx.x_shape)
+            if need_w:
+                gw = _accumulate_wgrad(weight, lambda out, add: ws.gemm(g2, h.full, True, True, out=out, add=add,
+                                                                        gather=h, bcast=not need_x, dep="b"))
+                ws.release(h)
+        else:
+            if need_x:
+                gx = ws.gemm_reduce(g2, weight, True).reshape(ctx.x_shape)
+            if need_w:
+                full = _nccl_gather_rows(x2)
+                gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g2, full, a_mn=True, b_mn=True, out=out,
+                                                                       add=add))
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
         return gx, gw, gb, None
@@ -324,28 +404,33 @@ class _Row(torch.autograd.Function):
         need_full_bias = ctx.has_bias and ctx.bias_partial and ctx.needs_input_grad[2]
         if not ctx.sp:
             g_full = g2                                   # backward of an all-reduce is the identity
-        elif need_add or need_full_bias:
-            e = ws.publish(g2)
-            g_full = ws.gather(e, g2.shape[0], N)        # the addend's gradient is the gathered tensor itself
-        else:
-            g_full = None
-        if g_full is not None:
             if need_x:
                 gx = G.gemm(g_full, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
             if need_w:
                 gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g_full, x2, a_mn=True, b_mn=True, out=out,
                                                                        add=add))
-            if need_add:
-                g_add = g_full.reshape(ctx.add_shape)
         else:
-            rows = g2.shape[0]
-            e = ws.publish(g2)
-            if need_x:
-                gx = ws.gemm_a_gathered(e, rows, weight, True, last_reader=not need_w).reshape(ctx.x_shape)
-            if need_w:
-                gw = _accumulate_wgrad(weight, lambda out, add: ws.wgrad_a_gathered(e, rows, N, x2, out=out, add=add))
-            if not (need_x or need_w):
-                ws.gather(e, rows, N)                     # keeps the epoch protocol balanced (never hit in training)
+            # backward of the reduce-scatter is an all-gather of g: it arrives while the first GEMM that reads it runs
+            if not fused_all_gather():
+                g_full = _nccl_gather_rows(g2)
+                if need_x:
+                    gx = G.gemm(g_full, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
+                if need_w:
+                    gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g_full, x2, a_mn=True, b_mn=True, out=out,
+                                                                           add=add))
+            elif need_x or need_w:
+                h = ws.begin_gather(g2)
+                if need_x:
+                    gx = ws.gemm(h.full, weight, False, True, gather=h, bcast=True, dep="a").reshape(ctx.x_shape)
+                if need_w:
+                    gw = _accumulate_wgrad(weight, lambda out, add: ws.gemm(h.full, x2, True, True, out=out, add=add,
+                                                                            gather=h, bcast=not need_x, dep="a"))
+                g_full = h.full.clone() if (need_add or need_full_bias) else None
+                ws.release(h)
+            else:
+                g_full = ws.all_gather(g2)
+        if need_add:
+            g_add = g_full.reshape(ctx.add_shape)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             # post-reduction bias under SP: partial over this rank's shard, summed with the other replicated grads
             gb = (g_full if (ctx.bias_partial or not ctx.sp) else g2).sum(0)

@@ -25,6 +25,8 @@ MAX_RANKS = 8
 # word offsets inside the signal pad (each block has one slot per rank)
 AG_READY, AG_DONE, RS_READY, RS_DONE, AR_READY, AR_DONE = 0, 8, 16, 24, 32, 40
 CTR_PUBLISH, CTR_GEMM, CTR_REDUCE, CTR_GCOPY = 48, 49, 50, 51
+BC_DONE = 56                      # gathered-buffer release flags of the in-GEMM broadcast
+CNT_WORDS = 4096                  # block counters per buffer parity
 PAD_BYTES = 4096
 
 

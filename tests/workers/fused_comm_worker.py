@@ -42,29 +42,34 @@ def main():
         return (torch.randn(*shape, device=dev, generator=g) * scale).to(torch.bfloat16)
 
     for it in range(5):                            # > 2 iterations: both buffer parities get reused
-        # ---- all-gather -> GEMM (A gathered along M), K-major B and MN-major B
+        # ---- all-gather -> GEMM: the shards arrive while the GEMM runs; K-major B, then MN-major B
         x = rnd(rows, K)
         w = rnd(N, K, scale=0.05)
         full = torch.empty(rows * world, K, device=dev, dtype=torch.bfloat16)
         dist.all_gather_into_tensor(full, x, group=grp)
-        e = ws.publish(x)
-        y = ws.gemm_a_gathered(e, rows, w, False, last_reader=False)
+        h = ws.begin_gather(x)
+        y = ws.gemm(h.full, w, gather=h, bcast=True, dep="a")
         ok &= close(y, full.float() @ w.float().t(), 2e-2, f"ag_gemm it{it}")
+        ok &= bool(torch.equal(h.full, full))
         w2 = rnd(K, N, scale=0.05)
-        y2 = ws.gemm_a_gathered(e, rows, w2, True, last_reader=False)
+        y2 = ws.gemm(h.full, w2, False, True, gather=h, dep="a")       # second reader of the same gathered buffer
         ok &= close(y2, full.float() @ w2.float(), 2e-2, f"ag_gemm(b_mn) it{it}")
+        ws.release(h)
         # ---- wgrad with the gathered operand on the A side:  dW[K, N2] = full^T @ b
         b = rnd(rows * world, 384)
-        dw = ws.wgrad_a_gathered(e, rows, K, b, last_reader=False)
+        h = ws.begin_gather(x)
+        dw = ws.gemm(h.full, b, True, True, gather=h, bcast=True, dep="a")
+        ws.release(h)
         ok &= close(dw, full.float().t() @ b.float(), 2e-2, f"wgrad_a it{it}")
         # ---- ... and on the B side, accumulating into fp32:  dW[M2, K] += a^T @ full
         a = rnd(rows * world, 256)
         acc = torch.ones(256, K, device=dev, dtype=torch.float32)
-        ws.wgrad_b_gathered(a, e, rows, K, out=acc, add=acc, last_reader=False)
+        h = ws.begin_gather(x)
+        ws.gemm(a, h.full, True, True, out=acc, add=acc, gather=h, bcast=True, dep="b")
+        ws.release(h)
         ok &= close(acc, 1.0 + a.float().t() @ full.float(), 2e-2, f"wgrad_b it{it}")
-        # ---- plain gather (last reader: releases the staging buffer)
-        gat = ws.gather(e, rows, K)
-        ok &= bool(torch.equal(gat, full))
+        # ---- stand-alone all-gather by peer loads
+        ok &= bool(torch.equal(ws.all_gather(x), full))
 
         # ---- GEMM -> reduce-scatter, with post-reduction bias and residual
         xa = rnd(rows * world, K)
@@ -87,8 +92,12 @@ def main():
         part3 = (dy.float() @ wr.float()).to(torch.bfloat16).float()
         ref3 = torch.empty(rows, K, device=dev, dtype=torch.float32)
         dist.reduce_scatter_tensor(ref3, part3.contiguous(), group=grp)
-        out3 = ws.gemm_reduce(dy, wr, True)
+        h = ws.begin_gather(x)
+        out3 = ws.gemm_reduce(dy, wr, True, gather=h)                 # the broadcast rides along as a prefetch
         ok &= close(out3, ref3, 2e-2, f"gemm_rs(b_mn) it{it}")
+        dw3 = ws.gemm(a, h.full, True, True, gather=h, dep="b")       # ... for this GEMM, which only checks arrival
+        ws.release(h)
+        ok &= close(dw3, a.float().t() @ full.float(), 2e-2, f"prefetched wgrad it{it}")
 
     st = native.read_status()
     if st != 0:
@@ -101,7 +110,8 @@ def main():
     from gpt_neox_b200.parallel.layers import ColumnParallelLinear, RowParallelLinear
     from gpt_neox_b200.parallel.rng import model_parallel_cuda_manual_seed
     model_parallel_cuda_manual_seed(4321)
-    for sp in (True, False):
+    for sp, fused_ag in ((True, "1"), (True, "0"), (False, "0")):
+        os.environ["NEOX_FUSED_AG"] = fused_ag
         args = make_args(hidden_size=512, num_attention_heads=8, seq_length=128 * world,
                          max_position_embeddings=128 * world, precision="bfloat16", model_parallel_size=world,
                          sequence_parallel=sp, train_micro_batch_size_per_gpu=4, global_num_gpus=world,
