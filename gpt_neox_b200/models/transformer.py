@@ -21,7 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
-from ..ops.attention import attention_ref, flash_attention
+from ..ops.attention import attention_ref, flash_attention, packed_qkv_attention, packed_qkv_ok
 from ..ops.linear import linear as fused_linear
 from ..parallel import mappings as M
 from ..parallel import mpu
@@ -77,8 +77,11 @@ class ParallelMLP(nn.Module):
         With ``post_residual`` it returns ``reduce(mlp + bias + partial_add) + post_residual`` as one tensor."""
         l1 = self.linear1
         if self.activation_type == "gelu":
-            # bias + GeLU in the GEMM epilogue
-            inter = l1.matmul(hidden_states, l1.bias, act="gelu")
+            # bias + GeLU in linear1's epilogue; GeLU' in linear2's data-gradient epilogue
+            inter, pre = l1.matmul(hidden_states, l1.bias, act="gelu", split_pre=True)
+            if post_residual is not None:
+                return self.linear2.forward_reduced(inter, partial_add, post_residual, dgelu_aux=pre)
+            return self.linear2(inter, residual=residual, dgelu_aux=pre)
         else:
             inter, bias = l1(hidden_states)
             if self.is_gated:
@@ -278,8 +281,34 @@ class ParallelSelfAttention(nn.Module):
         ctx = torch.matmul(probs, v.permute(1, 2, 0, 3))                  # [b, np, sq, hn]
         return ctx.permute(2, 0, 1, 3).contiguous()
 
+    def _packed_path(self, hidden_states, layer_past):
+        """rotary + flash attention on the packed QKV projection, in place (training / no kv-cache)."""
+        if self.gqa or self.use_qk_layernorm or self.use_cache or self.rpe is not None or self.sparse or \
+                (self.dropout_p > 0 and self.training) or (layer_past is not None and layer_past[0].numel() > 0):
+            return None
+        mixed, _ = self.query_key_value(hidden_states)
+        np_, hn = self.num_attention_heads_per_partition, self.hidden_size_per_attention_head
+        mixed = mixed.view(*mixed.shape[:-1], np_, 3 * hn)
+        if not packed_qkv_ok(mixed, hn):
+            return (mixed,)
+        cos = sin = None
+        if self.rotary_emb is not None:
+            cos, sin = self.rotary_emb(mixed, seq_len=mixed.shape[0])
+            cos, sin = cos[:mixed.shape[0]], sin[:mixed.shape[0]]
+        slopes = self.alibi_embed.slopes if self.pos_emb == "alibi" else None
+        return packed_qkv_attention(mixed, cos, sin, causal=True, softmax_scale=(self.coeff or 1.0) / self.norm_factor,
+                                    window=self.sliding_window_width, alibi_slopes=slopes)
+
     def forward(self, hidden_states, attention_mask=None, layer_past=None, residual=None):
-        q, k, v = self._project(hidden_states)
+        packed = self._packed_path(hidden_states, layer_past)
+        if packed is not None and not isinstance(packed, tuple):
+            ctx = packed.reshape(packed.shape[0], packed.shape[1], self.hidden_size_per_partition)
+            return self.dense(ctx, residual=residual)
+        if isinstance(packed, tuple):
+            mixed, hn = packed[0], self.hidden_size_per_attention_head
+            q, k, v = mixed[..., :hn], mixed[..., hn:2 * hn], mixed[..., 2 * hn:]
+        else:
+            q, k, v = self._project(hidden_states)
         if self.use_qk_layernorm:
             q, k = self.qk_layernorm(q), self.qk_layernorm(k)
         if self.rotary_emb is not None:

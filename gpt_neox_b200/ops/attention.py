@@ -104,6 +104,100 @@ class _FlashFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+class _PackedQKVFn(torch.autograd.Function):
+    """Rotary embedding + causal flash attention on the packed projection ``mixed`` = [s, b, heads, 3 * d]
+    (q | k | v per head), entirely in place:
+
+    * forward rotates the first ``rot`` dims of q and k INSIDE ``mixed`` (its producer, the QKV GEMM, does not need
+      its own output again) and runs the attention kernel on the three strided views;
+    * backward lets the attention kernels write dq / dk / dv straight into the three views of one ``d_mixed``
+      buffer and un-rotates dq and dk there, so the gradient of the projection is born packed.
+
+    Compared with slicing + out-of-place rotary this removes two full-tensor rotary passes, the three zero-filled
+    slice gradients and their adds, and the contiguous copies in front of the QKV weight-gradient GEMM.
+    """
+
+    @staticmethod
+    def forward(ctx, mixed, cos, sin, causal, scale, window, slopes):
+        s, b, h, d3 = mixed.shape
+        d = d3 // 3
+        assert mixed.is_contiguous()
+        q, k, v = mixed[..., :d], mixed[..., d:2 * d], mixed[..., 2 * d:]
+        L = native.lib()
+        ll = ctypes.c_longlong
+        rot = 0
+        c = sn = None
+        if cos is not None:
+            rot = cos.shape[-1]
+            c = cos.reshape(-1, rot)[:s].float().contiguous()
+            sn = sin.reshape(-1, rot)[:s].float().contiguous()
+            rc = L.neox_rope_qk_inplace(native.ptr(q), native.ptr(k), native.ptr(c), native.ptr(sn), s, b, h, h, rot,
+                                        ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
+                                        ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)), 0, _DT[mixed.dtype], _s())
+            native.check(rc, "neox_rope_qk_inplace")
+        out = torch.empty(s, b, h, d, dtype=mixed.dtype, device=mixed.device)
+        lse = torch.empty(b, h, s, dtype=torch.float32, device=mixed.device)
+        rc = L.neox_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse),
+                              s, s, b, h, h, d,
+                              ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
+                              ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+                              ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)),
+                              ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
+                              native.ptr(slopes), _s())
+        native.check(rc, "neox_flash_fwd")
+        empty = torch.empty(0, device=mixed.device)
+        ctx.save_for_backward(mixed, out, lse, slopes if slopes is not None else empty,
+                              c if c is not None else empty, sn if sn is not None else empty)
+        ctx.cfg = (causal, scale, window, slopes is not None, rot)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        mixed, out, lse, slopes, c, sn = ctx.saved_tensors
+        causal, scale, window, has_slopes, rot = ctx.cfg
+        s, b, h, d3 = mixed.shape
+        d = d3 // 3
+        q, k, v = mixed[..., :d], mixed[..., d:2 * d], mixed[..., 2 * d:]
+        do = do.contiguous()
+        dm = torch.empty_like(mixed)
+        dq, dk, dv = dm[..., :d], dm[..., d:2 * d], dm[..., 2 * d:]
+        delta = torch.empty(b, h, s, dtype=torch.float32, device=mixed.device)
+        L = native.lib()
+        ll = ctypes.c_longlong
+        gs = (ctypes.c_longlong * 9)(dq.stride(0), dq.stride(1), dq.stride(2), dk.stride(0), dk.stride(1), dk.stride(2),
+                                     dv.stride(0), dv.stride(1), dv.stride(2))
+        rc = L.neox_flash_bwd_strided(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(do),
+                                      native.ptr(lse), native.ptr(dq), native.ptr(dk), native.ptr(dv),
+                                      native.ptr(delta), s, s, b, h, h, d,
+                                      ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
+                                      ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+                                      ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), gs,
+                                      ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
+                                      native.ptr(slopes) if has_slopes else None, _s())
+        native.check(rc, "neox_flash_bwd_strided")
+        if rot:
+            rc = L.neox_rope_qk_inplace(native.ptr(dq), native.ptr(dk), native.ptr(c), native.ptr(sn), s, b, h, h, rot,
+                                        ll(dq.stride(0)), ll(dq.stride(1)), ll(dq.stride(2)),
+                                        ll(dk.stride(0)), ll(dk.stride(1)), ll(dk.stride(2)), 1, _DT[mixed.dtype], _s())
+            native.check(rc, "neox_rope_qk_inplace")
+        return dm, None, None, None, None, None, None
+
+
+def packed_qkv_ok(mixed, head_dim) -> bool:
+    return (mixed.is_cuda and native.available() and mixed.dtype == torch.bfloat16 and mixed.dim() == 4
+            and mixed.is_contiguous() and head_dim in (64, 96, 128) and mixed.shape[-1] == 3 * head_dim
+            and have_flash_kernel())
+
+
+def packed_qkv_attention(mixed, cos=None, sin=None, causal=True, softmax_scale=None, window=None, alibi_slopes=None):
+    """``flash_attention(rope(q), rope(k), v)`` for ``mixed`` = [s, b, heads, 3 * d]; ``mixed`` is overwritten.
+    ``cos`` / ``sin``: [s, 1, 1, rot] tables (None = no rotary)."""
+    d = mixed.shape[-1] // 3
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    slopes = alibi_slopes.float().contiguous() if alibi_slopes is not None else None
+    return _PackedQKVFn.apply(mixed, cos, sin, causal, scale, window, slopes)
+
+
 _FLASH_IMPL = {"fwd": None}
 
 

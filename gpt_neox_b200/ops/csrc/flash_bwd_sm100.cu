@@ -32,7 +32,8 @@ struct BwdParams {
     const float* slopes;
     const float* lse;    // [b, hq, sq] natural log
     const float* delta;  // [b, hq, sq]
-    __nv_bfloat16 *dq, *dk, *dv;  // contiguous [s, b, h, d]
+    __nv_bfloat16 *dq, *dk, *dv;  // [s, b, h, d] views; element strides of (s, b, h) below, d contiguous
+    long long dq_s[3], dk_s[3], dv_s[3];
     int* status;
 };
 
@@ -315,8 +316,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         const bool live = kv < p.sk;
         if (ok) {
-            __nv_bfloat16* dkp = p.dk + (((size_t)(live ? kv : 0) * p.b + bb) * p.hkv + hk) * D;
-            __nv_bfloat16* dvp = p.dv + (((size_t)(live ? kv : 0) * p.b + bb) * p.hkv + hk) * D;
+            __nv_bfloat16* dkp = p.dk + (long long)(live ? kv : 0) * p.dk_s[0] + bb * p.dk_s[1] + hk * p.dk_s[2];
+            __nv_bfloat16* dvp = p.dv + (long long)(live ? kv : 0) * p.dv_s[0] + bb * p.dv_s[1] + hk * p.dv_s[2];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
@@ -565,7 +566,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
         const bool live = q < p.sq;
         if (ok) {
-            __nv_bfloat16* dqp = p.dq + (((size_t)(live ? q : 0) * p.b + bb) * p.hq + h) * D;
+            __nv_bfloat16* dqp = p.dq + (long long)(live ? q : 0) * p.dq_s[0] + bb * p.dq_s[1] + h * p.dq_s[2];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
@@ -615,12 +616,38 @@ int launch_bwd(const CUtensorMap (&t)[8], const BwdParams& p, cudaStream_t st) {
 }  // namespace
 
 // delta_ws: fp32 scratch of b*hq*sq elements (row sums of dO*O), provided by the caller.
+// dq / dk / dv are [s, b, h, d] views with element strides g_s = {dq_ss, dq_sb, dq_sh, dk_ss, ..., dv_sh}; rows must be
+// 16-byte aligned (strides multiples of 8 elements).
+extern "C" int neox_flash_bwd_strided(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                      const float* lse, void* dq, void* dk, void* dv, float* delta_ws, int sq, int sk,
+                                      int b, int hq, int hkv, int d, long long q_ss, long long q_sb, long long q_sh,
+                                      long long k_ss, long long k_sb, long long k_sh, long long v_ss, long long v_sb,
+                                      long long v_sh, const long long* g_s, float scale, int causal, int window,
+                                      const float* slopes, void* stream);
+
 extern "C" int neox_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                               const float* lse, void* dq, void* dk, void* dv, float* delta_ws, int sq, int sk, int b,
                               int hq, int hkv, int d, long long q_ss, long long q_sb, long long q_sh, long long k_ss,
                               long long k_sb, long long k_sh, long long v_ss, long long v_sb, long long v_sh,
                               float scale, int causal, int window, const float* slopes, void* stream) {
+    const long long g_s[9] = {(long long)b * hq * d,  (long long)hq * d,  d, (long long)b * hkv * d, (long long)hkv * d, d,
+                              (long long)b * hkv * d, (long long)hkv * d, d};
+    return neox_flash_bwd_strided(q, k, v, out, dout, lse, dq, dk, dv, delta_ws, sq, sk, b, hq, hkv, d, q_ss, q_sb, q_sh,
+                                  k_ss, k_sb, k_sh, v_ss, v_sb, v_sh, g_s, scale, causal, window, slopes, stream);
+}
+
+extern "C" int neox_flash_bwd_strided(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                      const float* lse, void* dq, void* dk, void* dv, float* delta_ws, int sq, int sk,
+                                      int b, int hq, int hkv, int d, long long q_ss, long long q_sb, long long q_sh,
+                                      long long k_ss, long long k_sb, long long k_sh, long long v_ss, long long v_sb,
+                                      long long v_sh, const long long* g_s, float scale, int causal, int window,
+                                      const float* slopes, void* stream) {
     if (d != 64 && d != 96 && d != 128) return NEOX_ERR_SHAPE;
+    for (int i = 0; i < 9; ++i)
+        if (g_s[i] % 8) return NEOX_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(dq) & 15) || (reinterpret_cast<uintptr_t>(dk) & 15) ||
+        (reinterpret_cast<uintptr_t>(dv) & 15))
+        return NEOX_ERR_ALIGN;
     if (sq <= 0 || sk <= 0 || b <= 0) return 0;
     if (hq % hkv) return NEOX_ERR_SHAPE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -649,6 +676,11 @@ extern "C" int neox_flash_bwd(const void* q, const void* k, const void* v, const
     p.causal = causal; p.window = window; p.slopes = slopes;
     p.lse = lse; p.delta = delta_ws;
     p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
+    for (int i = 0; i < 3; ++i) {
+        p.dq_s[i] = g_s[i];
+        p.dk_s[i] = g_s[3 + i];
+        p.dv_s[i] = g_s[6 + i];
+    }
     p.status = neox_status_word();
     if (!p.status) return NEOX_ERR_DRIVER;
     if (d == 64) return launch_bwd<64>(t, p, st);

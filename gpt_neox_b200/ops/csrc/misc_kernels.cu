@@ -160,6 +160,35 @@ __global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, T* _
     }
 }
 
+// In-place rotary embedding of the first `rot` dims of every head of q and k (views of one packed QKV tensor): one
+// thread owns the pair (e, e + rot/2), so nothing is read after it was overwritten.  cs / sn: [s, rot] fp32.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_qk_inplace_kernel(T* __restrict__ q, T* __restrict__ k,
+                                                              const float* __restrict__ cs, const float* __restrict__ sn,
+                                                              int s, int b, int hq, int hk, int rot, long long q_ss,
+                                                              long long q_sb, long long q_sh, long long k_ss,
+                                                              long long k_sb, long long k_sh, int inverse) {
+    const int half = rot >> 1;
+    const int heads = hq + hk;
+    const long long total = (long long)s * b * heads * half;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int e = (int)(i % half);
+        long long r = i / half;
+        const int hh = (int)(r % heads);
+        r /= heads;
+        const int bb = (int)(r % b);
+        const int sI = (int)(r / b);
+        T* xp = hh < hq ? q + sI * q_ss + bb * q_sb + hh * q_sh : k + sI * k_ss + bb * k_sb + (hh - hq) * k_sh;
+        const float a = to_f<T>(xp[e]), c2 = to_f<T>(xp[e + half]);
+        const float* cr = cs + (long long)sI * rot;
+        const float* sr = sn + (long long)sI * rot;
+        const float sg = inverse ? -1.f : 1.f;
+        xp[e] = from_f<T>(a * cr[e] - c2 * sr[e] * sg);
+        xp[e + half] = from_f<T>(c2 * cr[e + half] + a * sr[e + half] * sg);
+    }
+}
+
 // ------------------------------------------------------------------ cross entropy
 template <typename T>
 __global__ void __launch_bounds__(256) row_max_kernel(const T* __restrict__ x, float* __restrict__ out, int rows,
@@ -311,6 +340,17 @@ int neox_rope(const void* x, void* out, const float* cs, const float* sn, int s,
     cudaStream_t st = (cudaStream_t)stream;
     DISPATCH(dtype, (rope_kernel<T><<<grid_for(total, 16), 256, 0, st>>>((const T*)x, (T*)out, cs, sn, s, b, h, d, rot,
                                                                          ss, sb, sh, inverse)));
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_rope_qk_inplace(void* q, void* k, const float* cs, const float* sn, int s, int b, int hq, int hk, int rot,
+                         long long q_ss, long long q_sb, long long q_sh, long long k_ss, long long k_sb, long long k_sh,
+                         int inverse, int dtype, void* stream) {
+    const long long total = (long long)s * b * (hq + hk) * (rot / 2);
+    if (total <= 0) return 0;
+    if (rot % 2) return NEOX_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dtype, (rope_qk_inplace_kernel<T><<<grid_for(total, 16), 256, 0, st>>>(
+                        (T*)q, (T*)k, cs, sn, s, b, hq, hk, rot, q_ss, q_sb, q_sh, k_ss, k_sb, k_sh, inverse)));
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 int neox_row_max(const void* x, float* out, int rows, int cols, int dtype, void* stream) {

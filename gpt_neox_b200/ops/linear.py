@@ -26,9 +26,15 @@ def kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 class _LinearFn(torch.autograd.Function):
+    """``split_pre``: also return the pre-activation (non-differentiable) and expect the incoming gradient to be
+    w.r.t. the PRE-activation already.  ``dgelu_aux``: the pre-activation of the layer that produced ``x``; the data
+    gradient is multiplied by GeLU'(aux) in the dgrad GEMM's epilogue.  Together they move the GeLU backward of an
+    MLP out of a separate element-wise pass and into the second linear's dgrad GEMM."""
+
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, act):
+    def forward(ctx, x, weight, bias, residual, act, dgelu_aux=None, split_pre=False):
         ctx.act = act
+        ctx.split_pre = split_pre
         ctx.x_shape = x.shape
         N, K = weight.shape
         x2 = x.reshape(-1, K)
@@ -52,25 +58,36 @@ class _LinearFn(torch.autograd.Function):
                 out = out + res2
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
-        ctx.save_for_backward(x2, weight, pre)
-        return out.reshape(*x.shape[:-1], N)
+        ctx.has_aux = dgelu_aux is not None
+        aux2 = dgelu_aux.reshape(-1, K) if dgelu_aux is not None else None
+        ctx.save_for_backward(x2, weight, None if split_pre else pre, aux2)
+        out = out.reshape(*x.shape[:-1], N)
+        if split_pre:
+            if pre is not None:
+                pre = pre.reshape(*x.shape[:-1], N)
+                ctx.mark_non_differentiable(pre)
+            return out, pre
+        return out
 
     @staticmethod
-    def backward(ctx, g):
-        x2, weight, pre = ctx.saved_tensors
+    def backward(ctx, g, g_pre=None):
+        x2, weight, pre, aux2 = ctx.saved_tensors
         N, K = weight.shape
         g_in = g
         g2 = g.reshape(-1, N)
         if not g2.is_contiguous():
             g2 = g2.contiguous()
         g_res = g_in if ctx.has_res else None
-        if ctx.act == "gelu":
+        if ctx.act == "gelu" and not ctx.split_pre:
             from .functional import dgelu_mul
             g2 = dgelu_mul(g2, pre)
         gx = gw = gb = None
         if ctx.use_k and g2.dtype == torch.bfloat16:
             if ctx.needs_input_grad[0]:
-                gx = G.gemm(g2, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
+                if aux2 is not None:
+                    gx = G.gemm(g2, weight, a_mn=False, b_mn=True, act=G.ACT_DGELU, aux=aux2).reshape(ctx.x_shape)
+                else:
+                    gx = G.gemm(g2, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
             if ctx.needs_input_grad[1]:
                 mg = getattr(weight, "main_grad", None)
                 if mg is not None:
@@ -80,7 +97,10 @@ class _LinearFn(torch.autograd.Function):
                     gw = G.gemm(g2, x2, a_mn=True, b_mn=True)
         else:
             if ctx.needs_input_grad[0]:
-                gx = (g2 @ weight).reshape(ctx.x_shape)
+                gx = g2 @ weight
+                if aux2 is not None:
+                    gx = (gx.float() * G.dgelu_tanh_ref(aux2.float())).to(gx.dtype)
+                gx = gx.reshape(ctx.x_shape)
             if ctx.needs_input_grad[1]:
                 gw = g2.t() @ x2
                 mg = getattr(weight, "main_grad", None)
@@ -90,9 +110,10 @@ class _LinearFn(torch.autograd.Function):
                     gw = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
-        return gx, gw, gb, g_res, None
+        return gx, gw, gb, g_res, None, None, None
 
 
-def linear(x, weight, bias=None, residual=None, act=None):
-    """``act(x @ weight.T + bias) + residual`` with the epilogue fused into the GEMM."""
-    return _LinearFn.apply(x, weight, bias, residual, act)
+def linear(x, weight, bias=None, residual=None, act=None, dgelu_aux=None, split_pre=False):
+    """``act(x @ weight.T + bias) + residual`` with the epilogue fused into the GEMM (see ``_LinearFn`` for the
+    two GeLU-backward options)."""
+    return _LinearFn.apply(x, weight, bias, residual, act, dgelu_aux, split_pre)

@@ -308,7 +308,7 @@ class _ColumnSP(torch.autograd.Function):
     """Column-parallel linear under sequence parallelism: input [rows, K] is this rank's sequence shard."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, act):
+    def forward(ctx, x, weight, bias, act, split_pre=False):
         ws = workspace()
         N, K = weight.shape
         x2 = x.reshape(-1, K)
@@ -316,6 +316,7 @@ class _ColumnSP(torch.autograd.Function):
             x2 = x2.contiguous()
         rows = x2.shape[0]
         need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
+        ctx.split_pre = split_pre
         act_id = G.ACT_GELU if act == "gelu" else G.ACT_NONE
         if fused_all_gather():
             h = ws.begin_gather(x2)
@@ -325,18 +326,24 @@ class _ColumnSP(torch.autograd.Function):
             r = G.gemm(_nccl_gather_rows(x2), weight, bias=bias, act=act_id, want_preact=need_pre)
         out, pre = r if need_pre else (r, None)
         ctx.act, ctx.rows, ctx.x_shape, ctx.has_bias = act, rows, x.shape, bias is not None
-        ctx.save_for_backward(x2, weight, pre)
-        return out.reshape(x.shape[0] * ws.world, *x.shape[1:-1], N)
+        ctx.save_for_backward(x2, weight, None if split_pre else pre)
+        out = out.reshape(x.shape[0] * ws.world, *x.shape[1:-1], N)
+        if split_pre:
+            if pre is not None:
+                pre = pre.reshape(out.shape)
+                ctx.mark_non_differentiable(pre)
+            return out, pre
+        return out
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, g, g_pre=None):
         ws = workspace()
         x2, weight, pre = ctx.saved_tensors
         N, K = weight.shape
         g2 = g.reshape(-1, N)
         if not g2.is_contiguous():
             g2 = g2.contiguous()
-        if ctx.act == "gelu":
+        if ctx.act == "gelu" and not ctx.split_pre:
             from ..ops.functional import dgelu_mul
             g2 = dgelu_mul(g2, pre)
         gx = gw = gb = None
@@ -359,7 +366,7 @@ class _ColumnSP(torch.autograd.Function):
                                                                        add=add))
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
-        return gx, gw, gb, None
+        return gx, gw, gb, None, None
 
 
 class _Row(torch.autograd.Function):
@@ -371,7 +378,7 @@ class _Row(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, partial_add, sp, bias_partial):
+    def forward(ctx, x, weight, bias, residual, partial_add, sp, bias_partial, dgelu_aux=None):
         ws = workspace()
         N, K = weight.shape
         x2 = x.reshape(-1, K)
@@ -386,26 +393,33 @@ class _Row(torch.autograd.Function):
         ctx.x_shape, ctx.sp, ctx.bias_partial = x.shape, sp, bias_partial
         ctx.has_bias, ctx.has_res, ctx.has_add = bias is not None, residual is not None, partial_add is not None
         ctx.add_shape = partial_add.shape if partial_add is not None else None
-        ctx.save_for_backward(x2, weight)
+        ctx.save_for_backward(x2, weight, dgelu_aux.reshape(-1, K) if dgelu_aux is not None else None)
         lead = x.shape[0] // ws.world if sp else x.shape[0]
         return out.reshape(lead, *x.shape[1:-1], N)
 
     @staticmethod
     def backward(ctx, g):
         ws = workspace()
-        x2, weight = ctx.saved_tensors
+        x2, weight, aux2 = ctx.saved_tensors
         N, K = weight.shape
         g2 = g.reshape(-1, N)
         if not g2.is_contiguous():
             g2 = g2.contiguous()
         gx = gw = gb = g_add = None
+
+        def dgrad(gf):
+            # the GeLU' factor of the producing layer rides in this GEMM's epilogue
+            if aux2 is not None:
+                return G.gemm(gf, weight, a_mn=False, b_mn=True, act=G.ACT_DGELU, aux=aux2)
+            return G.gemm(gf, weight, a_mn=False, b_mn=True)
+
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         need_add = ctx.has_add and ctx.needs_input_grad[4]
         need_full_bias = ctx.has_bias and ctx.bias_partial and ctx.needs_input_grad[2]
         if not ctx.sp:
             g_full = g2                                   # backward of an all-reduce is the identity
             if need_x:
-                gx = G.gemm(g_full, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
+                gx = dgrad(g_full).reshape(ctx.x_shape)
             if need_w:
                 gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g_full, x2, a_mn=True, b_mn=True, out=out,
                                                                        add=add))
@@ -414,14 +428,18 @@ class _Row(torch.autograd.Function):
             if not fused_all_gather():
                 g_full = _nccl_gather_rows(g2)
                 if need_x:
-                    gx = G.gemm(g_full, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
+                    gx = dgrad(g_full).reshape(ctx.x_shape)
                 if need_w:
                     gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g_full, x2, a_mn=True, b_mn=True, out=out,
                                                                            add=add))
             elif need_x or need_w:
                 h = ws.begin_gather(g2)
                 if need_x:
-                    gx = ws.gemm(h.full, weight, False, True, gather=h, bcast=True, dep="a").reshape(ctx.x_shape)
+                    gx = ws.gemm(h.full, weight, False, True, gather=h, bcast=True, dep="a")
+                    if aux2 is not None:
+                        from ..ops.functional import dgelu_mul
+                        gx = dgelu_mul(gx, aux2)
+                    gx = gx.reshape(ctx.x_shape)
                 if need_w:
                     gw = _accumulate_wgrad(weight, lambda out, add: ws.gemm(h.full, x2, True, True, out=out, add=add,
                                                                             gather=h, bcast=not need_x, dep="a"))
@@ -434,14 +452,14 @@ class _Row(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             # post-reduction bias under SP: partial over this rank's shard, summed with the other replicated grads
             gb = (g_full if (ctx.bias_partial or not ctx.sp) else g2).sum(0)
-        return gx, gw, gb, (g if ctx.has_res else None), g_add, None, None
+        return gx, gw, gb, (g if ctx.has_res else None), g_add, None, None, None
 
 
 class _ColumnAR(torch.autograd.Function):
     """Column-parallel linear without sequence parallelism: forward is local, the data gradient is all-reduced."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, act):
+    def forward(ctx, x, weight, bias, act, split_pre=False):
         N, K = weight.shape
         x2 = x.reshape(-1, K)
         if not x2.is_contiguous():
@@ -449,19 +467,25 @@ class _ColumnAR(torch.autograd.Function):
         need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
         r = G.gemm(x2, weight, bias=bias, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE, want_preact=need_pre)
         out, pre = r if need_pre else (r, None)
-        ctx.act, ctx.x_shape, ctx.has_bias = act, x.shape, bias is not None
-        ctx.save_for_backward(x2, weight, pre)
-        return out.reshape(*x.shape[:-1], N)
+        ctx.act, ctx.x_shape, ctx.has_bias, ctx.split_pre = act, x.shape, bias is not None, split_pre
+        ctx.save_for_backward(x2, weight, None if split_pre else pre)
+        out = out.reshape(*x.shape[:-1], N)
+        if split_pre:
+            if pre is not None:
+                pre = pre.reshape(out.shape)
+                ctx.mark_non_differentiable(pre)
+            return out, pre
+        return out
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, g, g_pre=None):
         ws = workspace()
         x2, weight, pre = ctx.saved_tensors
         N, K = weight.shape
         g2 = g.reshape(-1, N)
         if not g2.is_contiguous():
             g2 = g2.contiguous()
-        if ctx.act == "gelu":
+        if ctx.act == "gelu" and not ctx.split_pre:
             from ..ops.functional import dgelu_mul
             g2 = dgelu_mul(g2, pre)
         gx = gw = gb = None
@@ -471,12 +495,12 @@ class _ColumnAR(torch.autograd.Function):
             gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g2, x2, a_mn=True, b_mn=True, out=out, add=add))
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
-        return gx, gw, gb, None
+        return gx, gw, gb, None, None
 
 
-def column_linear(x, weight, bias, act, sequence_parallel):
-    return (_ColumnSP if sequence_parallel else _ColumnAR).apply(x, weight, bias, act)
+def column_linear(x, weight, bias, act, sequence_parallel, split_pre=False):
+    return (_ColumnSP if sequence_parallel else _ColumnAR).apply(x, weight, bias, act, split_pre)
 
 
-def row_linear(x, weight, bias, residual, sequence_parallel, partial_add=None, bias_partial=False):
-    return _Row.apply(x, weight, bias, residual, partial_add, bool(sequence_parallel), bool(bias_partial))
+def row_linear(x, weight, bias, residual, sequence_parallel, partial_add=None, bias_partial=False, dgelu_aux=None):
+    return _Row.apply(x, weight, bias, residual, partial_add, bool(sequence_parallel), bool(bias_partial), dgelu_aux)

@@ -177,9 +177,11 @@ class ColumnParallelLinear(nn.Module):
     def width_mult(self):
         return self.width_mult_val
 
-    def matmul(self, input_, bias, act=None):
+    def matmul(self, input_, bias, act=None, split_pre=False):
         """Region mapping + GEMM: ``act(gather_or_copy(input_) W^T + bias)``.  Uses the kernel that overlaps the
-        collective with the GEMM when the shapes allow it, the NCCL mapping otherwise."""
+        collective with the GEMM when the shapes allow it, the NCCL mapping otherwise.  ``split_pre``: return
+        ``(out, pre_activation)`` and take the gradient w.r.t. the pre-activation in backward (the consumer applies
+        GeLU' in its own dgrad GEMM, see ``ops.linear._LinearFn``)."""
         K = input_.shape[-1]
         if self.tp > 1 and self.tp == mpu.get_model_parallel_world_size() and not mpu.get_fp32_allreduce():
             tokens = input_.numel() // K
@@ -189,14 +191,15 @@ class ColumnParallelLinear(nn.Module):
             if ok and (bias is None or bias.dtype == torch.bfloat16) and \
                     fused_comm.eligible(input_, self.weight, self.tp, rows):
                 if self.sequence_parallel and self.seq_dim != 0:
+                    assert not split_pre
                     out = fused_comm.column_linear(input_[0], self.weight, bias, act, True)
                     return out.unsqueeze(0)
-                return fused_comm.column_linear(input_, self.weight, bias, act, self.sequence_parallel)
+                return fused_comm.column_linear(input_, self.weight, bias, act, self.sequence_parallel, split_pre)
         if self.sequence_parallel:
             x = M.gather_from_sequence_parallel_region(input_, self.seq_dim)
         else:
             x = M.copy_to_model_parallel_region(input_)
-        return fused_linear(x, self.weight, bias, act=act)
+        return fused_linear(x, self.weight, bias, act=act, split_pre=split_pre)
 
     def forward(self, input_, act=None):
         if self.use_mup and self.mup_rescale_parameters:
@@ -251,17 +254,19 @@ class RowParallelLinear(nn.Module):
         return tokens % self.tp == 0 and fused_comm.eligible(x, self.weight, self.tp, tokens // self.tp) and \
             (self.bias is None or self.bias.dtype == torch.bfloat16)
 
-    def forward(self, input_, residual=None):
+    def forward(self, input_, residual=None, dgelu_aux=None):
         """``residual`` (optional) is added to the layer's output: after the cross-rank reduction when this layer
-        performs it, to this rank's partial product when the caller defers it (``parallel_output``)."""
+        performs it, to this rank's partial product when the caller defers it (``parallel_output``).
+        ``dgelu_aux``: pre-activation of the layer that produced ``input_`` through a GeLU (see ``matmul``)."""
         x = input_ if self.input_is_parallel else M.scatter_to_model_parallel_region(input_)
         bias = None if self.skip_bias_add else self.bias
         if not self.parallel_output and self._fusable(x):
             # GEMM -> reduce-scatter / all-reduce in one pass; bias and residual are added after the reduction
-            out = fused_comm.row_linear(x, self.weight, bias, residual, self.sequence_parallel)
+            out = fused_comm.row_linear(x, self.weight, bias, residual, self.sequence_parallel, dgelu_aux=dgelu_aux)
             return out, (self.bias if self.skip_bias_add else None)
         local = self.tp == 1 or self.parallel_output
-        out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None)
+        out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None,
+                           dgelu_aux=dgelu_aux)
         if not local:
             if self.sequence_parallel:
                 out = M.reduce_scatter_to_sequence_parallel_region(out)
@@ -273,7 +278,7 @@ class RowParallelLinear(nn.Module):
                 out = out + residual
         return out, (self.bias if self.skip_bias_add else None)
 
-    def forward_reduced(self, input_, partial_add, post_residual):
+    def forward_reduced(self, input_, partial_add, post_residual, dgelu_aux=None):
         """``reduce_over_tp(input_ W^T + bias + partial_add) + post_residual`` regardless of ``parallel_output``:
         the GPT-J style residual, where attention and MLP partial sums share one reduction.  Every rank's bias is
         added to its own partial product (they are distinct parameters, as in the reference's
@@ -281,8 +286,8 @@ class RowParallelLinear(nn.Module):
         x = input_ if self.input_is_parallel else M.scatter_to_model_parallel_region(input_)
         if self._fusable(x):
             return fused_comm.row_linear(x, self.weight, self.bias, post_residual, self.sequence_parallel,
-                                         partial_add=partial_add, bias_partial=True)
-        out = fused_linear(x, self.weight, self.bias, residual=partial_add)
+                                         partial_add=partial_add, bias_partial=True, dgelu_aux=dgelu_aux)
+        out = fused_linear(x, self.weight, self.bias, residual=partial_add, dgelu_aux=dgelu_aux)
         if self.tp > 1:
             if self.sequence_parallel:
                 out = M.reduce_scatter_to_sequence_parallel_region(out)

@@ -255,6 +255,33 @@ def test_flash_attention_fwd_bwd(sq, sk, b, hq, hkv, d, causal, window, alibi, f
         _close(got.grad, want.grad, 0.02 + 0.02 * want.grad.abs().max().item(), rtol=3e-2)
 
 
+@pytest.mark.parametrize("s,b,h,d,rot", [(256, 2, 4, 96, 24), (300, 1, 2, 64, 64), (512, 1, 2, 128, 0)])
+def test_packed_qkv_attention_with_inplace_rotary(s, b, h, d, rot):
+    """rotary + attention on the packed projection, in place, against fp32 rotary + fp32 attention."""
+    from gpt_neox_b200.models.positional import RotaryEmbedding
+    from gpt_neox_b200.ops import attention as A
+    from gpt_neox_b200.ops import functional as OF
+    torch.manual_seed(0)
+    mixed = torch.randn(s, b, h, 3 * d, device=DEV, dtype=torch.bfloat16)
+    leaf = mixed.clone().requires_grad_(True)
+    cos = sin = None
+    if rot:
+        cos, sin = RotaryEmbedding(rot, s, precision=torch.bfloat16).to(DEV)(mixed, seq_len=s)
+    work = leaf * 1.0                                   # non-leaf copy: the op overwrites its input
+    out = A.packed_qkv_attention(work, cos, sin)
+    g = torch.randn_like(out)
+    out.backward(g)
+    assert native.read_status() == 0
+    ref_leaf = mixed.detach().float().requires_grad_(True)
+    q, k, v = ref_leaf[..., :d], ref_leaf[..., d:2 * d], ref_leaf[..., 2 * d:]
+    if rot:
+        q, k = OF.rope_ref(q, cos, sin), OF.rope_ref(k, cos, sin)
+    ref = A.attention_ref(q, k, v, True, None, None, None)
+    ref.backward(g.float())
+    _close(out, ref, 3e-2)
+    _close(leaf.grad, ref_leaf.grad, 0.02 + 0.02 * ref_leaf.grad.abs().max().item(), rtol=3e-2)
+
+
 def test_flash_attention_is_deterministic():
     from gpt_neox_b200.ops import attention as A
     torch.manual_seed(0)
@@ -270,3 +297,33 @@ def test_flash_attention_is_deterministic():
     assert torch.equal(outs[0], outs[1])
     for a, b_ in zip(grads[0], grads[1]):
         assert torch.equal(a, b_)      # no atomics anywhere: bitwise repeatable
+
+
+@pytest.mark.parametrize("b,l,d", [(2, 70, 192), (1, 256, 100)])
+def test_selective_scan_fwd_bwd(b, l, d):
+    """Mamba S6 scan kernel (state in registers, 32-step checkpoints) against the step-by-step fp32 recurrence."""
+    from gpt_neox_b200.ops import selective_scan as SS
+    torch.manual_seed(0)
+    n = 16
+    mk = lambda *s, scale=1.0: (torch.randn(*s, device=DEV) * scale)
+    u = mk(b, l, d).to(torch.bfloat16).requires_grad_(True)
+    dt = mk(b, l, d, scale=0.5).to(torch.bfloat16).requires_grad_(True)
+    z = mk(b, l, d).to(torch.bfloat16).requires_grad_(True)
+    A = (-torch.rand(d, n, device=DEV) * 2 - 0.1).requires_grad_(True)
+    B = mk(b, l, n, scale=0.5).requires_grad_(True)
+    C = mk(b, l, n, scale=0.5).requires_grad_(True)
+    D = mk(d).requires_grad_(True)
+    bias = mk(d, scale=0.3).requires_grad_(True)
+    leaves = [u, dt, A, B, C, D, z, bias]
+    assert SS.have_scan_kernel()
+    out = SS.selective_scan(u, dt, A, B, C, D, z, bias)
+    g = torch.randn_like(out)
+    out.backward(g)
+    got = [t.grad.clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    ref = SS.selective_scan_ref(u.float(), dt.float(), A, B, C, D, z.float(), bias, True)
+    ref.backward(g.float())
+    _close(out, ref, 3e-2)
+    for have, t in zip(got, leaves):
+        _close(have, t.grad, 0.03 + 0.03 * t.grad.abs().max().item(), rtol=5e-2)
