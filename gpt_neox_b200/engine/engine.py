@@ -90,6 +90,9 @@ class NeoXEngine:
         """Back-propagate ``loss`` (scaled for fp16).  Gradients accumulate into fp32 ``main_grad``
         buffers; division by the number of micro-batches happens once, inside the optimizer step."""
         scaled = self.optimizer.scale_loss(loss) if self.optimizer is not None else loss
+        if self.optimizer is not None and self.is_gradient_accumulation_boundary() and \
+                hasattr(self.optimizer, "arm_overlap"):
+            self.optimizer.arm_overlap()     # last micro-batch: reduce each bucket as soon as its gradients exist
         scaled.backward(retain_graph=retain_graph)
         return loss
 
@@ -340,7 +343,12 @@ class PipelineEngine(NeoXEngine):
                     losses.append(loss.detach())
             return out, loss
 
+        bwd_count = [0]
+
         def bwd(out, loss, grads):
+            bwd_count[0] += 1
+            if bwd_count[0] == M and self.optimizer is not None and hasattr(self.optimizer, "arm_overlap"):
+                self.optimizer.arm_overlap()     # last micro-batch of the step on this stage
             if last:
                 self.backward(loss)
             else:

@@ -82,6 +82,11 @@ class Bucket:
             self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi])   # a view: updated in place
         self.master.model_out = self.flat_param[self.lo:self.hi] if self.mixed else None
         self.grad_shard = self.flat_grad[self.lo:self.hi] if grad_dtype == torch.float32 else None
+        # overlap bookkeeping (see FlatMixedPrecisionOptimizer.arm_overlap)
+        self.n_expected = len(self.params)
+        self.ready = 0
+        self.pending_reduce = None
+        self.pending_gather = None
 
     # ---- gradients
     def reduce_grads(self, average_factor):
@@ -93,6 +98,58 @@ class Bucket:
                 dist.reduce_scatter_tensor(self.flat_grad[self.lo:self.hi], self.flat_grad, group=self.comm_group)
             else:
                 dist.all_reduce(self.flat_grad, group=self.comm_group)
+
+    def reduce_grads_async(self, stream):
+        """Start the gradient reduction of this bucket on ``stream`` (ordered after everything launched so far on the
+        current stream); ``finish_reduce`` makes the current stream wait for it."""
+        if self.world <= 1 or self.pending_reduce is not None:
+            return
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(stream)
+        else:
+            from contextlib import nullcontext
+            ctx = nullcontext()
+        with ctx:
+            if self.sharded:
+                dst = self.flat_grad[self.lo:self.hi]
+                if not dst.is_cuda:
+                    self._rs_tmp = torch.empty_like(dst)
+                    dst = self._rs_tmp
+                self.pending_reduce = dist.reduce_scatter_tensor(dst, self.flat_grad, group=self.comm_group,
+                                                                 async_op=True)
+            else:
+                self.pending_reduce = dist.all_reduce(self.flat_grad, group=self.comm_group, async_op=True)
+
+    def finish_reduce(self):
+        """Wait for an early reduction, or do it now if none was started.  Returns True if it had been overlapped."""
+        if self.pending_reduce is None:
+            self.reduce_grads(1.0)
+            return False
+        self.pending_reduce.wait()
+        self.pending_reduce = None
+        tmp = getattr(self, "_rs_tmp", None)
+        if tmp is not None:
+            self.flat_grad[self.lo:self.hi].copy_(tmp)
+            self._rs_tmp = None
+        return True
+
+    def gather_params_async(self, stream):
+        """Start the all-gather of the updated parameter shards; ``wait_params`` is called before their first use."""
+        if not self.sharded:
+            return
+        if stream is None or not self.flat_param.is_cuda:
+            self.gather_params()
+            return
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self.pending_gather = dist.all_gather_into_tensor(self.flat_param, self.flat_param[self.lo:self.hi],
+                                                              group=self.comm_group, async_op=True)
+
+    def wait_params(self):
+        if self.pending_gather is not None:
+            self.pending_gather.wait()
+            self.pending_gather = None
 
     def shard_sq_norm(self, tp_rank):
         """Squared L2 norm of this rank's gradient shard, counting TP-replicated entries on TP rank 0 only.
@@ -136,8 +193,19 @@ class FlatMixedPrecisionOptimizer:
     bucket whose ``.grad`` is the reduced gradient shard."""
 
     def __init__(self, param_groups, inner_cls, inner_defaults, model_dtype, zero_stage=0, clip_grad=0.0,
-                 fp16_cfg=None, gradient_predivide_factor=1.0, prescale_gradients=False, device=None):
+                 fp16_cfg=None, gradient_predivide_factor=1.0, prescale_gradients=False, device=None,
+                 overlap_comm=False, reduce_bucket_size=None):
+        """``overlap_comm``: split every parameter group into buckets of at most ``reduce_bucket_size`` elements (in
+        model order), start each bucket's data-parallel gradient reduction on a side stream as soon as the LAST
+        micro-batch's backward has produced all of its gradients, and all-gather the updated parameter shards
+        asynchronously, each layer waiting for its own bucket in a forward pre-hook
+        (``zero_optimization.overlap_comm`` / ``reduce_bucket_size`` of the DeepSpeed ZeRO-1/2 config the reference
+        passes through)."""
         self.zero_stage = int(zero_stage or 0)
+        self.overlap_comm = bool(overlap_comm)
+        self._armed = False
+        self._comm_stream = None
+        self.overlapped_reductions = 0
         self.clip_grad = float(clip_grad or 0.0)
         self.model_dtype = model_dtype
         self.overflow = False
@@ -161,9 +229,21 @@ class FlatMixedPrecisionOptimizer:
                 if not plist:
                     continue
                 dev = device or plist[0].device
-                b = Bucket(plist, opts, cg, cw, cr, model_dtype, dev, sharded=self.zero_stage >= 1)
-                self.buckets.append(b)
-                inner_groups.append({"params": [b.master], **opts})
+                chunks = [plist]
+                if self.overlap_comm and cw > 1 and reduce_bucket_size:
+                    chunks, cur, n = [], [], 0
+                    for p in plist:
+                        if cur and n + p.numel() > reduce_bucket_size:
+                            chunks.append(cur)
+                            cur, n = [], 0
+                        cur.append(p)
+                        n += p.numel()
+                    if cur:
+                        chunks.append(cur)
+                for chunk in chunks:
+                    b = Bucket(chunk, opts, cg, cw, cr, model_dtype, dev, sharded=self.zero_stage >= 1)
+                    self.buckets.append(b)
+                    inner_groups.append({"params": [b.master], **opts})
         self.optimizer = inner_cls(inner_groups, **inner_defaults)
         self.param_groups = self.optimizer.param_groups
         self.dp_world = dp_world
@@ -183,16 +263,59 @@ class FlatMixedPrecisionOptimizer:
     # ------------------------------------------------------------------ hooks
     def _install_grad_hooks(self):
         """Fold autograd-produced ``.grad`` tensors (biases, norms, embeddings ...) into ``main_grad``."""
-        def make(p):
+        def make(p, bucket):
             def hook(param):
                 if param.grad is not None:
                     param.main_grad.add_(param.grad.to(param.main_grad.dtype))
                     param.grad = None
+                    self._on_grad_ready(bucket)
             return hook
         self._hooks = []
         for b in self.buckets:
             for p in b.params:
-                self._hooks.append(p.register_post_accumulate_grad_hook(make(p)))
+                p._bucket = b
+                # kernels that accumulate straight into main_grad report here (ops.linear.notify_grad_ready)
+                p._grad_ready = (lambda bucket=b: self._on_grad_ready(bucket))
+                self._hooks.append(p.register_post_accumulate_grad_hook(make(p, b)))
+
+    # ------------------------------------------------------------------ communication overlap
+    def _stream(self):
+        if self._comm_stream is None and torch.cuda.is_available():
+            self._comm_stream = torch.cuda.Stream()
+        return self._comm_stream
+
+    def arm_overlap(self):
+        """Call right before the backward pass of the last micro-batch of a step: from now on a bucket whose
+        parameters have all reported their gradient is reduced immediately, concurrently with the rest of backward."""
+        if not self.overlap_comm:
+            return
+        self._armed = True
+        for b in self.buckets:
+            b.ready = 0
+
+    def _on_grad_ready(self, bucket):
+        if not self._armed or bucket.world <= 1:
+            return
+        bucket.ready += 1
+        if bucket.ready == bucket.n_expected:
+            bucket.reduce_grads_async(self._stream())
+
+    def install_param_wait_hooks(self, module):
+        """Forward pre-hooks on the direct children of ``module`` (the layers): a layer waits for the all-gather of
+        exactly the buckets that hold its parameters, so the gather of later layers overlaps earlier layers' forward."""
+        if not self.overlap_comm:
+            return
+        for child in module.children():
+            if isinstance(child, (torch.nn.ModuleDict, torch.nn.ModuleList, torch.nn.Sequential)):
+                self.install_param_wait_hooks(child)
+                continue
+            buckets = []
+            for p in child.parameters():
+                b = getattr(p, "_bucket", None)
+                if b is not None and b.sharded and all(b is not x for x in buckets):
+                    buckets.append(b)
+            if buckets:
+                child.register_forward_pre_hook(lambda m, a, bs=tuple(buckets): [b.wait_params() for b in bs] and None)
 
     # ------------------------------------------------------------------ properties the training loop reads
     @property
@@ -237,8 +360,9 @@ class FlatMixedPrecisionOptimizer:
     def step(self, grad_divisor=1.0):
         """Reduce, check, clip, update, gather.  ``grad_divisor``: value the summed gradients must be
         divided by in total (micro-batches x data-parallel size)."""
+        self._armed = False
         for b in self.buckets:
-            b.reduce_grads(1.0)
+            self.overlapped_reductions += int(b.finish_reduce())
         norm_t = self.global_grad_norm()
         scale = self.loss_scaler.cur_scale * grad_divisor
         norm = float(norm_t) / scale
@@ -250,6 +374,8 @@ class FlatMixedPrecisionOptimizer:
             self.skipped_steps += 1
             self.zero_grad()
             return False
+        for b in self.buckets:
+            b.wait_params()          # a gather still in flight (no forward ran since the last step)
         combined = scale
         if self.clip_grad > 0.0:
             clip = norm / self.clip_grad
@@ -270,7 +396,10 @@ class FlatMixedPrecisionOptimizer:
             if b.mixed and not getattr(self.optimizer, "writes_model_out", False):
                 b.flat_param[b.lo:b.hi].copy_(b.master.data)
             b.master.grad = None
-            b.gather_params()
+            if self.overlap_comm:
+                b.gather_params_async(self._stream())
+            else:
+                b.gather_params()
         self.zero_grad()
         return True
 

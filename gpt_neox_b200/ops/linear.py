@@ -20,6 +20,13 @@ from . import gemm as G
 from . import native
 
 
+def notify_grad_ready(weight):
+    """Tell the optimizer (if it listens) that ``weight.main_grad`` now holds this backward pass' contribution."""
+    cb = getattr(weight, "_grad_ready", None)
+    if cb is not None:
+        cb()
+
+
 def kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.is_cuda and native.available() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous())
@@ -93,6 +100,7 @@ class _LinearFn(torch.autograd.Function):
                 if mg is not None:
                     G.gemm(g2, x2, a_mn=True, b_mn=True, out=mg, add=mg)
                     weight.grad_in_main = True
+                    notify_grad_ready(weight)
                 else:
                     gw = G.gemm(g2, x2, a_mn=True, b_mn=True)
         else:
@@ -108,6 +116,7 @@ class _LinearFn(torch.autograd.Function):
                     mg.add_(gw)
                     weight.grad_in_main = True
                     gw = None
+                    notify_grad_ready(weight)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
         return gx, gw, gb, g_res, None, None, None

@@ -300,6 +300,8 @@ def _accumulate_wgrad(weight, fn):
     if mg is not None:
         fn(mg, mg)
         weight.grad_in_main = True
+        from ..ops.linear import notify_grad_ready
+        notify_grad_ready(weight)
         return None
     return fn(None, None)
 

@@ -25,6 +25,7 @@ import torch.nn.functional as F
 from torch.nn import init
 from torch.nn.parameter import Parameter
 
+from ..ops import embedding as fused_embedding
 from ..ops.linear import linear as fused_linear
 from . import fused_comm
 from . import mappings as M
@@ -89,6 +90,10 @@ class VocabParallelEmbedding(nn.Module):
         init_sharded_weight(neox_args, self.weight, num_embeddings, embedding_dim, 0, init_method)
 
     def forward(self, input_):
+        if fused_embedding.kernel_ok(input_, self.weight):
+            # gather kernel: rows of ids owned by another rank come out as zeros; backward scatter-adds in fp32
+            out = fused_embedding.embedding(input_, self.weight, self.vocab_start_index)
+            return M.reduce_from_model_parallel_region(out)
         if self.model_parallel_size > 1:
             mask = (input_ < self.vocab_start_index) | (input_ >= self.vocab_end_index)
             local = (input_ - self.vocab_start_index).masked_fill(mask, 0)

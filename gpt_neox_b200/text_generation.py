@@ -57,7 +57,18 @@ def pad_batch(context_tokens: List[List[int]], pad_id: int, pad_len: int, trunca
 
 def filter_logits(logits, top_k=0, top_p=0.0, filter_value=-float("Inf")):
     """Top-k then nucleus filtering, all rows at once (the reference loops over the batch in Python,
-    ``text_generation_utils.py:120-122``)."""
+    ``text_generation_utils.py:120-122``).  On the GPU one kernel does both filters without sorting."""
+    if logits.is_cuda and logits.dim() == 2 and filter_value == -float("Inf") and (top_k > 0 or 0.0 < top_p < 1.0) \
+            and logits.shape[-1] * 4 <= 224 * 1024:
+        import ctypes
+        from .ops import native
+        if native.available() and native.lib().has("neox_sample_filter"):
+            x = logits.float().contiguous()
+            out = torch.empty_like(x)
+            rc = native.lib().neox_sample_filter(native.ptr(x), native.ptr(out), x.shape[0], x.shape[1], int(top_k),
+                                                 ctypes.c_float(top_p), ctypes.c_void_p(native.stream_ptr()))
+            native.check(rc, "neox_sample_filter")
+            return out.to(logits.dtype)
     if top_k > 0:
         kth = torch.topk(logits, top_k)[0][..., -1, None]
         logits = logits.masked_fill(logits < kth, filter_value)

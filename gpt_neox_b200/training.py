@@ -348,7 +348,12 @@ def get_optimizer(model, neox_args, dummy=False):
     fp16_cfg = dict(neox_args.fp16 or {})
     optimizer = FlatMixedPrecisionOptimizer(groups, inner_cls, inner_kw, neox_args.params_dtype,
                                             zero_stage=neox_args.zero_stage if isinstance(neox_args.zero_stage, int) else 0,
-                                            clip_grad=neox_args.gradient_clipping, fp16_cfg=fp16_cfg)
+                                            clip_grad=neox_args.gradient_clipping, fp16_cfg=fp16_cfg,
+                                            overlap_comm=bool((neox_args.zero_optimization or {}).get("overlap_comm", False)),
+                                            reduce_bucket_size=neox_args.zero_reduce_bucket_size)
+    if getattr(optimizer, "overlap_comm", False):
+        # each layer waits only for the all-gather of its own parameters
+        optimizer.install_param_wait_hooks(model)
     return optimizer, groups
 
 

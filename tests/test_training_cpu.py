@@ -78,6 +78,28 @@ def test_zero1_matches_zero0(tmp_path):
     assert all(abs(x - y) < 1e-4 for x, y in zip(l0, l1)), (l0, l1)
 
 
+def _overlap_losses(rank, world, cfg, out):
+    args, model, opt, sched = _setup({**cfg, "global_num_gpus": world})
+    losses = _train(args, model, opt, sched, 8)
+    if rank == 0:
+        with open(out, "w") as fh:
+            json.dump({"losses": losses, "overlapped": getattr(opt, "overlapped_reductions", 0),
+                       "buckets": len(getattr(opt, "buckets", []))}, fh)
+
+
+def test_zero1_overlapped_reduction_matches_plain(tmp_path):
+    """Bucketed gradient reduce-scatter started from backward hooks + asynchronous parameter all-gather give the
+    same losses as the reduce-at-step form, and the early path is really taken."""
+    a, b = str(tmp_path / "plain.json"), str(tmp_path / "overlap.json")
+    base = {"gradient_accumulation_steps": 2}
+    run_distributed(_overlap_losses, 2, {**base, "zero_optimization": {"stage": 1}}, a)
+    run_distributed(_overlap_losses, 2, {**base, "zero_optimization": {"stage": 1, "overlap_comm": True,
+                                                                       "reduce_bucket_size": 20000}}, b)
+    ra, rb = json.load(open(a)), json.load(open(b))
+    assert all(abs(x - y) < 1e-4 for x, y in zip(ra["losses"], rb["losses"])), (ra, rb)
+    assert rb["buckets"] > ra["buckets"] and rb["overlapped"] > 0, rb
+
+
 def test_tensor_and_data_parallel_training():
     run_distributed(_loss_decreases, 4, {"model_parallel_size": 2, "sequence_parallel": True,
                                          "zero_optimization": {"stage": 1}}, None)

@@ -1,0 +1,67 @@
+"""2-GPU data-parallel ZeRO-1 training with and without overlapped communication (launched by torchrun).
+
+Trains the same tiny bf16 model twice from the same seed -- gradient reduce-scatter at the optimizer step vs.
+bucketed reduce-scatter started from backward hooks on a side stream plus asynchronous parameter all-gather --
+and checks that the losses agree and that buckets were really reduced early.  Prints ``DP_OVERLAP_OK`` on rank 0.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+sys.path.insert(0, os.path.dirname(HERE))
+
+
+def run(overlap):
+    from common import make_args
+    from gpt_neox_b200.parallel import mpu
+    from gpt_neox_b200.training import setup_model_and_optimizer, train_step
+    from gpt_neox_b200.utils import Timers
+    world = int(os.environ["WORLD_SIZE"])
+    zero = {"stage": 1, "overlap_comm": True, "reduce_bucket_size": 300000} if overlap else {"stage": 1}
+    args = make_args(hidden_size=256, num_attention_heads=4, num_layers=4, seq_length=128, max_position_embeddings=128,
+                     precision="bfloat16", global_num_gpus=world, distributed_backend="nccl", zero_optimization=zero,
+                     train_micro_batch_size_per_gpu=4, gradient_accumulation_steps=2,
+                     attention_config=[[["flash"], "all"]])
+    from gpt_neox_b200.initialize import initialize_megatron
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    torch.manual_seed(1234)
+    model, opt, sched, _ = setup_model_and_optimizer(args)
+    g = torch.Generator().manual_seed(7 + mpu.get_data_parallel_rank())
+    batches = [{"text": torch.randint(0, args.padded_vocab_size, (4, 129), generator=g)} for _ in range(4)]
+
+    def it():
+        i = 0
+        while True:
+            yield batches[i % 4]
+            i += 1
+    data = it()
+    losses = []
+    for _ in range(6):
+        d, _ = train_step(args, Timers(), data, model, opt, sched)
+        losses.append(float(d["lm_loss"]))
+    return losses, getattr(opt, "overlapped_reductions", 0), len(opt.buckets)
+
+
+def main():
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    plain, _, nb0 = run(False)
+    over, early, nb1 = run(True)
+    ok = all(abs(a - b) < 2e-2 for a, b in zip(plain, over)) and early > 0 and nb1 > nb0
+    if not ok:
+        print(f"[rank {dist.get_rank()}] plain {plain} overlap {over} early {early} buckets {nb0}->{nb1}", flush=True)
+    flag = torch.tensor([int(ok)], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if dist.get_rank() == 0 and flag.item() == 1:
+        print("DP_OVERLAP_OK", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
