@@ -27,6 +27,7 @@ from torch.nn.parameter import Parameter
 
 from ..ops import embedding as fused_embedding
 from ..ops.linear import linear as fused_linear
+from ..ops.mxfp8 import mx_linear
 from . import fused_comm
 from . import mappings as M
 from . import mpu
@@ -166,6 +167,10 @@ class ColumnParallelLinear(nn.Module):
         self.mup_rescale_parameters = mup_rescale_parameters
         self.use_mup = getattr(neox_args, "use_mup", False)
         self.width_mult_val = 1.0
+        # block-scaled fp8 GEMMs (the switch the reference uses to swap in Transformer Engine layers)
+        self.fp8 = bool(getattr(neox_args, "te_columnparallel", False))
+        self.fp8_hybrid = getattr(neox_args, "te_fp8_format", "hybrid") == "hybrid"
+        self.fp8_wgrad = bool(getattr(neox_args, "te_fp8_wgrad", True))
         dev = _device(neox_args)
         self.weight = Parameter(torch.empty(self.output_size_per_partition, input_size, device=dev,
                                             dtype=neox_args.params_dtype))
@@ -188,6 +193,13 @@ class ColumnParallelLinear(nn.Module):
         ``(out, pre_activation)`` and take the gradient w.r.t. the pre-activation in backward (the consumer applies
         GeLU' in its own dgrad GEMM, see ``ops.linear._LinearFn``)."""
         K = input_.shape[-1]
+        if self.fp8:
+            x = M.gather_from_sequence_parallel_region(input_, self.seq_dim) if self.sequence_parallel else \
+                M.copy_to_model_parallel_region(input_)
+            out = mx_linear(x, self.weight, bias, self.fp8_hybrid, self.fp8_wgrad)
+            if act == "gelu":
+                out = F.gelu(out, approximate="tanh")
+            return (out, None) if split_pre else out
         if self.tp > 1 and self.tp == mpu.get_model_parallel_world_size() and not mpu.get_fp32_allreduce():
             tokens = input_.numel() // K
             rows = tokens if self.sequence_parallel else tokens // self.tp
@@ -237,6 +249,9 @@ class RowParallelLinear(nn.Module):
         self.init_method, self.stride = init_method, stride
         self.mup_rescale_parameters = mup_rescale_parameters
         self.use_mup = getattr(neox_args, "use_mup", False)
+        self.fp8 = bool(getattr(neox_args, "te_rowparallel", False))
+        self.fp8_hybrid = getattr(neox_args, "te_fp8_format", "hybrid") == "hybrid"
+        self.fp8_wgrad = bool(getattr(neox_args, "te_fp8_wgrad", True))
         dev = _device(neox_args)
         self.weight = Parameter(torch.empty(output_size, self.input_size_per_partition, device=dev,
                                             dtype=neox_args.params_dtype))
@@ -253,6 +268,8 @@ class RowParallelLinear(nn.Module):
         self.parallel_output = value
 
     def _fusable(self, x):
+        if self.fp8:
+            return False
         if self.tp == 1 or self.tp != mpu.get_model_parallel_world_size() or mpu.get_fp32_allreduce():
             return False
         tokens = x.numel() // x.shape[-1]
@@ -270,8 +287,13 @@ class RowParallelLinear(nn.Module):
             out = fused_comm.row_linear(x, self.weight, bias, residual, self.sequence_parallel, dgelu_aux=dgelu_aux)
             return out, (self.bias if self.skip_bias_add else None)
         local = self.tp == 1 or self.parallel_output
-        out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None,
-                           dgelu_aux=dgelu_aux)
+        if self.fp8:
+            out = mx_linear(x, self.weight, bias if local else None, self.fp8_hybrid, self.fp8_wgrad)
+            if local and residual is not None:
+                out = out + residual
+        else:
+            out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None,
+                               dgelu_aux=dgelu_aux)
         if not local:
             if self.sequence_parallel:
                 out = M.reduce_scatter_to_sequence_parallel_region(out)
@@ -292,7 +314,12 @@ class RowParallelLinear(nn.Module):
         if self._fusable(x):
             return fused_comm.row_linear(x, self.weight, self.bias, post_residual, self.sequence_parallel,
                                          partial_add=partial_add, bias_partial=True, dgelu_aux=dgelu_aux)
-        out = fused_linear(x, self.weight, self.bias, residual=partial_add, dgelu_aux=dgelu_aux)
+        if self.fp8:
+            out = mx_linear(x, self.weight, self.bias, self.fp8_hybrid, self.fp8_wgrad)
+            if partial_add is not None:
+                out = out + partial_add
+        else:
+            out = fused_linear(x, self.weight, self.bias, residual=partial_add, dgelu_aux=dgelu_aux)
         if self.tp > 1:
             if self.sequence_parallel:
                 out = M.reduce_scatter_to_sequence_parallel_region(out)

@@ -17,6 +17,8 @@ from test_training_cpu import _loss_decreases
     {"attention_config": [[["global", "bigbird"], 1]], "sparsity_config": {"block": 4}},
     {"attention_config": [[["local", "bslongformer"], 1]], "sparsity_config": {"block": 4}},
     {"sliding_window_width": 8},
+    # block-scaled fp8 linears (the Transformer-Engine switches of the 1-3B-transformer-engine config)
+    {"te_columnparallel": True, "te_rowparallel": True, "te_fp8_format": "hybrid", "precision": "bfloat16"},
 ])
 def test_family_trains(cfg):
     run_distributed(_loss_decreases, 1, cfg, None)

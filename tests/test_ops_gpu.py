@@ -367,3 +367,41 @@ def test_sampling_filter_matches_sort_based_filter(top_k, top_p):
     if top_p < 0.99:
         assert (kept_g != kept_w).sum(dim=-1).max().item() <= 1
     assert torch.equal(got[kept_g & kept_w], logits[kept_g & kept_w])
+
+
+@pytest.mark.parametrize("along_rows,e5m2", [(False, False), (True, False), (False, True), (True, True)])
+def test_mxfp8_quantise_round_trip_matches_torch_float8(along_rows, e5m2):
+    from gpt_neox_b200.ops import mxfp8 as MX
+    torch.manual_seed(0)
+    x = (torch.randn(200, 176, device=DEV) * torch.logspace(-3, 2, 176, device=DEV)).to(torch.bfloat16)
+    x[3, :40] = 0
+    got = MX.qdq(x, along_rows, e5m2)
+    want = MX.qdq_ref(x, along_rows, e5m2)
+    assert torch.equal(got, want)
+    q, s = MX.quantize(x, along_rows, e5m2)
+    assert torch.equal(MX.dequantize(q, s, along_rows, e5m2), got)
+    # error of every element is at most 1/8 of its block's maximum: half an ulp of the top binade, or the
+    # saturation of scaled values in (max_fp8, 2 * 2^emax) that the power-of-two scale allows
+    blk, _, _ = MX._blocks((got.float() - x.float()).abs(), along_rows)
+    ref_blk, _, _ = MX._blocks(x.float().abs(), along_rows)
+    assert bool((blk.amax(-1) <= ref_blk.amax(-1) * 0.125 + 1e-30).all())
+
+
+def test_mxfp8_linear_fwd_bwd_against_fp32_on_quantised_operands():
+    from gpt_neox_b200.ops import mxfp8 as MX
+    torch.manual_seed(0)
+    x = torch.randn(256, 192, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(320, 192, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(320, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = MX.mx_linear(x, w, b, hybrid=True, fp8_wgrad=True)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xq, wq = MX.qdq_ref(x.detach(), False), MX.qdq_ref(w.detach(), False)
+    _close(y, xq.float() @ wq.float().t() + b.float(), 2e-2, rtol=2e-2)
+    gq, wq2 = MX.qdq_ref(g, False, True), MX.qdq_ref(w.detach(), True)
+    _close(x.grad, gq.float() @ wq2.float(), 2e-2, rtol=2e-2)
+    gq2, xq2 = MX.qdq_ref(g, True, True), MX.qdq_ref(x.detach(), True)
+    _close(w.grad, gq2.float().t() @ xq2.float(), 5e-2, rtol=2e-2)
+    # and the block-scaled result stays close to the unquantised layer
+    ref = x.detach().float() @ w.detach().float().t() + b.detach().float()
+    assert ((y.float() - ref).abs().mean() / ref.abs().mean()).item() < 0.05
