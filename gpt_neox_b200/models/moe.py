@@ -31,7 +31,7 @@ import torch.nn.functional as F
 
 from ..ops import functional as OF
 from ..ops.linear import linear as fused_linear
-from ..parallel import mpu
+from ..parallel import moe_comm, mpu
 from ..parallel.rng import get_cuda_rng_tracker
 
 
@@ -165,12 +165,20 @@ class ParallelMoE(nn.Module):
         if self.ep > 1:
             grp = mpu.get_expert_parallel_group()
             send = counts.view(self.ep, self.local_experts)
-            recv = torch.empty_like(send)
-            dist.all_to_all_single(recv, send.contiguous(), group=grp)
-            in_splits = send.sum(1).tolist()
-            out_splits = recv.sum(1).tolist()
-            recv_l = recv.tolist()
-            xr = _AllToAll.apply(xs, out_splits, in_splits, grp)
+            # every rank learns the whole count table in one small all-gather: [src rank, dst rank, local expert]
+            table = torch.empty((self.ep, self.ep, self.local_experts), dtype=send.dtype, device=send.device)
+            dist.all_gather_into_tensor(table.view(-1), send.contiguous().view(-1), group=grp)
+            table_l = table.tolist()
+            me = mpu.get_expert_parallel_rank()
+            recv_l = [table_l[r][me] for r in range(self.ep)]
+            in_splits = [sum(table_l[me][d]) for d in range(self.ep)]
+            out_splits = [sum(recv_l[r]) for r in range(self.ep)]
+            peer = moe_comm.eligible(xs, grp)
+            if peer:
+                matrix = [[sum(table_l[r][d]) for d in range(self.ep)] for r in range(self.ep)]
+                xr = moe_comm.all_to_all_rows(xs, matrix, grp)
+            else:
+                xr = _AllToAll.apply(xs, out_splits, in_splits, grp)
             # received layout: for each source rank, its segments for local experts 0..L-1
             outs = torch.empty((xr.shape[0], shape[-1]), dtype=x.dtype, device=x.device)
             pieces, off = [[] for _ in range(self.local_experts)], 0
@@ -188,7 +196,10 @@ class ParallelMoE(nn.Module):
                     res_parts[o] = out_e[o2:o2 + n]
                     o2 += n
             outs = torch.cat([res_parts[o] for o in sorted(res_parts)]) if res_parts else xr
-            ys = _AllToAll.apply(outs, in_splits, out_splits, grp)
+            if peer:
+                ys = moe_comm.all_to_all_rows(outs, [list(c) for c in zip(*matrix)], grp)
+            else:
+                ys = _AllToAll.apply(outs, in_splits, out_splits, grp)
         else:
             cl = counts.tolist()
             parts, off = [], 0

@@ -964,3 +964,88 @@ extern "C" int neox_symm_release(void* cnt, int n, const unsigned long long* pad
                                                                       sig_offset, epoch);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
+
+// ------------------------------------------------------------------ variable-split all-to-all of rows (MoE)
+namespace {
+
+struct A2AParams {
+    const uint4* src;                 // local send rows, grouped by destination rank
+    uint4* dst[MAX_RANKS];            // every rank's receive buffer (peer-mapped)
+    long long send_off[MAX_RANKS];    // first local row for destination d
+    long long send_cnt[MAX_RANKS];    // rows for destination d
+    long long recv_off[MAX_RANKS];    // row offset of this rank's block inside destination d's buffer
+    int row_vec;                      // 16-byte vectors per row
+    int world, rank;
+    const uint32_t* free_flags;       // local pad: free_flags[d] >= free_epoch  <=>  d's buffer may be rewritten
+    uint32_t free_epoch;
+};
+
+// One warp per row: 32 lanes x 16 bytes = 512-byte contiguous segments, which travel as full NVLink packets.
+// Destinations are visited starting at rank + 1 so that at any time every rank receives from a different peer.
+__global__ void __launch_bounds__(256) a2a_push_kernel(A2AParams ap, PeerPads pads, int sig_offset, uint32_t epoch,
+                                                       unsigned* counter, int* status) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long gw = (long long)blockIdx.x * 8 + warp, GW = (long long)gridDim.x * 8;
+    bool ok = true;
+    for (int i = 0; i < ap.world && ok; ++i) {
+        const int d = (ap.rank + 1 + i) % ap.world;
+        if (ap.send_cnt[d] == 0) continue;
+        if (d != ap.rank) {
+            int okf = 1;
+            if (lane == 0) okf = wait_flag(ap.free_flags + d, ap.free_epoch) ? 1 : 0;
+            okf = __shfl_sync(0xffffffffu, okf, 0);
+            if (!okf) {
+                if (lane == 0) atomicExch(status, 540 + d);
+                ok = false;
+                break;
+            }
+        }
+        const uint4* s = ap.src + ap.send_off[d] * ap.row_vec;
+        uint4* o = ap.dst[d] + ap.recv_off[d] * ap.row_vec;
+        for (long long r = gw; r < ap.send_cnt[d]; r += GW)
+            for (int v = lane; v < ap.row_vec; v += 32) o[r * ap.row_vec + v] = __ldg(s + r * ap.row_vec + v);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) grid_done_signal(counter, pads.p, ap.world, ap.rank, sig_offset, epoch);
+}
+
+}  // namespace
+
+// Push this rank's rows to their destination ranks' receive buffers and signal "epoch" to everyone.
+// send_off / send_cnt / recv_off: world entries each (rows).  The receiver calls neox_gathered_copy with the matching
+// ready / done flag offsets to wait for all sources and move the rows into an ordinary tensor.
+extern "C" int neox_a2a_push(const void* src, const unsigned long long* dst_ptrs, const long long* send_off,
+                             const long long* send_cnt, const long long* recv_off, int row_bytes, int world, int rank,
+                             const void* free_flags, unsigned free_epoch, const unsigned long long* pad_ptrs,
+                             int sig_offset, unsigned epoch, void* counter, void* stream) {
+    if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
+    if ((row_bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15)) return NEOX_ERR_ALIGN;
+    int* status = neox_status_word();
+    if (!status) return NEOX_ERR_DRIVER;
+    A2AParams ap;
+    memset(&ap, 0, sizeof(ap));
+    PeerPads pads;
+    memset(&pads, 0, sizeof(pads));
+    long long total = 0;
+    for (int i = 0; i < world; ++i) {
+        ap.dst[i] = reinterpret_cast<uint4*>(dst_ptrs[i]);
+        ap.send_off[i] = send_off[i];
+        ap.send_cnt[i] = send_cnt[i];
+        ap.recv_off[i] = recv_off[i];
+        pads.p[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
+        total += send_cnt[i];
+    }
+    ap.src = static_cast<const uint4*>(src);
+    ap.row_vec = row_bytes / 16;
+    ap.world = world; ap.rank = rank;
+    ap.free_flags = static_cast<const uint32_t*>(free_flags);
+    ap.free_epoch = free_epoch;
+    long long grid = (total + 7) / 8;
+    const long long cap = (long long)neox_sm_count() * 4;
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    a2a_push_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ap, pads, sig_offset, epoch,
+                                                                                   static_cast<unsigned*>(counter),
+                                                                                   status);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}

@@ -42,3 +42,17 @@ def test_zero1_overlap_two_gpus():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     out = r.stdout + r.stderr
     assert r.returncode == 0 and "DP_OVERLAP_OK" in out, out[-4000:]
+
+
+@pytest.mark.gpu
+def test_moe_peer_all_to_all_two_gpus():
+    """Expert-parallel MoE on 2 GPUs: token exchange by peer-memory kernels == NCCL all-to-all (fwd and bwd)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(ROOT, "tests", "workers", "moe_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and "MOE_A2A_OK" in out, out[-4000:]
