@@ -30,6 +30,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
+from ..ops import gemm as G
 from ..ops.linear import linear as fused_linear
 from ..parallel import moe_comm, mpu
 from ..parallel.rng import get_cuda_rng_tracker
@@ -52,6 +53,59 @@ class _AllToAll(torch.autograd.Function):
         dist.all_to_all_single(out, g.contiguous(), output_split_sizes=ctx.in_splits,
                                input_split_sizes=ctx.out_splits, group=ctx.group)
         return out, None, None, None
+
+
+class _ExpertOutCombine(torch.autograd.Function):
+    """Output projection of all local experts fused with the return all-to-all.
+
+    forward: for expert e, ``hdn[a:b] @ w2[e]^T`` is computed by the tcgen05 GEMM whose epilogue stores row i at
+    ``dest[i]`` -- the slot of that token in the combine buffer of the rank it came from (peer memory).  A flag tells
+    every rank when this rank's rows are in place; the rows arriving here are then copied out.
+    backward: the gradient rows travel the opposite way (peer push), are put back into expert-major order and feed
+    the two gradient GEMMs of every expert (weight gradients accumulate into ``w2.main_grad`` when present).
+    """
+
+    @staticmethod
+    def forward(ctx, hdn, w2, bounds, perm_t, perm, src, block_start, back, matrix, grp):
+        import numpy as np
+        comm = moe_comm.comm_for(grp)
+        h = w2.shape[1]
+        row_bytes = h * 2
+        e, recv_off = comm.begin_push(back)
+        buf = comm.push_buffer(e, back, row_bytes)
+        base = np.asarray(buf.ptrs, dtype=np.int64)
+        roff = np.asarray(recv_off, dtype=np.int64)
+        dest = base[src] + (roff[src] + perm - np.asarray(block_start, dtype=np.int64)[src]) * row_bytes
+        dest_t = torch.from_numpy(dest).to(hdn.device, non_blocking=True)
+        for ei, (a, b) in enumerate(bounds):
+            if b > a:
+                G.gemm_rowmap(hdn[a:b], w2[ei], dest_t[a:b])
+        ys = comm.finish_push(e, buf, back, h, hdn.device)
+        ctx.save_for_backward(hdn, w2, perm_t)
+        ctx.bounds, ctx.matrix, ctx.grp = bounds, matrix, grp
+        return ys
+
+    @staticmethod
+    def backward(ctx, g):
+        hdn, w2, perm_t = ctx.saved_tensors
+        g_src = moe_comm.comm_for(ctx.grp).exchange(g.contiguous(), ctx.matrix)      # back on the expert rank
+        g_e = g_src.index_select(0, perm_t)
+        d_hdn = torch.empty_like(hdn)
+        mg = getattr(w2, "main_grad", None)
+        gw = None if mg is not None else torch.zeros_like(w2)
+        for ei, (a, b) in enumerate(ctx.bounds):
+            if b <= a:
+                continue
+            G.gemm(g_e[a:b], w2[ei], a_mn=False, b_mn=True, out=d_hdn[a:b])
+            if mg is not None:
+                G.gemm(g_e[a:b], hdn[a:b], a_mn=True, b_mn=True, out=mg[ei], add=mg[ei])
+            else:
+                G.gemm(g_e[a:b], hdn[a:b], a_mn=True, b_mn=True, out=gw[ei])
+        if mg is not None:
+            w2.grad_in_main = True
+            from ..ops.linear import notify_grad_ready
+            notify_grad_ready(w2)
+        return d_hdn, gw, None, None, None, None, None, None, None, None
 
 
 class Router(nn.Module):
@@ -132,6 +186,40 @@ class ParallelMoE(nn.Module):
             hdn = OF.get_activation(self.activation)(fused_linear(seg, w1))
         return fused_linear(hdn, w2)
 
+    def _hidden(self, e, seg):
+        """First half of expert ``e``: projection + activation."""
+        w1 = self.w1[e]
+        if self.glu:
+            return OF.gated_act(fused_linear(seg, w1), "swiglu" if self.activation in ("swiglu", "silu") else "geglu")
+        if self.activation == "gelu":
+            return fused_linear(seg, w1, act="gelu")
+        return OF.get_activation(self.activation)(fused_linear(seg, w1))
+
+    def _experts_fused_combine(self, xr, pieces, matrix, out_splits, grp):
+        """Expert MLPs whose output projection writes every row straight into the combine buffer of the rank the
+        token came from (per-row destination table in the GEMM epilogue): the return all-to-all is part of the GEMM."""
+        import numpy as np
+        L = self.local_experts
+        # expert-major order of the received rows, and for every row its source rank and position in that block
+        block_start = np.concatenate(([0], np.cumsum(out_splits)))[:-1]
+        perm, src, bounds, lo = [], [], [], 0
+        for e in range(L):
+            n_e = 0
+            for o, n, r in pieces[e]:
+                if n:
+                    perm.append(np.arange(o, o + n, dtype=np.int64))
+                    src.append(np.full(n, r, dtype=np.int64))
+                    n_e += n
+            bounds.append((lo, lo + n_e))
+            lo += n_e
+        perm = np.concatenate(perm) if perm else np.zeros(0, dtype=np.int64)
+        src = np.concatenate(src) if src else np.zeros(0, dtype=np.int64)
+        perm_t = torch.from_numpy(perm).to(xr.device, non_blocking=True)
+        xe = xr.index_select(0, perm_t)
+        hdn = torch.cat([self._hidden(e, xe[a:b]) for e, (a, b) in enumerate(bounds) if b > a])
+        back = [list(c) for c in zip(*matrix)]          # rows this rank returns to rank r = rows r sent here
+        return _ExpertOutCombine.apply(hdn, self.w2, bounds, perm_t, perm, src, block_start, back, matrix, grp)
+
     def _capacity(self, tokens):
         cf = self.train_cf if self.training else self.eval_cf
         return max(self.min_capacity, int(math.ceil(cf * tokens * self.top_k / self.num_experts)))
@@ -180,26 +268,28 @@ class ParallelMoE(nn.Module):
             else:
                 xr = _AllToAll.apply(xs, out_splits, in_splits, grp)
             # received layout: for each source rank, its segments for local experts 0..L-1
-            outs = torch.empty((xr.shape[0], shape[-1]), dtype=x.dtype, device=x.device)
             pieces, off = [[] for _ in range(self.local_experts)], 0
             for r in range(self.ep):
                 for e in range(self.local_experts):
                     n = recv_l[r][e]
-                    pieces[e].append((off, n))
+                    pieces[e].append((off, n, r))
                     off += n
-            res_parts = {}
-            for e in range(self.local_experts):
-                seg = torch.cat([xr[o:o + n] for o, n in pieces[e]]) if pieces[e] else xr[:0]
-                out_e = self._expert(e, seg)
-                o2 = 0
-                for o, n in pieces[e]:
-                    res_parts[o] = out_e[o2:o2 + n]
-                    o2 += n
-            outs = torch.cat([res_parts[o] for o in sorted(res_parts)]) if res_parts else xr
-            if peer:
-                ys = moe_comm.all_to_all_rows(outs, [list(c) for c in zip(*matrix)], grp)
+            if peer and moe_comm.fused_combine_enabled() and xr.shape[0] > 0:
+                ys = self._experts_fused_combine(xr, pieces, matrix, out_splits, grp)
             else:
-                ys = _AllToAll.apply(outs, in_splits, out_splits, grp)
+                res_parts = {}
+                for e in range(self.local_experts):
+                    seg = torch.cat([xr[o:o + n] for o, n, _ in pieces[e]]) if pieces[e] else xr[:0]
+                    out_e = self._expert(e, seg)
+                    o2 = 0
+                    for o, n, _ in pieces[e]:
+                        res_parts[o] = out_e[o2:o2 + n]
+                        o2 += n
+                outs = torch.cat([res_parts[o] for o in sorted(res_parts)]) if res_parts else xr
+                if peer:
+                    ys = moe_comm.all_to_all_rows(outs, [list(c) for c in zip(*matrix)], grp)
+                else:
+                    ys = _AllToAll.apply(outs, in_splits, out_splits, grp)
         else:
             cl = counts.tolist()
             parts, off = [], 0

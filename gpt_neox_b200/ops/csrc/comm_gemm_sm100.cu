@@ -1049,3 +1049,21 @@ extern "C" int neox_a2a_push(const void* src, const unsigned long long* dst_ptrs
                                                                                    status);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
+
+// Wait (bounded) until flags[r] >= epoch for every r != rank; a stream-ordered guard in front of kernels that write
+// into peers' buffers without checking themselves.
+namespace {
+__global__ void wait_flags_kernel(const uint32_t* flags, uint32_t epoch, int world, int rank, int* status) {
+    for (int r = threadIdx.x; r < world; r += blockDim.x)
+        if (r != rank && !wait_flag(flags + r, epoch)) atomicExch(status, 560 + r);
+}
+}  // namespace
+
+extern "C" int neox_wait_flags(const void* flags, unsigned epoch, int world, int rank, void* stream) {
+    if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
+    int* status = neox_status_word();
+    if (!status) return NEOX_ERR_DRIVER;
+    wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(flags), epoch, world,
+                                                                        rank, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}

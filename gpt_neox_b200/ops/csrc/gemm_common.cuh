@@ -35,6 +35,9 @@ struct GemmParams {
     float alpha;
     int vec_ok;
     int* status;
+    // optional per-row destination table (bf16 output only): row r is stored at address row_ptrs[r] instead of
+    // D + r * ldd -- the rows of one GEMM can then land in different buffers, including peers' memory
+    const unsigned long long* row_ptrs;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
@@ -127,7 +130,9 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
 #pragma unroll
             for (int j = 0; j < 8; ++j) o[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
         } else {
-            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0);
+            __nv_bfloat16* drow = p.row_ptrs ? reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row])
+                                             : reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd;
+            uint4* o = reinterpret_cast<uint4*>(drow + col0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint4 q;
@@ -153,6 +158,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
                 else x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.add)[(long long)row * p.ldadd + col]);
             }
             if (p.d_fp32) reinterpret_cast<float*>(p.D)[(long long)row * p.ldd + col] = x;
+            else if (p.row_ptrs) reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row])[col] = __float2bfloat16(x);
             else reinterpret_cast<__nv_bfloat16*>(p.D)[(long long)row * p.ldd + col] = __float2bfloat16(x);
         }
     }

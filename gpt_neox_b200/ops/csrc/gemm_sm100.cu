@@ -288,11 +288,29 @@ int neox_make_tmap_bf16_4d(CUtensorMap* out, const void* ptr, unsigned long long
     return r == CUDA_SUCCESS ? 0 : NEOX_ERR_TMAP;
 }
 
+extern "C" int neox_gemm_bf16_rowmap(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
+                                     const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
+                                     const void* aux, long long ldaux, int act, float alpha, const void* row_ptrs,
+                                     void* stream_);
+
 extern "C" int neox_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
                               long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
                               const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
                               const void* aux, long long ldaux, int act, float alpha, void* stream_) {
+    return neox_gemm_bf16_rowmap(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, d_fp32, bias, add, ldadd, add_fp32, preact,
+                                 ldpre, aux, ldaux, act, alpha, nullptr, stream_);
+}
+
+// row_ptrs (device array of M addresses, or NULL): destination of every output row (bf16 output; each address
+// 16-byte aligned and valid for N elements).  With it D may be NULL.
+extern "C" int neox_gemm_bf16_rowmap(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
+                                     const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
+                                     const void* aux, long long ldaux, int act, float alpha, const void* row_ptrs,
+                                     void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (row_ptrs && d_fp32) return NEOX_ERR_SHAPE;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes.
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8))
@@ -319,8 +337,9 @@ extern "C" int neox_gemm_bf16(const void* A, const void* B, void* D, int M, int 
     p.aux = static_cast<const __nv_bfloat16*>(aux); p.ldaux = ldaux;
     p.act = act; p.alpha = alpha;
     p.status = status;
+    p.row_ptrs = static_cast<const unsigned long long*>(row_ptrs);
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    bool vec = al16(D) && (ldd % 8 == 0);
+    bool vec = row_ptrs ? (N % 8 == 0) : (al16(D) && (ldd % 8 == 0));
     if (bias) vec = vec && al16(bias);
     if (add) vec = vec && al16(add) && (ldadd % 8 == 0);
     if (preact) vec = vec && al16(preact) && (ldpre % 8 == 0);

@@ -56,6 +56,23 @@ def gemm_ref(a, b, a_mn=False, b_mn=False, out_dtype=torch.bfloat16, bias=None, 
     return (v, pre) if want_preact else v
 
 
+def gemm_rowmap(a, b, row_ptrs, b_mn=False, bias=None):
+    """``a @ op(b) + bias`` whose output row r is stored (bf16) at device address ``row_ptrs[r]`` (int64 tensor of
+    M addresses, 16-byte aligned, possibly in other GPUs' peer-mapped memory) instead of into one matrix."""
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and row_ptrs.dtype == torch.int64
+    M, K = a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert row_ptrs.numel() == M and N % 8 == 0
+    if M == 0:
+        return
+    rc = native.lib().neox_gemm_bf16_rowmap(
+        native.ptr(a), native.ptr(b), None, M, N, K, ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),
+        ctypes.c_longlong(N), 0, int(b_mn), 0, native.ptr(bias), None, ctypes.c_longlong(0), 0, None,
+        ctypes.c_longlong(0), None, ctypes.c_longlong(0), ACT_NONE, ctypes.c_float(1.0), native.ptr(row_ptrs),
+        ctypes.c_void_p(native.stream_ptr()))
+    native.check(rc, "neox_gemm_bf16_rowmap")
+
+
 def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=None, add=None, act=ACT_NONE,
          aux=None, alpha=1.0, want_preact=False):
     """See module docstring.  ``add`` may alias ``out`` (in-place accumulate, e.g. wgrad into main_grad)."""

@@ -33,6 +33,12 @@ def enabled() -> bool:
     return os.environ.get("NEOX_FUSED_MOE_A2A", "1") != "0" and torch.cuda.is_available()
 
 
+def fused_combine_enabled() -> bool:
+    """Expert output GEMMs write their rows straight into the source ranks' combine buffers (``NEOX_FUSED_MOE_COMBINE=0``
+    keeps GEMM and exchange separate)."""
+    return os.environ.get("NEOX_FUSED_MOE_COMBINE", "1") != "0"
+
+
 def _ll_array(vals):
     arr = (ctypes.c_longlong * S.MAX_RANKS)()
     for i, v in enumerate(vals):
@@ -87,6 +93,45 @@ class PeerAllToAll:
         total = sum(recv)
         out = torch.empty(max(total, 1), h, device=x.device, dtype=x.dtype)
         rc = L.neox_gathered_copy(ctypes.c_void_p(buf.local), native.ptr(out), ctypes.c_ulonglong(total * row_bytes),
+                                  self.pad.word(A2A_READY), ctypes.c_uint(e), self.pad.c_ptrs, W, me, A2A_DONE,
+                                  self.pad.word(CTR_COPY), stream)
+        native.check(rc, "neox_gathered_copy")
+        return out[:total]
+
+
+    # ---- exchange whose rows are written by GEMM epilogues instead of a copy kernel
+    def begin_push(self, matrix):
+        """Open an exchange with count matrix ``matrix`` (as in ``exchange``) in which the caller's own kernels store
+        the rows: returns ``(epoch, buf, recv_off)`` -- row ``j`` of this rank's block for destination ``d`` belongs
+        at ``buf.ptrs[d] + (recv_off[d] + j) * row_bytes``.  The call waits (on the stream) until every destination
+        has released the buffer."""
+        me, W = self.rank, self.world
+        self.epoch += 1
+        e = self.epoch
+        rc = native.lib().neox_wait_flags(self.pad.word(A2A_DONE), ctypes.c_uint((e - 2) & 0xFFFFFFFF), W, me,
+                                          ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_wait_flags")
+        recv_off = [sum(matrix[r][d] for r in range(me)) for d in range(W)]
+        return e, recv_off
+
+    def push_buffer(self, e, matrix, row_bytes):
+        need = max(sum(matrix[r][d] for r in range(self.world)) for d in range(self.world)) * row_bytes
+        return self._buf(e & 1, max(need, 16))
+
+    def finish_push(self, e, buf, matrix, h, device):
+        """All rows of exchange ``e`` have been stored (by kernels launched on this stream): publish, wait for the
+        other ranks' rows and return them as a tensor."""
+        me, W = self.rank, self.world
+        L = native.lib()
+        stream = ctypes.c_void_p(native.stream_ptr())
+        zeros = _ll_array([0] * W)
+        rc = L.neox_a2a_push(ctypes.c_void_p(buf.local), buf.c_ptrs, zeros, zeros, zeros, 16, W, me,
+                             self.pad.word(A2A_DONE), ctypes.c_uint((e - 2) & 0xFFFFFFFF), self.pad.c_ptrs, A2A_READY,
+                             ctypes.c_uint(e), self.pad.word(CTR_PUSH), stream)
+        native.check(rc, "neox_a2a_push")
+        total = sum(matrix[r][me] for r in range(W))
+        out = torch.empty(max(total, 1), h, device=device, dtype=torch.bfloat16)
+        rc = L.neox_gathered_copy(ctypes.c_void_p(buf.local), native.ptr(out), ctypes.c_ulonglong(total * h * 2),
                                   self.pad.word(A2A_READY), ctypes.c_uint(e), self.pad.c_ptrs, W, me, A2A_DONE,
                                   self.pad.word(CTR_COPY), stream)
         native.check(rc, "neox_gathered_copy")

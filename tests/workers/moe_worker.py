@@ -35,19 +35,22 @@ def main():
         x = torch.randn(48 + 16 * it, 2, 256, device=dev, generator=g).to(torch.bfloat16)
         gy = torch.randn(48 + 16 * it, 2, 256, device=dev, generator=g).to(torch.bfloat16)
         res = {}
-        for mode in ("1", "0"):
+        for mode, comb in (("1", "1"), ("1", "0"), ("0", "0")):
             os.environ["NEOX_FUSED_MOE_A2A"] = mode
+            os.environ["NEOX_FUSED_MOE_COMBINE"] = comb
+            mode = mode + comb
             for p in moe.parameters():
                 p.grad = None
             xi = x.clone().requires_grad_(True)
             y, aux = moe(xi)
             (y.float() * gy.float()).sum().backward()
             res[mode] = [y.detach(), xi.grad] + [p.grad.clone() for p in moe.parameters()]
-        for i, (a, b) in enumerate(zip(res["1"], res["0"])):
-            err = (a.float() - b.float()).abs().max().item()
-            if err > 1e-2 * (b.float().abs().max().item() + 1e-6):
-                print(f"[rank {dist.get_rank()}] it {it} tensor {i}: max err {err}", flush=True)
-                ok = False
+        for variant in ("11", "10"):
+            for i, (a, b) in enumerate(zip(res[variant], res["00"])):
+                err = (a.float() - b.float()).abs().max().item()
+                if err > 1e-2 * (b.float().abs().max().item() + 1e-6):
+                    print(f"[rank {dist.get_rank()}] it {it} variant {variant} tensor {i}: max err {err}", flush=True)
+                    ok = False
     if native.read_status() != 0:
         ok = False
     flag = torch.tensor([int(ok)], device=dev)
