@@ -59,18 +59,21 @@ __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restr
     }
 }
 
-// 64 bf16 values of one row into a K-major swizzled [rows x 64] chunk (row pitch 128 bytes).
-__device__ __forceinline__ void store_row64(uint8_t* chunk, int row, const float (&v)[64]) {
+// 32 bf16 values (columns half * 32 .. + 31) of one row into a K-major swizzled [rows x 64] chunk (row pitch
+// 128 bytes).
+__device__ __forceinline__ void store_row32(uint8_t* chunk, int row, int half, const float (&v)[32]) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < 4; ++u) {
         uint4 q;
         q.x = pack_bf16x2(v[u * 8 + 0], v[u * 8 + 1]);
         q.y = pack_bf16x2(v[u * 8 + 2], v[u * 8 + 3]);
         q.z = pack_bf16x2(v[u * 8 + 4], v[u * 8 + 5]);
         q.w = pack_bf16x2(v[u * 8 + 6], v[u * 8 + 7]);
-        *reinterpret_cast<uint4*>(chunk + row * 128 + ((u ^ (row & 7)) << 4)) = q;
+        *reinterpret_cast<uint4*>(chunk + row * 128 + (((half * 4 + u) ^ (row & 7)) << 4)) = q;
     }
 }
+
+constexpr int BWD_THREADS = 384;   // warp 0 TMA, warp 1 MMA, warps 4-11 softmax (two warps per TMEM lane quarter)
 
 template <int D>
 struct BCfg {
@@ -88,7 +91,7 @@ struct BCfg {
 
 // =================================================================== dK / dV
 template <int D>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                      const BwdParams p) {
@@ -106,12 +109,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint64_t* kv_full = bars;            // 1
     uint64_t* st_full = bars + 1;        // 2  Q_i / dO_i landed
     uint64_t* st_empty = bars + 3;       // 2
-    uint64_t* sdp_full = bars + 5;       // 1  S^T, dP^T ready in TMEM
-    uint64_t* sdp_empty = bars + 6;      // 1
-    uint64_t* pds_full = bars + 7;       // 1  P^T, dS^T written to smem
-    uint64_t* pds_empty = bars + 8;      // 1
-    uint64_t* acc_full = bars + 9;       // 1  dK, dV final
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* sdp_full = bars + 5;       // 2  S^T, dP^T ready in TMEM (double-buffered)
+    uint64_t* sdp_empty = bars + 7;      // 2
+    uint64_t* pds_full = bars + 9;       // 1  P^T, dS^T written to smem
+    uint64_t* pds_empty = bars + 10;     // 1
+    uint64_t* acc_full = bars + 11;      // 1  dK, dV final
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kv0 = blockIdx.x * 128;
@@ -133,9 +136,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             mbar_init(&st_full[i], 1);
             mbar_init(&st_empty[i], 1);
         }
-        mbar_init(sdp_full, 1);
-        mbar_init(sdp_empty, 4);
-        mbar_init(pds_full, 4);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sdp_full[i], 1);
+            mbar_init(&sdp_empty[i], 8);
+        }
+        mbar_init(pds_full, 8);
         mbar_init(pds_empty, 1);
         mbar_init(acc_full, 1);
         fence_barrier_init();
@@ -148,7 +153,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t TM_ST = tmem_base, TM_DPT = tmem_base + 64, TM_DV = tmem_base + 128, TM_DK = tmem_base + 256;
+    // Two score buffers (S^T | dP^T, 64 columns each) so that the scores of query block i + 1 are computed while
+    // the softmax warps work on block i; dV and dK accumulate behind them.
+    const uint32_t TM_SC = tmem_base, TM_DV = tmem_base + 256, TM_DK = tmem_base + 384;
 
     if (warp == 0) {
         if (lane == 0 && niter > 0) {
@@ -186,8 +193,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             auto issue_scores = [&](int it) -> bool {
                 const int st = it & 1;
                 if (!mbar_wait(&st_full[st], (it >> 1) & 1)) return false;
-                if (!mbar_wait(sdp_empty, (it & 1) ^ 1)) return false;
+                if (!mbar_wait(&sdp_empty[st], ((it >> 1) & 1) ^ 1)) return false;
                 tc_fence_after();
+                const uint32_t TM_ST = TM_SC + st * 128, TM_DPT = TM_ST + 64;
                 const uint32_t q_base = smem_u32(sStage + st * 2 * C::SMALL);
                 const uint32_t do_base = q_base + C::SMALL;
 #pragma unroll
@@ -202,7 +210,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     umma_bf16_ss(TM_DPT, make_smem_desc_sw128(v_base + oa, 16, 1024),
                                  make_smem_desc_sw128(do_base + ob, 16, 1024), id_s, k != 0);
                 }
-                umma_commit(sdp_full);
+                umma_commit(&sdp_full[st]);
                 return true;
             };
             if (ok && !issue_scores(0)) {
@@ -211,6 +219,13 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             }
             for (int it = 0; it < niter && ok; ++it) {
                 const int st = it & 1;
+                // scores of the next query block first: the softmax warps can start on them as soon as they are
+                // done with this one, while the tensor core runs this block's dV / dK products
+                if (it + 1 < niter && !issue_scores(it + 1)) {
+                    atomicExch(p.status, 305);
+                    ok = false;
+                    break;
+                }
                 if (!mbar_wait(pds_full, it & 1)) {
                     atomicExch(p.status, 304);
                     ok = false;
@@ -231,58 +246,56 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 }
                 umma_commit(&st_empty[st]);
                 umma_commit(pds_empty);
-                if (it + 1 < niter && !issue_scores(it + 1)) {
-                    atomicExch(p.status, 305);
-                    ok = false;
-                    break;
-                }
             }
             umma_commit(acc_full);
         }
     } else if (warp >= 4) {
-        const int row = (warp - 4) * 32 + lane;   // key row inside the tile
-        float* my_lse = s_lse + (warp - 4) * 64;   // per-warp staging: only warp-level syncs are needed
-        float* my_dl = s_dl + (warp - 4) * 64;
+        // Two warps share each TMEM lane quarter (= 32 key rows): warps 4-7 take query columns 0-31 of the block,
+        // warps 8-11 columns 32-63, which halves the per-thread work and doubles the warps available to hide latency.
+        const int cw = warp - 4;
+        const int half = cw >> 2;
+        const int row = (warp & 3) * 32 + lane;    // key row inside the tile
+        float* my_lse = s_lse + cw * 32;           // per-warp staging: only warp-level syncs are needed
+        float* my_dl = s_dl + cw * 32;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         const int kv = kv0 + row;
         bool ok = true;
         for (int it = 0; it < niter; ++it) {
             const int h = hk * G + it / nq;
-            const int qi0 = (ib + it % nq) * 64;
+            const int qi0 = (ib + it % nq) * 64 + half * 32;
             __syncwarp();
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int q = qi0 + half * 32 + lane;
+            {
+                const int q = qi0 + lane;
                 const size_t idx = ((size_t)bb * p.hq + h) * p.sq + q;
-                my_lse[half * 32 + lane] = (q < p.sq) ? p.lse[idx] * LOG2E : INFINITY;
-                my_dl[half * 32 + lane] = (q < p.sq) ? p.delta[idx] : 0.f;
+                my_lse[lane] = (q < p.sq) ? p.lse[idx] * LOG2E : INFINITY;
+                my_dl[lane] = (q < p.sq) ? p.delta[idx] : 0.f;
             }
             __syncwarp();
-            if (!mbar_wait_warp(sdp_full, it & 1)) {
+            if (!mbar_wait_warp(&sdp_full[it & 1], (it >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.status, 306);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            float pt[64], ds[64];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            const uint32_t TM_ST = TM_SC + (it & 1) * 128, TM_DPT = TM_ST + 64;
+            float pt[32], ds[32];
+            {
                 uint32_t r[32];
-                tmem_ld_32x32(TM_ST + lane_base + c * 32, r);
+                tmem_ld_32x32(TM_ST + lane_base + half * 32, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 32; ++k) pt[c * 32 + k] = __uint_as_float(r[k]);
-                tmem_ld_32x32(TM_DPT + lane_base + c * 32, r);
+                for (int k = 0; k < 32; ++k) pt[k] = __uint_as_float(r[k]);
+                tmem_ld_32x32(TM_DPT + lane_base + half * 32, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 32; ++k) ds[c * 32 + k] = __uint_as_float(r[k]);
+                for (int k = 0; k < 32; ++k) ds[k] = __uint_as_float(r[k]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(sdp_empty);
+            if (lane == 0) mbar_arrive(&sdp_empty[it & 1]);
             const float slope = p.slopes ? p.slopes[h] * LOG2E : 0.f;
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
+            for (int c = 0; c < 32; ++c) {
                 const int q = qi0 + c;
                 const int qpos = q + off;
                 float t = pt[c] * p.scale_log2;
@@ -298,8 +311,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 ok = false;
                 break;
             }
-            store_row64(sPt, row, pt);
-            store_row64(sdSt, row, ds);
+            store_row32(sPt, row, half, pt);
+            store_row32(sdSt, row, half, ds);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(pds_full);
@@ -315,7 +328,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // guarded by warp-uniform conditions only and the per-row bound check applies to the stores.
         ok = __all_sync(0xffffffffu, ok);
         const bool live = kv < p.sk;
-        if (ok) {
+        if (ok && half == 0) {       // one warp per lane quarter writes the accumulators out
             __nv_bfloat16* dkp = p.dk + (long long)(live ? kv : 0) * p.dk_s[0] + bb * p.dk_s[1] + hk * p.dk_s[2];
             __nv_bfloat16* dvp = p.dv + (long long)(live ? kv : 0) * p.dv_s[0] + bb * p.dv_s[1] + hk * p.dv_s[2];
 #pragma unroll
@@ -362,7 +375,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
 // =================================================================== dQ
 template <int D>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const BwdParams p) {
@@ -377,12 +390,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t* q_full = bars;
     uint64_t* st_full = bars + 1;
     uint64_t* st_empty = bars + 3;
-    uint64_t* sdp_full = bars + 5;
-    uint64_t* sdp_empty = bars + 6;
-    uint64_t* ds_full = bars + 7;
-    uint64_t* ds_empty = bars + 8;
-    uint64_t* acc_full = bars + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* sdp_full = bars + 5;       // 2  S, dP ready in TMEM (double-buffered)
+    uint64_t* sdp_empty = bars + 7;      // 2
+    uint64_t* ds_full = bars + 9;
+    uint64_t* ds_empty = bars + 10;
+    uint64_t* acc_full = bars + 11;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_tile = gridDim.x - 1 - blockIdx.x;
@@ -404,22 +417,26 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&st_full[i], 1);
             mbar_init(&st_empty[i], 1);
         }
-        mbar_init(sdp_full, 1);
-        mbar_init(sdp_empty, 4);
-        mbar_init(ds_full, 4);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sdp_full[i], 1);
+            mbar_init(&sdp_empty[i], 8);
+        }
+        mbar_init(ds_full, 8);
         mbar_init(ds_empty, 1);
         mbar_init(acc_full, 1);
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 256);
+        tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t TM_S = tmem_base, TM_DP = tmem_base + 64, TM_DQ = tmem_base + 128;
+    // two score buffers (S | dP, 64 columns each): the scores of key block j + 1 are computed while the softmax warps
+    // work on block j; dQ accumulates behind them
+    const uint32_t TM_SC = tmem_base, TM_DQ = tmem_base + 256;
 
     if (warp == 0) {
         if (lane == 0 && niter > 0) {
@@ -455,8 +472,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             auto issue_scores = [&](int it) -> bool {
                 const int st = it & 1;
                 if (!mbar_wait(&st_full[st], (it >> 1) & 1)) return false;
-                if (!mbar_wait(sdp_empty, (it & 1) ^ 1)) return false;
+                if (!mbar_wait(&sdp_empty[st], ((it >> 1) & 1) ^ 1)) return false;
                 tc_fence_after();
+                const uint32_t TM_S = TM_SC + st * 128, TM_DP = TM_S + 64;
                 const uint32_t k_base = smem_u32(sStage + st * 2 * C::SMALL);
                 const uint32_t v_base = k_base + C::SMALL;
 #pragma unroll
@@ -471,7 +489,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     umma_bf16_ss(TM_DP, make_smem_desc_sw128(do_base + oa, 16, 1024),
                                  make_smem_desc_sw128(v_base + ob, 16, 1024), id_s, k != 0);
                 }
-                umma_commit(sdp_full);
+                umma_commit(&sdp_full[st]);
                 return true;
             };
             if (ok && !issue_scores(0)) {
@@ -480,6 +498,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             for (int it = 0; it < niter && ok; ++it) {
                 const int st = it & 1;
+                if (it + 1 < niter && !issue_scores(it + 1)) {      // next block's scores before this block's dQ
+                    atomicExch(p.status, 315);
+                    ok = false;
+                    break;
+                }
                 if (!mbar_wait(ds_full, it & 1)) {
                     atomicExch(p.status, 314);
                     ok = false;
@@ -494,16 +517,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
                 umma_commit(&st_empty[st]);
                 umma_commit(ds_empty);
-                if (it + 1 < niter && !issue_scores(it + 1)) {
-                    atomicExch(p.status, 315);
-                    ok = false;
-                    break;
-                }
             }
             umma_commit(acc_full);
         }
     } else if (warp >= 4) {
-        const int row = (warp - 4) * 32 + lane;
+        // two warps per TMEM lane quarter (32 query rows): warps 4-7 take key columns 0-31 of the block, 8-11 the rest
+        const int half = (warp - 4) >> 2;
+        const int row = (warp & 3) * 32 + lane;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         const int q = q0 + row;
         const int qpos = q + off;
@@ -513,31 +533,31 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float slope = p.slopes ? p.slopes[h] * LOG2E : 0.f;
         bool ok = true;
         for (int it = 0; it < niter; ++it) {
-            const int kvj = (jb + it) * 64;
-            if (!mbar_wait_warp(sdp_full, it & 1)) {
+            const int kvj = (jb + it) * 64 + half * 32;
+            if (!mbar_wait_warp(&sdp_full[it & 1], (it >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.status, 316);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            float pt[64], ds[64];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            const uint32_t TM_S = TM_SC + (it & 1) * 128, TM_DP = TM_S + 64;
+            float pt[32], ds[32];
+            {
                 uint32_t r[32];
-                tmem_ld_32x32(TM_S + lane_base + c * 32, r);
+                tmem_ld_32x32(TM_S + lane_base + half * 32, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 32; ++k) pt[c * 32 + k] = __uint_as_float(r[k]);
-                tmem_ld_32x32(TM_DP + lane_base + c * 32, r);
+                for (int k = 0; k < 32; ++k) pt[k] = __uint_as_float(r[k]);
+                tmem_ld_32x32(TM_DP + lane_base + half * 32, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 32; ++k) ds[c * 32 + k] = __uint_as_float(r[k]);
+                for (int k = 0; k < 32; ++k) ds[k] = __uint_as_float(r[k]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(sdp_empty);
+            if (lane == 0) mbar_arrive(&sdp_empty[it & 1]);
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
+            for (int c = 0; c < 32; ++c) {
                 const int kv = kvj + c;
                 float t = pt[c] * p.scale_log2;
                 if (p.slopes) t -= slope * fabsf((float)(qpos - kv));
@@ -551,7 +571,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 ok = false;
                 break;
             }
-            store_row64(sdS, row, ds);
+            store_row32(sdS, row, half, ds);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_full);
@@ -565,7 +585,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
         const bool live = q < p.sq;
-        if (ok) {
+        if (ok && half == 0) {
             __nv_bfloat16* dqp = p.dq + (long long)(live ? q : 0) * p.dq_s[0] + bb * p.dq_s[1] + h * p.dq_s[2];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -593,7 +613,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -607,9 +627,9 @@ int launch_bwd(const CUtensorMap (&t)[8], const BwdParams& p, cudaStream_t st) {
         attr = true;
     }
     dim3 g1((p.sk + 127) / 128, p.b * p.hkv);
-    flash_bwd_dkv_kernel<D><<<g1, 256, BCfg<D>::SMEM, st>>>(t[0], t[1], t[2], t[3], p);
+    flash_bwd_dkv_kernel<D><<<g1, BWD_THREADS, BCfg<D>::SMEM, st>>>(t[0], t[1], t[2], t[3], p);
     dim3 g2((p.sq + 127) / 128, p.b * p.hq);
-    flash_bwd_dq_kernel<D><<<g2, 256, BCfg<D>::SMEM, st>>>(t[4], t[5], t[6], t[7], p);
+    flash_bwd_dq_kernel<D><<<g2, BWD_THREADS, BCfg<D>::SMEM, st>>>(t[4], t[5], t[6], t[7], p);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
