@@ -59,21 +59,25 @@ __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restr
     }
 }
 
-// 32 bf16 values (columns half * 32 .. + 31) of one row into a K-major swizzled [rows x 64] chunk (row pitch
-// 128 bytes).
-__device__ __forceinline__ void store_row32(uint8_t* chunk, int row, int half, const float (&v)[32]) {
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32(taddr, r); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
+
+constexpr int PARTS = 4;                           // softmax warps per TMEM lane quarter
+constexpr int CPT = 64 / PARTS;                    // score columns per softmax thread
+constexpr int BWD_THREADS = 128 + PARTS * 128;     // warp 0 TMA, warp 1 MMA, warps 4.. softmax
+
+// CPT bf16 values (columns part * CPT ...) of one row into a K-major swizzled [rows x 64] chunk (row pitch 128 bytes).
+__device__ __forceinline__ void store_row_part(uint8_t* chunk, int row, int part, const float (&v)[CPT]) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < CPT / 8; ++u) {
         uint4 q;
         q.x = pack_bf16x2(v[u * 8 + 0], v[u * 8 + 1]);
         q.y = pack_bf16x2(v[u * 8 + 2], v[u * 8 + 3]);
         q.z = pack_bf16x2(v[u * 8 + 4], v[u * 8 + 5]);
         q.w = pack_bf16x2(v[u * 8 + 6], v[u * 8 + 7]);
-        *reinterpret_cast<uint4*>(chunk + row * 128 + (((half * 4 + u) ^ (row & 7)) << 4)) = q;
+        *reinterpret_cast<uint4*>(chunk + row * 128 + (((part * (CPT / 8) + u) ^ (row & 7)) << 4)) = q;
     }
 }
-
-constexpr int BWD_THREADS = 384;   // warp 0 TMA, warp 1 MMA, warps 4-11 softmax (two warps per TMEM lane quarter)
 
 template <int D>
 struct BCfg {
@@ -138,9 +142,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sdp_full[i], 1);
-            mbar_init(&sdp_empty[i], 8);
+            mbar_init(&sdp_empty[i], 4 * PARTS);
         }
-        mbar_init(pds_full, 8);
+        mbar_init(pds_full, 4 * PARTS);
         mbar_init(pds_empty, 1);
         mbar_init(acc_full, 1);
         fence_barrier_init();
@@ -253,18 +257,18 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // Two warps share each TMEM lane quarter (= 32 key rows): warps 4-7 take query columns 0-31 of the block,
         // warps 8-11 columns 32-63, which halves the per-thread work and doubles the warps available to hide latency.
         const int cw = warp - 4;
-        const int half = cw >> 2;
+        const int half = cw >> 2;                 // which CPT-column slice of the block this warp owns
         const int row = (warp & 3) * 32 + lane;    // key row inside the tile
-        float* my_lse = s_lse + cw * 32;           // per-warp staging: only warp-level syncs are needed
-        float* my_dl = s_dl + cw * 32;
+        float* my_lse = s_lse + cw * CPT;          // per-warp staging: only warp-level syncs are needed
+        float* my_dl = s_dl + cw * CPT;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         const int kv = kv0 + row;
         bool ok = true;
         for (int it = 0; it < niter; ++it) {
             const int h = hk * G + it / nq;
-            const int qi0 = (ib + it % nq) * 64 + half * 32;
+            const int qi0 = (ib + it % nq) * 64 + half * CPT;
             __syncwarp();
-            {
+            if (lane < CPT) {
                 const int q = qi0 + lane;
                 const size_t idx = ((size_t)bb * p.hq + h) * p.sq + q;
                 my_lse[lane] = (q < p.sq) ? p.lse[idx] * LOG2E : INFINITY;
@@ -278,24 +282,24 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             }
             tc_fence_after();
             const uint32_t TM_ST = TM_SC + (it & 1) * 128, TM_DPT = TM_ST + 64;
-            float pt[32], ds[32];
+            float pt[CPT], ds[CPT];
             {
-                uint32_t r[32];
-                tmem_ld_32x32(TM_ST + lane_base + half * 32, r);
+                uint32_t r[CPT], r2[CPT];
+                tmem_ld_cols(TM_ST + lane_base + half * CPT, r);
+                tmem_ld_cols(TM_DPT + lane_base + half * CPT, r2);
                 tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 32; ++k) pt[k] = __uint_as_float(r[k]);
-                tmem_ld_32x32(TM_DPT + lane_base + half * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 32; ++k) ds[k] = __uint_as_float(r[k]);
+                for (int k = 0; k < CPT; ++k) {
+                    pt[k] = __uint_as_float(r[k]);
+                    ds[k] = __uint_as_float(r2[k]);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sdp_empty[it & 1]);
             const float slope = p.slopes ? p.slopes[h] * LOG2E : 0.f;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < CPT; ++c) {
                 const int q = qi0 + c;
                 const int qpos = q + off;
                 float t = pt[c] * p.scale_log2;
@@ -311,8 +315,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 ok = false;
                 break;
             }
-            store_row32(sPt, row, half, pt);
-            store_row32(sdSt, row, half, ds);
+            store_row_part(sPt, row, half, pt);
+            store_row_part(sdSt, row, half, ds);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(pds_full);
@@ -336,7 +340,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 uint32_t r[32];
                 uint4 q;
                 if (niter > 0) {
-                    tmem_ld_32x32(TM_DV + lane_base + c * 32, r);
+                    tmem_ld_cols(TM_DV + lane_base + c * 32, r);
                     tmem_wait_ld();
                 } else {
 #pragma unroll
@@ -351,7 +355,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     if (live) reinterpret_cast<uint4*>(dvp + c * 32)[u] = q;
                 }
                 if (niter > 0) {
-                    tmem_ld_32x32(TM_DK + lane_base + c * 32, r);
+                    tmem_ld_cols(TM_DK + lane_base + c * 32, r);
                     tmem_wait_ld();
                 }
 #pragma unroll
@@ -419,9 +423,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sdp_full[i], 1);
-            mbar_init(&sdp_empty[i], 8);
+            mbar_init(&sdp_empty[i], 4 * PARTS);
         }
-        mbar_init(ds_full, 8);
+        mbar_init(ds_full, 4 * PARTS);
         mbar_init(ds_empty, 1);
         mbar_init(acc_full, 1);
         fence_barrier_init();
@@ -533,7 +537,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float slope = p.slopes ? p.slopes[h] * LOG2E : 0.f;
         bool ok = true;
         for (int it = 0; it < niter; ++it) {
-            const int kvj = (jb + it) * 64 + half * 32;
+            const int kvj = (jb + it) * 64 + half * CPT;
             if (!mbar_wait_warp(&sdp_full[it & 1], (it >> 1) & 1)) {
                 if (lane == 0) atomicExch(p.status, 316);
                 ok = false;
@@ -541,23 +545,23 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             tc_fence_after();
             const uint32_t TM_S = TM_SC + (it & 1) * 128, TM_DP = TM_S + 64;
-            float pt[32], ds[32];
+            float pt[CPT], ds[CPT];
             {
-                uint32_t r[32];
-                tmem_ld_32x32(TM_S + lane_base + half * 32, r);
+                uint32_t r[CPT], r2[CPT];
+                tmem_ld_cols(TM_S + lane_base + half * CPT, r);
+                tmem_ld_cols(TM_DP + lane_base + half * CPT, r2);
                 tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 32; ++k) pt[k] = __uint_as_float(r[k]);
-                tmem_ld_32x32(TM_DP + lane_base + half * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 32; ++k) ds[k] = __uint_as_float(r[k]);
+                for (int k = 0; k < CPT; ++k) {
+                    pt[k] = __uint_as_float(r[k]);
+                    ds[k] = __uint_as_float(r2[k]);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sdp_empty[it & 1]);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < CPT; ++c) {
                 const int kv = kvj + c;
                 float t = pt[c] * p.scale_log2;
                 if (p.slopes) t -= slope * fabsf((float)(qpos - kv));
@@ -571,7 +575,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 ok = false;
                 break;
             }
-            store_row32(sdS, row, half, ds);
+            store_row_part(sdS, row, half, ds);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_full);
@@ -591,7 +595,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
                 if (niter > 0) {
-                    tmem_ld_32x32(TM_DQ + lane_base + c * 32, r);
+                    tmem_ld_cols(TM_DQ + lane_base + c * 32, r);
                     tmem_wait_ld();
                 } else {
 #pragma unroll
