@@ -634,7 +634,7 @@ class NeoXArgs:
             f"train {self.train_data_paths}, valid {self.valid_data_paths}, test {self.test_data_paths}")
         for split in ("train", "valid", "test"):
             paths, weights = getattr(self, f"{split}_data_paths"), getattr(self, f"{split}_data_weights")
-            if paths is not None:
+            if paths is not None and weights is not None:
                 assert len(paths) == len(weights), f"{split}_data_paths and {split}_data_weights differ in length"
         if self.sequence_parallel and self.model_parallel_size > 1 and self.seq_length is not None:
             if self.seq_length % self.model_parallel_size != 0:

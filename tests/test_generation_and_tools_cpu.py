@@ -156,3 +156,59 @@ def test_objectives_match_dense_formulas():
     l3, m3 = O.reward_model_loss(vals, one)
     want3 = -torch.nn.functional.logsigmoid(vals[:2, -1, 0] - vals[2:, -1, 0]).mean()
     assert torch.allclose(l3, want3, atol=1e-6)
+
+
+def test_raw_llama_conversion_layout(tmp_path):
+    """Meta-format shards -> NeoX shards (TP 2) -> Hugging Face llama: every matrix lands where the HF layout wants
+    it, with q / k rows permuted from interleaved-pair to rotate-half rotary order."""
+    import json
+    from gpt_neox_b200.tools.ckpts import convert_neox_to_hf
+    from gpt_neox_b200.tools.ckpts import convert_raw_llama_weights_to_neox as RAW
+    torch.manual_seed(0)
+    L, heads, kvh, dim, ffn, vocab, in_shards = 2, 4, 2, 64, 96, 128, 2
+    hd = dim // heads
+    full = {"tok_embeddings.weight": torch.randn(vocab, dim), "norm.weight": torch.randn(dim),
+            "output.weight": torch.randn(vocab, dim)}
+    for i in range(L):
+        p = f"layers.{i}."
+        full[p + "attention.wq.weight"] = torch.randn(heads * hd, dim)
+        full[p + "attention.wk.weight"] = torch.randn(kvh * hd, dim)
+        full[p + "attention.wv.weight"] = torch.randn(kvh * hd, dim)
+        full[p + "attention.wo.weight"] = torch.randn(dim, heads * hd)
+        full[p + "feed_forward.w1.weight"] = torch.randn(ffn, dim)
+        full[p + "feed_forward.w2.weight"] = torch.randn(dim, ffn)
+        full[p + "feed_forward.w3.weight"] = torch.randn(ffn, dim)
+        full[p + "attention_norm.weight"] = torch.randn(dim)
+        full[p + "ffn_norm.weight"] = torch.randn(dim)
+    col = ("wo.weight", "w2.weight", "tok_embeddings.weight")
+    raw_dir = tmp_path / "raw"
+    raw_dir.mkdir()
+    for r in range(in_shards):
+        shard = {}
+        for k, v in full.items():
+            if v.dim() == 1:
+                shard[k] = v
+            else:
+                shard[k] = torch.chunk(v, in_shards, dim=1 if k.endswith(col) else 0)[r].clone()
+        torch.save(shard, raw_dir / f"consolidated.{r:02d}.pth")
+    json.dump({"dim": dim, "n_layers": L, "n_heads": heads, "n_kv_heads": kvh}, open(raw_dir / "params.json", "w"))
+    shards, _ = RAW.convert(str(raw_dir), 2)
+    out = tmp_path / "neox"
+    RAW.save(shards, str(out))
+    conf = {"num_layers": L, "hidden_size": dim, "num_attention_heads": heads, "num_kv_heads": kvh,
+            "max_position_embeddings": 64, "rotary_pct": 1.0, "rotary_emb_base": 10000, "rms_norm_epsilon": 1e-5,
+            "gpt_j_residual": False, "no_weight_tying": True, "padded_vocab_size": vocab, "model_parallel_size": 2,
+            "intermediate_size": 3 * ffn, "activation": "swiglu", "use_bias_in_attn_linear": False}   # NeoX counts up + gate + down
+    hf = convert_neox_to_hf.convert(str(out / "global_step0"), conf, architecture="llama")
+    sd = hf.state_dict()
+    for i in range(L):
+        p, hp = f"layers.{i}.", f"model.layers.{i}."
+        assert torch.equal(sd[hp + "self_attn.q_proj.weight"], RAW.permute_rotary(full[p + "attention.wq.weight"], heads, hd))
+        assert torch.equal(sd[hp + "self_attn.k_proj.weight"], RAW.permute_rotary(full[p + "attention.wk.weight"], kvh, hd))
+        assert torch.equal(sd[hp + "self_attn.v_proj.weight"], full[p + "attention.wv.weight"])
+        assert torch.equal(sd[hp + "self_attn.o_proj.weight"], full[p + "attention.wo.weight"])
+        assert torch.equal(sd[hp + "mlp.up_proj.weight"], full[p + "feed_forward.w3.weight"])
+        assert torch.equal(sd[hp + "mlp.gate_proj.weight"], full[p + "feed_forward.w1.weight"])
+        assert torch.equal(sd[hp + "mlp.down_proj.weight"], full[p + "feed_forward.w2.weight"])
+    assert torch.equal(sd["model.embed_tokens.weight"], full["tok_embeddings.weight"])
+    assert torch.equal(sd["lm_head.weight"], full["output.weight"])
