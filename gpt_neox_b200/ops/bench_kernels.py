@@ -1,0 +1,122 @@
+"""Roofline check of the single-GPU kernels: achieved bandwidth / throughput against the measured peaks.
+
+    python -m gpt_neox_b200.ops.bench_kernels [--only gemm_fwd,layernorm_fwd,...] [--tokens 8192] [--hidden 6144]
+
+Every entry is timed with CUDA events after warm-up with a 256 MiB buffer rewritten between iterations (L2 flush), and
+reported as ``algorithmic bytes (or FLOPs) / time`` and as a fraction of the measured copy bandwidth / cuBLAS bf16
+throughput (``MEASURED_PEAKS.json`` at the repository root when present, else 6650 GB/s and 1590 TFLOP/s).
+The same entry points are what the ncu summaries under ``profiles/`` were captured from (``--only`` selects one).
+"""
+import argparse
+import json
+import os
+
+import torch
+
+from . import functional as OF
+from . import gemm as G
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        p = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=6144)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    only = set(x for x in a.only.split(",") if x)
+    dev = torch.device("cuda")
+    T, h = a.tokens, a.hidden
+    hbm, tf, kind = peaks()
+    flush = torch.zeros(64 << 20, device=dev)
+    bf = lambda *s: (torch.randn(*s, device=dev) * 0.05).to(torch.bfloat16)
+    out = []
+
+    def run(name, fn, nbytes=0.0, flops=0.0):
+        if only and name not in only:
+            return
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(a.iters):
+            flush.add_(1.0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = sorted(ts)[len(ts) // 2]
+        rec = {"kernel": name, "ms": round(ms, 4)}
+        if nbytes:
+            rec["gbs"] = round(nbytes / ms / 1e6, 1)
+            rec[f"of_{kind}_hbm"] = round(nbytes / ms / 1e6 / hbm, 3)
+        if flops:
+            rec["tflops"] = round(flops / ms / 1e9, 1)
+            rec[f"of_{kind}_bf16"] = round(flops / ms / 1e9 / tf, 3)
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+
+    x = bf(T, h)
+    w_qkv, w_fc1, w_fc2 = bf(3 * h, h), bf(4 * h, h), bf(h, 4 * h)
+    y4 = bf(T, 4 * h)
+    g_h = bf(T, h)
+    acc = torch.zeros(4 * h, h, device=dev, dtype=torch.float32)
+    bias4 = bf(4 * h)
+    run("gemm_fwd_qkv", lambda: G.gemm(x, w_qkv), flops=2.0 * T * h * 3 * h)
+    run("gemm_fwd_fc1_bias_gelu", lambda: G.gemm(x, w_fc1, bias=bias4, act=G.ACT_GELU, want_preact=True),
+        flops=2.0 * T * h * 4 * h)
+    run("gemm_fwd_fc2", lambda: G.gemm(y4, w_fc2), flops=2.0 * T * h * 4 * h)
+    run("gemm_dgrad_fc1", lambda: G.gemm(y4, w_fc1, b_mn=True), flops=2.0 * T * h * 4 * h)
+    run("gemm_wgrad_fc1_fp32_accumulate", lambda: G.gemm(y4, x, a_mn=True, b_mn=True, out=acc, add=acc),
+        flops=2.0 * T * h * 4 * h)
+
+    gamma, beta = bf(h), bf(h)
+    run("layernorm_fwd", lambda: OF.layer_norm(x, gamma, beta, 1e-5), nbytes=2.0 * T * h * 2)
+    xl = x.clone().requires_grad_(True)
+    gl, bl = gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True)
+    yl = OF.layer_norm(xl, gl, bl, 1e-5)
+    run("layernorm_bwd", lambda: torch.autograd.grad(yl, (xl, gl, bl), g_h, retain_graph=True),
+        nbytes=3.0 * T * h * 2)
+    run("rmsnorm_fwd", lambda: OF.rms_norm(x, gamma, None, 1e-6), nbytes=2.0 * T * h * 2)
+    run("bias_gelu_fwd", lambda: OF.bias_gelu(y4, bias4), nbytes=2.0 * T * 4 * h * 2)
+    sw = bf(T, 8 * h // 3 // 64 * 64 * 2)
+    run("swiglu_fwd", lambda: OF.gated_act(sw, "swiglu"), nbytes=1.5 * sw.numel() * 2)
+    sc = bf(4, 16, 2048, 2048)
+    run("causal_softmax_fwd", lambda: OF.scaled_upper_triang_masked_softmax(sc.view(-1, 2048, 2048), 1.0),
+        nbytes=2.0 * sc.numel() * 2)
+    V = 50432
+    logits = bf(T, V)
+    tgt = torch.randint(0, V, (T,), device=dev)
+    from ..parallel.cross_entropy import vocab_parallel_cross_entropy
+    run("cross_entropy_fwd", lambda: vocab_parallel_cross_entropy(logits, tgt), nbytes=2.0 * T * V * 2)
+    n = 400 * 1000 * 1000
+    p32, m32, v32, g32 = (torch.zeros(n, device=dev) for _ in range(4))
+    pb = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+    import ctypes
+    from . import native
+
+    def adam():
+        rc = native.lib().neox_adam_step(native.ptr(p32), native.ptr(m32), native.ptr(v32), native.ptr(g32),
+                                         native.ptr(pb), 0, ctypes.c_longlong(n), ctypes.c_float(1e-4),
+                                         ctypes.c_float(0.9), ctypes.c_float(0.95), ctypes.c_float(1e-8),
+                                         ctypes.c_float(0.01), ctypes.c_float(0.1), ctypes.c_float(0.05),
+                                         ctypes.c_float(1.0), 1, ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_adam_step")
+    run("adam_step_bf16_writeback", adam, nbytes=n * (4 * 4 + 3 * 4 + 2.0))
+    if not only:
+        print(json.dumps({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "kind": kind}, "results": out}))
+
+
+if __name__ == "__main__":
+    main()
