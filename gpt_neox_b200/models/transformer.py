@@ -72,7 +72,7 @@ class ParallelMLP(nn.Module):
         if not self.is_gated and self.activation_type != "gelu":
             self.act = OF.get_activation(self.activation_type)
 
-    def forward(self, hidden_states, residual=None, partial_add=None, post_residual=None):
+    def forward(self, hidden_states, residual=None, partial_add=None, post_residual=None, fuse_bias=False):
         """Returns ``(output, output_bias)``; ``residual`` is added by linear2 (see ``RowParallelLinear.forward``).
         With ``post_residual`` it returns ``reduce(mlp + bias + partial_add) + post_residual`` as one tensor."""
         l1 = self.linear1
@@ -81,7 +81,7 @@ class ParallelMLP(nn.Module):
             inter, pre = l1.matmul(hidden_states, l1.bias, act="gelu", split_pre=True)
             if post_residual is not None:
                 return self.linear2.forward_reduced(inter, partial_add, post_residual, dgelu_aux=pre)
-            return self.linear2(inter, residual=residual, dgelu_aux=pre)
+            return self.linear2(inter, residual=residual, dgelu_aux=pre, fuse_bias=fuse_bias)
         else:
             inter, bias = l1(hidden_states)
             if self.is_gated:
@@ -90,7 +90,7 @@ class ParallelMLP(nn.Module):
                 inter = self.act(inter + bias if bias is not None else inter)
         if post_residual is not None:
             return self.linear2.forward_reduced(inter, partial_add, post_residual)
-        return self.linear2(inter, residual=residual)
+        return self.linear2(inter, residual=residual, fuse_bias=fuse_bias)
 
 
 class ParallelLinear(nn.Module):
@@ -299,11 +299,11 @@ class ParallelSelfAttention(nn.Module):
         return packed_qkv_attention(mixed, cos, sin, causal=True, softmax_scale=(self.coeff or 1.0) / self.norm_factor,
                                     window=self.sliding_window_width, alibi_slopes=slopes)
 
-    def forward(self, hidden_states, attention_mask=None, layer_past=None, residual=None):
+    def forward(self, hidden_states, attention_mask=None, layer_past=None, residual=None, fuse_bias=False):
         packed = self._packed_path(hidden_states, layer_past)
         if packed is not None and not isinstance(packed, tuple):
             ctx = packed.reshape(packed.shape[0], packed.shape[1], self.hidden_size_per_partition)
-            return self.dense(ctx, residual=residual)
+            return self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
         if isinstance(packed, tuple):
             mixed, hn = packed[0], self.hidden_size_per_attention_head
             q, k, v = mixed[..., :hn], mixed[..., hn:2 * hn], mixed[..., 2 * hn:]
@@ -335,7 +335,7 @@ class ParallelSelfAttention(nn.Module):
             ctx = flash_attention(q, k, v, causal=True, softmax_scale=(self.coeff or 1.0) / self.norm_factor,
                                   window=self.sliding_window_width, alibi_slopes=slopes)
         ctx = ctx.reshape(ctx.shape[0], ctx.shape[1], self.hidden_size_per_partition)
-        out, bias = self.dense(ctx, residual=residual)
+        out, bias = self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
         if self.use_cache:
             out = [out, present]
         return out, bias
@@ -395,11 +395,13 @@ class ParallelTransformerLayer(nn.Module):
                 # attention partial (+ its bias) [+ residual when no reduction follows] accumulated by the
                 # GEMM epilogues:  out = residual + attn + b_a + mlp + b_m
                 attn_res = residual if self.tp == 1 else None
-                a_out, a_bias = self.attention(x1, attention_mask, layer_past=layer_past, residual=attn_res)
+                # the attention output bias rides in the dense GEMM's epilogue (every rank adds its own to its partial)
+                a_out, a_bias = self.attention(x1, attention_mask, layer_past=layer_past, residual=attn_res,
+                                               fuse_bias=True)
                 if a_bias is not None:
                     a_out = a_out + a_bias
                 if self.tp == 1:
-                    m_out, m_bias = self.mlp(x2, residual=a_out)
+                    m_out, m_bias = self.mlp(x2, residual=a_out, fuse_bias=True)
                     if m_bias is not None:
                         m_out = m_out + m_bias
                     return m_out, moe_loss

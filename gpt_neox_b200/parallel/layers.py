@@ -276,16 +276,19 @@ class RowParallelLinear(nn.Module):
         return tokens % self.tp == 0 and fused_comm.eligible(x, self.weight, self.tp, tokens // self.tp) and \
             (self.bias is None or self.bias.dtype == torch.bfloat16)
 
-    def forward(self, input_, residual=None, dgelu_aux=None):
+    def forward(self, input_, residual=None, dgelu_aux=None, fuse_bias=False):
         """``residual`` (optional) is added to the layer's output: after the cross-rank reduction when this layer
         performs it, to this rank's partial product when the caller defers it (``parallel_output``).
-        ``dgelu_aux``: pre-activation of the layer that produced ``input_`` through a GeLU (see ``matmul``)."""
+        ``dgelu_aux``: pre-activation of the layer that produced ``input_`` through a GeLU (see ``matmul``).
+        ``fuse_bias``: add the bias here (GEMM epilogue) even if the layer was built with ``skip_bias_add``; the
+        returned bias is then ``None``."""
         x = input_ if self.input_is_parallel else M.scatter_to_model_parallel_region(input_)
-        bias = None if self.skip_bias_add else self.bias
+        skip = self.skip_bias_add and not fuse_bias
+        bias = None if skip else self.bias
         if not self.parallel_output and self._fusable(x):
             # GEMM -> reduce-scatter / all-reduce in one pass; bias and residual are added after the reduction
             out = fused_comm.row_linear(x, self.weight, bias, residual, self.sequence_parallel, dgelu_aux=dgelu_aux)
-            return out, (self.bias if self.skip_bias_add else None)
+            return out, (self.bias if skip else None)
         local = self.tp == 1 or self.parallel_output
         if self.fp8:
             out = mx_linear(x, self.weight, bias if local else None, self.fp8_hybrid, self.fp8_wgrad)
@@ -303,7 +306,7 @@ class RowParallelLinear(nn.Module):
                 out = out + bias
             if residual is not None:
                 out = out + residual
-        return out, (self.bias if self.skip_bias_add else None)
+        return out, (self.bias if skip else None)
 
     def forward_reduced(self, input_, partial_add, post_residual, dgelu_aux=None):
         """``reduce_over_tp(input_ W^T + bias + partial_add) + post_residual`` regardless of ``parallel_output``:
