@@ -19,6 +19,16 @@ template <typename T>
 struct Vec8;
 template <>
 struct Vec8<__nv_bfloat16> {
+    typedef uint4 Raw;   // 8 packed elements: what a prefetch keeps in registers
+    static __device__ __forceinline__ Raw raw_load(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+    static __device__ __forceinline__ void unpack(const Raw& u, float (&v)[8]) {
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
     static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
         uint4 u = *reinterpret_cast<const uint4*>(p);
         uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -40,6 +50,17 @@ struct Vec8<__nv_bfloat16> {
 };
 template <>
 struct Vec8<__half> {
+    typedef uint4 Raw;
+    static __device__ __forceinline__ Raw raw_load(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+    static __device__ __forceinline__ void unpack(const Raw& u, float (&v)[8]) {
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
     static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
         uint4 u = *reinterpret_cast<const uint4*>(p);
         const __half2* h = reinterpret_cast<const __half2*>(&u);
@@ -60,6 +81,18 @@ struct Vec8<__half> {
 };
 template <>
 struct Vec8<float> {
+    struct Raw {
+        float4 a, b;
+    };
+    static __device__ __forceinline__ Raw raw_load(const float* p) {
+        Raw r;
+        r.a = *reinterpret_cast<const float4*>(p);
+        r.b = *reinterpret_cast<const float4*>(p + 4);
+        return r;
+    }
+    static __device__ __forceinline__ void unpack(const Raw& r, float (&v)[8]) {
+        v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+    }
     static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
         float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
@@ -128,6 +161,17 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const T* __restrict__ x, 
     __shared__ float red[66];
     const int nvec = cols >> 3;
     const bool cached = nvec <= MAXV * (int)blockDim.x;
+    // Cached path: the next row's (packed) data is requested before this row's reductions start, so two rows per
+    // CTA are in flight and the loads overlap the block-wide sums.
+    typename Vec8<T>::Raw nxt[MAXV];
+    auto fetch = [&](int r) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int c = threadIdx.x + j * blockDim.x;
+            if (c < nvec) nxt[j] = Vec8<T>::raw_load(x + (size_t)r * cols + c * 8);
+        }
+    };
+    if (cached && (int)blockIdx.x < rows) fetch(blockIdx.x);
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* xr = x + (size_t)row * cols;
         T* yr = y + (size_t)row * cols;
@@ -138,11 +182,12 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const T* __restrict__ x, 
             for (int j = 0; j < MAXV; ++j) {
                 const int c = threadIdx.x + j * blockDim.x;
                 if (c < nvec) {
-                    Vec8<T>::load(xr + c * 8, v[j]);
+                    Vec8<T>::unpack(nxt[j], v[j]);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) s += RMS ? v[j][i] * v[j][i] : v[j][i];
                 }
             }
+            if (row + (int)gridDim.x < rows) fetch(row + gridDim.x);
         } else {
             for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
                 float t[8];
@@ -234,22 +279,45 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const T* __restrict__ g, 
     } else {
         for (int c = threadIdx.x; c < cols; c += blockDim.x) pg[c] = pb[c] = 0.f;
     }
+    typename Vec8<T>::Raw nx[MAXV], ng[MAXV];      // next row, packed (see the forward kernel)
+    float n_mean = 0.f, n_sc = 0.f;                 // ... and its saved statistics
+    auto fetch = [&](int r) {
+        n_mean = RMS ? 0.f : stat0[r];
+        n_sc = stat1[r];
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int c = threadIdx.x + j * blockDim.x;
+            if (c < nvec) {
+                nx[j] = Vec8<T>::raw_load(x + (size_t)r * cols + c * 8);
+                ng[j] = Vec8<T>::raw_load(g + (size_t)r * cols + c * 8);
+            }
+        }
+    };
+    if (cached && (int)blockIdx.x < rows) fetch(blockIdx.x);
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* xr = x + (size_t)row * cols;
         const T* gr = g + (size_t)row * cols;
         T* dr = dx + (size_t)row * cols;
-        const float mean = RMS ? 0.f : stat0[row];
-        const float sc = stat1[row];
+        float mean, sc;
         float s1 = 0.f, s2 = 0.f;
         float xv[MAXV][8], gv[MAXV][8];
         if (cached) {
+            mean = n_mean;
+            sc = n_sc;
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j) {
+                const int c = threadIdx.x + j * blockDim.x;
+                if (c < nvec) {
+                    Vec8<T>::unpack(nx[j], xv[j]);
+                    Vec8<T>::unpack(ng[j], gv[j]);
+                }
+            }
+            if (row + (int)gridDim.x < rows) fetch(row + gridDim.x);
 #pragma unroll
             for (int j = 0; j < MAXV; ++j) {
                 const int c = threadIdx.x + j * blockDim.x;
                 if (c < nvec) {
                     float gm[8];
-                    Vec8<T>::load(xr + c * 8, xv[j]);
-                    Vec8<T>::load(gr + c * 8, gv[j]);
                     Vec8<T>::load(gamma + c * 8, gm);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -265,6 +333,8 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const T* __restrict__ g, 
                 }
             }
         } else {
+            mean = RMS ? 0.f : stat0[row];
+            sc = stat1[row];
             for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
                 float xt[8], gt[8], gm[8];
                 Vec8<T>::load(xr + c * 8, xt);
