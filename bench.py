@@ -71,6 +71,56 @@ def model_config(n_gpus, layers=None, micro_batch=4, seq=2048, seq_per_gpu=SEQ_P
     }
 
 
+def alt_model_config(name, n_gpus, micro_batch=None, seq_per_gpu=None, layout=None):
+    """The other BASELINE configurations (secondary numbers; the headline stays the 20B shape).
+
+    pythia-1.4b : 24 layers, h 2048, 16 heads, rotary 25 %, parallel residual, GeLU, vocab 50304, seq 2048, micro-batch
+                  8, TP 2 x DP n/2 with sequence parallelism, ZeRO-1 with overlapped communication
+    llama2-7b   : 32 layers, h 4096, 32 heads, full rotary, RMSNorm 1e-5, SwiGLU 11008, no biases, vocab 32000, seq
+                  4096, micro-batch 2, TP 4 x PP 2 at 8 GPUs (TP n at fewer)
+    dmoe-125m   : 12 layers, h 768, 12 heads, 8 GeLU experts (ffn 3072) per layer, top-2, capacity 1.25, aux loss 0.01,
+                  vocab 50304, seq 2048, micro-batch 8, expert parallel = n GPUs
+    """
+    base = model_config(n_gpus, layers=1, layout=(1, 0))
+    for k in ("num_layers", "hidden_size", "num_attention_heads", "seq_length", "max_position_embeddings",
+              "model_parallel_size", "pipe_parallel_size", "train_micro_batch_size_per_gpu", "train_batch_size"):
+        base.pop(k)
+    if name == "pythia-1.4b":
+        tp, pp = layout or ((2, 0) if n_gpus >= 2 else (1, 0))
+        mb = micro_batch or 8
+        spg = seq_per_gpu or 128
+        base.update({"num_layers": 24, "hidden_size": 2048, "num_attention_heads": 16, "seq_length": 2048,
+                     "max_position_embeddings": 2048, "sequence_parallel": tp > 1, "checkpoint_activations": False})
+        base["zero_optimization"] = dict(base["zero_optimization"], overlap_comm=True, reduce_bucket_size=200000000)
+        vocab = 50304
+    elif name == "llama2-7b":
+        tp, pp = layout or {1: (1, 0), 2: (2, 0), 4: (4, 0), 8: (4, 2)}[n_gpus]
+        mb = micro_batch or 2
+        spg = seq_per_gpu or 64
+        L = {1: 4, 2: 8, 4: 16, 8: 32}[n_gpus]
+        base.update({"num_layers": L, "hidden_size": 4096, "num_attention_heads": 32, "seq_length": 4096,
+                     "max_position_embeddings": 4096, "rotary_pct": 1.0, "gpt_j_residual": False, "norm": "rmsnorm",
+                     "rms_norm_epsilon": 1.0e-5, "activation": "swiglu", "intermediate_size": 3 * 11008,
+                     "use_bias_in_mlp": False, "use_bias_in_attn_linear": False, "use_bias_in_norms": False,
+                     "bias_gelu_fusion": False, "checkpoint_activations": True})
+        vocab = 32000
+    elif name == "dmoe-125m":
+        tp, pp = layout or (1, 0)
+        mb = micro_batch or 8
+        spg = seq_per_gpu or 64
+        base.update({"num_layers": 12, "hidden_size": 768, "num_attention_heads": 12, "seq_length": 2048,
+                     "max_position_embeddings": 2048, "gpt_j_residual": False, "moe_num_experts": 8, "moe_top_k": 2,
+                     "expert_interval": 1, "moe_expert_parallel_size": n_gpus, "moe_token_dropping": True,
+                     "moe_train_capacity_factor": 1.25, "moe_loss_coeff": 0.01, "intermediate_size": 3072,
+                     "checkpoint_activations": False})
+        vocab = 50304
+    else:
+        raise ValueError(name)
+    base.update({"model_parallel_size": tp, "pipe_parallel_size": pp, "train_micro_batch_size_per_gpu": mb,
+                 "train_batch_size": spg * n_gpus})
+    return base, vocab, (tp, pp)
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -149,6 +199,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--no-act-ckpt", action="store_true", help="secondary number: activation checkpointing off")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--model", default="neox-20b", choices=["neox-20b", "pythia-1.4b", "llama2-7b", "dmoe-125m"],
+                    help="neox-20b is the headline configuration; the others are the secondary BASELINE configs")
     ap.add_argument("--tp", type=int, default=None, help="override the tensor-parallel degree (debugging)")
     ap.add_argument("--pp", type=int, default=None, help="override the pipeline stages (debugging; 0 = none)")
     a = ap.parse_args()
@@ -173,12 +225,19 @@ def main():
     layout = None
     if a.tp is not None or a.pp is not None:
         layout = (a.tp or PARALLEL[n][0], a.pp if a.pp is not None else PARALLEL[n][1])
-    cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch, seq_per_gpu=a.seq_per_gpu,
-                       ckpt=not a.no_act_ckpt, layout=layout)
+    vocab_size = 50432
+    if a.model == "neox-20b":
+        cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch, seq_per_gpu=a.seq_per_gpu,
+                           ckpt=not a.no_act_ckpt, layout=layout)
+    else:
+        cfg, vocab_size, layout = alt_model_config(a.model, n, None if a.micro_batch == 4 else a.micro_batch,
+                                                   None if a.seq_per_gpu == SEQ_PER_GPU else a.seq_per_gpu, layout)
+        if a.layers:
+            cfg["num_layers"] = a.layers
     neox_args = NeoXArgs.from_dict(cfg)
     neox_args.configure_distributed_args()
     neox_args.build_tokenizer()
-    neox_args.padded_vocab_size = 50432
+    neox_args.padded_vocab_size = vocab_size
     initialize_megatron(neox_args)
     rank = neox_args.rank
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -241,20 +300,23 @@ def main():
     tp, pp = layout or PARALLEL[n]
     if rank == 0:
         out = {
-            "metric": "tokens_per_sec (20B-shape 3D-parallel training; TFLOPS/GPU in tflops_per_gpu)",
+            "metric": ("tokens_per_sec (20B-shape 3D-parallel training; TFLOPS/GPU in tflops_per_gpu)" if a.model == "neox-20b"
+                       else f"tokens_per_sec ({a.model} training; TFLOPS/GPU in tflops_per_gpu)"),
             "value": round(tps, 1), "unit": "tokens/s", "n_gpus": n, "steps": a.steps, "warmup": warm,
             "ms_per_step": round(ms_dev, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights (small_init / wang_init)",
             "tflops_per_gpu": {"model_c3": round(mfu_flops, 1), "hardware_c4": round(hfu_flops, 1),
                                "formula": "24*c*B*s*L*h^2*(1+s/6h+V/16Lh) / (t*gpus)"},
             "vs_paper_a100_tflops_per_gpu": round(hfu_flops / PAPER_TFLOPS_PER_GPU_A100, 2),
-            "config": {"model": f"GPT-NeoX-20B layer shape (h6144, 64 heads, ffn 24576, vocab 50432), "
-                                f"{neox_args.num_layers} of 44 layers" + (" = full model" if neox_args.num_layers == 44 else
-                                                                          " (depth scales with GPUs: 5.5 layers/GPU)"),
+            "config": {"model": (f"GPT-NeoX-20B layer shape (h6144, 64 heads, ffn 24576, vocab 50432), "
+                                 f"{neox_args.num_layers} of 44 layers" + (" = full model" if neox_args.num_layers == 44 else
+                                                                           " (depth scales with GPUs: 5.5 layers/GPU)"))
+                       if a.model == "neox-20b" else f"{a.model} shape, {neox_args.num_layers} layers, h{neox_args.hidden_size}",
                        "global_batch": neox_args.train_batch_size, "seq_len": seq, "micro_batch": mb,
                        "grad_accum": gas, "activation_checkpointing": bool(neox_args.checkpoint_activations),
                        "parallelism": f"tp{tp}" + (f"pp{pp}" if pp else "") + f"dp{world // (tp * max(pp, 1))}"
-                                      + " zero1",
+                                      + (f" ep{neox_args.moe_expert_parallel_size}" if neox_args.moe_num_experts > 1 else "")
+                                      + (" sp" if neox_args.sequence_parallel else "") + " zero1",
                        "l2": "inputs larger than L2 (no flush needed)"},
             "clocks": clocks,
             "e2e": None if ms_e2e is None else {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
@@ -263,7 +325,7 @@ def main():
                                                 "d2h_bytes_per_step": 4, "final_loss": loss},
             # depth (and batch) grow with N, so tokens/s stays flat under perfect weak scaling; this is the same
             # measurement scaled to the 44-layer model: tokens/s * layers / 44, which grows with N
-            "tokens_per_sec_44_layer_equivalent": round(tps * neox_args.num_layers / 44.0, 1),
+            "tokens_per_sec_44_layer_equivalent": round(tps * neox_args.num_layers / 44.0, 1) if a.model == "neox-20b" else None,
             "gpu_launches": launches, "kernel_status": status,
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
