@@ -171,11 +171,12 @@ class ClockSampler:
 
 def reference_arm(args):
     """The unmodified reference needs DeeperSpeed (imported at module scope by deepy.py, training.py and
-    the model files), which is not installable offline; see DESIGN.md for the recorded attempt."""
+    the model files) and is not installable offline: the pip install of the reference tree fails because it is a
+    script tree without setup.py / pyproject.toml, and deepspeed is in no local wheel."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref_dir, "megatron")):
-        why = "baseline/_ref is not installed (pip install of /root/reference was not possible offline)"
+        why = "baseline/_ref is not installed (the offline pip install of the reference tree was not possible)"
     else:
         sys.path.insert(0, ref_dir)
         try:

@@ -128,7 +128,15 @@ def test_preprocess_tool_and_mask(tmp_path):
 def test_tokenizers(tmp_path):
     from types import SimpleNamespace
     from gpt_neox_b200.tokenizer import build_tokenizer
-    ref = "/root/reference/tests/data/hf_cache/tokenizer/gpt2.json"
+    # a small byte-level BPE vocabulary trained on the spot stands in for a downloaded GPT-2 tokenizer file
+    from gpt_neox_b200.tokenizer.train_tokenizer import train_tokenizer
+    corpus = tmp_path / "corpus"
+    corpus.mkdir()
+    with open(corpus / "a.jsonl", "w") as fh:
+        for i in range(300):
+            fh.write(json.dumps({"text": f"Hello, world! The quick brown fox's {i} jumps\n over  lazy dogs."}) + "\n")
+    ref = str(tmp_path / "tok.json")
+    train_tokenizer(str(corpus), ref, vocab_size=600)
     args = SimpleNamespace(tokenizer_type="CharLevelTokenizer", make_vocab_size_divisible_by=128, model_parallel_size=2,
                            rank=0, vocab_file=None, merge_file=None)
     t = build_tokenizer(args)
