@@ -76,6 +76,11 @@ def initialize_megatron(neox_args, allow_no_cuda=False):
     if neox_args.rank == 0:
         print(f"> setting random seeds to {neox_args.seed} ...", flush=True)
     _set_random_seed(seed)
+    # activation-checkpoint storage: sliced over the tensor-parallel group and / or parked in host memory.  Under
+    # sequence parallelism the layer inputs are already per-rank shards, so there is nothing left to partition.
+    from .parallel.rng import configure_checkpointing
+    configure_checkpointing(bool(neox_args.partition_activations) and not bool(neox_args.sequence_parallel),
+                            bool(neox_args.checkpoint_in_cpu))
     # build (local rank 0) and load the native libraries before any training step needs them
     from .ops import build as _build
     if neox_args.local_rank == 0:

@@ -40,6 +40,11 @@ class Embedding(nn.Module):
         else:
             self.tokentype_embeddings = None
         self.embedding_dropout = nn.Dropout(embedding_dropout_prob)
+        # with 8-bit optimizer states the token embeddings are layer-normalised ("stable embedding")
+        self.stable_norm = None
+        if getattr(neox_args, "use_bnb_optimizer", False):
+            from ..optim.adam8bit import StableEmbeddingNorm
+            self.stable_norm = StableEmbeddingNorm(hidden_size, device=dev, dtype=neox_args.params_dtype)
         self.opt_pos_emb_offset = neox_args.opt_pos_emb_offset
         self.layer_past = None
 
@@ -53,6 +58,8 @@ class Embedding(nn.Module):
 
     def forward(self, input_ids, position_ids, tokentype_ids=None):
         emb = self.word_embeddings(input_ids)
+        if self.stable_norm is not None:
+            emb = self.stable_norm(emb)
         if self.embedding_type in ("learned", "sinusoidal"):
             if self.opt_pos_emb_offset:
                 if self.layer_past is not None:

@@ -97,6 +97,53 @@ def model_parallel_cuda_manual_seed(seed: int):
     _TRACKER.add(_MODEL_PARALLEL_RNG, tp_seed)
 
 
+# How checkpointed inputs are kept between forward and backward (reference: the DeepSpeed activation-checkpointing
+# options the reference forwards in ``megatron/initialize.py:89-118``):
+#   partition   -- every tensor-parallel rank keeps only its 1/tp slice of each saved floating-point input and the
+#                  slices are all-gathered over the TP group right before the recomputation (the inputs of a layer are
+#                  replicated across TP ranks, so nothing is lost and activation memory drops by tp);
+#   cpu         -- the kept (slice of the) tensor is parked in pinned host memory and copied back for the recomputation.
+_CKPT_CFG = {"partition": False, "cpu": False}
+
+
+def configure_checkpointing(partition_activations=False, checkpoint_in_cpu=False):
+    _CKPT_CFG["partition"] = bool(partition_activations)
+    _CKPT_CFG["cpu"] = bool(checkpoint_in_cpu)
+
+
+def _stash(t):
+    """(kept tensor, recipe to rebuild the original)."""
+    from . import mpu
+    tp = mpu.get_model_parallel_world_size() if mpu.model_parallel_is_initialized() else 1
+    meta = {"shape": t.shape, "part": False, "cpu": False, "device": t.device, "req": t.requires_grad}
+    keep = t
+    if _CKPT_CFG["partition"] and tp > 1 and t.is_floating_point() and t.numel() % tp == 0 and t.numel() >= tp:
+        r = mpu.get_model_parallel_rank()
+        n = t.numel() // tp
+        keep = t.detach().reshape(-1)[r * n:(r + 1) * n].clone()
+        meta["part"] = True
+    if _CKPT_CFG["cpu"] and keep.is_cuda:
+        host = torch.empty(keep.shape, dtype=keep.dtype, device="cpu", pin_memory=True)
+        host.copy_(keep.detach(), non_blocking=True)
+        keep = host
+        meta["cpu"] = True
+    return keep, meta
+
+
+def _unstash(keep, meta):
+    import torch.distributed as dist
+    from . import mpu
+    t = keep
+    if meta["cpu"]:
+        t = t.to(meta["device"], non_blocking=True)
+    if meta["part"]:
+        tp = mpu.get_model_parallel_world_size()
+        full = torch.empty(t.numel() * tp, dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(full, t.contiguous(), group=mpu.get_model_parallel_group())
+        t = full.view(meta["shape"])
+    return t
+
+
 class _Checkpoint(torch.autograd.Function):
     """Recompute-in-backward with RNG replay (default stream, CUDA stream and tracker states)."""
 
@@ -108,7 +155,14 @@ class _Checkpoint(torch.autograd.Function):
         ctx.tracker_states = _TRACKER.get_states()
         ctx.is_tensor = [torch.is_tensor(a) for a in args]
         ctx.consts = [None if t else a for a, t in zip(args, ctx.is_tensor)]
-        ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
+        tensors = [a for a in args if torch.is_tensor(a)]
+        if _CKPT_CFG["partition"] or _CKPT_CFG["cpu"]:
+            kept = [_stash(t) for t in tensors]
+            ctx.metas = [m for _, m in kept]
+            ctx.save_for_backward(*[k for k, _ in kept])
+        else:
+            ctx.metas = None
+            ctx.save_for_backward(*tensors)
         with torch.no_grad():
             out = fn(*args)
         return out
@@ -116,12 +170,17 @@ class _Checkpoint(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         saved = list(ctx.saved_tensors)
-        args, it = [], iter(saved)
+        if ctx.metas is not None:
+            reqs = [m["req"] for m in ctx.metas]
+            saved = [_unstash(k, m) for k, m in zip(saved, ctx.metas)]
+        else:
+            reqs = [t.requires_grad for t in saved]
+        args, it, rq = [], iter(saved), iter(reqs)
         for is_t, c in zip(ctx.is_tensor, ctx.consts):
             if is_t:
                 t = next(it)
                 d = t.detach()
-                d.requires_grad_(t.requires_grad)
+                d.requires_grad_(next(rq))
                 args.append(d)
             else:
                 args.append(c)

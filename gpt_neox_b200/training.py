@@ -295,9 +295,12 @@ def _inner_optimizer(neox_args):
         if name == "onebitadam":
             from .optim.onebit_adam import OneBitAdam
             return OneBitAdam, dict(weight_decay=neox_args.weight_decay, **params)
-        from .optim.fused_adam import FusedAdam
         params.pop("cuda_aware", None)
         params.pop("momentum", None)
+        if neox_args.use_bnb_optimizer:
+            from .optim.adam8bit import Adam8bit
+            return Adam8bit, dict(weight_decay=neox_args.weight_decay, **params)
+        from .optim.fused_adam import FusedAdam
         return FusedAdam, dict(weight_decay=neox_args.weight_decay, **params)
     if name == "sm3":
         from .optim.sm3 import SM3

@@ -100,3 +100,33 @@ def _tp_model(rank, world, sequence_parallel, gpt_j):
 @pytest.mark.parametrize("sequence_parallel,gpt_j", [(False, True), (True, True), (True, False)])
 def test_tensor_parallel_model_matches_dense(sequence_parallel, gpt_j):
     run_distributed(_tp_model, 2, sequence_parallel, gpt_j)
+
+
+def _partitioned_checkpoint(rank, world, _cfg, _out):
+    """Activation checkpointing with the saved inputs sliced over the TP group (and parked on the host) reproduces
+    plain checkpointing exactly."""
+    import torch
+    from gpt_neox_b200.parallel import mpu, rng
+    mpu.initialize_model_parallel(world)
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(16, 16)
+    x0 = torch.randn(6, 4, 16)            # replicated input, as between transformer layers without sequence parallelism
+
+    def run(partition, cpu):
+        rng.configure_checkpointing(partition, cpu)
+        x = x0.clone().requires_grad_(True)
+        y = rng.checkpoint(lambda t: torch.tanh(lin(t)) * t, x)
+        lin.zero_grad()
+        y.square().sum().backward()
+        return y.detach().clone(), x.grad.clone(), lin.weight.grad.clone()
+
+    base = run(False, False)
+    for mode in ((True, False), (True, True), (False, True)):
+        got = run(*mode)
+        for a, b in zip(base, got):
+            assert torch.allclose(a, b, atol=1e-6), mode
+    rng.configure_checkpointing(False, False)
+
+
+def test_partitioned_activation_checkpointing():
+    run_distributed(_partitioned_checkpoint, 2, None, None)

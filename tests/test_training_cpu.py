@@ -65,6 +65,8 @@ def _loss_decreases(rank, world, cfg, out):
     {"pos_emb": "rpe", "gpt_j_residual": False},
     {"precision": "bfloat16", "zero_optimization": {"stage": 1}},
     {"precision": "fp16", "fp16": {"enabled": True, "loss_scale": 0, "initial_scale_power": 8}},
+    {"use_bnb_optimizer": True},                                             # block-wise 8-bit Adam states + stable embedding
+    {"checkpoint_activations": True, "checkpoint_in_cpu": True},
 ])
 def test_loss_decreases_single_process(cfg):
     run_distributed(_loss_decreases, 1, cfg, None)
