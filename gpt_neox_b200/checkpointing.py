@@ -10,10 +10,9 @@ Layout written under ``<save>/`` (what DeepSpeed's engine writes for the referen
                                                  "global_steps", "global_samples", "skipped_steps", "iteration", + client state}
         layer_{idx:02d}-model_{tp:02d}-model_states.pt   pipeline model: one bare state dict per layer owned by a stage
         zero_pp_rank_{dp}_mp_rank_{tp:02d}_optim_states.pt   one optimizer shard per data-parallel rank
-                                                 (prefix ``bf16_`` for bf16 runs); pipeline runs carry the
-                                                 stage in the model-state file name ``mp_rank_{tp:02d}_model_states.pt``
-                                                 is written per stage-0..P-1 as ``mp_rank_{(pp_stage*tp_size+tp):02d}...`` is
-                                                 NOT used: stage files are the layer files above.
+                                                 (prefix ``bf16_`` for bf16 runs).  Pipeline runs keep the weights
+                                                 only in the per-layer files above; their ``mp_rank_*`` files hold
+                                                 the engine counters and client state.
         configs/*.yml                            verbatim copies of the launch configs
 
 Client state: ``iteration``, a subset of args for consistency checks, five RNG states, optional

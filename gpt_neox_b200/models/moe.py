@@ -124,7 +124,8 @@ class Router(nn.Module):
             noise = torch.empty_like(x).uniform_(1.0 - self.jitter_eps, 1.0 + self.jitter_eps)
             x = x * noise
         logits = self.layer(x)
-        probs = F.softmax(logits.float() if self.fp32 or True else logits, dim=-1)
+        # router probabilities always in fp32 (``moe_lbl_in_fp32`` only matters for the statistics built from them)
+        probs = F.softmax(logits.float(), dim=-1)
         w, idx = torch.topk(probs, self.top_k, dim=-1)
         if self.top_k > 1:
             w = w / w.sum(dim=-1, keepdim=True)

@@ -242,6 +242,108 @@ __global__ void __launch_bounds__(256) ce_bwd_kernel(const T* __restrict__ x, co
     }
 }
 
+// Single-pass (online) statistics for bf16 logits with cols % 8 == 0: one sweep of 16-byte loads keeps a running
+// (max, sum of exp relative to that max) per thread, merged across the CTA at the end.
+//   row_max[row] = max_c x,   stats[row] = (sum_c exp(x - row_max), x[target - v0] (raw) if owned else 0)
+// The caller turns these local quantities into global ones after the tensor-parallel all-reduce of the maxima.
+__global__ void __launch_bounds__(256) ce_online_bf16_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             const long long* __restrict__ target,
+                                                             float* __restrict__ row_max, float* __restrict__ stats,
+                                                             int rows, int cols, int v0) {
+    __shared__ float red_m[8], red_s[8];
+    const int nvec = cols >> 3;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+        float m = -FLT_MAX, s = 0.f;
+        for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+            const uint4 u = __ldg(xr + c);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            float vm = v[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) vm = fmaxf(vm, v[i]);
+            if (vm > m) {
+                s *= __expf(m - vm);
+                m = vm;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s += __expf(v[i] - m);
+        }
+        // merge (m, s) pairs: warp, then CTA
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+            const float nm = fmaxf(m, om);
+            s = s * __expf(m - nm) + os * __expf(om - nm);
+            m = nm;
+        }
+        __syncthreads();
+        if (lane == 0) {
+            red_m[warp] = m;
+            red_s[warp] = s;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float gm = red_m[0], gs = red_s[0];
+            for (int i = 1; i < (int)(blockDim.x >> 5); ++i) {
+                const float nm = fmaxf(gm, red_m[i]);
+                gs = gs * __expf(gm - nm) + red_s[i] * __expf(red_m[i] - nm);
+                gm = nm;
+            }
+            const long long t = target[row] - v0;
+            row_max[row] = gm;
+            stats[2 * row] = gs;
+            stats[2 * row + 1] = (t >= 0 && t < cols) ? __bfloat162float(x[(size_t)row * cols + t]) : 0.f;
+        }
+    }
+}
+
+// Vectorised backward for bf16, cols % 8 == 0 (same math as ce_bwd_kernel).
+__global__ void __launch_bounds__(256) ce_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const long long* __restrict__ target,
+                                                          const float* __restrict__ row_max,
+                                                          const float* __restrict__ stats, const float* __restrict__ g,
+                                                          __nv_bfloat16* __restrict__ grad, int rows, int cols, int v0) {
+    const int nvec = cols >> 3;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+        uint4* gr = reinterpret_cast<uint4*>(grad + (size_t)row * cols);
+        const float m = row_max[row], inv = 1.0f / stats[2 * row], gv = g[row];
+        const long long t = target[row] - v0;
+        for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+            const uint4 u = __ldg(xr + c);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+            float p[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                p[2 * i] = __expf(__uint_as_float(w[i] << 16) - m) * inv;
+                p[2 * i + 1] = __expf(__uint_as_float(w[i] & 0xFFFF0000u) - m) * inv;
+            }
+            const long long d = t - (long long)c * 8;
+            if (d >= 0 && d < 8) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i == (int)d) p[i] -= 1.0f;
+            }
+            uint4 o;
+            uint32_t ow[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p[2 * i] * gv, p[2 * i + 1] * gv);
+                ow[i] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            gr[c] = o;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ optimizers
 template <typename OUT>
 __global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
@@ -367,10 +469,25 @@ int neox_ce_stats(const void* x, const long long* target, const float* row_max, 
                                                                        cols, v0)));
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
+// bf16 only, cols % 8 == 0: local row maximum, sum of exp relative to it, and the raw target logit in one pass.
+int neox_ce_online_bf16(const void* x, const long long* target, float* row_max, float* stats, int rows, int cols,
+                        int v0, void* stream) {
+    if (rows <= 0) return 0;
+    if (cols % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return NEOX_ERR_ALIGN;
+    ce_online_bf16_kernel<<<row_grid(rows), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, target, row_max,
+                                                                            stats, rows, cols, v0);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
 int neox_ce_bwd(const void* x, const long long* target, const float* row_max, const float* stats, const float* g,
                 void* grad, int rows, int cols, int v0, int dtype, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == 0 && cols % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+        !(reinterpret_cast<uintptr_t>(grad) & 15)) {
+        ce_bwd_bf16_kernel<<<row_grid(rows), 256, 0, st>>>((const __nv_bfloat16*)x, target, row_max, stats, g,
+                                                          (__nv_bfloat16*)grad, rows, cols, v0);
+        return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    }
     DISPATCH(dtype, (ce_bwd_kernel<T><<<row_grid(rows), 256, 0, st>>>((const T*)x, target, row_max, stats, g, (T*)grad,
                                                                      rows, cols, v0)));
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;

@@ -61,10 +61,29 @@ class _VocabParallelCE(torch.autograd.Function):
         tgt = target.reshape(-1).contiguous()
         tp = mpu.get_model_parallel_world_size()
         v0 = mpu.get_model_parallel_rank() * vloc
-        row_max = _row_max(logits2)
-        if tp > 1:
-            dist.all_reduce(row_max, op=dist.ReduceOp.MAX, group=mpu.get_model_parallel_group())
-        stats = _row_stats(logits2, tgt, v0, row_max)
+        if _k(logits2) and logits2.dtype == torch.bfloat16 and vloc % 8 == 0 and \
+                native.lib().has("neox_ce_online_bf16"):
+            # one pass over the logits: local (max, sum exp, raw target logit), re-based on the global maximum after
+            # the first all-reduce
+            rows = logits2.shape[0]
+            row_max = torch.empty(rows, dtype=torch.float32, device=logits2.device)
+            stats = torch.empty(rows, 2, dtype=torch.float32, device=logits2.device)
+            rc = native.lib().neox_ce_online_bf16(native.ptr(logits2), native.ptr(tgt), native.ptr(row_max),
+                                                  native.ptr(stats), rows, vloc, v0, _s())
+            native.check(rc, "neox_ce_online_bf16")
+            local_max = row_max
+            if tp > 1:
+                row_max = local_max.clone()
+                dist.all_reduce(row_max, op=dist.ReduceOp.MAX, group=mpu.get_model_parallel_group())
+                stats[:, 0] *= torch.exp(local_max - row_max)
+            local_t = tgt - v0
+            owned = (local_t >= 0) & (local_t < vloc)
+            stats[:, 1] = torch.where(owned, stats[:, 1] - row_max, torch.zeros_like(row_max))
+        else:
+            row_max = _row_max(logits2)
+            if tp > 1:
+                dist.all_reduce(row_max, op=dist.ReduceOp.MAX, group=mpu.get_model_parallel_group())
+            stats = _row_stats(logits2, tgt, v0, row_max)
         if tp > 1:
             dist.all_reduce(stats, group=mpu.get_model_parallel_group())
         loss = torch.log(stats[:, 0]) - stats[:, 1]

@@ -141,6 +141,20 @@ def main():
         print(f"[rank {rank}] device status {st} after layer test", flush=True)
         ok = False
 
+    # ---- vocabulary-parallel cross entropy (single-pass statistics re-based on the global maximum) vs the dense loss
+    from gpt_neox_b200.parallel.cross_entropy import vocab_parallel_cross_entropy
+    V = 1024 * world
+    full_logits = (torch.randn(96, V, device=dev, generator=torch.Generator(device=dev).manual_seed(77)) * 4).to(torch.bfloat16)
+    tgt = torch.randint(0, V, (96,), device=dev, generator=torch.Generator(device=dev).manual_seed(78))
+    shard_l = full_logits[:, rank * 1024:(rank + 1) * 1024].contiguous().requires_grad_(True)
+    loss = vocab_parallel_cross_entropy(shard_l, tgt)
+    loss.sum().backward()
+    ref_l = full_logits.float().requires_grad_(True)
+    ref_loss = torch.nn.functional.cross_entropy(ref_l, tgt, reduction="none")
+    ref_loss.sum().backward()
+    ok &= close(loss, ref_loss, 2e-3, "vocab-parallel CE loss")
+    ok &= close(shard_l.grad, ref_l.grad[:, rank * 1024:(rank + 1) * 1024], 2e-2, "vocab-parallel CE grad")
+
     # ---- bounded wait: nobody publishes this epoch, the gather must give up, report, and leave the context usable
     if os.environ.get("NEOX_TEST_TIMEOUT_PATH", "1") == "1":
         ws.gather(ws.ag_epoch + 1000, rows, K, last_reader=False)
