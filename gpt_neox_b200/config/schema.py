@@ -89,14 +89,15 @@ serve_model_weights : bool = False                 # export CUDA IPC handles of 
 weight_server_port : int|list = 6000               # base port of the weight server
 online_dataserver_ips : str|list = 'localhost'     # hosts of the online data servers
 online_dataserver_ports : int|list = 10000         # ports of the online data servers
-te_columnparallel : bool = False                   # run column-parallel linears in block-scaled fp8
-te_rowparallel : bool = False                      # run row-parallel linears in block-scaled fp8
+te_columnparallel : bool = False                   # run column-parallel linears on the fp8 tensor cores
+te_rowparallel : bool = False                      # run row-parallel linears on the fp8 tensor cores
+te_fp8_recipe : lit[current|delayed|mxfp8] = 'current'   # per-tensor scale from this tensor's amax / from an amax history / 32-element block scales (MXFP8 numerics through the bf16 GEMM)
 te_layernorm_mlp : bool = False                    # fused norm + MLP in fp8
 te_mha : bool = False                              # fused attention block in fp8 mode
 te_fp8_format : lit[e4m3|hybrid] = 'hybrid'        # 'hybrid' = E4M3 forward, E5M2 gradients
 te_fp8_wgrad : bool = True                         # weight gradients in fp8 too
-te_fp8_amax_history_len : int = 1                  # delayed-scaling history (accepted, unused by block scaling)
-te_fp8_amax_compute_algo : str = 'most_recent'     # delayed-scaling amax rule (accepted, unused by block scaling)
+te_fp8_amax_history_len : int = 1                  # delayed-scaling history length
+te_fp8_amax_compute_algo : str = 'most_recent'     # delayed-scaling amax rule: 'max' over the history or 'most_recent'
 te_fp8_margin : int = 0                            # scaling margin
 te_fp8_mha : bool = False                          # fp8 attention
 dim_att : int = None                               # RWKV attention width

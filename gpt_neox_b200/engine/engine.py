@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from ..parallel import mpu
 from ..models.utils import reduce_sequence_parallel_grads
+from ..ops import fp8
 
 _DTYPES = [torch.float32, torch.float16, torch.bfloat16, torch.int64, torch.int32, torch.bool, torch.uint8]
 
@@ -113,6 +114,7 @@ class NeoXEngine:
         if self.store_gradients:
             self.stored_gradients = [p.main_grad.detach().clone() for b in self.optimizer.buckets for p in b.params]
         ok = self.optimizer.step(grad_divisor=float(self.gas * self.dp_world_size))
+        fp8.invalidate_weight_cache()          # the fused optimizer rewrites parameters through raw pointers
         if ok:
             if self.lr_scheduler is not None:
                 self.lr_scheduler.step()
@@ -133,6 +135,7 @@ class NeoXEngine:
     def load_checkpoint(self, load_dir, tag=None, load_optimizer_states=True, load_lr_scheduler_states=True,
                         load_module_only=False, load_module_strict=True):
         from ..checkpointing import engine_load_checkpoint
+        fp8.invalidate_weight_cache()
         return engine_load_checkpoint(self, load_dir, tag, load_optimizer_states, load_lr_scheduler_states,
                                       load_module_only, load_module_strict)
 

@@ -81,6 +81,31 @@ def main():
     run("gemm_wgrad_fc1_fp32_accumulate", lambda: G.gemm(y4, x, a_mn=True, b_mn=True, out=acc, add=acc),
         flops=2.0 * T * h * 4 * h)
 
+    # fp8 tensor cores (per-tensor scaling): the three GEMMs of fc1 and the casts that feed them
+    from . import fp8 as F8
+    if not only or any(n.startswith("fp8_") for n in only):
+        xq, wq, yq = F8.cast(x), F8.cast(w_fc1), F8.cast(y4, e5m2=True)
+        run("fp8_gemm_fwd_fc1", lambda: F8.gemm_fp8(xq, wq), flops=2.0 * T * h * 4 * h)
+        run("fp8_gemm_dgrad_fc1", lambda: F8.gemm_fp8(yq, wq, b_mn=True), flops=2.0 * T * h * 4 * h)
+        run("fp8_gemm_wgrad_fc1_fp32_accumulate", lambda: F8.gemm_fp8(yq, xq, a_mn=True, b_mn=True, out=acc, add=acc),
+            flops=2.0 * T * h * 4 * h)
+        run("fp8_cast_current_T_x_4h", lambda: F8.cast(y4, e5m2=True), nbytes=(2 + 2 + 1.0) * T * 4 * h)
+        lin_x = x.clone().requires_grad_(True)
+        lin_w = torch.nn.Parameter(w_fc1.clone())
+        rec = F8.Fp8Recipe()
+
+        def lin_fp8():
+            F8.fp8_linear(lin_x, lin_w, None, rec).backward(y4)
+            lin_x.grad = lin_w.grad = None
+
+        def lin_bf16():
+            from .linear import linear
+            linear(lin_x, lin_w, None).backward(y4)
+            lin_x.grad = lin_w.grad = None
+
+        run("fp8_linear_fc1_fwd_bwd", lin_fp8, flops=6.0 * T * h * 4 * h)
+        run("fp8_ref_bf16_linear_fc1_fwd_bwd", lin_bf16, flops=6.0 * T * h * 4 * h)
+
     gamma, beta = bf(h), bf(h)
     run("layernorm_fwd", lambda: OF.layer_norm(x, gamma, beta, 1e-5), nbytes=2.0 * T * h * 2)
     xl = x.clone().requires_grad_(True)

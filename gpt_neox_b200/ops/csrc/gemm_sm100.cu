@@ -218,8 +218,9 @@ struct MapKey {
     const void* ptr;
     unsigned long long d0, d1, ld;
     unsigned b0, b1;
+    unsigned esize;
     bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1;
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && esize == o.esize;
     }
 };
 struct MapKeyHash {
@@ -229,6 +230,7 @@ struct MapKeyHash {
         h = h * 1000003u ^ k.d1;
         h = h * 1000003u ^ k.ld;
         h = h * 1000003u ^ (size_t(k.b0) << 16 | k.b1);
+        h = h * 1000003u ^ k.esize;
         return h;
     }
 };
@@ -238,11 +240,11 @@ std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
 }  // namespace
 
-// Build (or fetch from a cache) the 2-D bf16 tensor map of a row-major [d1, d0] view with a row
-// pitch of `ld` elements and a [b1, b0] box, 128-byte swizzled.
-int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
-                           unsigned long long ld, unsigned b0, unsigned b1) {
-    MapKey key{ptr, d0, d1, ld, b0, b1};
+// Build (or fetch from a cache) the 2-D tensor map of a row-major [d1, d0] view of 1-byte (esize 1) or bf16
+// (esize 2) elements with a row pitch of `ld` elements and a [b1, b0] box, 128-byte swizzled.
+static int make_tmap_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                        unsigned long long ld, unsigned b0, unsigned b1, unsigned esize) {
+    MapKey key{ptr, d0, d1, ld, b0, b1, esize};
     {
         std::lock_guard<std::mutex> g(g_map_mu);
         auto it = g_maps.find(key);
@@ -254,17 +256,27 @@ int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return NEOX_ERR_DRIVER;
     cuuint64_t dims[2] = {d0, d1};
-    cuuint64_t strides[1] = {ld * 2};
+    cuuint64_t strides[1] = {ld * esize};
     cuuint32_t box[2] = {b0, b1};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(out, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return NEOX_ERR_TMAP;
     std::lock_guard<std::mutex> g(g_map_mu);
     if (g_maps.size() > 8192) g_maps.clear();
     g_maps.emplace(key, *out);
     return 0;
+}
+
+int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                           unsigned long long ld, unsigned b0, unsigned b1) {
+    return make_tmap_2d(out, ptr, d0, d1, ld, b0, b1, 2);
+}
+
+int neox_make_tmap_u8_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                         unsigned long long ld, unsigned b0, unsigned b1) {
+    return make_tmap_2d(out, ptr, d0, d1, ld, b0, b1, 1);
 }
 
 // 4-D bf16 tensor map over a strided [d3, d2, d1, d0] view (d0 contiguous; strides in elements), box

@@ -20,6 +20,8 @@ int neox_sm_count();
 int neox_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
                            unsigned long long ld, unsigned b0, unsigned b1);
 
+int neox_make_tmap_u8_2d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                         unsigned long long ld, unsigned b0, unsigned b1);
 int neox_make_tmap_bf16_4d(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
                            unsigned long long d2, unsigned long long d3, long long s1, long long s2, long long s3,
                            unsigned b0, unsigned b3);

@@ -140,6 +140,16 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t adesc, ui
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same with 8-bit floating-point operands (E4M3 / E5M2 chosen per operand in the instruction descriptor), K = 32.
+__device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]; A operand read from tensor memory (used for P·V in attention).
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -222,6 +232,19 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_bf16(int M, int N, int a
     d |= 1u << 4;                    // D format fp32
     d |= 1u << 7;                    // A format bf16
     d |= 1u << 10;                   // B format bf16
+    d |= (uint32_t)(a_mn & 1) << 15;
+    d |= (uint32_t)(b_mn & 1) << 16;
+    d |= (uint32_t)(N >> 3) << 17;
+    d |= (uint32_t)(M >> 4) << 24;
+    return d;
+}
+
+// Instruction descriptor for kind::f8f6f4 with fp8 A/B (format 0 = E4M3, 1 = E5M2) and fp32 accumulate.
+__host__ __device__ __forceinline__ uint32_t make_idesc_f8(int M, int N, int a_mn, int b_mn, int a_fmt, int b_fmt) {
+    uint32_t d = 0;
+    d |= 1u << 4;                    // D format fp32
+    d |= (uint32_t)(a_fmt & 7) << 7;
+    d |= (uint32_t)(b_fmt & 7) << 10;
     d |= (uint32_t)(a_mn & 1) << 15;
     d |= (uint32_t)(b_mn & 1) << 16;
     d |= (uint32_t)(N >> 3) << 17;

@@ -28,6 +28,7 @@ from torch.nn.parameter import Parameter
 from ..ops import embedding as fused_embedding
 from ..ops.linear import linear as fused_linear
 from ..ops.mxfp8 import mx_linear
+from ..ops import fp8 as F8
 from . import fused_comm
 from . import mappings as M
 from . import mpu
@@ -149,6 +150,29 @@ class ParallelRelativePositionBias(nn.Module):
         return values.movedim(2, 0).unsqueeze(0) * self.scale     # [1, heads/tp, q, k]
 
 
+def _fp8_setup(layer, neox_args, switch):
+    """Read the ``te_*`` switches (the keys with which the reference swaps in Transformer Engine layers,
+    megatron/model/transformer_engine.py) into ``layer.fp8`` and a per-layer recipe object."""
+    layer.fp8 = bool(getattr(neox_args, switch, False))
+    layer.fp8_hybrid = getattr(neox_args, "te_fp8_format", "hybrid") == "hybrid"
+    layer.fp8_wgrad = bool(getattr(neox_args, "te_fp8_wgrad", True))
+    kind = getattr(neox_args, "te_fp8_recipe", "current") or "current"
+    layer.fp8_block_scaled = kind == "mxfp8"
+    layer.fp8_recipe = F8.Fp8Recipe(
+        recipe=kind if kind != "mxfp8" else "current", hybrid=layer.fp8_hybrid, fp8_wgrad=layer.fp8_wgrad,
+        margin=int(getattr(neox_args, "te_fp8_margin", 0) or 0),
+        history_len=max(1, int(getattr(neox_args, "te_fp8_amax_history_len", 1) or 1)),
+        most_recent=getattr(neox_args, "te_fp8_amax_compute_algo", "most_recent") != "max")
+
+
+def _fp8_matmul(layer, x, bias):
+    n_out, n_in = layer.weight.shape
+    if layer.fp8_block_scaled or not F8.shapes_ok(x.numel() // n_in, n_out, n_in) or \
+            (x.numel() // n_in) % 16 or x.dtype != torch.bfloat16:
+        return mx_linear(x, layer.weight, bias, layer.fp8_hybrid, layer.fp8_wgrad)
+    return F8.fp8_linear(x, layer.weight, bias, layer.fp8_recipe)
+
+
 class ColumnParallelLinear(nn.Module):
     """``Y = X A + b`` with ``A`` split along its output (column) dimension."""
 
@@ -167,10 +191,7 @@ class ColumnParallelLinear(nn.Module):
         self.mup_rescale_parameters = mup_rescale_parameters
         self.use_mup = getattr(neox_args, "use_mup", False)
         self.width_mult_val = 1.0
-        # block-scaled fp8 GEMMs (the switch the reference uses to swap in Transformer Engine layers)
-        self.fp8 = bool(getattr(neox_args, "te_columnparallel", False))
-        self.fp8_hybrid = getattr(neox_args, "te_fp8_format", "hybrid") == "hybrid"
-        self.fp8_wgrad = bool(getattr(neox_args, "te_fp8_wgrad", True))
+        _fp8_setup(self, neox_args, "te_columnparallel")
         dev = _device(neox_args)
         self.weight = Parameter(torch.empty(self.output_size_per_partition, input_size, device=dev,
                                             dtype=neox_args.params_dtype))
@@ -196,7 +217,7 @@ class ColumnParallelLinear(nn.Module):
         if self.fp8:
             x = M.gather_from_sequence_parallel_region(input_, self.seq_dim) if self.sequence_parallel else \
                 M.copy_to_model_parallel_region(input_)
-            out = mx_linear(x, self.weight, bias, self.fp8_hybrid, self.fp8_wgrad)
+            out = _fp8_matmul(self, x, bias)
             if act == "gelu":
                 out = F.gelu(out, approximate="tanh")
             return (out, None) if split_pre else out
@@ -249,9 +270,7 @@ class RowParallelLinear(nn.Module):
         self.init_method, self.stride = init_method, stride
         self.mup_rescale_parameters = mup_rescale_parameters
         self.use_mup = getattr(neox_args, "use_mup", False)
-        self.fp8 = bool(getattr(neox_args, "te_rowparallel", False))
-        self.fp8_hybrid = getattr(neox_args, "te_fp8_format", "hybrid") == "hybrid"
-        self.fp8_wgrad = bool(getattr(neox_args, "te_fp8_wgrad", True))
+        _fp8_setup(self, neox_args, "te_rowparallel")
         dev = _device(neox_args)
         self.weight = Parameter(torch.empty(output_size, self.input_size_per_partition, device=dev,
                                             dtype=neox_args.params_dtype))
@@ -291,7 +310,7 @@ class RowParallelLinear(nn.Module):
             return out, (self.bias if skip else None)
         local = self.tp == 1 or self.parallel_output
         if self.fp8:
-            out = mx_linear(x, self.weight, bias if local else None, self.fp8_hybrid, self.fp8_wgrad)
+            out = _fp8_matmul(self, x, bias if local else None)
             if local and residual is not None:
                 out = out + residual
         else:
@@ -318,7 +337,7 @@ class RowParallelLinear(nn.Module):
             return fused_comm.row_linear(x, self.weight, self.bias, post_residual, self.sequence_parallel,
                                          partial_add=partial_add, bias_partial=True, dgelu_aux=dgelu_aux)
         if self.fp8:
-            out = mx_linear(x, self.weight, self.bias, self.fp8_hybrid, self.fp8_wgrad)
+            out = _fp8_matmul(self, x, self.bias)
             if partial_add is not None:
                 out = out + partial_add
         else:

@@ -405,3 +405,70 @@ def test_mxfp8_linear_fwd_bwd_against_fp32_on_quantised_operands():
     # and the block-scaled result stays close to the unquantised layer
     ref = x.detach().float() @ w.detach().float().t() + b.detach().float()
     assert ((y.float() - ref).abs().mean() / ref.abs().mean()).item() < 0.05
+
+
+# ------------------------------------------------------------------ per-tensor fp8 (fp8 tensor cores)
+@pytest.mark.parametrize("e5m2", [False, True])
+def test_fp8_cast_matches_torch_float8(e5m2):
+    from gpt_neox_b200.ops import fp8 as F8
+    torch.manual_seed(0)
+    x = (torch.randn(203, 176, device=DEV) * torch.logspace(-2, 1, 176, device=DEV)).to(torch.bfloat16)
+    got = F8.cast(x, e5m2, margin=1)
+    want = F8._cast_ref(x, e5m2, 1, None)
+    assert torch.allclose(got.inv, want.inv, rtol=1e-6)
+    assert torch.equal(got.q, want.q)
+    # delayed scaling: the first cast runs at scale 1 and records the amax, the second uses it
+    meta = F8.DelayedMeta(x.device, length=4, e5m2=e5m2)
+    meta.update()
+    first = F8.cast(x, e5m2, meta=meta)
+    assert float(first.inv) == 1.0
+    meta.update()
+    second = F8.cast(x, e5m2, meta=meta)
+    lim = F8.E5M2_MAX if e5m2 else F8.E4M3_MAX
+    assert abs(float(second.inv) - float(x.float().abs().max()) / lim) < 1e-6 * float(second.inv) + 1e-12
+    assert torch.equal(second.q, F8._cast_ref(x, e5m2, 0, None).q)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("a_e5,b_e5", [(False, False), (True, False)])
+def test_fp8_gemm_matches_fp32_on_the_same_fp8_operands(a_mn, b_mn, a_e5, b_e5):
+    from gpt_neox_b200.ops import fp8 as F8
+    from gpt_neox_b200.ops import gemm as G
+    torch.manual_seed(1)
+    M, N, K = 304, 528, 400               # ragged against the 128 x 256 x 128 tile in every dimension
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = (torch.randn((K, N) if b_mn else (N, K), device=DEV) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    aq, bq = F8.cast(a, a_e5), F8.cast(b, b_e5)
+    got = F8.gemm_fp8(aq, bq, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
+    want = F8.gemm_fp8_ref(aq, bq, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
+    _close(got, want, 2e-3, rtol=1e-3)
+    acc = torch.randn(M, N, device=DEV)
+    got2 = F8.gemm_fp8(aq, bq, a_mn, b_mn, out=acc.clone(), add=acc)
+    _close(got2, F8.gemm_fp8_ref(aq, bq, a_mn, b_mn, out_dtype=torch.float32) + acc, 2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("recipe", ["current", "delayed"])
+def test_fp8_linear_fwd_bwd_tracks_the_bf16_layer(recipe):
+    from gpt_neox_b200.ops import fp8 as F8
+    torch.manual_seed(2)
+    x = torch.randn(512, 384, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.nn.Parameter((torch.randn(640, 384, device=DEV) * 0.05).to(torch.bfloat16))
+    b = torch.nn.Parameter(torch.randn(640, device=DEV, dtype=torch.bfloat16))
+    g = torch.randn(512, 640, device=DEV, dtype=torch.bfloat16)
+    rec = F8.Fp8Recipe(recipe=recipe, history_len=4)
+    for _ in range(3 if recipe == "delayed" else 1):     # delayed scaling needs a step to learn its scales
+        x.grad = w.grad = b.grad = None
+        F8.invalidate_weight_cache()                      # what the engine does after an optimizer step
+        y = F8.fp8_linear(x, w, b, rec)
+        y.backward(g)
+    xr, wr = x.detach().float(), w.detach().float()
+    rel = lambda got, want: ((got.float() - want).norm() / want.norm()).item()
+    assert rel(y, xr @ wr.t() + b.detach().float()) < 0.05
+    assert rel(x.grad, g.float() @ wr) < 0.08
+    assert rel(w.grad, g.float().t() @ xr) < 0.08
+    _close(b.grad, g.float().sum(0), 0.5, rtol=2e-2)
+    # exactness against the quantised operands (forward)
+    xq, wq = F8._cast_ref(x.detach(), False, 0, None), F8._cast_ref(w.detach(), False, 0, None)
+    if recipe == "current":
+        _close(y, xq.dequant() @ wq.dequant().t() + b.detach().float(), 3e-2, rtol=1e-2)
