@@ -202,6 +202,8 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--model", default="neox-20b", choices=["neox-20b", "pythia-1.4b", "llama2-7b", "dmoe-125m"],
                     help="neox-20b is the headline configuration; the others are the secondary BASELINE configs")
+    ap.add_argument("--fp8", default=None, choices=["current", "delayed", "mxfp8"],
+                    help="secondary number: linear layers through the te_* fp8 switches with this recipe")
     ap.add_argument("--tp", type=int, default=None, help="override the tensor-parallel degree (debugging)")
     ap.add_argument("--pp", type=int, default=None, help="override the pipeline stages (debugging; 0 = none)")
     a = ap.parse_args()
@@ -235,6 +237,9 @@ def main():
                                                    None if a.seq_per_gpu == SEQ_PER_GPU else a.seq_per_gpu, layout)
         if a.layers:
             cfg["num_layers"] = a.layers
+    if a.fp8:
+        cfg.update({"te_columnparallel": True, "te_rowparallel": True, "te_fp8_recipe": a.fp8,
+                    "te_fp8_amax_history_len": 16, "te_fp8_amax_compute_algo": "max"})
     neox_args = NeoXArgs.from_dict(cfg)
     neox_args.configure_distributed_args()
     neox_args.build_tokenizer()
@@ -305,7 +310,8 @@ def main():
                        else f"tokens_per_sec ({a.model} training; TFLOPS/GPU in tflops_per_gpu)"),
             "value": round(tps, 1), "unit": "tokens/s", "n_gpus": n, "steps": a.steps, "warmup": warm,
             "ms_per_step": round(ms_dev, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights (small_init / wang_init)",
+            "dtype": "bf16" if not a.fp8 else f"fp8 linear layers ({a.fp8} scaling, e4m3 fwd / e5m2 grads), bf16 elsewhere",
+            "data": "synthetic uniform-random token ids, random-init weights (small_init / wang_init)",
             "tflops_per_gpu": {"model_c3": round(mfu_flops, 1), "hardware_c4": round(hfu_flops, 1),
                                "formula": "24*c*B*s*L*h^2*(1+s/6h+V/16Lh) / (t*gpus)"},
             "vs_paper_a100_tflops_per_gpu": round(hfu_flops / PAPER_TFLOPS_PER_GPU_A100, 2),

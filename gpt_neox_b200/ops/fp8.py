@@ -209,30 +209,54 @@ def _cast_weight(weight, recipe: Fp8Recipe):
 
 
 class _Fp8LinearFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, weight, bias, recipe):
-        N, K = weight.shape
-        x2 = x.reshape(-1, K)
-        xq = cast(x2, False, recipe.margin, recipe.meta("x", x.device, False))
-        wq = _cast_weight(weight, recipe)
-        out = gemm_fp8(xq, wq, bias=bias)
-        ctx.save_for_backward(xq.q, xq.inv, wq.q, wq.inv, x2 if not recipe.fp8_wgrad else None)
-        ctx.weight = weight
-        ctx.cfg = (x.shape, recipe, bias is not None)
-        return out.reshape(*x.shape[:-1], N)
+    """``residual``, ``act``, ``dgelu_aux`` and ``split_pre`` mean what they mean in ``ops.linear._LinearFn``: bias,
+    GeLU and residual ride in the forward GEMM's epilogue, and the GeLU backward of an MLP rides in the second
+    linear's dgrad epilogue."""
 
     @staticmethod
-    def backward(ctx, g):
-        xq_q, xq_inv, wq_q, wq_inv, x2 = ctx.saved_tensors
-        x_shape, recipe, has_bias = ctx.cfg
+    def forward(ctx, x, weight, bias, recipe, residual=None, act=None, dgelu_aux=None, split_pre=False):
+        N, K = weight.shape
+        x2 = x.reshape(-1, K)
+        res2 = residual.reshape(-1, N) if residual is not None else None
+        xq = cast(x2, False, recipe.margin, recipe.meta("x", x.device, False))
+        wq = _cast_weight(weight, recipe)
+        need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
+        r = gemm_fp8(xq, wq, bias=bias, add=res2, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE,
+                     want_preact=need_pre)
+        out, pre = r if need_pre else (r, None)
+        aux2 = dgelu_aux.reshape(-1, K) if dgelu_aux is not None else None
+        ctx.save_for_backward(xq.q, xq.inv, wq.q, wq.inv, x2 if not recipe.fp8_wgrad else None,
+                              None if split_pre else pre, aux2)
+        ctx.weight = weight
+        ctx.cfg = (x.shape, recipe, bias is not None, residual is not None, act, split_pre)
+        out = out.reshape(*x.shape[:-1], N)
+        if split_pre:
+            if pre is not None:
+                pre = pre.reshape(*x.shape[:-1], N)
+                ctx.mark_non_differentiable(pre)
+            return out, pre
+        return out
+
+    @staticmethod
+    def backward(ctx, g, g_pre=None):
+        xq_q, xq_inv, wq_q, wq_inv, x2, pre, aux2 = ctx.saved_tensors
+        x_shape, recipe, has_bias, has_res, act, split_pre = ctx.cfg
         weight = ctx.weight
         N, K = weight.shape
+        g_res = g if has_res else None
         g2 = g.reshape(-1, N).contiguous()
+        if act == "gelu" and not split_pre:
+            from .functional import dgelu_mul
+            g2 = dgelu_mul(g2, pre)
         e5 = recipe.hybrid
         gq = cast(g2, e5, recipe.margin, recipe.meta("g", g.device, e5))
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            gx = gemm_fp8(gq, Fp8Tensor(wq_q, wq_inv, False), a_mn=False, b_mn=True).reshape(x_shape)
+            wq = Fp8Tensor(wq_q, wq_inv, False)
+            if aux2 is not None:
+                gx = gemm_fp8(gq, wq, a_mn=False, b_mn=True, act=G.ACT_DGELU, aux=aux2).reshape(x_shape)
+            else:
+                gx = gemm_fp8(gq, wq, a_mn=False, b_mn=True).reshape(x_shape)
         if ctx.needs_input_grad[1]:
             mg = getattr(weight, "main_grad", None)
             if recipe.fp8_wgrad:
@@ -249,9 +273,10 @@ class _Fp8LinearFn(torch.autograd.Function):
                 gw = run()
         if has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
-        return gx, gw, gb, None
+        return gx, gw, gb, None, g_res, None, None, None
 
 
-def fp8_linear(x, weight, bias=None, recipe: Fp8Recipe | None = None):
-    """``x @ weight.T + bias`` with the three GEMMs of the layer on the fp8 tensor cores."""
-    return _Fp8LinearFn.apply(x, weight, bias, recipe or Fp8Recipe())
+def fp8_linear(x, weight, bias=None, recipe: Fp8Recipe | None = None, residual=None, act=None, dgelu_aux=None,
+               split_pre=False):
+    """``act(x @ weight.T + bias) + residual`` with the three GEMMs of the layer on the fp8 tensor cores."""
+    return _Fp8LinearFn.apply(x, weight, bias, recipe or Fp8Recipe(), residual, act, dgelu_aux, split_pre)

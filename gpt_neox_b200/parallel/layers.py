@@ -165,12 +165,37 @@ def _fp8_setup(layer, neox_args, switch):
         most_recent=getattr(neox_args, "te_fp8_amax_compute_algo", "most_recent") != "max")
 
 
-def _fp8_matmul(layer, x, bias):
+class _GeluGradOnInput(torch.autograd.Function):
+    """Identity whose backward multiplies by GeLU'(aux): the contract of ``dgelu_aux`` for a layer that cannot fold
+    it into its dgrad GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, aux):
+        ctx.save_for_backward(aux)
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops.functional import dgelu_mul
+        (aux,) = ctx.saved_tensors
+        return dgelu_mul(g.contiguous(), aux), None
+
+
+def _fp8_matmul(layer, x, bias, residual=None, act=None, dgelu_aux=None, split_pre=False):
+    """``act(x W^T + bias) + residual`` through the layer's fp8 recipe; the epilogue fusions of ``ops.linear`` apply
+    on the tensor-core fp8 path, the block-scaled path composes them from separate ops."""
     n_out, n_in = layer.weight.shape
     if layer.fp8_block_scaled or not F8.shapes_ok(x.numel() // n_in, n_out, n_in) or \
-            (x.numel() // n_in) % 16 or x.dtype != torch.bfloat16:
-        return mx_linear(x, layer.weight, bias, layer.fp8_hybrid, layer.fp8_wgrad)
-    return F8.fp8_linear(x, layer.weight, bias, layer.fp8_recipe)
+            (x.numel() // n_in) % 16 or x.dtype != torch.bfloat16 or (bias is not None and bias.dtype != x.dtype):
+        if dgelu_aux is not None:
+            x = _GeluGradOnInput.apply(x, dgelu_aux)
+        out = mx_linear(x, layer.weight, bias, layer.fp8_hybrid, layer.fp8_wgrad)
+        if act == "gelu":
+            out = F.gelu(out, approximate="tanh")          # autograd owns GeLU': no pre-activation is handed out
+        if residual is not None:
+            out = out + residual
+        return (out, None) if split_pre else out
+    return F8.fp8_linear(x, layer.weight, bias, layer.fp8_recipe, residual, act, dgelu_aux, split_pre)
 
 
 class ColumnParallelLinear(nn.Module):
@@ -217,10 +242,7 @@ class ColumnParallelLinear(nn.Module):
         if self.fp8:
             x = M.gather_from_sequence_parallel_region(input_, self.seq_dim) if self.sequence_parallel else \
                 M.copy_to_model_parallel_region(input_)
-            out = _fp8_matmul(self, x, bias)
-            if act == "gelu":
-                out = F.gelu(out, approximate="tanh")
-            return (out, None) if split_pre else out
+            return _fp8_matmul(self, x, bias, act=act, split_pre=split_pre)
         if self.tp > 1 and self.tp == mpu.get_model_parallel_world_size() and not mpu.get_fp32_allreduce():
             tokens = input_.numel() // K
             rows = tokens if self.sequence_parallel else tokens // self.tp
@@ -310,9 +332,8 @@ class RowParallelLinear(nn.Module):
             return out, (self.bias if skip else None)
         local = self.tp == 1 or self.parallel_output
         if self.fp8:
-            out = _fp8_matmul(self, x, bias if local else None)
-            if local and residual is not None:
-                out = out + residual
+            out = _fp8_matmul(self, x, bias if local else None, residual=residual if local else None,
+                              dgelu_aux=dgelu_aux)
         else:
             out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None,
                                dgelu_aux=dgelu_aux)
@@ -337,9 +358,7 @@ class RowParallelLinear(nn.Module):
             return fused_comm.row_linear(x, self.weight, self.bias, post_residual, self.sequence_parallel,
                                          partial_add=partial_add, bias_partial=True, dgelu_aux=dgelu_aux)
         if self.fp8:
-            out = _fp8_matmul(self, x, self.bias)
-            if partial_add is not None:
-                out = out + partial_add
+            out = _fp8_matmul(self, x, self.bias, residual=partial_add, dgelu_aux=dgelu_aux)
         else:
             out = fused_linear(x, self.weight, self.bias, residual=partial_add, dgelu_aux=dgelu_aux)
         if self.tp > 1:

@@ -19,6 +19,10 @@ from test_training_cpu import _loss_decreases
     {"sliding_window_width": 8},
     # block-scaled fp8 linears (the Transformer-Engine switches of the 1-3B-transformer-engine config)
     {"te_columnparallel": True, "te_rowparallel": True, "te_fp8_format": "hybrid", "precision": "bfloat16"},
+    {"te_columnparallel": True, "te_rowparallel": True, "te_fp8_recipe": "delayed", "te_fp8_amax_history_len": 4,
+     "te_fp8_amax_compute_algo": "max", "precision": "bfloat16"},
+    {"te_columnparallel": True, "te_rowparallel": True, "te_fp8_recipe": "mxfp8", "precision": "bfloat16"},
+    {"te_rowparallel": True, "precision": "bfloat16"},        # bf16 fc1 hands its pre-activation to an fp8 fc2
 ])
 def test_family_trains(cfg):
     run_distributed(_loss_decreases, 1, cfg, None)
