@@ -92,14 +92,14 @@ online_dataserver_ports : int|list = 10000         # ports of the online data se
 te_columnparallel : bool = False                   # run column-parallel linears on the fp8 tensor cores
 te_rowparallel : bool = False                      # run row-parallel linears on the fp8 tensor cores
 te_fp8_recipe : lit[current|delayed|mxfp8] = 'current'   # per-tensor scale from this tensor's amax / from an amax history / 32-element block scales (MXFP8 numerics through the bf16 GEMM)
-te_layernorm_mlp : bool = False                    # fused norm + MLP in fp8
-te_mha : bool = False                              # fused attention block in fp8 mode
+te_layernorm_mlp : bool = False                    # both MLP linears in fp8 (whatever te_columnparallel / te_rowparallel say)
+te_mha : bool = False                              # QKV and output projections of attention in fp8
 te_fp8_format : lit[e4m3|hybrid] = 'hybrid'        # 'hybrid' = E4M3 forward, E5M2 gradients
 te_fp8_wgrad : bool = True                         # weight gradients in fp8 too
 te_fp8_amax_history_len : int = 1                  # delayed-scaling history length
 te_fp8_amax_compute_algo : str = 'most_recent'     # delayed-scaling amax rule: 'max' over the history or 'most_recent'
 te_fp8_margin : int = 0                            # scaling margin
-te_fp8_mha : bool = False                          # fp8 attention
+te_fp8_mha : bool = False                          # accepted; the attention core (QK^T, PV) stays bf16
 dim_att : int = None                               # RWKV attention width
 head_size : int = None                             # RWKV head size
 ffn_dim : int = None                               # RWKV channel-mix width

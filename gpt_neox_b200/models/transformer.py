@@ -64,11 +64,13 @@ class ParallelMLP(nn.Module):
         self.ffn_dim, self.ffn_dim_in = ffn, ffn_in
         self.linear1 = ColumnParallelLinear(neox_args, neox_args.hidden_size, ffn, gather_output=False,
                                             init_method=init_method, skip_bias_add=True, MOE=MOE,
-                                            MoE_mp_size=MoE_mp_size, bias=neox_args.use_bias_in_mlp)
+                                            MoE_mp_size=MoE_mp_size, bias=neox_args.use_bias_in_mlp,
+                                            fp8=not MOE and (neox_args.te_columnparallel or neox_args.te_layernorm_mlp))
         self.linear2 = RowParallelLinear(neox_args, ffn_in, neox_args.hidden_size, input_is_parallel=True,
                                          init_method=output_layer_init_method, parallel_output=parallel_output,
                                          skip_bias_add=True, MOE=MOE, MoE_mp_size=MoE_mp_size,
-                                         bias=neox_args.use_bias_in_mlp)
+                                         bias=neox_args.use_bias_in_mlp,
+                                         fp8=not MOE and (neox_args.te_rowparallel or neox_args.te_layernorm_mlp))
         if not self.is_gated and self.activation_type != "gelu":
             self.act = OF.get_activation(self.activation_type)
 
@@ -184,7 +186,8 @@ class ParallelSelfAttention(nn.Module):
         out_features = neox_args.hidden_size + 2 * self.kv_hidden_size
         self.query_key_value = ColumnParallelLinear(neox_args, neox_args.hidden_size, out_features,
                                                     gather_output=False, init_method=init_method,
-                                                    bias=neox_args.use_bias_in_attn_linear)
+                                                    bias=neox_args.use_bias_in_attn_linear,
+                                                    fp8=neox_args.te_columnparallel or neox_args.te_mha)
 
         coeff = None
         self.norm_factor = math.sqrt(hn)
@@ -227,7 +230,8 @@ class ParallelSelfAttention(nn.Module):
         self.dense = RowParallelLinear(neox_args, neox_args.hidden_size, neox_args.hidden_size,
                                        input_is_parallel=True, init_method=output_layer_init_method,
                                        skip_bias_add=True, parallel_output=parallel_output,
-                                       bias=neox_args.use_bias_in_attn_linear)
+                                       bias=neox_args.use_bias_in_attn_linear,
+                                       fp8=neox_args.te_rowparallel or neox_args.te_mha)
 
     # ------------------------------------------------------------------ projections
     def _project(self, hidden_states):

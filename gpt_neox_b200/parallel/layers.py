@@ -150,10 +150,12 @@ class ParallelRelativePositionBias(nn.Module):
         return values.movedim(2, 0).unsqueeze(0) * self.scale     # [1, heads/tp, q, k]
 
 
-def _fp8_setup(layer, neox_args, switch):
-    """Read the ``te_*`` switches (the keys with which the reference swaps in Transformer Engine layers,
-    megatron/model/transformer_engine.py) into ``layer.fp8`` and a per-layer recipe object."""
-    layer.fp8 = bool(getattr(neox_args, switch, False))
+def _fp8_setup(layer, neox_args, enabled):
+    """``enabled``: whether this layer runs in fp8.  The transformer block decides that from the ``te_*`` switches
+    (the keys with which the reference swaps Transformer Engine layers into attention and MLP,
+    megatron/model/transformer.py:93-140, 395-420); every other user of these classes (output projection, MoE
+    experts, reward head) stays in bf16, as there.  The remaining ``te_fp8_*`` keys fill the per-layer recipe."""
+    layer.fp8 = bool(enabled)
     layer.fp8_hybrid = getattr(neox_args, "te_fp8_format", "hybrid") == "hybrid"
     layer.fp8_wgrad = bool(getattr(neox_args, "te_fp8_wgrad", True))
     kind = getattr(neox_args, "te_fp8_recipe", "current") or "current"
@@ -203,7 +205,7 @@ class ColumnParallelLinear(nn.Module):
 
     def __init__(self, neox_args, input_size, output_size, bias=True, gather_output=True,
                  init_method=init.xavier_normal_, stride=1, keep_master_weight_for_test=False, skip_bias_add=False,
-                 MOE=False, MoE_mp_size=1, mup_rescale_parameters=False, seq_dim=0):
+                 MOE=False, MoE_mp_size=1, mup_rescale_parameters=False, seq_dim=0, fp8=False):
         super().__init__()
         self.input_size, self.output_size, self.gather_output = input_size, output_size, gather_output
         world = MoE_mp_size if MOE else mpu.get_model_parallel_world_size()
@@ -216,7 +218,7 @@ class ColumnParallelLinear(nn.Module):
         self.mup_rescale_parameters = mup_rescale_parameters
         self.use_mup = getattr(neox_args, "use_mup", False)
         self.width_mult_val = 1.0
-        _fp8_setup(self, neox_args, "te_columnparallel")
+        _fp8_setup(self, neox_args, fp8)
         dev = _device(neox_args)
         self.weight = Parameter(torch.empty(self.output_size_per_partition, input_size, device=dev,
                                             dtype=neox_args.params_dtype))
@@ -278,7 +280,7 @@ class RowParallelLinear(nn.Module):
 
     def __init__(self, neox_args, input_size, output_size, bias=True, input_is_parallel=False,
                  init_method=init.xavier_normal_, stride=1, keep_master_weight_for_test=False, skip_bias_add=False,
-                 MOE=False, MoE_mp_size=1, parallel_output=False, mup_rescale_parameters=False):
+                 MOE=False, MoE_mp_size=1, parallel_output=False, mup_rescale_parameters=False, fp8=False):
         super().__init__()
         self.input_size, self.output_size, self.input_is_parallel = input_size, output_size, input_is_parallel
         world = MoE_mp_size if MOE else mpu.get_model_parallel_world_size()
@@ -292,7 +294,7 @@ class RowParallelLinear(nn.Module):
         self.init_method, self.stride = init_method, stride
         self.mup_rescale_parameters = mup_rescale_parameters
         self.use_mup = getattr(neox_args, "use_mup", False)
-        _fp8_setup(self, neox_args, "te_rowparallel")
+        _fp8_setup(self, neox_args, fp8)
         dev = _device(neox_args)
         self.weight = Parameter(torch.empty(output_size, self.input_size_per_partition, device=dev,
                                             dtype=neox_args.params_dtype))
