@@ -81,6 +81,25 @@ def main():
     run("gemm_wgrad_fc1_fp32_accumulate", lambda: G.gemm(y4, x, a_mn=True, b_mn=True, out=acc, add=acc),
         flops=2.0 * T * h * 4 * h)
 
+    # the same five GEMMs through the CTA-pair kernel (cta_group::2)
+    def paired(fn):
+        def run_it():
+            old = G._PAIR
+            G._PAIR = "1"
+            try:
+                return fn()
+            finally:
+                G._PAIR = old
+        return run_it
+
+    run("pair_gemm_fwd_qkv", paired(lambda: G.gemm(x, w_qkv)), flops=2.0 * T * h * 3 * h)
+    run("pair_gemm_fwd_fc1_bias_gelu", paired(lambda: G.gemm(x, w_fc1, bias=bias4, act=G.ACT_GELU, want_preact=True)),
+        flops=2.0 * T * h * 4 * h)
+    run("pair_gemm_fwd_fc2", paired(lambda: G.gemm(y4, w_fc2)), flops=2.0 * T * h * 4 * h)
+    run("pair_gemm_dgrad_fc1", paired(lambda: G.gemm(y4, w_fc1, b_mn=True)), flops=2.0 * T * h * 4 * h)
+    run("pair_gemm_wgrad_fc1_fp32_accumulate", paired(lambda: G.gemm(y4, x, a_mn=True, b_mn=True, out=acc, add=acc)),
+        flops=2.0 * T * h * 4 * h)
+
     # fp8 tensor cores (per-tensor scaling): the three GEMMs of fc1 and the casts that feed them
     from . import fp8 as F8
     if not only or any(n.startswith("fp8_") for n in only):

@@ -125,6 +125,15 @@ gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc_f8(BM, BN, p.a_mn, p.b_mn, x.a_fmt, x.b_fmt);
+            // operand descriptors: constant upper half; lower half = stage base + k-step offset (16-byte units).
+            // K-major: the next 32 elements of K are 32 bytes further along each swizzled 128-byte row.  MN-major:
+            // they are the next 32 rows of 128 bytes; 8-row groups are 1024 bytes apart and 128-element chunks of
+            // the MN dimension MN_CHUNK8 * BK8 bytes apart.
+            const uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), p.a_mn ? MN_CHUNK8 * BK8 : 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), p.b_mn ? MN_CHUNK8 * BK8 : 16);
+            const uint32_t a_step = (p.a_mn ? UMMA_K8 * 128 : UMMA_K8) >> 4;
+            const uint32_t b_step = (p.b_mn ? UMMA_K8 * 128 : UMMA_K8) >> 4;
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
@@ -144,21 +153,12 @@ gemm_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
-                    const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+                    const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK8 / UMMA_K8; ++k) {
-                        // K-major: the next 32 elements of K are 32 bytes further along each swizzled 128-byte row.
-                        // MN-major: they are the next 32 rows of 128 bytes; 8-row groups are 1024 bytes apart and
-                        // 128-element chunks of the MN dimension MN_CHUNK8 * BK8 bytes apart.
-                        const uint64_t adesc =
-                            p.a_mn ? make_smem_desc_sw128(a_base + k * (UMMA_K8 * 128), MN_CHUNK8 * BK8, 1024)
-                                   : make_smem_desc_sw128(a_base + k * UMMA_K8, 16, 1024);
-                        const uint64_t bdesc =
-                            p.b_mn ? make_smem_desc_sw128(b_base + k * (UMMA_K8 * 128), MN_CHUNK8 * BK8, 1024)
-                                   : make_smem_desc_sw128(b_base + k * UMMA_K8, 16, 1024);
-                        umma_f8_ss(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
-                    }
+                    for (int k = 0; k < BK8 / UMMA_K8; ++k)
+                        umma_ss_lohi<false, true>(tmem_d, a_lo + k * a_step, desc_hi, b_lo + k * b_step, desc_hi, idesc,
+                                                  (kb | k) != 0);
                     umma_commit(&empty[stage]);
                     if (++stage == STAGES) {
                         stage = 0;

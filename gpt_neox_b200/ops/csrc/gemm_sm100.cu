@@ -115,6 +115,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+            // operand descriptors: constant upper half; lower half = stage base + k-step offset (16-byte units), so
+            // the issuing thread spends one add per operand per MMA.  K-major: the next 16 elements of K are 32
+            // bytes along the swizzled row; MN-major: the next 16 rows of 128 bytes, with 64-element chunks of the
+            // MN dimension 64 * BK * 2 bytes apart.
+            const uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), p.a_mn ? 64 * BK * 2 : 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), p.b_mn ? 64 * BK * 2 : 16);
+            const uint32_t a_step = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+            const uint32_t b_step = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
@@ -134,16 +143,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
-                    const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+                    const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(a_base + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                                      : make_smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
-                        const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_base + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                                      : make_smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
-                        umma_bf16_ss(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_ss_lohi<false, false>(tmem_d, a_lo + k * a_step, desc_hi, b_lo + k * b_step, desc_hi, idesc,
+                                                   (kb | k) != 0);
                     umma_commit(&empty[stage]);
                     if (++stage == STAGES) {
                         stage = 0;

@@ -145,7 +145,8 @@ def gemm_fp8(a: Fp8Tensor, b: Fp8Tensor, a_mn=False, b_mn=False, out=None, out_d
         assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
     if act == G.ACT_DGELU:
         assert aux is not None and aux.shape == (M, N) and aux.dtype == torch.bfloat16 and aux.stride(1) == 1
-    rc = native.lib().neox_gemm_fp8(
+    L = native.lib()
+    rc = (L.neox_gemm_fp8_2cta if G.use_pair_kernel(M, N, K) else L.neox_gemm_fp8)(
         native.ptr(aq), native.ptr(bq), native.ptr(out), M, N, K,
         ctypes.c_longlong(aq.stride(0)), ctypes.c_longlong(bq.stride(0)), ctypes.c_longlong(out.stride(0)),
         int(a_mn), int(b_mn), int(a.e5m2), int(b.e5m2), native.ptr(a.inv), native.ptr(b.inv),

@@ -56,6 +56,26 @@ def gemm_ref(a, b, a_mn=False, b_mn=False, out_dtype=torch.bfloat16, bias=None, 
     return (v, pre) if want_preact else v
 
 
+_PAIR = None
+
+
+def use_pair_kernel(M, N, K):
+    """The CTA-pair kernel (``csrc/gemm_2cta_sm100.cu``, 256 x 256 tiles on two SMs) pays off once the problem
+    fills the machine with such tiles; small problems keep the one-CTA kernel.  ``NEOX_GEMM_2CTA=0/1`` forces it."""
+    global _PAIR
+    if _PAIR is None:
+        import os
+        _PAIR = os.environ.get("NEOX_GEMM_2CTA", "auto")
+    if _PAIR == "0":
+        return False
+    if _PAIR == "1":
+        return True
+    return PAIR_DEFAULT and ((M + 255) // 256) * ((N + 255) // 256) >= 74 and K >= 256
+
+
+PAIR_DEFAULT = True
+
+
 def gemm_rowmap(a, b, row_ptrs, b_mn=False, bias=None):
     """``a @ op(b) + bias`` whose output row r is stored (bf16) at device address ``row_ptrs[r]`` (int64 tensor of
     M addresses, 16-byte aligned, possibly in other GPUs' peer-mapped memory) instead of into one matrix."""
@@ -105,7 +125,8 @@ def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=
     if act == ACT_DGELU:
         assert aux is not None and aux.shape == (M, N) and aux.dtype == torch.bfloat16 and aux.stride(1) == 1
     L = native.lib()
-    rc = L.neox_gemm_bf16(
+    fn = L.neox_gemm_bf16_2cta if use_pair_kernel(M, N, K) else L.neox_gemm_bf16
+    rc = fn(
         native.ptr(a), native.ptr(b), native.ptr(out), M, N, K,
         ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(out.stride(0)),
         int(a_mn), int(b_mn), int(out.dtype == torch.float32),

@@ -472,3 +472,44 @@ def test_fp8_linear_fwd_bwd_tracks_the_bf16_layer(recipe):
     xq, wq = F8._cast_ref(x.detach(), False, 0, None), F8._cast_ref(w.detach(), False, 0, None)
     if recipe == "current":
         _close(y, xq.dequant() @ wq.dequant().t() + b.detach().float(), 3e-2, rtol=1e-2)
+
+
+# ------------------------------------------------------------------ CTA-pair GEMM (tcgen05 cta_group::2)
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(256, 256, 64, 0, 0), (512, 512, 256, 0, 1), (512, 512, 256, 1, 0),
+                                             (640, 264, 136, 1, 1), (1000, 840, 328, 0, 0), (77, 96, 200, 0, 1),
+                                             (2304, 1536, 512, 0, 0)])
+def test_gemm_cta_pair_kernel_matches_fp32(M, N, K, a_mn, b_mn, monkeypatch):
+    from gpt_neox_b200.ops import gemm as G
+    monkeypatch.setattr(G, "_PAIR", "1")
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    add = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    got = G.gemm(a, b, a_mn, b_mn, bias=bias, add=add, out_dtype=torch.float32)
+    want = G.gemm_ref(a, b, a_mn, b_mn, out_dtype=torch.float32, bias=bias, add=add)
+    _close(got, want, 2e-2 * (K ** 0.5) / 8, rtol=1e-3)
+    got2, pre = G.gemm(a, b, a_mn, b_mn, bias=bias, act=G.ACT_GELU, want_preact=True)
+    want2, wpre = G.gemm_ref(a, b, a_mn, b_mn, bias=bias, act=G.ACT_GELU, want_preact=True)
+    _close(pre, wpre, 0.25, rtol=1e-2)
+    _close(got2, want2, 0.25, rtol=1e-2)
+    from gpt_neox_b200.ops import native
+    assert native.read_status() == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_fp8_gemm_cta_pair_kernel_matches_fp32_on_the_same_fp8_operands(a_mn, b_mn, monkeypatch):
+    from gpt_neox_b200.ops import fp8 as F8
+    from gpt_neox_b200.ops import gemm as G
+    from gpt_neox_b200.ops import native
+    monkeypatch.setattr(G, "_PAIR", "1")
+    torch.manual_seed(1)
+    M, N, K = 560, 528, 400
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = (torch.randn((K, N) if b_mn else (N, K), device=DEV) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    aq, bq = F8.cast(a, True), F8.cast(b, False)
+    got = F8.gemm_fp8(aq, bq, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
+    want = F8.gemm_fp8_ref(aq, bq, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
+    _close(got, want, 2e-3, rtol=1e-3)
+    assert native.read_status() == 0
