@@ -125,6 +125,33 @@ def main():
         run("fp8_linear_fc1_fwd_bwd", lin_fp8, flops=6.0 * T * h * 4 * h)
         run("fp8_ref_bf16_linear_fc1_fwd_bwd", lin_bf16, flops=6.0 * T * h * 4 * h)
 
+    # MXFP8 on the block-scaled tensor cores
+    from . import mxfp8 as MX
+    if not only or any(n.startswith("mx_") for n in only):
+        xm, wm = MX.quantize_tiled(x, False), MX.quantize_tiled(w_fc1, False)
+        ym, wm_r = MX.quantize_tiled(y4, False, True), MX.quantize_tiled(w_fc1, True)
+        ym_r, xm_r = MX.quantize_tiled(y4, True, True), MX.quantize_tiled(x, True)
+        run("mx_gemm_fwd_fc1", lambda: MX.gemm_mx(xm, wm), flops=2.0 * T * h * 4 * h)
+        run("mx_gemm_dgrad_fc1", lambda: MX.gemm_mx(ym, wm_r), flops=2.0 * T * h * 4 * h)
+        run("mx_gemm_wgrad_fc1_fp32_accumulate", lambda: MX.gemm_mx(ym_r, xm_r, out=acc, add=acc),
+            flops=2.0 * T * h * 4 * h)
+        run("mx_quant_T_x_4h_along_cols", lambda: MX.quantize_tiled(y4, False, True), nbytes=(2 + 1.03) * T * 4 * h)
+        run("mx_quant_T_x_4h_along_rows", lambda: MX.quantize_tiled(y4, True, True), nbytes=(2 + 1.03) * T * 4 * h)
+        run("mx_quant_T_x_4h_both_directions_one_pass", lambda: MX.quantize_dual(y4, True), nbytes=(2 + 2.06) * T * 4 * h)
+        run("mx_quant_T_x_4h_one_pass_cols_only", lambda: MX.quantize_dual(y4, True, rows=False),
+            nbytes=(2 + 1.03) * T * 4 * h)
+        mlin_x = x.clone().requires_grad_(True)
+        mlin_w = torch.nn.Parameter(w_fc1.clone())
+
+        def lin_mx(hw):
+            def f():
+                MX.mx_linear(mlin_x, mlin_w, None, hardware=hw).backward(y4)
+                mlin_x.grad = mlin_w.grad = None
+            return f
+
+        run("mx_linear_fc1_fwd_bwd_hardware", lin_mx(True), flops=6.0 * T * h * 4 * h)
+        run("mx_linear_fc1_fwd_bwd_emulated", lin_mx(False), flops=6.0 * T * h * 4 * h)
+
     gamma, beta = bf(h), bf(h)
     run("layernorm_fwd", lambda: OF.layer_norm(x, gamma, beta, 1e-5), nbytes=2.0 * T * h * 2)
     xl = x.clone().requires_grad_(True)

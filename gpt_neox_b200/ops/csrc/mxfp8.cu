@@ -39,15 +39,26 @@ __device__ __forceinline__ float from_fp8(unsigned char q) {
     return __half2float(__half(h));
 }
 
+// Where the scale of (mn, ks) -- mn: index along the non-contracted dimension, ks: 32-element block along the
+// contracted one -- sits in the layout the block-scaled MMA kernel (gemm_mxfp8_sm100.cu) consumes: 512-byte chunks,
+// one per (128 values of mn, 4 values of ks), ordered [ks / 4][mn / 128] with `mnb` chunks per row of chunks; inside
+// a chunk byte (mn % 32) * 16 + ((mn % 128) / 32) * 4 + ks % 4.  A chunk copied to tensor memory as 32 lanes x 16
+// bytes puts the scale of row mn at lane mn % 32, column (mn % 128) / 32, byte ks % 4, which is where the MMA looks.
+__device__ __forceinline__ long long sf_tiled_offset(long long mn, long long ks, long long mnb) {
+    return ((ks >> 2) * mnb + (mn >> 7)) * 512 + (mn & 31) * 16 + ((mn & 127) >> 5) * 4 + (ks & 3);
+}
+
 // One thread per 32-element block.  mode 0: q + scales out; mode 1: dequantised bf16 out (fused q -> dq).
+// tiled_mnb > 0: scales go to the tiled layout above instead of the linear one.
 template <bool E5M2>
 __global__ void __launch_bounds__(256) mx_quant_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q,
                                                        unsigned char* __restrict__ scales, bf16* __restrict__ dq,
-                                                       long long rows, long long cols, int along_rows) {
+                                                       long long rows, long long cols, int along_rows,
+                                                       long long tiled_mnb) {
     const long long nblk = along_rows ? ((rows + 31) / 32) * cols : rows * ((cols + 31) / 32);
     for (long long bi = blockIdx.x * (long long)blockDim.x + threadIdx.x; bi < nblk;
          bi += (long long)gridDim.x * blockDim.x) {
-        long long base, stride;
+        long long base, stride, mn, ks;
         int n;
         if (along_rows) {
             // consecutive threads take consecutive columns of the same 32-row band: coalesced
@@ -55,12 +66,16 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const bf16* __restrict__ 
             base = band * 32 * cols + c;
             stride = cols;
             n = (int)min(32LL, rows - band * 32);
+            mn = c;
+            ks = band;
         } else {
             const long long bpr = (cols + 31) / 32;
             const long long r = bi / bpr, b = bi - r * bpr;
             base = r * cols + b * 32;
             stride = 1;
             n = (int)min(32LL, cols - b * 32);
+            mn = r;
+            ks = b;
         }
         float v[32];
         float amax = 0.f;
@@ -77,7 +92,7 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const bf16* __restrict__ 
             sc = pow2i(e);
             inv = pow2i(-e > 127 ? 127 : -e);
         }
-        if (scales) scales[bi] = (unsigned char)(amax > 0.f ? e + 127 : 0);
+        if (scales) scales[tiled_mnb > 0 ? sf_tiled_offset(mn, ks, tiled_mnb) : bi] = (unsigned char)(amax > 0.f ? e + 127 : 0);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             if (i < n) {
@@ -105,6 +120,101 @@ __global__ void __launch_bounds__(256) mx_dequant_kernel(const unsigned char* __
     }
 }
 
+// Both block directions from ONE read of the tensor.  A warp owns a band of 32 rows x 256 columns; a lane owns 8
+// consecutive columns of it and walks the 32 rows with the raw bf16 vectors kept in registers.
+//   * blocks along a row (32 consecutive columns = 4 adjacent lanes): amax by two shuffles, quantise, store 8 bytes;
+//   * blocks along a column (the lane's 32 rows of each of its 8 columns): amax accumulated over the walk, then the
+//     registers are quantised a second time with the column scales.
+// Either output pair may be NULL.  Scales go to the tiled layout (sf_tiled_offset): mn = row, ks = column block for
+// the row direction; mn = column, ks = row band for the column direction.  cols % 8 == 0.
+template <bool E5M2>
+__global__ void __launch_bounds__(256) mx_quant_dual_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q_c,
+                                                            unsigned char* __restrict__ sf_c, long long mnb_c,
+                                                            unsigned char* __restrict__ q_r,
+                                                            unsigned char* __restrict__ sf_r, long long mnb_r,
+                                                            long long rows, long long cols) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long band = blockIdx.y;
+    const long long col0 = ((long long)blockIdx.x * 8 + warp) * 256 + lane * 8;
+    const long long row0 = band * 32;
+    if (((long long)blockIdx.x * 8 + warp) * 256 >= cols) return;           // warp-uniform
+    const bool col_ok = col0 < cols;
+    const int nrows = (int)min(32LL, rows - row0);
+    const int emax = E5M2 ? 15 : 8;
+
+    uint4 raw[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        raw[r] = make_uint4(0, 0, 0, 0);
+        if (col_ok && r < nrows) raw[r] = __ldg(reinterpret_cast<const uint4*>(x + (row0 + r) * cols + col0));
+    }
+    float cmax[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cmax[j] = 0.f;
+
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
+        float v[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            v[2 * t] = __uint_as_float(w[t] << 16);
+            v[2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+            cmax[2 * t] = fmaxf(cmax[2 * t], fabsf(v[2 * t]));
+            cmax[2 * t + 1] = fmaxf(cmax[2 * t + 1], fabsf(v[2 * t + 1]));
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * t]), fabsf(v[2 * t + 1])));
+        }
+        if (q_c) {                                                            // uniform
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            int e = -127;
+            float inv = 0.f;
+            if (amax > 0.f && amax < 3.0e38f) {
+                e = max(block_exponent(amax, emax), -126);
+                inv = pow2i(-e > 127 ? 127 : -e);
+            }
+            if (col_ok && r < nrows) {
+                uint2 o;
+                o.x = (uint32_t)to_fp8<E5M2>(v[0] * inv) | ((uint32_t)to_fp8<E5M2>(v[1] * inv) << 8) |
+                      ((uint32_t)to_fp8<E5M2>(v[2] * inv) << 16) | ((uint32_t)to_fp8<E5M2>(v[3] * inv) << 24);
+                o.y = (uint32_t)to_fp8<E5M2>(v[4] * inv) | ((uint32_t)to_fp8<E5M2>(v[5] * inv) << 8) |
+                      ((uint32_t)to_fp8<E5M2>(v[6] * inv) << 16) | ((uint32_t)to_fp8<E5M2>(v[7] * inv) << 24);
+                *reinterpret_cast<uint2*>(q_c + (row0 + r) * cols + col0) = o;
+                if ((lane & 3) == 0)
+                    sf_c[sf_tiled_offset(row0 + r, col0 >> 5, mnb_c)] = (unsigned char)(amax > 0.f ? e + 127 : 0);
+            }
+        }
+    }
+    if (q_r && col_ok) {
+        float inv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int e = -127;
+            inv[j] = 0.f;
+            if (cmax[j] > 0.f && cmax[j] < 3.0e38f) {
+                e = max(block_exponent(cmax[j], emax), -126);
+                inv[j] = pow2i(-e > 127 ? 127 : -e);
+            }
+            sf_r[sf_tiled_offset(col0 + j, band, mnb_r)] = (unsigned char)(cmax[j] > 0.f ? e + 127 : 0);
+        }
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            if (r < nrows) {
+                const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
+                uint32_t o[2] = {0, 0};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const uint32_t lo = to_fp8<E5M2>(__uint_as_float(w[t] << 16) * inv[2 * t]);
+                    const uint32_t hi = to_fp8<E5M2>(__uint_as_float(w[t] & 0xFFFF0000u) * inv[2 * t + 1]);
+                    o[t >> 1] |= (lo | (hi << 8)) << ((t & 1) * 16);
+                }
+                *reinterpret_cast<uint2*>(q_r + (row0 + r) * cols + col0) = make_uint2(o[0], o[1]);
+            }
+        }
+    }
+}
+
 int grid_for_blocks(long long n) {
     long long g = (n + 255) / 256;
     const long long cap = 148LL * 16;
@@ -115,8 +225,18 @@ int grid_for_blocks(long long n) {
 
 // x: bf16 [rows, cols] contiguous.  q (bytes, same shape) and scales (one byte per block) may be NULL, dq (bf16, same
 // shape) may be NULL; e5m2 selects the element format.
+extern "C" int neox_mxfp8_quant_tiled(const void* x, void* q, void* scales, void* dq, long long rows, long long cols,
+                                      int along_rows, int e5m2, long long tiled_mnb, void* stream);
+
 extern "C" int neox_mxfp8_quant(const void* x, void* q, void* scales, void* dq, long long rows, long long cols,
                                 int along_rows, int e5m2, void* stream) {
+    return neox_mxfp8_quant_tiled(x, q, scales, dq, rows, cols, along_rows, e5m2, 0, stream);
+}
+
+// tiled_mnb > 0: `scales` is a zero-initialised buffer of ceil(K_blocks / 4) * tiled_mnb * 512 bytes in the tiled
+// layout (see sf_tiled_offset); tiled_mnb >= ceil(MN / 128).
+extern "C" int neox_mxfp8_quant_tiled(const void* x, void* q, void* scales, void* dq, long long rows, long long cols,
+                                      int along_rows, int e5m2, long long tiled_mnb, void* stream) {
     if (rows <= 0 || cols <= 0) return 0;
     const long long nblk = along_rows ? ((rows + 31) / 32) * cols : rows * ((cols + 31) / 32);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -124,12 +244,12 @@ extern "C" int neox_mxfp8_quant(const void* x, void* q, void* scales, void* dq, 
         mx_quant_kernel<true><<<grid_for_blocks(nblk), 256, 0, st>>>(static_cast<const bf16*>(x),
                                                                       static_cast<unsigned char*>(q),
                                                                       static_cast<unsigned char*>(scales),
-                                                                      static_cast<bf16*>(dq), rows, cols, along_rows);
+                                                                      static_cast<bf16*>(dq), rows, cols, along_rows, tiled_mnb);
     else
         mx_quant_kernel<false><<<grid_for_blocks(nblk), 256, 0, st>>>(static_cast<const bf16*>(x),
                                                                        static_cast<unsigned char*>(q),
                                                                        static_cast<unsigned char*>(scales),
-                                                                       static_cast<bf16*>(dq), rows, cols, along_rows);
+                                                                       static_cast<bf16*>(dq), rows, cols, along_rows, tiled_mnb);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
@@ -145,5 +265,31 @@ extern "C" int neox_mxfp8_dequant(const void* q, const void* scales, void* out, 
         mx_dequant_kernel<false><<<grid_for_blocks(rows * cols), 256, 0, st>>>(
             static_cast<const unsigned char*>(q), static_cast<const unsigned char*>(scales), static_cast<bf16*>(out),
             rows, cols, along_rows);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+// Quantise x (bf16 [rows, cols], cols % 8 == 0, 16-byte aligned) in one pass along its columns (q_c, sf_c: blocks of
+// 32 consecutive columns, usable as a K-major operand) and / or along its rows (q_r, sf_r: blocks of 32 consecutive
+// rows, usable as an MN-major operand).  Scale buffers: tiled layout, zero-initialised by the caller, with mnb_c >=
+// ceil(rows / 128) and mnb_r >= ceil(cols / 128) chunks per chunk row.  Either pair may be NULL.
+extern "C" int neox_mxfp8_quant_dual(const void* x, void* q_c, void* sf_c, long long mnb_c, void* q_r, void* sf_r,
+                                     long long mnb_r, long long rows, long long cols, int e5m2, void* stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (cols % 8) return NEOX_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q_c) & 7) ||
+        (reinterpret_cast<uintptr_t>(q_r) & 7))
+        return NEOX_ERR_ALIGN;
+    const dim3 grid((unsigned)((cols + 2047) / 2048), (unsigned)((rows + 31) / 32));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (e5m2)
+        mx_quant_dual_kernel<true><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), static_cast<unsigned char*>(q_c),
+                                                         static_cast<unsigned char*>(sf_c), mnb_c,
+                                                         static_cast<unsigned char*>(q_r),
+                                                         static_cast<unsigned char*>(sf_r), mnb_r, rows, cols);
+    else
+        mx_quant_dual_kernel<false><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), static_cast<unsigned char*>(q_c),
+                                                          static_cast<unsigned char*>(sf_c), mnb_c,
+                                                          static_cast<unsigned char*>(q_r),
+                                                          static_cast<unsigned char*>(sf_r), mnb_r, rows, cols);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }

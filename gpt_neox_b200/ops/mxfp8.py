@@ -97,6 +97,173 @@ def qdq(x, along_rows=False, e5m2=False):
     return out
 
 
+# ------------------------------------------------------------------ hardware path (block-scaled tensor cores)
+class MXTensor:
+    """FP8 bytes plus E8M0 scales in the tiled layout the block-scaled MMA kernel reads (``csrc/mxfp8.cu``,
+    ``sf_tiled_offset``).  ``along_rows`` says which dimension the 32-element blocks run along, i.e. which dimension
+    a GEMM may contract over with this copy."""
+
+    def __init__(self, q, sf, mnb, along_rows, e5m2):
+        self.q, self.sf, self.mnb, self.along_rows, self.e5m2 = q, sf, mnb, along_rows, e5m2
+
+
+def hw_ok(x):
+    return _kernel_ok(x) and native.lib().has("neox_gemm_mxfp8") and x.shape[0] >= 1 and x.shape[1] % 16 == 0
+
+
+def quantize_tiled(x, along_rows=False, e5m2=False) -> MXTensor:
+    assert _kernel_ok(x)
+    x = x.contiguous()
+    rows, cols = x.shape
+    mn, kdim = (cols, rows) if along_rows else (rows, cols)
+    mnb = (mn + 127) // 128 + 1                      # one spare chunk: a 192-wide tile reads one chunk past its last
+    kchunks = ((kdim + 31) // 32 + 3) // 4
+    q = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
+    sf = torch.zeros(kchunks * mnb * 512, dtype=torch.uint8, device=x.device)
+    rc = native.lib().neox_mxfp8_quant_tiled(native.ptr(x), native.ptr(q), native.ptr(sf), None,
+                                             ctypes.c_longlong(rows), ctypes.c_longlong(cols), int(along_rows),
+                                             int(e5m2), ctypes.c_longlong(mnb), ctypes.c_void_p(native.stream_ptr()))
+    native.check(rc, "neox_mxfp8_quant_tiled")
+    return MXTensor(q, sf, mnb, along_rows, e5m2)
+
+
+def quantize_dual(x, e5m2=False, cols=True, rows=True):
+    """One pass over ``x`` (bf16 [R, C], C % 8 == 0) producing the copy blocked along columns and / or the copy
+    blocked along rows: ``(MXTensor | None, MXTensor | None)``."""
+    assert _kernel_ok(x) and x.shape[1] % 8 == 0 and (cols or rows)
+    x = x.contiguous()
+    R, C = x.shape
+    dev = x.device
+    tc = tr = None
+    if cols:
+        mnb = (R + 127) // 128 + 1
+        tc = MXTensor(torch.empty(R, C, dtype=torch.uint8, device=dev),
+                      torch.zeros((((C + 31) // 32 + 3) // 4) * mnb * 512, dtype=torch.uint8, device=dev), mnb, False,
+                      e5m2)
+    if rows:
+        mnb = (C + 127) // 128 + 1
+        tr = MXTensor(torch.empty(R, C, dtype=torch.uint8, device=dev),
+                      torch.zeros((((R + 31) // 32 + 3) // 4) * mnb * 512, dtype=torch.uint8, device=dev), mnb, True,
+                      e5m2)
+    rc = native.lib().neox_mxfp8_quant_dual(
+        native.ptr(x), native.ptr(tc.q) if tc else None, native.ptr(tc.sf) if tc else None,
+        ctypes.c_longlong(tc.mnb if tc else 0), native.ptr(tr.q) if tr else None, native.ptr(tr.sf) if tr else None,
+        ctypes.c_longlong(tr.mnb if tr else 0), ctypes.c_longlong(R), ctypes.c_longlong(C), int(e5m2),
+        ctypes.c_void_p(native.stream_ptr()))
+    native.check(rc, "neox_mxfp8_quant_dual")
+    return tc, tr
+
+
+def gemm_mx(a: MXTensor, b: MXTensor, out=None, out_dtype=torch.bfloat16, bias=None, add=None, act=G.ACT_NONE,
+            aux=None, alpha=1.0, want_preact=False):
+    """``epilogue(alpha * op(a) @ op(b))`` with the block scales applied by the tensor cores.  An operand quantised
+    along its columns is used K-major (``[M, K]`` / ``[N, K]``), one quantised along its rows MN-major
+    (``[K, M]`` / ``[K, N]``): either way the contraction runs along the blocked dimension."""
+    a_mn, b_mn = a.along_rows, b.along_rows
+    K, M = a.q.shape if a_mn else a.q.shape[::-1]
+    Kb, N = b.q.shape if b_mn else b.q.shape[::-1]
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, device=a.q.device, dtype=out_dtype)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    pre = torch.empty(M, N, device=a.q.device, dtype=torch.bfloat16) if want_preact else None
+    rc = native.lib().neox_gemm_mxfp8(
+        native.ptr(a.q), native.ptr(b.q), native.ptr(out), M, N, K,
+        ctypes.c_longlong(a.q.stride(0)), ctypes.c_longlong(b.q.stride(0)), ctypes.c_longlong(out.stride(0)),
+        int(a_mn), int(b_mn), int(a.e5m2), int(b.e5m2), native.ptr(a.sf), ctypes.c_longlong(a.mnb),
+        native.ptr(b.sf), ctypes.c_longlong(b.mnb), int(out.dtype == torch.float32),
+        native.ptr(bias), native.ptr(add), ctypes.c_longlong(add.stride(0) if add is not None else 0),
+        int(add is not None and add.dtype == torch.float32),
+        native.ptr(pre), ctypes.c_longlong(pre.stride(0) if pre is not None else 0),
+        native.ptr(aux), ctypes.c_longlong(aux.stride(0) if aux is not None else 0),
+        int(act), ctypes.c_float(alpha), ctypes.c_void_p(native.stream_ptr()))
+    native.check(rc, "neox_gemm_mxfp8")
+    return (out, pre) if want_preact else out
+
+
+_wcache: dict = {}
+
+
+def _weight_mx(weight, along_rows):
+    """Quantised copies of a parameter live until the optimizer step (``fp8.invalidate_weight_cache``)."""
+    from . import fp8 as F8
+    key = (id(weight), along_rows)
+    tag = (F8._weight_epoch, weight.data_ptr(), weight._version, tuple(weight.shape))
+    hit = _wcache.get(key)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    if len(_wcache) > 8192:
+        _wcache.clear()
+    if weight.shape[1] % 8 == 0:
+        tc, tr = quantize_dual(weight.detach())
+        _wcache[(id(weight), False)] = (tag, tc)
+        _wcache[(id(weight), True)] = (tag, tr)
+        return tr if along_rows else tc
+    t = quantize_tiled(weight.detach(), along_rows)
+    _wcache[key] = (tag, t)
+    return t
+
+
+class _MXLinearHwFn(torch.autograd.Function):
+    """The three GEMMs of a linear layer on the block-scaled tensor cores; same quantisation points as
+    ``_MXLinearFn`` (each operand blocked along the contraction dimension of the GEMM it enters)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, hybrid, fp8_wgrad):
+        N, K = weight.shape
+        x2 = x.reshape(-1, K).contiguous()
+        # the copy blocked along tokens is what the weight-gradient GEMM reads: make it in the same pass and keep
+        # it (fp8 + scales) instead of the bf16 activation
+        keep = fp8_wgrad and torch.is_grad_enabled() and weight.requires_grad
+        xc, xr = quantize_dual(x2, False, cols=True, rows=keep)
+        out = gemm_mx(xc, _weight_mx(weight, False), bias=bias)
+        if keep:
+            ctx.save_for_backward(xr.q, xr.sf)
+            ctx.xr_mnb = xr.mnb
+        else:
+            ctx.save_for_backward(x2)
+        ctx.keep = keep
+        ctx.weight = weight
+        ctx.cfg = (x.shape, hybrid, fp8_wgrad, bias is not None)
+        return out.reshape(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, g):
+        weight = ctx.weight
+        x_shape, hybrid, fp8_wgrad, has_bias = ctx.cfg
+        N, K = weight.shape
+        g2 = g.reshape(-1, N).contiguous()
+        gx = gw = gb = None
+        need_w = ctx.needs_input_grad[1]
+        gc, gr = quantize_dual(g2, hybrid, cols=ctx.needs_input_grad[0], rows=need_w and fp8_wgrad) \
+            if (ctx.needs_input_grad[0] or (need_w and fp8_wgrad)) else (None, None)
+        if ctx.keep:
+            xq, xsf = ctx.saved_tensors
+            xa = MXTensor(xq, xsf, ctx.xr_mnb, True, False)
+            x2 = None
+        else:
+            (x2,) = ctx.saved_tensors
+            xa = quantize_dual(x2, False, cols=False, rows=True)[1] if (need_w and fp8_wgrad) else None
+        if ctx.needs_input_grad[0]:
+            gx = gemm_mx(gc, _weight_mx(weight, True)).reshape(x_shape)
+        if need_w:
+            mg = getattr(weight, "main_grad", None)
+            if fp8_wgrad:
+                run = lambda **kw: gemm_mx(gr, xa, **kw)
+            else:
+                run = lambda **kw: G.gemm(g2, x2, a_mn=True, b_mn=True, **kw)
+            if mg is not None:
+                run(out=mg, add=mg)
+                weight.grad_in_main = True
+                from .linear import notify_grad_ready
+                notify_grad_ready(weight)
+            else:
+                gw = run()
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = g2.sum(0)
+        return gx, gw, gb, None, None
+
+
 class _MXLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, hybrid, fp8_wgrad):
@@ -138,6 +305,20 @@ class _MXLinearFn(torch.autograd.Function):
         return gx, gw, gb, None, None
 
 
-def mx_linear(x, weight, bias=None, hybrid=True, fp8_wgrad=True):
-    """``x @ weight.T + bias`` with all three GEMMs of the layer on MXFP8 operands (see module docstring)."""
+HW_DEFAULT = True
+
+
+def mx_linear(x, weight, bias=None, hybrid=True, fp8_wgrad=True, hardware=None):
+    """``x @ weight.T + bias`` with all three GEMMs of the layer on MXFP8 operands (see module docstring).
+    ``hardware``: run them on the block-scaled tensor cores (``csrc/gemm_mxfp8_sm100.cu``) instead of dequantising
+    into the bf16 GEMM; ``None`` = ``NEOX_MXFP8_HW`` / the module default."""
+    if hardware is None:
+        import os
+        hardware = os.environ.get("NEOX_MXFP8_HW", "1" if HW_DEFAULT else "0") == "1"
+    N, K = weight.shape
+    tokens = x.numel() // K
+    if hardware and x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and K % 16 == 0 and \
+            N % 16 == 0 and tokens % 16 == 0 and native.lib().has("neox_gemm_mxfp8") and \
+            (bias is None or bias.dtype == torch.bfloat16):
+        return _MXLinearHwFn.apply(x, weight, bias, hybrid, fp8_wgrad)
     return _MXLinearFn.apply(x, weight, bias, hybrid, fp8_wgrad)

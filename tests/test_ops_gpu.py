@@ -513,3 +513,62 @@ def test_fp8_gemm_cta_pair_kernel_matches_fp32_on_the_same_fp8_operands(a_mn, b_
     want = F8.gemm_fp8_ref(aq, bq, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
     _close(got, want, 2e-3, rtol=1e-3)
     assert native.read_status() == 0
+
+
+# ------------------------------------------------------------------ MXFP8 on the block-scaled tensor cores
+@pytest.mark.parametrize("a_rows,b_rows", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("mode", ["unit_scales", "row_scales", "k_scales", "random"])
+def test_mxfp8_block_scaled_gemm_matches_dequantised_product(a_rows, b_rows, mode):
+    """forward (K-major, K-major), dgrad (K-major, MN-major) and wgrad (MN-major, MN-major) layouts; the scale
+    patterns isolate the scale plumbing: all scales equal / varying along mn only / along K blocks only / both."""
+    from gpt_neox_b200.ops import mxfp8 as MX
+    from gpt_neox_b200.ops import gemm as G
+    torch.manual_seed(3)
+    M, N, K = 272, 464, 416          # N: three 192-wide tiles (even, odd, ragged); K: ragged against 128
+    def make(mn, k, rows_are_k):
+        base = torch.empty(mn, k, device=DEV).uniform_(1.0, 1.9)
+        sign = torch.where(torch.rand(mn, k, device=DEV) < 0.5, -1.0, 1.0)
+        mn_e = torch.randint(-3, 4, (mn, 1), device=DEV).float()
+        k_e = torch.randint(-3, 4, (1, (k + 31) // 32), device=DEV).float().repeat_interleave(32, dim=1)[:, :k]
+        e = {"unit_scales": 0 * mn_e + 0 * k_e, "row_scales": mn_e + 0 * k_e, "k_scales": 0 * mn_e + k_e,
+             "random": mn_e + k_e}[mode]
+        t = (base * sign * torch.exp2(e)).to(torch.bfloat16)          # [mn, k]
+        return t.t().contiguous() if rows_are_k else t
+    a = make(M, K, a_rows)           # [M, K] or [K, M]
+    b = make(N, K, b_rows)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    got = MX.gemm_mx(MX.quantize_tiled(a, a_rows, False), MX.quantize_tiled(b, b_rows, True), bias=bias,
+                     out_dtype=torch.float32)
+    want = G.gemm_ref(MX.qdq_ref(a, a_rows, False), MX.qdq_ref(b, b_rows, True), a_rows, b_rows,
+                      out_dtype=torch.float32, bias=bias)
+    assert native.read_status() == 0
+    _close(got, want, 1e-2, rtol=2e-3)
+
+
+def test_mxfp8_hardware_linear_matches_the_emulated_layer():
+    from gpt_neox_b200.ops import mxfp8 as MX
+    torch.manual_seed(0)
+    x = torch.randn(256, 192, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(320, 192, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(320, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(256, 320, device=DEV, dtype=torch.bfloat16)
+    outs = []
+    for hw in (False, True):
+        x.grad = w.grad = b.grad = None
+        y = MX.mx_linear(x, w, b, hybrid=True, fp8_wgrad=True, hardware=hw)
+        y.backward(g)
+        outs.append((y.detach().float(), x.grad.float().clone(), w.grad.float().clone()))
+    for e, h in zip(*outs):
+        _close(h, e, 3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("e5m2", [False, True])
+def test_mxfp8_dual_quantise_equals_the_two_single_direction_passes(e5m2):
+    from gpt_neox_b200.ops import mxfp8 as MX
+    torch.manual_seed(5)
+    x = (torch.randn(203, 2184, device=DEV) * torch.logspace(-3, 2, 2184, device=DEV)).to(torch.bfloat16)
+    x[40:80, 64:96] = 0
+    tc, tr = MX.quantize_dual(x, e5m2)
+    sc, sr = MX.quantize_tiled(x, False, e5m2), MX.quantize_tiled(x, True, e5m2)
+    assert torch.equal(tc.q, sc.q) and torch.equal(tc.sf, sc.sf) and tc.mnb == sc.mnb
+    assert torch.equal(tr.q, sr.q) and torch.equal(tr.sf, sr.sf) and tr.mnb == sr.mnb
