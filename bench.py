@@ -4,17 +4,21 @@
     python bench.py --gpus N --steps K --warmup W              (N = 1)
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
 
-Metric: tokens/s over the whole job (and TFLOPS/GPU from the reference FLOPs formula) for the
-layer shape of GPT-NeoX-20B: hidden 6144, 64 heads (head size 96), rotary on 25 % of each head,
+Metric: tokens/s of the 44-layer GPT-NeoX-20B over the whole job (and TFLOPS/GPU from the reference FLOPs formula) for
+the layer shape of GPT-NeoX-20B: hidden 6144, 64 heads (head size 96), rotary on 25 % of each head,
 parallel attention+MLP residual, LayerNorm, GeLU MLP 24576, vocab 50432, sequence 2048, micro-batch 4,
 activation checkpointing on, bf16 parameters with fp32 master weights and Adam (ZeRO-1 layout).
 
 The full 44-layer model needs 8 GPUs (it is ~330 GB of parameter + optimizer state), so the depth
-scales with the GPU count -- 5.5 layers per GPU, as in the 8-GPU run -- and so does the global batch
-(192 sequences per GPU; 1536 at N = 8): work per GPU is constant (weak scaling).
+scales with the GPU count -- 5.5 layers per GPU, as in the 8-GPU run -- while the global batch stays at 192
+sequences: work per GPU and per step is constant (weak scaling), and a step takes about as long at every N.
 
     N = 1: 6 layers            N = 2: 11 layers, TP 2
     N = 4: 22 layers, TP 4     N = 8: 44 layers, TP 4 x PP 2 (1F1B)   <- the named configuration
+
+``value`` is the throughput expressed for the named 44-layer model: measured tokens/s x layers / 44.  At N = 8 that
+is the measured tokens/s itself; at smaller N it is what the same per-layer rate means for the full model, so the
+numbers at different N are comparable (the raw figure is kept in ``tokens_per_sec_at_measured_depth``).
 
 Two timed regions of K optimizer steps each, both through the public API
 (``gpt_neox_b200.training.train_step``):
@@ -39,11 +43,12 @@ sys.path.insert(0, ROOT)
 
 LAYERS = {1: 6, 2: 11, 4: 22, 8: 44}
 PARALLEL = {1: (1, 0), 2: (2, 0), 4: (4, 0), 8: (4, 2)}      # (tensor parallel, pipeline stages)
-SEQ_PER_GPU = 192
+SEQ_PER_GPU = 192          # secondary models: sequences per GPU per step
+GLOBAL_SEQS = 192          # headline: sequences per step at every N
 PAPER_TFLOPS_PER_GPU_A100 = 117.0
 
 
-def model_config(n_gpus, layers=None, micro_batch=4, seq=2048, seq_per_gpu=SEQ_PER_GPU, ckpt=True, layout=None):
+def model_config(n_gpus, layers=None, micro_batch=4, seq=2048, global_seqs=GLOBAL_SEQS, ckpt=True, layout=None):
     tp, pp = layout or PARALLEL[n_gpus]
     L = layers or LAYERS[n_gpus]
     return {
@@ -58,7 +63,7 @@ def model_config(n_gpus, layers=None, micro_batch=4, seq=2048, seq_per_gpu=SEQ_P
         "zero_optimization": {"stage": 1, "allgather_partitions": True, "allgather_bucket_size": 1260000000,
                               "overlap_comm": True, "reduce_scatter": True, "reduce_bucket_size": 1260000000,
                               "contiguous_gradients": True},
-        "train_micro_batch_size_per_gpu": micro_batch, "train_batch_size": seq_per_gpu * n_gpus,
+        "train_micro_batch_size_per_gpu": micro_batch, "train_batch_size": global_seqs,
         "gradient_accumulation_steps": None,
         "checkpoint_activations": ckpt, "checkpoint_num_layers": 1, "partition_activations": False,
         "synchronize_each_layer": True, "gradient_clipping": 1.0, "weight_decay": 0.01, "hidden_dropout": 0,
@@ -196,7 +201,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="override depth (debugging)")
-    ap.add_argument("--seq-per-gpu", type=int, default=SEQ_PER_GPU, help="sequences per GPU per step")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_SEQS, help="sequences per step (headline model)")
+    ap.add_argument("--seq-per-gpu", type=int, default=None,
+                    help="sequences per GPU per step: overrides --global-batch with this x GPUs")
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--no-act-ckpt", action="store_true", help="secondary number: activation checkpointing off")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -230,11 +237,12 @@ def main():
         layout = (a.tp or PARALLEL[n][0], a.pp if a.pp is not None else PARALLEL[n][1])
     vocab_size = 50432
     if a.model == "neox-20b":
-        cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch, seq_per_gpu=a.seq_per_gpu,
+        cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch,
+                           global_seqs=a.seq_per_gpu * n if a.seq_per_gpu else a.global_batch,
                            ckpt=not a.no_act_ckpt, layout=layout)
     else:
         cfg, vocab_size, layout = alt_model_config(a.model, n, None if a.micro_batch == 4 else a.micro_batch,
-                                                   None if a.seq_per_gpu == SEQ_PER_GPU else a.seq_per_gpu, layout)
+                                                   a.seq_per_gpu, layout)
         if a.layers:
             cfg["num_layers"] = a.layers
     if a.fp8:
@@ -301,14 +309,17 @@ def main():
 
     tokens = neox_args.train_batch_size * seq
     tps = tokens / (ms_dev / 1e3)
+    # the headline is quoted for the 44-layer model: a run with fewer layers counts its tokens in that proportion
+    depth = neox_args.num_layers / 44.0 if a.model == "neox-20b" else 1.0
     mfu_flops = flops_per_iteration(neox_args, 3) / (ms_dev / 1e3) / n / 1e12
     hfu_flops = flops_per_iteration(neox_args, 4 if neox_args.checkpoint_activations else 3) / (ms_dev / 1e3) / n / 1e12
     tp, pp = layout or PARALLEL[n]
     if rank == 0:
         out = {
-            "metric": ("tokens_per_sec (20B-shape 3D-parallel training; TFLOPS/GPU in tflops_per_gpu)" if a.model == "neox-20b"
+            "metric": ("tokens_per_sec of the 44-layer GPT-NeoX-20B (3D-parallel training; measured tokens/s x layers/44 "
+                       "where fewer layers fit; TFLOPS/GPU in tflops_per_gpu)" if a.model == "neox-20b"
                        else f"tokens_per_sec ({a.model} training; TFLOPS/GPU in tflops_per_gpu)"),
-            "value": round(tps, 1), "unit": "tokens/s", "n_gpus": n, "steps": a.steps, "warmup": warm,
+            "value": round(tps * depth, 1), "unit": "tokens/s", "n_gpus": n, "steps": a.steps, "warmup": warm,
             "ms_per_step": round(ms_dev, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if not a.fp8 else f"fp8 linear layers ({a.fp8} scaling, e4m3 fwd / e5m2 grads), bf16 elsewhere",
             "data": "synthetic uniform-random token ids, random-init weights (small_init / wang_init)",
@@ -317,7 +328,7 @@ def main():
             "vs_paper_a100_tflops_per_gpu": round(hfu_flops / PAPER_TFLOPS_PER_GPU_A100, 2),
             "config": {"model": (f"GPT-NeoX-20B layer shape (h6144, 64 heads, ffn 24576, vocab 50432), "
                                  f"{neox_args.num_layers} of 44 layers" + (" = full model" if neox_args.num_layers == 44 else
-                                                                           " (depth scales with GPUs: 5.5 layers/GPU)"))
+                                                                           " (depth scales with GPUs: 5.5 layers/GPU; value = measured tokens/s x layers/44)"))
                        if a.model == "neox-20b" else f"{a.model} shape, {neox_args.num_layers} layers, h{neox_args.hidden_size}",
                        "global_batch": neox_args.train_batch_size, "seq_len": seq, "micro_batch": mb,
                        "grad_accum": gas, "activation_checkpointing": bool(neox_args.checkpoint_activations),
@@ -326,13 +337,12 @@ def main():
                                       + (" sp" if neox_args.sequence_parallel else "") + " zero1",
                        "l2": "inputs larger than L2 (no flush needed)"},
             "clocks": clocks,
-            "e2e": None if ms_e2e is None else {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
+            "e2e": None if ms_e2e is None else {"value": round(tokens / (ms_e2e / 1e3) * depth, 1), "unit": "tokens/s",
                                                 "ms_per_step": round(ms_e2e, 2),
                                                 "h2d_bytes_per_step": gas * mb * (seq + 1) * 8,
                                                 "d2h_bytes_per_step": 4, "final_loss": loss},
-            # depth (and batch) grow with N, so tokens/s stays flat under perfect weak scaling; this is the same
-            # measurement scaled to the 44-layer model: tokens/s * layers / 44, which grows with N
-            "tokens_per_sec_44_layer_equivalent": round(tps * neox_args.num_layers / 44.0, 1) if a.model == "neox-20b" else None,
+            # what was actually timed: tokens/s of the model with `num_layers` layers
+            "tokens_per_sec_at_measured_depth": round(tps, 1),
             "gpu_launches": launches, "kernel_status": status,
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
