@@ -43,13 +43,14 @@ struct PairScales {
     const float* inv_scale_a;                         // fp8 only: device scalars multiplied into alpha; NULL = 1
     const float* inv_scale_b;
     int a_fmt, b_fmt;                                 // fp8 only: 0 = E4M3, 1 = E5M2
+    int group_m;                                      // 256-row tile rows per L2 group
 };
 
-__device__ __forceinline__ void tile_coords2(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-    const int per_group = GROUP_M2 * num_n;
+__device__ __forceinline__ void tile_coords2(int tile, int num_m, int num_n, int group_m, int& m_blk, int& n_blk) {
+    const int per_group = group_m * num_n;
     const int group = tile / per_group;
-    const int first_m = group * GROUP_M2;
-    const int gsize = min(num_m - first_m, GROUP_M2);
+    const int first_m = group * group_m;
+    const int gsize = min(num_m - first_m, group_m);
     const int in_group = tile - group * per_group;
     m_blk = first_m + in_group % gsize;
     n_blk = in_group / gsize;
@@ -120,7 +121,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool ok = true;
             for (int tile = pair; tile < ntiles && ok; tile += npairs) {
                 int m_blk, n_blk;
-                tile_coords2(tile, num_m, num_n, m_blk, n_blk);
+                tile_coords2(tile, num_m, num_n, x.group_m, m_blk, n_blk);
                 const int m0 = m_blk * 2 * BM + (int)rank * BM;
                 const int n0 = n_blk * BN + (int)rank * BN_HALF;
                 for (int kb = 0; kb < nk; ++kb) {
@@ -217,7 +218,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t bphase = 0;
         for (int tile = pair; tile < ntiles; tile += npairs) {
             int m_blk, n_blk;
-            tile_coords2(tile, num_m, num_n, m_blk, n_blk);
+            tile_coords2(tile, num_m, num_n, x.group_m, m_blk, n_blk);
             if (!mbar_wait_warp(&tfull[buf], bphase)) {
                 if (lane == 0) atomicExch(p.status, 124);
                 break;
@@ -253,7 +254,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <bool F8>
 int launch_pair(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
-                int a_mn, int b_mn, const PairScales& x, int d_fp32, const void* bias, const void* add, long long ldadd,
+                int a_mn, int b_mn, PairScales x, int d_fp32, const void* bias, const void* add, long long ldadd,
                 int add_fp32, void* preact, long long ldpre, const void* aux, long long ldaux, int act, float alpha,
                 cudaStream_t stream) {
     constexpr int BKE = F8 ? 128 : 64, MNC = F8 ? 128 : 64, PITCH = F8 ? 16 : 8;
@@ -292,6 +293,13 @@ int launch_pair(const void* A, const void* B, void* D, int M, int N, int K, long
     if (aux) vec = vec && al16(aux) && (ldaux % 8 == 0);
     p.vec_ok = vec ? 1 : 0;
 
+    static int group_m = 0;
+    if (!group_m) {
+        const char* e = getenv("NEOX_PAIR_GROUP_M");
+        group_m = e ? atoi(e) : GROUP_M2;
+        if (group_m < 1) group_m = GROUP_M2;
+    }
+    x.group_m = group_m;
     static bool attr_set = false;     // one per instantiation
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_2cta_kernel<F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES) !=
@@ -314,7 +322,7 @@ extern "C" int neox_gemm_bf16_2cta(const void* A, const void* B, void* D, int M,
                                    long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
                                    const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
                                    const void* aux, long long ldaux, int act, float alpha, void* stream_) {
-    return launch_pair<false>(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, PairScales{nullptr, nullptr, 0, 0}, d_fp32,
+    return launch_pair<false>(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, PairScales{nullptr, nullptr, 0, 0, 0}, d_fp32,
                               bias, add, ldadd, add_fp32, preact, ldpre, aux, ldaux, act, alpha,
                               static_cast<cudaStream_t>(stream_));
 }
@@ -327,6 +335,6 @@ extern "C" int neox_gemm_fp8_2cta(const void* A, const void* B, void* D, int M, 
                                   const void* aux, long long ldaux, int act, float alpha, void* stream_) {
     if ((a_fmt | b_fmt) & ~1) return NEOX_ERR_SHAPE;
     return launch_pair<true>(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn,
-                             PairScales{inv_scale_a, inv_scale_b, a_fmt, b_fmt}, d_fp32, bias, add, ldadd, add_fp32,
+                             PairScales{inv_scale_a, inv_scale_b, a_fmt, b_fmt, 0}, d_fp32, bias, add, ldadd, add_fp32,
                              preact, ldpre, aux, ldaux, act, alpha, static_cast<cudaStream_t>(stream_));
 }

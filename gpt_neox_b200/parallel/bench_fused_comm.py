@@ -43,6 +43,34 @@ def timed(fn, iters, flush):
     return t.item()
 
 
+def timed_interleaved(fns, iters, flush):
+    """Median time of every callable in ``fns``, the callables taking turns call by call: all of them see the same
+    clocks and power state (back-to-back loops favour whichever runs first, while the GPU is still cool)."""
+    if _skip:
+        return [float("nan")] * len(fns)
+    for fn in fns:
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+          for _ in fns]
+    for i in range(iters):
+        for k, fn in enumerate(fns):
+            flush.add_(1.0)
+            ev[k][i][0].record()
+            fn()
+            ev[k][i][1].record()
+    torch.cuda.synchronize()
+    out = []
+    for k in range(len(fns)):
+        ts = sorted(s.elapsed_time(e) for s, e in ev[k])
+        t = torch.tensor([ts[len(ts) // 2]], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out.append(t.item())
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--hidden", type=int, default=6144)
@@ -96,9 +124,8 @@ def main():
             ws.release(hd)
             return y
 
-        t_g = timed(lambda: G.gemm(full, w), a.iters, flush)
-        report(name, 2.0 * T * h * n_out, (world - 1) * rows * h * 2, t_g, timed(nccl, a.iters, flush),
-               timed(fused, a.iters, flush))
+        t_g, t_n, t_f = timed_interleaved([lambda: G.gemm(full, w), nccl, fused], a.iters, flush)
+        report(name, 2.0 * T * h * n_out, (world - 1) * rows * h * 2, t_g, t_n, t_f)
 
     # ---- GEMM -> reduce-scatter (row-parallel forward): attention dense and fc2
     for name, k_in in (("gemm_rs_dense", h // world), ("gemm_rs_fc2", 4 * h // world)):
@@ -111,9 +138,9 @@ def main():
             dist.reduce_scatter_tensor(out, y, group=grp)
             return out
 
-        t_g = timed(lambda: G.gemm(x, w), a.iters, flush)
-        report(name, 2.0 * T * h * k_in, (world - 1) * rows * h * 2, t_g, timed(nccl, a.iters, flush),
-               timed(lambda: ws.gemm_reduce(x, w, False), a.iters, flush))
+        t_g, t_n, t_f = timed_interleaved([lambda: G.gemm(x, w), nccl, lambda: ws.gemm_reduce(x, w, False)], a.iters,
+                                          flush)
+        report(name, 2.0 * T * h * k_in, (world - 1) * rows * h * 2, t_g, t_n, t_f)
 
     # ---- GEMM -> all-reduce (row-parallel forward without sequence parallelism)
     select("gemm_ar_fc2")
@@ -124,9 +151,9 @@ def main():
         dist.all_reduce(y, group=grp)
         return y
 
-    t_g = timed(lambda: G.gemm(x, w), a.iters, flush)
-    report("gemm_ar_fc2", 2.0 * T * h * (4 * h // world), 2 * (world - 1) * rows * h * 2, t_g,
-           timed(nccl_ar, a.iters, flush), timed(lambda: ws.gemm_reduce(x, w, False, all_reduce=True), a.iters, flush))
+    t_g, t_n, t_f = timed_interleaved([lambda: G.gemm(x, w), nccl_ar,
+                                       lambda: ws.gemm_reduce(x, w, False, all_reduce=True)], a.iters, flush)
+    report("gemm_ar_fc2", 2.0 * T * h * (4 * h // world), 2 * (world - 1) * rows * h * 2, t_g, t_n, t_f)
 
     # ---- weight gradient with the gathered operand (column-parallel backward)
     select("ag_wgrad_fc1")
