@@ -26,6 +26,7 @@
 // No multicast of any kind is used.
 #include "gemm_common.cuh"
 #include "neox_b200.h"
+#include <stdlib.h>
 #include <string.h>
 
 using namespace gemm;
@@ -38,6 +39,10 @@ constexpr int COPY_WARPS = COMM_THREADS / 32;       // copy CTA: every warp copi
 constexpr int PIECE_BYTES = 32768;
 constexpr int STG_BYTES = 32 * 128;                // one 32-row x 64-column bf16 sub-tile
 constexpr int COMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 8 * STG_BYTES + 256 + 1024;
+// CTA-pair form (cta_group::2, see gemm_2cta_sm100.cu): each CTA stages 128 rows of A and half of the B tile
+constexpr int PSTAGES = 6;
+constexpr int PB_STAGE_BYTES = (BN / 2) * BK * 2;
+constexpr int PAIR_SMEM_BYTES = PSTAGES * (A_STAGE_BYTES + PB_STAGE_BYTES) + 8 * STG_BYTES + 256 + 1024;
 
 struct OutMaps {
     CUtensorMap m[MAX_RANKS];
@@ -171,18 +176,26 @@ __device__ __forceinline__ void pack_partial(const uint32_t (&r)[32], int row, i
     }
 }
 
+// PAIR: launched as (2,1,1) clusters; the two CTAs of a cluster compute one 256 x 256 tile with cta_group::2 MMAs
+// issued by the even CTA (barrier protocol of gemm_2cta_sm100.cu).  Everything a CTA does on its own -- waiting for
+// gathered blocks before loading them, the epilogue of its 128 output rows including the push to the rows' owner,
+// the watcher warp, copy CTAs (which come in pairs too) -- is the same in both forms.
+template <bool PAIR>
 __global__ void __launch_bounds__(COMM_THREADS, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ OutMaps outm, const CommParams cp) {
+    constexpr int NSTG = PAIR ? PSTAGES : STAGES;
+    constexpr int BSTG = PAIR ? PB_STAGE_BYTES : B_STAGE_BYTES;
+    constexpr int TM = PAIR ? 2 * BM : BM;                       // output rows per tile
     const GemmParams& p = cp.g;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
-    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-    uint8_t* sStg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+    uint8_t* sB = smem + NSTG * A_STAGE_BYTES;
+    uint8_t* sStg = smem + NSTG * (A_STAGE_BYTES + BSTG);
     uint64_t* full = reinterpret_cast<uint64_t*>(sStg + 8 * STG_BYTES);
-    uint64_t* empty = full + STAGES;
-    uint64_t* tfull = empty + STAGES;
+    uint64_t* empty = full + NSTG;
+    uint64_t* tfull = empty + NSTG;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* watermark = reinterpret_cast<volatile int*>(tmem_slot + 1);   // gathered blocks complete so far
@@ -191,43 +204,59 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int lane = threadIdx.x & 31;
     const int n_gemm = gridDim.x - cp.n_copy;            // GEMM CTAs come first, copy CTAs last
     const bool copy_cta = (int)blockIdx.x >= n_gemm;
+    const int crank = PAIR ? (int)cluster_ctarank() : 0; // 0 = the CTA that issues the MMAs
+    const int unit = PAIR ? (int)blockIdx.x >> 1 : (int)blockIdx.x;      // tile-processing unit: a CTA or a pair
+    const int n_units = PAIR ? n_gemm >> 1 : n_gemm;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NSTG; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 4);
+            mbar_init(&tempty[b], PAIR ? 8 : 4);
         }
         *watermark = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
     }
+    if (PAIR) cluster_sync_all();                        // both CTAs' barriers exist before anyone signals across
     if (warp == 1 && !copy_cta) {
-        tmem_alloc(tmem_slot, 512);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = copy_cta ? 0u : *tmem_slot;
 
-    const int num_m = (p.M + BM - 1) / BM;
+    const int num_m = (p.M + TM - 1) / TM;
     const int num_n = (p.N + BN - 1) / BN;
     const int ntiles = num_m * num_n;
     const int nk = (p.K + BK - 1) / BK;
     // Rotations: start on the local shard when an operand is being gathered, on the next rank's rows when pushing.
     int m_rot = 0, k_rot = 0;
-    if (cp.a_dep && !p.a_mn) m_rot = (cp.rank * cp.rows_per_shard) / BM;
+    if (cp.a_dep && !p.a_mn) m_rot = (cp.rank * cp.rows_per_shard) / TM;
     if ((cp.a_dep && p.a_mn) || (cp.b_dep && p.b_mn)) k_rot = (cp.rank * cp.rows_per_shard) / BK;
-    if (cp.scatter) m_rot = (((cp.rank + 1) % cp.world) * cp.rows_per_rank) / BM;
+    if (cp.scatter) m_rot = (((cp.rank + 1) % cp.world) * cp.rows_per_rank) / TM;
 
     auto coords = [&](int tile, int& m_blk, int& n_blk) {
-        tile_coords(tile, num_m, num_n, m_blk, n_blk);
-        m_blk = (m_blk + m_rot) % num_m;
+        // groups of 2048 rows of tiles walk across N together (the A panel stays in L2)
+        constexpr int GM = PAIR ? GROUP_M / 2 : GROUP_M;
+        const int per_group = GM * num_n;
+        const int group = tile / per_group;
+        const int first_m = group * GM;
+        const int gsize = min(num_m - first_m, GM);
+        const int in_group = tile - group * per_group;
+        m_blk = (first_m + in_group % gsize + m_rot) % num_m;
+        n_blk = in_group / gsize;
     };
 
     const int dep_total = cp.world * cp.blocks_per_rank;          // gathered blocks, consumed starting at the local shard
@@ -316,62 +345,85 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 asm volatile("fence.proxy.async.global;" ::: "memory");
                 return true;
             };
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += n_gemm) {
+            // one load, counted on this CTA's barrier or (PAIR) on the leader's
+            auto load = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x0, int y0) {
+                if (PAIR) tma_load_2d_pair(dst, m, bar, x0, y0);
+                else tma_load_2d(dst, m, bar, x0, y0);
+            };
+            constexpr int BN_CTA = PAIR ? BN / 2 : BN;    // B columns this CTA stages
+            // Everything the loop needs sits in registers: one thread runs this loop, and at one k-block per ~500
+            // clocks a chain of dependent parameter loads, a modulo and branches per iteration is enough to make
+            // it the limiter of the whole kernel (measured: tensor pipe 78 % busy against 96 % in the plain kernel).
+            const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0, a_dep = cp.a_dep != 0, b_dep = cp.b_dep != 0;
+            const int dep_rows = cp.rows_per_shard * cp.world;
+            const uint32_t tx_bytes = PAIR ? 2 * (A_STAGE_BYTES + PB_STAGE_BYTES) : A_STAGE_BYTES + B_STAGE_BYTES;
+            const bool arm = !PAIR || crank == 0;
+            for (int tile = unit; tile < ntiles && ok; tile += n_units) {
                 int m_blk, n_blk;
                 coords(tile, m_blk, n_blk);
-                for (int kk = 0; kk < nk && ok; ++kk) {
-                    const int kb = (kk + k_rot) % nk;
+                const int m0 = m_blk * TM + crank * BM;   // this CTA's rows of A
+                const int n0 = n_blk * BN + crank * BN_CTA;
+                int kb = k_rot;
+                for (int kk = 0; kk < nk; ++kk) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) {
                         atomicExch(p.status, 101);
                         ok = false;
                         break;
                     }
+                    const int k0 = kb * BK;
                     // y coordinate = row of the operand's 2-D view
-                    const int ay = p.a_mn ? kb * BK : m_blk * BM;
-                    const int by = p.b_mn ? kb * BK : n_blk * BN;
-                    if (cp.a_dep && !block_ready(ay)) { ok = false; break; }
-                    if (cp.b_dep) {
-                        // an N-side K-major tile spans two 128-row blocks
+                    const int ay = a_mn ? k0 : m0;
+                    const int by = b_mn ? k0 : n0;
+                    if (a_dep && !block_ready(ay)) { ok = false; break; }
+                    if (b_dep) {
+                        // an N-side K-major tile of 256 rows spans two 128-row blocks
                         if (!block_ready(by)) { ok = false; break; }
-                        if (!p.b_mn && by + 128 < cp.rows_per_shard * cp.world && !block_ready(by + 128)) {
+                        if (!PAIR && !b_mn && by + 128 < dep_rows && !block_ready(by + 128)) {
                             ok = false;
                             break;
                         }
                     }
-                    mbar_expect_tx(&full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+                    if (arm) mbar_expect_tx(&full[stage], tx_bytes);
                     uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
-                    uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
-                    if (!p.a_mn) {
-                        tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, ay);
+                    uint8_t* b_dst = sB + stage * BSTG;
+                    if (!a_mn) {
+                        load(a_dst, &tmA, &full[stage], k0, ay);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j)
-                            tma_load_2d(a_dst + j * (64 * BK * 2), &tmA, &full[stage], m_blk * BM + j * 64, ay);
+                            load(a_dst + j * (64 * BK * 2), &tmA, &full[stage], m0 + j * 64, ay);
                     }
-                    if (!p.b_mn) {
-                        tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, by);
+                    if (!b_mn) {
+                        load(b_dst, &tmB, &full[stage], k0, by);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(b_dst + j * (64 * BK * 2), &tmB, &full[stage], n_blk * BN + j * 64, by);
+                        for (int j = 0; j < BN_CTA / 64; ++j)
+                            load(b_dst + j * (64 * BK * 2), &tmB, &full[stage], n0 + j * 64, by);
                     }
-                    if (++stage == STAGES) {
+                    if (++stage == NSTG) {
                         stage = 0;
                         phase ^= 1;
                     }
+                    if (++kb == nk) kb = 0;
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+        if (lane == 0 && crank == 0) {
+            const uint32_t idesc = make_idesc_bf16(TM, BN, p.a_mn, p.b_mn);
+            // operand descriptors as in gemm_sm100.cu: constant upper half, one add per operand per MMA
+            const uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), p.a_mn ? 64 * BK * 2 : 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), p.b_mn ? 64 * BK * 2 : 16);
+            const uint32_t a_step = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+            const uint32_t b_step = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
             uint32_t bphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += n_gemm) {
+            for (int tile = unit; tile < ntiles && ok; tile += n_units) {
                 if (!mbar_wait(&tempty[buf], bphase ^ 1)) {
                     atomicExch(p.status, 102);
                     break;
@@ -385,24 +437,22 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
-                    const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+                    const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (BSTG >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(a_base + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                                      : make_smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
-                        const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_base + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                                      : make_smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
-                        umma_bf16_ss(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
-                    }
-                    umma_commit(&empty[stage]);
-                    if (++stage == STAGES) {
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_ss_lohi<PAIR, false>(tmem_d, a_lo + k * a_step, desc_hi, b_lo + k * b_step, desc_hi, idesc,
+                                                  (kb | k) != 0);
+                    if (PAIR) umma_commit_pair(&empty[stage], 3);
+                    else umma_commit(&empty[stage]);
+                    if (++stage == NSTG) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
                 if (!ok) break;
-                umma_commit(&tfull[buf]);
+                if (PAIR) umma_commit_pair(&tfull[buf], 3);
+                else umma_commit(&tfull[buf]);
                 buf ^= 1;
                 if (buf == 0) bphase ^= 1;
             }
@@ -415,15 +465,18 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t freed = 1u << cp.rank;   // bit o: owner o's receive buffer is known to be reusable
         uint8_t* stg = sStg + q * 2 * STG_BYTES;
         int sbuf = 0;
-        for (int tile = blockIdx.x; tile < ntiles; tile += n_gemm) {
+        // PAIR: both CTAs' epilogue warps free an accumulator buffer on the LEADER's barrier
+        const uint32_t tempty_leader0 = PAIR ? cluster_map(smem_u32(&tempty[0]), 0) : 0u;
+        for (int tile = unit; tile < ntiles; tile += n_units) {
             int m_blk, n_blk;
             coords(tile, m_blk, n_blk);
+            const int mrow0 = m_blk * TM + crank * BM;            // first output row of this CTA
             if (!mbar_wait_warp(&tfull[buf], bphase)) {
                 if (lane == 0) atomicExch(p.status, 104);
                 break;
             }
             tc_fence_after();
-            const int row = m_blk * BM + q * 32 + lane;
+            const int row = mrow0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
             if (!cp.scatter) {
 #pragma unroll 1
@@ -436,7 +489,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (row < p.M) epilogue_chunk(r, row, col0, p);
                 }
             } else {
-                const int owner = min((m_blk * BM) / cp.rows_per_rank, cp.world - 1);   // warp-uniform
+                const int owner = min(mrow0 / cp.rows_per_rank, cp.world - 1);   // warp-uniform
                 if (!(freed & (1u << owner))) {
                     int okf = 1;
                     if (lane == 0) okf = wait_flag(cp.free_flags + owner, cp.free_epoch) ? 1 : 0;
@@ -447,7 +500,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     freed |= 1u << owner;
                 }
-                const int lrow0 = m_blk * BM + q * 32 - owner * cp.rows_per_rank;   // first row of this warp in the slot
+                const int lrow0 = mrow0 + q * 32 - owner * cp.rows_per_rank;   // first row of this warp in the slot
 #pragma unroll 1
                 for (int c = 0; c < BN / 64; ++c) {
                     const int col0 = n_blk * BN + c * 64;
@@ -476,7 +529,10 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty[buf]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(tempty_leader0 + buf * 8);
+                else mbar_arrive(&tempty[buf]);
+            }
             buf ^= 1;
             if (buf == 0) bphase ^= 1;
         }
@@ -522,9 +578,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     tc_fence_before();
     __syncthreads();
+    // PAIR: no CTA leaves, or frees tensor memory, while its partner may still signal it or run MMAs into it
+    if (PAIR) cluster_sync_all();
     if (warp == 1 && !copy_cta) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
     }
     if (threadIdx.x == 0 && (cp.sig_offset >= 0 || cp.sig2_offset >= 0))
         grid_done_signal(cp.counter, cp.peer_pad, cp.world, cp.rank, cp.sig_offset, cp.sig_value, cp.sig2_offset,
@@ -808,7 +867,14 @@ extern "C" int neox_comm_gemm(const void* A, const void* B, void* D, int M, int 
     if (!a_mn) rc = neox_make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
     else rc = neox_make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
     if (rc) return rc;
-    if (!b_mn) rc = neox_make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, BN);
+    static int use_pair = -1;
+    if (use_pair < 0) {
+        const char* e = getenv("NEOX_COMM_GEMM_2CTA");
+        use_pair = (e && e[0] == '0') ? 0 : 1;
+    }
+    // the pair form wants at least one 256 x 256 tile per pair of SMs' worth of work; tiny problems keep one CTA
+    const bool pair = use_pair && (long long)((M + 255) / 256) * ((N + BN - 1) / BN) >= 8;
+    if (!b_mn) rc = neox_make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, pair ? BN / 2 : BN);
     else rc = neox_make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
     if (rc) return rc;
     OutMaps outm;
@@ -867,25 +933,45 @@ extern "C" int neox_comm_gemm(const void* A, const void* B, void* D, int M, int 
         for (int r = 0; r < world; ++r) cp.peer_pad[r] = reinterpret_cast<uint32_t*>(pad_ptrs[r]);
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(comm_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, COMM_SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(comm_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 COMM_SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(comm_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PAIR_SMEM_BYTES) != cudaSuccess)
             return NEOX_ERR_LAUNCH;
         attr_set = true;
     }
-    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
-    int grid = num_m * num_n;
+    const int tile_m = pair ? 2 * BM : BM;
+    const int num_m = (M + tile_m - 1) / tile_m, num_n = (N + BN - 1) / BN;
     const int sms = neox_sm_count();
-    if (grid > sms) grid = sms;
+    const int per_tile = pair ? 2 : 1;                  // CTAs per tile-processing unit
+    int grid = num_m * num_n * per_tile;
+    if (grid > sms) grid = sms / per_tile * per_tile;
     if (bcast) {
         // the last n_copy CTAs of the grid copy instead of computing; all CTAs must be co-resident (one per SM)
         if (n_copy < 1) n_copy = 8;
         if (n_copy > sms / 2) n_copy = sms / 2;
-        if (grid + n_copy > sms) grid = sms - n_copy;
+        if (pair) n_copy = (n_copy + 1) & ~1;           // copy CTAs come in pairs too
+        if (grid + n_copy > sms) grid = (sms - n_copy) / per_tile * per_tile;
         cp.n_copy = n_copy;
         grid += n_copy;
     }
-    comm_gemm_kernel<<<grid, COMM_THREADS, COMM_SMEM_BYTES, stream>>>(tmA, tmB, outm, cp);
-    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    if (!pair) {
+        comm_gemm_kernel<false><<<grid, COMM_THREADS, COMM_SMEM_BYTES, stream>>>(tmA, tmB, outm, cp);
+        return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(COMM_THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, comm_gemm_kernel<true>, tmA, tmB, outm, cp) == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
 // Reduce the receive buffer of a scattered GEMM.  gathered_ptrs != NULL selects all-reduce mode (see the kernel).
