@@ -98,7 +98,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
                 }
             }
         }
-        if (p.add) {
+        // fp32 accumulate into the output itself (weight gradients into the main-gradient buffer): every element is
+        // owned by one thread, so a vector reduction at the L2 does the read-modify-write and the SM never waits
+        // for the old value
+        const bool inplace = p.d_fp32 && p.add_fp32 && p.add == p.D && p.ldadd == p.ldd;
+        if (p.add && !inplace) {
             if (p.add_fp32) {
                 const float4* a4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.add) +
                                                                    (long long)row * p.ldadd + col0);
@@ -127,8 +131,13 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
         }
         if (p.d_fp32) {
             float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0);
+            if (inplace) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+                for (int j = 0; j < 8; ++j) atomicAdd(o + j, make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            }
         } else {
             __nv_bfloat16* drow = p.row_ptrs ? reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row])
                                              : reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd;
