@@ -48,6 +48,12 @@ __device__ __forceinline__ long long sf_tiled_offset(long long mn, long long ks,
     return ((ks >> 2) * mnb + (mn >> 7)) * 512 + (mn & 31) * 16 + ((mn & 127) >> 5) * 4 + (ks & 3);
 }
 
+// Two values -> two fp8 bytes in one conversion instruction (low byte = first value).
+template <bool E5M2>
+__device__ __forceinline__ uint32_t to_fp8x2(float a, float b) {
+    return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
+}
+
 // One thread per 32-element block.  mode 0: q + scales out; mode 1: dequantised bf16 out (fused q -> dq).
 // tiled_mnb > 0: scales go to the tiled layout above instead of the linear one.
 template <bool E5M2>
@@ -120,54 +126,56 @@ __global__ void __launch_bounds__(256) mx_dequant_kernel(const unsigned char* __
     }
 }
 
-// Both block directions from ONE read of the tensor.  A warp owns a band of 32 rows x 256 columns; a lane owns 8
-// consecutive columns of it and walks the 32 rows with the raw bf16 vectors kept in registers.
-//   * blocks along a row (32 consecutive columns = 4 adjacent lanes): amax by two shuffles, quantise, store 8 bytes;
-//   * blocks along a column (the lane's 32 rows of each of its 8 columns): amax accumulated over the walk, then the
+// Both block directions from ONE read of the tensor.  A warp owns a band of 32 rows x 128 columns; a lane owns 4
+// consecutive columns of it and walks the 32 rows with the raw bf16 pairs kept in registers (64 registers, so two
+// CTAs fit on an SM and one CTA's loads overlap the other's conversions).
+//   * blocks along a row (32 consecutive columns = 8 adjacent lanes): amax by three shuffles, quantise, store 4 bytes;
+//   * blocks along a column (the lane's 32 rows of each of its 4 columns): amax accumulated over the walk, then the
 //     registers are quantised a second time with the column scales.
 // Either output pair may be NULL.  Scales go to the tiled layout (sf_tiled_offset): mn = row, ks = column block for
 // the row direction; mn = column, ks = row band for the column direction.  cols % 8 == 0.
 template <bool E5M2>
-__global__ void __launch_bounds__(256) mx_quant_dual_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q_c,
-                                                            unsigned char* __restrict__ sf_c, long long mnb_c,
-                                                            unsigned char* __restrict__ q_r,
-                                                            unsigned char* __restrict__ sf_r, long long mnb_r,
-                                                            long long rows, long long cols) {
+__global__ void __launch_bounds__(256, 2) mx_quant_dual_kernel(const bf16* __restrict__ x,
+                                                               unsigned char* __restrict__ q_c,
+                                                               unsigned char* __restrict__ sf_c, long long mnb_c,
+                                                               unsigned char* __restrict__ q_r,
+                                                               unsigned char* __restrict__ sf_r, long long mnb_r,
+                                                               long long rows, long long cols) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long band = blockIdx.y;
-    const long long col0 = ((long long)blockIdx.x * 8 + warp) * 256 + lane * 8;
+    const long long wcol0 = ((long long)blockIdx.x * 8 + warp) * 128;
+    if (wcol0 >= cols) return;                                               // warp-uniform
+    const long long col0 = wcol0 + lane * 4;
     const long long row0 = band * 32;
-    if (((long long)blockIdx.x * 8 + warp) * 256 >= cols) return;           // warp-uniform
-    const bool col_ok = col0 < cols;
+    const bool col_ok = col0 < cols;                                         // cols % 4 == 0: all four or none
     const int nrows = (int)min(32LL, rows - row0);
     const int emax = E5M2 ? 15 : 8;
 
-    uint4 raw[32];
+    uint2 raw[32];
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
-        raw[r] = make_uint4(0, 0, 0, 0);
-        if (col_ok && r < nrows) raw[r] = __ldg(reinterpret_cast<const uint4*>(x + (row0 + r) * cols + col0));
+        raw[r] = make_uint2(0, 0);
+        if (col_ok && r < nrows) raw[r] = __ldg(reinterpret_cast<const uint2*>(x + (row0 + r) * cols + col0));
     }
-    float cmax[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) cmax[j] = 0.f;
+    float cmax[4] = {0.f, 0.f, 0.f, 0.f};
 
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
-        const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
-        float v[8];
+        float v[4];
+        v[0] = __uint_as_float(raw[r].x << 16);
+        v[1] = __uint_as_float(raw[r].x & 0xFFFF0000u);
+        v[2] = __uint_as_float(raw[r].y << 16);
+        v[3] = __uint_as_float(raw[r].y & 0xFFFF0000u);
         float amax = 0.f;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            v[2 * t] = __uint_as_float(w[t] << 16);
-            v[2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
-            cmax[2 * t] = fmaxf(cmax[2 * t], fabsf(v[2 * t]));
-            cmax[2 * t + 1] = fmaxf(cmax[2 * t + 1], fabsf(v[2 * t + 1]));
-            amax = fmaxf(amax, fmaxf(fabsf(v[2 * t]), fabsf(v[2 * t + 1])));
+            cmax[t] = fmaxf(cmax[t], fabsf(v[t]));
+            amax = fmaxf(amax, fabsf(v[t]));
         }
         if (q_c) {                                                            // uniform
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
             int e = -127;
             float inv = 0.f;
             if (amax > 0.f && amax < 3.0e38f) {
@@ -175,21 +183,17 @@ __global__ void __launch_bounds__(256) mx_quant_dual_kernel(const bf16* __restri
                 inv = pow2i(-e > 127 ? 127 : -e);
             }
             if (col_ok && r < nrows) {
-                uint2 o;
-                o.x = (uint32_t)to_fp8<E5M2>(v[0] * inv) | ((uint32_t)to_fp8<E5M2>(v[1] * inv) << 8) |
-                      ((uint32_t)to_fp8<E5M2>(v[2] * inv) << 16) | ((uint32_t)to_fp8<E5M2>(v[3] * inv) << 24);
-                o.y = (uint32_t)to_fp8<E5M2>(v[4] * inv) | ((uint32_t)to_fp8<E5M2>(v[5] * inv) << 8) |
-                      ((uint32_t)to_fp8<E5M2>(v[6] * inv) << 16) | ((uint32_t)to_fp8<E5M2>(v[7] * inv) << 24);
-                *reinterpret_cast<uint2*>(q_c + (row0 + r) * cols + col0) = o;
-                if ((lane & 3) == 0)
+                const uint32_t o = to_fp8x2<E5M2>(v[0] * inv, v[1] * inv) | (to_fp8x2<E5M2>(v[2] * inv, v[3] * inv) << 16);
+                *reinterpret_cast<uint32_t*>(q_c + (row0 + r) * cols + col0) = o;
+                if ((lane & 7) == 0)
                     sf_c[sf_tiled_offset(row0 + r, col0 >> 5, mnb_c)] = (unsigned char)(amax > 0.f ? e + 127 : 0);
             }
         }
     }
     if (q_r && col_ok) {
-        float inv[8];
+        float inv[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
             int e = -127;
             inv[j] = 0.f;
             if (cmax[j] > 0.f && cmax[j] < 3.0e38f) {
@@ -201,15 +205,11 @@ __global__ void __launch_bounds__(256) mx_quant_dual_kernel(const bf16* __restri
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             if (r < nrows) {
-                const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
-                uint32_t o[2] = {0, 0};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const uint32_t lo = to_fp8<E5M2>(__uint_as_float(w[t] << 16) * inv[2 * t]);
-                    const uint32_t hi = to_fp8<E5M2>(__uint_as_float(w[t] & 0xFFFF0000u) * inv[2 * t + 1]);
-                    o[t >> 1] |= (lo | (hi << 8)) << ((t & 1) * 16);
-                }
-                *reinterpret_cast<uint2*>(q_r + (row0 + r) * cols + col0) = make_uint2(o[0], o[1]);
+                const uint32_t o =
+                    to_fp8x2<E5M2>(__uint_as_float(raw[r].x << 16) * inv[0], __uint_as_float(raw[r].x & 0xFFFF0000u) * inv[1]) |
+                    (to_fp8x2<E5M2>(__uint_as_float(raw[r].y << 16) * inv[2], __uint_as_float(raw[r].y & 0xFFFF0000u) * inv[3])
+                     << 16);
+                *reinterpret_cast<uint32_t*>(q_r + (row0 + r) * cols + col0) = o;
             }
         }
     }
@@ -279,7 +279,7 @@ extern "C" int neox_mxfp8_quant_dual(const void* x, void* q_c, void* sf_c, long 
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q_c) & 7) ||
         (reinterpret_cast<uintptr_t>(q_r) & 7))
         return NEOX_ERR_ALIGN;
-    const dim3 grid((unsigned)((cols + 2047) / 2048), (unsigned)((rows + 31) / 32));
+    const dim3 grid((unsigned)((cols + 1023) / 1024), (unsigned)((rows + 31) / 32));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (e5m2)
         mx_quant_dual_kernel<true><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), static_cast<unsigned char*>(q_c),
