@@ -310,22 +310,6 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// Bounded wait with cluster-scope acquire (the arrivals may come from the peer CTA).
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
-    const long long t0 = clock64();
-    for (;;) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (clock64() - t0 > SPIN_LIMIT_CYCLES) return false;
-    }
-}
 // 2-D tiled load into THIS CTA's shared memory whose bytes are counted on the LEADER CTA's barrier at the same
 // offset (bit 24 of a shared::cluster address selects the odd CTA of a pair).  No cluster multicast: each CTA
 // fetches its own tile.

@@ -21,3 +21,45 @@ def test_fp8_linear_gelu_split_matches_plain_composition():
     assert ((y.float() - yr).norm() / yr.norm()).item() < 0.05
     for g, t in zip(got, (x, w1, w2)):
         assert ((g - t.grad.float()).norm() / t.grad.float().norm()).item() < 0.12
+
+
+def test_fp8_delayed_scaling_history_and_weight_cache():
+    import torch
+    from gpt_neox_b200.ops import fp8 as F8
+    m = F8.DelayedMeta(torch.device("cpu"), length=3, e5m2=False, margin=1, most_recent=False)
+    m.update()
+    assert float(m.buf[0]) == 1.0 and float(m.buf[1]) == 1.0            # nothing seen yet: scale 1
+    x = torch.tensor([[0.5, -2.0], [1.0, 0.25]]).bfloat16()
+    F8.cast(x, meta=m)
+    assert float(m.buf[2]) == 2.0                                        # recorded amax
+    m.update()
+    assert abs(float(m.buf[0]) - 448.0 / (2.0 * 2.0)) < 1e-6             # fp8_max / (amax * 2^margin)
+    F8.cast(x * 0.25, meta=m)
+    m.update()
+    assert abs(float(m.buf[0]) - 448.0 / (2.0 * 2.0)) < 1e-6             # 'max' over the history keeps the larger amax
+    mr = F8.DelayedMeta(torch.device("cpu"), length=3, most_recent=True)
+    mr.update(); F8.cast(x, meta=mr); mr.update(); F8.cast(x * 0.25, meta=mr); mr.update()
+    assert abs(float(mr.buf[0]) - 448.0 / 0.5) < 1e-4                    # 'most_recent' follows the last amax
+
+    w = torch.nn.Parameter(torch.randn(16, 16).bfloat16())
+    rec = F8.Fp8Recipe()
+    a = F8._cast_weight(w, rec)
+    assert F8._cast_weight(w, rec) is a                                  # cached
+    F8.invalidate_weight_cache()
+    assert F8._cast_weight(w, rec) is not a                              # the engine's optimizer step invalidates
+    with torch.no_grad():
+        w.add_(1.0)                                                      # so does an in-place update autograd can see
+    b = F8._cast_weight(w, rec)
+    assert not torch.equal(b.q, a.q)
+
+
+def test_pair_kernel_selection(monkeypatch):
+    from gpt_neox_b200.ops import gemm as G
+    monkeypatch.setattr(G, "_PAIR", "auto")
+    assert G.use_pair_kernel(8192, 6144, 6144)                           # fills the machine with 256 x 256 tiles
+    assert not G.use_pair_kernel(512, 512, 4096)                         # 4 tiles: one-CTA kernel
+    assert not G.use_pair_kernel(8192, 6144, 128)                        # short K: nothing to pipeline
+    monkeypatch.setattr(G, "_PAIR", "0")
+    assert not G.use_pair_kernel(8192, 6144, 6144)
+    monkeypatch.setattr(G, "_PAIR", "1")
+    assert G.use_pair_kernel(64, 64, 64)
