@@ -134,31 +134,42 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // loop state in registers: this one thread must finish a k-block's bookkeeping well inside the ~500
+            // clocks the tensor core spends on it
+            const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0;
+            const uint32_t tx_bytes = AX_STAGE + b_bytes + SF_STAGE;
+            const long long sfa_step = x.sfa_mnb * 512, sfb_step = x.sfb_mnb * 512;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 int m_blk, n_blk;
                 tile_coords(tile, num_m, num_n, m_blk, n_blk);
                 const int n0 = n_blk * BNX;
+                const int m0 = m_blk * BM;
+                const unsigned char* sfa = x.sfa + (long long)m_blk * 512;
+                const unsigned char* sfb = x.sfb + (long long)(n0 >> 7) * 512;
+                int k0 = 0;
                 for (int kb = 0; kb < nk; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) {
                         atomicExch(p.status, 131);
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&full[stage], AX_STAGE + b_bytes + SF_STAGE);
+                    mbar_expect_tx(&full[stage], tx_bytes);
                     uint8_t* a_dst = sA + stage * AX_STAGE;
                     uint8_t* b_dst = sB + stage * BX_STAGE;
                     uint8_t* sf_dst = sSF + stage * SF_STAGE;
-                    if (!p.a_mn) tma_load_2d(a_dst, &tmA, &full[stage], kb * BKX, m_blk * BM);
-                    else tma_load_2d(a_dst, &tmA, &full[stage], m_blk * BM, kb * BKX);
-                    if (!p.b_mn) {
-                        tma_load_2d(b_dst, &tmB, &full[stage], kb * BKX, n0);
+                    if (!a_mn) tma_load_2d(a_dst, &tmA, &full[stage], k0, m0);
+                    else tma_load_2d(a_dst, &tmA, &full[stage], m0, k0);
+                    if (!b_mn) {
+                        tma_load_2d(b_dst, &tmB, &full[stage], k0, n0);
                     } else {
-                        tma_load_2d(b_dst, &tmB, &full[stage], n0, kb * BKX);
-                        tma_load_2d(b_dst + 128 * BKX, &tmB, &full[stage], n0 + 128, kb * BKX);
+                        tma_load_2d(b_dst, &tmB, &full[stage], n0, k0);
+                        tma_load_2d(b_dst + 128 * BKX, &tmB, &full[stage], n0 + 128, k0);
                     }
-                    bulk_load(sf_dst, x.sfa + ((long long)kb * x.sfa_mnb + m_blk) * 512, SFA_BYTES, &full[stage]);
-                    bulk_load(sf_dst + SFA_BYTES, x.sfb + ((long long)kb * x.sfb_mnb + (n0 >> 7)) * 512, SFB_BYTES,
-                              &full[stage]);
+                    bulk_load(sf_dst, sfa, SFA_BYTES, &full[stage]);
+                    bulk_load(sf_dst + SFA_BYTES, sfb, SFB_BYTES, &full[stage]);
+                    sfa += sfa_step;
+                    sfb += sfb_step;
+                    k0 += BKX;
                     if (++stage == STAGESX) {
                         stage = 0;
                         phase ^= 1;
@@ -176,6 +187,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const uint32_t a_step = (p.a_mn ? 32 * 128 : 32) >> 4;
             const uint32_t b_step = (p.b_mn ? 32 * 128 : 32) >> 4;
             const uint32_t sf_smem0 = smem_u32(sSF);
+            uint32_t idesc_k[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) idesc_k[k] = idesc0 | ((uint32_t)k << 29) | ((uint32_t)k << 4);
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
@@ -210,7 +224,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         umma_mx_ss(tmem_d, a_lo + k * a_step, desc_hi, b_lo + k * b_step, desc_hi,
-                                   idesc0 | ((uint32_t)k << 29) | ((uint32_t)k << 4), sf_t, sf_t + 4 + sfb_col,
+                                   idesc_k[k], sf_t, sf_t + 4 + sfb_col,
                                    (kb | k) != 0);
                     umma_commit(&empty[stage]);
                     sfr ^= 1;
