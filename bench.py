@@ -10,8 +10,8 @@ parallel attention+MLP residual, LayerNorm, GeLU MLP 24576, vocab 50432, sequenc
 activation checkpointing on, bf16 parameters with fp32 master weights and Adam (ZeRO-1 layout).
 
 The full 44-layer model needs 8 GPUs (it is ~330 GB of parameter + optimizer state), so the depth
-scales with the GPU count -- 5.5 layers per GPU, as in the 8-GPU run -- while the global batch stays at 192
-sequences: work per GPU and per step is constant (weak scaling), and a step takes about as long at every N.
+scales with the GPU count -- 5.5 layers per GPU, as in the 8-GPU run -- while the global batch stays at 128
+sequences (micro-batch 4 x 32 accumulation steps, the accumulation depth of the reference's 20B config): work per GPU and per step is constant (weak scaling), and a step takes about as long at every N.
 
     N = 1: 6 layers            N = 2: 11 layers, TP 2
     N = 4: 22 layers, TP 4     N = 8: 44 layers, TP 4 x PP 2 (1F1B)   <- the named configuration
@@ -44,7 +44,7 @@ sys.path.insert(0, ROOT)
 LAYERS = {1: 6, 2: 11, 4: 22, 8: 44}
 PARALLEL = {1: (1, 0), 2: (2, 0), 4: (4, 0), 8: (4, 2)}      # (tensor parallel, pipeline stages)
 SEQ_PER_GPU = 192          # secondary models: sequences per GPU per step
-GLOBAL_SEQS = 192          # headline: sequences per step at every N
+GLOBAL_SEQS = 128          # headline: sequences per step at every N (micro-batch 4 x 32 accumulation steps)
 PAPER_TFLOPS_PER_GPU_A100 = 117.0
 
 
