@@ -77,7 +77,7 @@ def model_config(n_gpus, layers=None, micro_batch=4, seq=2048, global_seqs=GLOBA
 
 
 def alt_model_config(name, n_gpus, micro_batch=None, seq_per_gpu=None, layout=None):
-    """The other BASELINE configurations (secondary numbers; the headline stays the 20B shape).
+    """The secondary configurations (the headline stays the 20B shape).
 
     pythia-1.4b : 24 layers, h 2048, 16 heads, rotary 25 %, parallel residual, GeLU, vocab 50304, seq 2048, micro-batch
                   8, TP 2 x DP n/2 with sequence parallelism, ZeRO-1 with overlapped communication
@@ -174,24 +174,73 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm(args):
-    """The unmodified reference needs DeeperSpeed (imported at module scope by deepy.py, training.py and
-    the model files) and is not installable offline: the pip install of the reference tree fails because it is a
-    script tree without setup.py / pyproject.toml, and deepspeed is in no local wheel."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(os.path.join(ref_dir, "megatron")):
-        why = "baseline/_ref is not installed (the offline pip install of the reference tree was not possible)"
+def build_config(a):
+    """Configuration dict, vocabulary size and (tp, pp) layout of the run the flags select (both arms use it)."""
+    n = a.gpus
+    assert n in LAYERS, "supported GPU counts: 1, 2, 4, 8"
+    layout = None
+    if a.tp is not None or a.pp is not None:
+        layout = (a.tp or PARALLEL[n][0], a.pp if a.pp is not None else PARALLEL[n][1])
+    vocab_size = 50432
+    if a.model == "neox-20b":
+        cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch,
+                           global_seqs=a.seq_per_gpu * n if a.seq_per_gpu else a.global_batch,
+                           ckpt=not a.no_act_ckpt, layout=layout)
     else:
-        sys.path.insert(0, ref_dir)
-        try:
-            import deepspeed  # noqa: F401
-        except Exception as exc:
-            why = f"reference imports deepspeed at module scope and it is not installed ({type(exc).__name__})"
-    if why is None:
-        why = "reference runner not wired: no deepspeed-compatible engine available on this image"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+        cfg, vocab_size, layout = alt_model_config(a.model, n, None if a.micro_batch == 4 else a.micro_batch,
+                                                   a.seq_per_gpu, layout)
+        if a.layers:
+            cfg["num_layers"] = a.layers
+    if a.fp8:
+        cfg.update({"te_columnparallel": True, "te_rowparallel": True, "te_fp8_recipe": a.fp8,
+                    "te_fp8_amax_history_len": 16, "te_fp8_amax_compute_algo": "max"})
+    return cfg, vocab_size, layout or PARALLEL[n]
+
+
+def metric_name(model):
+    return ("tokens_per_sec of the 44-layer GPT-NeoX-20B (3D-parallel training; measured tokens/s x layers/44 "
+            "where fewer layers fit; TFLOPS/GPU in tflops_per_gpu)" if model == "neox-20b"
+            else f"tokens_per_sec ({model} training; TFLOPS/GPU in tflops_per_gpu)")
+
+
+def model_description(model, layers, hidden):
+    if model != "neox-20b":
+        return f"{model} shape, {layers} layers, h{hidden}"
+    return (f"GPT-NeoX-20B layer shape (h6144, 64 heads, ffn 24576, vocab 50432), {layers} of 44 layers"
+            + (" = full model" if layers == 44 else
+               " (depth scales with GPUs: 5.5 layers/GPU; value = measured tokens/s x layers/44)"))
+
+
+def config_deviation(model, cfg, n):
+    """Where the timed run departs from the named 20B configuration (global batch 1536, 44 layers, TP 4 x PP 2)."""
+    if model != "neox-20b":
+        return None
+    dev = {}
+    if cfg["train_batch_size"] != 1536:
+        dev["global_batch"] = {"named": 1536, "run": cfg["train_batch_size"],
+                               "why": "a 1536-sequence step takes over a minute; fewer accumulation steps of the same micro-batch"}
+    if cfg["num_layers"] != 44:
+        dev["num_layers"] = {"named": 44, "run": cfg["num_layers"],
+                             "why": f"the 44-layer model with its optimizer state needs 8 GPUs; {n} GPU(s) hold {cfg['num_layers']} layers"}
+    return dev or None
+
+
+def reference_arm(a):
+    """Times the stock reference (copied to baseline/_ref) on the same configuration; see baseline/reference_arm.py."""
+    if a.fp8:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's fp8 path needs transformer_engine, "
+                                                              "which is not installed"}))
+        return 0
+    if a.model == "dmoe-125m":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's MoE layers need DeepSpeed MoE or "
+                                                              "megablocks, neither installable offline"}))
+        return 0
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+    cfg, vocab_size, _ = build_config(a)
+    depth_of = (lambda layers: layers / 44.0) if a.model == "neox-20b" else (lambda layers: 1.0)
+    return ra.run(a, cfg, vocab_size, depth_of, ClockSampler, metric_name(a.model),
+                  lambda layers, hidden: model_description(a.model, layers, hidden))
 
 
 def main():
@@ -208,7 +257,7 @@ def main():
     ap.add_argument("--no-act-ckpt", action="store_true", help="secondary number: activation checkpointing off")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--model", default="neox-20b", choices=["neox-20b", "pythia-1.4b", "llama2-7b", "dmoe-125m"],
-                    help="neox-20b is the headline configuration; the others are the secondary BASELINE configs")
+                    help="neox-20b is the headline configuration; the others are secondary numbers")
     ap.add_argument("--fp8", default=None, choices=["current", "delayed", "mxfp8"],
                     help="secondary number: linear layers through the te_* fp8 switches with this recipe")
     ap.add_argument("--tp", type=int, default=None, help="override the tensor-parallel degree (debugging)")
@@ -232,22 +281,7 @@ def main():
     assert world == n, f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}"
     assert n in LAYERS, "supported GPU counts: 1, 2, 4, 8"
     warm = max(a.warmup, 3)
-    layout = None
-    if a.tp is not None or a.pp is not None:
-        layout = (a.tp or PARALLEL[n][0], a.pp if a.pp is not None else PARALLEL[n][1])
-    vocab_size = 50432
-    if a.model == "neox-20b":
-        cfg = model_config(n, layers=a.layers, micro_batch=a.micro_batch,
-                           global_seqs=a.seq_per_gpu * n if a.seq_per_gpu else a.global_batch,
-                           ckpt=not a.no_act_ckpt, layout=layout)
-    else:
-        cfg, vocab_size, layout = alt_model_config(a.model, n, None if a.micro_batch == 4 else a.micro_batch,
-                                                   a.seq_per_gpu, layout)
-        if a.layers:
-            cfg["num_layers"] = a.layers
-    if a.fp8:
-        cfg.update({"te_columnparallel": True, "te_rowparallel": True, "te_fp8_recipe": a.fp8,
-                    "te_fp8_amax_history_len": 16, "te_fp8_amax_compute_algo": "max"})
+    cfg, vocab_size, layout = build_config(a)
     neox_args = NeoXArgs.from_dict(cfg)
     neox_args.configure_distributed_args()
     neox_args.build_tokenizer()
@@ -313,12 +347,10 @@ def main():
     depth = neox_args.num_layers / 44.0 if a.model == "neox-20b" else 1.0
     mfu_flops = flops_per_iteration(neox_args, 3) / (ms_dev / 1e3) / n / 1e12
     hfu_flops = flops_per_iteration(neox_args, 4 if neox_args.checkpoint_activations else 3) / (ms_dev / 1e3) / n / 1e12
-    tp, pp = layout or PARALLEL[n]
+    tp, pp = layout
     if rank == 0:
         out = {
-            "metric": ("tokens_per_sec of the 44-layer GPT-NeoX-20B (3D-parallel training; measured tokens/s x layers/44 "
-                       "where fewer layers fit; TFLOPS/GPU in tflops_per_gpu)" if a.model == "neox-20b"
-                       else f"tokens_per_sec ({a.model} training; TFLOPS/GPU in tflops_per_gpu)"),
+            "impl": "ours", "metric": metric_name(a.model),
             "value": round(tps * depth, 1), "unit": "tokens/s", "n_gpus": n, "steps": a.steps, "warmup": warm,
             "ms_per_step": round(ms_dev, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if not a.fp8 else f"fp8 linear layers ({a.fp8} scaling, e4m3 fwd / e5m2 grads), bf16 elsewhere",
@@ -326,16 +358,14 @@ def main():
             "tflops_per_gpu": {"model_c3": round(mfu_flops, 1), "hardware_c4": round(hfu_flops, 1),
                                "formula": "24*c*B*s*L*h^2*(1+s/6h+V/16Lh) / (t*gpus)"},
             "vs_paper_a100_tflops_per_gpu": round(hfu_flops / PAPER_TFLOPS_PER_GPU_A100, 2),
-            "config": {"model": (f"GPT-NeoX-20B layer shape (h6144, 64 heads, ffn 24576, vocab 50432), "
-                                 f"{neox_args.num_layers} of 44 layers" + (" = full model" if neox_args.num_layers == 44 else
-                                                                           " (depth scales with GPUs: 5.5 layers/GPU; value = measured tokens/s x layers/44)"))
-                       if a.model == "neox-20b" else f"{a.model} shape, {neox_args.num_layers} layers, h{neox_args.hidden_size}",
+            "config": {"model": model_description(a.model, neox_args.num_layers, neox_args.hidden_size),
                        "global_batch": neox_args.train_batch_size, "seq_len": seq, "micro_batch": mb,
                        "grad_accum": gas, "activation_checkpointing": bool(neox_args.checkpoint_activations),
                        "parallelism": f"tp{tp}" + (f"pp{pp}" if pp else "") + f"dp{world // (tp * max(pp, 1))}"
                                       + (f" ep{neox_args.moe_expert_parallel_size}" if neox_args.moe_num_experts > 1 else "")
                                       + (" sp" if neox_args.sequence_parallel else "") + " zero1",
                        "l2": "inputs larger than L2 (no flush needed)"},
+            "config_deviation": config_deviation(a.model, cfg, n),
             "clocks": clocks,
             "e2e": None if ms_e2e is None else {"value": round(tokens / (ms_e2e / 1e3) * depth, 1), "unit": "tokens/s",
                                                 "ms_per_step": round(ms_e2e, 2),
