@@ -121,6 +121,9 @@ def engine_save_checkpoint(engine, save_dir, tag, client_state):
     tp = mpu.get_model_parallel_rank()
     module = engine.module
     writer = mpu.get_data_parallel_rank() == 0
+    # the parameter all-gather of the last step may still be in flight on the optimizer's side stream
+    if hasattr(engine.optimizer, "wait_all_params"):
+        engine.optimizer.wait_all_params()
     common = {
         "optimizer": None,
         "lr_scheduler": engine.lr_scheduler.state_dict() if engine.lr_scheduler is not None else None,

@@ -84,7 +84,8 @@ class Bucket:
         self.grad_shard = self.flat_grad[self.lo:self.hi] if grad_dtype == torch.float32 else None
         # overlap bookkeeping (see FlatMixedPrecisionOptimizer.arm_overlap)
         self.n_expected = len(self.params)
-        self.ready = 0
+        self.ready = set()             # ids of the parameters whose gradient has been reported this backward
+        self.never_early = any(getattr(p, "late_grad_sync", False) for p in self.params)
         self.pending_reduce = None
         self.pending_gather = None
 
@@ -231,8 +232,13 @@ class FlatMixedPrecisionOptimizer:
                 dev = device or plist[0].device
                 chunks = [plist]
                 if self.overlap_comm and cw > 1 and reduce_bucket_size:
-                    chunks, cur, n = [], [], 0
+                    # gradients that are rewritten after backward (norms under sequence parallelism, weights tied
+                    # across layers or pipeline stages) get a bucket of their own that is reduced in step()
+                    late = [p for p in plist if getattr(p, "late_grad_sync", False)]
+                    chunks, cur, n = ([late] if late else []), [], 0
                     for p in plist:
+                        if getattr(p, "late_grad_sync", False):
+                            continue
                         if cur and n + p.numel() > reduce_bucket_size:
                             chunks.append(cur)
                             cur, n = [], 0
@@ -268,14 +274,14 @@ class FlatMixedPrecisionOptimizer:
                 if param.grad is not None:
                     param.main_grad.add_(param.grad.to(param.main_grad.dtype))
                     param.grad = None
-                    self._on_grad_ready(bucket)
+                    self._on_grad_ready(bucket, param)
             return hook
         self._hooks = []
         for b in self.buckets:
             for p in b.params:
                 p._bucket = b
                 # kernels that accumulate straight into main_grad report here (ops.linear.notify_grad_ready)
-                p._grad_ready = (lambda bucket=b: self._on_grad_ready(bucket))
+                p._grad_ready = (lambda bucket=b, param=p: self._on_grad_ready(bucket, param))
                 self._hooks.append(p.register_post_accumulate_grad_hook(make(p, b)))
 
     # ------------------------------------------------------------------ communication overlap
@@ -291,13 +297,15 @@ class FlatMixedPrecisionOptimizer:
             return
         self._armed = True
         for b in self.buckets:
-            b.ready = 0
+            b.ready = set()
 
-    def _on_grad_ready(self, bucket):
-        if not self._armed or bucket.world <= 1:
+    def _on_grad_ready(self, bucket, param):
+        """A parameter may report more than once per backward (a weight with several uses): readiness is counted
+        per distinct parameter, and a bucket holding a gradient that is still rewritten after backward never fires."""
+        if not self._armed or bucket.world <= 1 or bucket.never_early:
             return
-        bucket.ready += 1
-        if bucket.ready == bucket.n_expected:
+        bucket.ready.add(id(param))
+        if len(bucket.ready) == bucket.n_expected:
             bucket.reduce_grads_async(self._stream())
 
     def install_param_wait_hooks(self, module):
@@ -339,18 +347,29 @@ class FlatMixedPrecisionOptimizer:
         tp_rank = mpu.get_model_parallel_rank()
         dev = self.buckets[0].flat_grad.device if self.buckets else torch.device("cpu")
         total = torch.zeros((), dtype=torch.float32, device=dev)
+        expert_parallel = mpu.get_expert_parallel_world_size() > 1
+        across_dp = torch.zeros((), dtype=torch.float32, device=dev)   # part that differs between DP ranks
+        need_dp = False
         for b in self.buckets:
             sq = b.shard_sq_norm(tp_rank)
-            if b.world > 1 and not b.sharded:
-                pass  # replicated over DP: every rank already holds the full sum
-            total = total + sq
             b._sq = sq
+            is_expert = b.comm_group is not mpu.get_data_parallel_group() and expert_parallel
+            if b.sharded:
+                # shards partition the bucket over its group (expert buckets: a sub-group of DP, and the
+                # expert-parallel ranks hold different experts, so the full DP sum counts every element once)
+                across_dp = across_dp + sq
+                need_dp = True
+            elif is_expert:
+                # unsharded expert bucket: different experts per expert-parallel rank, replicated over the
+                # expert-data-parallel group -> DP sum divided by that replication
+                across_dp = across_dp + sq / float(max(b.world, 1))
+                need_dp = True
+            else:
+                total = total + sq      # replicated over DP: every rank already holds the full sum
         if dist.is_available() and dist.is_initialized():
-            # shards partition the bucket over DP; TP shards and PP stages partition the model
-            if any(b.sharded for b in self.buckets):
-                # sum over data-parallel ranks (expert buckets use a sub-group of it; summing their shards
-                # over the full DP group counts each expert shard exactly once as well)
-                dist.all_reduce(total, group=mpu.get_data_parallel_group())
+            if need_dp:
+                dist.all_reduce(across_dp, group=mpu.get_data_parallel_group())
+            total = total + across_dp
             if mpu.get_model_parallel_world_size() > 1:
                 dist.all_reduce(total, group=mpu.get_model_parallel_group())
             if mpu.get_pipe_parallel_world_size() > 1:
@@ -403,6 +422,12 @@ class FlatMixedPrecisionOptimizer:
         self.zero_grad()
         return True
 
+    def wait_all_params(self):
+        """Make the current stream wait for every parameter all-gather still in flight (anything that reads
+        parameters outside a layer's forward -- checkpoint writing, weight export -- calls this first)."""
+        for b in self.buckets:
+            b.wait_params()
+
     # ------------------------------------------------------------------ checkpointing
     def state_dict(self):
         return {
@@ -420,12 +445,18 @@ class FlatMixedPrecisionOptimizer:
         self.skipped_steps = sd.get("skipped_steps", 0)
         if load_optimizer_states and "optimizer_state_dict" in sd:
             self.optimizer.load_state_dict(sd["optimizer_state_dict"])
-        for b, m in zip(self.buckets, sd.get("single_partition_of_fp32_groups", [])):
-            if m.numel() == b.master.numel():
-                b.master.data.copy_(m.to(b.master.device))
+        for i, (b, m) in enumerate(zip(self.buckets, sd.get("single_partition_of_fp32_groups", []))):
+            if m.numel() != b.master.numel():
+                raise ValueError(
+                    f"optimizer state of bucket {i} holds {m.numel()} master weights but this run shards the bucket "
+                    f"into {b.master.numel()}: the data-parallel size or the bucket layout changed since the "
+                    "checkpoint was written; reload with load_optimizer_states=False (finetune / no_load_optim) or "
+                    "with the original layout")
+            b.master.data.copy_(m.to(b.master.device))
 
     def refresh_master_from_params(self):
         """After loading module weights: re-derive the fp32 master shards from ``flat_param``."""
+        self.wait_all_params()
         for b in self.buckets:
             if b.mixed:
                 b.master.data.copy_(b.flat_param[b.lo:b.hi].float())

@@ -216,6 +216,12 @@ class PipelineModule(nn.Module):
                             group, ranks_mine = g, ranks
             comms[key] = {"stages": stages, "group": group, "ranks": ranks_mine,
                           "weight_attr": self.tied_weight_attrs.get(key)}
+            uses = sum(1 for s in self._layer_specs if isinstance(s, TiedLayerSpec) and s.key == key)
+            if uses > 1 and key in self.tied_modules:
+                # several uses (possibly on other stages) contribute to this gradient: an optimizer that reduces
+                # gradients early over the data-parallel group must leave it until the whole backward and the
+                # tied all-reduce have finished
+                self.tied_weight(key).late_grad_sync = True
         return comms
 
     def tied_weight(self, key):

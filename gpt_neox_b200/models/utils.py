@@ -51,6 +51,7 @@ def mark_norms_for_sequence_parallel_grad_sync(module, neox_args):
     params = norm_parameters(module)
     for p in params:
         p.sequence_parallel_grad_sync = True
+        p.late_grad_sync = True        # rewritten after backward: not part of an early data-parallel reduction
     return params
 
 

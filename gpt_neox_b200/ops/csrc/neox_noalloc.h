@@ -10,7 +10,8 @@
 //
 // computes exactly what neox_layernorm_bwd() computes (dx in the storage dtype, dgamma / dbeta in fp32) with
 // the same kernels.  dtype: 0 = bf16, 1 = fp32, 2 = fp16.  Returns 0, or NEOX_ERR_SHAPE / NEOX_ERR_TOO_LARGE /
-// NEOX_ERR_DRIVER / NEOX_ERR_LAUNCH; neox_noalloc_last_error() then describes the refusal in words.
+// NEOX_ERR_DRIVER / NEOX_ERR_LAUNCH; neox_noalloc_last_error() then describes the refusal in words (the text is kept
+// per host thread: read it on the thread whose call was refused).
 //
 // Contract:
 //   * cols <= NEOX_NOALLOC_MAX_COLS (and a multiple of 8); any number of rows.

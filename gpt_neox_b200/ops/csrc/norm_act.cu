@@ -674,8 +674,10 @@ static __device__ __align__(256) float g_noalloc_scratch[2LL * NEOX_NOALLOC_MAX_
 
 namespace {
 constexpr int NOALLOC_MAX_DEV = 64;
-float* g_noalloc_ptr[NOALLOC_MAX_DEV] = {nullptr};
-char g_noalloc_err[256] = "";
+float* g_noalloc_ptr[NOALLOC_MAX_DEV] = {nullptr};   // idempotent per-device cache: racing first calls store the same value
+// One message buffer per host thread: a refusal on one thread cannot tear or overwrite the text another thread
+// is about to read through neox_noalloc_last_error().
+thread_local char g_noalloc_err[256] = "";
 
 int noalloc_fail(int code, const char* fmt, long long a, long long b) {
     snprintf(g_noalloc_err, sizeof(g_noalloc_err), fmt, a, b);

@@ -349,6 +349,8 @@ def get_optimizer(model, neox_args, dummy=False):
         from .engine.plain_optimizer import PlainOptimizer
         return PlainOptimizer(opt, clip_grad=neox_args.gradient_clipping), groups
     fp16_cfg = dict(neox_args.fp16 or {})
+    # tags (late_grad_sync) must be in place before the optimizer lays out its buckets
+    mark_norms_for_sequence_parallel_grad_sync(model, neox_args)
     optimizer = FlatMixedPrecisionOptimizer(groups, inner_cls, inner_kw, neox_args.params_dtype,
                                             zero_stage=neox_args.zero_stage if isinstance(neox_args.zero_stage, int) else 0,
                                             clip_grad=neox_args.gradient_clipping, fp16_cfg=fp16_cfg,

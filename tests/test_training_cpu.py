@@ -102,6 +102,25 @@ def test_zero1_overlapped_reduction_matches_plain(tmp_path):
     assert rb["buckets"] > ra["buckets"] and rb["overlapped"] > 0, rb
 
 
+@pytest.mark.parametrize("world,cfg", [
+    (4, {"model_parallel_size": 2, "sequence_parallel": True}),        # norm gradients are all-reduced after backward
+    (2, {"no_weight_tying": False}),                                   # the embedding weight is used twice
+    (4, {"pipe_parallel_size": 2, "num_layers": 4, "no_weight_tying": False}),   # tied across pipeline stages
+])
+def test_overlapped_reduction_leaves_late_gradients_alone(tmp_path, world, cfg):
+    """Gradients that are completed only after backward (sequence-parallel norm gradients, weights tied across
+    layers or stages) must not be part of an early data-parallel reduction: the run with overlap reproduces
+    the losses of the run without it, and other buckets are still reduced early."""
+    a, b = str(tmp_path / "plain.json"), str(tmp_path / "overlap.json")
+    base = {"gradient_accumulation_steps": 2, **cfg}
+    run_distributed(_overlap_losses, world, {**base, "zero_optimization": {"stage": 1}}, a)
+    run_distributed(_overlap_losses, world, {**base, "zero_optimization": {"stage": 1, "overlap_comm": True,
+                                                                           "reduce_bucket_size": 20000}}, b)
+    ra, rb = json.load(open(a)), json.load(open(b))
+    assert all(abs(x - y) < 1e-5 for x, y in zip(ra["losses"], rb["losses"])), (ra, rb)
+    assert rb["overlapped"] > 0, rb
+
+
 def test_tensor_and_data_parallel_training():
     run_distributed(_loss_decreases, 4, {"model_parallel_size": 2, "sequence_parallel": True,
                                          "zero_optimization": {"stage": 1}}, None)
