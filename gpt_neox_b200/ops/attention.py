@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -58,6 +59,24 @@ def kernel_ok(q, k, v, bias=None) -> bool:
             and q.shape[0] >= 1)
 
 
+def _launch_fwd(q, k, v, out, lse, sq, sk, b, hq, hkv, d, scale, causal, window, slopes):
+    """Forward kernel launch.  Default: the two-query-tile kernel (``csrc/flash_fwd2_sm100.cu``, P kept in tensor
+    memory); ``NEOX_FLASH_FWD=1`` selects the one-tile kernel (``csrc/flash_fwd_sm100.cu``, bf16 only)."""
+    L = native.lib()
+    ll = ctypes.c_longlong
+    strides = (ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+               ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)))
+    tail = (ctypes.c_float(scale), int(causal), int(window if window is not None else -1), native.ptr(slopes))
+    if os.environ.get("NEOX_FLASH_FWD", "2") == "1" and q.dtype == torch.bfloat16:
+        rc = L.neox_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse),
+                              sq, sk, b, hq, hkv, d, *strides, *tail, _s())
+        native.check(rc, "neox_flash_fwd")
+        return
+    rc = L.neox_flash_fwd2(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse),
+                           sq, sk, b, hq, hkv, d, *strides, *tail, _DT[q.dtype], _s())
+    native.check(rc, "neox_flash_fwd2")
+
+
 class _FlashFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale, window, slopes):
@@ -67,14 +86,7 @@ class _FlashFn(torch.autograd.Function):
         lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
         L = native.lib()
         ll = ctypes.c_longlong
-        rc = L.neox_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse),
-                              sq, sk, b, hq, hkv, d,
-                              ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
-                              ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
-                              ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)),
-                              ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
-                              native.ptr(slopes), _s())
-        native.check(rc, "neox_flash_fwd")
+        _launch_fwd(q, k, v, out, lse, sq, sk, b, hq, hkv, d, scale, causal, window, slopes)
         ctx.save_for_backward(q, k, v, out, lse, slopes if slopes is not None else torch.empty(0, device=q.device))
         ctx.cfg = (causal, scale, window, slopes is not None)
         return out
@@ -137,14 +149,7 @@ class _PackedQKVFn(torch.autograd.Function):
             native.check(rc, "neox_rope_qk_inplace")
         out = torch.empty(s, b, h, d, dtype=mixed.dtype, device=mixed.device)
         lse = torch.empty(b, h, s, dtype=torch.float32, device=mixed.device)
-        rc = L.neox_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse),
-                              s, s, b, h, h, d,
-                              ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
-                              ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
-                              ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)),
-                              ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
-                              native.ptr(slopes), _s())
-        native.check(rc, "neox_flash_fwd")
+        _launch_fwd(q, k, v, out, lse, s, s, b, h, h, d, scale, causal, window, slopes)
         empty = torch.empty(0, device=mixed.device)
         ctx.save_for_backward(mixed, out, lse, slopes if slopes is not None else empty,
                               c if c is not None else empty, sn if sn is not None else empty)
