@@ -58,6 +58,26 @@ struct Cfg2 {
     static constexpr int SMEM = OFF_MISC + MISC_BYTES + 1024;
 };
 
+// 2^x on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
+// [-0.5, 0.5] (relative error 8e-5, far below the 16-bit rounding of P) and n added into the exponent field.
+// The softmax computes one element in four this way, because the exponential unit (16 results per clock per SM)
+// is the busiest pipe of the kernel.
+__device__ __forceinline__ float ex2_fma(float x) {
+    x = fmaxf(x, -125.0f);
+    const float r = x + 12582912.0f;
+    const float f = x - (r - 12582912.0f);
+    float q = fmaf(f, 0.05520550534129143f, 0.24261397123336792f);
+    q = fmaf(q, f, 0.6932547688484192f);
+    q = fmaf(q, f, 0.9999276995658875f);
+    return __int_as_float(__float_as_int(q) + (__float_as_int(r) << 23));
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -96,6 +116,16 @@ __device__ __forceinline__ void reg_inc() {
 template <int N>
 __device__ __forceinline__ void reg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// D[tmem] (+)= A[tmem] * B[smem], B descriptor given as halves.
+__device__ __forceinline__ void umma_ts_lohi(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 template <bool FP16>
@@ -242,16 +272,22 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(p.status, 233);
             auto active = [&](int i, int g) { return i == 0 ? (g >= a0 && g < e0) : (g >= a1 && g < e1); };
+            // Operand descriptors are formed with one 32-bit add per MMA (constant upper half; the lower half counts
+            // 16-byte units): a single thread issues every MMA, so the instruction count per MMA is what limits it.
+            const uint32_t hi = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo[2] = {smem_desc_lo(smem_u32(sQ), 16), smem_desc_lo(smem_u32(sQ + C::TILE), 16)};
+            const uint32_t k_lo[2] = {smem_desc_lo(smem_u32(sK), 16), smem_desc_lo(smem_u32(sK + C::TILE), 16)};
+            const uint32_t v_lo[2] = {smem_desc_lo(smem_u32(sV), CHUNK_BYTES),
+                                      smem_desc_lo(smem_u32(sV + C::TILE), CHUNK_BYTES)};
             auto qk = [&](int i, int g) -> bool {
                 const int st = g & 1;
                 if (!mbar_wait(&k_full[st], (g >> 1) & 1)) return false;
                 tc_fence_after();
-                const uint32_t q_base = smem_u32(sQ + i * C::TILE), k_base = smem_u32(sK + st * C::TILE);
+                const uint32_t ql = q_lo[i], kl = k_lo[st], td = tmem_base + i * 128;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t o = (k >> 2) * CHUNK_BYTES + (k & 3) * 32;
-                    umma_bf16_ss(tmem_base + i * 128, make_smem_desc_sw128(q_base + o, 16, 1024),
-                                 make_smem_desc_sw128(k_base + o, 16, 1024), idesc_qk, k != 0);
+                    const uint32_t o = ((k >> 2) * CHUNK_BYTES + (k & 3) * 32) >> 4;
+                    umma_ss_lohi<false, false>(td, ql + o, hi, kl + o, hi, idesc_qk, k != 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[i]);
                 return true;
@@ -263,14 +299,12 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     !mbar_wait(&v_full[st], (g >> 1) & 1))
                     return false;
                 tc_fence_after();
-                const uint32_t v_base = smem_u32(sV + st * C::TILE);
+                    const uint32_t vl = v_lo[st], td = tmem_base + 256 + i * 128, ta = tmem_base + i * 128;
+                umma_ts_lohi(td, ta, vl, hi, idesc_pv, t != 0 ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)
-                    umma_bf16_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8,
-                                 make_smem_desc_sw128(v_base + k * 2048, CHUNK_BYTES, 1024), idesc_pv,
-                                 (t != 0 || k != 0) ? 1u : 0u);
+                for (int k = 1; k < BN / 16; ++k) umma_ts_lohi(td, ta + k * 8, vl + k * 128, hi, idesc_pv, 1u);
                 umma_commit(&pv_done[i]);
-                return true;
+                    return true;
             };
             if (ok) {
                 for (int i = 0; i < 2 && ok; ++i)
@@ -350,10 +384,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 };
                 mx = fmaxf(fmaxf(fix(r0, 0), fix(r1, 32)), fmaxf(fix(r2, 64), fix(r3, 96)));
             } else {
-                auto rowmax = [&](uint32_t(&r)[32]) {
-                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                auto rowmax = [&](uint32_t(&r)[32]) {     // 3-input maxima, four independent chains
+                    float m4[4];
 #pragma unroll
-                    for (int k = 0; k < 32; ++k) m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(r[k]));
+                    for (int k = 0; k < 4; ++k) m4[k] = fmaxf(__uint_as_float(r[2 * k]), __uint_as_float(r[2 * k + 1]));
+#pragma unroll
+                    for (int k = 0; k < 12; ++k)
+                        m4[k & 3] = max3(m4[k & 3], __uint_as_float(r[8 + 2 * k]), __uint_as_float(r[9 + 2 * k]));
                     return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                 };
                 mx = fmaxf(fmaxf(rowmax(r0), rowmax(r1)), fmaxf(rowmax(r2), rowmax(r3)));
@@ -381,7 +418,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
                     const float e0 = ex2(fmaf(__uint_as_float(r[2 * k]), scale, -m_sub));
-                    const float e1 = ex2(fmaf(__uint_as_float(r[2 * k + 1]), scale, -m_sub));
+                    const float x1 = fmaf(__uint_as_float(r[2 * k + 1]), scale, -m_sub);
+                    const float e1 = (k & 1) ? ex2_fma(x1) : ex2(x1);
                     s4[k & 3] += e0 + e1;
                     pk[k] = pack16<FP16>(e0, e1);
                 }
