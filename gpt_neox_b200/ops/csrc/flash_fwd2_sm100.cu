@@ -58,20 +58,6 @@ struct Cfg2 {
     static constexpr int SMEM = OFF_MISC + MISC_BYTES + 1024;
 };
 
-// 2^x on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
-// [-0.5, 0.5] (relative error 8e-5, far below the 16-bit rounding of P) and n added into the exponent field.
-// The softmax computes one element in four this way, because the exponential unit (16 results per clock per SM)
-// is the busiest pipe of the kernel.
-__device__ __forceinline__ float ex2_fma(float x) {
-    x = fmaxf(x, -125.0f);
-    const float r = x + 12582912.0f;
-    const float f = x - (r - 12582912.0f);
-    float q = fmaf(f, 0.05520550534129143f, 0.24261397123336792f);
-    q = fmaf(q, f, 0.6932547688484192f);
-    q = fmaf(q, f, 0.9999276995658875f);
-    return __int_as_float(__float_as_int(q) + (__float_as_int(r) << 23));
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float y;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
@@ -418,8 +404,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
                     const float e0 = ex2(fmaf(__uint_as_float(r[2 * k]), scale, -m_sub));
-                    const float x1 = fmaf(__uint_as_float(r[2 * k + 1]), scale, -m_sub);
-                    const float e1 = (k & 1) ? ex2_fma(x1) : ex2(x1);
+                    const float e1 = ex2(fmaf(__uint_as_float(r[2 * k + 1]), scale, -m_sub));
                     s4[k & 3] += e0 + e1;
                     pk[k] = pack16<FP16>(e0, e1);
                 }
