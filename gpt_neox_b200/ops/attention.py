@@ -77,6 +77,23 @@ def _launch_fwd(q, k, v, out, lse, sq, sk, b, hq, hkv, d, scale, causal, window,
     native.check(rc, "neox_flash_fwd2")
 
 
+def _launch_bwd(q, k, v, out, do, lse, dq, dk, dv, delta, gs, sq, sk, b, hq, hkv, d, scale, causal, window, slopes):
+    """Backward kernels (delta, dK/dV, dQ) writing into the strided ``dq`` / ``dk`` / ``dv`` views (``gs``: their
+    nine element strides).  Default: 128-wide blocks with P / dS kept in tensor memory
+    (``csrc/flash_bwd2_sm100.cu``); ``NEOX_FLASH_BWD=1`` selects the 64-wide form (``csrc/flash_bwd_sm100.cu``)."""
+    L = native.lib()
+    ll = ctypes.c_longlong
+    args = (native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(do), native.ptr(lse),
+            native.ptr(dq), native.ptr(dk), native.ptr(dv), native.ptr(delta), sq, sk, b, hq, hkv, d,
+            ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+            ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), gs,
+            ctypes.c_float(scale), int(causal), int(window if window is not None else -1), native.ptr(slopes))
+    if os.environ.get("NEOX_FLASH_BWD", "2") == "1" and q.dtype == torch.bfloat16:
+        native.check(L.neox_flash_bwd_strided(*args, _s()), "neox_flash_bwd_strided")
+    else:
+        native.check(L.neox_flash_bwd2_strided(*args, _DT[q.dtype], _s()), "neox_flash_bwd2_strided")
+
+
 class _FlashFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale, window, slopes):
@@ -104,15 +121,10 @@ class _FlashFn(torch.autograd.Function):
         delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
         L = native.lib()
         ll = ctypes.c_longlong
-        rc = L.neox_flash_bwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(do),
-                              native.ptr(lse), native.ptr(dq), native.ptr(dk), native.ptr(dv), native.ptr(delta),
-                              sq, sk, b, hq, hkv, d,
-                              ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
-                              ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
-                              ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)),
-                              ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
-                              native.ptr(slopes) if has_slopes else None, _s())
-        native.check(rc, "neox_flash_bwd")
+        gs = (ctypes.c_longlong * 9)(dq.stride(0), dq.stride(1), dq.stride(2), dk.stride(0), dk.stride(1), dk.stride(2),
+                                     dv.stride(0), dv.stride(1), dv.stride(2))
+        _launch_bwd(q, k, v, out, do, lse, dq, dk, dv, delta, gs, sq, sk, b, hq, hkv, d, scale, causal, window,
+                    slopes if has_slopes else None)
         return dq, dk, dv, None, None, None, None
 
 
@@ -171,15 +183,8 @@ class _PackedQKVFn(torch.autograd.Function):
         ll = ctypes.c_longlong
         gs = (ctypes.c_longlong * 9)(dq.stride(0), dq.stride(1), dq.stride(2), dk.stride(0), dk.stride(1), dk.stride(2),
                                      dv.stride(0), dv.stride(1), dv.stride(2))
-        rc = L.neox_flash_bwd_strided(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(do),
-                                      native.ptr(lse), native.ptr(dq), native.ptr(dk), native.ptr(dv),
-                                      native.ptr(delta), s, s, b, h, h, d,
-                                      ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)),
-                                      ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
-                                      ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), gs,
-                                      ctypes.c_float(scale), int(causal), int(window if window is not None else -1),
-                                      native.ptr(slopes) if has_slopes else None, _s())
-        native.check(rc, "neox_flash_bwd_strided")
+        _launch_bwd(q, k, v, out, do, lse, dq, dk, dv, delta, gs, s, s, b, h, h, d, scale, causal, window,
+                    slopes if has_slopes else None)
         if rot:
             rc = L.neox_rope_qk_inplace(native.ptr(dq), native.ptr(dk), native.ptr(c), native.ptr(sn), s, b, h, h, rot,
                                         ll(dq.stride(0)), ll(dq.stride(1)), ll(dq.stride(2)),
