@@ -150,9 +150,7 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint8_t* sK = smem + C::OFF_R0;
     uint8_t* sV = smem + C::OFF_R1;
     uint8_t* sStage = smem + C::OFF_S;   // stage st: Q at st*2*TILE, dO at st*2*TILE + TILE
-    float* s_lse = reinterpret_cast<float*>(smem + C::OFF_MISC);   // [16 warps][32] (log2 domain)
-    float* s_dl = s_lse + 16 * CPT;                                 // [16 warps][32]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_dl + 16 * CPT);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_MISC);
     uint64_t* kv_full = bars;            // 1
     uint64_t* st_full = bars + 1;        // 2  Q_i / dO_i landed
     uint64_t* st_empty = bars + 3;       // 2
@@ -275,28 +273,32 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             umma_commit(acc_full);
         }
     } else if (warp >= 4) {
-        const int cw = warp - 4;
-        const int part = cw >> 2;                  // which 32-query slice of the block this warp owns
+        const int part = (warp - 4) >> 2;                  // which 32-query slice of the block this warp owns
         const int qtr = warp & 3;
         const int row = qtr * 32 + lane;           // key row inside the tile
-        float* my_lse = s_lse + cw * CPT;          // per-warp staging: only warp-level syncs are needed
-        float* my_dl = s_dl + cw * CPT;
         const uint32_t lane_base = uint32_t(qtr * 32) << 16;
         const uint32_t col0 = lane_base + part * CPT;
         const int kv = kv0 + row;
         bool ok = true;
+        auto load_stats = [&](int it, float& lse_o, float& dl_o) {
+            const int hh = hk * G + it / nq;
+            const int q = (ib + it % nq) * 128 + part * CPT + lane;
+            const size_t idx = ((size_t)bb * p.hq + hh) * p.sq + min(q, p.sq - 1);
+            const float a = p.lse[idx], d = p.delta[idx];
+            lse_o = (q < p.sq) ? a * LOG2E : INFINITY;
+            dl_o = (q < p.sq) ? d : 0.f;
+        };
+        float lse_n = INFINITY, dl_n = 0.f;
+        if (niter > 0) load_stats(0, lse_n, dl_n);
         for (int it = 0; it < niter; ++it) {
             const int h = hk * G + it / nq;
             const int qb0 = (ib + it % nq) * 128;
             const int qc0 = qb0 + part * CPT;
-            __syncwarp();
-            {
-                const int q = qc0 + lane;
-                const size_t idx = ((size_t)bb * p.hq + h) * p.sq + q;
-                my_lse[lane] = (q < p.sq) ? p.lse[idx] * LOG2E : INFINITY;
-                my_dl[lane] = (q < p.sq) ? p.delta[idx] : 0.f;
-            }
-            __syncwarp();
+            // lane l holds the statistics of query column l of this warp's slice (broadcast with shuffles below).
+            // They were loaded during the previous iteration: a global load issued here would sit on the critical
+            // path of the block (measured: ~2800 cycles).
+            const float lse_l = lse_n, dl_l = dl_n;
+            if (it + 1 < niter) load_stats(it + 1, lse_n, dl_n);
             const bool need_mask = (kv0 + 127 >= p.sk) || (qb0 + 127 >= p.sq) || (p.causal && kv0 + 127 > qb0 + off) ||
                                    (p.window >= 0 && kv0 < qb0 + 127 + off - p.window);
             const float slope = p.slopes ? p.slopes[h] * LOG2E : 0.f;
@@ -313,7 +315,7 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 wait_ld_dep(r);
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) {
-                    float t = fmaf(__uint_as_float(r[c]), p.scale_log2, -my_lse[c]);
+                    float t = fmaf(__uint_as_float(r[c]), p.scale_log2, -__shfl_sync(0xffffffffu, lse_l, c));
                     if (p.slopes) t -= slope * fabsf((float)(qc0 + c + off - kv));
                     float e = ex2(t);
                     if (need_mask) {
@@ -346,8 +348,9 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float d0 = pf[2 * c] * (__uint_as_float(r[2 * c]) - my_dl[2 * c]);
-                    const float d1 = pf[2 * c + 1] * (__uint_as_float(r[2 * c + 1]) - my_dl[2 * c + 1]);
+                    const float d0 = pf[2 * c] * (__uint_as_float(r[2 * c]) - __shfl_sync(0xffffffffu, dl_l, 2 * c));
+                    const float d1 =
+                        pf[2 * c + 1] * (__uint_as_float(r[2 * c + 1]) - __shfl_sync(0xffffffffu, dl_l, 2 * c + 1));
                     pk[c] = pack16<FP16>(d0, d1);
                 }
                 tmem_st_32x16(TM_DPT + col0, pk);
