@@ -91,29 +91,32 @@ __device__ __forceinline__ void wait_ld_dep(uint32_t (&r)[32]) {
 }
 
 // ------------------------------------------------------------------ delta
+// One thread per 8 elements (16-byte loads), d / 8 threads per row, rows packed into the warp; the partial sums of a row
+// are combined with shuffles inside groups of 16 lanes (d / 8 <= 16).
 template <bool FP16>
-__global__ void __launch_bounds__(256) delta2_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout,
-                                                     float* __restrict__ delta, int sq, int b, int hq, int d) {
-    const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);  // row over [sq, b, hq]
-    const long long rows = (long long)sq * b * hq;
-    if (row >= rows) return;
-    const int lane = threadIdx.x & 31;
-    const uint32_t* op = reinterpret_cast<const uint32_t*>(o + row * d);
-    const uint32_t* gp = reinterpret_cast<const uint32_t*>(dout + row * d);
+__global__ void __launch_bounds__(256) delta2_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
+                                                     float* __restrict__ delta, long long rows, int sq, int b, int hq,
+                                                     int tpr) {
+    const int sub = threadIdx.x & 15;                                  // position inside the 16-lane group
+    const long long row = (blockIdx.x * 256LL + threadIdx.x) >> 4;     // one row per 16-lane group
     float s = 0.f;
-    for (int c = lane; c < d / 2; c += 32) {
-        const uint32_t a = op[c], g = gp[c];
-        if (FP16) {
-            const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a));
-            const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&g));
-            s += fa.x * fg.x + fa.y * fg.y;
-        } else {
-            s += bf16_lo(a) * bf16_lo(g) + bf16_hi(a) * bf16_hi(g);
+    if (row < rows && sub < tpr) {
+        const uint4 a = o[row * tpr + sub], g = dout[row * tpr + sub];
+        const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (FP16) {
+                const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&av[k]));
+                const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[k]));
+                s += fa.x * fg.x + fa.y * fg.y;
+            } else {
+                s += bf16_lo(av[k]) * bf16_lo(gv[k]) + bf16_hi(av[k]) * bf16_hi(gv[k]);
+            }
         }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) {
+    for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (row < rows && sub == 0) {
         const int h = (int)(row % hq);
         const long long t = row / hq;
         const int bb = (int)(t % b);
@@ -280,15 +283,16 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t col0 = lane_base + part * CPT;
         const int kv = kv0 + row;
         bool ok = true;
+        // raw loads only: the first instruction that touches a loaded value stalls the warp until the load returns,
+        // so nothing is computed from them before the iteration that uses them
         auto load_stats = [&](int it, float& lse_o, float& dl_o) {
             const int hh = hk * G + it / nq;
             const int q = (ib + it % nq) * 128 + part * CPT + lane;
             const size_t idx = ((size_t)bb * p.hq + hh) * p.sq + min(q, p.sq - 1);
-            const float a = p.lse[idx], d = p.delta[idx];
-            lse_o = (q < p.sq) ? a * LOG2E : INFINITY;
-            dl_o = (q < p.sq) ? d : 0.f;
+            lse_o = __ldg(p.lse + idx);
+            dl_o = __ldg(p.delta + idx);
         };
-        float lse_n = INFINITY, dl_n = 0.f;
+        float lse_n = 0.f, dl_n = 0.f;
         if (niter > 0) load_stats(0, lse_n, dl_n);
         for (int it = 0; it < niter; ++it) {
             const int h = hk * G + it / nq;
@@ -297,7 +301,8 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             // lane l holds the statistics of query column l of this warp's slice (broadcast with shuffles below).
             // They were loaded during the previous iteration: a global load issued here would sit on the critical
             // path of the block (measured: ~2800 cycles).
-            const float lse_l = lse_n, dl_l = dl_n;
+            const bool qin = qc0 + lane < p.sq;
+            const float lse_l = qin ? lse_n * LOG2E : INFINITY, dl_l = qin ? dl_n : 0.f;
             if (it + 1 < niter) load_stats(it + 1, lse_n, dl_n);
             const bool need_mask = (kv0 + 127 >= p.sk) || (qb0 + 127 >= p.sq) || (p.causal && kv0 + 127 > qb0 + off) ||
                                    (p.window >= 0 && kv0 < qb0 + 127 + off - p.window);
@@ -313,18 +318,22 @@ flash_bwd2_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 uint32_t r[32];
                 tmem_ld_32x32(TM_ST + col0, r);
                 wait_ld_dep(r);
+                // The compute warps are bound by instruction issue (four warps per scheduler, every predicated-off
+                // instruction still takes a slot), so the common unmasked block gets a loop of its own.
+                if (!(need_mask || p.slopes)) {
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) {
-                    float t = fmaf(__uint_as_float(r[c]), p.scale_log2, -__shfl_sync(0xffffffffu, lse_l, c));
-                    if (p.slopes) t -= slope * fabsf((float)(qc0 + c + off - kv));
-                    float e = ex2(t);
-                    if (need_mask) {
+                    for (int c = 0; c < CPT; ++c)
+                        pf[c] = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -__shfl_sync(0xffffffffu, lse_l, c)));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) {
+                        float t = fmaf(__uint_as_float(r[c]), p.scale_log2, -__shfl_sync(0xffffffffu, lse_l, c));
                         const int qpos = qc0 + c + off;
+                        if (p.slopes) t -= slope * fabsf((float)(qpos - kv));
                         const bool dead = (kv >= p.sk) || (p.causal && kv > qpos) ||
                                           (p.window >= 0 && kv < qpos - p.window);
-                        if (dead) e = 0.f;       // query rows beyond sq have lse = +inf, i.e. e = 0 already
+                        pf[c] = dead ? 0.f : ex2(t);   // query rows beyond sq have lse = +inf, i.e. 0 already
                     }
-                    pf[c] = e;
                 }
                 uint32_t pk[16];
 #pragma unroll
@@ -566,18 +575,19 @@ flash_bwd2_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_empty);
+                if (!(need_mask || p.slopes)) {
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) {
-                    const int kvp = kc0 + c;
-                    float t = fmaf(__uint_as_float(r[c]), p.scale_log2, -lse2);
-                    if (p.slopes) t -= slope * fabsf((float)(qpos - kvp));
-                    float e = ex2(t);
-                    if (need_mask) {
+                    for (int c = 0; c < CPT; ++c) pf[c] = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -lse2));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) {
+                        const int kvp = kc0 + c;
+                        float t = fmaf(__uint_as_float(r[c]), p.scale_log2, -lse2);
+                        if (p.slopes) t -= slope * fabsf((float)(qpos - kvp));
                         const bool dead = (kvp >= p.sk) || (p.causal && kvp > qpos) ||
                                           (p.window >= 0 && kvp < qpos - p.window);
-                        if (dead) e = 0.f;
+                        pf[c] = dead ? 0.f : ex2(t);
                     }
-                    pf[c] = e;
                 }
             }
             const uint32_t TM_DPB = TM_DP + (j & 1) * 128;
@@ -685,12 +695,14 @@ extern "C" int neox_flash_bwd2_strided(const void* q, const void* k, const void*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const long long rows = (long long)sq * b * hq;
     const bool h16 = dtype == 2;
+    if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return NEOX_ERR_ALIGN;
+    const unsigned dblocks = (unsigned)((rows + 15) / 16);
     if (h16)
-        delta2_kernel<true><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-            static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(dout), delta_ws, sq, b, hq, d);
+        delta2_kernel<true><<<dblocks, 256, 0, st>>>(static_cast<const uint4*>(out), static_cast<const uint4*>(dout),
+                                                     delta_ws, rows, sq, b, hq, d / 8);
     else
-        delta2_kernel<false><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-            static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(dout), delta_ws, sq, b, hq, d);
+        delta2_kernel<false><<<dblocks, 256, 0, st>>>(static_cast<const uint4*>(out), static_cast<const uint4*>(dout),
+                                                      delta_ws, rows, sq, b, hq, d / 8);
     const long long o_sh = d, o_sb = (long long)hq * d, o_ss = (long long)b * hq * d;
     CUtensorMap t[4];
     int rc = 0;
