@@ -156,6 +156,11 @@ class Tee:
 class NeoXArgs:
     """All configuration of one run; attribute access by key name (``args.hidden_size``)."""
 
+    @staticmethod
+    def known_keys():
+        """Every declared argument name (the schema table)."""
+        return list(FIELDS.keys())
+
     def __init__(self, **kwargs):
         unknown = [k for k in kwargs if k not in FIELDS]
         if unknown:

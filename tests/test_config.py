@@ -123,18 +123,64 @@ def test_hostfile_resource_pool(tmp_path):
     assert a.global_num_gpus == 8
 
 
-@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(CONFIGS, "*.yml"))))
-def test_every_shipped_config_loads(path):
-    base = os.path.basename(path)
-    if base in ("local_setup.yml", "cpu_mock_config.yml"):
-        pytest.skip("overlay file")
+def _config_keys(path):
     with open(path) as fh:
-        keys = {k.replace("-", "_") for k in (yaml.load(fh, Loader=yaml.FullLoader) or {})}
-    files = [path]
+        return {k.replace("-", "_") for k in (yaml.load(fh, Loader=yaml.FullLoader) or {})}
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(CONFIGS, "**", "*.yml"), recursive=True)),
+                         ids=lambda p: os.path.relpath(p, CONFIGS))
+def test_every_shipped_config_loads(path):
+    """Model files load (with the overlays they are meant to be combined with); overlays only contain declared keys."""
+    keys = _config_keys(path)
     if "num_layers" not in keys:
-        pytest.skip("overlay file")
-    if not keys & {"data_path", "train_data_paths", "vocab_file", "save", "load"}:
+        unknown = keys - set(NeoXArgs.known_keys())
+        assert not unknown, f"{path}: undeclared keys {sorted(unknown)}"
+        return
+    files = [path]
+    if "optimizer" not in keys and os.path.basename(os.path.dirname(path)) == "llama":
+        files.append(os.path.join(CONFIGS, "llama", "train_config.yml"))
+    have = set().union(*[_config_keys(f) for f in files])
+    if not have & {"data_path", "train_data_paths", "vocab_file", "save", "load"}:
         files.append(os.path.join(CONFIGS, "local_setup.yml"))
-    over = {} if "global_num_gpus" in keys else {"global_num_gpus": 8}
+        have |= _config_keys(files[-1])
+    over = {} if "global_num_gpus" in have else {"global_num_gpus": 8}
+    if not have & {"train_micro_batch_size_per_gpu", "train_batch_size"}:
+        over["train_micro_batch_size_per_gpu"] = 1
+    if not have & {"checkpoint_factor", "extra_save_iters"}:
+        over["checkpoint_factor"] = 1000
     a = NeoXArgs.from_ymls(files, overwrite_values=over)
     assert a.num_layers > 0 and a.train_batch_size > 0
+    # the precision named in the file is the one the run gets
+    want = "fp16" if (keys & {"fp16"}) and not (keys & {"bf16"}) and "precision" not in keys else None
+    if want:
+        assert a.precision == "fp16", (path, a.precision)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(CONFIGS, "**", "*.json"), recursive=True)),
+                         ids=lambda p: os.path.relpath(p, CONFIGS))
+def test_json_configs_parse(path):
+    import json
+    with open(path) as fh:
+        assert isinstance(json.load(fh), dict)
+
+
+def test_every_argument_used_in_code_is_declared():
+    """Scan the package for ``neox_args.<name>`` / ``args.<name>`` reads and check each name against the schema
+    (the check the reference runs in tests/neox_args/test_neoxargs_usage.py:24-85)."""
+    import re
+    # attributes attached at run time (objects, not configuration)
+    runtime = {"tokenizer", "tensorboard_writer", "comet_experiment", "py"}
+    known = set(NeoXArgs.known_keys()) | set(dir(NeoXArgs)) | runtime
+    pat = re.compile(r"\bneox_args\.([a-zA-Z_][a-zA-Z0-9_]*)")
+    root = os.path.join(os.path.dirname(CONFIGS), "gpt_neox_b200")
+    missing = {}
+    for dirpath, _, files in os.walk(root):
+        for f in files:
+            if not f.endswith(".py"):
+                continue
+            with open(os.path.join(dirpath, f)) as fh:
+                for name in pat.findall(fh.read()):
+                    if name not in known:
+                        missing.setdefault(name, []).append(os.path.relpath(os.path.join(dirpath, f), root))
+    assert not missing, missing
