@@ -54,9 +54,15 @@ def attention_ref(q, k, v, causal=True, softmax_scale=None, window=None, alibi_s
 
 
 def kernel_ok(q, k, v, bias=None) -> bool:
-    return (q.is_cuda and native.available() and q.dtype == torch.bfloat16 and bias is None
-            and q.shape[-1] in (64, 96, 128) and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
-            and q.shape[0] >= 1)
+    if not (q.is_cuda and native.available()):
+        return False
+    ok = (q.dtype in (torch.bfloat16, torch.float16) and k.dtype == q.dtype and v.dtype == q.dtype and bias is None
+          and q.shape[-1] in (64, 96, 128) and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+          and q.shape[0] >= 1)
+    if not ok:
+        from .linear import warn_fallback
+        warn_fallback("flash_attention", f"dtype {q.dtype}, head size {q.shape[-1]}, additive bias {bias is not None}")
+    return ok
 
 
 def _launch_fwd(q, k, v, out, lse, sq, sk, b, hq, hkv, d, scale, causal, window, slopes):
@@ -194,7 +200,7 @@ class _PackedQKVFn(torch.autograd.Function):
 
 
 def packed_qkv_ok(mixed, head_dim) -> bool:
-    return (mixed.is_cuda and native.available() and mixed.dtype == torch.bfloat16 and mixed.dim() == 4
+    return (mixed.is_cuda and native.available() and mixed.dtype in (torch.bfloat16, torch.float16) and mixed.dim() == 4
             and mixed.is_contiguous() and head_dim in (64, 96, 128) and mixed.shape[-1] == 3 * head_dim
             and have_flash_kernel())
 

@@ -158,7 +158,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = F8 ? make_idesc_f8(2 * BM, BN, p.a_mn, p.b_mn, x.a_fmt, x.b_fmt)
-                                      : make_idesc_bf16(2 * BM, BN, p.a_mn, p.b_mn);
+                                      : make_idesc_16(2 * BM, BN, p.a_mn, p.b_mn, p.h16);
             // operand descriptors: constant upper half; lower half = stage base + k-step offset (16-byte units).
             // K-major: the next 32 bytes of K lie 32 bytes along the swizzled row; MN-major: they are the next
             // 16 (bf16) or 32 (fp8) rows of 128 bytes, with chunks of the MN dimension CHUNK_BYTES apart.
@@ -256,7 +256,7 @@ template <bool F8>
 int launch_pair(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
                 int a_mn, int b_mn, PairScales x, int d_fp32, const void* bias, const void* add, long long ldadd,
                 int add_fp32, void* preact, long long ldpre, const void* aux, long long ldaux, int act, float alpha,
-                cudaStream_t stream) {
+                cudaStream_t stream, int h16 = 0) {
     constexpr int BKE = F8 ? 128 : 64, MNC = F8 ? 128 : 64, PITCH = F8 ? 16 : 8;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % PITCH) || (ldb % PITCH))
@@ -285,6 +285,7 @@ int launch_pair(const void* A, const void* B, void* D, int M, int N, int K, long
     p.act = act; p.alpha = alpha;
     p.status = status;
     p.row_ptrs = nullptr;
+    p.h16 = h16 ? 1 : 0;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     bool vec = al16(D) && (ldd % 8 == 0);
     if (bias) vec = vec && al16(bias);
@@ -325,6 +326,16 @@ extern "C" int neox_gemm_bf16_2cta(const void* A, const void* B, void* D, int M,
     return launch_pair<false>(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, PairScales{nullptr, nullptr, 0, 0, 0}, d_fp32,
                               bias, add, ldadd, add_fp32, preact, ldpre, aux, ldaux, act, alpha,
                               static_cast<cudaStream_t>(stream_));
+}
+
+// Same with the 16-bit type chosen by h16 (0 = bf16, 1 = fp16).
+extern "C" int neox_gemm_16_2cta(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
+                                 const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
+                                 const void* aux, long long ldaux, int act, float alpha, int h16, void* stream_) {
+    return launch_pair<false>(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, PairScales{nullptr, nullptr, 0, 0, 0}, d_fp32,
+                              bias, add, ldadd, add_fp32, preact, ldpre, aux, ldaux, act, alpha,
+                              static_cast<cudaStream_t>(stream_), h16);
 }
 
 // Same contract as neox_gemm_fp8.

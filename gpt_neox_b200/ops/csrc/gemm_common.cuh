@@ -38,6 +38,7 @@ struct GemmParams {
     // optional per-row destination table (bf16 output only): row r is stored at address row_ptrs[r] instead of
     // D + r * ldd -- the rows of one GEMM can then land in different buffers, including peers' memory
     const unsigned long long* row_ptrs;
+    int h16 = 0;   // 16-bit storage type of the operands, D, bias, add, preact, aux: 0 = bf16, 1 = fp16
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
@@ -50,8 +51,9 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
     n_blk = in_group / gsize;
 }
 
-// Apply the fused epilogue to 32 consecutive columns of one output row.
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row, int col0, const GemmParams& p) {
+// Apply the fused epilogue to 32 consecutive columns of one output row (H16: fp16 storage, else bf16).
+template <bool H16>
+__device__ __forceinline__ void epilogue_chunk_t(const uint32_t (&r)[32], int row, int col0, const GemmParams& p) {
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -65,8 +67,8 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
                 uint32_t w[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    v[j * 8 + t * 2] += bf16_lo(w[t]);
-                    v[j * 8 + t * 2 + 1] += bf16_hi(w[t]);
+                    v[j * 8 + t * 2] += lo_16<H16>(w[t]);
+                    v[j * 8 + t * 2 + 1] += hi_16<H16>(w[t]);
                 }
             }
         }
@@ -75,10 +77,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint4 q;
-                q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-                q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-                q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-                q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+                q.x = pack_16x2<H16>(v[j * 8 + 0], v[j * 8 + 1]);
+                q.y = pack_16x2<H16>(v[j * 8 + 2], v[j * 8 + 3]);
+                q.z = pack_16x2<H16>(v[j * 8 + 4], v[j * 8 + 5]);
+                q.w = pack_16x2<H16>(v[j * 8 + 6], v[j * 8 + 7]);
                 o[j] = q;
             }
         }
@@ -93,8 +95,8 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
                 uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    v[j * 8 + t * 2] *= dgelu_tanh(bf16_lo(w[t]));
-                    v[j * 8 + t * 2 + 1] *= dgelu_tanh(bf16_hi(w[t]));
+                    v[j * 8 + t * 2] *= dgelu_tanh(lo_16<H16>(w[t]));
+                    v[j * 8 + t * 2 + 1] *= dgelu_tanh(hi_16<H16>(w[t]));
                 }
             }
         }
@@ -123,8 +125,8 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
                     uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
-                        v[j * 8 + t * 2] += bf16_lo(w[t]);
-                        v[j * 8 + t * 2 + 1] += bf16_hi(w[t]);
+                        v[j * 8 + t * 2] += lo_16<H16>(w[t]);
+                        v[j * 8 + t * 2 + 1] += hi_16<H16>(w[t]);
                     }
                 }
             }
@@ -145,10 +147,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint4 q;
-                q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-                q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-                q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-                q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+                q.x = pack_16x2<H16>(v[j * 8 + 0], v[j * 8 + 1]);
+                q.y = pack_16x2<H16>(v[j * 8 + 2], v[j * 8 + 3]);
+                q.z = pack_16x2<H16>(v[j * 8 + 4], v[j * 8 + 5]);
+                q.w = pack_16x2<H16>(v[j * 8 + 6], v[j * 8 + 7]);
                 o[j] = q;
             }
         }
@@ -158,20 +160,24 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row,
             const int col = col0 + i;
             if (col >= p.N) break;
             float x = v[i];
-            if (p.bias) x += __bfloat162float(p.bias[col]);
-            if (p.preact) p.preact[(long long)row * p.ldpre + col] = __float2bfloat16(x);
+            if (p.bias) x += ld_16<H16>(p.bias, col);
+            if (p.preact) st_16<H16>(p.preact, (long long)row * p.ldpre + col, x);
             if (p.act == 1) x = gelu_tanh(x);
-            else if (p.act == 2) x *= dgelu_tanh(__bfloat162float(p.aux[(long long)row * p.ldaux + col]));
+            else if (p.act == 2) x *= dgelu_tanh(ld_16<H16>(p.aux, (long long)row * p.ldaux + col));
             if (p.add) {
                 if (p.add_fp32) x += reinterpret_cast<const float*>(p.add)[(long long)row * p.ldadd + col];
-                else x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.add)[(long long)row * p.ldadd + col]);
+                else x += ld_16<H16>(p.add, (long long)row * p.ldadd + col);
             }
             if (p.d_fp32) reinterpret_cast<float*>(p.D)[(long long)row * p.ldd + col] = x;
-            else if (p.row_ptrs) reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row])[col] = __float2bfloat16(x);
-            else reinterpret_cast<__nv_bfloat16*>(p.D)[(long long)row * p.ldd + col] = __float2bfloat16(x);
+            else if (p.row_ptrs) st_16<H16>(reinterpret_cast<void*>(p.row_ptrs[row]), col, x);
+            else st_16<H16>(p.D, (long long)row * p.ldd + col, x);
         }
     }
 }
 
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], int row, int col0, const GemmParams& p) {
+    if (p.h16) epilogue_chunk_t<true>(r, row, col0, p);
+    else epilogue_chunk_t<false>(r, row, col0, p);
+}
 
 }  // namespace gemm

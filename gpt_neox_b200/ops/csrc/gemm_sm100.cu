@@ -114,7 +114,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+            const uint32_t idesc = make_idesc_16(BM, BN, p.a_mn, p.b_mn, p.h16);
             // operand descriptors: constant upper half; lower half = stage base + k-step offset (16-byte units), so
             // the issuing thread spends one add per operand per MMA.  K-major: the next 16 elements of K are 32
             // bytes along the swizzled row; MN-major: the next 16 rows of 128 bytes, with 64-element chunks of the
@@ -311,6 +311,11 @@ extern "C" int neox_gemm_bf16_rowmap(const void* A, const void* B, void* D, int 
                                      const void* aux, long long ldaux, int act, float alpha, const void* row_ptrs,
                                      void* stream_);
 
+extern "C" int neox_gemm_16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                            long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias, const void* add,
+                            long long ldadd, int add_fp32, void* preact, long long ldpre, const void* aux,
+                            long long ldaux, int act, float alpha, const void* row_ptrs, int h16, void* stream_);
+
 extern "C" int neox_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
                               long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
                               const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
@@ -319,13 +324,22 @@ extern "C" int neox_gemm_bf16(const void* A, const void* B, void* D, int M, int 
                                  ldpre, aux, ldaux, act, alpha, nullptr, stream_);
 }
 
-// row_ptrs (device array of M addresses, or NULL): destination of every output row (bf16 output; each address
+// row_ptrs (device array of M addresses, or NULL): destination of every output row (16-bit output; each address
 // 16-byte aligned and valid for N elements).  With it D may be NULL.
 extern "C" int neox_gemm_bf16_rowmap(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
                                      long long ldb, long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias,
                                      const void* add, long long ldadd, int add_fp32, void* preact, long long ldpre,
                                      const void* aux, long long ldaux, int act, float alpha, const void* row_ptrs,
                                      void* stream_) {
+    return neox_gemm_16(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, d_fp32, bias, add, ldadd, add_fp32, preact, ldpre,
+                        aux, ldaux, act, alpha, row_ptrs, 0, stream_);
+}
+
+// The general entry point: h16 = 0 for bf16, 1 for fp16 (operands and every 16-bit epilogue tensor share the type).
+extern "C" int neox_gemm_16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                            long long ldd, int a_mn, int b_mn, int d_fp32, const void* bias, const void* add,
+                            long long ldadd, int add_fp32, void* preact, long long ldpre, const void* aux,
+                            long long ldaux, int act, float alpha, const void* row_ptrs, int h16, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (row_ptrs && d_fp32) return NEOX_ERR_SHAPE;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -355,6 +369,7 @@ extern "C" int neox_gemm_bf16_rowmap(const void* A, const void* B, void* D, int 
     p.act = act; p.alpha = alpha;
     p.status = status;
     p.row_ptrs = static_cast<const unsigned long long*>(row_ptrs);
+    p.h16 = h16 ? 1 : 0;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     bool vec = row_ptrs ? (N % 8 == 0) : (al16(D) && (ldd % 8 == 0));
     if (bias) vec = vec && al16(bias);

@@ -10,6 +10,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace sm100 {
@@ -277,6 +278,13 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_bf16(int M, int N, int a
     return d;
 }
 
+// Same for either 16-bit operand type: h16 = 1 selects fp16 (format code 0), 0 selects bf16 (format code 1).
+__host__ __device__ __forceinline__ uint32_t make_idesc_16(int M, int N, int a_mn, int b_mn, int h16) {
+    uint32_t d = make_idesc_bf16(M, N, a_mn, b_mn);
+    if (h16) d &= ~((1u << 7) | (1u << 10));
+    return d;
+}
+
 // Instruction descriptor for kind::f8f6f4 with fp8 A/B (format 0 = E4M3, 1 = E5M2) and fp32 accumulate.
 __host__ __device__ __forceinline__ uint32_t make_idesc_f8(int M, int N, int a_mn, int b_mn, int a_fmt, int b_fmt) {
     uint32_t d = 0;
@@ -371,5 +379,34 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+// 16-bit pairs of either storage type (H16: fp16, else bf16)
+template <bool H16>
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi) {
+    if (H16) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    return pack_bf16x2(lo, hi);
+}
+template <bool H16>
+__device__ __forceinline__ float lo_16(uint32_t v) {
+    if (H16) return __low2float(*reinterpret_cast<const __half2*>(&v));
+    return bf16_lo(v);
+}
+template <bool H16>
+__device__ __forceinline__ float hi_16(uint32_t v) {
+    if (H16) return __high2float(*reinterpret_cast<const __half2*>(&v));
+    return bf16_hi(v);
+}
+template <bool H16>
+__device__ __forceinline__ float ld_16(const void* base, long long idx) {
+    if (H16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+}
+template <bool H16>
+__device__ __forceinline__ void st_16(void* base, long long idx, float x) {
+    if (H16) reinterpret_cast<__half*>(base)[idx] = __float2half_rn(x);
+    else reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16(x);
+}
 
 }  // namespace sm100

@@ -1,4 +1,4 @@
-"""bf16 GEMM front-end for the tcgen05 kernel in ``csrc/gemm_sm100.cu``.
+"""16-bit (bf16 / fp16) GEMM front-end for the tcgen05 kernels in ``csrc/gemm_sm100.cu`` and ``csrc/gemm_2cta_sm100.cu``.
 
 ``gemm(a, b, ...)`` computes ``epilogue(alpha * op(a) @ op(b))`` where each operand is given as a
 2-D tensor and a flag telling whether it is stored "K-major" (contraction index contiguous) or
@@ -45,7 +45,7 @@ def gemm_ref(a, b, a_mn=False, b_mn=False, out_dtype=torch.bfloat16, bias=None, 
     v = alpha * (A @ B)
     if bias is not None:
         v = v + bias.float()
-    pre = v.to(torch.bfloat16) if want_preact else None
+    pre = v.to(a.dtype if a.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16) if want_preact else None
     if act == ACT_GELU:
         v = gelu_tanh_ref(v)
     elif act == ACT_DGELU:
@@ -103,7 +103,10 @@ def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=
                 out.copy_(r[0]); return out, r[1]
             out.copy_(r); return out
         return r
-    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
+    dt = a.dtype
+    assert dt in (torch.bfloat16, torch.float16) and b.dtype == dt, "tcgen05 GEMM takes two bf16 or two fp16 operands"
+    if out is None and out_dtype == torch.bfloat16:
+        out_dtype = dt                      # the default output type is the operand type
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     if a_mn:
         K, M = a.shape
@@ -116,16 +119,19 @@ def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
     if out is None:
         out = torch.empty(M, N, device=a.device, dtype=out_dtype)
-    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
-    pre = torch.empty(M, N, device=a.device, dtype=torch.bfloat16) if want_preact else None
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (dt, torch.float32)
+    pre = torch.empty(M, N, device=a.device, dtype=dt) if want_preact else None
     if add is not None:
-        assert add.shape == (M, N) and add.stride(1) == 1 and add.dtype in (torch.bfloat16, torch.float32)
+        assert add.shape == (M, N) and add.stride(1) == 1 and add.dtype in (dt, torch.float32)
     if bias is not None:
-        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+        assert bias.dtype == dt and bias.numel() == N and bias.is_contiguous()
     if act == ACT_DGELU:
-        assert aux is not None and aux.shape == (M, N) and aux.dtype == torch.bfloat16 and aux.stride(1) == 1
+        assert aux is not None and aux.shape == (M, N) and aux.dtype == dt and aux.stride(1) == 1
     L = native.lib()
-    fn = L.neox_gemm_bf16_2cta if use_pair_kernel(M, N, K) else L.neox_gemm_bf16
+    h16 = int(dt == torch.float16)
+    pair = use_pair_kernel(M, N, K)
+    tail = (h16, ctypes.c_void_p(native.stream_ptr())) if pair else (None, h16, ctypes.c_void_p(native.stream_ptr()))
+    fn = L.neox_gemm_16_2cta if pair else L.neox_gemm_16
     rc = fn(
         native.ptr(a), native.ptr(b), native.ptr(out), M, N, K,
         ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(out.stride(0)),
@@ -134,6 +140,6 @@ def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=
         int(add is not None and add.dtype == torch.float32),
         native.ptr(pre), ctypes.c_longlong(pre.stride(0) if pre is not None else 0),
         native.ptr(aux), ctypes.c_longlong(aux.stride(0) if aux is not None else 0),
-        int(act), ctypes.c_float(alpha), ctypes.c_void_p(native.stream_ptr()))
-    native.check(rc, "neox_gemm_bf16")
+        int(act), ctypes.c_float(alpha), *tail)
+    native.check(rc, "neox_gemm_16")
     return (out, pre) if want_preact else out

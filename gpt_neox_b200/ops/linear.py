@@ -27,9 +27,26 @@ def notify_grad_ready(weight):
         cb()
 
 
+_warned = set()
+
+
+def warn_fallback(what, why):
+    """A CUDA tensor that misses the native kernel is a performance bug worth one line in the log (never silent)."""
+    key = (what, why)
+    if key not in _warned:
+        _warned.add(key)
+        import warnings
+        warnings.warn(f"{what}: CUDA input falls back to the library / eager path ({why})", RuntimeWarning, stacklevel=3)
+
+
 def kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.is_cuda and native.available() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous())
+    if not (x.is_cuda and native.available()):
+        return False
+    ok = (x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype
+          and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous())
+    if not ok:
+        warn_fallback("linear", f"dtypes {x.dtype}/{w.dtype}, shapes {tuple(x.shape)} x {tuple(w.shape)}")
+    return ok
 
 
 class _LinearFn(torch.autograd.Function):
@@ -49,7 +66,7 @@ class _LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         res2 = residual.reshape(-1, N) if residual is not None else None
         need_pre = act == "gelu" and any(ctx.needs_input_grad[:3])
-        use_k = kernel_ok(x2, weight) and (bias is None or bias.dtype == torch.bfloat16)
+        use_k = kernel_ok(x2, weight) and (bias is None or bias.dtype == x2.dtype)
         ctx.use_k = use_k
         pre = None
         if use_k:
@@ -89,7 +106,7 @@ class _LinearFn(torch.autograd.Function):
             from .functional import dgelu_mul
             g2 = dgelu_mul(g2, pre)
         gx = gw = gb = None
-        if ctx.use_k and g2.dtype == torch.bfloat16:
+        if ctx.use_k and g2.dtype == x2.dtype:
             if ctx.needs_input_grad[0]:
                 if aux2 is not None:
                     gx = G.gemm(g2, weight, a_mn=False, b_mn=True, act=G.ACT_DGELU, aux=aux2).reshape(ctx.x_shape)

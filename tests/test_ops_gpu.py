@@ -572,3 +572,129 @@ def test_mxfp8_dual_quantise_equals_the_two_single_direction_passes(e5m2):
     sc, sr = MX.quantize_tiled(x, False, e5m2), MX.quantize_tiled(x, True, e5m2)
     assert torch.equal(tc.q, sc.q) and torch.equal(tc.sf, sc.sf) and tc.mnb == sc.mnb
     assert torch.equal(tr.q, sr.q) and torch.equal(tr.sf, sr.sf) and tr.mnb == sr.mnb
+
+
+# ------------------------------------------------------------------ fp16 operands, long persistent loops, small kernels
+@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_gemm_fp16_operands(a_mn, b_mn, pair, monkeypatch):
+    """fp16 A / B / bias / output through both tcgen05 kernels (instruction-descriptor format bit + fp16 epilogue)."""
+    monkeypatch.setattr(G, "_PAIR", pair)
+    torch.manual_seed(0)
+    M, N, K = 520, 776, 392
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.float16)
+    b = (torch.randn((K, N) if b_mn else (N, K), device=DEV) * 0.1).to(torch.float16)
+    bias = torch.randn(N, device=DEV, dtype=torch.float16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.float16)
+    got, pre = G.gemm(a, b, a_mn, b_mn, bias=bias, act=G.ACT_GELU, add=res, want_preact=True)
+    assert got.dtype == torch.float16 and pre.dtype == torch.float16
+    want, wpre = G.gemm_ref(a, b, a_mn, b_mn, bias=bias, act=G.ACT_GELU, add=res, want_preact=True, out_dtype=torch.float32)
+    _close(pre, wpre, 0.02, rtol=4e-3)           # fp16 keeps 11 bits: tighter than the bf16 cases above
+    _close(got, want, 0.02, rtol=4e-3)
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    want = G.gemm_ref(a, b, a_mn, b_mn, add=acc, out_dtype=torch.float32)
+    G.gemm(a, b, a_mn, b_mn, out=acc, add=acc)
+    _close(acc, want, 0.02, rtol=2e-3)
+    assert native.read_status() == 0
+
+
+@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 512), (8192, 6144, 1024)])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_gemm_many_tiles_per_cta(M, N, K, a_mn, b_mn, pair, monkeypatch):
+    """Problems with several tiles per persistent CTA (accumulator double-buffering, barrier phase flips over many
+    tiles, L2 tile order) against the fp32 product."""
+    monkeypatch.setattr(G, "_PAIR", pair)
+    torch.manual_seed(2)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = (torch.randn((K, N) if b_mn else (N, K), device=DEV) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    got = G.gemm(a, b, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
+    want = G.gemm_ref(a, b, a_mn, b_mn, bias=bias, out_dtype=torch.float32)
+    _close(got, want, 0.03, rtol=2e-3)
+    assert native.read_status() == 0
+
+
+@pytest.mark.parametrize("sq,sk,b,hq,hkv,d,causal", [(256, 256, 2, 4, 4, 96, True), (300, 300, 1, 4, 2, 64, True),
+                                                     (200, 328, 1, 2, 2, 128, False)])
+def test_flash_attention_fp16(sq, sk, b, hq, hkv, d, causal):
+    from gpt_neox_b200.ops import attention as A
+    torch.manual_seed(0)
+    q = torch.randn(sq, b, hq, d, device=DEV, dtype=torch.float16, requires_grad=True)
+    k = torch.randn(sk, b, hkv, d, device=DEV, dtype=torch.float16, requires_grad=True)
+    v = torch.randn(sk, b, hkv, d, device=DEV, dtype=torch.float16, requires_grad=True)
+    out = A.flash_attention(q, k, v, causal=causal)
+    assert out.dtype == torch.float16
+    g = torch.randn_like(out)
+    out.backward(g)
+    assert native.read_status() == 0
+    refl = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ref = A.attention_ref(*refl, causal, None, None, None)
+    ref.backward(g.float())
+    _close(out, ref, 1e-2)
+    for got, want in zip((q, k, v), refl):
+        _close(got.grad, want.grad, 0.01 + 0.01 * want.grad.abs().max().item(), rtol=1e-2)
+
+
+@pytest.mark.parametrize("B,T,H,N", [(2, 64, 4, 64), (1, 100, 2, 64)])
+def test_wkv6_kernel_matches_reference_scan(B, T, H, N):
+    """RWKV-6 wkv forward and backward (CUDA) against the sequential fp32 recurrence."""
+    from gpt_neox_b200.ops import wkv6 as W
+    torch.manual_seed(0)
+    C = H * N
+    mk = lambda scale=1.0: (torch.randn(B, T, C, device=DEV) * scale).to(torch.bfloat16).requires_grad_()
+    r, k, v = mk(), mk(0.5), mk()
+    w = (-torch.rand(B, T, C, device=DEV) * 2 - 0.1).to(torch.bfloat16).requires_grad_()      # log-decay, negative
+    u = (torch.randn(H, N, device=DEV) * 0.3).to(torch.bfloat16).requires_grad_()
+    y = W.wkv6(r, k, v, w, u)
+    g = torch.randn_like(y)
+    y.backward(g)
+    got = [t.grad.clone() for t in (r, k, v, w, u)]
+    ref_in = [t.detach().float().requires_grad_() for t in (r, k, v, w, u)]
+    yr = W.wkv6_ref(*ref_in)
+    yr.backward(g.float())
+    _close(y, yr, 0.05 + 0.02 * yr.abs().max().item(), rtol=2e-2)
+    for a, b_ in zip(got, ref_in):
+        _close(a, b_.grad, 0.05 + 0.03 * b_.grad.abs().max().item(), rtol=3e-2)
+
+
+def test_lion_kernel_matches_eager_update():
+    from gpt_neox_b200.optim.lion import Lion
+    torch.manual_seed(0)
+    n = 100_003
+    p0 = torch.randn(n, device=DEV)
+    grads = [torch.randn(n, device=DEV) for _ in range(3)]
+    p_gpu = torch.nn.Parameter(p0.clone())
+    out = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    p_gpu.model_out = out
+    p_cpu = torch.nn.Parameter(p0.cpu().clone())
+    o_gpu = Lion([p_gpu], lr=1e-2, betas=(0.9, 0.98), weight_decay=0.1)
+    o_cpu = Lion([p_cpu], lr=1e-2, betas=(0.9, 0.98), weight_decay=0.1)
+    for g in grads:
+        p_gpu.grad, p_cpu.grad = g.clone(), g.cpu().clone()
+        o_gpu.step()
+        o_cpu.step()
+    # a sign flip needs |m*b1 + g*(1-b1)| at rounding level: allow a handful of elements to differ by 2*lr
+    diff = (p_gpu.detach().cpu() - p_cpu.detach()).abs()
+    assert (diff > 1e-5).sum().item() <= 3, diff.max()
+    _close(out, p_gpu.detach(), 1e-2, rtol=1e-2)
+    _close(o_gpu.state[p_gpu]["exp_avg"], o_cpu.state[p_cpu]["exp_avg"], 1e-5, rtol=1e-4)
+
+
+def test_adam8bit_tracks_fp32_adam():
+    """Block-wise 8-bit optimizer states: after 20 steps on a quadratic the parameters stay close to fp32 Adam."""
+    from gpt_neox_b200.optim.adam8bit import Adam8bit
+    torch.manual_seed(0)
+    n = 4096 + 77
+    target = torch.randn(n, device=DEV)
+    p8 = torch.nn.Parameter(torch.zeros(n, device=DEV))
+    p32 = torch.nn.Parameter(torch.zeros(n, device=DEV))
+    o8 = Adam8bit([p8], lr=5e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0)
+    o32 = torch.optim.Adam([p32], lr=5e-2, betas=(0.9, 0.95), eps=1e-8)
+    for _ in range(20):
+        for p, o in ((p8, o8), (p32, o32)):
+            p.grad = (p.detach() - target) * (1 + 0.1 * torch.randn(n, device=DEV, generator=None))
+            o.step()
+    assert (p8 - p32).abs().max().item() < 0.15 and (p8 - target).norm() < 0.8 * target.norm()
+    st = o8.state[p8]
+    assert any(t.dtype in (torch.int8, torch.uint8) for t in st.values() if torch.is_tensor(t))

@@ -1,0 +1,24 @@
+"""Whole-model training runs on one GPU (child processes, so each gets a fresh process group and CUDA context)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from common import ROOT, free_port
+
+
+def _run(worker, marker, timeout=600):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), WORLD_SIZE="1", RANK="0",
+               LOCAL_RANK="0")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "workers", worker)], env=env, capture_output=True,
+                       text=True, timeout=timeout)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and marker in out, out[-4000:]
+
+
+@pytest.mark.gpu
+def test_fp16_training_with_overflow_recovery():
+    """fp16 parameters on the native kernels (GEMM, flash attention, norms), dynamic loss scale: the oversized initial
+    scale overflows, those steps are skipped without touching the parameters, the scale drops and the loss falls."""
+    _run("fp16_smoke_worker.py", "FP16_SMOKE_OK")
