@@ -10,8 +10,9 @@
                     tied-weight gradient all-reduce, loss broadcast from the last stage.
 
 B200-first choices: the attention mask is never shipped between stages (kernels build masks
-in-register); activations are sent with ``batch_isend_irecv`` so the send of micro-batch *i* and
-the receive for micro-batch *i+1* are in flight while compute proceeds on the main stream.
+in-register); every pipeline link has one communicator per direction, sends are posted and never
+waited on, and the receive for micro-batch *i+1* is posted before micro-batch *i* is computed, so
+transfers run under compute (``_P2P``).
 """
 from __future__ import annotations
 
@@ -142,16 +143,41 @@ class NeoXEngine:
 
 # ============================================================================================== pipeline
 class _P2P:
-    """Adjacent-stage tensor exchange with a one-time (per direction) meta handshake."""
+    """Adjacent-stage tensor exchange.
+
+    Every (stage s -> stage s + 1) link has TWO two-rank communicators, one per direction, so that activations going
+    down the pipeline and gradients coming back never share a communication stream: a send can be posted and left
+    in flight while the stage computes (it completes when the neighbour posts its receive), a receive can be posted
+    one micro-batch ahead, and nothing deadlocks the way unpaired sends on one communicator do.  ``wait`` is only
+    called on a receive, right where its tensors are consumed; finished sends are reaped a few micro-batches later.
+    The one-time (per direction) shape handshake travels over the same communicators.
+    """
+    _links = {}          # (lo_rank, hi_rank) -> (forward-direction group, backward-direction group)
 
     def __init__(self):
         self.ranks = mpu.get_pipe_parallel_ranks()
         self.stage = mpu.get_pipe_parallel_rank()
         self.group = mpu.get_pipe_parallel_group()
         self.meta = {}
+        self.inflight = []          # (work, tensors) of posted sends
+        topo = mpu.get_topology()
+        key = (topo.pp, topo.dp, topo.mp)
+        if _P2P._links.get("topology") != key:
+            _P2P._links = {"topology": key}
+            for pipe in topo.axis_lists("pipe"):           # every rank creates every link, in the same order
+                for lo, hi in zip(pipe[:-1], pipe[1:]):
+                    _P2P._links[(lo, hi)] = (dist.new_group([lo, hi]), dist.new_group([lo, hi]))
+
+    @classmethod
+    def forget_links(cls):
+        cls._links = {}
 
     def peer(self, delta):
         return self.ranks[self.stage + delta]
+
+    def _comm(self, delta, forward_traffic):
+        me, other = self.ranks[self.stage], self.peer(delta)
+        return _P2P._links[(min(me, other), max(me, other))][0 if forward_traffic else 1]
 
     def reset(self):
         self.meta = {}
@@ -166,14 +192,16 @@ class _P2P:
         for t in tensors:
             hdr += [t.dim(), _DTYPES.index(t.dtype)] + list(t.shape) + [0] * (6 - t.dim())
         buf = torch.tensor(hdr + [0] * (64 - len(hdr)), dtype=torch.int64, device=self._device())
-        dist.send(buf, dst)
+        for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, buf, dst, group=self._comm(+1, True))]):
+            w.wait()
         self.meta[key] = ([(tuple(t.shape), t.dtype) for t in tensors], is_tuple)
 
     def _recv_meta(self, src, key):
         if key in self.meta:
             return self.meta[key]
         buf = torch.zeros(64, dtype=torch.int64, device=self._device())
-        dist.recv(buf, src)
+        for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, src, group=self._comm(-1, True))]):
+            w.wait()
         h = buf.tolist()
         n, is_tuple, pos, metas = h[0], bool(h[1]), 2, []
         for _ in range(n):
@@ -183,19 +211,36 @@ class _P2P:
         self.meta[key] = (metas, is_tuple)
         return self.meta[key]
 
-    def send_ops(self, tensors, delta):
-        dst = self.peer(delta)
-        return [dist.P2POp(dist.isend, t.contiguous(), dst) for t in tensors]
+    def post_send(self, tensors, delta):
+        """Start sending ``tensors`` to the neighbour; returns immediately (see ``reap``)."""
+        if not tensors:
+            return
+        g = self._comm(delta, forward_traffic=delta > 0)
+        ts = [t.contiguous() for t in tensors]
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, self.peer(delta), group=g) for t in ts])
+        self.inflight.append((works, ts))
+        self.reap(keep=4)
 
-    def recv_ops(self, metas, delta):
-        src = self.peer(delta)
+    def post_recv(self, metas, delta):
+        """Start receiving tensors of the given shapes from the neighbour; ``wait`` the handle where they are used."""
+        g = self._comm(delta, forward_traffic=delta < 0)
         bufs = [torch.empty(shape, dtype=dt, device=self._device()) for shape, dt in metas]
-        return bufs, [dist.P2POp(dist.irecv, b, src) for b in bufs]
+        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, self.peer(delta), group=g) for b in bufs]) if bufs else []
+        return works, bufs
 
     @staticmethod
-    def run(ops):
-        if ops:
-            for w in dist.batch_isend_irecv(ops):
+    def wait(handle):
+        works, bufs = handle
+        for w in works:
+            w.wait()
+        return bufs
+
+    def reap(self, keep=0):
+        """Release sends posted more than ``keep`` posts ago (they have long completed; ``wait`` only orders the
+        current stream after them and drops the references that kept their buffers alive)."""
+        while len(self.inflight) > keep:
+            works, _ = self.inflight.pop(0)
+            for w in works:
                 w.wait()
 
 
@@ -282,57 +327,39 @@ class PipelineEngine(NeoXEngine):
                     b.requires_grad_(True)
             return bufs
 
-        def recv_fwd():
+        def post_recv_fwd():
+            """Post the receive of the next activation (None on the first stage)."""
             if first:
                 return None
             metas, is_tuple = p2p._recv_meta(p2p.peer(-1), "act")
             state["tuple"] = is_tuple
-            bufs, ops = p2p.recv_ops(metas, -1)
-            _P2P.run(ops)
-            return prep(bufs)
+            return p2p.post_recv(metas, -1)
+
+        def take_fwd(handle):
+            return None if handle is None else prep(_P2P.wait(handle))
 
         def send_fwd(out):
             if last:
                 return
             ts, is_tuple = self._tensors_of(out)
             p2p._send_meta(ts, p2p.peer(+1), "act", is_tuple)
-            _P2P.run(p2p.send_ops(ts, +1))
+            p2p.post_send(ts, +1)
 
         def grad_metas(out):
             ts, _ = self._tensors_of(out)
             return [(tuple(t.shape), t.dtype) for t in ts if t.is_floating_point()]
 
-        def send_fwd_recv_bwd(out):
-            if last:
-                return None
-            ts, is_tuple = self._tensors_of(out)
-            p2p._send_meta(ts, p2p.peer(+1), "act", is_tuple)
-            bufs, rops = p2p.recv_ops(grad_metas(out), +1)
-            _P2P.run(p2p.send_ops(ts, +1) + rops)
-            return bufs
+        def post_recv_bwd(out):
+            return None if last else p2p.post_recv(grad_metas(out), +1)
 
-        def recv_bwd(out):
-            if last:
-                return None
-            bufs, rops = p2p.recv_ops(grad_metas(out), +1)
-            _P2P.run(rops)
-            return bufs
-
-        def in_grads(recv):
-            return [b.grad if b.grad is not None else torch.zeros_like(b) for b in recv if b.is_floating_point()]
+        def take_bwd(handle):
+            return None if handle is None else _P2P.wait(handle)
 
         def send_bwd(recv):
             if first:
                 return
-            _P2P.run(p2p.send_ops(in_grads(recv), -1))
-
-        def send_bwd_recv_fwd(recv):
-            if first:
-                return None
-            metas, is_tuple = p2p._recv_meta(p2p.peer(-1), "act")
-            bufs, rops = p2p.recv_ops(metas, -1)
-            _P2P.run(p2p.send_ops(in_grads(recv), -1) + rops)
-            return prep(bufs)
+            p2p.post_send([b.grad if b.grad is not None else torch.zeros_like(b) for b in recv if b.is_floating_point()],
+                          -1)
 
         def fwd(recv):
             inputs, labels = self._load_micro_batch(data_iter)
@@ -362,37 +389,41 @@ class PipelineEngine(NeoXEngine):
 
         if not train:
             with torch.no_grad():
-                for _ in range(M):
-                    recv = recv_fwd()
+                nxt = post_recv_fwd() if M > 0 else None
+                for i in range(M):
+                    recv = take_fwd(nxt)
+                    nxt = post_recv_fwd() if i + 1 < M else None       # next activation arrives during this forward
                     out, loss = fwd(recv)
                     send_fwd(out)
         else:
+            # One-forward-one-backward.  The receive of the NEXT activation is posted before the current micro-batch
+            # is computed and the receive of a gradient right after its forward has been sent on, so transfers
+            # run under compute; sends are never waited on.
+            nxt = post_recv_fwd() if M > 0 else None
+            n_fwd = 0
             for _ in range(warm):
-                recv = recv_fwd()
+                recv = take_fwd(nxt)
+                n_fwd += 1
+                nxt = post_recv_fwd() if n_fwd < M else None
                 out, loss = fwd(recv)
                 send_fwd(out)
-                queue.append((recv, out, loss))
-            remaining = M - warm
-            recv = recv_fwd() if remaining > 0 else None
-            for i in range(remaining):
+                queue.append((recv, out, loss, post_recv_bwd(out)))
+            for i in range(M - warm):
+                recv = take_fwd(nxt)
+                n_fwd += 1
+                nxt = post_recv_fwd() if n_fwd < M else None
                 out, loss = fwd(recv)
-                grads = send_fwd_recv_bwd(out)
-                queue.append((recv, out, loss))
-                r0, o0, l0 = queue.pop(0)
-                if warm > 0:
-                    # the gradient that just arrived belongs to the OLDEST outstanding micro-batch
-                    pass
-                bwd(o0, l0, grads)
-                if i == remaining - 1:
-                    send_bwd(r0)
-                    recv = None
-                else:
-                    recv = send_bwd_recv_fwd(r0)
-            for _ in range(warm):
-                r0, o0, l0 = queue.pop(0)
-                grads = recv_bwd(o0)
-                bwd(o0, l0, grads)
+                send_fwd(out)
+                queue.append((recv, out, loss, post_recv_bwd(out)))
+                r0, o0, l0, gh = queue.pop(0)          # the oldest outstanding micro-batch
+                bwd(o0, l0, take_bwd(gh))
                 send_bwd(r0)
+            while queue:
+                r0, o0, l0, gh = queue.pop(0)
+                bwd(o0, l0, take_bwd(gh))
+                send_bwd(r0)
+        if p2p is not None:
+            p2p.reap()
 
         # mean loss of the micro-batches, broadcast from the last stage to the whole pipeline group
         dev = p2p._device() if p2p else (losses[0].device if losses else torch.device("cpu"))

@@ -5,6 +5,7 @@ compared with the NCCL collective + fp32 matmul statement of the same math, over
 parities are reused, then a column->row parallel layer pair is run forward and backward both ways, and finally a wait
 on an epoch nobody publishes must time out with a status code and leave the context usable.
 """
+import json
 import os
 import subprocess
 import sys
@@ -16,11 +17,11 @@ from common import ROOT, free_port
 
 
 @pytest.mark.gpu
-def test_fused_comm_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_comm_kernels(world):
     n = torch.cuda.device_count()
-    if n < 2:
-        pytest.skip("needs at least 2 GPUs")
-    world = 2
+    if n < world:
+        pytest.skip(f"needs at least {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
@@ -56,3 +57,29 @@ def test_moe_peer_all_to_all_two_gpus():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     out = r.stdout + r.stderr
     assert r.returncode == 0 and "MOE_A2A_OK" in out, out[-4000:]
+
+
+@pytest.mark.gpu
+def test_tensor_parallel_training_parity(tmp_path):
+    """The same model, data and host-drawn initial weights trained for ten steps at tensor-parallel degree 1, 2 and
+    (with four GPUs) 4, through the fused compute+collective kernels, through the NCCL mappings and with sequence
+    parallelism: every run must follow the degree-1 losses to bf16 accuracy."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    results = {}
+    for world in [w for w in (1, 2, 4) if w <= n]:
+        out = str(tmp_path / f"tp{world}.json")
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_PARITY_OUT=out)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+               os.path.join(ROOT, "tests", "workers", "tp_parity_worker.py")]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0 and "TP_PARITY_DONE" in r.stdout, (r.stdout + r.stderr)[-4000:]
+        results[world] = json.load(open(out))
+    base = results[1]["nccl"]
+    assert base[-1] < base[0] - 0.05, base                  # it trains
+    for world, runs in results.items():
+        for name, losses in runs.items():
+            worst = max(abs(a - b) for a, b in zip(losses, base))
+            assert worst < 0.06, f"tp{world} {name}: {losses} vs tp1 {base}"

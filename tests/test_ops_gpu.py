@@ -206,12 +206,21 @@ def test_fused_adam_matches_torch():
 
 
 def test_bounded_wait_reports_instead_of_hanging():
-    """Status word plumbing: a clean run leaves the status at 0 and reading it does not disturb later launches."""
+    """A device-side wait that nobody satisfies gives up after its cycle limit, records a status code the host can
+    read, and leaves the context usable: a flag-wait kernel is pointed at a flag word that stays 0 (it waits for
+    epoch 7 of a second rank that does not exist), on one GPU.  A clean launch before and after reads status 0."""
+    import ctypes
     a = torch.randn(128, 64, device=DEV, dtype=torch.bfloat16)
     b = torch.randn(256, 64, device=DEV, dtype=torch.bfloat16)
     G.gemm(a, b)
     assert native.read_status() == 0
-    G.gemm(a, b)
+    flags = torch.zeros(64, dtype=torch.int32, device=DEV)
+    rc = native.lib().neox_wait_flags(native.ptr(flags), ctypes.c_uint(7), 2, 0,
+                                      ctypes.c_void_p(native.stream_ptr()))
+    assert rc == 0
+    assert native.read_status() == 561            # 560 + the rank whose flag never arrived
+    out = G.gemm(a, b)                            # the context is intact: kernels still run and are correct
+    _close(out, G.gemm_ref(a, b, out_dtype=torch.float32), atol=0.5)
     assert native.read_status() == 0
 
 
