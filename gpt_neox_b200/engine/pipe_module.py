@@ -24,6 +24,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..parallel import mpu
+from ..parallel.rng import set_block_tail
 from ..parallel.rng import checkpoint as ckpt_fn
 
 
@@ -260,7 +261,9 @@ class PipelineModule(nn.Module):
     def exec_range(self, start, end):
         def run(*inputs):
             x = inputs[0] if len(inputs) == 1 else inputs
-            for f in self.forward_funcs[start:end]:
+            block = self.forward_funcs[start:end]
+            for i, f in enumerate(block):
+                set_block_tail(i == len(block) - 1)
                 x = f(x)
             return x
         return run

@@ -21,6 +21,7 @@ import torch.nn as nn
 
 from ..engine.pipe_module import LayerSpec, PipelineModule, TiedLayerSpec
 from ..parallel import mpu
+from ..parallel.rng import set_block_tail
 from ..parallel.cross_entropy import vocab_parallel_cross_entropy
 from ..parallel.layers import ParallelRelativePositionBias
 from ..parallel.rng import checkpoint as ckpt_fn
@@ -137,7 +138,9 @@ class SequentialWrapper(nn.Module):
         def exec_range(start, end):
             def run(*inputs):
                 x = inputs[0] if len(inputs) == 1 else inputs
-                for layer in self.sequential[start:end]:
+                block = self.sequential[start:end]
+                for i, layer in enumerate(block):
+                    set_block_tail(i == len(block) - 1)
                     x = layer(x)
                     if hasattr(layer, "last_moe_loss"):
                         moe_losses.append(layer.last_moe_loss)

@@ -22,11 +22,11 @@ import torch.nn.functional as F
 
 from ..ops import functional as OF
 from ..ops.attention import attention_ref, flash_attention, packed_qkv_attention, packed_qkv_ok
-from ..ops.linear import linear as fused_linear
+from ..ops.linear import dead_outputs, linear as fused_linear
 from ..parallel import mappings as M
 from ..parallel import mpu
 from ..parallel.layers import ColumnParallelLinear, ParallelRelativePositionBias, RowParallelLinear
-from ..parallel.rng import get_cuda_rng_tracker
+from ..parallel.rng import get_cuda_rng_tracker, recompute_tail
 from .norms import LayerNorm, get_norm
 from .positional import AliBi, RotaryEmbedding, apply_rotary_pos_emb
 
@@ -74,25 +74,34 @@ class ParallelMLP(nn.Module):
         if not self.is_gated and self.activation_type != "gelu":
             self.act = OF.get_activation(self.activation_type)
 
-    def forward(self, hidden_states, residual=None, partial_add=None, post_residual=None, fuse_bias=False):
+    def forward(self, hidden_states, residual=None, partial_add=None, post_residual=None, fuse_bias=False,
+                dead_output=False):
         """Returns ``(output, output_bias)``; ``residual`` is added by linear2 (see ``RowParallelLinear.forward``).
-        With ``post_residual`` it returns ``reduce(mlp + bias + partial_add) + post_residual`` as one tensor."""
+        With ``post_residual`` it returns ``reduce(mlp + bias + partial_add) + post_residual`` as one tensor.
+        ``dead_output``: the result is not going to be read (recomputation of a checkpointed block's last layer), so
+        linear2 only records its inputs for backward."""
+        with dead_outputs(False):
+            return self._forward(hidden_states, residual, partial_add, post_residual, fuse_bias, dead_output)
+
+    def _forward(self, hidden_states, residual, partial_add, post_residual, fuse_bias, dead_output):
         l1 = self.linear1
         if self.activation_type == "gelu":
             # bias + GeLU in linear1's epilogue; GeLU' in linear2's data-gradient epilogue
             inter, pre = l1.matmul(hidden_states, l1.bias, act="gelu", split_pre=True)
-            if post_residual is not None:
-                return self.linear2.forward_reduced(inter, partial_add, post_residual, dgelu_aux=pre)
-            return self.linear2(inter, residual=residual, dgelu_aux=pre, fuse_bias=fuse_bias)
+            with dead_outputs(dead_output):
+                if post_residual is not None:
+                    return self.linear2.forward_reduced(inter, partial_add, post_residual, dgelu_aux=pre)
+                return self.linear2(inter, residual=residual, dgelu_aux=pre, fuse_bias=fuse_bias)
         else:
             inter, bias = l1(hidden_states)
             if self.is_gated:
                 inter = OF.gated_act(inter, self.activation_type, bias)
             else:
                 inter = self.act(inter + bias if bias is not None else inter)
-        if post_residual is not None:
-            return self.linear2.forward_reduced(inter, partial_add, post_residual)
-        return self.linear2(inter, residual=residual, fuse_bias=fuse_bias)
+        with dead_outputs(dead_output):
+            if post_residual is not None:
+                return self.linear2.forward_reduced(inter, partial_add, post_residual)
+            return self.linear2(inter, residual=residual, fuse_bias=fuse_bias)
 
 
 class ParallelLinear(nn.Module):
@@ -303,11 +312,13 @@ class ParallelSelfAttention(nn.Module):
         return packed_qkv_attention(mixed, cos, sin, causal=True, softmax_scale=(self.coeff or 1.0) / self.norm_factor,
                                     window=self.sliding_window_width, alibi_slopes=slopes)
 
-    def forward(self, hidden_states, attention_mask=None, layer_past=None, residual=None, fuse_bias=False):
+    def forward(self, hidden_states, attention_mask=None, layer_past=None, residual=None, fuse_bias=False,
+                dead_dense=False):
         packed = self._packed_path(hidden_states, layer_past)
         if packed is not None and not isinstance(packed, tuple):
             ctx = packed.reshape(packed.shape[0], packed.shape[1], self.hidden_size_per_partition)
-            return self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
+            with dead_outputs(dead_dense):
+                return self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
         if isinstance(packed, tuple):
             mixed, hn = packed[0], self.hidden_size_per_attention_head
             q, k, v = mixed[..., :hn], mixed[..., hn:2 * hn], mixed[..., 2 * hn:]
@@ -339,7 +350,8 @@ class ParallelSelfAttention(nn.Module):
             ctx = flash_attention(q, k, v, causal=True, softmax_scale=(self.coeff or 1.0) / self.norm_factor,
                                   window=self.sliding_window_width, alibi_slopes=slopes)
         ctx = ctx.reshape(ctx.shape[0], ctx.shape[1], self.hidden_size_per_partition)
-        out, bias = self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
+        with dead_outputs(dead_dense and not self.use_cache):
+            out, bias = self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
         if self.use_cache:
             out = [out, present]
         return out, bias
@@ -399,18 +411,22 @@ class ParallelTransformerLayer(nn.Module):
                 # attention partial (+ its bias) [+ residual when no reduction follows] accumulated by the
                 # GEMM epilogues:  out = residual + attn + b_a + mlp + b_m
                 attn_res = residual if self.tp == 1 else None
+                # Recomputation of a checkpointed block's last layer: the layer output is never read, and both
+                # output projections (attention dense, MLP linear2) feed nothing else, so they only record their
+                # inputs for backward -- no GEMM, no tensor-parallel reduction.
+                dead = recompute_tail()
                 # the attention output bias rides in the dense GEMM's epilogue (every rank adds its own to its partial)
                 a_out, a_bias = self.attention(x1, attention_mask, layer_past=layer_past, residual=attn_res,
-                                               fuse_bias=True)
+                                               fuse_bias=True, dead_dense=dead)
                 if a_bias is not None:
                     a_out = a_out + a_bias
                 if self.tp == 1:
-                    m_out, m_bias = self.mlp(x2, residual=a_out, fuse_bias=True)
+                    m_out, m_bias = self.mlp(x2, residual=a_out, fuse_bias=True, dead_output=dead)
                     if m_bias is not None:
                         m_out = m_out + m_bias
                     return m_out, moe_loss
                 # one reduction for both partial sums, fused with the last GEMM:  reduce(mlp + b_m + attn + b_a) + x
-                return self.mlp(x2, partial_add=a_out, post_residual=residual), moe_loss
+                return self.mlp(x2, partial_add=a_out, post_residual=residual, dead_output=dead), moe_loss
             a_out, a_bias = self.attention(x1, attention_mask, layer_past=layer_past)
             if self.use_cache:
                 a_out, presents = a_out
@@ -443,7 +459,8 @@ class ParallelTransformerLayer(nn.Module):
             out = OF.bias_dropout_add(m_out, None, x, p, self.training)
         else:
             fuse_m = can_fuse_res and self.mlp.linear2.bias is None
-            m_out, m_bias = self.mlp(ln2, residual=x if fuse_m else None)
+            # (see the parallel-residual branch: in a recomputed block tail only linear2's inputs are needed)
+            m_out, m_bias = self.mlp(ln2, residual=x if fuse_m else None, dead_output=fuse_m and recompute_tail())
             out = m_out if fuse_m else OF.bias_dropout_add(m_out, m_bias, x, p, self.training)
         return out, moe_loss
 

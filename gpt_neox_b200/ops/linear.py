@@ -27,6 +27,29 @@ def notify_grad_ready(weight):
         cb()
 
 
+_DEAD = [False]
+
+
+class dead_outputs:
+    """Inside this context the OUTPUT VALUES of linear layers are not needed (only their saved inputs are, for the
+    backward pass of a recomputed block): the GEMM -- and the tensor-parallel reduction that follows it -- is skipped
+    and an uninitialised tensor of the right shape is returned."""
+
+    def __init__(self, flag=True):
+        self.flag = bool(flag)
+
+    def __enter__(self):
+        self.old, _DEAD[0] = _DEAD[0], self.flag
+
+    def __exit__(self, *exc):
+        _DEAD[0] = self.old
+        return False
+
+
+def output_is_dead() -> bool:
+    return _DEAD[0]
+
+
 _warned = set()
 
 
@@ -69,7 +92,9 @@ class _LinearFn(torch.autograd.Function):
         use_k = kernel_ok(x2, weight) and (bias is None or bias.dtype == x2.dtype)
         ctx.use_k = use_k
         pre = None
-        if use_k:
+        if _DEAD[0] and act is None and not split_pre:
+            out = torch.empty(x2.shape[0], N, dtype=x2.dtype, device=x2.device)
+        elif use_k:
             r = G.gemm(x2, weight, bias=bias, add=res2, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE,
                        want_preact=need_pre)
             out, pre = r if need_pre else (r, None)

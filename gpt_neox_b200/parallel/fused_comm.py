@@ -390,8 +390,14 @@ class _Row(torch.autograd.Function):
         add2 = partial_add.reshape(-1, N) if partial_add is not None else None
         if add2 is not None and not add2.is_contiguous():
             add2 = add2.contiguous()
-        out = ws.gemm_reduce(x2, weight, False, bias=None if bias_partial else bias, residual=res2, all_reduce=not sp,
-                             partial_bias=bias if bias_partial else None, partial_add=add2)
+        from ..ops.linear import output_is_dead
+        if output_is_dead():
+            # recomputation of a block's last layer: nobody reads this result (every rank takes this branch, so the
+            # buffer epochs stay in step)
+            out = torch.empty(x2.shape[0] // ws.world if sp else x2.shape[0], N, dtype=x2.dtype, device=x2.device)
+        else:
+            out = ws.gemm_reduce(x2, weight, False, bias=None if bias_partial else bias, residual=res2,
+                                 all_reduce=not sp, partial_bias=bias if bias_partial else None, partial_add=add2)
         ctx.x_shape, ctx.sp, ctx.bias_partial = x.shape, sp, bias_partial
         ctx.has_bias, ctx.has_res, ctx.has_add = bias is not None, residual is not None, partial_add is not None
         ctx.add_shape = partial_add.shape if partial_add is not None else None

@@ -26,6 +26,7 @@ from torch.nn import init
 from torch.nn.parameter import Parameter
 
 from ..ops import embedding as fused_embedding
+from ..ops.linear import output_is_dead
 from ..ops.linear import linear as fused_linear
 from ..ops.mxfp8 import mx_linear
 from ..ops import fp8 as F8
@@ -340,7 +341,11 @@ class RowParallelLinear(nn.Module):
             out = fused_linear(x, self.weight, bias if local else None, residual=residual if local else None,
                                dgelu_aux=dgelu_aux)
         if not local:
-            if self.sequence_parallel:
+            if output_is_dead() and not self.fp8:
+                # recomputed block tail: the reduced values are never read, keep only shape and autograd edge
+                if self.sequence_parallel:
+                    out = M.reduce_scatter_to_sequence_parallel_region(out, values_unused=True)
+            elif self.sequence_parallel:
                 out = M.reduce_scatter_to_sequence_parallel_region(out)
             else:
                 out = M.reduce_from_model_parallel_region(out)
@@ -364,7 +369,10 @@ class RowParallelLinear(nn.Module):
         else:
             out = fused_linear(x, self.weight, self.bias, residual=partial_add, dgelu_aux=dgelu_aux)
         if self.tp > 1:
-            if self.sequence_parallel:
+            if output_is_dead() and not self.fp8:
+                if self.sequence_parallel:
+                    out = M.reduce_scatter_to_sequence_parallel_region(out, values_unused=True)
+            elif self.sequence_parallel:
                 out = M.reduce_scatter_to_sequence_parallel_region(out)
             else:
                 out = M.reduce_from_model_parallel_region(out)

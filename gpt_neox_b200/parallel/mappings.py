@@ -143,13 +143,17 @@ class _Gather(torch.autograd.Function):
 
 class _ReduceScatterSeq(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, seq_dim):
+    def forward(ctx, x, seq_dim, values_unused=False):
         ctx.seq_dim = seq_dim
+        if values_unused:
+            # shape and autograd edge only (backward still all-gathers): the result of a recomputed block tail
+            world = mpu.get_model_parallel_world_size()
+            return x.narrow(seq_dim, 0, x.shape[seq_dim] // world).contiguous()
         return _reduce_scatter_seq(x, seq_dim)
 
     @staticmethod
     def backward(ctx, g):
-        return _gather_seq(g, ctx.seq_dim), None
+        return _gather_seq(g, ctx.seq_dim), None, None
 
 
 class _GatherSeq(torch.autograd.Function):
@@ -190,8 +194,8 @@ def gather_from_model_parallel_region(x):
     return _Gather.apply(x)
 
 
-def reduce_scatter_to_sequence_parallel_region(x, seq_dim=0):
-    return _ReduceScatterSeq.apply(x, seq_dim)
+def reduce_scatter_to_sequence_parallel_region(x, seq_dim=0, values_unused=False):
+    return _ReduceScatterSeq.apply(x, seq_dim, values_unused)
 
 
 def gather_from_sequence_parallel_region(x, seq_dim=0):

@@ -144,6 +144,34 @@ def _unstash(keep, meta):
     return t
 
 
+# While a checkpointed block is re-run in backward, the output of its LAST layer is never read: backward only needs
+# what the ops saved (their inputs).  ``recompute_tail()`` tells that layer so, and it skips the GEMMs (and the
+# tensor-parallel reduction) that produce nothing but that output.
+_RECOMPUTE = {"active": False, "tail": False}
+
+
+def in_recompute() -> bool:
+    return _RECOMPUTE["active"]
+
+
+def set_block_tail(is_last: bool):
+    """Called by the layer runners before each layer of a block: is this the last layer of the block?"""
+    _RECOMPUTE["tail"] = bool(is_last)
+
+
+def recompute_tail() -> bool:
+    """True inside the recomputation of the last layer of a checkpointed block (``NEOX_RECOMPUTE_SKIP_TAIL=0`` turns
+    the short-cut off)."""
+    if "enabled" not in _RECOMPUTE:
+        import os
+        _RECOMPUTE["enabled"] = os.environ.get("NEOX_RECOMPUTE_SKIP_TAIL", "1") != "0"
+    return _RECOMPUTE["active"] and _RECOMPUTE["tail"] and _RECOMPUTE["enabled"]
+
+
+def set_recompute_skip(enabled: bool):
+    _RECOMPUTE["enabled"] = bool(enabled)
+
+
 class _Checkpoint(torch.autograd.Function):
     """Recompute-in-backward with RNG replay (default stream, CUDA stream and tracker states)."""
 
@@ -192,8 +220,13 @@ class _Checkpoint(torch.autograd.Function):
         if ctx.cuda_state is not None:
             torch.cuda.set_rng_state(ctx.cuda_state)
         _TRACKER.set_states(ctx.tracker_states)
-        with torch.enable_grad():
-            out = ctx.fn(*args)
+        _RECOMPUTE["active"] = True
+        try:
+            with torch.enable_grad():
+                out = ctx.fn(*args)
+        finally:
+            _RECOMPUTE["active"] = False
+            _RECOMPUTE["tail"] = False
         torch.set_rng_state(cur_cpu)
         if cur_cuda is not None:
             torch.cuda.set_rng_state(cur_cuda)

@@ -687,7 +687,7 @@ def test_lion_kernel_matches_eager_update():
     diff = (p_gpu.detach().cpu() - p_cpu.detach()).abs()
     assert (diff > 1e-5).sum().item() <= 3, diff.max()
     _close(out, p_gpu.detach(), 1e-2, rtol=1e-2)
-    _close(o_gpu.state[p_gpu]["exp_avg"], o_cpu.state[p_cpu]["exp_avg"], 1e-5, rtol=1e-4)
+    _close(o_gpu.state[p_gpu]["exp_avg"].cpu(), o_cpu.state[p_cpu]["exp_avg"], 1e-5, rtol=1e-4)
 
 
 def test_adam8bit_tracks_fp32_adam():

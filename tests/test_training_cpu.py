@@ -121,6 +121,34 @@ def test_overlapped_reduction_leaves_late_gradients_alone(tmp_path, world, cfg):
     assert rb["overlapped"] > 0, rb
 
 
+def _recompute_losses(rank, world, cfg, skip, out):
+    from gpt_neox_b200.parallel import rng
+    rng.set_recompute_skip(skip)
+    args, model, opt, sched = _setup({**cfg, "global_num_gpus": world, "checkpoint_activations": True})
+    losses = _train(args, model, opt, sched, 6)
+    if rank == 0:
+        with open(out, "w") as fh:
+            json.dump(losses, fh)
+
+
+@pytest.mark.parametrize("world,cfg", [
+    (1, {}),                                                              # parallel residual: dense and linear2 skipped
+    (1, {"gpt_j_residual": False, "use_bias_in_mlp": False}),             # sequential residual: linear2 skipped
+    (2, {"model_parallel_size": 2}),                                      # ... and the tensor-parallel all-reduce
+    (2, {"model_parallel_size": 2, "sequence_parallel": True, "checkpoint_num_layers": 2}),
+    (2, {"pipe_parallel_size": 2, "num_layers": 4, "gradient_accumulation_steps": 2}),
+])
+def test_recomputation_skips_the_block_tail_without_changing_the_training(tmp_path, world, cfg):
+    """When a checkpointed block is re-run in backward the output of its last layer is never read; the GEMMs (and
+    the reduction) that only produce it are skipped.  Losses must be identical to the full recomputation."""
+    a, b = str(tmp_path / "full.json"), str(tmp_path / "skip.json")
+    run_distributed(_recompute_losses, world, cfg, False, a)
+    run_distributed(_recompute_losses, world, cfg, True, b)
+    la, lb = json.load(open(a)), json.load(open(b))
+    assert la == lb, (la, lb)
+    assert lb[-1] < lb[0]
+
+
 def test_tensor_and_data_parallel_training():
     run_distributed(_loss_decreases, 4, {"model_parallel_size": 2, "sequence_parallel": True,
                                          "zero_optimization": {"stage": 1}}, None)
