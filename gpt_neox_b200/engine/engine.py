@@ -167,6 +167,36 @@ class _P2P:
             for pipe in topo.axis_lists("pipe"):           # every rank creates every link, in the same order
                 for lo, hi in zip(pipe[:-1], pipe[1:]):
                     _P2P._links[(lo, hi)] = (dist.new_group([lo, hi]), dist.new_group([lo, hi]))
+            self._connect()
+
+    def _connect(self):
+        """Bring up every communicator this rank will use -- its pipeline links in both directions and the tensor /
+        pipe / data parallel groups -- with one tiny exchange each, then drain the device.  Communicator creation and
+        the first connection between two peers synchronise the device; if that happened lazily in the middle of a
+        step, while a receive posted ahead of time is still waiting for its sender, the two stages could wait on
+        each other for ever."""
+        dev = self._device()
+        me = self.ranks[self.stage]
+        one = torch.ones(8, device=dev)
+        for delta in (-1, +1):
+            if not 0 <= self.stage + delta < len(self.ranks):
+                continue
+            other = self.peer(delta)
+            lo, hi = min(me, other), max(me, other)
+            fwd, bwd = _P2P._links[(lo, hi)]
+            buf = torch.zeros(8, device=dev)
+            # forward-traffic communicator carries lo -> hi, the other one hi -> lo
+            ops = [dist.P2POp(dist.isend if me == lo else dist.irecv, one if me == lo else buf, other, group=fwd)]
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+            ops = [dist.P2POp(dist.isend if me == hi else dist.irecv, one if me == hi else buf, other, group=bwd)]
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        for g in (mpu.get_model_parallel_group(), mpu.get_pipe_parallel_group(), mpu.get_data_parallel_group()):
+            if g is not None and dist.get_world_size(g) > 1:
+                dist.all_reduce(one.clone(), group=g)
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
 
     @classmethod
     def forget_links(cls):
@@ -254,6 +284,7 @@ class PipelineEngine(NeoXEngine):
         self.batch_fn = None
         self.has_attention_mask = False
         self.p2p = _P2P() if self.num_stages > 1 else None
+        self._batches_run = 0
         self.first_output_send = True
         self.pipe_recv_buf = None
         self.grid = SimpleNamespace(stage_to_global=self._stage_to_global, pipe_parallel_size=self.num_stages,
@@ -327,16 +358,26 @@ class PipelineEngine(NeoXEngine):
                     b.requires_grad_(True)
             return bufs
 
+        # The first executed batch posts every receive only when it is needed: that batch is where buffers,
+        # workspaces and library handles are created (calls that may synchronise the device), which must not
+        # happen while a receive posted ahead of time waits for a sender.  Later batches post receives early.
+        ahead = self._batches_run > 0
+
         def post_recv_fwd():
             """Post the receive of the next activation (None on the first stage)."""
             if first:
                 return None
-            metas, is_tuple = p2p._recv_meta(p2p.peer(-1), "act")
-            state["tuple"] = is_tuple
-            return p2p.post_recv(metas, -1)
+
+            def post():
+                metas, is_tuple = p2p._recv_meta(p2p.peer(-1), "act")
+                state["tuple"] = is_tuple
+                return p2p.post_recv(metas, -1)
+            return post() if ahead else post
 
         def take_fwd(handle):
-            return None if handle is None else prep(_P2P.wait(handle))
+            if handle is None:
+                return None
+            return prep(_P2P.wait(handle() if callable(handle) else handle))
 
         def send_fwd(out):
             if last:
@@ -350,10 +391,15 @@ class PipelineEngine(NeoXEngine):
             return [(tuple(t.shape), t.dtype) for t in ts if t.is_floating_point()]
 
         def post_recv_bwd(out):
-            return None if last else p2p.post_recv(grad_metas(out), +1)
+            if last:
+                return None
+            metas = grad_metas(out)
+            return p2p.post_recv(metas, +1) if ahead else (lambda: p2p.post_recv(metas, +1))
 
         def take_bwd(handle):
-            return None if handle is None else _P2P.wait(handle)
+            if handle is None:
+                return None
+            return _P2P.wait(handle() if callable(handle) else handle)
 
         def send_bwd(recv):
             if first:
@@ -424,6 +470,7 @@ class PipelineEngine(NeoXEngine):
                 send_bwd(r0)
         if p2p is not None:
             p2p.reap()
+        self._batches_run += 1
 
         # mean loss of the micro-batches, broadcast from the last stage to the whole pipeline group
         dev = p2p._device() if p2p else (losses[0].device if losses else torch.device("cpu"))
