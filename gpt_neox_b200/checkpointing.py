@@ -102,6 +102,43 @@ def _optim_file(save_dir, tag, bf16):
                                        f"{_mp_file_rank():02d}_optim_states.pt")
 
 
+def _atomic_save(obj, path):
+    """Write through a temporary name and rename: a run that is killed while writing never leaves a truncated file
+    under the final name."""
+    tmp = f"{path}.tmp.{os.getpid()}"
+    try:
+        torch.save(obj, tmp)
+        os.replace(tmp, path)
+    finally:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+
+
+def _read(path):
+    """``torch.load`` with an error that names the damaged file."""
+    try:
+        return torch.load(path, map_location="cpu", weights_only=False)
+    except Exception as exc:      # truncated zip, pickle error, ...
+        raise CheckpointDamaged(f"checkpoint file {path} cannot be read ({type(exc).__name__}: {exc}); "
+                                "it is truncated or corrupt") from exc
+
+
+class CheckpointDamaged(RuntimeError):
+    pass
+
+
+COMPLETE_MARKER = ".complete"
+
+
+def complete_tags(load_dir):
+    """Tags under ``load_dir`` whose save ran to the end (newest first)."""
+    if not os.path.isdir(load_dir):
+        return []
+    tags = [t for t in os.listdir(load_dir)
+            if t.startswith("global_step") and os.path.isfile(os.path.join(load_dir, t, COMPLETE_MARKER))]
+    return sorted(tags, key=lambda t: int(re.sub(r"\D", "", t) or 0), reverse=True)
+
+
 def _mp_file_rank():
     """File index over the model-parallel grid: tp rank for sequential models, ``stage * tp + tp_rank``
     when the pipeline holds several stages."""
@@ -141,22 +178,27 @@ def engine_save_checkpoint(engine, save_dir, tag, client_state):
                 layer = module.layer_module(idx)
                 if layer is None or not any(True for _ in layer.state_dict()):
                     continue
-                torch.save({k: v.detach().cpu() for k, v in layer.state_dict().items()},
-                           os.path.join(d, f"layer_{idx:02d}-model_{tp:02d}-model_states.pt"))
-            torch.save({"module": None, **common}, os.path.join(d, f"mp_rank_{_mp_file_rank():02d}_model_states.pt"))
+                _atomic_save({k: v.detach().cpu() for k, v in layer.state_dict().items()},
+                             os.path.join(d, f"layer_{idx:02d}-model_{tp:02d}-model_states.pt"))
+            _atomic_save({"module": None, **common}, os.path.join(d, f"mp_rank_{_mp_file_rank():02d}_model_states.pt"))
     elif writer:
         sd = {k: v.detach().cpu() for k, v in module.state_dict().items()}
-        torch.save({"module": sd, **common}, os.path.join(d, f"mp_rank_{tp:02d}_model_states.pt"))
+        _atomic_save({"module": sd, **common}, os.path.join(d, f"mp_rank_{tp:02d}_model_states.pt"))
     if engine.optimizer is not None and not engine.neox_args.no_save_optim:
         zero = getattr(engine.optimizer, "zero_stage", 0) >= 1
         if zero or writer:
-            torch.save({"optimizer_state_dict": engine.optimizer.state_dict(),
-                        "ds_config": engine.neox_args.deepspeed_config, "ds_version": "neox-b200"},
-                       _optim_file(save_dir, tag, engine.neox_args.precision == "bfloat16"))
+            _atomic_save({"optimizer_state_dict": engine.optimizer.state_dict(),
+                          "ds_config": engine.neox_args.deepspeed_config, "ds_version": "neox-b200"},
+                         _optim_file(save_dir, tag, engine.neox_args.precision == "bfloat16"))
     _barrier()
     if _rank() == 0:
-        with open(os.path.join(save_dir, "latest"), "w") as fh:
+        # every rank has finished writing: mark the tag complete, then move ``latest`` (both atomically)
+        with open(os.path.join(d, COMPLETE_MARKER), "w") as fh:
+            fh.write("ok\n")
+        tmp = os.path.join(save_dir, f"latest.tmp.{os.getpid()}")
+        with open(tmp, "w") as fh:
             fh.write(tag)
+        os.replace(tmp, os.path.join(save_dir, "latest"))
     _barrier()
     return True
 
@@ -170,12 +212,55 @@ def _load_module_sequential(module, sd, strict):
 
 def engine_load_checkpoint(engine, load_dir, tag, load_optimizer_states, load_lr_scheduler_states, load_module_only,
                            load_module_strict):
-    if tag is None:
-        latest = os.path.join(load_dir, "latest")
-        if not os.path.isfile(latest):
-            return None, None
+    """Load ``tag`` (default: the tag named by ``latest``).  Without an explicit tag a damaged or missing newest
+    checkpoint is not fatal: the newest tag whose save completed is used instead, with a message; if ``latest``
+    itself is missing the newest completed tag is taken."""
+    if tag is not None:
+        return _load_tag(engine, load_dir, tag, load_optimizer_states, load_lr_scheduler_states, load_module_only,
+                         load_module_strict)
+    candidates = []
+    latest = os.path.join(load_dir, "latest")
+    if os.path.isfile(latest):
         with open(latest) as fh:
-            tag = fh.read().strip()
+            candidates.append(fh.read().strip())
+    else:
+        found = complete_tags(load_dir)
+        if found:
+            print_rank_0(f" > {latest} is missing; newest completed checkpoint is {found[0]}")
+    candidates += [t for t in complete_tags(load_dir) if t not in candidates]
+    for i, cand in enumerate(candidates):
+        err, got = None, (None, None)
+        try:
+            got = _load_tag(engine, load_dir, cand, load_optimizer_states, load_lr_scheduler_states, load_module_only,
+                            load_module_strict)
+        except (CheckpointDamaged, FileNotFoundError) as exc:
+            err = exc
+        # every rank reads its own files: all of them must agree before a tag is accepted
+        if _all_ranks_ok(err is None):
+            if got[0] is not None:
+                return got
+            continue
+        nxt = candidates[i + 1] if i + 1 < len(candidates) else None
+        why = err if err is not None else "another rank could not read its part"
+        print(f" > [rank {_rank()}] checkpoint {cand} is unusable: {why}" +
+              (f"\n > falling back to {nxt}" if nxt else "\n > no older completed checkpoint to fall back to"),
+              flush=True)
+        if nxt is None:
+            raise err if err is not None else CheckpointDamaged(f"checkpoint {cand} is unreadable on another rank")
+    return None, None
+
+
+def _all_ranks_ok(ok: bool) -> bool:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return ok
+    dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
+def _load_tag(engine, load_dir, tag, load_optimizer_states, load_lr_scheduler_states, load_module_only,
+              load_module_strict):
     d = os.path.join(load_dir, tag)
     tp = mpu.get_model_parallel_rank()
     module = engine.module
@@ -185,7 +270,7 @@ def engine_load_checkpoint(engine, load_dir, tag, load_optimizer_states, load_lr
             state_file = os.path.join(d, f"mp_rank_{tp:02d}_model_states.pt")
         if not os.path.isfile(state_file):
             return None, None
-        state = torch.load(state_file, map_location="cpu", weights_only=False)
+        state = _read(state_file)
         for idx in module.local_layer_indices():
             layer = module.layer_module(idx)
             if layer is None or not any(True for _ in layer.state_dict()):
@@ -195,13 +280,13 @@ def engine_load_checkpoint(engine, load_dir, tag, load_optimizer_states, load_lr
                 if load_module_strict:
                     raise FileNotFoundError(f)
                 continue
-            sd = torch.load(f, map_location="cpu", weights_only=False)
+            sd = _read(f)
             _load_module_sequential(layer, sd, load_module_strict)
     else:
         state_file = os.path.join(d, f"mp_rank_{tp:02d}_model_states.pt")
         if not os.path.isfile(state_file):
             return None, None
-        state = torch.load(state_file, map_location="cpu", weights_only=False)
+        state = _read(state_file)
         if state.get("module") is not None:
             _load_module_sequential(module, state["module"], load_module_strict)
         else:
@@ -209,7 +294,7 @@ def engine_load_checkpoint(engine, load_dir, tag, load_optimizer_states, load_lr
             for idx, layer in enumerate(module.sequential):
                 f = os.path.join(d, f"layer_{idx:02d}-model_{tp:02d}-model_states.pt")
                 if os.path.isfile(f) and any(True for _ in layer.state_dict()):
-                    _load_module_sequential(layer, torch.load(f, map_location="cpu", weights_only=False),
+                    _load_module_sequential(layer, _read(f),
                                             load_module_strict)
     if engine.optimizer is not None and hasattr(engine.optimizer, "refresh_master_from_params"):
         engine.optimizer.refresh_master_from_params()
@@ -225,7 +310,7 @@ def engine_load_checkpoint(engine, load_dir, tag, load_optimizer_states, load_lr
                 f2 = _optim_file(load_dir, tag, not (engine.neox_args.precision == "bfloat16"))
                 f = f2 if os.path.isfile(f2) else f
             if os.path.isfile(f):
-                osd = torch.load(f, map_location="cpu", weights_only=False)
+                osd = _read(f)
                 engine.optimizer.load_state_dict(osd["optimizer_state_dict"])
             else:
                 print_rank_0(f" > optimizer state file {f} not found; optimizer starts fresh")

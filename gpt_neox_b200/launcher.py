@@ -56,6 +56,9 @@ def worker_argv(neox_args):
     return argv[i:]
 
 
+TEARDOWN_GRACE_S = 15.0     # between SIGTERM and SIGKILL when a failed rank takes the job down
+
+
 def spawn_local(script_argv, local_ids, node_rank, nnodes_offsets, world_size, master_addr, master_port,
                 extra_env=None):
     """Start this host's workers and wait; returns the first non-zero exit code (0 if all succeeded)."""
@@ -68,6 +71,7 @@ def spawn_local(script_argv, local_ids, node_rank, nnodes_offsets, world_size, m
                    MASTER_ADDR=master_addr, MASTER_PORT=str(master_port))
         procs.append(subprocess.Popen([sys.executable, "-u", *script_argv], env=env))
     rc = 0
+    deadline = float("inf")
     try:
         alive = set(range(len(procs)))
         while alive:
@@ -80,6 +84,10 @@ def spawn_local(script_argv, local_ids, node_rank, nnodes_offsets, world_size, m
                     rc = r
                     for j in alive:                 # one rank failed: stop the others
                         procs[j].send_signal(signal.SIGTERM)
+                    deadline = time.time() + TEARDOWN_GRACE_S
+            if rc != 0 and alive and time.time() > deadline:
+                for j in alive:                     # a rank stuck in a collective may ignore SIGTERM
+                    procs[j].kill()
             time.sleep(0.2)
     except KeyboardInterrupt:
         for p in procs:

@@ -96,10 +96,25 @@ def _get_batch(neox_args, tokenizer, keys, data, datatype, label_mask_zero=False
     return tokens, labels, loss_mask, attention_mask, position_ids
 
 
+def _next_batch(data_iterator, neox_args):
+    """``next(data_iterator)`` with the rank and iteration attached to any failure of the data pipeline (a worker
+    exception, a corrupt index, an exhausted dataset), so that the one failing rank of a large job can be found."""
+    if data_iterator is None:
+        return None
+    try:
+        return next(data_iterator)
+    except StopIteration:
+        raise RuntimeError(f"data iterator exhausted on rank {neox_args.rank} at iteration "
+                           f"{getattr(neox_args, 'iteration', '?')}") from None
+    except Exception as exc:
+        raise RuntimeError(f"data loader failed on rank {neox_args.rank} at iteration "
+                           f"{getattr(neox_args, 'iteration', '?')}: {type(exc).__name__}: {exc}") from exc
+
+
 def get_batch(neox_args, data_iterator):
     """One micro-batch for the sequential engine, shaped by ``train_impl``."""
     impl = neox_args.train_impl
-    data = next(data_iterator) if data_iterator is not None else None
+    data = _next_batch(data_iterator, neox_args)
     dt = torch.int64
     if impl in ("normal", "kto"):
         keys = ["text", "label"] if neox_args.train_label_data_paths else ["text"]
