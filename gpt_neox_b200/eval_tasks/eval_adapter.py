@@ -118,6 +118,7 @@ class EvalHarnessAdapter:
     def _loglikelihood_tokens(self, requests, disable_tqdm=True):
         """requests: list of ((context str, continuation str) | None, context ids, continuation ids)."""
         self.model.module.inference_mode(use_cache=False)
+        self.model.module.clear_cache()          # key/value caches left by a generation request must not leak in
         order = sorted(range(len(requests)), key=lambda i: -(len(requests[i][1]) + len(requests[i][2])))
         results = [None] * len(requests)
         with torch.no_grad():
@@ -176,13 +177,21 @@ class EvalHarnessAdapter:
             until = kw.get("until", []) if isinstance(kw, dict) else kw
             until = [until] if isinstance(until, str) else list(until)
             stop = [self.tok_encode(u) for u in until if u]
+            # prompt and continuation share the model's context: keep the tail of a long prompt, cap the continuation
+            ids = self.tok_encode(ctx)
+            room = max(1, min(self.max_gen_toks, self.max_length // 2))
+            if len(ids) > self.max_length - room:
+                ctx = self.tok_decode(ids[-(self.max_length - room):])
+                ids = ids[-(self.max_length - room):]
+            budget = max(1, min(self.max_gen_toks, self.max_length - len(ids)))
             out = generate_samples_from_prompt(self.neox_args, self.model, text=ctx, recompute=self.neox_args.recompute,
-                                               temperature=0.0, maximum_tokens=self.max_gen_toks, stop_tokens=stop or None)
+                                               temperature=0.0, maximum_tokens=budget, stop_tokens=stop or None)
             text = (out[0]["text"] if out else "") or ""
             for u in until:
                 if u:
                     text = text.split(u)[0]
             res.append(text)
+        self.model.module.clear_cache()
         self.model.module.train_mode()
         return res
 

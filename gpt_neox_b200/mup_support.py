@@ -76,3 +76,73 @@ def get_coord_data(neox_args, timers, lr_scheduler, models, dataloader, optcls=N
             for h in hooks:
                 h.remove()
     return pd.DataFrame(rows)
+
+
+def mup_coord_check(neox_args, timers, train_data_iterator, widths=None, nsteps=3, out_dir="."):
+    """The ``coord_check`` run (``megatron/training.py:139-177`` of the reference): train models of several widths for
+    a few steps, once with the maximal-update parametrisation and once with the standard one, record the mean
+    absolute activation of every module per step, and write ``coord_check_up.<rank>.csv`` /
+    ``coord_check_sp.<rank>.csv`` (plus ``.jpg`` plots when matplotlib is importable).  Flat curves over width for
+    the first file and growing ones for the second are the sign of a correct muP implementation.  Returns the two
+    data frames."""
+    import copy
+
+    from .training import setup_model_and_optimizer
+    base_hidden = neox_args.hidden_size
+    heads = neox_args.num_attention_heads
+    widths = widths or [base_hidden * (2 ** k) for k in range(3)]
+    rank = getattr(neox_args, "rank", 0) or 0
+    frames = {}
+    keep = {k: getattr(neox_args, k) for k in ("hidden_size", "use_mup", "mup_width_scale", "save_base_shapes",
+                                               "intermediate_size")}
+    batches = [next(train_data_iterator) for _ in range(max(1, neox_args.gradient_accumulation_steps) * nsteps)]
+    for tag, use_mup in (("up", True), ("sp", False)):
+        def models():
+            out = {}
+            for w in widths:
+                def make(w=w):
+                    neox_args.hidden_size = w
+                    neox_args.use_mup = use_mup
+                    neox_args.save_base_shapes = False
+                    neox_args.mup_width_scale = w / base_hidden
+                    assert w % heads == 0
+                    from .parallel import fused_comm  # noqa: F401  (same imports as a normal run)
+                    engine, _, sched, _ = setup_model_and_optimizer(neox_args)
+                    make.sched = sched
+                    return engine
+                out[w] = make
+            return out
+
+        class _Replay:
+            def __init__(self):
+                self.i = 0
+
+            def __iter__(self):
+                return self
+
+            def __next__(self):
+                b = batches[self.i % len(batches)]
+                self.i += 1
+                return copy.deepcopy(b)
+        df = get_coord_data(neox_args, timers, None, models(), _Replay(), nsteps=nsteps)
+        frames[tag] = df
+        path = os.path.join(out_dir, f"coord_check_{tag}.{rank}")
+        df.to_csv(path + ".csv", index=False)
+        try:
+            import matplotlib
+            matplotlib.use("Agg")
+            import matplotlib.pyplot as plt
+            fig, axes = plt.subplots(1, nsteps, figsize=(4 * nsteps, 3))
+            for t, ax in enumerate(axes if nsteps > 1 else [axes]):
+                for mod, g in df[df.t == t + 1].groupby("module"):
+                    ax.plot(g.width, g.l1, alpha=0.4)
+                ax.set_xscale("log", base=2)
+                ax.set_yscale("log")
+                ax.set_title(f"t={t + 1}")
+            fig.savefig(path + ".jpg")
+            plt.close(fig)
+        except Exception:
+            pass
+    for k, v in keep.items():
+        setattr(neox_args, k, v)
+    return frames["up"], frames["sp"]

@@ -633,6 +633,12 @@ def pretrain(neox_args):
         if dist.is_available() and dist.is_initialized():
             dist.barrier()
     train_it, valid_it, test_it = shift_and_wrap_data_loaders(neox_args, train_dl, valid_dl, test_dl)
+    if neox_args.use_mup and neox_args.coord_check:
+        # muP coordinate check: a diagnostic run that replaces training (reference: training.py:273-275)
+        from .mup_support import mup_coord_check
+        mup_coord_check(neox_args, timers, train_it)
+        print_rank_0("coordinate check written to coord_check_up.* / coord_check_sp.*; exiting")
+        sys.exit(0)
     print_rank_0("done with setups ...")
     timers.log(["train/valid/test data loaders", "model and optimizer"])
     print_rank_0("training ...")

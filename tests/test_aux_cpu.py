@@ -1,0 +1,204 @@
+"""Auxiliary components on CPU: pairwise and online datasets, the muP coordinate check, the evaluation-harness
+adapter (against a stand-in ``lm_eval``), the S3 mirror of a checkpoint (against a stand-in ``boto3``) and the
+weight server's wire protocol."""
+import json
+import os
+import pickle
+import socket
+import sys
+import threading
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from common import make_args, run_distributed
+
+
+class _FakeIndexed:
+    def __init__(self, docs):
+        self.docs = [np.asarray(d) for d in docs]
+        self.sizes = np.asarray([len(d) for d in self.docs], dtype=np.int32)
+
+    def get(self, i):
+        return self.docs[i]
+
+
+def test_pairwise_dataset_keeps_pairs_aligned():
+    from gpt_neox_b200.data.pairwise_dataset import PairwiseDataset
+    rng = np.random.default_rng(0)
+    pos = _FakeIndexed([rng.integers(1, 99, size=n) for n in (5, 9, 3, 12, 7, 4)])
+    neg = _FakeIndexed([d + 100 for d in pos.docs])                       # neg doc i = pos doc i + 100
+    lab = _FakeIndexed([np.where(np.arange(len(d)) < 2, -100, d) for d in pos.docs])
+    ref = _FakeIndexed([np.full(len(d), 0.5, dtype=np.float32) for d in pos.docs])
+    ds = PairwiseDataset("t", "p", np.arange(6), pos, neg, num_samples=10, seq_length=15, seed=1,
+                         pos_label_dataset=lab, neg_label_dataset=lab, pos_ref_dataset=ref, neg_ref_dataset=ref)
+    assert len(ds) == 10
+    for i in range(len(ds)):
+        s = ds[i]
+        assert s["pos"].shape == s["neg"].shape == (16,)
+        live = s["pos"] > 0
+        assert np.array_equal(s["neg"][live], s["pos"][live] + 100)        # the same document on both sides
+        assert (s["pos_label"][~live] == -100).all() and s["pos_ref"].dtype == np.float32
+    packed = PairwiseDataset("t", "p", np.arange(6), pos, neg, num_samples=4, seq_length=15, seed=1,
+                             pack_impl="pack_until_overflow")
+    assert any(len(g) > 1 for g in packed.groups)
+    for g in packed.groups:
+        assert sum(int(max(pos.sizes[d], neg.sizes[d])) for d in g) <= 16 or len(g) == 1
+    with pytest.raises(AssertionError):
+        PairwiseDataset("t", "p", np.arange(6), pos, neg, 4, 15, 1, pack_impl="packed")
+
+
+def test_online_dataset_consumes_a_sampling_server():
+    from gpt_neox_b200.data.online_dataset import OnlineDataset
+    batch = {"prefix": [5, 6, 7], "completions": [[8, 9], [10], [11, 12, 13]], "rewards": [1.0, 0.0, 2.0]}
+    srv = socket.socket()
+    srv.bind(("127.0.0.1", 0))
+    srv.listen(4)
+    port = srv.getsockname()[1]
+
+    def serve():
+        for _ in range(2):
+            conn, _ = srv.accept()
+            assert conn.recv(64) == b"train"
+            conn.sendall(pickle.dumps(batch))
+            conn.close()
+    threading.Thread(target=serve, daemon=True).start()
+    ds = OnlineDataset(num_samples=6, seq_length=8, leave_one_out=True, dataserver_ips="127.0.0.1", dataserver_ports=port)
+    items = [ds[i] for i in range(3)]
+    assert [int(x["raw_reward"]) for x in items] == [1, 0, 2]
+    # leave-one-out baseline: reward minus the mean of the other completions' rewards
+    assert np.allclose([x["reward"][0] for x in items], [1 - 1.0, 0 - 1.5, 2 - 0.5])
+    first = items[0]
+    assert first["text"][:5].tolist() == [5, 6, 7, 8, 9] and first["label"][:5].tolist() == [-100, -100, -100, 8, 9]
+    assert (first["label"][5:] == -100).all()
+    assert ds[3]["text"][:3].tolist() == [5, 6, 7]        # second request to the server
+
+
+def _coord_check(rank, world, out_dir):
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.mup_support import mup_coord_check
+    from gpt_neox_b200.utils import Timers
+    args = make_args(hidden_size=32, num_attention_heads=4, num_layers=2, use_mup=True, coord_check=True,
+                     base_shapes_file=os.path.join(out_dir, "base"), global_num_gpus=world)
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    g = torch.Generator().manual_seed(0)
+
+    def it():
+        while True:
+            yield {"text": torch.randint(0, args.padded_vocab_size, (2, 33), generator=g)}
+    up, sp = mup_coord_check(args, Timers(), it(), widths=[32, 64, 128], nsteps=2, out_dir=out_dir)
+    assert set(up.width) == {32, 64, 128} and set(up.t) == {1, 2} and len(up) == len(sp) > 0
+    assert np.isfinite(up.l1).all() and np.isfinite(sp.l1).all()
+    assert args.hidden_size == 32 and args.use_mup is True          # the run's own settings are restored
+
+
+def test_mup_coordinate_check_writes_both_tables(tmp_path):
+    run_distributed(_coord_check, 1, str(tmp_path))
+    for tag in ("up", "sp"):
+        assert os.path.getsize(tmp_path / f"coord_check_{tag}.0.csv") > 0
+
+
+def _adapter(rank, world, out):
+    from gpt_neox_b200.eval_tasks.eval_adapter import EvalHarnessAdapter
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.training import forward_step, setup_model_and_optimizer
+    args = make_args(global_num_gpus=world, seq_length=32)
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    model, _, _, _ = setup_model_and_optimizer(args)
+    ad = EvalHarnessAdapter(model, forward_step, args, batch_size=3)
+    reqs = [("the quick brown", " fox"), ("", "hello"), ("abc" * 30, "xyz"), ("q", " a b c")]
+    res = ad.loglikelihood(reqs)
+    assert len(res) == 4 and all(r[0] < 0 and isinstance(r[1], bool) for r in res)
+    # scoring does not depend on how requests are batched
+    solo = [ad.loglikelihood([r])[0] for r in reqs]
+    assert all(abs(a[0] - b[0]) < 1e-3 for a, b in zip(res, solo)), (res, solo)
+    roll = ad.loglikelihood_rolling(["some longer text " * 8])
+    assert len(roll) == 1 and roll[0] < 0
+    gen = ad.generate_until([("hello", {"until": ["\\n"]})])
+    assert len(gen) == 1 and isinstance(gen[0], str)
+
+    # the harness driver, against a stand-in lm_eval package that calls back into the three request types
+    calls = {}
+
+    class LM:
+        pass
+
+    def evaluate(lm, task_dict, limit=None, bootstrap_iters=0, log_samples=False):
+        calls["ll"] = lm.loglikelihood([("ctx", " cont")])
+        calls["roll"] = lm.loglikelihood_rolling(["text"])
+        calls["gen"] = lm.generate_until([("hi", {"until": ["."]})])
+        return {"results": {t: {"acc": 0.5} for t in task_dict}}
+    pkg = types.ModuleType("lm_eval")
+    pkg.evaluator = types.SimpleNamespace(evaluate=evaluate)
+    pkg.tasks = types.SimpleNamespace(TaskManager=lambda: None, get_task_dict=lambda names, tm: {n: object() for n in names})
+    pkg.utils = types.SimpleNamespace()
+    api = types.ModuleType("lm_eval.api")
+    api_model = types.ModuleType("lm_eval.api.model")
+    api_model.LM = LM
+    sys.modules.update({"lm_eval": pkg, "lm_eval.api": api, "lm_eval.api.model": api_model})
+    out_res = ad.run_eval(eval_tasks=["lambada_openai", "piqa"], num_fewshot=0)
+    assert set(out_res["results"]) == {"lambada_openai", "piqa"} and out_res["config"]["model"] == "neox"
+    assert len(calls["ll"]) == 1 and len(calls["roll"]) == 1 and len(calls["gen"]) == 1
+    if rank == 0:
+        with open(out, "w") as fh:
+            json.dump([r[0] for r in res], fh)
+
+
+def test_eval_harness_adapter_scores_and_drives_the_harness(tmp_path):
+    run_distributed(_adapter, 1, str(tmp_path / "scores.json"))
+    assert len(json.load(open(tmp_path / "scores.json"))) == 4
+
+
+def test_s3_upload_mirrors_the_checkpoint_tree(tmp_path, monkeypatch):
+    from gpt_neox_b200 import checkpointing as C
+    save = tmp_path / "run1"
+    tag = save / "global_step7"
+    (tag / "configs").mkdir(parents=True)
+    (tag / "mp_rank_00_model_states.pt").write_bytes(b"x" * 10)
+    (tag / "configs" / "a.yml").write_text("{}")
+    uploaded = []
+
+    class Client:
+        def upload_file(self, path, bucket, key, Config=None):
+            uploaded.append((os.path.relpath(path, tag), bucket, key, Config.multipart_chunksize))
+    boto3 = types.ModuleType("boto3")
+    boto3.client = lambda kind: Client()
+    s3 = types.ModuleType("boto3.s3")
+    transfer = types.ModuleType("boto3.s3.transfer")
+
+    class TransferConfig:
+        def __init__(self, **kw):
+            self.__dict__.update(kw)
+    transfer.TransferConfig = TransferConfig
+    monkeypatch.setitem(sys.modules, "boto3", boto3)
+    monkeypatch.setitem(sys.modules, "boto3.s3", s3)
+    monkeypatch.setitem(sys.modules, "boto3.s3.transfer", transfer)
+    args = types.SimpleNamespace(save=str(save), s3_path="s3://bucket/prefix", s3_chunk_size=1 << 20)
+    C.upload_checkpoint(7, args)
+    assert sorted(u[0] for u in uploaded) == ["configs/a.yml", "mp_rank_00_model_states.pt"]
+    assert all(b == "bucket" and k.startswith("prefix/run1/global_step7/") and c == 1 << 20 for _, b, k, c in uploaded)
+
+
+def test_weight_server_answers_with_a_length_prefixed_map():
+    from gpt_neox_b200 import weight_server as W
+    model = types.SimpleNamespace(module=torch.nn.Linear(4, 4))       # CPU parameters: nothing to share, empty map
+    with socket.socket() as s:
+        s.bind(("localhost", 0))
+        port = s.getsockname()[1]
+    W.start_server(model, ports=port)
+    for _ in range(50):
+        try:
+            c = socket.create_connection(("localhost", port), timeout=2)
+            break
+        except ConnectionRefusedError:
+            import time
+            time.sleep(0.1)
+    n = int.from_bytes(c.recv(8), "little")
+    payload = b""
+    while len(payload) < n:
+        payload += c.recv(n - len(payload))
+    assert pickle.loads(payload) == {}
