@@ -32,6 +32,10 @@ def main():
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=6144)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ab-gemm", action="store_true",
+                    help="only the five GEMM shapes, three ways taking turns call by call: one-CTA kernel, CTA-pair "
+                         "kernel, cuBLAS through torch (F.linear / matmul, plus the element-wise kernels the fused "
+                         "epilogues replace)")
     a = ap.parse_args()
     only = set(x for x in a.only.split(",") if x)
     dev = torch.device("cuda")
@@ -67,6 +71,8 @@ def main():
         out.append(rec)
         print(json.dumps(rec), flush=True)
 
+    if a.ab_gemm:
+        return ab_gemm(a, dev, bf, flush)
     x = bf(T, h)
     w_qkv, w_fc1, w_fc2 = bf(3 * h, h), bf(4 * h, h), bf(h, 4 * h)
     y4 = bf(T, 4 * h)
@@ -187,6 +193,62 @@ def main():
     run("adam_step_bf16_writeback", adam, nbytes=n * (4 * 4 + 3 * 4 + 2.0))
     if not only:
         print(json.dumps({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "kind": kind}, "results": out}))
+
+
+def ab_gemm(a, dev, bf, flush):
+    """Interleaved A/B/C of the GEMM kernels against cuBLAS on identical shapes: the variants take turns call by
+    call (L2 flushed before every call), so all of them see the same clocks and power state; medians are reported."""
+    import torch.nn.functional as F
+    T, h = a.tokens, a.hidden
+    x, y4, g_h = bf(T, h), bf(T, 4 * h), bf(T, h)
+    w_qkv, w_fc1, w_fc2, bias4 = bf(3 * h, h), bf(4 * h, h), bf(h, 4 * h), bf(4 * h)
+    acc = torch.zeros(4 * h, h, device=dev, dtype=torch.float32)
+
+    def with_pair(flag, fn):
+        def f():
+            old, G._PAIR = G._PAIR, flag
+            try:
+                return fn()
+            finally:
+                G._PAIR = old
+        return f
+
+    def cublas_wgrad():
+        acc.add_(y4.t() @ x)
+
+    shapes = [
+        ("fwd_qkv", 2.0 * T * h * 3 * h, lambda: G.gemm(x, w_qkv), lambda: F.linear(x, w_qkv)),
+        ("fwd_fc1_bias_gelu", 2.0 * T * h * 4 * h, lambda: G.gemm(x, w_fc1, bias=bias4, act=G.ACT_GELU, want_preact=True),
+         lambda: F.gelu(F.linear(x, w_fc1, bias4), approximate="tanh")),
+        ("fwd_fc2", 2.0 * T * h * 4 * h, lambda: G.gemm(y4, w_fc2), lambda: F.linear(y4, w_fc2)),
+        ("dgrad_fc1", 2.0 * T * h * 4 * h, lambda: G.gemm(y4, w_fc1, b_mn=True), lambda: y4 @ w_fc1),
+        ("wgrad_fc1_fp32_accumulate", 2.0 * T * h * 4 * h,
+         lambda: G.gemm(y4, x, a_mn=True, b_mn=True, out=acc, add=acc), cublas_wgrad),
+    ]
+    results = []
+    for name, flops, ours, lib in shapes:
+        fns = {"one_cta": with_pair("0", ours), "cta_pair": with_pair("1", ours), "cublas": lib}
+        for f in fns.values():
+            for _ in range(3):
+                f()
+        torch.cuda.synchronize()
+        ts = {k: [] for k in fns}
+        for _ in range(a.iters):
+            for k, f in fns.items():
+                flush.add_(1.0)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                f()
+                e1.record()
+                torch.cuda.synchronize()
+                ts[k].append(e0.elapsed_time(e1))
+        med = {k: sorted(v)[len(v) // 2] for k, v in ts.items()}
+        rec = {"gemm": name, **{f"{k}_ms": round(v, 4) for k, v in med.items()},
+               **{f"{k}_tflops": round(flops / v / 1e9, 1) for k, v in med.items()},
+               "pair_over_cublas": round(med["cublas"] / med["cta_pair"], 3)}
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+    return results
 
 
 if __name__ == "__main__":
