@@ -356,7 +356,9 @@ def main():
             "dtype": "bf16" if not a.fp8 else f"fp8 linear layers ({a.fp8} scaling, e4m3 fwd / e5m2 grads), bf16 elsewhere",
             "data": "synthetic uniform-random token ids, random-init weights (small_init / wang_init)",
             "tflops_per_gpu": {"model_c3": round(mfu_flops, 1), "hardware_c4": round(hfu_flops, 1),
-                               "formula": "24*c*B*s*L*h^2*(1+s/6h+V/16Lh) / (t*gpus)"},
+                               "formula": "24*c*B*s*L*h^2*(1+s/6h+V/16Lh) / (t*gpus)",
+                               "note": "c=4 is the reference's count for a full recomputation; this build skips the "
+                                       "output projections of a recomputed block's last layer, so compare model_c3"},
             "vs_paper_a100_tflops_per_gpu": round(hfu_flops / PAPER_TFLOPS_PER_GPU_A100, 2),
             "config": {"model": model_description(a.model, neox_args.num_layers, neox_args.hidden_size),
                        "global_batch": neox_args.train_batch_size, "seq_len": seq, "micro_batch": mb,

@@ -91,7 +91,7 @@ online_dataserver_ips : str|list = 'localhost'     # hosts of the online data se
 online_dataserver_ports : int|list = 10000         # ports of the online data servers
 te_columnparallel : bool = False                   # run column-parallel linears on the fp8 tensor cores
 te_rowparallel : bool = False                      # run row-parallel linears on the fp8 tensor cores
-te_fp8_recipe : lit[current|delayed|mxfp8] = 'current'   # per-tensor scale from this tensor's amax / from an amax history / 32-element block scales (MXFP8 numerics through the bf16 GEMM)
+te_fp8_recipe : lit[current|delayed|mxfp8] = 'current'   # per-tensor scale from this tensor's amax / from an amax history / 32-element E8M0 block scales fed to the block-scaled tcgen05 GEMM (csrc/gemm_mxfp8_sm100.cu)
 te_layernorm_mlp : bool = False                    # both MLP linears in fp8 (whatever te_columnparallel / te_rowparallel say)
 te_mha : bool = False                              # QKV and output projections of attention in fp8
 te_fp8_format : lit[e4m3|hybrid] = 'hybrid'        # 'hybrid' = E4M3 forward, E5M2 gradients

@@ -11,6 +11,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
+from ..ops.linear import linear
 from ..parallel import mpu
 from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
 from .norms import get_norm
@@ -58,7 +59,7 @@ class SpatialGatingUnit(nn.Module):
         if self.causal:
             weight = weight[:n, :n].tril()
             bias = bias[:n]
-        gate = F.linear(gate.transpose(2, 1), weight, bias).transpose(2, 1)
+        gate = linear(gate.transpose(2, 1).contiguous(), weight.contiguous(), bias).transpose(2, 1)
         if self.use_attn:
             gate = gate + self.attn(x.transpose(0, 1), attention_mask).transpose(0, 1)
         return (gate * res).transpose(0, 1)

@@ -18,7 +18,7 @@ import os
 
 import torch
 
-from . import native
+from . import flop_count, native
 from .functional import _DT, _s
 
 
@@ -26,6 +26,7 @@ def attention_ref(q, k, v, causal=True, softmax_scale=None, window=None, alibi_s
                   return_lse=False):
     sq, b, hq, d = q.shape
     sk, _, hkv, _ = k.shape
+    flop_count.attention(b, hq, sq, sk, d, causal)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
     qf = q.float().permute(1, 2, 0, 3)                       # [b, hq, sq, d]
     kf = k.float().permute(1, 2, 0, 3)
@@ -107,8 +108,7 @@ class _FlashFn(torch.autograd.Function):
         sk, _, hkv, _ = k.shape
         out = torch.empty(sq, b, hq, d, dtype=q.dtype, device=q.device)
         lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
-        L = native.lib()
-        ll = ctypes.c_longlong
+        flop_count.attention(b, hq, sq, sk, d, causal)
         _launch_fwd(q, k, v, out, lse, sq, sk, b, hq, hkv, d, scale, causal, window, slopes)
         ctx.save_for_backward(q, k, v, out, lse, slopes if slopes is not None else torch.empty(0, device=q.device))
         ctx.cfg = (causal, scale, window, slopes is not None)
@@ -152,6 +152,7 @@ class _PackedQKVFn(torch.autograd.Function):
         s, b, h, d3 = mixed.shape
         d = d3 // 3
         assert mixed.is_contiguous()
+        flop_count.attention(b, h, s, s, d, causal)
         q, k, v = mixed[..., :d], mixed[..., d:2 * d], mixed[..., 2 * d:]
         L = native.lib()
         ll = ctypes.c_longlong

@@ -368,6 +368,44 @@ __global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, float*
     }
 }
 
+// Adam(W) with block-wise 8-bit states: one CTA per block of 256 elements.  m is stored as round(127 m / absmax),
+// v as round(255 sqrt(v / max)); a step de-quantises, applies the fp32 recurrences, re-quantises with the block's
+// new maxima (two block reductions) and updates the fp32 parameter (+ optional 16-bit model copy).
+template <typename OUT>
+__global__ void __launch_bounds__(256) adam8bit_kernel(float* __restrict__ p, int8_t* __restrict__ qm,
+                                                       uint8_t* __restrict__ qv, float* __restrict__ sm,
+                                                       float* __restrict__ sv, const float* __restrict__ g,
+                                                       OUT* __restrict__ out, long long n, float lr, float b1, float b2,
+                                                       float eps, float wd, float bc1, float bc2, float gs, int adamw) {
+    __shared__ float red[33];
+    const long long blk = blockIdx.x;
+    const long long i = blk * 256 + threadIdx.x;
+    const bool live = i < n;
+    float pi = live ? p[i] : 0.f;
+    float gi = live ? g[i] * gs : 0.f;
+    if (!adamw && wd != 0.f) gi += wd * pi;
+    const float r = (float)qv[i] * (1.0f / 255.0f);
+    float mi = (float)qm[i] * (sm[blk] * (1.0f / 127.0f));
+    float vi = r * r * sv[blk];
+    mi = b1 * mi + (1.f - b1) * gi;
+    vi = b2 * vi + (1.f - b2) * gi * gi;
+    const float amax = fmaxf(block_reduce<true>(fabsf(mi), red), 1e-30f);
+    const float vmax = fmaxf(block_reduce<true>(vi, red), 1e-38f);
+    qm[i] = (int8_t)__float2int_rn(mi / amax * 127.0f);
+    qv[i] = (uint8_t)__float2int_rn(sqrtf(vi / vmax) * 255.0f);
+    if (threadIdx.x == 0) {
+        sm[blk] = amax;
+        sv[blk] = vmax;
+    }
+    if (live) {
+        float upd = (mi / bc1) / (sqrtf(vi / bc2) + eps);
+        if (adamw && wd != 0.f) upd += wd * pi;
+        pi -= lr * upd;
+        p[i] = pi;
+        if (out) out[i] = from_f<OUT>(pi);
+    }
+}
+
 template <typename OUT>
 __global__ void __launch_bounds__(256) lion_kernel(float* __restrict__ p, float* __restrict__ m,
                                                    const float* __restrict__ g, OUT* __restrict__ out, long long n,
@@ -504,6 +542,28 @@ int neox_adam_step(float* p, float* m, float* v, const float* g, void* out, int 
                                                           bc2, gs, adamw);
     else
         adam_kernel<__half><<<grid, 256, 0, st>>>(p, m, v, g, (__half*)out, n, lr, b1, b2, eps, wd, bc1, bc2, gs, adamw);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+// qm / qv hold ceil(n / 256) * 256 quantised states, sm / sv one fp32 scale per block of 256.
+int neox_adam8bit_step(float* p, void* qm, void* qv, float* sm, float* sv, const float* g, void* out, int out_dtype,
+                       long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float gs,
+                       int adamw, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return NEOX_ERR_TOO_LARGE;
+    const unsigned grid = (unsigned)blocks;
+    int8_t* m8 = static_cast<int8_t*>(qm);
+    uint8_t* v8 = static_cast<uint8_t*>(qv);
+    if (!out || out_dtype == 1)
+        adam8bit_kernel<float><<<grid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (float*)out, n, lr, b1, b2, eps, wd, bc1, bc2,
+                                                     gs, adamw);
+    else if (out_dtype == 0)
+        adam8bit_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (__nv_bfloat16*)out, n, lr, b1, b2,
+                                                             eps, wd, bc1, bc2, gs, adamw);
+    else
+        adam8bit_kernel<__half><<<grid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (__half*)out, n, lr, b1, b2, eps, wd, bc1,
+                                                      bc2, gs, adamw);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 int neox_lion_step(float* p, float* m, const float* g, void* out, int out_dtype, long long n, float lr, float b1,

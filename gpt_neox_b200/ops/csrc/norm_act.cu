@@ -560,6 +560,75 @@ __global__ void __launch_bounds__(256) gated_bwd_kernel(const T* __restrict__ g,
     }
 }
 
+// ---------------------------------------------------------------- bias + dropout + residual add (training)
+// Philox-4x32-10 counter-based generator (Salmon et al., SC'11): the mask of element i is a pure function of
+// (seed, offset, i), so the backward kernel regenerates it instead of reading a stored mask, and a recomputed
+// forward (activation checkpointing) reproduces it from the replayed generator state.
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += 0x9E3779B9u;
+        k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+
+// keep[k] for the 8 elements of vector i: two Philox blocks, element kept when its 32 random bits >= threshold
+__device__ __forceinline__ void dropout_keep8(unsigned long long seed, unsigned long long offset, long long i,
+                                              uint32_t threshold, bool (&keep)[8]) {
+    const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+    const unsigned long long c0 = offset + 2ULL * (unsigned long long)i;
+    const uint4 a = philox4x32_10(make_uint4((uint32_t)c0, (uint32_t)(c0 >> 32), 0u, 0u), key);
+    const uint4 b = philox4x32_10(make_uint4((uint32_t)(c0 + 1), (uint32_t)((c0 + 1) >> 32), 0u, 0u), key);
+    const uint32_t r[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) keep[k] = r[k] >= threshold;
+}
+
+// out = residual + dropout(x + bias)        (residual may be null: plain dropout of x + bias)
+template <typename T>
+__global__ void __launch_bounds__(256) bias_dropout_add_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                                               const T* __restrict__ residual, T* __restrict__ out,
+                                                               long long nvec, int colvec, uint32_t threshold,
+                                                               float scale, unsigned long long seed,
+                                                               unsigned long long offset) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        float v[8], bb[8], rr[8], o[8];
+        bool keep[8];
+        Vec8<T>::load(x + i * 8, v);
+        if (bias) Vec8<T>::load(bias + (i % colvec) * 8, bb);
+        if (residual) Vec8<T>::load(residual + i * 8, rr);
+        dropout_keep8(seed, offset, i, threshold, keep);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float t = v[k] + (bias ? bb[k] : 0.f);
+            o[k] = (keep[k] ? t * scale : 0.f) + (residual ? rr[k] : 0.f);
+        }
+        Vec8<T>::store(out + i * 8, o);
+    }
+}
+
+// dx = g * mask * scale  (the gradient of the residual is g itself; the bias gradient is the column sum of dx)
+template <typename T>
+__global__ void __launch_bounds__(256) dropout_bwd_kernel(const T* __restrict__ g, T* __restrict__ dx, long long nvec,
+                                                          uint32_t threshold, float scale, unsigned long long seed,
+                                                          unsigned long long offset) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        float v[8], o[8];
+        bool keep[8];
+        Vec8<T>::load(g + i * 8, v);
+        dropout_keep8(seed, offset, i, threshold, keep);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = keep[k] ? v[k] * scale : 0.f;
+        Vec8<T>::store(dx + i * 8, o);
+    }
+}
+
 int ew_grid(long long nvec) {
     long long b = (nvec + 255) / 256;
     const long long cap = (long long)neox_sm_count() * 16;
@@ -621,6 +690,41 @@ int neox_bias_gelu_bwd(const void* g, const void* x, const void* bias, void* dx,
 int neox_bias_residual_add(const void* x, const void* bias, const void* residual, void* out, long long rows, int cols,
                            int dtype, void* stream) {
     return launch_ew<3>(x, residual, bias, out, rows * cols, cols, dtype, (cudaStream_t)stream);
+}
+// out = residual + dropout(x + bias, p) with the Philox stream (seed, offset); consumes 2 * rows * cols / 8 counter
+// values starting at `offset`.  bias and residual may be null.
+int neox_bias_dropout_add_fwd(const void* x, const void* bias, const void* residual, void* out, long long rows,
+                              int cols, float p, unsigned long long seed, unsigned long long offset, int dtype,
+                              void* stream) {
+    if (cols % 8 || p < 0.f || p >= 1.f) return NEOX_ERR_SHAPE;
+    const long long nvec = rows * cols / 8;
+    if (nvec == 0) return 0;
+    const uint32_t thr = (uint32_t)fmin(4294967295.0, (double)p * 4294967296.0);
+    const float scale = 1.0f / (1.0f - p);
+    const int grid = ew_grid(nvec);
+    cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(T) bias_dropout_add_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (const T*)bias, (const T*)residual, (T*)out, nvec, cols / 8, thr, scale, seed, offset)
+    if (dtype == 0) LAUNCH(__nv_bfloat16);
+    else if (dtype == 1) LAUNCH(float);
+    else LAUNCH(__half);
+#undef LAUNCH
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+int neox_dropout_bwd(const void* g, void* dx, long long n, float p, unsigned long long seed, unsigned long long offset,
+                     int dtype, void* stream) {
+    if (n % 8 || p < 0.f || p >= 1.f) return NEOX_ERR_SHAPE;
+    const long long nvec = n / 8;
+    if (nvec == 0) return 0;
+    const uint32_t thr = (uint32_t)fmin(4294967295.0, (double)p * 4294967296.0);
+    const float scale = 1.0f / (1.0f - p);
+    const int grid = ew_grid(nvec);
+    cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(T) dropout_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)g, (T*)dx, nvec, thr, scale, seed, offset)
+    if (dtype == 0) LAUNCH(__nv_bfloat16);
+    else if (dtype == 1) LAUNCH(float);
+    else LAUNCH(__half);
+#undef LAUNCH
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 int neox_gated_act_fwd(const void* x, void* out, long long rows, int cols, int kind, int dtype, void* stream) {
     if (cols % 8) return NEOX_ERR_SHAPE;

@@ -33,7 +33,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import gemm as G
-from . import native
+from . import flop_count, native
 
 E4M3_MAX, E5M2_MAX = 448.0, 57344.0
 
@@ -123,6 +123,9 @@ def gemm_fp8(a: Fp8Tensor, b: Fp8Tensor, a_mn=False, b_mn=False, out=None, out_d
              add=None, act=G.ACT_NONE, aux=None, alpha=1.0, want_preact=False):
     """``epilogue(alpha * op(a) @ op(b))`` on fp8 operands; arguments as ``ops.gemm.gemm``."""
     aq, bq = a.q, b.q
+    if flop_count.ACTIVE[0] is not None:
+        flop_count.gemm(aq.shape[1] if a_mn else aq.shape[0], bq.shape[1] if b_mn else bq.shape[0],
+                        aq.shape[0] if a_mn else aq.shape[1])
     if not aq.is_cuda:
         r = gemm_fp8_ref(a, b, a_mn, b_mn, out_dtype=out_dtype if out is None else out.dtype, bias=bias, add=add,
                          act=act, aux=aux, alpha=alpha, want_preact=want_preact)

@@ -300,9 +300,75 @@ def bias_dropout_add(x, bias, residual, prob, training):
         if bias is not None:
             x = x + bias
         return residual + x
+    if _k(x) and x.is_contiguous() and residual.is_contiguous() and x.dtype == residual.dtype \
+            and x.shape[-1] % 8 == 0 and (bias is None or bias.dtype == x.dtype) and 0.0 < prob < 1.0:
+        return _BiasDropoutAdd.apply(x, bias, residual, float(prob))
     if bias is not None:
         x = x + bias
     return residual + F.dropout(x, p=prob, training=training)
+
+
+def philox_mask_ref(n, p, seed, offset, device="cpu"):
+    """The keep-mask the dropout kernels generate for ``n`` elements (n % 8 == 0): Philox-4x32-10 with key = seed,
+    counter = offset + 2 * (i // 8) + (i % 8) // 4, element kept when its 32 random bits >= p * 2^32.  Pure torch
+    (int64 arithmetic), used by the tests."""
+    idx = torch.arange(n // 4, dtype=torch.int64, device=device)         # one counter per 4 elements
+    ctr = offset + idx
+    M32 = 0xFFFFFFFF
+    c = [ctr & M32, (ctr >> 32) & M32, torch.zeros_like(ctr), torch.zeros_like(ctr)]
+    k0, k1 = seed & M32, (seed >> 32) & M32
+
+    def mulhilo(a, b):
+        # 32 x 32 -> 64-bit product without overflowing int64: split b into 16-bit halves
+        lo16, hi16 = b & 0xFFFF, b >> 16
+        p0 = a * lo16                       # < 2^48
+        p1 = a * hi16                       # < 2^48
+        lo = (p0 + ((p1 & 0xFFFF) << 16))
+        carry = lo >> 32
+        hi = (p1 >> 16) + carry
+        return hi & M32, lo & M32
+    for _ in range(10):
+        hi0, lo0 = mulhilo(torch.full_like(ctr, 0xD2511F53), c[0])
+        hi1, lo1 = mulhilo(torch.full_like(ctr, 0xCD9E8D57), c[2])
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0, k1 = (k0 + 0x9E3779B9) & M32, (k1 + 0xBB67AE85) & M32
+    r = torch.stack(c, dim=1).reshape(-1)
+    thr = min(4294967295, int(p * 4294967296.0))
+    return r >= thr
+
+
+class _BiasDropoutAdd(torch.autograd.Function):
+    """``residual + dropout(x + bias)`` in one pass; the mask is regenerated in backward from the Philox (seed, offset)
+    taken from the device's default generator -- host-side reads only, replayed by activation checkpointing and
+    distinct per tensor-parallel rank inside the model-parallel RNG fork."""
+
+    @staticmethod
+    def forward(ctx, x, bias, residual, p):
+        gen = torch.cuda.default_generators[x.device.index if x.device.index is not None else torch.cuda.current_device()]
+        seed, offset = gen.initial_seed(), gen.get_offset()
+        cols = x.shape[-1]
+        n = x.numel()
+        gen.set_offset(offset + ((n // 4 + 3) // 4) * 4)       # one counter value per four elements
+        out = torch.empty_like(x)
+        rc = native.lib().neox_bias_dropout_add_fwd(native.ptr(x), native.ptr(bias), native.ptr(residual),
+                                                    native.ptr(out), ctypes.c_longlong(n // cols), cols,
+                                                    ctypes.c_float(p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+                                                    ctypes.c_ulonglong(offset), _DT[x.dtype], _s())
+        native.check(rc, "neox_bias_dropout_add_fwd")
+        ctx.cfg = (p, seed & (2 ** 64 - 1), offset, bias is not None, cols)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        p, seed, offset, has_bias, cols = ctx.cfg
+        g = g.contiguous()
+        dx = torch.empty_like(g)
+        rc = native.lib().neox_dropout_bwd(native.ptr(g), native.ptr(dx), ctypes.c_longlong(g.numel()),
+                                           ctypes.c_float(p), ctypes.c_ulonglong(seed), ctypes.c_ulonglong(offset),
+                                           _DT[g.dtype], _s())
+        native.check(rc, "neox_dropout_bwd")
+        gb = dx.reshape(-1, cols).sum(0) if has_bias and ctx.needs_input_grad[1] else None
+        return dx, gb, g, None
 
 
 # ------------------------------------------------------------------------------------ softmax

@@ -22,7 +22,7 @@ import ctypes
 import torch
 import torch.nn.functional as F
 
-from . import native
+from . import flop_count, native
 
 ACT_NONE, ACT_GELU, ACT_DGELU = 0, 1, 2
 
@@ -96,6 +96,9 @@ def gemm_rowmap(a, b, row_ptrs, b_mn=False, bias=None):
 def gemm(a, b, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=None, add=None, act=ACT_NONE,
          aux=None, alpha=1.0, want_preact=False):
     """See module docstring.  ``add`` may alias ``out`` (in-place accumulate, e.g. wgrad into main_grad)."""
+    if flop_count.ACTIVE[0] is not None:
+        flop_count.gemm(a.shape[0], b.shape[1] if b_mn else b.shape[0], a.shape[1]) if not a_mn else \
+            flop_count.gemm(a.shape[1], b.shape[1] if b_mn else b.shape[0], a.shape[0])
     if not a.is_cuda:
         r = gemm_ref(a, b, a_mn, b_mn, out_dtype if out is None else out.dtype, bias, add, act, aux, alpha, want_preact)
         if out is not None:

@@ -17,7 +17,7 @@ import torch
 import torch.nn.functional as F
 
 from . import gemm as G
-from . import native
+from . import flop_count, native
 
 
 def notify_grad_ready(weight):
@@ -99,6 +99,7 @@ class _LinearFn(torch.autograd.Function):
                        want_preact=need_pre)
             out, pre = r if need_pre else (r, None)
         else:
+            flop_count.gemm(x2.shape[0], N, x2.shape[1])
             out = F.linear(x2, weight, bias)
             if act == "gelu":
                 pre = out if need_pre else None

@@ -7,14 +7,20 @@ Both moments are stored as one signed / unsigned byte per element plus one fp32 
 * ``exp_avg_sq`` : ``q = round(255 * sqrt(v / max_block))``                  (square-root domain, unsigned: the second
   moment spans many orders of magnitude inside a block and its square root is what the update divides by)
 
-Every step de-quantises a block, applies the usual Adam(W) recurrences in fp32 and re-quantises, so the state costs
+Every step de-quantises a block, applies the usual Adam(W) recurrences in fp32 and re-quantises (on a GPU in one
+kernel, ``adam8bit_kernel`` in ``ops/csrc/misc_kernels.cu``: one CTA per block of 256), so the state costs
 2 bytes + 1/32 byte per parameter instead of 8.  The update itself is element-wise, so it works on the flat fp32 master
 shard of the mixed-precision optimizer like any other inner optimizer (and writes the bf16 model copy when the shard
 carries ``model_out``).  Large tensors are processed in chunks to bound the fp32 temporaries.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
+
+from ..ops import native
+from ..ops.functional import _DT
 
 BLOCK = 256
 CHUNK = 1 << 24      # elements per pass (multiple of BLOCK)
@@ -82,6 +88,18 @@ class Adam8bit(torch.optim.Optimizer):
                         st["qv"] = torch.zeros(n + pad, dtype=torch.uint8, device=p.device)
                         st["sm"] = torch.zeros((n + pad) // BLOCK, dtype=torch.float32, device=p.device)
                         st["sv"] = torch.zeros((n + pad) // BLOCK, dtype=torch.float32, device=p.device)
+                if (not small and p.is_cuda and native.available() and p.dtype == torch.float32
+                        and flat_g.dtype == torch.float32 and flat_p.is_contiguous() and flat_g.is_contiguous()):
+                    # one kernel: de-quantise, update, re-quantise, write the parameter (and its 16-bit copy)
+                    rc = native.lib().neox_adam8bit_step(
+                        native.ptr(flat_p), native.ptr(st["qm"]), native.ptr(st["qv"]), native.ptr(st["sm"]),
+                        native.ptr(st["sv"]), native.ptr(flat_g), native.ptr(out),
+                        _DT[out.dtype] if out is not None else 1, ctypes.c_longlong(n), ctypes.c_float(lr),
+                        ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(eps), ctypes.c_float(wd),
+                        ctypes.c_float(bc1), ctypes.c_float(bc2), ctypes.c_float(gs), int(self.adam_w_mode),
+                        ctypes.c_void_p(native.stream_ptr()))
+                    native.check(rc, "neox_adam8bit_step")
+                    continue
                 for lo in range(0, n, CHUNK):
                     hi = min(lo + CHUNK, n)
                     g = flat_g[lo:hi].float() * gs

@@ -9,7 +9,8 @@ Differences in mechanism, not in math: the reference issues three all-reduces (m
 sum-exp) and keeps the full softmax alive for backward; here the target logit and the sum-exp travel
 in ONE all-reduce of a ``[rows, 2]`` tensor, only two fp32 scalars per row are saved, and the
 softmax is re-formed in backward directly into the gradient buffer.  On CUDA the row statistics
-and the backward are single-pass kernels (``csrc/loss.cu``).
+and the backward are single-pass kernels (the ``ce_*`` kernels of
+``ops/csrc/misc_kernels.cu``).
 """
 from __future__ import annotations
 

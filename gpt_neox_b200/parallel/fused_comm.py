@@ -32,7 +32,7 @@ import torch.distributed as dist
 
 from ..ops import gemm as G
 from ..ops import native
-from . import mpu
+from . import comms_logger, mpu
 from . import symm_mem as S
 
 _workspaces = {}
@@ -40,12 +40,19 @@ _workspaces = {}
 COPY_CTAS = int(os.environ.get("NEOX_COPY_CTAS", "16"))
 
 
-def fused_all_gather() -> bool:
-    """Whether gathered operands arrive by the in-GEMM broadcast (``NEOX_FUSED_AG=1``) or by an NCCL all-gather
-    before a plain GEMM (default).  Measured on 2 B200s at h=6144, 8192 tokens: the broadcast shares the L2 ports
-    with the GEMM's operand traffic and ends up 5-10% slower than "NCCL all-gather, then GEMM", while the pushed
-    reduce-scatter / all-reduce is 5-45% faster than its NCCL form and is always on."""
-    return os.environ.get("NEOX_FUSED_AG", "0") == "1"
+def fused_all_gather(world=None) -> bool:
+    """Whether gathered operands arrive by the in-GEMM broadcast or by an NCCL all-gather before a plain GEMM.
+    ``NEOX_FUSED_AG=1`` / ``0`` forces one; by default the broadcast is used from 4 ranks up.  Measured at h=6144,
+    8192 tokens: on 2 B200s the broadcast shares the L2 ports with the GEMM's operand traffic and ends up 5-10%
+    slower than "NCCL all-gather, then GEMM"; on 4 it is 2-7% faster (each rank sends the same shard to three
+    peers while the NCCL ring needs three serial steps).  The pushed reduce-scatter / all-reduce is faster than
+    its NCCL form at every size and is always on."""
+    mode = os.environ.get("NEOX_FUSED_AG", "auto")
+    if mode in ("0", "1"):
+        return mode == "1"
+    if world is None:
+        world = mpu.get_model_parallel_world_size()
+    return world >= 4
 
 
 def _nccl_gather_rows(x2):
@@ -124,6 +131,7 @@ class Workspace:
         until ``release(h)``; a tensor that must outlive that has to be cloned.
         """
         assert x2.is_contiguous() and x2.dtype == torch.bfloat16 and x2.shape[0] % 128 == 0
+        comms_logger.record_fused("fused_all_gather_gemm", x2.numel() * 2 * self.world, self.world)
         self.bc_epoch += 1
         e = self.bc_epoch
         rows, cols = x2.shape
@@ -229,6 +237,8 @@ class Workspace:
         M, K = a.shape
         N = b.shape[1] if b_mn else b.shape[0]
         rows = M // self.world
+        comms_logger.record_fused("fused_gemm_all_reduce" if all_reduce else "fused_gemm_reduce_scatter",
+                                  M * N * 2, self.world)
         self.rs_epoch += 1
         e = self.rs_epoch
         recv = self._buf("recv", e & 1, M * N * 2)

@@ -27,6 +27,8 @@ from .models import (GPT2ModelPipe, SoftEmbedding, cross_entropy, get_params_for
                      mark_norms_for_sequence_parallel_grad_sync)
 from .parallel import mpu
 from .parallel.data import broadcast_data
+from .parallel import comms_logger
+from .utils.flops_profiler import FlopsProfiler
 from .utils import (CharCounter, OverflowMonitor, Timers, get_ltor_masks_and_position_ids, get_noise_scale_logger,
                     get_total_params, print_rank_0, reduce_losses)
 
@@ -499,6 +501,10 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
     if noise_scale_logger is not None:
         noise_scale_logger = noise_scale_logger(model)
     overflow_monitor = OverflowMonitor(optimizer)
+    ds_cfg = neox_args.deepspeed_config
+    comms = comms_logger.configure(neox_args.comms_logger or ds_cfg.get("comms_logger"))
+    flops_prof = FlopsProfiler.from_config(getattr(model, "module", model),
+                                           neox_args.flops_profiler or ds_cfg.get("flops_profiler"))
     prof = None
     if neox_args.profile and torch.cuda.is_available():
         sched = torch.profiler.schedule(wait=neox_args.profile_step_start, warmup=1,
@@ -513,9 +519,17 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
             prof.step()
         if neox_args.profile and iteration == neox_args.profile_step_start and torch.cuda.is_available():
             torch.cuda.cudart().cudaProfilerStart()
+        profiling_flops = flops_prof.enabled and iteration + 1 == flops_prof.profile_step
+        if profiling_flops:
+            flops_prof.start_profile()
         loss_dict, skipped_iter = train_step(neox_args=neox_args, timers=timers, data_iterator=train_data_iterator,
                                              model=model, optimizer=optimizer, lr_scheduler=lr_scheduler,
                                              reference_model=reference_model)
+        if profiling_flops:
+            flops_prof.stop_profile()
+            print_rank_0(flops_prof.report(batch_size=neox_args.train_batch_size // max(mpu.get_data_parallel_world_size(), 1)))
+        if comms.enabled and (iteration + 1) % neox_args.log_interval == 0:
+            comms.log_summary()
         if neox_args.profile and iteration == neox_args.profile_step_stop and torch.cuda.is_available():
             torch.cuda.cudart().cudaProfilerStop()
             if prof is not None:

@@ -202,3 +202,100 @@ def test_weight_server_answers_with_a_length_prefixed_map():
     while len(payload) < n:
         payload += c.recv(n - len(payload))
     assert pickle.loads(payload) == {}
+
+
+# ------------------------------------------------------------------ comms logger / flops profiler
+def _comms_worker(rank, world, port, q):
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from gpt_neox_b200.parallel import comms_logger
+    stock = dist.all_reduce
+    log = comms_logger.configure({"enabled": True, "verbose": False, "prof_all": True})
+    x = torch.ones(1024)
+    for _ in range(3):
+        dist.all_reduce(x)
+    out = torch.empty(2048)
+    dist.all_gather_into_tensor(out, torch.ones(1024))
+    w = dist.all_reduce(torch.ones(256), async_op=True)
+    w.wait()
+    comms_logger.record_fused("fused_gemm_reduce_scatter", 1 << 20, world)
+    rows = log.summary()
+    text = log.log_summary(print_fn=lambda s: None)
+    log.uninstall()
+    assert dist.all_reduce is stock
+    dist.destroy_process_group()
+    q.put((rank, rows, text))
+
+
+def test_comms_logger_counts_sizes_and_bandwidth():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29000 + os.getpid() % 2000
+    procs = [ctx.Process(target=_comms_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    for rank, rows, text in res:
+        by = {(op, nbytes): (count, total, mean, alg, bus) for op, nbytes, count, total, mean, alg, bus in rows}
+        assert by[("all_reduce", 4096)][0] == 3 and by[("all_reduce", 1024)][0] == 1
+        assert by[("all_gather_into_tensor", 8192)][0] == 1
+        assert by[("fused_gemm_reduce_scatter", 1 << 20)][0] == 1
+        count, total, mean, alg, bus = by[("all_reduce", 4096)]
+        assert total > 0 and abs(mean - total / 3) < 1e-9 and abs(bus - alg * 1.0) < 1e-6     # 2 (n-1)/n = 1 at n = 2
+        assert "all_reduce" in text and "busbw_avg" in text
+
+
+def test_comms_logger_disabled_leaves_torch_distributed_alone():
+    import torch.distributed as dist
+    from gpt_neox_b200.parallel import comms_logger
+    before = dist.all_reduce
+    log = comms_logger.configure({"enabled": False})
+    assert dist.all_reduce is before and not log.enabled
+    log = comms_logger.configure({"enabled": True, "prof_all": False, "prof_ops": ["all_reduce"]})
+    assert dist.all_reduce is not before and log.wants("all_reduce") and not log.wants("broadcast")
+    log.uninstall()
+    assert dist.all_reduce is before
+    comms_logger.configure(None)
+
+
+def _flops_worker(rank, world, out_file):
+    import torch
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.training import setup_model_and_optimizer, train_step
+    from gpt_neox_b200.utils import Timers
+    from gpt_neox_b200.utils.flops_profiler import FlopsProfiler
+    from common import make_args
+    counts = []
+    for ckpt in (False, True):
+        args = make_args(global_num_gpus=1, checkpoint_activations=ckpt, checkpoint_num_layers=1)
+        args.configure_distributed_args()
+        if not counts:
+            initialize_megatron(args)
+        model, opt, sched, _ = setup_model_and_optimizer(args)
+        g = torch.Generator().manual_seed(0)
+        batch = {"text": torch.randint(0, args.padded_vocab_size, (2, args.seq_length + 1), generator=g)}
+        prof = FlopsProfiler.from_config(model.module, {"enabled": True, "profile_step": 1, "module_depth": 2,
+                                                        "top_modules": 3, "detailed": True, "output_file": out_file})
+        prof.start_profile()
+        train_step(args, Timers(), iter([batch]), model, opt, sched)
+        prof.stop_profile()
+        text = prof.report(batch_size=2)
+        T, h, s, L, V = 2 * args.seq_length, args.hidden_size, args.seq_length, args.num_layers, args.padded_vocab_size
+        expect = L * (2 * T * h * (3 * h + h + 4 * h + 4 * h) + 4 * 2 * args.num_attention_heads * s * s
+                      * (h // args.num_attention_heads) * 0.5) + 2 * T * h * V
+        assert abs(prof.total_flops() - expect) / expect < 1e-6, (prof.total_flops(), expect)
+        assert "fwd flops per GPU" in text and "depth 1:" in text and open(out_file).read().strip() == text.strip()
+        counts.append(prof.total_flops())
+    assert counts[0] == counts[1]           # a recomputed forward is not counted a second time
+
+
+def test_flops_profiler_counts_forward_flops_of_a_small_model(tmp_path):
+    from common import run_distributed
+    run_distributed(_flops_worker, 1, str(tmp_path / "flops.txt"))

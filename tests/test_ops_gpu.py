@@ -707,3 +707,47 @@ def test_adam8bit_tracks_fp32_adam():
     assert (p8 - p32).abs().max().item() < 0.15 and (p8 - target).norm() < 0.8 * target.norm()
     st = o8.state[p8]
     assert any(t.dtype in (torch.int8, torch.uint8) for t in st.values() if torch.is_tensor(t))
+    # the CUDA kernel and the chunked torch statement of the same update agree (same quantised states, same result)
+    pc = torch.nn.Parameter(torch.zeros(n))
+    oc = Adam8bit([pc], lr=5e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    pg = torch.nn.Parameter(torch.zeros(n, device=DEV))
+    og = Adam8bit([pg], lr=5e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    gen = torch.Generator().manual_seed(5)
+    for _ in range(5):
+        gr = torch.randn(n, generator=gen)
+        pc.grad, pg.grad = gr.clone(), gr.to(DEV)
+        oc.step()
+        og.step()
+    _close(pg.detach().cpu(), pc.detach(), 2e-3, rtol=1e-3)
+    assert (og.state[pg]["qm"].cpu().int() - oc.state[pc]["qm"].int()).abs().max().item() <= 1
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_bias_dropout_add_kernel_matches_the_philox_mask(dtype):
+    """Training-mode bias + dropout + residual add in one kernel: forward and backward against the same Philox
+    mask generated in plain torch; the keep rate is 1 - p; a replayed generator state reproduces the mask."""
+    torch.manual_seed(123)
+    rows, cols, p = 300, 1024, 0.1
+    x = torch.randn(rows, cols, device=DEV, dtype=dtype, requires_grad=True)
+    bias = torch.randn(cols, device=DEV, dtype=dtype, requires_grad=True)
+    res = torch.randn(rows, cols, device=DEV, dtype=dtype, requires_grad=True)
+    gen = torch.cuda.default_generators[torch.cuda.current_device()]
+    state = torch.cuda.get_rng_state()
+    seed, offset = gen.initial_seed(), gen.get_offset()
+    out = OF.bias_dropout_add(x, bias, res, p, True)
+    assert gen.get_offset() > offset                       # the stream was advanced: the next call draws a new mask
+    keep = OF.philox_mask_ref(rows * cols, p, seed, offset, device=DEV).view(rows, cols)
+    assert abs(keep.float().mean().item() - (1 - p)) < 5e-3
+    want = res.float() + torch.where(keep, (x.float() + bias.float()) / (1 - p), torch.zeros((), device=DEV))
+    _close(out, want, 2e-2 if dtype != torch.float32 else 1e-5)
+    g = torch.randn_like(out)
+    out.backward(g)
+    gx = torch.where(keep, g.float() / (1 - p), torch.zeros((), device=DEV))
+    _close(x.grad, gx, 2e-2 if dtype != torch.float32 else 1e-5)
+    _close(res.grad, g, 0.0, rtol=0.0)
+    _close(bias.grad, gx.sum(0), 0.5 if dtype != torch.float32 else 1e-3, rtol=2e-2)
+    torch.cuda.set_rng_state(state)                        # what activation checkpointing does before recomputing
+    again = OF.bias_dropout_add(x.detach(), bias.detach(), res.detach(), p, True)
+    assert torch.equal(again, out.detach())
+    other = OF.bias_dropout_add(x.detach(), bias.detach(), res.detach(), p, True)
+    assert not torch.equal(other, out.detach())
