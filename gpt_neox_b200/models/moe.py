@@ -23,6 +23,7 @@ over the expert-data-parallel group only.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -31,6 +32,7 @@ import torch.nn.functional as F
 
 from ..ops import functional as OF
 from ..ops import gemm as G
+from ..ops import moe_ops as MO
 from ..ops.linear import linear as fused_linear
 from ..parallel import moe_comm, mpu
 from ..parallel.rng import get_cuda_rng_tracker
@@ -124,12 +126,9 @@ class Router(nn.Module):
             noise = torch.empty_like(x).uniform_(1.0 - self.jitter_eps, 1.0 + self.jitter_eps)
             x = x * noise
         logits = self.layer(x)
-        # router probabilities always in fp32 (``moe_lbl_in_fp32`` only matters for the statistics built from them)
-        probs = F.softmax(logits.float(), dim=-1)
-        w, idx = torch.topk(probs, self.top_k, dim=-1)
-        if self.top_k > 1:
-            w = w / w.sum(dim=-1, keepdim=True)
-        return probs, w, idx
+        # router probabilities always in fp32 (``moe_lbl_in_fp32`` only matters for the statistics built from them);
+        # softmax, top-k, renormalisation and the expert histogram are one kernel on a GPU
+        return MO.router(logits, self.top_k)
 
 
 class ParallelMoE(nn.Module):
@@ -173,6 +172,9 @@ class ParallelMoE(nn.Module):
             self.w1.expert_parallel = True
             self.w2.expert_parallel = True
         self.w1.moe_expert = self.w2.moe_expert = True
+        # None: grouped expert GEMMs whenever the kernels take the shapes (GPU); True forces the grouped data flow
+        # through its eager statement (CPU oracle), False keeps the per-expert loop
+        self.grouped = None
 
     # ------------------------------------------------------------------ expert compute
     def _expert(self, e, seg):
@@ -221,6 +223,55 @@ class ParallelMoE(nn.Module):
         back = [list(c) for c in zip(*matrix)]          # rows this rank returns to rank r = rows r sent here
         return _ExpertOutCombine.apply(hdn, self.w2, bounds, perm_t, perm, src, block_start, back, matrix, grp)
 
+    def _activate(self, x_pad, counts):
+        """First expert projection + activation over the padded expert-major matrix."""
+        if self.glu:
+            kind = "swiglu" if self.activation in ("swiglu", "silu") else "geglu"
+            return OF.gated_act(MO.grouped_linear(x_pad, self.w1, counts), kind)
+        if self.activation == "gelu":
+            return MO.grouped_linear(x_pad, self.w1, counts, act="gelu")
+        return OF.get_activation(self.activation)(MO.grouped_linear(x_pad, self.w1, counts))
+
+    def _use_grouped(self, x):
+        if self.grouped is not None:
+            return self.grouped
+        if os.environ.get("NEOX_MOE_GROUPED", "1") == "0":     # per-expert loop, for A/B timing
+            return False
+        probe = x.new_empty(128, x.shape[1])
+        return MO.grouped_kernel_ok(probe, self.w1) and MO.grouped_kernel_ok(x.new_empty(128, self.ffn), self.w2)
+
+    def _forward_grouped(self, x, w, idx, counts):
+        """All local experts in two grouped GEMM launches; no value is read back by the host."""
+        T, k = idx.shape
+        cap = self._capacity(T) if self.token_dropping else None
+        row_of, kept = MO.plan_rows(idx, counts, cap)
+        xs = MO.dispatch(x, row_of, MO.padded_rows(T * k, self.num_experts))
+        out = MO.grouped_linear(self._activate(xs, kept), self.w2, kept)
+        return MO.combine(out, row_of, w)
+
+    def _experts_grouped(self, xr, recv_l):
+        """Local experts over the rows received from the expert-parallel group (ordered by source rank, then local
+        expert): re-ordered into the padded expert-major matrix, two grouped GEMM launches, and back."""
+        import numpy as np
+        L = self.local_experts
+        n_e = [sum(recv_l[r][e] for r in range(self.ep)) for e in range(L)]
+        start, row = [], 0
+        for n in n_e:
+            start.append(row)
+            row += (n + MO.PAD - 1) // MO.PAD * MO.PAD
+        rows = max(128, (row + 127) // 128 * 128)
+        dst, fill = [], [0] * L
+        for r in range(self.ep):
+            for e in range(L):
+                n = recv_l[r][e]
+                dst.append(np.arange(start[e] + fill[e], start[e] + fill[e] + n, dtype=np.int64))
+                fill[e] += n
+        dst_t = torch.from_numpy(np.concatenate(dst)).to(xr.device, non_blocking=True)
+        counts = torch.tensor(n_e, dtype=torch.int64).to(xr.device, non_blocking=True)
+        xe = torch.zeros(rows, xr.shape[1], dtype=xr.dtype, device=xr.device).index_copy(0, dst_t, xr)
+        out = MO.grouped_linear(self._activate(xe, counts), self.w2, counts)
+        return out.index_select(0, dst_t)
+
     def _capacity(self, tokens):
         cf = self.train_cf if self.training else self.eval_cf
         return max(self.min_capacity, int(math.ceil(cf * tokens * self.top_k / self.num_experts)))
@@ -229,13 +280,15 @@ class ParallelMoE(nn.Module):
         shape = hidden_states.shape
         x = hidden_states.reshape(-1, shape[-1])
         T, E, k = x.shape[0], self.num_experts, self.top_k
-        probs, w, idx = self.router(x)
+        probs, w, idx, counts = self.router(x)
         # ---- load-balancing statistics
         flat_e = idx.reshape(-1)
-        counts = torch.bincount(flat_e, minlength=E)
         f = counts.float() / float(T * k)
         P = probs.mean(dim=0)
         lbl = E * torch.sum(f.detach() * P)
+        if self.ep == 1 and self._use_grouped(x):
+            y = self._forward_grouped(x, w, idx, counts)
+            return y.reshape(shape), lbl.to(hidden_states.dtype)
         # ---- sort assignments by expert (stable: token order preserved inside an expert)
         order = torch.argsort(flat_e, stable=True)
         sorted_e = flat_e[order]
@@ -277,6 +330,12 @@ class ParallelMoE(nn.Module):
                     off += n
             if peer and moe_comm.fused_combine_enabled() and xr.shape[0] > 0:
                 ys = self._experts_fused_combine(xr, pieces, matrix, out_splits, grp)
+            elif xr.shape[0] > 0 and self._use_grouped(x):
+                outs = self._experts_grouped(xr, recv_l)
+                if peer:
+                    ys = moe_comm.all_to_all_rows(outs, [list(c) for c in zip(*matrix)], grp)
+                else:
+                    ys = _AllToAll.apply(outs, in_splits, out_splits, grp)
             else:
                 res_parts = {}
                 for e in range(self.local_experts):
@@ -301,3 +360,24 @@ class ParallelMoE(nn.Module):
         y = torch.zeros_like(x)
         y.index_add_(0, tok, ys * gate[:, None])
         return y.reshape(shape), lbl.to(hidden_states.dtype)
+
+
+class ResidualMoE(nn.Module):
+    """Residual mixture of experts (DeepSpeed's ``use_residual``, which the reference passes as ``moe_use_residual``
+    when ``moe_type`` is ``deepspeed``, ``megatron/model/transformer.py:1084-1100``): a dense MLP runs beside the
+    experts and a learned per-token two-way softmax mixes the two outputs."""
+
+    def __init__(self, neox_args, init_method, output_layer_init_method, num_experts, dense_mlp):
+        super().__init__()
+        self.moe = ParallelMoE(neox_args, init_method, output_layer_init_method, num_experts)
+        self.mlp = dense_mlp
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
+        self.coefficient = nn.Linear(neox_args.hidden_size, 2, device=dev, dtype=neox_args.params_dtype)
+
+    def forward(self, hidden_states):
+        out, lbl = self.moe(hidden_states)
+        dense, bias = self.mlp(hidden_states)
+        if bias is not None:
+            dense = dense + bias
+        coef = F.softmax(self.coefficient(hidden_states).float(), dim=-1).to(out.dtype)
+        return out * coef[..., 0:1] + dense * coef[..., 1:], lbl

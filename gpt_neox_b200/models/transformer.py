@@ -389,8 +389,12 @@ class ParallelTransformerLayer(nn.Module):
             self.mlp = ParallelMLP(neox_args, init_method, output_layer_init_method,
                                    parallel_output=self.gpt_j_residual)
         else:
-            from .moe import ParallelMoE
-            self.mlp = ParallelMoE(neox_args, init_method, output_layer_init_method, self.num_experts)
+            from .moe import ParallelMoE, ResidualMoE
+            if neox_args.moe_type == "deepspeed" and neox_args.moe_use_residual:
+                dense = ParallelMLP(neox_args, init_method, output_layer_init_method, parallel_output=False)
+                self.mlp = ResidualMoE(neox_args, init_method, output_layer_init_method, self.num_experts, dense)
+            else:
+                self.mlp = ParallelMoE(neox_args, init_method, output_layer_init_method, self.num_experts)
             self.mlp_type = "moe"
 
     def _reduce(self, x):

@@ -39,6 +39,27 @@ struct GemmParams {
     // D + r * ldd -- the rows of one GEMM can then land in different buffers, including peers' memory
     const unsigned long long* row_ptrs;
     int h16 = 0;   // 16-bit storage type of the operands, D, bias, add, preact, aux: 0 = bf16, 1 = fp16
+    // grouped GEMM (one launch for all experts of a mixture-of-experts layer): a device-built table with one int4
+    // per output tile, and a device word with the number of valid entries.
+    //   mode 1, rows grouped (forward, dgrad): {first row of A / D, end row of the segment, offset of this expert
+    //           in B (rows of a K-major B, contraction rows of an MN-major B), column block}
+    //   mode 2, contraction grouped (wgrad): {first contraction row, number of 64-row contraction blocks, expert
+    //           (output rows e * M ...), row block << 16 | column block}
+    const int4* groups = nullptr;
+    const int* group_ntiles = nullptr;
+    int group_mode = 0;
+};
+
+// Where one output tile reads and writes: plain tiles come from tile_coords, grouped ones from the table.
+struct TileInfo {
+    int a_m0;      // row coordinate of A's tile (MN index)
+    int a_k0;      // contraction offset of an MN-major A
+    int b_n0;      // row coordinate of B's tile (MN index, plus the expert's row offset for a K-major B)
+    int b_k0;      // contraction offset of an MN-major B
+    int n0;        // first output column
+    int nk;        // contraction blocks of BK
+    int row0;      // output row of accumulator lane 0
+    int row_end;   // rows at or beyond it are not stored
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
@@ -49,6 +70,28 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
     const int in_group = tile - group * per_group;
     m_blk = first_m + in_group % gsize;
     n_blk = in_group / gsize;
+}
+
+__device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int num_m, int num_n, int nk_all) {
+    TileInfo t;
+    if (p.group_mode == 0) {
+        int m_blk, n_blk;
+        tile_coords(tile, num_m, num_n, m_blk, n_blk);
+        t.a_m0 = m_blk * BM; t.a_k0 = 0; t.b_n0 = n_blk * BN; t.b_k0 = 0; t.n0 = n_blk * BN; t.nk = nk_all;
+        t.row0 = m_blk * BM; t.row_end = p.M;
+    } else if (p.group_mode == 1) {
+        const int4 g = __ldg(p.groups + tile);
+        t.a_m0 = g.x; t.a_k0 = 0; t.n0 = g.w * BN; t.nk = nk_all;
+        t.b_n0 = p.b_mn ? t.n0 : g.z + t.n0;
+        t.b_k0 = p.b_mn ? g.z : 0;
+        t.row0 = g.x; t.row_end = g.y;
+    } else {
+        const int4 g = __ldg(p.groups + tile);
+        const int m_blk = g.w >> 16, n_blk = g.w & 0xffff;
+        t.a_m0 = m_blk * BM; t.a_k0 = g.x; t.b_n0 = n_blk * BN; t.b_k0 = g.x; t.n0 = n_blk * BN; t.nk = g.y;
+        t.row0 = g.z * p.M + m_blk * BM; t.row_end = g.z * p.M + p.M;
+    }
+    return t;
 }
 
 // Apply the fused epilogue to 32 consecutive columns of one output row (H16: fp16 storage, else bf16).

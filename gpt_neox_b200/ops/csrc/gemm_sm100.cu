@@ -69,7 +69,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
     const int num_m = (p.M + BM - 1) / BM;
     const int num_n = (p.N + BN - 1) / BN;
-    const int ntiles = num_m * num_n;
+    const int ntiles = p.group_mode ? __ldg(p.group_ntiles) : num_m * num_n;
     const int nk = (p.K + BK - 1) / BK;
 
     if (warp == 0) {
@@ -79,9 +79,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                int m_blk, n_blk;
-                tile_coords(tile, num_m, num_n, m_blk, n_blk);
-                for (int kb = 0; kb < nk; ++kb) {
+                const TileInfo t = tile_info(p, tile, num_m, num_n, nk);
+                for (int kb = 0; kb < t.nk; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) {
                         atomicExch(p.status, 101);
                         ok = false;
@@ -91,18 +90,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
                     uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
                     if (!p.a_mn) {
-                        tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m_blk * BM);
+                        tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, t.a_m0);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j)
-                            tma_load_2d(a_dst + j * (64 * BK * 2), &tmA, &full[stage], m_blk * BM + j * 64, kb * BK);
+                            tma_load_2d(a_dst + j * (64 * BK * 2), &tmA, &full[stage], t.a_m0 + j * 64,
+                                        t.a_k0 + kb * BK);
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n_blk * BN);
+                        tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, t.b_n0);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(b_dst + j * (64 * BK * 2), &tmB, &full[stage], n_blk * BN + j * 64, kb * BK);
+                            tma_load_2d(b_dst + j * (64 * BK * 2), &tmB, &full[stage], t.b_n0 + j * 64,
+                                        t.b_k0 + kb * BK);
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -136,7 +137,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < nk; ++kb) {
+                const int nk_t = p.group_mode == 2 ? __ldg(p.groups + tile).y : nk;
+                for (int kb = 0; kb < nk_t; ++kb) {
                     if (!mbar_wait(&full[stage], phase)) {
                         atomicExch(p.status, 103);
                         ok = false;
@@ -167,23 +169,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         int buf = 0;
         uint32_t bphase = 0;
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            int m_blk, n_blk;
-            tile_coords(tile, num_m, num_n, m_blk, n_blk);
+            const TileInfo t = tile_info(p, tile, num_m, num_n, nk);
             if (!mbar_wait_warp(&tfull[buf], bphase)) {
                 if (lane == 0) atomicExch(p.status, 104);
                 break;
             }
             tc_fence_after();
-            const int row = m_blk * BM + q * 32 + lane;
+            const int row = t.row0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
-                const int col0 = n_blk * BN + c * 32;
+                const int col0 = t.n0 + c * 32;
                 if (col0 >= p.N) break;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32, r);
                 tmem_wait_ld();
-                if (row < p.M) epilogue_chunk(r, row, col0, p);
+                if (row < t.row_end) epilogue_chunk(r, row, col0, p);
             }
             tc_fence_before();
             __syncwarp();
@@ -387,6 +388,130 @@ extern "C" int neox_gemm_16(const void* A, const void* B, void* D, int M, int N,
     }
     const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     int grid = num_m * num_n;
+    const int sms = neox_sm_count();
+    if (grid > sms) grid = sms;
+    gemm_bf16_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Grouped GEMM for mixture-of-experts layers: all experts in one launch of the kernel above.
+//
+// The rows routed to expert e form one contiguous segment of the activation matrix; segment e starts at
+// sum_{i<e} round_up(count_i, pad) (pad = 64 keeps every segment on a contraction-block boundary, which the weight
+// gradient needs; the padding rows must hold zeros).  The tile table is built ON THE DEVICE from the per-expert
+// counts, so routing never needs a host synchronisation.  Counterpart of the grouped / block-sparse expert GEMMs
+// of the MegaBlocks library that the reference calls (megatron/model/moe_mlp.py of the reference: `gg.ops.gmm`).
+__global__ void __launch_bounds__(256) moe_tile_table_kernel(const long long* __restrict__ counts, int E, int pad,
+                                                             int mode, int num_m, int num_n, int b_stride,
+                                                             int max_tiles, int4* __restrict__ table,
+                                                             int* __restrict__ ntiles) {
+    extern __shared__ int sh[];   // [E] segment starts, [E] first tile of each expert
+    int* seg = sh;
+    int* first = sh + E;
+    if (threadIdx.x == 0) {
+        int row = 0, tile = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = (int)counts[e];
+            seg[e] = row;
+            first[e] = tile;
+            row += (c + pad - 1) / pad * pad;
+            if (mode == 1) tile += ((c + pad - 1) / pad * pad + BM - 1) / BM * num_n;
+            else tile += c > 0 ? num_m * num_n : 0;
+        }
+        *ntiles = tile < max_tiles ? tile : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int c = (int)counts[e];
+        int t = first[e];
+        if (mode == 1) {
+            // the padding rows of a segment are computed too (their inputs are zero), so that every row a later
+            // contraction-grouped GEMM reads holds a finite value
+            const int cp = (c + pad - 1) / pad * pad;
+            const int mb_n = (cp + BM - 1) / BM;
+            for (int nb = 0; nb < num_n; ++nb)
+                for (int mb = 0; mb < mb_n; ++mb, ++t)
+                    if (t < max_tiles) table[t] = make_int4(seg[e] + mb * BM, seg[e] + cp, e * b_stride, nb);
+        } else if (c > 0) {
+            for (int nb = 0; nb < num_n; ++nb)
+                for (int mb = 0; mb < num_m; ++mb, ++t)
+                    if (t < max_tiles) table[t] = make_int4(seg[e], (c + BK - 1) / BK, e, (mb << 16) | nb);
+        }
+    }
+}
+
+// mode 1: D[rows of segment e, :] = act(alpha * A[rows, :] @ op(B_e)) (+ add), A [m_total, K] K-major, B the stacked
+//         expert matrices: [E * N, K] K-major (b_mn = 0) or [E * K, N] MN-major (b_mn = 1; K % 64 == 0).
+//         M = m_total (rows of A and D).
+// mode 2: D[e * M + m, n] = sum over the rows r of segment e of A[r, m] * B[r, n] (+ add): A [m_total, M] and
+//         B [m_total, N] both MN-major (a_mn = b_mn = 1), D the stacked [E * M, N]; `K` = m_total.
+// `table` holds max_tiles int4 entries, `ntiles` one int; both are written by this call (on `stream`).
+extern "C" int neox_gemm_grouped_16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldd, int b_mn, int d_fp32, const void* add,
+                                    long long ldadd, int add_fp32, void* preact, long long ldpre, const void* aux,
+                                    long long ldaux, int act, float alpha, const long long* counts, int E, int pad,
+                                    int mode, void* table, int max_tiles, int* ntiles, int h16, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0 || K <= 0 || E <= 0 || max_tiles <= 0) return 0;
+    if (mode != 1 && mode != 2) return NEOX_ERR_SHAPE;
+    if (E > 4096 || pad < 1) return NEOX_ERR_SHAPE;
+    if (mode == 1 && b_mn && (K % BK)) return NEOX_ERR_SHAPE;   // an expert's contraction rows end on a block edge
+    if (mode == 2 && (pad % BK)) return NEOX_ERR_SHAPE;         // segments start and end on contraction blocks
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8))
+        return NEOX_ERR_ALIGN;
+    int* status = neox_status_word();
+    if (!status) return NEOX_ERR_DRIVER;
+
+    CUtensorMap tmA, tmB;
+    int rc;
+    const int a_mn = mode == 2;
+    if (mode == 1) {
+        rc = neox_make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
+        if (rc) return rc;
+        if (!b_mn) rc = neox_make_tmap_bf16_2d(&tmB, B, K, (unsigned long long)E * N, ldb, BK, BN);
+        else rc = neox_make_tmap_bf16_2d(&tmB, B, N, (unsigned long long)E * K, ldb, 64, BK);
+    } else {
+        b_mn = 1;
+        rc = neox_make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+        if (rc) return rc;
+        rc = neox_make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+    }
+    if (rc) return rc;
+
+    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    if (mode == 2 && (num_m > 0x7fff || num_n > 0xffff)) return NEOX_ERR_SHAPE;
+    moe_tile_table_kernel<<<1, 256, 2 * E * sizeof(int), stream>>>(counts, E, pad, mode, num_m, num_n,
+                                                                    b_mn ? K : N, max_tiles,
+                                                                    static_cast<int4*>(table), ntiles);
+    if (cudaGetLastError() != cudaSuccess) return NEOX_ERR_LAUNCH;
+
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K;
+    p.a_mn = a_mn; p.b_mn = b_mn;
+    p.D = D; p.ldd = ldd; p.d_fp32 = d_fp32;
+    p.bias = nullptr;
+    p.add = add; p.ldadd = ldadd; p.add_fp32 = add_fp32;
+    p.preact = static_cast<__nv_bfloat16*>(preact); p.ldpre = ldpre;
+    p.aux = static_cast<const __nv_bfloat16*>(aux); p.ldaux = ldaux;
+    p.act = act; p.alpha = alpha;
+    p.status = status;
+    p.row_ptrs = nullptr;
+    p.h16 = h16 ? 1 : 0;
+    p.groups = static_cast<const int4*>(table);
+    p.group_ntiles = ntiles;
+    p.group_mode = mode;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    bool vec = al16(D) && (ldd % 8 == 0);
+    if (add) vec = vec && al16(add) && (ldadd % 8 == 0);
+    if (preact) vec = vec && al16(preact) && (ldpre % 8 == 0);
+    if (aux) vec = vec && al16(aux) && (ldaux % 8 == 0);
+    p.vec_ok = vec ? 1 : 0;
+
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) return NEOX_ERR_LAUNCH;
+    int grid = max_tiles;
     const int sms = neox_sm_count();
     if (grid > sms) grid = sms;
     gemm_bf16_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);

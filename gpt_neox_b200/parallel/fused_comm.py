@@ -55,6 +55,12 @@ def fused_all_gather(world=None) -> bool:
     return world >= 4
 
 
+def overlap_tail() -> bool:
+    """Whether the reduction tail of a data-gradient GEMM is enqueued on a side stream so that it overlaps the
+    weight-gradient GEMM of the same layer (``NEOX_OVERLAP_AR_TAIL=0`` keeps everything on one stream)."""
+    return os.environ.get("NEOX_OVERLAP_AR_TAIL", "1") != "0"
+
+
 def _nccl_gather_rows(x2):
     ws = workspace()
     full = torch.empty(x2.shape[0] * ws.world, x2.shape[1], device=x2.device, dtype=x2.dtype)
@@ -87,6 +93,8 @@ class Workspace:
         self.bc_epoch = 0
         self.rs_epoch = 0
         self._gath_last = [0, 0]
+
+    side = None     # stream of deferred reduction tails
 
     def _buf(self, kind, parity, nbytes):
         b = self.bufs[kind][parity]
@@ -228,12 +236,17 @@ class Workspace:
         return out
 
     def gemm_reduce(self, a, b, b_mn, bias=None, residual=None, all_reduce=False, partial_bias=None,
-                    partial_add=None, gather=None):
+                    partial_add=None, gather=None, defer=False):
         """``reduce_over_ranks(a @ op(b) + partial_bias + partial_add) + bias + residual``: returns this rank's
         [M / world, N] row block (reduce-scatter) or the whole [M, N] result (``all_reduce``).  The ``partial_*``
         terms are added to this rank's product before the reduction (in the GEMM epilogue), ``bias`` / ``residual``
         once after it (``residual`` has the shape of the result).  ``gather``: a handle whose broadcast rides on this
-        GEMM as a prefetch for a later op (see ``gemm``)."""
+        GEMM as a prefetch for a later op (see ``gemm``).
+
+        ``defer``: the reduction tail (reduce the received partial tiles, hand the result to the peers) is enqueued
+        on a side stream and ``(out, join)`` is returned; work launched on the calling stream before ``join()`` --
+        the weight-gradient GEMM of the same layer -- then runs while the tail waits for the peers and moves data.
+        ``out`` must not be read before ``join()``."""
         M, K = a.shape
         N = b.shape[1] if b_mn else b.shape[0]
         rows = M // self.world
@@ -249,6 +262,20 @@ class Workspace:
         out = torch.empty(M if all_reduce else rows, N, device=a.device, dtype=torch.bfloat16)
         if residual is not None:
             assert residual.is_contiguous() and residual.dtype == torch.bfloat16
+        if defer:
+            main = torch.cuda.current_stream()
+            if self.side is None:
+                self.side = torch.cuda.Stream()
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self._reduce_tail(recv, gath, out, bias, residual, all_reduce, rows, M, N, e)
+            side = self.side
+            return out, lambda: torch.cuda.current_stream().wait_stream(side)
+        self._reduce_tail(recv, gath, out, bias, residual, all_reduce, rows, M, N, e)
+        return out
+
+    def _reduce_tail(self, recv, gath, out, bias, residual, all_reduce, rows, M, N, e):
+        L = native.lib()
         res_ptr = native.ptr(residual)
         if all_reduce and residual is not None:
             # the owner adds the residual rows it owns
@@ -267,7 +294,6 @@ class Workspace:
                                       self.rank, S.AR_DONE, self.pad.word(S.CTR_GCOPY),
                                       ctypes.c_void_p(native.stream_ptr()))
             native.check(rc, "neox_gathered_copy")
-        return out
 
 
 def workspace(group=None) -> Workspace:
@@ -370,12 +396,19 @@ class _ColumnSP(torch.autograd.Function):
                                                                         gather=h, bcast=not need_x, dep="b"))
                 ws.release(h)
         else:
+            join = None
             if need_x:
-                gx = ws.gemm_reduce(g2, weight, True).reshape(ctx.x_shape)
+                if overlap_tail() and need_w:
+                    gx, join = ws.gemm_reduce(g2, weight, True, defer=True)
+                    gx = gx.reshape(ctx.x_shape)
+                else:
+                    gx = ws.gemm_reduce(g2, weight, True).reshape(ctx.x_shape)
             if need_w:
                 full = _nccl_gather_rows(x2)
                 gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g2, full, a_mn=True, b_mn=True, out=out,
                                                                        add=add))
+            if join is not None:
+                join()
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
         return gx, gw, gb, None, None
@@ -507,10 +540,18 @@ class _ColumnAR(torch.autograd.Function):
             from ..ops.functional import dgelu_mul
             g2 = dgelu_mul(g2, pre)
         gx = gw = gb = None
+        join = None
         if ctx.needs_input_grad[0]:
-            gx = ws.gemm_reduce(g2, weight, True, all_reduce=True).reshape(ctx.x_shape)
+            # the all-reduce tail of the data gradient runs beside the weight-gradient GEMM
+            if overlap_tail() and ctx.needs_input_grad[1]:
+                gx, join = ws.gemm_reduce(g2, weight, True, all_reduce=True, defer=True)
+                gx = gx.reshape(ctx.x_shape)
+            else:
+                gx = ws.gemm_reduce(g2, weight, True, all_reduce=True).reshape(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             gw = _accumulate_wgrad(weight, lambda out, add: G.gemm(g2, x2, a_mn=True, b_mn=True, out=out, add=add))
+        if join is not None:
+            join()
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.sum(0)
         return gx, gw, gb, None, None

@@ -11,6 +11,9 @@ from test_training_cpu import _loss_decreases
     {"moe_num_experts": 4, "moe_top_k": 2, "expert_interval": 1, "moe_token_dropping": False, "gpt_j_residual": False},
     {"moe_num_experts": 4, "moe_top_k": 1, "expert_interval": 2, "moe_token_dropping": True,
      "moe_train_capacity_factor": 1.25, "gpt_j_residual": False},
+    # DeepSpeed-style MoE: a dense MLP beside the experts, mixed by a learned per-token coefficient
+    {"moe_num_experts": 4, "moe_top_k": 1, "expert_interval": 1, "moe_type": "deepspeed", "moe_use_residual": True,
+     "moe_token_dropping": True, "gpt_j_residual": False},
     {"attention_config": [[["rwkv"], "all"]], "num_attention_heads": 2, "hidden_size": 64, "pos_emb": "none"},
     {"attention_config": [[["mamba"], "all"]], "pos_emb": "none"},
     {"attention_config": [[["gmlp"], 1], [["amlp"], 1]], "pos_emb": "none", "gpt_j_residual": False},
@@ -76,3 +79,40 @@ def test_wkv6_reference_gradients_are_consistent():
     assert torch.allclose(gw, w.grad, atol=1e-9), (gw - w.grad).abs().max()
     assert torch.allclose(wkv6_ref(r.detach().float(), k.detach().float(), v.detach().float(), w.detach().float(),
                                    u.detach().float()).double(), y.detach(), atol=1e-4)
+
+
+def _moe_grouped_matches_loop(rank, world, cfg):
+    """The grouped data flow (router -> row plan -> dispatch -> grouped linears -> combine) against the per-expert
+    loop: same outputs, same gradients, with and without a capacity limit."""
+    import torch
+    from common import make_args
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.models.init_functions import get_init_methods
+    from gpt_neox_b200.models.moe import ParallelMoE
+    args = make_args(**{**cfg, "global_num_gpus": world})
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    init, out_init = get_init_methods(args)
+    moe = ParallelMoE(args, init, out_init, args.moe_num_experts).float()
+    x = torch.randn(args.seq_length, 3, args.hidden_size)
+    res = []
+    for grouped in (False, True):
+        moe.grouped = grouped
+        moe.zero_grad()
+        xi = x.clone().requires_grad_(True)
+        y, lbl = moe(xi)
+        (y.square().sum() + lbl).backward()
+        res.append((y.detach(), lbl.detach(), xi.grad, moe.w1.grad.clone(), moe.w2.grad.clone(),
+                    moe.router.layer.weight.grad.clone()))
+    for a, b in zip(*res):
+        torch.testing.assert_close(a, b, atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("cfg", [
+    {"moe_num_experts": 4, "moe_top_k": 2, "moe_token_dropping": False},
+    {"moe_num_experts": 8, "moe_top_k": 1, "moe_token_dropping": True, "moe_train_capacity_factor": 0.5,
+     "moe_min_capacity": 2},
+    {"moe_num_experts": 4, "moe_top_k": 2, "moe_token_dropping": False, "moe_glu": True, "activation": "swiglu"},
+])
+def test_moe_grouped_data_flow_matches_per_expert_loop(cfg):
+    run_distributed(_moe_grouped_matches_loop, 1, cfg)

@@ -751,3 +751,102 @@ def test_bias_dropout_add_kernel_matches_the_philox_mask(dtype):
     assert torch.equal(again, out.detach())
     other = OF.bias_dropout_add(x.detach(), bias.detach(), res.detach(), p, True)
     assert not torch.equal(other, out.detach())
+
+
+# ------------------------------------------------------------------ mixture-of-experts kernels
+@pytest.mark.parametrize("T,E,k,dtype", [(1000, 8, 2, torch.bfloat16), (513, 64, 1, torch.float32),
+                                         (300, 200, 4, torch.float16)])
+def test_moe_router_kernel_matches_eager(T, E, k, dtype):
+    from gpt_neox_b200.ops import moe_ops as MO
+    torch.manual_seed(0)
+    logits = (torch.randn(T, E, device=DEV) * 2).to(dtype)
+    a = logits.clone().requires_grad_(True)
+    b = logits.clone().requires_grad_(True)
+    probs, w, idx, counts = MO.router(a, k)
+    probs_r, w_r, idx_r, counts_r = MO.router_ref(b, k)
+    _close(probs, probs_r, 1e-6, rtol=1e-4)
+    _close(w, w_r, 1e-6, rtol=1e-4)
+    # ties between equal probabilities may be broken differently: compare the selected probabilities and the histogram
+    assert torch.equal(probs_r.gather(1, idx).sort(1).values, probs_r.gather(1, idx_r).sort(1).values)
+    same = (idx.sort(1).values == idx_r.sort(1).values).all()
+    if same:
+        assert torch.equal(counts, counts_r)
+    assert int(counts.sum()) == T * k
+    gw = torch.randn(T, k, device=DEV)
+    gp = torch.randn(T, E, device=DEV) * 0.1
+    (w * gw).sum().add((probs * gp).sum()).backward()
+    (w_r * gw).sum().add((probs_r * gp).sum()).backward()
+    if same:
+        _close(a.grad, b.grad, 2e-3 if dtype != torch.float32 else 1e-5, rtol=2e-2 if dtype != torch.float32 else 1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_moe_dispatch_and_combine_kernels(dtype):
+    from gpt_neox_b200.ops import moe_ops as MO
+    torch.manual_seed(1)
+    T, E, k, h = 700, 8, 2, 264
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)])
+    counts = torch.bincount(idx.reshape(-1), minlength=E)
+    for cap in (None, 100):
+        row_of, kept = MO.plan_rows(idx, counts, cap)
+        rows = MO.padded_rows(T * k, E)
+        # every kept assignment has its own row inside its expert's segment
+        flat = row_of.reshape(-1)
+        ok = flat >= 0
+        assert flat[ok].unique().numel() == int(ok.sum()) == int(kept.sum())
+        starts = torch.cumsum((kept + 63) // 64 * 64, 0) - (kept + 63) // 64 * 64
+        e_of = idx.reshape(-1)[ok]
+        assert bool(((flat[ok] >= starts[e_of]) & (flat[ok] < starts[e_of] + kept[e_of])).all())
+        x = torch.randn(T, h, device=DEV).to(dtype)
+        gate = torch.rand(T, k, device=DEV)
+        xa = x.clone().requires_grad_(True)
+        xb = x.clone().requires_grad_(True)
+        ga = gate.clone().requires_grad_(True)
+        gb = gate.clone().requires_grad_(True)
+        pa = MO.dispatch(xa, row_of, rows)
+        pb = MO.dispatch_ref(xb, row_of, rows)
+        assert torch.equal(pa, pb)
+        ya = MO.combine(pa * 1.0, row_of, ga)
+        yb = MO.combine_ref(pb * 1.0, row_of, gb)
+        _close(ya, yb, 1e-2)
+        gy = torch.randn_like(ya)
+        ya.backward(gy)
+        yb.backward(gy)
+        _close(xa.grad, xb.grad, 2e-2)
+        _close(ga.grad, gb.grad, 5e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("counts,N,K,act", [([300, 0, 129, 64, 1, 700, 5, 90], 512, 256, None),
+                                            ([37, 1000], 384, 192, "gelu"),
+                                            ([0, 0, 0, 256], 256, 64, "gelu")])
+def test_grouped_gemm_matches_per_expert_eager(counts, N, K, act):
+    from gpt_neox_b200.ops import moe_ops as MO
+    torch.manual_seed(2)
+    E = len(counts)
+    cnt = torch.tensor(counts, device=DEV)
+    rows = MO.padded_rows(sum(counts), E)
+    x = torch.zeros(rows, K, device=DEV, dtype=torch.bfloat16)
+    g = torch.zeros(rows, N, device=DEV, dtype=torch.bfloat16)
+    row = 0
+    for c in counts:
+        x[row:row + c] = torch.randn(c, K, device=DEV).to(torch.bfloat16)
+        g[row:row + c] = torch.randn(c, N, device=DEV).to(torch.bfloat16)
+        row += (c + 63) // 64 * 64
+    w = (torch.randn(E, N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    assert MO.grouped_kernel_ok(x, w)
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xb, wb = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    ya = MO.grouped_linear(xa, wa, cnt, act)
+    yb = MO.grouped_linear_ref(xb, wb, cnt, act)
+    assert native.read_status() == 0
+    _close(ya, yb, 3e-2, rtol=2e-2)
+    ya.backward(g)
+    yb.backward(g.float())
+    assert native.read_status() == 0
+    _close(xa.grad, xb.grad, 5e-2, rtol=3e-2)
+    _close(wa.grad, wb.grad, 0.25, rtol=3e-2)
+    # weight gradients accumulate into the optimizer's fp32 buffer when it is attached
+    wa2 = w.clone().requires_grad_(True)
+    wa2.main_grad = torch.ones(E, N, K, device=DEV)
+    MO.grouped_linear(x.clone().requires_grad_(True), wa2, cnt, act).backward(g)
+    _close(wa2.main_grad - 1.0, wb.grad, 0.25, rtol=3e-2)

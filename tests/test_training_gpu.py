@@ -22,3 +22,10 @@ def test_fp16_training_with_overflow_recovery():
     """fp16 parameters on the native kernels (GEMM, flash attention, norms), dynamic loss scale: the oversized initial
     scale overflows, those steps are skipped without touching the parameters, the scale drops and the loss falls."""
     _run("fp16_smoke_worker.py", "FP16_SMOKE_OK")
+
+
+@pytest.mark.gpu
+def test_moe_grouped_kernels_match_the_per_expert_loop_and_train():
+    """Fused router, dispatch, grouped tcgen05 GEMMs (forward, dgrad, wgrad) and combine against the per-expert loop
+    (dropless and with a capacity limit), then a small MoE model trains through them."""
+    _run("moe_grouped_worker.py", "MOE_GROUPED_OK")
