@@ -27,7 +27,9 @@ are data-parallel only over the expert-data-parallel group, live in their own bu
 """
 from __future__ import annotations
 
+import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -36,6 +38,43 @@ from ..parallel import mpu
 from .loss_scaler import DynamicLossScaler, StaticLossScaler
 
 _ALIGN = 128  # elements; keeps every shard boundary 256-byte aligned for bf16 and 512 for fp32
+
+
+# signal-pad slots of the peer-memory traffic (one block of 8 rank slots each) and the bound of its waits
+_READY, _DONE, _GATHERED = 0, 8, 16
+_WAIT_ROUNDS = 60      # x about two seconds
+
+
+def peer_traffic_enabled() -> bool:
+    """ZeRO-1 reduce-scatter / all-gather through peer memory instead of NCCL (``NEOX_ZERO_PEER=1``; one NVLink
+    domain, at most 8 data-parallel ranks)."""
+    return os.environ.get("NEOX_ZERO_PEER", "0") == "1"
+
+
+def _lib():
+    from ..ops import native
+    return native.lib()
+
+
+def _check(rc, what):
+    from ..ops import native
+    native.check(rc, what)
+
+
+def _cur_stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _StreamWork:
+    """``wait()`` makes the current stream wait for everything enqueued so far on ``stream`` (the handle of a
+    reduction that was launched as kernels rather than as an NCCL call)."""
+
+    def __init__(self, stream):
+        self.event = torch.cuda.Event()
+        self.event.record(stream)
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
 
 
 def _pad_to(n, m):
@@ -64,8 +103,26 @@ class Bucket:
         self.numel = off
         self.padded = _pad_to(max(off, 1), _ALIGN * max(comm_world, 1))
         self.offsets = offs
-        self.flat_param = torch.zeros(self.padded, dtype=model_dtype, device=device)
-        self.flat_grad = torch.zeros(self.padded, dtype=grad_dtype, device=device)
+        self.peer = (self.sharded and peer_traffic_enabled() and torch.device(device).type == "cuda"
+                     and comm_world <= 8 and grad_dtype == torch.float32
+                     and model_dtype in (torch.bfloat16, torch.float16, torch.float32))
+        if self.peer:
+            # both flat buffers in symmetric memory: the owner of a shard reads it from every rank's gradient
+            # buffer, and writes its updated shard into every rank's parameter buffer (csrc/comm_gemm_sm100.cu)
+            from ..parallel import symm_mem as S
+            esize = torch.empty((), dtype=model_dtype).element_size()
+            self._sym_p = S.SymmBuffer(self.padded * esize, comm_group)
+            self._sym_g = S.SymmBuffer(self.padded * 4, comm_group)
+            self._pad = S.SignalPad(comm_group)
+            self.flat_param = self._sym_p.tensor((self.padded,), model_dtype)
+            self.flat_grad = self._sym_g.tensor((self.padded,), torch.float32)
+            self._ctr = torch.zeros(4, dtype=torch.int32, device=device)
+            self._esize = esize
+            self.epoch = 0                  # one reduction (and at most one gather) per epoch
+            self._gather_epoch = 0          # epoch of a gather that has not been waited for yet
+        else:
+            self.flat_param = torch.zeros(self.padded, dtype=model_dtype, device=device)
+            self.flat_grad = torch.zeros(self.padded, dtype=grad_dtype, device=device)
         for p, o in zip(self.params, offs):
             view = self.flat_param[o:o + p.numel()].view(p.shape)
             view.copy_(p.data)
@@ -93,6 +150,9 @@ class Bucket:
     def reduce_grads(self, average_factor):
         """Sum gradients over the communication group (and divide by ``average_factor``)."""
         if self.world > 1:
+            if self.peer:
+                self._peer_reduce(1.0 / average_factor)
+                return
             if average_factor != 1.0:
                 self.flat_grad.div_(average_factor)
             if self.sharded:
@@ -112,7 +172,10 @@ class Bucket:
             from contextlib import nullcontext
             ctx = nullcontext()
         with ctx:
-            if self.sharded:
+            if self.peer:
+                self._peer_reduce(1.0)
+                self.pending_reduce = _StreamWork(stream)
+            elif self.sharded:
                 dst = self.flat_grad[self.lo:self.hi]
                 if not dst.is_cuda:
                     self._rs_tmp = torch.empty_like(dst)
@@ -143,11 +206,23 @@ class Bucket:
             self.gather_params()
             return
         stream.wait_stream(torch.cuda.current_stream())
+        if self.peer:
+            with torch.cuda.stream(stream):
+                self._peer_push()
+            return
         with torch.cuda.stream(stream):
             self.pending_gather = dist.all_gather_into_tensor(self.flat_param, self.flat_param[self.lo:self.hi],
                                                               group=self.comm_group, async_op=True)
 
     def wait_params(self):
+        if self.peer:
+            if self._gather_epoch:
+                # the peers' shards of that epoch have landed in this rank's parameter buffer
+                rc = _lib().neox_wait_flags_long(self._pad.word(_GATHERED), ctypes.c_uint(self._gather_epoch),
+                                                 self.world, self.rank, _WAIT_ROUNDS, _cur_stream())
+                _check(rc, "neox_wait_flags_long")
+                self._gather_epoch = 0
+            return
         if self.pending_gather is not None:
             self.pending_gather.wait()
             self.pending_gather = None
@@ -175,13 +250,48 @@ class Bucket:
         return total
 
     def gather_params(self):
+        if self.peer:
+            self._peer_push()
+            self.wait_params()
+            return
         if self.sharded:
             src = self.flat_param[self.lo:self.hi]
             if not src.is_cuda:
                 src = src.clone()      # gloo does not define the aliased (in-place) form
             dist.all_gather_into_tensor(self.flat_param, src, group=self.comm_group)
 
+    # ---- peer-memory forms (launched on the current stream)
+    def _peer_reduce(self, scale):
+        """This rank's shard <- scale * sum over ranks (rank order, fp32), read from the peers' gradient buffers."""
+        L = _lib()
+        self.epoch += 1
+        e = ctypes.c_uint(self.epoch)
+        st = _cur_stream()
+        # "my gradients of this bucket are final" to every rank, then wait for everybody else's
+        _check(L.neox_symm_release(None, 0, self._pad.c_ptrs, self.world, self.rank, _READY, e, st), "neox_symm_release")
+        _check(L.neox_wait_flags_long(self._pad.word(_READY), e, self.world, self.rank, _WAIT_ROUNDS, st),
+               "neox_wait_flags_long")
+        rc = L.neox_zero_reduce_scatter(self._sym_g.c_ptrs, ctypes.c_ulonglong(self.lo),
+                                        ctypes.c_ulonglong(self.hi - self.lo), ctypes.c_float(scale),
+                                        self._pad.word(_READY), e, self._pad.c_ptrs, self.world, self.rank, _DONE,
+                                        ctypes.c_void_p(self._ctr.data_ptr()), st)
+        _check(rc, "neox_zero_reduce_scatter")
+
+    def _peer_push(self):
+        """Write this rank's updated parameter shard into every rank's parameter buffer."""
+        rc = _lib().neox_zero_param_push(self._sym_p.c_ptrs, ctypes.c_ulonglong(self.lo * self._esize),
+                                         ctypes.c_ulonglong((self.hi - self.lo) * self._esize), self._pad.c_ptrs,
+                                         self.world, self.rank, _GATHERED, ctypes.c_uint(self.epoch),
+                                         ctypes.c_void_p(self._ctr.data_ptr() + 4), _cur_stream())
+        _check(rc, "neox_zero_param_push")
+        self._gather_epoch = self.epoch
+
     def zero_grad(self):
+        if self.peer and self.epoch:
+            # every rank has finished reading this rank's gradients of the last reduction
+            rc = _lib().neox_wait_flags_long(self._pad.word(_DONE), ctypes.c_uint(self.epoch), self.world, self.rank,
+                                             _WAIT_ROUNDS, _cur_stream())
+            _check(rc, "neox_wait_flags_long")
         self.flat_grad.zero_()
         for p in self.params:
             p.grad = None
@@ -302,7 +412,7 @@ class FlatMixedPrecisionOptimizer:
     def _on_grad_ready(self, bucket, param):
         """A parameter may report more than once per backward (a weight with several uses): readiness is counted
         per distinct parameter, and a bucket holding a gradient that is still rewritten after backward never fires."""
-        if not self._armed or bucket.world <= 1 or bucket.never_early:
+        if not self._armed or bucket.world <= 1 or bucket.never_early or self._local_grads():
             return
         bucket.ready.add(id(param))
         if len(bucket.ready) == bucket.n_expected:
@@ -343,7 +453,12 @@ class FlatMixedPrecisionOptimizer:
             b.zero_grad()
 
     # ------------------------------------------------------------------ the step
-    def global_grad_norm(self):
+    def _local_grads(self) -> bool:
+        """The inner optimizer communicates by itself (1-bit Adam after its warm-up: compressed momentum instead of
+        gradients), so the data-parallel gradient reduction is skipped and every rank steps on its local gradients."""
+        return bool(getattr(self.optimizer, "compression_active", False)) and self.dp_world > 1
+
+    def global_grad_norm(self, local_grads=False):
         tp_rank = mpu.get_model_parallel_rank()
         dev = self.buckets[0].flat_grad.device if self.buckets else torch.device("cpu")
         total = torch.zeros((), dtype=torch.float32, device=dev)
@@ -364,6 +479,11 @@ class FlatMixedPrecisionOptimizer:
                 # expert-data-parallel group -> DP sum divided by that replication
                 across_dp = across_dp + sq / float(max(b.world, 1))
                 need_dp = True
+            elif local_grads:
+                # unreduced gradients differ per rank: use the root-mean-square over the ranks, so that clipping
+                # and overflow decisions are the same everywhere
+                across_dp = across_dp + sq / float(max(self.dp_world, 1))
+                need_dp = True
             else:
                 total = total + sq      # replicated over DP: every rank already holds the full sum
         if dist.is_available() and dist.is_initialized():
@@ -380,9 +500,15 @@ class FlatMixedPrecisionOptimizer:
         """Reduce, check, clip, update, gather.  ``grad_divisor``: value the summed gradients must be
         divided by in total (micro-batches x data-parallel size)."""
         self._armed = False
-        for b in self.buckets:
-            self.overlapped_reductions += int(b.finish_reduce())
-        norm_t = self.global_grad_norm()
+        local = self._local_grads()
+        if local:
+            assert self.zero_stage == 0, "compressed-communication optimizers need every rank to hold the whole " \
+                                         "parameter: use zero_optimization.stage 0"
+            grad_divisor = grad_divisor / self.dp_world     # the momentum average supplies the 1 / world
+        else:
+            for b in self.buckets:
+                self.overlapped_reductions += int(b.finish_reduce())
+        norm_t = self.global_grad_norm(local_grads=local)
         scale = self.loss_scaler.cur_scale * grad_divisor
         norm = float(norm_t) / scale
         self._global_grad_norm = norm

@@ -1145,11 +1145,150 @@ __global__ void wait_flags_kernel(const uint32_t* flags, uint32_t epoch, int wor
 }
 }  // namespace
 
+// The same with a limit of `rounds` spin periods (about two seconds each): for waits on ranks that are only loosely
+// coupled to this one (data-parallel peers, which may be a host hiccup behind), in a one-warp kernel of their own so
+// that nothing else is held up while it spins.
+namespace {
+__global__ void wait_flags_long_kernel(const uint32_t* flags, uint32_t epoch, int world, int rank, int rounds,
+                                       int* status) {
+    for (int r = threadIdx.x; r < world; r += blockDim.x) {
+        if (r == rank) continue;
+        bool ok = false;
+        for (int i = 0; i < rounds && !ok; ++i) ok = wait_flag(flags + r, epoch);
+        if (!ok) atomicExch(status, 580 + r);
+    }
+}
+}  // namespace
+
+extern "C" int neox_wait_flags_long(const void* flags, unsigned epoch, int world, int rank, int rounds, void* stream) {
+    if (world > MAX_RANKS || world < 1 || rounds < 1 || rounds > 600) return NEOX_ERR_TOO_LARGE;
+    int* status = neox_status_word();
+    if (!status) return NEOX_ERR_DRIVER;
+    wait_flags_long_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(flags), epoch,
+                                                                             world, rank, rounds, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
 extern "C" int neox_wait_flags(const void* flags, unsigned epoch, int world, int rank, void* stream) {
     if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
     int* status = neox_status_word();
     if (!status) return NEOX_ERR_DRIVER;
     wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(flags), epoch, world,
                                                                         rank, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+// ------------------------------------------------------------------ ZeRO-1 gradient / parameter traffic over peer memory
+// The flat fp32 gradient buffer and the flat 16-bit parameter buffer of a bucket live in symmetric memory.
+//   reduce-scatter: every rank announces "my gradients of this bucket are final" (neox_symm_release with n = 0 on the
+//     READY slot); the owner of a shard then READS that shard from every rank's buffer over NVLink, adds the copies
+//     in rank order in fp32 (bit-identical on every run), scales, and writes its own copy -- one pass, no staging
+//     buffer, the only NVLink traffic is the (world - 1) / world of the bucket that NCCL's ring also moves.  When
+//     done it tells every rank (DONE slot) that their buffers may be rewritten.
+//   all-gather: after the optimizer step the owner WRITES its updated 16-bit shard into every rank's parameter buffer
+//     and raises the GATHERED slot; consumers put neox_wait_flags in front of the first kernel that reads the bucket.
+// Reference counterpart: DeepSpeed ZeRO stage 1's NCCL reduce-scatter / all-gather of flattened buckets
+// (driven from megatron/training.py of the reference through deepspeed.initialize).
+namespace {
+
+struct PeerF32 {
+    const float* p[MAX_RANKS];
+};
+struct PeerVec {
+    uint4* p[MAX_RANKS];
+};
+
+__global__ void __launch_bounds__(256) zero_reduce_scatter_kernel(PeerF32 src, float* __restrict__ out, size_t lo,
+                                                                  size_t nvec, float scale,
+                                                                  const uint32_t* ready_flags, uint32_t epoch,
+                                                                  PeerPads pads, int world, int rank, int done_offset,
+                                                                  unsigned* counter, int* status) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        for (int r = 0; r < world && ok; ++r)
+            if (r != rank && !wait_flag(ready_flags + r, epoch)) {
+                atomicExch(status, 600 + r);
+                ok = 0;
+            }
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;      // nothing reduced, DONE never raised: the peers' bounded waits report it too
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < world; ++r) {
+            const float4 v = reinterpret_cast<const float4*>(src.p[r] + lo)[i];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+        reinterpret_cast<float4*>(out + lo)[i] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) grid_done_signal(counter, pads.p, world, rank, done_offset, epoch);
+}
+
+__global__ void __launch_bounds__(256) zero_param_push_kernel(const uint4* __restrict__ src, PeerVec dst, size_t nvec,
+                                                              PeerPads pads, int world, int rank, int sig_offset,
+                                                              uint32_t epoch, unsigned* counter) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = src[i];
+        for (int d = 1; d < world; ++d) {
+            int r = rank + d;
+            if (r >= world) r -= world;
+            dst.p[r][i] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) grid_done_signal(counter, pads.p, world, rank, sig_offset, epoch);
+}
+
+}  // namespace
+
+// grad_ptrs[r]: rank r's flat fp32 gradient buffer (peer-mapped); this rank's shard is elements [lo, lo + n),
+// lo and n multiples of 4.  ready_flags: local pad slots [ready_offset ...]; counter: a zero-initialised local word.
+extern "C" int neox_zero_reduce_scatter(const unsigned long long* grad_ptrs, unsigned long long lo, unsigned long long n,
+                                        float scale, const void* ready_flags, unsigned epoch,
+                                        const unsigned long long* pad_ptrs, int world, int rank, int done_offset,
+                                        void* counter, void* stream) {
+    if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
+    if ((lo % 4) || (n % 4)) return NEOX_ERR_ALIGN;
+    if (n == 0) return 0;
+    int* status = neox_status_word();
+    if (!status) return NEOX_ERR_DRIVER;
+    PeerF32 src;
+    PeerPads pads;
+    memset(&src, 0, sizeof(src));
+    memset(&pads, 0, sizeof(pads));
+    for (int i = 0; i < world; ++i) {
+        src.p[i] = reinterpret_cast<const float*>(grad_ptrs[i]);
+        pads.p[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
+    }
+    const size_t nvec = n / 4;
+    zero_reduce_scatter_kernel<<<copy_grid(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        src, reinterpret_cast<float*>(grad_ptrs[rank]), lo, nvec, scale, static_cast<const uint32_t*>(ready_flags),
+        epoch, pads, world, rank, done_offset, static_cast<unsigned*>(counter), status);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+}
+
+// param_ptrs[r]: rank r's flat parameter buffer (peer-mapped); copies `bytes` (a multiple of 16) starting at byte
+// offset `byte_lo` of this rank's buffer to the same offset of every other rank's, then raises slot sig_offset.
+extern "C" int neox_zero_param_push(const unsigned long long* param_ptrs, unsigned long long byte_lo,
+                                    unsigned long long bytes, const unsigned long long* pad_ptrs, int world, int rank,
+                                    int sig_offset, unsigned epoch, void* counter, void* stream) {
+    if (world > MAX_RANKS || world < 1) return NEOX_ERR_TOO_LARGE;
+    if ((byte_lo % 16) || (bytes % 16)) return NEOX_ERR_ALIGN;
+    PeerVec dst;
+    PeerPads pads;
+    memset(&dst, 0, sizeof(dst));
+    memset(&pads, 0, sizeof(pads));
+    for (int i = 0; i < world; ++i) {
+        dst.p[i] = reinterpret_cast<uint4*>(param_ptrs[i] + byte_lo);
+        pads.p[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
+    }
+    const size_t nvec = bytes / 16;
+    zero_param_push_kernel<<<copy_grid(nvec > 0 ? nvec : 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(param_ptrs[rank] + byte_lo), dst, nvec, pads, world, rank, sig_offset, epoch,
+        static_cast<unsigned*>(counter));
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }

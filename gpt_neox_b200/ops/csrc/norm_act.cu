@@ -650,6 +650,48 @@ int launch_ew(const void* a, const void* b, const void* bias, void* out, long lo
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
+
+// ------------------------------------------------------------------ column sums (bias gradients)
+// partial[blockIdx.y][c] = sum over this CTA's rows of g[r][c]; a CTA is 32 column lanes (8 columns each) x 8 row
+// lanes.  The second pass adds the partial rows in a fixed order (bit-reproducible) and stores or accumulates.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ g, float* __restrict__ partial,
+                                                             long long rows, int cols, long long ld) {
+    __shared__ float sh[8][256];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int col0 = blockIdx.x * 256 + tx * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (col0 < cols) {
+        for (long long r = (long long)blockIdx.y * 8 + ty; r < rows; r += (long long)gridDim.y * 8) {
+            float v[8];
+            Vec8<T>::load(g + r * ld + col0, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += v[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sh[ty][tx * 8 + i] = acc[i];
+    __syncthreads();
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t += sh[j][threadIdx.x];
+        partial[(size_t)blockIdx.y * cols + c] = t;
+    }
+}
+
+template <typename OUT>
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, OUT* __restrict__ out,
+                                                           int nblk, int cols, int accumulate) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float a = 0.f;
+    for (int r = 0; r < nblk; ++r) a += partial[(size_t)r * cols + c];
+    if (accumulate) a += (float)out[c];
+    out[c] = (OUT)a;
+}
+
 }  // namespace
 
 extern "C" {
@@ -657,6 +699,31 @@ extern "C" {
 int neox_norm_bwd_blocks(int rows) {
     const int cap = neox_sm_count() * 2;
     return rows < cap ? (rows > 0 ? rows : 1) : cap;
+}
+
+// out[c] (+)= sum_r g[r, c] for a [rows, cols] 16-bit matrix with row pitch ld (cols % 8 == 0, ld % 8 == 0);
+// dtype of g: 0 bf16, 2 fp16; out_dtype: 1 fp32 (may accumulate), else the type of g (store only).
+// ws: at least neox_colsum_blocks(rows) * cols floats of scratch.
+int neox_colsum_blocks(long long rows) {
+    long long b = (rows + 63) / 64;
+    const long long cap = 64;
+    return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+int neox_colsum(const void* g, void* out, float* ws, long long rows, int cols, long long ld, int dtype, int out_dtype,
+                int accumulate, void* stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if ((cols % 8) || (ld % 8) || (dtype != 0 && dtype != 2)) return NEOX_ERR_SHAPE;
+    if (accumulate && out_dtype != 1) return NEOX_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nblk = neox_colsum_blocks(rows);
+    dim3 grid((cols + 255) / 256, nblk);
+    if (dtype == 0) colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)g, ws, rows, cols, ld);
+    else colsum_partial_kernel<__half><<<grid, 256, 0, st>>>((const __half*)g, ws, rows, cols, ld);
+    const int fg = (cols + 255) / 256;
+    if (out_dtype == 1) colsum_final_kernel<float><<<fg, 256, 0, st>>>(ws, (float*)out, nblk, cols, accumulate);
+    else if (dtype == 0) colsum_final_kernel<__nv_bfloat16><<<fg, 256, 0, st>>>(ws, (__nv_bfloat16*)out, nblk, cols, 0);
+    else colsum_final_kernel<__half><<<fg, 256, 0, st>>>(ws, (__half*)out, nblk, cols, 0);
+    return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 
 int neox_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,

@@ -47,6 +47,23 @@ def workspace(nbytes: int, device, tag="ws") -> torch.Tensor:
     return buf
 
 
+def _param_grad(param, g32):
+    """Hand an fp32 parameter gradient to the optimizer: added to ``param.main_grad`` (the flat fp32 gradient buffer)
+    when it exists -- no round trip through the 16-bit ``.grad`` and its accumulate hook -- else returned in the
+    parameter's type."""
+    if param is None:
+        return None
+    mg = getattr(param, "main_grad", None)
+    if mg is not None and mg.dtype == torch.float32 and mg.shape == g32.shape:
+        mg.add_(g32)
+        param.grad_in_main = True
+        ready = getattr(param, "_grad_ready", None)
+        if ready is not None:
+            ready()
+        return None
+    return g32.to(param.dtype)
+
+
 # ------------------------------------------------------------------------------------ LayerNorm
 def layer_norm_ref(x, weight, bias, eps):
     xf = x.float()
@@ -77,6 +94,7 @@ class _LayerNormFn(torch.autograd.Function):
         native.check(rc, "neox_layernorm_fwd")
         ctx.save_for_backward(x2, weight, mean, rstd)
         ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
         ctx.shape = x.shape
         return y.reshape(x.shape)
 
@@ -96,8 +114,8 @@ class _LayerNormFn(torch.autograd.Function):
                                              native.ptr(rstd), native.ptr(dx), native.ptr(dgamma), native.ptr(dbeta),
                                              native.ptr(ws), rows, cols, _DT[x2.dtype], _s())
         native.check(rc, "neox_layernorm_bwd")
-        return (dx.reshape(ctx.shape), dgamma.to(weight.dtype), dbeta.to(weight.dtype) if ctx.has_bias else None,
-                None)
+        return (dx.reshape(ctx.shape), _param_grad(weight, dgamma) if ctx.needs_input_grad[1] else None,
+                _param_grad(ctx.bias_ref, dbeta) if ctx.has_bias and ctx.needs_input_grad[2] else None, None)
 
 
 def layer_norm(x, weight, bias, eps=1e-5):
@@ -133,6 +151,7 @@ class _RMSNormFn(torch.autograd.Function):
         native.check(rc, "neox_rmsnorm_fwd")
         ctx.save_for_backward(x2, scale, rinv)
         ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
         ctx.eps = eps
         ctx.shape = x.shape
         return y.reshape(x.shape)
@@ -153,7 +172,8 @@ class _RMSNormFn(torch.autograd.Function):
                                            native.ptr(dx), native.ptr(dscale), native.ptr(dbias), native.ptr(ws),
                                            rows, cols, ctypes.c_float(ctx.eps), _DT[x2.dtype], _s())
         native.check(rc, "neox_rmsnorm_bwd")
-        return dx.reshape(ctx.shape), dscale.to(scale.dtype), dbias.to(scale.dtype) if ctx.has_bias else None, None
+        return (dx.reshape(ctx.shape), _param_grad(scale, dscale) if ctx.needs_input_grad[1] else None,
+                _param_grad(ctx.bias_ref, dbias) if ctx.has_bias and ctx.needs_input_grad[2] else None, None)
 
 
 def rms_norm(x, scale, bias=None, eps=1e-8):
@@ -370,6 +390,35 @@ class _BiasDropoutAdd(torch.autograd.Function):
         gb = dx.reshape(-1, cols).sum(0) if has_bias and ctx.needs_input_grad[1] else None
         return dx, gb, g, None
 
+
+
+# ------------------------------------------------------------------------------------ bias gradient
+def bias_grad(g2, bias=None):
+    """Column sums of ``g2`` ([rows, cols]): the gradient of a bias added to every row.  On a GPU one two-pass kernel
+    (fixed summation order) that accumulates straight into ``bias.main_grad`` when the optimizer provides that fp32
+    buffer -- then ``None`` is returned and the parameter is reported ready, as the weight-gradient GEMMs do."""
+    cols = g2.shape[-1]
+    if (_k(g2) and g2.dtype in (torch.bfloat16, torch.float16) and g2.dim() == 2 and g2.stride(1) == 1
+            and cols % 8 == 0 and g2.stride(0) % 8 == 0 and g2.data_ptr() % 16 == 0):
+        L = native.lib()
+        rows = g2.shape[0]
+        nblk = L.neox_colsum_blocks(ctypes.c_longlong(rows))
+        ws = workspace(nblk * cols * 4, g2.device, "colsum")
+        mg = getattr(bias, "main_grad", None) if bias is not None else None
+        into_main = mg is not None and mg.dtype == torch.float32 and mg.is_contiguous()
+        out = mg if into_main else torch.empty(cols, dtype=g2.dtype, device=g2.device)
+        rc = L.neox_colsum(native.ptr(g2), native.ptr(out), native.ptr(ws), ctypes.c_longlong(rows), cols,
+                           ctypes.c_longlong(g2.stride(0)), _DT[g2.dtype], 1 if into_main else _DT[g2.dtype],
+                           int(into_main), _s())
+        native.check(rc, "neox_colsum")
+        if into_main:
+            bias.grad_in_main = True
+            ready = getattr(bias, "_grad_ready", None)
+            if ready is not None:
+                ready()
+            return None
+        return out
+    return g2.sum(0)
 
 # ------------------------------------------------------------------------------------ softmax
 def scaled_masked_softmax_ref(x, mask, scale, fill=-10000.0):

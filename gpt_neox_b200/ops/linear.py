@@ -107,6 +107,7 @@ class _LinearFn(torch.autograd.Function):
             if res2 is not None:
                 out = out + res2
         ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
         ctx.has_res = residual is not None
         ctx.has_aux = dgelu_aux is not None
         aux2 = dgelu_aux.reshape(-1, K) if dgelu_aux is not None else None
@@ -161,7 +162,8 @@ class _LinearFn(torch.autograd.Function):
                     gw = None
                     notify_grad_ready(weight)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = g2.sum(0)
+            from .functional import bias_grad
+            gb = bias_grad(g2, ctx.bias_ref)
         return gx, gw, gb, g_res, None, None, None
 
 

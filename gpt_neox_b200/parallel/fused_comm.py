@@ -30,6 +30,7 @@ import os
 import torch
 import torch.distributed as dist
 
+from ..ops import functional as OF
 from ..ops import gemm as G
 from ..ops import native
 from . import comms_logger, mpu
@@ -364,6 +365,7 @@ class _ColumnSP(torch.autograd.Function):
             r = G.gemm(_nccl_gather_rows(x2), weight, bias=bias, act=act_id, want_preact=need_pre)
         out, pre = r if need_pre else (r, None)
         ctx.act, ctx.rows, ctx.x_shape, ctx.has_bias = act, rows, x.shape, bias is not None
+        ctx.bias_ref = bias
         ctx.save_for_backward(x2, weight, None if split_pre else pre)
         out = out.reshape(x.shape[0] * ws.world, *x.shape[1:-1], N)
         if split_pre:
@@ -410,7 +412,7 @@ class _ColumnSP(torch.autograd.Function):
             if join is not None:
                 join()
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = g2.sum(0)
+            gb = OF.bias_grad(g2, ctx.bias_ref)
         return gx, gw, gb, None, None
 
 
@@ -443,6 +445,7 @@ class _Row(torch.autograd.Function):
                                  all_reduce=not sp, partial_bias=bias if bias_partial else None, partial_add=add2)
         ctx.x_shape, ctx.sp, ctx.bias_partial = x.shape, sp, bias_partial
         ctx.has_bias, ctx.has_res, ctx.has_add = bias is not None, residual is not None, partial_add is not None
+        ctx.bias_ref = bias
         ctx.add_shape = partial_add.shape if partial_add is not None else None
         ctx.save_for_backward(x2, weight, dgelu_aux.reshape(-1, K) if dgelu_aux is not None else None)
         lead = x.shape[0] // ws.world if sp else x.shape[0]
@@ -502,7 +505,7 @@ class _Row(torch.autograd.Function):
             g_add = g_full.reshape(ctx.add_shape)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             # post-reduction bias under SP: partial over this rank's shard, summed with the other replicated grads
-            gb = (g_full if (ctx.bias_partial or not ctx.sp) else g2).sum(0)
+            gb = OF.bias_grad(g_full if (ctx.bias_partial or not ctx.sp) else g2, ctx.bias_ref)
         return gx, gw, gb, (g if ctx.has_res else None), g_add, None, None, None
 
 
@@ -519,6 +522,7 @@ class _ColumnAR(torch.autograd.Function):
         r = G.gemm(x2, weight, bias=bias, act=G.ACT_GELU if act == "gelu" else G.ACT_NONE, want_preact=need_pre)
         out, pre = r if need_pre else (r, None)
         ctx.act, ctx.x_shape, ctx.has_bias, ctx.split_pre = act, x.shape, bias is not None, split_pre
+        ctx.bias_ref = bias
         ctx.save_for_backward(x2, weight, None if split_pre else pre)
         out = out.reshape(*x.shape[:-1], N)
         if split_pre:
@@ -553,7 +557,7 @@ class _ColumnAR(torch.autograd.Function):
         if join is not None:
             join()
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = g2.sum(0)
+            gb = OF.bias_grad(g2, ctx.bias_ref)
         return gx, gw, gb, None, None
 
 

@@ -88,7 +88,8 @@ class SymmBuffer:
     def tensor(self, shape, dtype=torch.bfloat16, byte_offset=0, rank=None):
         """A torch view of (part of) one copy; for tests and debugging (the kernels take raw pointers)."""
         ptr = self.ptrs[self.rank if rank is None else rank] + byte_offset
-        typestr = {torch.bfloat16: "<u2", torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1"}[dtype]
+        typestr = {torch.bfloat16: "<u2", torch.float16: "<f2", torch.float32: "<f4", torch.int32: "<i4",
+                   torch.uint8: "|u1"}[dtype]
 
         class _Iface:
             __cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}

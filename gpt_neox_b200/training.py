@@ -311,7 +311,8 @@ def _inner_optimizer(neox_args):
             return CPUAdam, dict(weight_decay=neox_args.weight_decay, **params)
         if name == "onebitadam":
             from .optim.onebit_adam import OneBitAdam
-            return OneBitAdam, dict(weight_decay=neox_args.weight_decay, **params)
+            return OneBitAdam, dict(weight_decay=neox_args.weight_decay, comm_group=mpu.get_data_parallel_group(),
+                                    **params)
         params.pop("cuda_aware", None)
         params.pop("momentum", None)
         if neox_args.use_bnb_optimizer:

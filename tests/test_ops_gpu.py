@@ -766,18 +766,20 @@ def test_moe_router_kernel_matches_eager(T, E, k, dtype):
     probs_r, w_r, idx_r, counts_r = MO.router_ref(b, k)
     _close(probs, probs_r, 1e-6, rtol=1e-4)
     _close(w, w_r, 1e-6, rtol=1e-4)
-    # ties between equal probabilities may be broken differently: compare the selected probabilities and the histogram
+    # ties between equal probabilities (frequent with 16-bit logits) may be broken differently: the selected
+    # probabilities always agree; indices, histogram and gradients are compared on the rows without a tie
     assert torch.equal(probs_r.gather(1, idx).sort(1).values, probs_r.gather(1, idx_r).sort(1).values)
-    same = (idx.sort(1).values == idx_r.sort(1).values).all()
-    if same:
+    rows = (idx == idx_r).all(1)
+    assert rows.float().mean().item() > 0.9
+    if bool(rows.all()):
         assert torch.equal(counts, counts_r)
     assert int(counts.sum()) == T * k
     gw = torch.randn(T, k, device=DEV)
     gp = torch.randn(T, E, device=DEV) * 0.1
     (w * gw).sum().add((probs * gp).sum()).backward()
     (w_r * gw).sum().add((probs_r * gp).sum()).backward()
-    if same:
-        _close(a.grad, b.grad, 2e-3 if dtype != torch.float32 else 1e-5, rtol=2e-2 if dtype != torch.float32 else 1e-3)
+    lo = dtype != torch.float32
+    _close(a.grad[rows], b.grad[rows], 4e-3 if lo else 1e-5, rtol=2e-2 if lo else 1e-3)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -850,3 +852,23 @@ def test_grouped_gemm_matches_per_expert_eager(counts, N, K, act):
     wa2.main_grad = torch.ones(E, N, K, device=DEV)
     MO.grouped_linear(x.clone().requires_grad_(True), wa2, cnt, act).backward(g)
     _close(wa2.main_grad - 1.0, wb.grad, 0.25, rtol=3e-2)
+
+
+@pytest.mark.parametrize("rows,cols,dtype", [(4096, 6144, torch.bfloat16), (1000, 264, torch.float16), (7, 8, torch.bfloat16)])
+def test_bias_grad_column_sum_kernel(rows, cols, dtype):
+    torch.manual_seed(3)
+    g = torch.randn(rows, cols, device=DEV).to(dtype)
+    ref = g.float().sum(0)
+    out = OF.bias_grad(g)
+    assert out.dtype == dtype
+    _close(out, ref, 0.05 * math.sqrt(rows) / 8, rtol=1e-2)
+    # with the optimizer's fp32 buffer attached the sum is accumulated there and the parameter is reported ready
+    bias = torch.nn.Parameter(torch.zeros(cols, device=DEV, dtype=dtype))
+    bias.main_grad = torch.full((cols,), 2.0, device=DEV)
+    seen = []
+    bias._grad_ready = lambda: seen.append(1)
+    assert OF.bias_grad(g, bias) is None and seen == [1] and bias.grad_in_main
+    _close(bias.main_grad - 2.0, ref, 1e-3 * math.sqrt(rows), rtol=1e-5)
+    # a strided view (the rows of a wider matrix)
+    wide = torch.randn(rows, cols * 2, device=DEV).to(dtype)
+    _close(OF.bias_grad(wide[:, :cols]), wide[:, :cols].float().sum(0), 0.05 * math.sqrt(rows) / 8, rtol=1e-2)

@@ -227,3 +227,67 @@ def test_keep_last_n_checkpoints(tmp_path):
         os.makedirs(tmp_path / f"global_step{i}")
     delete_old_checkpoints(str(tmp_path), 2)
     assert sorted(os.listdir(tmp_path)) == ["global_step10", "global_step20"]
+
+
+# ------------------------------------------------------------------ 1-bit Adam: compressed momentum communication
+def _onebit_collective(rank, world):
+    import torch.distributed as dist
+    from gpt_neox_b200.optim.onebit_adam import compressed_allreduce, pack_signs, unpack_signs
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x = torch.randn(64)
+    assert torch.equal(unpack_signs(pack_signs(x)), torch.where(x >= 0, 1.0, -1.0))
+    n = 8 * world * 50
+    g = torch.Generator().manual_seed(11 + rank)
+    werr, serr = torch.zeros(n), torch.zeros(n // world)
+    sum_out, sum_true = torch.zeros(n), torch.zeros(n)
+    for step in range(40):
+        local = torch.randn(n, generator=g) + 0.3            # a common drift plus rank-specific noise
+        true = local.clone()
+        dist.all_reduce(true)
+        true /= world
+        out = compressed_allreduce(local.clone(), werr, serr)
+        ref = out.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(out, ref)                          # every rank reconstructs the same tensor
+        sum_out += out
+        sum_true += true
+    # error feedback: what one step loses is re-sent later, so the running sums stay within a few quantisation steps
+    drift = (sum_out - sum_true).abs().max().item()
+    assert drift < 6.0, drift
+    assert (sum_out - sum_true).abs().mean().item() < 0.05 * sum_true.abs().mean().item() + 1.5
+
+
+def test_onebit_compressed_allreduce_error_feedback():
+    run_distributed(_onebit_collective, 2)
+
+
+def _onebit_training(rank, world):
+    import torch.distributed as dist
+    from gpt_neox_b200.parallel import comms_logger
+    cfg = {"optimizer": {"type": "OneBitAdam", "params": {"lr": 2e-3, "betas": [0.9, 0.95], "eps": 1e-8,
+                                                          "freeze_step": 4}},
+           "zero_optimization": {"stage": 0}, "global_num_gpus": world, "train_iters": 20, "lr_decay_iters": 20}
+    args, model, opt, sched = _setup(cfg)
+    log = comms_logger.configure({"enabled": True})
+    grad_bytes = {b.flat_grad.numel() * 4 for b in opt.buckets}
+    it = _fixed_batches(args)
+    from gpt_neox_b200.training import train_step
+    from gpt_neox_b200.utils import Timers
+    losses, grad_reductions = [], []
+    for _ in range(14):
+        d, _ = train_step(args, Timers(), it, model, opt, sched)
+        losses.append(float(d["lm_loss"]))
+        grad_reductions.append(sum(c for (op, nbytes, c, *_r) in log.summary() if op == "all_reduce" and nbytes in grad_bytes))
+    log.uninstall()
+    comms_logger.configure(None)
+    # warm-up steps all-reduce the gradients; afterwards only sign bits and scales travel
+    assert grad_reductions[3] > grad_reductions[0] and grad_reductions[-1] == grad_reductions[3], grad_reductions
+    assert min(losses[6:]) < losses[0], losses
+    for p in model.module.parameters():
+        ref = p.detach().clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(ref, p.detach())                   # the ranks never drift apart
+
+
+def test_onebit_adam_trains_with_compressed_momentum():
+    run_distributed(_onebit_training, 2)

@@ -2,7 +2,9 @@
 
 Trains the same tiny bf16 model twice from the same seed -- gradient reduce-scatter at the optimizer step vs.
 bucketed reduce-scatter started from backward hooks on a side stream plus asynchronous parameter all-gather --
-and checks that the losses agree and that buckets were really reduced early.  Prints ``DP_OVERLAP_OK`` on rank 0.
+and checks that the losses agree and that buckets were really reduced early; then both once more with the gradient
+reduce-scatter and the parameter all-gather done by the peer-memory kernels instead of NCCL (``NEOX_ZERO_PEER=1``):
+same losses, no bounded wait expired.  Prints ``DP_OVERLAP_OK`` on rank 0.
 """
 import os
 import sys
@@ -41,9 +43,17 @@ def run(overlap):
             i += 1
     data = it()
     losses = []
-    for _ in range(6):
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(8):
+        if i == 3:
+            torch.cuda.synchronize()
+            t0.record()
         d, _ = train_step(args, Timers(), data, model, opt, sched)
         losses.append(float(d["lm_loss"]))
+    t1.record()
+    torch.cuda.synchronize()
+    run.ms = t0.elapsed_time(t1) / 5
+    run.peer = all(getattr(b, "peer", False) for b in opt.buckets)
     return losses, getattr(opt, "overlapped_reductions", 0), len(opt.buckets)
 
 
@@ -51,9 +61,28 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     plain, _, nb0 = run(False)
     over, early, nb1 = run(True)
-    ok = all(abs(a - b) < 2e-2 for a, b in zip(plain, over)) and early > 0 and nb1 > nb0
+    ms_over = run.ms
+    ok = all(abs(a - b) < 2e-2 for a, b in zip(plain, over)) and early > 0 and nb1 > nb0 and not run.peer
     if not ok:
         print(f"[rank {dist.get_rank()}] plain {plain} overlap {over} early {early} buckets {nb0}->{nb1}", flush=True)
+    # the same two runs with the data-parallel traffic on the peer-memory kernels
+    from gpt_neox_b200.ops import native
+    os.environ["NEOX_ZERO_PEER"] = "1"
+    peer_plain, _, _ = run(False)
+    used = run.peer
+    peer_over, early_p, _ = run(True)
+    used = used and run.peer
+    ms_peer = run.ms
+    os.environ["NEOX_ZERO_PEER"] = "0"
+    status = native.read_status()
+    ok_peer = (used and status == 0 and early_p > 0 and all(abs(a - b) < 2e-2 for a, b in zip(plain, peer_plain))
+               and all(abs(a - b) < 2e-2 for a, b in zip(plain, peer_over)))
+    if not ok_peer:
+        print(f"[rank {dist.get_rank()}] peer traffic: used {used} status {status} early {early_p} plain {plain} "
+              f"peer {peer_plain} peer+overlap {peer_over}", flush=True)
+    elif dist.get_rank() == 0:
+        print(f"ZERO_PEER_OK ms/step overlapped: nccl {ms_over:.2f} peer {ms_peer:.2f}", flush=True)
+    ok = ok and ok_peer
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if dist.get_rank() == 0 and flag.item() == 1:
