@@ -475,6 +475,18 @@ class NeoXArgs:
         dp = (gpus / pp) / mp
         if dp % 1 != 0:
             raise AssertionError(f"(global_num_gpus / pp_size) / mp_size [({gpus} / {pp}) / {mp}] must be a whole number")
+        if self.elasticity and self.elasticity.get("enabled", False):
+            # the elastic batch replaces the configured triple (an explicit one must agree with it unless told so)
+            from .elasticity import compute_elastic_config
+            e_batch, _, e_micro = compute_elastic_config(self.elasticity, world_size=int(dp))
+            given = (self.train_batch_size, self.train_micro_batch_size_per_gpu, self.gradient_accumulation_steps)
+            if not self.elasticity.get("ignore_non_elastic_batch_info", False) and any(v is not None for v in given):
+                if self.train_batch_size not in (None, e_batch):
+                    raise AssertionError(
+                        f"train_batch_size {self.train_batch_size} disagrees with the elastic batch size {e_batch}; "
+                        "remove it or set elasticity.ignore_non_elastic_batch_info")
+            self.train_batch_size, self.train_micro_batch_size_per_gpu = e_batch, e_micro
+            self.gradient_accumulation_steps = e_batch // (e_micro * int(dp))
         tb, mb, ga = self.calculate_batch_parameters(dp, self.train_batch_size, self.train_micro_batch_size_per_gpu,
                                                      self.gradient_accumulation_steps)
         self.check_batch_parameters(dp, tb, mb, ga)

@@ -184,6 +184,7 @@ padded_vocab_size : int = None
 
 [training]
 data_path : str = None
+autotuning_metric_path : str = None             # set by the autotuner for a trial run: file that receives the measured throughput
 use_shared_fs : bool = True
 train_data_paths : list = None
 train_label_data_paths : list = None

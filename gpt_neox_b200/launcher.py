@@ -130,6 +130,13 @@ def multinode_command(neox_args, world, script_argv, master_addr):
 
 
 def launch(neox_args):
+    if neox_args.autotuning_run in ("tune", "run"):
+        from .autotuning import Autotuner
+        tuner = Autotuner(neox_args)
+        best = tuner.tune()
+        if neox_args.autotuning_run == "tune" or best is None:
+            return 0 if best is not None else 1
+        neox_args = tuner.apply_best(best)
     world = _world_info(neox_args)
     script_argv = worker_argv(neox_args)
     extra = {}

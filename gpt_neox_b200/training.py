@@ -491,6 +491,37 @@ def collect_loss_for_unit_test(lm_loss):
     pass
 
 
+class _TrialMetric:
+    """Throughput of an autotuning trial: wall-clock (device-synchronised) between ``autotuning.start_profile_step``
+    and ``end_profile_step``, written by rank 0 to ``autotuning_metric_path`` (read back by ``autotuning.Autotuner``)."""
+
+    def __init__(self, neox_args):
+        block = neox_args.autotuning or {}
+        self.args = neox_args
+        self.start = int(block.get("start_profile_step", 3))
+        self.end = int(block.get("end_profile_step", 5))
+        self.t0 = None
+
+    @staticmethod
+    def _now():
+        import time
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        return time.perf_counter()
+
+    def before_step(self, iteration):
+        if iteration == self.start:
+            self.t0 = self._now()
+        elif iteration == self.end and self.t0 is not None:
+            dt = (self._now() - self.t0) / max(self.end - self.start, 1)
+            if (not dist.is_initialized()) or dist.get_rank() == 0:
+                import json
+                with open(self.args.autotuning_metric_path, "w") as fh:
+                    json.dump({"latency": dt, "throughput": self.args.train_batch_size / dt,
+                               "tokens_per_sec": self.args.train_batch_size * self.args.seq_length / dt}, fh)
+            self.t0 = None
+
+
 def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator, valid_data_iterator,
           reference_model=None):
     model.train()
@@ -515,7 +546,10 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
                                       record_shapes=True, profile_memory=True, with_flops=True, with_modules=True,
                                       with_stack=True)
         prof.start()
+    tune = _TrialMetric(neox_args) if neox_args.autotuning_metric_path else None
     while iteration < neox_args.train_iters:
+        if tune is not None:
+            tune.before_step(iteration)
         if prof is not None:
             prof.step()
         if neox_args.profile and iteration == neox_args.profile_step_start and torch.cuda.is_available():

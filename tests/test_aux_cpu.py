@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 import torch
 
-from common import make_args, run_distributed
+from common import ROOT, make_args, run_distributed
 
 
 class _FakeIndexed:
@@ -299,3 +299,59 @@ def _flops_worker(rank, world, out_file):
 def test_flops_profiler_counts_forward_flops_of_a_small_model(tmp_path):
     from common import run_distributed
     run_distributed(_flops_worker, 1, str(tmp_path / "flops.txt"))
+
+
+# ------------------------------------------------------------------ autotuner
+def _tuning_args(tmp_path, **block):
+    from common import make_args
+    return make_args(global_num_gpus=1, zero_optimization={"stage": "auto"},
+                     autotuning={"enabled": True, "start_profile_step": 1, "end_profile_step": 3,
+                                 "num_tuning_micro_batch_sizes": 3, "results_dir": str(tmp_path / "results"),
+                                 "exps_dir": str(tmp_path / "exps"), **block})
+
+
+def test_autotuner_search_with_a_stand_in_runner(tmp_path):
+    import json
+    from gpt_neox_b200.autotuning import Autotuner
+    args = _tuning_args(tmp_path)
+    seen = []
+
+    def runner(trial):
+        # throughput grows with the micro-batch; stage 1 is a little slower; micro-batch 4 "runs out of memory" at stage 0
+        mb, stage = trial.train_micro_batch_size_per_gpu, trial.zero_optimization["stage"]
+        seen.append((stage, mb, trial.train_iters, trial.save, trial.autotuning_run))
+        assert trial.train_batch_size == mb * trial.gradient_accumulation_steps
+        if stage == 0 and mb == 4:
+            return 1
+        with open(trial.autotuning_metric_path, "w") as fh:
+            json.dump({"throughput": 100.0 * mb - 10 * stage, "latency": 1.0 / mb, "tokens_per_sec": 1.0}, fh)
+        return 0
+
+    tuner = Autotuner(args, runner=runner)
+    assert tuner.micro_batch_sizes() == [1, 2, 4] and tuner.zero_stages() == [0, 1]
+    best = tuner.tune()
+    assert [s[:2] for s in seen] == [(0, 1), (0, 2), (0, 4), (1, 1), (1, 2), (1, 4)]
+    assert all(s[2] == 4 and s[3] is None and s[4] is None for s in seen)
+    assert best["zero_stage"] == 1 and best["micro_batch"] == 4 and best["throughput"] == 390.0
+    summary = json.load(open(tmp_path / "results" / "summary.json"))
+    assert summary["best"]["name"] == "z1_mbs4" and len(summary["experiments"]) == 6
+    assert "failed (1)" in open(tmp_path / "results" / "summary.txt").read()
+    final = tuner.apply_best(best)
+    assert final.train_micro_batch_size_per_gpu == 4 and final.zero_optimization["stage"] == 1
+    assert final.autotuning_run is None
+    # latency as the metric: lower is better; early stopping after one non-improving trial
+    tuner = Autotuner(_tuning_args(tmp_path, metric="latency", tuner_early_stopping=1, tune_zero_stage=False),
+                      runner=runner)
+    assert tuner.tune()["micro_batch"] == 2          # stage 0: 1, 2 ok, 4 fails
+
+
+def test_autotuner_runs_a_real_trial_through_the_launcher(tmp_path):
+    """One trial end to end on CPU: the launcher starts the training script, the training loop writes the metric."""
+    import json
+    from gpt_neox_b200.autotuning import Autotuner
+    args = _tuning_args(tmp_path, num_tuning_micro_batch_sizes=1)
+    args.update_values({"user_script": os.path.join(ROOT, "train.py"), "zero_optimization": {"stage": 0},
+                        "num_gpus": 1, "master_port": 29000 + os.getpid() % 2000})
+    best = Autotuner(args).tune()
+    assert best is not None and best["exit_code"] == 0 and best["throughput"] > 0 and best["latency"] > 0
+    assert json.load(open(tmp_path / "exps" / "z0_mbs1" / "metric.json"))["tokens_per_sec"] > 0

@@ -184,3 +184,33 @@ def test_every_argument_used_in_code_is_declared():
                     if name not in known:
                         missing.setdefault(name, []).append(os.path.relpath(os.path.join(dirpath, f), root))
     assert not missing, missing
+
+
+def test_elastic_batch_configuration():
+    from gpt_neox_b200.config.elasticity import ElasticityError, compute_elastic_config, valid_gpu_counts
+    block = {"enabled": True, "max_train_batch_size": 2000, "micro_batch_sizes": [2, 4, 6], "min_gpus": 1,
+             "max_gpus": 64}
+    batch, gpus, micro = compute_elastic_config(block, world_size=8)
+    assert batch <= 2000 and gpus == valid_gpu_counts(batch, [2, 4, 6], 1, 64) and 8 in gpus
+    assert micro in (2, 4, 6) and batch % (micro * 8) == 0
+    # no other batch size admits more GPU counts, and among equals the largest was taken
+    for other in range(2, 2001, 2):
+        n = len(valid_gpu_counts(other, [2, 4, 6], 1, 64))
+        assert n < len(gpus) or (n == len(gpus) and other <= batch)
+    small, _, _ = compute_elastic_config({**block, "prefer_larger_batch": False})
+    assert small <= batch and len(valid_gpu_counts(small, [2, 4, 6], 1, 64)) == len(gpus)
+    with pytest.raises(ElasticityError):
+        compute_elastic_config({"micro_batch_sizes": [8], "max_train_batch_size": 4})
+    with pytest.raises(ElasticityError):
+        compute_elastic_config({"micro_batch_sizes": [3], "max_train_batch_size": 9, "min_gpus": 1, "max_gpus": 4}, 2)
+
+
+def test_elasticity_block_sets_the_batch_triple():
+    cfg = {k: v for k, v in MINIMAL.items() if k != "train_micro_batch_size_per_gpu"}
+    cfg.update(global_num_gpus=4, elasticity={"enabled": True, "max_train_batch_size": 96, "micro_batch_sizes": [2, 3],
+                                              "min_gpus": 1, "max_gpus": 8})
+    args = NeoXArgs.from_dict(cfg)
+    assert args.train_batch_size == args.train_micro_batch_size_per_gpu * args.gradient_accumulation_steps * 4
+    assert args.train_batch_size <= 96 and args.train_micro_batch_size_per_gpu in (2, 3)
+    with pytest.raises(AssertionError):
+        NeoXArgs.from_dict(dict(cfg, train_batch_size=args.train_batch_size + 4))
