@@ -130,3 +130,32 @@ def _partitioned_checkpoint(rank, world, _cfg, _out):
 
 def test_partitioned_activation_checkpointing():
     run_distributed(_partitioned_checkpoint, 2, None, None)
+
+
+# ------------------------------------------------------------------ flag-protocol replay (stands in for a device race detector)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_flag_protocols_are_race_and_deadlock_free_under_random_interleavings(world):
+    from gpt_neox_b200.parallel import protocol_model as PM
+    seeds = range(60 if world < 8 else 20)
+    PM.check(PM.gemm_all_reduce_program, world, seeds=seeds, epochs=6)
+    PM.check(PM.gemm_all_reduce_program, world, seeds=seeds, epochs=6, deferred_tail=True)
+    PM.check(PM.zero_peer_program, world, seeds=seeds, steps=5)
+
+
+def test_protocol_checker_notices_a_missing_guard():
+    """The checker has teeth: drop one wait and some interleaving produces a stale or overwritten read."""
+    from gpt_neox_b200.parallel import protocol_model as PM
+    for kw in ({"program": PM.gemm_all_reduce_program, "epochs": 6, "wait_ready": False},
+               {"program": PM.gemm_all_reduce_program, "epochs": 6, "wait_ready": False, "deferred_tail": True},
+               {"program": PM.zero_peer_program, "steps": 5, "wait_done_before_zero": False}):
+        program = kw.pop("program")
+        with pytest.raises(PM.ProtocolViolation):
+            PM.check(program, 4, seeds=range(300), **kw)
+    # the "buffer is free again" guards of the all-reduce are implied by stream order in this call sequence
+    PM.check(PM.gemm_all_reduce_program, 4, seeds=range(100), epochs=6, guard_recv=False, guard_gathered=False)
+    # and a circular wait is reported as a deadlock, not as a hang
+    sim = PM.Simulator(2)
+    sim.add(0, "main", [("wait", "x", 1, 1), ("signal", 1, "x", 1)])
+    sim.add(1, "main", [("wait", "x", 0, 1), ("signal", 0, "x", 1)])
+    with pytest.raises(PM.ProtocolViolation, match="deadlock"):
+        sim.run(0)
