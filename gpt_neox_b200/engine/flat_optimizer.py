@@ -45,10 +45,27 @@ _READY, _DONE, _GATHERED = 0, 8, 16
 _WAIT_ROUNDS = 60      # x about two seconds
 
 
-def peer_traffic_enabled() -> bool:
-    """ZeRO-1 reduce-scatter / all-gather through peer memory instead of NCCL (``NEOX_ZERO_PEER=1``; one NVLink
-    domain, at most 8 data-parallel ranks)."""
-    return os.environ.get("NEOX_ZERO_PEER", "0") == "1"
+_same_host = {}
+
+
+def peer_traffic_enabled(group=None) -> bool:
+    """ZeRO-1 reduce-scatter / all-gather through peer memory instead of NCCL.  ``NEOX_ZERO_PEER=0`` / ``1`` forces
+    it; by default it is used when every rank of the communication group runs on this host (one NVLink domain: the
+    buffers are exchanged as CUDA IPC handles) under the NCCL backend."""
+    mode = os.environ.get("NEOX_ZERO_PEER", "auto")
+    if mode in ("0", "1"):
+        return mode == "1"
+    if not (torch.cuda.is_available() and dist.is_available() and dist.is_initialized()):
+        return False
+    if dist.get_backend(group) != "nccl":
+        return False
+    key = id(group)
+    if key not in _same_host:
+        import socket
+        names = [None] * dist.get_world_size(group)
+        dist.all_gather_object(names, socket.gethostname(), group=group)
+        _same_host[key] = len(set(names)) == 1
+    return _same_host[key]
 
 
 def _lib():
@@ -103,9 +120,10 @@ class Bucket:
         self.numel = off
         self.padded = _pad_to(max(off, 1), _ALIGN * max(comm_world, 1))
         self.offsets = offs
-        self.peer = (self.sharded and peer_traffic_enabled() and torch.device(device).type == "cuda"
-                     and comm_world <= 8 and grad_dtype == torch.float32
-                     and model_dtype in (torch.bfloat16, torch.float16, torch.float32))
+        self.peer = (self.sharded and torch.device(device).type == "cuda" and comm_world <= 8
+                     and grad_dtype == torch.float32
+                     and model_dtype in (torch.bfloat16, torch.float16, torch.float32)
+                     and peer_traffic_enabled(comm_group))
         if self.peer:
             # both flat buffers in symmetric memory: the owner of a shard reads it from every rank's gradient
             # buffer, and writes its updated shard into every rank's parameter buffer (csrc/comm_gemm_sm100.cu)

@@ -404,7 +404,7 @@ extern "C" int neox_gemm_16(const void* A, const void* B, void* D, int M, int N,
 // of the MegaBlocks library that the reference calls (megatron/model/moe_mlp.py of the reference: `gg.ops.gmm`).
 __global__ void __launch_bounds__(256) moe_tile_table_kernel(const long long* __restrict__ counts, int E, int pad,
                                                              int mode, int num_m, int num_n, int b_stride,
-                                                             int max_tiles, int4* __restrict__ table,
+                                                             int m_total, int max_tiles, int4* __restrict__ table,
                                                              int* __restrict__ ntiles) {
     extern __shared__ int sh[];   // [E] segment starts, [E] first tile of each expert
     int* seg = sh;
@@ -418,6 +418,14 @@ __global__ void __launch_bounds__(256) moe_tile_table_kernel(const long long* __
             row += (c + pad - 1) / pad * pad;
             if (mode == 1) tile += ((c + pad - 1) / pad * pad + BM - 1) / BM * num_n;
             else tile += c > 0 ? num_m * num_n : 0;
+        }
+        if (mode == 1 && row < m_total) {
+            // rows behind the last segment (the matrix has a static, generous row count): their inputs are zero,
+            // so running them through expert 0 stores zeros -- no row of the output is left uninitialised
+            const int mb_n = (m_total - row + BM - 1) / BM;
+            for (int nb = 0; nb < num_n; ++nb)
+                for (int mb = 0; mb < mb_n; ++mb, ++tile)
+                    if (tile < max_tiles) table[tile] = make_int4(row + mb * BM, m_total, 0, nb);
         }
         *ntiles = tile < max_tiles ? tile : max_tiles;
     }
@@ -482,7 +490,7 @@ extern "C" int neox_gemm_grouped_16(const void* A, const void* B, void* D, int M
     const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     if (mode == 2 && (num_m > 0x7fff || num_n > 0xffff)) return NEOX_ERR_SHAPE;
     moe_tile_table_kernel<<<1, 256, 2 * E * sizeof(int), stream>>>(counts, E, pad, mode, num_m, num_n,
-                                                                    b_mn ? K : N, max_tiles,
+                                                                    b_mn ? K : N, M, max_tiles,
                                                                     static_cast<int4*>(table), ntiles);
     if (cudaGetLastError() != cudaSuccess) return NEOX_ERR_LAUNCH;
 

@@ -202,7 +202,8 @@ def _segments(counts):
 
 
 def grouped_linear_ref(x_pad, w, counts, act=None):
-    """Eager statement: rows of segment e times ``w[e].T`` (padding rows give zeros)."""
+    """Eager statement: rows of segment e times ``w[e].T`` (padding rows and the rows behind the last segment give
+    zeros, as in the kernel, which runs them -- all-zero inputs -- through the GEMM as well)."""
     out = torch.zeros(x_pad.shape[0], w.shape[1], dtype=x_pad.dtype, device=x_pad.device)
     for e, (row, n) in enumerate(_segments(counts)):
         if n:
@@ -214,7 +215,7 @@ def grouped_linear_ref(x_pad, w, counts, act=None):
 
 def _grouped_call(A, B, D, M, N, K, lda, ldb, ldd, b_mn, counts, E, mode, add=None, preact=None, act=G.ACT_NONE):
     num_n = (N + 255) // 256
-    max_tiles = (M // 128 + E) * num_n if mode == 1 else E * ((M + 127) // 128) * num_n
+    max_tiles = (M // 128 + E + 1) * num_n if mode == 1 else E * ((M + 127) // 128) * num_n
     table = torch.empty(max_tiles * 4 + 4, dtype=torch.int32, device=A.device)   # [ntiles, pad x 3, entries]
     ll = ctypes.c_longlong
     rc = native.lib().neox_gemm_grouped_16(

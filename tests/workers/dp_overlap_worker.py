@@ -59,6 +59,7 @@ def run(overlap):
 
 def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    os.environ["NEOX_ZERO_PEER"] = "0"
     plain, _, nb0 = run(False)
     over, early, nb1 = run(True)
     ms_over = run.ms
