@@ -34,6 +34,7 @@ from ..ops import functional as OF
 from ..ops import gemm as G
 from ..ops import moe_ops as MO
 from ..ops.linear import linear as fused_linear
+from ..parallel import mappings as M
 from ..parallel import moe_comm, mpu
 from ..parallel.rng import get_cuda_rng_tracker
 
@@ -146,7 +147,16 @@ class ParallelMoE(nn.Module):
         self.glu = neox_args.moe_glu
         self.activation = neox_args.activation
         h = neox_args.hidden_size
-        ffn = neox_args.intermediate_size or int((neox_args.expansion_factor or 4) * h)
+        ffn_full = neox_args.intermediate_size or int((neox_args.expansion_factor or 4) * h)
+        # expert tensor parallelism (``enable_expert_tensor_parallelism``): every expert's hidden dimension is split
+        # over the tensor-parallel group (first projection column-parallel, second row-parallel, one all-reduce of
+        # the combined output); without it every tensor-parallel rank holds whole experts
+        tp = mpu.get_model_parallel_world_size()
+        self.expert_tp = bool(neox_args.enable_expert_tensor_parallelism) and tp > 1
+        if self.expert_tp:
+            assert ffn_full % tp == 0, f"expert hidden size {ffn_full} not divisible by tensor-parallel size {tp}"
+        tp_rank = mpu.get_model_parallel_rank() if self.expert_tp else 0
+        ffn = ffn_full // tp if self.expert_tp else ffn_full
         self.ffn = ffn
         dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
         dt = neox_args.params_dtype
@@ -154,20 +164,29 @@ class ParallelMoE(nn.Module):
         n_in = ffn * (2 if self.glu else 1)
         self.w1 = nn.Parameter(torch.empty(self.local_experts, n_in, h, device=dev, dtype=dt))
         self.w2 = nn.Parameter(torch.empty(self.local_experts, h, ffn, device=dev, dtype=dt))
-        # Every expert is initialised from its own seed (a function of the GLOBAL expert id), so the weights do
-        # not depend on how experts are spread over expert-parallel ranks.
+        # Every expert is initialised from its own seed (a function of the GLOBAL expert id) at full size and then
+        # sliced, so the weights depend neither on how experts are spread over expert-parallel ranks nor on the
+        # tensor-parallel degree.
         ep_rank = mpu.get_expert_parallel_rank()
+        lo, hi = tp_rank * ffn, (tp_rank + 1) * ffn
         for e in range(self.local_experts):
             gid = ep_rank * self.local_experts + e
             with torch.random.fork_rng(devices=[]):
                 torch.manual_seed(neox_args.seed + 7919 * (gid + 1))
-                tmp1 = torch.empty(n_in, h, dtype=torch.float)
-                tmp2 = torch.empty(h, ffn, dtype=torch.float)
+                tmp1 = torch.empty(ffn_full * (2 if self.glu else 1), h, dtype=torch.float)
+                tmp2 = torch.empty(h, ffn_full, dtype=torch.float)
                 init_method(tmp1)
                 output_layer_init_method(tmp2)
+            if self.glu:      # [gate; up] halves are sharded separately
+                tmp1 = torch.cat([tmp1[lo:hi], tmp1[ffn_full + lo:ffn_full + hi]])
+            else:
+                tmp1 = tmp1[lo:hi]
             with torch.no_grad():
                 self.w1[e].copy_(tmp1)
-                self.w2[e].copy_(tmp2)
+                self.w2[e].copy_(tmp2[:, lo:hi])
+        if self.expert_tp:
+            self.w1.model_parallel, self.w1.partition_dim, self.w1.partition_stride = True, 1, 2 if self.glu else 1
+            self.w2.model_parallel, self.w2.partition_dim, self.w2.partition_stride = True, 2, 1
         if self.ep > 1:
             self.w1.expert_parallel = True
             self.w2.expert_parallel = True
@@ -277,10 +296,21 @@ class ParallelMoE(nn.Module):
         return max(self.min_capacity, int(math.ceil(cf * tokens * self.top_k / self.num_experts)))
 
     def forward(self, hidden_states):
+        y, lbl = self._forward(hidden_states)
+        if self.expert_tp:
+            y = M.reduce_from_model_parallel_region(y)
+        return y, lbl
+
+    def _forward(self, hidden_states):
         shape = hidden_states.shape
         x = hidden_states.reshape(-1, shape[-1])
         T, E, k = x.shape[0], self.num_experts, self.top_k
         probs, w, idx, counts = self.router(x)
+        if self.expert_tp:
+            # the router runs replicated on the unsplit input; what enters the sharded experts is marked so that the
+            # partial gradients of the expert input and of the gates are summed over the tensor-parallel group
+            x = M.copy_to_model_parallel_region(x)
+            w = M.copy_to_model_parallel_region(w)
         # ---- load-balancing statistics
         flat_e = idx.reshape(-1)
         f = counts.float() / float(T * k)

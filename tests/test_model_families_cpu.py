@@ -116,3 +116,61 @@ def _moe_grouped_matches_loop(rank, world, cfg):
 ])
 def test_moe_grouped_data_flow_matches_per_expert_loop(cfg):
     run_distributed(_moe_grouped_matches_loop, 1, cfg)
+
+
+def _expert_tensor_parallel(rank, world):
+    """Experts sharded over the tensor-parallel group against a dense statement with the full weights: outputs,
+    input gradient, router gradient (replicated) and expert-weight gradients (the matching slices) agree."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from common import make_args
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.models.init_functions import get_init_methods
+    from gpt_neox_b200.models.moe import ParallelMoE
+    from gpt_neox_b200.parallel import mpu
+    args = make_args(global_num_gpus=world, model_parallel_size=world, moe_num_experts=4, moe_top_k=2,
+                     moe_token_dropping=False, enable_expert_tensor_parallelism=True)
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    init, out_init = get_init_methods(args)
+    moe = ParallelMoE(args, init, out_init, 4).float()
+    assert moe.expert_tp and moe.w1.shape[1] == 4 * args.hidden_size // world and moe.w1.model_parallel
+    grp = mpu.get_model_parallel_group()
+
+    def gather(t, dim):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous(), group=grp)
+        return torch.cat(parts, dim=dim)
+
+    W1 = gather(moe.w1.detach(), 1).requires_grad_(True)
+    W2 = gather(moe.w2.detach(), 2).requires_grad_(True)
+    Wr = moe.router.layer.weight.detach().clone().requires_grad_(True)
+    torch.manual_seed(5)
+    x = torch.randn(args.seq_length, 2, args.hidden_size)
+    xa = x.clone().requires_grad_(True)
+    y, lbl = moe(xa)
+    (y.square().sum() + lbl).backward()
+    xb = x.clone().requires_grad_(True)
+    flat = xb.reshape(-1, args.hidden_size)
+    probs = F.softmax(flat @ Wr.t(), dim=-1)
+    w, idx = torch.topk(probs, 2, dim=-1)
+    w = w / w.sum(-1, keepdim=True)
+    ref = torch.zeros_like(flat)
+    for e in range(4):
+        gate = (w * (idx == e)).sum(-1, keepdim=True)
+        ref = ref + gate * (F.gelu(flat @ W1[e].t(), approximate="tanh") @ W2[e].t())
+    counts = torch.bincount(idx.reshape(-1), minlength=4).float()
+    lbl_ref = 4 * torch.sum(counts / counts.sum() * probs.mean(0))
+    (ref.square().sum() + lbl_ref).backward()
+    tol = dict(atol=3e-5, rtol=1e-4)
+    torch.testing.assert_close(y.reshape(-1, args.hidden_size), ref, **tol)
+    torch.testing.assert_close(xa.grad, xb.grad, **tol)
+    torch.testing.assert_close(moe.router.layer.weight.grad, Wr.grad, **tol)
+    f = moe.ffn
+    torch.testing.assert_close(moe.w1.grad, W1.grad[:, rank * f:(rank + 1) * f], **tol)
+    torch.testing.assert_close(moe.w2.grad, W2.grad[:, :, rank * f:(rank + 1) * f], **tol)
+
+
+def test_moe_expert_tensor_parallelism_matches_dense_math():
+    run_distributed(_expert_tensor_parallel, 2)
