@@ -36,6 +36,12 @@ def main():
                     help="only the five GEMM shapes, three ways taking turns call by call: one-CTA kernel, CTA-pair "
                          "kernel, cuBLAS through torch (F.linear / matmul, plus the element-wise kernels the fused "
                          "epilogues replace)")
+    ap.add_argument("--moe", action="store_true",
+                    help="only the mixture-of-experts kernels: router, dispatch / combine, and the grouped expert "
+                         "GEMMs (forward, dgrad, wgrad) against the per-expert loop over the plain GEMM; "
+                         "--tokens rows x top-2 of --experts experts, hidden --hidden, expert hidden --ffn")
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--ffn", type=int, default=0, help="expert hidden size (default 4 x hidden)")
     a = ap.parse_args()
     only = set(x for x in a.only.split(",") if x)
     dev = torch.device("cuda")
@@ -73,6 +79,8 @@ def main():
 
     if a.ab_gemm:
         return ab_gemm(a, dev, bf, flush)
+    if a.moe:
+        return moe_kernels(a, dev, bf, flush)
     x = bf(T, h)
     w_qkv, w_fc1, w_fc2 = bf(3 * h, h), bf(4 * h, h), bf(h, 4 * h)
     y4 = bf(T, 4 * h)
@@ -248,6 +256,99 @@ def ab_gemm(a, dev, bf, flush):
                "pair_over_cublas": round(med["cublas"] / med["cta_pair"], 3)}
         results.append(rec)
         print(json.dumps(rec), flush=True)
+    return results
+
+
+def moe_kernels(a, dev, bf, flush):
+    """Router, dispatch / combine and the grouped expert GEMMs against the per-expert loop, taking turns call by
+    call (L2 flushed before every call); medians.  Assignments are drawn from a softmax over random logits, so the
+    experts are unevenly loaded the way a real router loads them."""
+    from . import moe_ops as MO
+    T, h, E, k = a.tokens, a.hidden, a.experts, 2
+    ffn = a.ffn or 4 * h
+    hbm, tf, kind = peaks()
+    x = bf(T, h)
+    logits = (torch.randn(T, E, device=dev) * 1.5).to(torch.bfloat16)
+    w1, w2 = bf(E, ffn, h), bf(E, h, ffn)
+    probs, gate, idx, counts = MO.router(logits, k)
+    row_of, kept = MO.plan_rows(idx, counts)
+    rows = MO.padded_rows(T * k, E)
+    xs = MO.dispatch(x, row_of, rows)
+    g_out = torch.zeros(rows, ffn, device=dev, dtype=torch.bfloat16)
+    g_out[row_of.reshape(-1)] = bf(T * k, ffn)
+    segs = MO._segments(kept)
+    acc = torch.zeros(E, ffn, h, device=dev, dtype=torch.float32)
+    pre = torch.empty(rows, ffn, device=dev, dtype=torch.bfloat16)
+    out_f, out_d = torch.empty(rows, ffn, device=dev, dtype=torch.bfloat16), torch.empty(rows, h, device=dev, dtype=torch.bfloat16)
+
+    def loop_fwd():
+        for e, (r, n) in enumerate(segs):
+            if n:
+                G.gemm(xs[r:r + n], w1[e], act=G.ACT_GELU, want_preact=True)
+
+    def loop_dgrad():
+        for e, (r, n) in enumerate(segs):
+            if n:
+                G.gemm(g_out[r:r + n], w1[e], b_mn=True)
+
+    def loop_wgrad():
+        for e, (r, n) in enumerate(segs):
+            if n:
+                G.gemm(g_out[r:r + n], xs[r:r + n], a_mn=True, b_mn=True, out=acc[e], add=acc[e])
+
+    def grouped_fwd():
+        MO._grouped_call(xs, w1, out_f, rows, ffn, h, h, h, ffn, False, kept, E, 1, preact=pre, act=G.ACT_GELU)
+
+    def grouped_dgrad():
+        MO._grouped_call(g_out, w1, out_d, rows, h, ffn, ffn, h, h, True, kept, E, 1)
+
+    def grouped_wgrad():
+        MO._grouped_call(g_out, xs, acc.view(E * ffn, h), ffn, h, rows, ffn, h, h, True, kept, E, 2,
+                         add=acc.view(E * ffn, h))
+
+    flops = 2.0 * T * k * h * ffn
+    cases = [
+        ("expert_fc1_fwd_gelu", flops, 0.0, {"per_expert_loop": loop_fwd, "grouped": grouped_fwd}),
+        ("expert_fc1_dgrad", flops, 0.0, {"per_expert_loop": loop_dgrad, "grouped": grouped_dgrad}),
+        ("expert_fc1_wgrad_fp32_accumulate", flops, 0.0, {"per_expert_loop": loop_wgrad, "grouped": grouped_wgrad}),
+        ("router_softmax_top2", 0.0, T * E * (2 + 4) + T * k * 12.0,
+         {"torch": lambda: MO.router_ref(logits, k), "kernel": lambda: MO.router(logits, k)}),
+        ("dispatch_rows", 0.0, T * h * 2.0 + T * k * h * 2.0 + rows * h * 2.0,
+         {"torch": lambda: MO.dispatch_ref(x, row_of, rows), "kernel": lambda: MO.dispatch(x, row_of, rows)}),
+        ("combine_rows", 0.0, T * k * h * 2.0 + T * h * 2.0,
+         {"torch": lambda: MO.combine_ref(out_d, row_of, gate), "kernel": lambda: MO.combine(out_d, row_of, gate)}),
+    ]
+    results = []
+    for name, fl, nbytes, fns in cases:
+        for f in fns.values():
+            for _ in range(3):
+                f()
+        torch.cuda.synchronize()
+        ts = {key: [] for key in fns}
+        for _ in range(a.iters):
+            for key, f in fns.items():
+                flush.add_(1.0)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                f()
+                e1.record()
+                torch.cuda.synchronize()
+                ts[key].append(e0.elapsed_time(e1))
+        med = {key: sorted(v)[len(v) // 2] for key, v in ts.items()}
+        rec = {"kernel": name, "tokens": T, "experts": E, "hidden": h, "ffn": ffn,
+               **{f"{key}_ms": round(v, 4) for key, v in med.items()}}
+        keys = list(med)
+        rec["speedup"] = round(med[keys[0]] / med[keys[1]], 3)
+        if fl:
+            rec["tflops"] = round(fl / med[keys[1]] / 1e9, 1)
+            rec[f"frac_of_{kind}_bf16_peak"] = round(fl / med[keys[1]] / 1e9 / tf, 3)
+        if nbytes:
+            rec["gbs"] = round(nbytes / med[keys[1]] / 1e6, 1)
+            rec[f"frac_of_{kind}_copy_bw"] = round(nbytes / med[keys[1]] / 1e6 / hbm, 3)
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+    from . import native
+    print(json.dumps({"status_word": native.read_status(), "counts": kept.tolist()}), flush=True)
     return results
 
 
