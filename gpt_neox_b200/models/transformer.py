@@ -408,9 +408,13 @@ class ParallelTransformerLayer(nn.Module):
         fuse = (p == 0.0 or not self.training)
         moe_loss = torch.tensor(0.0, device=x.device, dtype=x.dtype)
         if self.gpt_j_residual:
-            residual = x
-            x1 = self.input_layernorm(x)
-            x2 = x1 if self.gpt_j_tied else self.post_attention_layernorm(x)
+            # both norms and the residual connection read x: one autograd node, whose backward adds the three
+            # gradient contributions inside the norm-backward kernels (ops/functional.py::norm_fan_out)
+            if self.gpt_j_tied:
+                x1, residual = OF.norm_fan_out(x, [self.input_layernorm])
+                x2 = x1
+            else:
+                x1, x2, residual = OF.norm_fan_out(x, [self.input_layernorm, self.post_attention_layernorm])
             if fuse and self.mlp_type == "regular" and not self.use_cache:
                 # attention partial (+ its bias) [+ residual when no reduction follows] accumulated by the
                 # GEMM epilogues:  out = residual + attn + b_a + mlp + b_m
@@ -446,9 +450,9 @@ class ParallelTransformerLayer(nn.Module):
             return out, moe_loss
 
         # sequential residual
-        residual = x
+        h1, residual = OF.norm_fan_out(x, [self.input_layernorm])
         can_fuse_res = fuse and not self.use_cache
-        a_out, a_bias = self.attention(self.input_layernorm(x), attention_mask, layer_past=layer_past,
+        a_out, a_bias = self.attention(h1, attention_mask, layer_past=layer_past,
                                        residual=residual if (can_fuse_res and self.attention.dense.bias is None) else None)
         if self.use_cache:
             a_out, presents = a_out
@@ -457,7 +461,7 @@ class ParallelTransformerLayer(nn.Module):
             x = a_out
         else:
             x = OF.bias_dropout_add(a_out, a_bias, residual, p, self.training)
-        ln2 = self.post_attention_layernorm(x)
+        ln2, x = OF.norm_fan_out(x, [self.post_attention_layernorm])
         if self.mlp_type == "moe":
             m_out, moe_loss = self.mlp(ln2)
             out = OF.bias_dropout_add(m_out, None, x, p, self.training)

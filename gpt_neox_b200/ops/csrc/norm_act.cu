@@ -263,8 +263,11 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const T* __restrict__ x, 
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(256) norm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x,
                                                        const T* __restrict__ gamma, const float* __restrict__ stat0,
-                                                       const float* __restrict__ stat1, T* __restrict__ dx,
-                                                       float* __restrict__ partial, int rows, int cols, float eps) {
+                                                       const float* __restrict__ stat1, T* dx,
+                                                       float* __restrict__ partial, int rows, int cols, float eps,
+                                                       const T* add) {
+    // add (optional, may alias dx): dx = gradient through the norm + add -- lets the caller fold the other
+    // gradient contributions of the norm's input (residual path, a sibling norm) into this pass
     __shared__ float red[66];
     const int nvec = cols >> 3;
     const bool cached = nvec <= MAXV * (int)blockDim.x;
@@ -367,6 +370,12 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const T* __restrict__ g, 
             float o[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = RMS ? gg[i] * sc - xh[i] * k2 : sc * (gg[i] - k1 - xh[i] * k2);
+            if (add) {
+                float a8[8];
+                Vec8<T>::load(add + (size_t)row * cols + c * 8, a8);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] += a8[i];
+            }
             Vec8<T>::store(dr + c * 8, o);
         };
         if (cached) {
@@ -443,14 +452,15 @@ int launch_norm_fwd(const void* x, const void* gamma, const void* beta, void* y,
 
 template <bool RMS>
 int launch_norm_bwd(const void* g, const void* x, const void* gamma, const float* s0, const float* s1, void* dx,
-                    float* d0, float* d1, float* ws, int rows, int cols, float eps, int dtype, cudaStream_t st) {
+                    float* d0, float* d1, float* ws, int rows, int cols, float eps, int dtype, cudaStream_t st,
+                    const void* add = nullptr) {
     if (cols % 8) return NEOX_ERR_SHAPE;
     if (rows <= 0) return 0;
     const int threads = pick_threads(cols);
     const int nblk = neox_norm_bwd_blocks(rows);
 #define LAUNCH(T)                                                                                                    \
     norm_bwd_kernel<T, RMS><<<nblk, threads, 0, st>>>((const T*)g, (const T*)x, (const T*)gamma, s0, s1, (T*)dx, ws, \
-                                                      rows, cols, eps)
+                                                      rows, cols, eps, (const T*)add)
     if (dtype == 0) LAUNCH(__nv_bfloat16);
     else if (dtype == 1) LAUNCH(float);
     else LAUNCH(__half);
@@ -734,6 +744,19 @@ int neox_layernorm_bwd(const void* g, const void* x, const void* gamma, const fl
                        void* dx, float* dgamma, float* dbeta, float* ws, int rows, int cols, int dtype, void* stream) {
     return launch_norm_bwd<false>(g, x, gamma, mean, rstd, dx, dgamma, dbeta, ws, rows, cols, 0.f, dtype,
                                   (cudaStream_t)stream);
+}
+// dx = (gradient through the norm) + add; add has the shape of dx and may be dx itself.
+int neox_layernorm_bwd_add(const void* g, const void* x, const void* gamma, const float* mean, const float* rstd,
+                           void* dx, float* dgamma, float* dbeta, float* ws, int rows, int cols, int dtype,
+                           const void* add, void* stream) {
+    return launch_norm_bwd<false>(g, x, gamma, mean, rstd, dx, dgamma, dbeta, ws, rows, cols, 0.f, dtype,
+                                  (cudaStream_t)stream, add);
+}
+int neox_rmsnorm_bwd_add(const void* g, const void* x, const void* scale, const float* rinv, void* dx, float* dscale,
+                         float* dbias, float* ws, int rows, int cols, float eps, int dtype, const void* add,
+                         void* stream) {
+    return launch_norm_bwd<true>(g, x, scale, nullptr, rinv, dx, dscale, dbias, ws, rows, cols, eps, dtype,
+                                 (cudaStream_t)stream, add);
 }
 int neox_rmsnorm_fwd(const void* x, const void* scale, const void* bias, void* y, float* rinv, int rows, int cols,
                      float eps, int dtype, void* stream) {

@@ -392,6 +392,111 @@ class _BiasDropoutAdd(torch.autograd.Function):
 
 
 
+
+# ------------------------------------------------------------------------------------ norms + residual fan-out
+class _NormFanOutFn(torch.autograd.Function):
+    """``x -> (norm_1(x), ..., norm_n(x), x)``: the head of a residual block, where the block input feeds one or two
+    norms and the residual connection.  Autograd would add the n + 1 gradient contributions of ``x`` with separate
+    element-wise passes (a clone and an add per contribution, each a full pass over the activations); here every norm
+    backward kernel adds what has been accumulated so far while it writes ``dx`` (``neox_*norm_bwd_add``), so the
+    sum costs no pass of its own.  ``specs``: tuple of ``("ln" | "rms", eps)`` per norm; parameters follow as
+    ``weight_1, bias_1, ..., weight_n, bias_n``."""
+
+    @staticmethod
+    def forward(ctx, x, specs, *params):
+        cols = x.shape[-1]
+        x2 = x.reshape(-1, cols)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        L = native.lib()
+        outs, stats = [], []
+        for i, (kind, eps) in enumerate(specs):
+            w, b = params[2 * i], params[2 * i + 1]
+            y = torch.empty_like(x2)
+            s1 = torch.empty(rows, dtype=torch.float32, device=x.device)
+            if kind == "ln":
+                s0 = torch.empty(rows, dtype=torch.float32, device=x.device)
+                rc = L.neox_layernorm_fwd(native.ptr(x2), native.ptr(w), native.ptr(b), native.ptr(y), native.ptr(s0),
+                                          native.ptr(s1), rows, cols, ctypes.c_float(eps), _DT[x.dtype], _s())
+            else:
+                s0 = None
+                rc = L.neox_rmsnorm_fwd(native.ptr(x2), native.ptr(w), native.ptr(b), native.ptr(y), native.ptr(s1),
+                                        rows, cols, ctypes.c_float(eps), _DT[x.dtype], _s())
+            native.check(rc, "norm forward")
+            outs.append(y.reshape(x.shape))
+            stats += [s0 if s0 is not None else s1, s1]
+        ctx.specs, ctx.shape, ctx.params = specs, x.shape, params
+        ctx.save_for_backward(x2, *stats)
+        ctx.set_materialize_grads(False)
+        return (*outs, x.view_as(x))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        x2, *stats = ctx.saved_tensors
+        rows, cols = x2.shape
+        L = native.lib()
+        acc = grads[-1]                                   # gradient arriving through the residual connection
+        if acc is not None:
+            acc = acc.reshape(rows, cols)
+            if not acc.is_contiguous():
+                acc = acc.contiguous()
+        dx = None
+        pgrads = []
+        nblk = int(L.neox_norm_bwd_blocks(rows))
+        for i, (kind, eps) in enumerate(ctx.specs):
+            w, b = ctx.params[2 * i], ctx.params[2 * i + 1]
+            g = grads[i]
+            if g is None:
+                pgrads += [None, None]
+                continue
+            g2 = g.reshape(rows, cols)
+            if not g2.is_contiguous():
+                g2 = g2.contiguous()
+            if dx is None:
+                dx = torch.empty_like(x2)
+            ws = workspace(2 * nblk * cols * 4, x2.device, "ln_bwd")
+            d0 = torch.empty(cols, dtype=torch.float32, device=x2.device)
+            d1 = torch.empty(cols, dtype=torch.float32, device=x2.device)
+            if kind == "ln":
+                rc = L.neox_layernorm_bwd_add(native.ptr(g2), native.ptr(x2), native.ptr(w), native.ptr(stats[2 * i]),
+                                              native.ptr(stats[2 * i + 1]), native.ptr(dx), native.ptr(d0),
+                                              native.ptr(d1), native.ptr(ws), rows, cols, _DT[x2.dtype],
+                                              native.ptr(acc), _s())
+            else:
+                rc = L.neox_rmsnorm_bwd_add(native.ptr(g2), native.ptr(x2), native.ptr(w), native.ptr(stats[2 * i + 1]),
+                                            native.ptr(dx), native.ptr(d0), native.ptr(d1), native.ptr(ws), rows, cols,
+                                            ctypes.c_float(eps), _DT[x2.dtype], native.ptr(acc), _s())
+            native.check(rc, "norm backward")
+            acc = dx
+            pgrads.append(_param_grad(w, d0) if ctx.needs_input_grad[2 + 2 * i] else None)
+            pgrads.append(_param_grad(b, d1) if b is not None and ctx.needs_input_grad[3 + 2 * i] else None)
+        gx = acc.reshape(ctx.shape) if acc is not None else None
+        return (gx, None, *pgrads)
+
+
+def norm_fan_out(x, norms):
+    """``(norm_1(x), ..., norm_n(x), x_for_the_residual)`` for ``norms`` = modules with ``weight``/``bias``/``eps``
+    (LayerNorm) or ``scale``/``offset``/``eps`` (RMSNorm).  One fused autograd node on a GPU (see
+    ``_NormFanOutFn``); plain calls otherwise."""
+    specs, params = [], []
+    ok = _k(x) and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad
+    for m in norms:
+        if hasattr(m, "scale") and not hasattr(m, "weight"):
+            kind, w, b = "rms", m.scale, getattr(m, "offset", None)
+            ok = ok and not (0.0 <= getattr(m, "p", -1.0) <= 1.0)
+        elif hasattr(m, "weight") and hasattr(m, "eps") and hasattr(m, "dim"):
+            kind, w, b = "ln", m.weight, m.bias
+        else:
+            ok = False
+            break
+        ok = ok and w.dtype == x.dtype and (b is None or b.dtype == x.dtype)
+        specs.append((kind, float(m.eps)))
+        params += [w, b]
+    if not ok:
+        return (*[m(x) for m in norms], x)
+    return _NormFanOutFn.apply(x, tuple(specs), *params)
+
 # ------------------------------------------------------------------------------------ bias gradient
 def bias_grad(g2, bias=None):
     """Column sums of ``g2`` ([rows, cols]): the gradient of a bias added to every row.  On a GPU one two-pass kernel

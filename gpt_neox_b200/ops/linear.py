@@ -83,6 +83,9 @@ class _LinearFn(torch.autograd.Function):
         ctx.act = act
         ctx.split_pre = split_pre
         ctx.x_shape = x.shape
+        # the pre-activation output is not differentiable: without this autograd would hand backward a zero tensor
+        # of its size (a full pass over [tokens, 4h]) for it
+        ctx.set_materialize_grads(False)
         N, K = weight.shape
         x2 = x.reshape(-1, K)
         if not x2.is_contiguous():
@@ -124,6 +127,8 @@ class _LinearFn(torch.autograd.Function):
     def backward(ctx, g, g_pre=None):
         x2, weight, pre, aux2 = ctx.saved_tensors
         N, K = weight.shape
+        if g is None:
+            return None, None, None, None, None, None, None
         g_in = g
         g2 = g.reshape(-1, N)
         if not g2.is_contiguous():

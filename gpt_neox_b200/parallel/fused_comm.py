@@ -348,6 +348,7 @@ class _ColumnSP(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, bias, act, split_pre=False):
+        ctx.set_materialize_grads(False)    # no zero tensor for the non-differentiable pre-activation output
         ws = workspace()
         N, K = weight.shape
         x2 = x.reshape(-1, K)
@@ -377,6 +378,8 @@ class _ColumnSP(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g, g_pre=None):
+        if g is None:
+            return None, None, None, None, None
         ws = workspace()
         x2, weight, pre = ctx.saved_tensors
         N, K = weight.shape
@@ -514,6 +517,7 @@ class _ColumnAR(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, bias, act, split_pre=False):
+        ctx.set_materialize_grads(False)    # no zero tensor for the non-differentiable pre-activation output
         N, K = weight.shape
         x2 = x.reshape(-1, K)
         if not x2.is_contiguous():
@@ -534,6 +538,8 @@ class _ColumnAR(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g, g_pre=None):
+        if g is None:
+            return None, None, None, None, None
         ws = workspace()
         x2, weight, pre = ctx.saved_tensors
         N, K = weight.shape

@@ -872,3 +872,59 @@ def test_bias_grad_column_sum_kernel(rows, cols, dtype):
     # a strided view (the rows of a wider matrix)
     wide = torch.randn(rows, cols * 2, device=DEV).to(dtype)
     _close(OF.bias_grad(wide[:, :cols]), wide[:, :cols].float().sum(0), 0.05 * math.sqrt(rows) / 8, rtol=1e-2)
+
+
+@pytest.mark.parametrize("kinds", [("ln", "ln"), ("ln",), ("rms",), ("rms", "ln")])
+def test_norm_fan_out_adds_all_gradient_contributions_in_the_kernels(kinds):
+    """Block head ``x -> (norms(x)..., x)``: outputs equal the separate norm kernels bit for bit; the input gradient is
+    the sum of the residual gradient and every norm's gradient (fp32 oracle); parameter gradients as usual."""
+    from gpt_neox_b200.models.norms import LayerNorm, RMSNorm
+    torch.manual_seed(4)
+    rows, b, h = 192, 3, 1024
+    mods = [LayerNorm(h, eps=1e-5, device=DEV, dtype=torch.bfloat16) if k == "ln"
+            else RMSNorm(h, eps=1e-6, device=DEV, dtype=torch.bfloat16) for k in kinds]
+    for m in mods:
+        for p in m.parameters():
+            p.data.add_(torch.randn_like(p) * 0.2)
+    x = torch.randn(rows, b, h, device=DEV).to(torch.bfloat16)
+    gs = [torch.randn(rows, b, h, device=DEV).to(torch.bfloat16) for _ in range(len(mods) + 1)]
+    xa = x.clone().requires_grad_(True)
+    outs = OF.norm_fan_out(xa, mods)
+    assert len(outs) == len(mods) + 1 and outs[-1].data_ptr() == xa.data_ptr()
+    sep = [m(x) for m in mods]
+    for o, s in zip(outs, sep):
+        assert torch.equal(o, s)
+    torch.autograd.backward(list(outs), gs)
+    got = {id(p): p.grad.clone() for m in mods for p in m.parameters()}
+    for m in mods:
+        m.zero_grad()
+    # fp32 oracle through the modules' eager math
+    xb = x.float().requires_grad_(True)
+    ref_outs = []
+    for m, k in zip(mods, kinds):
+        if k == "ln":
+            ref_outs.append(torch.nn.functional.layer_norm(xb, (h,), m.weight.float(), m.bias.float(), m.eps))
+        else:
+            ref_outs.append(xb / (xb.norm(2, dim=-1, keepdim=True) * h ** -0.5 + m.eps) * m.scale.float())
+    ws = [p for m in mods for p in m.parameters()]
+    wf = [p.detach().float().requires_grad_(True) for p in ws]
+    ref_outs = []
+    it = iter(wf)
+    for m, k in zip(mods, kinds):
+        if k == "ln":
+            w_, b_ = next(it), next(it)
+            ref_outs.append(torch.nn.functional.layer_norm(xb, (h,), w_, b_, m.eps))
+        else:
+            s_ = next(it)
+            ref_outs.append(xb / (xb.norm(2, dim=-1, keepdim=True) * h ** -0.5 + m.eps) * s_)
+    torch.autograd.backward(ref_outs + [xb * 1.0], [g.float() for g in gs])
+    _close(xa.grad, xb.grad, 0.06, rtol=2e-2)
+    for p, f in zip(ws, wf):
+        _close(got[id(p)], f.grad, 0.02 * math.sqrt(rows * b), rtol=3e-2)
+    # only some outputs used: the others contribute nothing (no zero tensors are materialised for them)
+    xc = x.clone().requires_grad_(True)
+    outs = OF.norm_fan_out(xc, mods)
+    outs[0].backward(gs[0])
+    xd = x.clone().requires_grad_(True)
+    mods[0](xd).backward(gs[0])
+    _close(xc.grad, xd.grad, 1e-6, rtol=0)
