@@ -14,6 +14,7 @@ Reference call sites these replace: apex/TorchScript fused ops in ``megatron/mod
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 
 import torch
@@ -480,7 +481,8 @@ def norm_fan_out(x, norms):
     (LayerNorm) or ``scale``/``offset``/``eps`` (RMSNorm).  One fused autograd node on a GPU (see
     ``_NormFanOutFn``); plain calls otherwise."""
     specs, params = [], []
-    ok = _k(x) and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad
+    ok = (_k(x) and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad
+          and os.environ.get("NEOX_NORM_FANOUT", "1") != "0")
     for m in norms:
         if hasattr(m, "scale") and not hasattr(m, "weight"):
             kind, w, b = "rms", m.scale, getattr(m, "offset", None)
