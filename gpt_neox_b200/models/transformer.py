@@ -337,10 +337,16 @@ class ParallelSelfAttention(nn.Module):
                 k = OF.rope(k, cos_q, sin_q)
             else:
                 q, k = apply_rotary_pos_emb(q, k, cos, sin, offset=offset)
-        if layer_past is not None and layer_past[0].numel() > 0:
-            k = torch.cat((layer_past[0].type_as(k), k), dim=0)
-            v = torch.cat((layer_past[1].type_as(v), v), dim=0)
-        present = torch.stack((k, v)) if self.use_cache else None
+        if self.use_cache:
+            # keys and values live in one buffer with spare rows behind the filled part: a decoding step writes its
+            # new rows in place and hands out views, instead of re-copying the whole cache with cat + stack
+            present = _extend_kv_cache(layer_past, k, v)
+            k, v = present[0], present[1]
+        else:
+            if layer_past is not None and layer_past[0].numel() > 0:
+                k = torch.cat((layer_past[0].type_as(k), k), dim=0)
+                v = torch.cat((layer_past[1].type_as(v), v), dim=0)
+            present = None
 
         need_scores = self.rpe is not None or self.sparse or (self.dropout_p > 0 and self.training)
         if need_scores:
@@ -355,6 +361,33 @@ class ParallelSelfAttention(nn.Module):
         if self.use_cache:
             out = [out, present]
         return out, bias
+
+
+def _extend_kv_cache(layer_past, k, v):
+    """``[2, n + s, b, heads, d]`` view holding the cached keys / values followed by the new ones.  The view carries
+    its backing buffer (``_kv_buf``, capacity grown geometrically), so the next step appends in place when there is
+    room: O(s) per step instead of the O(n) of concatenating (reference: ``torch.cat`` + ``torch.stack`` per step,
+    ``megatron/model/transformer.py:1003-1012``)."""
+    s = k.shape[0]
+    n = layer_past[0].shape[0] if layer_past is not None and layer_past[0].numel() > 0 else 0
+    buf = getattr(layer_past, "_kv_buf", None) if n else None
+    # ``_filled``: rows written so far; a second consumer continuing from the same past (branching) must not overwrite
+    # what the first one appended, so it gets a buffer of its own
+    usable = (buf is not None and buf.dtype == k.dtype and buf.shape[2:] == k.shape[1:] and buf.shape[1] >= n + s
+              and buf.device == k.device and getattr(buf, "_filled", -1) == n)
+    if not usable:
+        cap = max(2 * (n + s), 64)
+        new = torch.empty((2, cap) + tuple(k.shape[1:]), dtype=k.dtype, device=k.device)
+        if n:
+            new[0, :n].copy_(layer_past[0])
+            new[1, :n].copy_(layer_past[1])
+        buf = new
+    buf[0, n:n + s].copy_(k)
+    buf[1, n:n + s].copy_(v)
+    buf._filled = n + s
+    present = buf[:, :n + s]
+    present._kv_buf = buf
+    return present
 
 
 class ParallelTransformerLayer(nn.Module):

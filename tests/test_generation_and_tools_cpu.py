@@ -212,3 +212,32 @@ def test_raw_llama_conversion_layout(tmp_path):
         assert torch.equal(sd[hp + "mlp.down_proj.weight"], full[p + "feed_forward.w2.weight"])
     assert torch.equal(sd["model.embed_tokens.weight"], full["tok_embeddings.weight"])
     assert torch.equal(sd["lm_head.weight"], full["output.weight"])
+
+
+def test_kv_cache_appends_in_place_and_survives_branching():
+    from gpt_neox_b200.models.transformer import _extend_kv_cache
+    torch.manual_seed(0)
+    mk = lambda s: (torch.randn(s, 2, 3, 4), torch.randn(s, 2, 3, 4))
+    k0, v0 = mk(5)
+    p0 = _extend_kv_cache(None, k0, v0)
+    assert p0.shape == (2, 5, 2, 3, 4) and torch.equal(p0[0], k0) and torch.equal(p0[1], v0)
+    k1, v1 = mk(1)
+    p1 = _extend_kv_cache(p0, k1, v1)
+    assert p1._kv_buf is p0._kv_buf                                  # appended in place
+    assert torch.equal(p1[0], torch.cat([k0, k1])) and torch.equal(p1[1], torch.cat([v0, v1]))
+    # a second continuation from the same past gets its own buffer and leaves the first one intact
+    k2, v2 = mk(1)
+    p2 = _extend_kv_cache(p0, k2, v2)
+    assert p2._kv_buf is not p1._kv_buf
+    assert torch.equal(p1[0], torch.cat([k0, k1])) and torch.equal(p2[0], torch.cat([k0, k2]))
+    # growth beyond the capacity re-allocates and keeps the contents
+    p = p1
+    ks = [k0, k1]
+    for _ in range(200):
+        kn, vn = mk(1)
+        ks.append(kn)
+        p = _extend_kv_cache(p, kn, vn)
+    assert torch.equal(p[0], torch.cat(ks)) and p._kv_buf.shape[1] >= p.shape[1]
+    # a plain tensor pair (no buffer attached) is accepted as the past
+    q = _extend_kv_cache(torch.stack((k0, v0)), k1, v1)
+    assert torch.equal(q[0], torch.cat([k0, k1]))
