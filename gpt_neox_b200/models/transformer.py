@@ -363,6 +363,19 @@ class ParallelSelfAttention(nn.Module):
         return out, bias
 
 
+_ZEROS = {}
+
+
+def _zero_scalar(device, dtype):
+    """A shared 0-d zero on ``device`` (read-only by convention): the auxiliary loss of a layer without experts.
+    Creating it per call would cost a host-to-device copy per layer and micro-batch."""
+    key = (device, dtype)
+    z = _ZEROS.get(key)
+    if z is None:
+        z = _ZEROS[key] = torch.zeros((), device=device, dtype=dtype)
+    return z
+
+
 def _extend_kv_cache(layer_past, k, v):
     """``[2, n + s, b, heads, d]`` view holding the cached keys / values followed by the new ones.  The view carries
     its backing buffer (``_kv_buf``, capacity grown geometrically), so the next step appends in place when there is
@@ -439,7 +452,7 @@ class ParallelTransformerLayer(nn.Module):
         layer_past = layer_past if layer_past is not None else self.layer_past
         p = self.hidden_dropout
         fuse = (p == 0.0 or not self.training)
-        moe_loss = torch.tensor(0.0, device=x.device, dtype=x.dtype)
+        moe_loss = _zero_scalar(x.device, x.dtype).view(())     # a fresh tensor object over the shared zero
         if self.gpt_j_residual:
             # both norms and the residual connection read x: one autograd node, whose backward adds the three
             # gradient contributions inside the norm-backward kernels (ops/functional.py::norm_fan_out)
