@@ -25,14 +25,14 @@ def ensure_reference_tree():
     """baseline/_ref is a plain copy of the reference tree (it is a script tree: pip cannot install it)."""
     if os.path.isdir(os.path.join(REF, "megatron")):
         return None
-    src = "/root/reference"
-    if os.path.isdir(os.path.join(src, "megatron")):
+    src = os.environ.get("NEOX_REFERENCE_SRC", "")          # where a checkout of the reference can be copied from
+    if src and os.path.isdir(os.path.join(src, "megatron")):
         try:
             shutil.copytree(src, REF, dirs_exist_ok=True)
             return None
         except Exception as exc:  # pragma: no cover
             return f"copying the reference tree to baseline/_ref failed ({type(exc).__name__}: {exc})"
-    return "baseline/_ref is absent and the reference tree is not mounted on this machine"
+    return "baseline/_ref is absent (set NEOX_REFERENCE_SRC to a checkout of the reference to have it copied)"
 
 
 def flops_per_iteration(batch, seq, layers, hidden, vocab, c):
