@@ -96,6 +96,11 @@ class NeoXEngine:
                 hasattr(self.optimizer, "arm_overlap"):
             self.optimizer.arm_overlap()     # last micro-batch: reduce each bucket as soon as its gradients exist
         scaled.backward(retain_graph=retain_graph)
+        if self.optimizer is not None and getattr(self.optimizer, "partition_grads", False):
+            # ZeRO stage 2: gradients leave their transient full-size buffers after every micro-batch, so the
+            # fix-ups that rewrite them (sequence-parallel norm gradients) run now, not at the step
+            self._pre_step_grad_sync()
+            self.optimizer.end_micro_batch()
         return loss
 
     def _pre_step_grad_sync(self):
@@ -113,7 +118,8 @@ class NeoXEngine:
     def _take_step(self):
         self._pre_step_grad_sync()
         if self.store_gradients:
-            self.stored_gradients = [p.main_grad.detach().clone() for b in self.optimizer.buckets for p in b.params]
+            self.stored_gradients = [p.main_grad.detach().clone() for b in self.optimizer.buckets for p in b.params
+                                     if getattr(p, "main_grad", None) is not None]
         ok = self.optimizer.step(grad_divisor=float(self.gas * self.dp_world_size))
         fp8.invalidate_weight_cache()          # the fused optimizer rewrites parameters through raw pointers
         if ok:
@@ -277,6 +283,11 @@ class _P2P:
 class PipelineEngine(NeoXEngine):
     def __init__(self, model, optimizer, lr_scheduler, neox_args, sp_sync_params=None):
         super().__init__(model, optimizer, lr_scheduler, neox_args, sp_sync_params)
+        if optimizer is not None and getattr(optimizer, "partition_grads", False):
+            # as in the reference's engine: gradients of several micro-batches are in flight on a pipeline stage and
+            # tied weights are summed after the last one, which a per-micro-batch gradient partition cannot serve
+            raise ValueError("ZeRO stage 2 (gradient partitioning) cannot be combined with pipeline parallelism; "
+                             "use zero_optimization.stage 1")
         self.is_pipe_parallel = True
         self.num_stages = mpu.get_pipe_parallel_world_size()
         self.stage_id = mpu.get_pipe_parallel_rank()

@@ -22,6 +22,13 @@ One step at a gradient-accumulation boundary:
    copy straight into ``flat_param``;
 4. ZeRO >= 1 all-gathers ``flat_param`` in place.
 
+ZeRO stage 2 (``zero_optimization.stage: 2``) additionally partitions the gradients: ``flat_grad`` becomes a
+transient per-bucket buffer that is allocated when a micro-batch's first gradient for the bucket appears
+(``ops.linear.main_grad_of``), reduce-scattered into a persistent fp32 accumulator of shard size as soon as all of the
+bucket's gradients of that micro-batch exist, and released -- so between buckets only ``1 / dp`` of the gradients
+is resident, at the price of one reduce-scatter per micro-batch instead of one per step (DeepSpeed's trade as well;
+like there it excludes pipeline parallelism).  Stage 3 (parameter partitioning) is not provided and runs as stage 2.
+
 A bucket is keyed by (optimizer param group, communication group) so MoE expert parameters, which
 are data-parallel only over the expert-data-parallel group, live in their own bucket.
 """
@@ -102,7 +109,7 @@ class Bucket:
     """One contiguous (param, grad, master-shard) triple."""
 
     def __init__(self, params, group_opts, comm_group, comm_world, comm_rank, model_dtype, device, sharded,
-                 grad_dtype=torch.float32):
+                 grad_dtype=torch.float32, partition_grads=False):
         # tensor-parallel-replicated parameters first: their squared norm is counted on TP rank 0 only
         rep = [p for p in params if not getattr(p, "model_parallel", False)]
         shd = [p for p in params if getattr(p, "model_parallel", False)]
@@ -110,6 +117,10 @@ class Bucket:
         self.opts = group_opts
         self.comm_group, self.world, self.rank = comm_group, comm_world, comm_rank
         self.sharded = sharded and comm_world > 1
+        # ZeRO stage 2: the full-size gradient buffer is transient -- allocated when the first gradient of a
+        # micro-batch arrives, reduce-scattered into the persistent fp32 shard accumulator as soon as the bucket is
+        # complete, and released; between those moments only 1 / world of the gradients is held
+        self.partition_grads = bool(partition_grads) and self.sharded
         offs, off = [], 0
         for p in self.params:
             offs.append(off)
@@ -120,7 +131,8 @@ class Bucket:
         self.numel = off
         self.padded = _pad_to(max(off, 1), _ALIGN * max(comm_world, 1))
         self.offsets = offs
-        self.peer = (self.sharded and torch.device(device).type == "cuda" and comm_world <= 8
+        self.peer = (self.sharded and not self.partition_grads and torch.device(device).type == "cuda"
+                     and comm_world <= 8
                      and grad_dtype == torch.float32
                      and model_dtype in (torch.bfloat16, torch.float16, torch.float32)
                      and peer_traffic_enabled(comm_group))
@@ -140,12 +152,13 @@ class Bucket:
             self._gather_epoch = 0          # epoch of a gather that has not been waited for yet
         else:
             self.flat_param = torch.zeros(self.padded, dtype=model_dtype, device=device)
-            self.flat_grad = torch.zeros(self.padded, dtype=grad_dtype, device=device)
+            self.flat_grad = None if self.partition_grads else torch.zeros(self.padded, dtype=grad_dtype, device=device)
+        self.device, self.grad_dtype = device, grad_dtype
         for p, o in zip(self.params, offs):
             view = self.flat_param[o:o + p.numel()].view(p.shape)
             view.copy_(p.data)
             p.data = view
-            p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
+            p.main_grad = None if self.partition_grads else self.flat_grad[o:o + p.numel()].view(p.shape)
             p.grad_in_main = False
         shard = self.padded // self.world if self.sharded else self.padded
         self.lo = shard * self.rank if self.sharded else 0
@@ -156,7 +169,8 @@ class Bucket:
         else:
             self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi])   # a view: updated in place
         self.master.model_out = self.flat_param[self.lo:self.hi] if self.mixed else None
-        self.grad_shard = self.flat_grad[self.lo:self.hi] if grad_dtype == torch.float32 else None
+        self.grad_acc = torch.zeros(shard, dtype=torch.float32, device=device) if self.partition_grads else None
+        self._partition_stream = None
         # overlap bookkeeping (see FlatMixedPrecisionOptimizer.arm_overlap)
         self.n_expected = len(self.params)
         self.ready = set()             # ids of the parameters whose gradient has been reported this backward
@@ -164,9 +178,56 @@ class Bucket:
         self.pending_reduce = None
         self.pending_gather = None
 
+    # ---- ZeRO stage 2: transient full-size gradients
+    def ensure_grad_buffer(self):
+        """Allocate (zeroed) the full-size gradient buffer of this micro-batch and point ``main_grad`` into it."""
+        if not self.partition_grads or self.flat_grad is not None:
+            return
+        self.flat_grad = torch.zeros(self.padded, dtype=self.grad_dtype, device=self.device)
+        for p, o in zip(self.params, self.offsets):
+            p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
+
+    def reduce_and_release(self, stream=None):
+        """Reduce-scatter this micro-batch's gradients into the shard accumulator and give the buffer back."""
+        if not self.partition_grads or self.flat_grad is None:
+            return
+        flat = self.flat_grad
+        self.flat_grad = None
+        for p in self.params:
+            p.main_grad = None
+            p.grad_in_main = False
+        self.ready = set()
+        if stream is not None and flat.is_cuda:
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                tmp = torch.empty_like(self.grad_acc)
+                dist.reduce_scatter_tensor(tmp, flat, group=self.comm_group)
+                self.grad_acc.add_(tmp)
+            flat.record_stream(stream)         # the allocator reuses the buffer only after the collective
+            tmp.record_stream(stream)
+            self._partition_stream = stream
+        else:
+            tmp = torch.empty_like(self.grad_acc)
+            dist.reduce_scatter_tensor(tmp, flat, group=self.comm_group)
+            self.grad_acc.add_(tmp)
+
+    def grad_of_shard(self):
+        """This rank's reduced fp32 gradient shard (view of the flat buffer, or the stage-2 accumulator)."""
+        if self.partition_grads:
+            if self._partition_stream is not None:
+                torch.cuda.current_stream().wait_stream(self._partition_stream)
+                self._partition_stream = None
+            return self.grad_acc
+        return self.flat_grad[self.lo:self.hi]
+
     # ---- gradients
     def reduce_grads(self, average_factor):
         """Sum gradients over the communication group (and divide by ``average_factor``)."""
+        if self.partition_grads:
+            self.reduce_and_release()
+            if average_factor != 1.0:
+                self.grad_acc.div_(average_factor)
+            return
         if self.world > 1:
             if self.peer:
                 self._peer_reduce(1.0 / average_factor)
@@ -182,6 +243,9 @@ class Bucket:
         """Start the gradient reduction of this bucket on ``stream`` (ordered after everything launched so far on the
         current stream); ``finish_reduce`` makes the current stream wait for it."""
         if self.world <= 1 or self.pending_reduce is not None:
+            return
+        if self.partition_grads:
+            self.reduce_and_release(stream)
             return
         if stream is not None:
             stream.wait_stream(torch.cuda.current_stream())
@@ -205,6 +269,9 @@ class Bucket:
 
     def finish_reduce(self):
         """Wait for an early reduction, or do it now if none was started.  Returns True if it had been overlapped."""
+        if self.partition_grads:
+            self.reduce_and_release()
+            return False
         if self.pending_reduce is None:
             self.reduce_grads(1.0)
             return False
@@ -248,7 +315,7 @@ class Bucket:
     def shard_sq_norm(self, tp_rank):
         """Squared L2 norm of this rank's gradient shard, counting TP-replicated entries on TP rank 0 only.
         On CUDA one reduction kernel per segment accumulates into a scalar (no temporaries)."""
-        g = self.flat_grad[self.lo:self.hi]
+        g = self.grad_of_shard()
         rep_hi = min(max(self.rep_end, self.lo), self.hi) - self.lo
         segs = []
         if rep_hi > 0 and tp_rank == 0:
@@ -310,6 +377,13 @@ class Bucket:
             rc = _lib().neox_wait_flags_long(self._pad.word(_DONE), ctypes.c_uint(self.epoch), self.world, self.rank,
                                              _WAIT_ROUNDS, _cur_stream())
             _check(rc, "neox_wait_flags_long")
+        if self.partition_grads:
+            self.grad_of_shard().zero_()
+            self.flat_grad = None
+            self.ready = set()
+            for p in self.params:
+                p.grad, p.main_grad, p.grad_in_main = None, None, False
+            return
         self.flat_grad.zero_()
         for p in self.params:
             p.grad = None
@@ -359,7 +433,7 @@ class FlatMixedPrecisionOptimizer:
                     continue
                 dev = device or plist[0].device
                 chunks = [plist]
-                if self.overlap_comm and cw > 1 and reduce_bucket_size:
+                if (self.overlap_comm or self.zero_stage >= 2) and cw > 1 and reduce_bucket_size:
                     # gradients that are rewritten after backward (norms under sequence parallelism, weights tied
                     # across layers or pipeline stages) get a bucket of their own that is reduced in step()
                     late = [p for p in plist if getattr(p, "late_grad_sync", False)]
@@ -375,7 +449,8 @@ class FlatMixedPrecisionOptimizer:
                     if cur:
                         chunks.append(cur)
                 for chunk in chunks:
-                    b = Bucket(chunk, opts, cg, cw, cr, model_dtype, dev, sharded=self.zero_stage >= 1)
+                    b = Bucket(chunk, opts, cg, cw, cr, model_dtype, dev, sharded=self.zero_stage >= 1,
+                               partition_grads=self.zero_stage >= 2)
                     self.buckets.append(b)
                     inner_groups.append({"params": [b.master], **opts})
         self.optimizer = inner_cls(inner_groups, **inner_defaults)
@@ -400,6 +475,7 @@ class FlatMixedPrecisionOptimizer:
         def make(p, bucket):
             def hook(param):
                 if param.grad is not None:
+                    bucket.ensure_grad_buffer()
                     param.main_grad.add_(param.grad.to(param.main_grad.dtype))
                     param.grad = None
                     self._on_grad_ready(bucket, param)
@@ -430,11 +506,30 @@ class FlatMixedPrecisionOptimizer:
     def _on_grad_ready(self, bucket, param):
         """A parameter may report more than once per backward (a weight with several uses): readiness is counted
         per distinct parameter, and a bucket holding a gradient that is still rewritten after backward never fires."""
+        if bucket.partition_grads:
+            # stage 2: every micro-batch -- the buffer goes back as soon as the bucket's gradients are complete
+            if bucket.never_early:
+                return
+            bucket.ready.add(id(param))
+            if len(bucket.ready) == bucket.n_expected:
+                bucket.reduce_and_release(self._stream() if self.overlap_comm else None)
+            return
         if not self._armed or bucket.world <= 1 or bucket.never_early or self._local_grads():
             return
         bucket.ready.add(id(param))
         if len(bucket.ready) == bucket.n_expected:
             bucket.reduce_grads_async(self._stream())
+
+    @property
+    def partition_grads(self) -> bool:
+        return any(b.partition_grads for b in self.buckets)
+
+    def end_micro_batch(self):
+        """Stage 2, after the backward pass of every micro-batch (and after the gradient fix-ups that follow it):
+        reduce and release whatever is still held -- buckets with late-synchronised or unused parameters."""
+        for b in self.buckets:
+            if b.partition_grads:
+                b.reduce_and_release(self._stream() if self.overlap_comm else None)
 
     def install_param_wait_hooks(self, module):
         """Forward pre-hooks on the direct children of ``module`` (the layers): a layer waits for the all-gather of
@@ -478,7 +573,7 @@ class FlatMixedPrecisionOptimizer:
 
     def global_grad_norm(self, local_grads=False):
         tp_rank = mpu.get_model_parallel_rank()
-        dev = self.buckets[0].flat_grad.device if self.buckets else torch.device("cpu")
+        dev = self.buckets[0].flat_param.device if self.buckets else torch.device("cpu")
         total = torch.zeros((), dtype=torch.float32, device=dev)
         expert_parallel = mpu.get_expert_parallel_world_size() > 1
         across_dp = torch.zeros((), dtype=torch.float32, device=dev)   # part that differs between DP ranks
@@ -546,7 +641,7 @@ class FlatMixedPrecisionOptimizer:
                 combined = scale * clip
         inv = 1.0 / combined
         for b, g in zip(self.buckets, self.optimizer.param_groups):
-            b.master.grad = b.flat_grad[b.lo:b.hi]
+            b.master.grad = b.grad_of_shard()
             g["grad_scale"] = inv
         if getattr(self.optimizer, "supports_grad_scale", False):
             self.optimizer.step()

@@ -37,6 +37,7 @@ from ..ops.linear import linear as fused_linear
 from ..parallel import mappings as M
 from ..parallel import moe_comm, mpu
 from ..parallel.rng import get_cuda_rng_tracker
+from ..ops.linear import main_grad_of
 
 
 class _AllToAll(torch.autograd.Function):
@@ -94,7 +95,7 @@ class _ExpertOutCombine(torch.autograd.Function):
         g_src = moe_comm.comm_for(ctx.grp).exchange(g.contiguous(), ctx.matrix)      # back on the expert rank
         g_e = g_src.index_select(0, perm_t)
         d_hdn = torch.empty_like(hdn)
-        mg = getattr(w2, "main_grad", None)
+        mg = main_grad_of(w2)
         gw = None if mg is not None else torch.zeros_like(w2)
         for ei, (a, b) in enumerate(ctx.bounds):
             if b <= a:

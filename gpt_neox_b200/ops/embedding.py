@@ -14,6 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from . import native
+from .linear import main_grad_of
 
 
 def embedding_ref(ids, weight, v0=0):
@@ -43,7 +44,7 @@ class _EmbedFn(torch.autograd.Function):
         weight, v0 = ctx.weight, ctx.v0
         rows, h = weight.shape
         g = g.contiguous()
-        mg = getattr(weight, "main_grad", None)
+        mg = main_grad_of(weight)
         target = mg if mg is not None else torch.zeros(rows, h, dtype=torch.float32, device=g.device)
         rc = native.lib().neox_embedding_bwd(native.ptr(ids_c), native.ptr(g), native.ptr(target),
                                              ctypes.c_longlong(ids_c.numel()), int(h), ctypes.c_longlong(v0),
@@ -58,7 +59,7 @@ class _EmbedFn(torch.autograd.Function):
 
 
 def kernel_ok(ids, weight) -> bool:
-    mg = getattr(weight, "main_grad", None)
+    mg = main_grad_of(weight)
     return (weight.is_cuda and native.available() and weight.dtype == torch.bfloat16 and ids.dtype == torch.int64
             and weight.is_contiguous() and weight.shape[1] % 8 == 0
             and (mg is None or (mg.dtype == torch.float32 and mg.is_contiguous())))

@@ -34,6 +34,7 @@ import torch
 
 from . import gemm as G
 from . import flop_count, native
+from .linear import main_grad_of
 
 E4M3_MAX, E5M2_MAX = 448.0, 57344.0
 
@@ -262,7 +263,7 @@ class _Fp8LinearFn(torch.autograd.Function):
             else:
                 gx = gemm_fp8(gq, wq, a_mn=False, b_mn=True).reshape(x_shape)
         if ctx.needs_input_grad[1]:
-            mg = getattr(weight, "main_grad", None)
+            mg = main_grad_of(weight)
             if recipe.fp8_wgrad:
                 xa = Fp8Tensor(xq_q, xq_inv, False)
                 run = lambda **kw: gemm_fp8(gq, xa, a_mn=True, b_mn=True, **kw)

@@ -54,7 +54,8 @@ def _param_grad(param, g32):
     parameter's type."""
     if param is None:
         return None
-    mg = getattr(param, "main_grad", None)
+    from .linear import main_grad_of
+    mg = main_grad_of(param)
     if mg is not None and mg.dtype == torch.float32 and mg.shape == g32.shape:
         mg.add_(g32)
         param.grad_in_main = True
@@ -511,7 +512,8 @@ def bias_grad(g2, bias=None):
         rows = g2.shape[0]
         nblk = L.neox_colsum_blocks(ctypes.c_longlong(rows))
         ws = workspace(nblk * cols * 4, g2.device, "colsum")
-        mg = getattr(bias, "main_grad", None) if bias is not None else None
+        from .linear import main_grad_of
+        mg = main_grad_of(bias) if bias is not None else None
         into_main = mg is not None and mg.dtype == torch.float32 and mg.is_contiguous()
         out = mg if into_main else torch.empty(cols, dtype=g2.dtype, device=g2.device)
         rc = L.neox_colsum(native.ptr(g2), native.ptr(out), native.ptr(ws), ctypes.c_longlong(rows), cols,

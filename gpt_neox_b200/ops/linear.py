@@ -20,6 +20,18 @@ from . import gemm as G
 from . import flop_count, native
 
 
+def main_grad_of(param):
+    """The fp32 gradient accumulator of ``param`` inside the optimizer's flat buffer, or ``None`` when there is no
+    such optimizer.  Under ZeRO stage 2 the buffer is transient: the first request of a micro-batch allocates it."""
+    mg = getattr(param, "main_grad", None)
+    if mg is None:
+        bucket = getattr(param, "_bucket", None)
+        if bucket is not None and bucket.partition_grads:
+            bucket.ensure_grad_buffer()
+            mg = param.main_grad
+    return mg
+
+
 def notify_grad_ready(weight):
     """Tell the optimizer (if it listens) that ``weight.main_grad`` now holds this backward pass' contribution."""
     cb = getattr(weight, "_grad_ready", None)
@@ -145,7 +157,7 @@ class _LinearFn(torch.autograd.Function):
                 else:
                     gx = G.gemm(g2, weight, a_mn=False, b_mn=True).reshape(ctx.x_shape)
             if ctx.needs_input_grad[1]:
-                mg = getattr(weight, "main_grad", None)
+                mg = main_grad_of(weight)
                 if mg is not None:
                     G.gemm(g2, x2, a_mn=True, b_mn=True, out=mg, add=mg)
                     weight.grad_in_main = True
@@ -160,7 +172,7 @@ class _LinearFn(torch.autograd.Function):
                 gx = gx.reshape(ctx.x_shape)
             if ctx.needs_input_grad[1]:
                 gw = g2.t() @ x2
-                mg = getattr(weight, "main_grad", None)
+                mg = main_grad_of(weight)
                 if mg is not None:
                     mg.add_(gw)
                     weight.grad_in_main = True

@@ -21,6 +21,7 @@ import torch.nn.functional as F
 from . import flop_count, native
 from . import gemm as G
 from .functional import _DT, dgelu_mul
+from .linear import main_grad_of
 
 PAD = 64
 
@@ -267,7 +268,7 @@ class _GroupedLinearFn(torch.autograd.Function):
             # the stacked weights [E * N, K] read MN-major: contraction over N, expert e at contraction rows e * N
             _grouped_call(g, w, gx, M, K, N, N, K, K, True, counts, E, 1)
         if ctx.needs_input_grad[1]:
-            mg = getattr(w, "main_grad", None)
+            mg = main_grad_of(w)
             if mg is not None:
                 _grouped_call(g, x_pad, mg.view(E * N, K), N, K, M, N, K, K, True, counts, E, 2, add=mg.view(E * N, K))
                 w.grad_in_main = True

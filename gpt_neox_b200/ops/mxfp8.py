@@ -21,6 +21,7 @@ import torch
 
 from . import gemm as G
 from . import native
+from .linear import main_grad_of
 
 E4M3_MAX, E5M2_MAX = 448.0, 57344.0
 
@@ -247,7 +248,7 @@ class _MXLinearHwFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gx = gemm_mx(gc, _weight_mx(weight, True)).reshape(x_shape)
         if need_w:
-            mg = getattr(weight, "main_grad", None)
+            mg = main_grad_of(weight)
             if fp8_wgrad:
                 run = lambda **kw: gemm_mx(gr, xa, **kw)
             else:
@@ -292,7 +293,7 @@ class _MXLinearFn(torch.autograd.Function):
             # dW = dy^T x: contraction over tokens = first dim of both
             ga = qdq(g2, along_rows=True, e5m2=hybrid) if fp8_wgrad else g2
             xa = qdq(x2, along_rows=True) if fp8_wgrad else x2
-            mg = getattr(weight, "main_grad", None)
+            mg = main_grad_of(weight)
             if mg is not None:
                 G.gemm(ga, xa, a_mn=True, b_mn=True, out=mg, add=mg)
                 weight.grad_in_main = True

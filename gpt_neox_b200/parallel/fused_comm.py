@@ -35,6 +35,7 @@ from ..ops import gemm as G
 from ..ops import native
 from . import comms_logger, mpu
 from . import symm_mem as S
+from ..ops.linear import main_grad_of
 
 _workspaces = {}
 # CTAs of a broadcasting GEMM's grid that copy instead of computing (each moves roughly 40-60 GB/s)
@@ -333,7 +334,7 @@ def eligible(x2, weight, world, sharded_rows=None) -> bool:
 
 def _accumulate_wgrad(weight, fn):
     """Run the weight-gradient GEMM ``fn(out, add)``: into ``weight.main_grad`` when the engine provides it."""
-    mg = getattr(weight, "main_grad", None)
+    mg = main_grad_of(weight)
     if mg is not None:
         fn(mg, mg)
         weight.grad_in_main = True

@@ -277,9 +277,8 @@ def get_model(neox_args, use_cache=False):
         if neox_args.pipe_parallel_size > 1:
             print_rank_0("ZeRO stage 2/3 and pipeline paralleism are not supported simultaneously")
             sys.exit(1)
-        if neox_args.model_parallel_size > 1:
-            print_rank_0("ZeRO stage 2/3 and model paralleism are not currently supported simultaneously")
-            sys.exit(1)
+        # (the reference also refuses model parallelism here, ``megatron/training.py:968-973``; this engine's
+        # gradient partitioning works per data-parallel group and composes with tensor / sequence parallelism)
     model = GPT2ModelPipe(neox_args=neox_args, num_tokentypes=0, parallel_output=neox_args.train_impl != "rm",
                           topology=mpu.get_topology(), use_cache=use_cache)
     if neox_args.soft_prompt_tuning is not None and neox_args.soft_prompt_tuning.get("enabled", False):

@@ -291,3 +291,48 @@ def _onebit_training(rank, world):
 
 def test_onebit_adam_trains_with_compressed_momentum():
     run_distributed(_onebit_training, 2)
+
+
+# ------------------------------------------------------------------ ZeRO stage 2: gradient partitioning
+def _zero2_losses(rank, world, cfg, out):
+    from gpt_neox_b200.training import train_step
+    from gpt_neox_b200.utils import Timers
+    args, model, opt, sched = _setup({**cfg, "global_num_gpus": world})
+    it = _fixed_batches(args)
+    losses = []
+    for _ in range(6):
+        d, _ = train_step(args, Timers(), it, model, opt, sched)
+        losses.append(float(d["lm_loss"]))
+        if opt.zero_stage >= 2:
+            # between steps no full-size gradient buffer is alive, only the fp32 shard accumulators
+            assert opt.partition_grads and all(b.flat_grad is None for b in opt.buckets if b.partition_grads)
+            assert all(b.grad_acc.numel() == b.padded // b.world for b in opt.buckets if b.partition_grads)
+            assert all(getattr(p, "main_grad", 0) is None for b in opt.buckets if b.partition_grads for p in b.params)
+    if rank == 0 and out:
+        with open(out, "w") as fh:
+            json.dump({"losses": losses, "buckets": len(opt.buckets)}, fh)
+
+
+@pytest.mark.parametrize("extra", [
+    {},                                                     # data parallel 2
+    {"model_parallel_size": 2, "sequence_parallel": True},  # tensor parallel 2 x data parallel 2, late norm-gradient sync
+])
+def test_zero2_gradient_partitioning_matches_zero1(tmp_path, extra):
+    world = 4 if extra else 2
+    base = {"gradient_accumulation_steps": 2, "train_micro_batch_size_per_gpu": 2, **extra}
+    a, b = str(tmp_path / "z1.json"), str(tmp_path / "z2.json")
+    run_distributed(_zero2_losses, world, {**base, "zero_optimization": {"stage": 1}}, a)
+    run_distributed(_zero2_losses, world, {**base, "zero_optimization": {"stage": 2, "reduce_bucket_size": 40000}}, b)
+    ra, rb = json.load(open(a)), json.load(open(b))
+    assert rb["buckets"] > ra["buckets"]                    # stage 2 bounds its transient memory by bucketing
+    for x, y in zip(ra["losses"], rb["losses"]):
+        assert abs(x - y) < 2e-4, (ra["losses"], rb["losses"])
+
+
+def _zero2_pp_worker(rank, world):
+    with pytest.raises((SystemExit, ValueError)):
+        _setup({"global_num_gpus": 2, "pipe_parallel_size": 2, "zero_optimization": {"stage": 2}})
+
+
+def test_zero2_refuses_pipeline_parallelism():
+    run_distributed(_zero2_pp_worker, 2)

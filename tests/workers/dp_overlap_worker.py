@@ -4,7 +4,8 @@ Trains the same tiny bf16 model twice from the same seed -- gradient reduce-scat
 bucketed reduce-scatter started from backward hooks on a side stream plus asynchronous parameter all-gather --
 and checks that the losses agree and that buckets were really reduced early; then both once more with the gradient
 reduce-scatter and the parameter all-gather done by the peer-memory kernels instead of NCCL (``NEOX_ZERO_PEER=1``):
-same losses, no bounded wait expired.  Prints ``DP_OVERLAP_OK`` on rank 0.
+same losses, no bounded wait expired; and once with ZeRO stage 2 (gradient partitioning).  Prints ``DP_OVERLAP_OK``
+on rank 0.
 """
 import os
 import sys
@@ -17,13 +18,13 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 sys.path.insert(0, os.path.dirname(HERE))
 
 
-def run(overlap):
+def run(overlap, stage=1):
     from common import make_args
     from gpt_neox_b200.parallel import mpu
     from gpt_neox_b200.training import setup_model_and_optimizer, train_step
     from gpt_neox_b200.utils import Timers
     world = int(os.environ["WORLD_SIZE"])
-    zero = {"stage": 1, "overlap_comm": True, "reduce_bucket_size": 300000} if overlap else {"stage": 1}
+    zero = {"stage": stage, "overlap_comm": True, "reduce_bucket_size": 300000} if overlap else {"stage": stage}
     args = make_args(hidden_size=256, num_attention_heads=4, num_layers=4, seq_length=128, max_position_embeddings=128,
                      precision="bfloat16", global_num_gpus=world, distributed_backend="nccl", zero_optimization=zero,
                      train_micro_batch_size_per_gpu=4, gradient_accumulation_steps=2,
@@ -84,6 +85,15 @@ def main():
     elif dist.get_rank() == 0:
         print(f"ZERO_PEER_OK ms/step overlapped: nccl {ms_over:.2f} peer {ms_peer:.2f}", flush=True)
     ok = ok and ok_peer
+    # ZeRO stage 2 (transient full-size gradient buffers, one reduce-scatter per micro-batch), with the reductions
+    # on the side stream: same losses, and no full-size gradient buffer left between steps
+    z2, _, _ = run(True, stage=2)
+    ok_z2 = all(abs(a - b) < 2e-2 for a, b in zip(plain, z2))
+    if not ok_z2:
+        print(f"[rank {dist.get_rank()}] stage 2: plain {plain} stage2 {z2}", flush=True)
+    elif dist.get_rank() == 0:
+        print(f"ZERO2_OK ms/step {run.ms:.2f}", flush=True)
+    ok = ok and ok_z2
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if dist.get_rank() == 0 and flag.item() == 1:
