@@ -150,7 +150,19 @@ def _is_pipe_module(module):
     return isinstance(module, PipelineModule)
 
 
+def _params_resident(engine, write_back=False):
+    """Under ZeRO stage 3 the module's parameters exist in full only inside this context."""
+    import contextlib
+    part = getattr(engine.optimizer, "param_partitioner", None) if engine.optimizer is not None else None
+    return part.all_resident(write_back=write_back) if part is not None else contextlib.nullcontext()
+
+
 def engine_save_checkpoint(engine, save_dir, tag, client_state):
+    with _params_resident(engine):
+        return _engine_save_checkpoint(engine, save_dir, tag, client_state)
+
+
+def _engine_save_checkpoint(engine, save_dir, tag, client_state):
     tag = tag or get_checkpoint_tag(engine.global_steps)
     d = os.path.join(save_dir, tag)
     os.makedirs(d, exist_ok=True)
@@ -260,6 +272,13 @@ def _all_ranks_ok(ok: bool) -> bool:
 
 
 def _load_tag(engine, load_dir, tag, load_optimizer_states, load_lr_scheduler_states, load_module_only,
+              load_module_strict):
+    with _params_resident(engine):
+        return _load_tag_impl(engine, load_dir, tag, load_optimizer_states, load_lr_scheduler_states,
+                              load_module_only, load_module_strict)
+
+
+def _load_tag_impl(engine, load_dir, tag, load_optimizer_states, load_lr_scheduler_states, load_module_only,
               load_module_strict):
     d = os.path.join(load_dir, tag)
     tp = mpu.get_model_parallel_rank()

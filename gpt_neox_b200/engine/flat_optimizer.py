@@ -27,7 +27,7 @@ transient per-bucket buffer that is allocated when a micro-batch's first gradien
 (``ops.linear.main_grad_of``), reduce-scattered into a persistent fp32 accumulator of shard size as soon as all of the
 bucket's gradients of that micro-batch exist, and released -- so between buckets only ``1 / dp`` of the gradients
 is resident, at the price of one reduce-scatter per micro-batch instead of one per step (DeepSpeed's trade as well;
-like there it excludes pipeline parallelism).  Stage 3 (parameter partitioning) is not provided and runs as stage 2.
+like there it excludes pipeline parallelism).  Stage 3 additionally partitions the parameters (``engine/zero3.py``).
 
 A bucket is keyed by (optimizer param group, communication group) so MoE expert parameters, which
 are data-parallel only over the expert-data-parallel group, live in their own bucket.
@@ -170,6 +170,8 @@ class Bucket:
             self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi])   # a view: updated in place
         self.master.model_out = self.flat_param[self.lo:self.hi] if self.mixed else None
         self.grad_acc = torch.zeros(shard, dtype=torch.float32, device=device) if self.partition_grads else None
+        self.partition_params = False      # ZeRO stage 3 (engine/zero3.py): flat_param is transient, param_shard persistent
+        self.param_shard = None
         self._partition_stream = None
         # overlap bookkeeping (see FlatMixedPrecisionOptimizer.arm_overlap)
         self.n_expected = len(self.params)
@@ -285,7 +287,7 @@ class Bucket:
 
     def gather_params_async(self, stream):
         """Start the all-gather of the updated parameter shards; ``wait_params`` is called before their first use."""
-        if not self.sharded:
+        if not self.sharded or self.partition_params:
             return
         if stream is None or not self.flat_param.is_cuda:
             self.gather_params()
@@ -335,6 +337,8 @@ class Bucket:
         return total
 
     def gather_params(self):
+        if self.partition_params:
+            return          # stage 3: parameters are gathered per layer, right before use
         if self.peer:
             self._peer_push()
             self.wait_params()
@@ -524,6 +528,15 @@ class FlatMixedPrecisionOptimizer:
     def partition_grads(self) -> bool:
         return any(b.partition_grads for b in self.buckets)
 
+    param_partitioner = None
+
+    def enable_param_partitioning(self, model):
+        """ZeRO stage 3: keep only this rank's shard of every parameter bucket between uses (engine/zero3.py)."""
+        from .zero3 import ParamPartitioner
+        if self.param_partitioner is None and self.partition_grads:
+            self.param_partitioner = ParamPartitioner(self).install(model)
+        return self.param_partitioner
+
     def end_micro_batch(self):
         """Stage 2, after the backward pass of every micro-batch (and after the gradient fix-ups that follow it):
         reduce and release whatever is still held -- buckets with late-synchronised or unused parameters."""
@@ -573,7 +586,7 @@ class FlatMixedPrecisionOptimizer:
 
     def global_grad_norm(self, local_grads=False):
         tp_rank = mpu.get_model_parallel_rank()
-        dev = self.buckets[0].flat_param.device if self.buckets else torch.device("cpu")
+        dev = self.buckets[0].master.device if self.buckets else torch.device("cpu")
         total = torch.zeros((), dtype=torch.float32, device=dev)
         expert_parallel = mpu.get_expert_parallel_world_size() > 1
         across_dp = torch.zeros((), dtype=torch.float32, device=dev)   # part that differs between DP ranks
@@ -652,12 +665,14 @@ class FlatMixedPrecisionOptimizer:
             self.optimizer.step()
         for b in self.buckets:
             if b.mixed and not getattr(self.optimizer, "writes_model_out", False):
-                b.flat_param[b.lo:b.hi].copy_(b.master.data)
+                (b.param_shard if b.partition_params else b.flat_param[b.lo:b.hi]).copy_(b.master.data)
             b.master.grad = None
             if self.overlap_comm:
                 b.gather_params_async(self._stream())
             else:
                 b.gather_params()
+        if self.param_partitioner is not None:
+            self.param_partitioner.release_all()      # what is resident predates this update
         self.zero_grad()
         return True
 
@@ -697,6 +712,13 @@ class FlatMixedPrecisionOptimizer:
         """After loading module weights: re-derive the fp32 master shards from ``flat_param``."""
         self.wait_all_params()
         for b in self.buckets:
+            if b.partition_params:
+                # stage 3: called with the parameters resident (checkpointing wraps the load in all_resident())
+                assert b.flat_param is not None, "refresh_master_from_params under ZeRO stage 3 needs resident parameters"
+                b.param_shard.copy_(b.flat_param[b.lo:b.hi])
+                if b.mixed:
+                    b.master.data.copy_(b.param_shard.float())
+                continue
             if b.mixed:
                 b.master.data.copy_(b.flat_param[b.lo:b.hi].float())
 

@@ -376,6 +376,8 @@ def get_optimizer(model, neox_args, dummy=False):
     if getattr(optimizer, "overlap_comm", False):
         # each layer waits only for the all-gather of its own parameters
         optimizer.install_param_wait_hooks(model)
+    if optimizer.zero_stage >= 3:
+        optimizer.enable_param_partitioning(model)
     return optimizer, groups
 
 

@@ -4,7 +4,7 @@ Trains the same tiny bf16 model twice from the same seed -- gradient reduce-scat
 bucketed reduce-scatter started from backward hooks on a side stream plus asynchronous parameter all-gather --
 and checks that the losses agree and that buckets were really reduced early; then both once more with the gradient
 reduce-scatter and the parameter all-gather done by the peer-memory kernels instead of NCCL (``NEOX_ZERO_PEER=1``):
-same losses, no bounded wait expired; and once with ZeRO stage 2 (gradient partitioning).  Prints ``DP_OVERLAP_OK``
+same losses, no bounded wait expired; and once each with ZeRO stage 2 (gradient partitioning) and stage 3 (parameter partitioning).  Prints ``DP_OVERLAP_OK``
 on rank 0.
 """
 import os
@@ -94,6 +94,14 @@ def main():
     elif dist.get_rank() == 0:
         print(f"ZERO2_OK ms/step {run.ms:.2f}", flush=True)
     ok = ok and ok_z2
+    # ZeRO stage 3: parameters gathered per layer right before use, only shards held between steps
+    z3, _, _ = run(True, stage=3)
+    ok_z3 = all(abs(a - b) < 2e-2 for a, b in zip(plain, z3))
+    if not ok_z3:
+        print(f"[rank {dist.get_rank()}] stage 3: plain {plain} stage3 {z3}", flush=True)
+    elif dist.get_rank() == 0:
+        print(f"ZERO3_OK ms/step {run.ms:.2f}", flush=True)
+    ok = ok and ok_z3
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if dist.get_rank() == 0 and flag.item() == 1:
