@@ -53,7 +53,8 @@ class Autotuner:
         zero = self.args.zero_optimization or {}
         stage = zero.get("stage", 0)
         if stage == "auto" or self.block.get("tune_zero_stage", False):
-            return [0, 1]          # stages 2 and 3 run as stage 1 in this engine
+            # gradient / parameter partitioning (2, 3) is not available under pipeline parallelism
+            return [0, 1] if (self.args.pipe_parallel_size or 0) >= 1 else [0, 1, 2, 3]
         return [int(stage)]
 
     def experiments(self):

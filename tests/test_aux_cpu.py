@@ -328,13 +328,14 @@ def test_autotuner_search_with_a_stand_in_runner(tmp_path):
         return 0
 
     tuner = Autotuner(args, runner=runner)
-    assert tuner.micro_batch_sizes() == [1, 2, 4] and tuner.zero_stages() == [0, 1]
+    assert tuner.micro_batch_sizes() == [1, 2, 4] and tuner.zero_stages() == [0, 1, 2, 3]
     best = tuner.tune()
-    assert [s[:2] for s in seen] == [(0, 1), (0, 2), (0, 4), (1, 1), (1, 2), (1, 4)]
+    # five trials in a row without an improvement (the default patience) end the search one trial early
+    assert [s[:2] for s in seen] == [(z, mb) for z in (0, 1, 2, 3) for mb in (1, 2, 4)][:-1]
     assert all(s[2] == 4 and s[3] is None and s[4] is None for s in seen)
     assert best["zero_stage"] == 1 and best["micro_batch"] == 4 and best["throughput"] == 390.0
     summary = json.load(open(tmp_path / "results" / "summary.json"))
-    assert summary["best"]["name"] == "z1_mbs4" and len(summary["experiments"]) == 6
+    assert summary["best"]["name"] == "z1_mbs4" and len(summary["experiments"]) == 11
     assert "failed (1)" in open(tmp_path / "results" / "summary.txt").read()
     final = tuner.apply_best(best)
     assert final.train_micro_batch_size_per_gpu == 4 and final.zero_optimization["stage"] == 1
