@@ -148,6 +148,38 @@ class NeoXEngine:
 
 
 # ============================================================================================== pipeline
+class _Timeline:
+    """Optional per-stage record of one training batch: CUDA events around every receive-wait and every forward /
+    backward of the 1F1B schedule, written as JSON (``NEOX_PP_TIMELINE=<path prefix>``; the batch recorded is the
+    fourth one executed, i.e. past warm-up).  The time between a ``*_wait`` mark and the following ``*_begin`` mark
+    is how long the compute stream stalled for a transfer: the exposed part of the pipeline communication."""
+
+    def __init__(self, prefix, stage):
+        self.path = f"{prefix}.stage{stage}.json"
+        self.marks = []
+
+    def mark(self, name, micro_batch):
+        if torch.cuda.is_available():
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+        else:
+            import time
+            e = time.perf_counter()
+        self.marks.append((name, micro_batch, e))
+
+    def dump(self):
+        import json
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        base = self.marks[0][2]
+        rows = []
+        for name, mb, e in self.marks:
+            t = base.elapsed_time(e) if not isinstance(e, float) else (e - base) * 1e3
+            rows.append({"event": name, "micro_batch": mb, "ms": round(t, 4)})
+        with open(self.path, "w") as fh:
+            json.dump(rows, fh)
+
+
 class _P2P:
     """Adjacent-stage tensor exchange.
 
@@ -373,6 +405,9 @@ class PipelineEngine(NeoXEngine):
         # workspaces and library handles are created (calls that may synchronise the device), which must not
         # happen while a receive posted ahead of time waits for a sender.  Later batches post receives early.
         ahead = self._batches_run > 0
+        prefix = os.environ.get("NEOX_PP_TIMELINE")
+        tl = _Timeline(prefix, s) if (prefix and train and self._batches_run == 3) else None
+        mark = tl.mark if tl is not None else (lambda name, mb: None)
 
         def post_recv_fwd():
             """Post the receive of the next activation (None on the first stage)."""
@@ -458,27 +493,39 @@ class PipelineEngine(NeoXEngine):
             # run under compute; sends are never waited on.
             nxt = post_recv_fwd() if M > 0 else None
             n_fwd = 0
-            for _ in range(warm):
+            n_bwd = [0]
+
+            def one_fwd():
+                nonlocal nxt, n_fwd
+                mark("fwd_wait", n_fwd)
                 recv = take_fwd(nxt)
                 n_fwd += 1
                 nxt = post_recv_fwd() if n_fwd < M else None
+                mark("fwd_begin", n_fwd - 1)
                 out, loss = fwd(recv)
+                mark("fwd_end", n_fwd - 1)
                 send_fwd(out)
                 queue.append((recv, out, loss, post_recv_bwd(out)))
-            for i in range(M - warm):
-                recv = take_fwd(nxt)
-                n_fwd += 1
-                nxt = post_recv_fwd() if n_fwd < M else None
-                out, loss = fwd(recv)
-                send_fwd(out)
-                queue.append((recv, out, loss, post_recv_bwd(out)))
+
+            def one_bwd():
                 r0, o0, l0, gh = queue.pop(0)          # the oldest outstanding micro-batch
-                bwd(o0, l0, take_bwd(gh))
+                mark("bwd_wait", n_bwd[0])
+                grads = take_bwd(gh)
+                mark("bwd_begin", n_bwd[0])
+                bwd(o0, l0, grads)
+                mark("bwd_end", n_bwd[0])
+                n_bwd[0] += 1
                 send_bwd(r0)
+
+            for _ in range(warm):
+                one_fwd()
+            for i in range(M - warm):
+                one_fwd()
+                one_bwd()
             while queue:
-                r0, o0, l0, gh = queue.pop(0)
-                bwd(o0, l0, take_bwd(gh))
-                send_bwd(r0)
+                one_bwd()
+            if tl is not None:
+                tl.dump()
         if p2p is not None:
             p2p.reap()
         self._batches_run += 1
