@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as OF
+from ..ops.sparse_attention import block_sparse_attention
 from ..ops.attention import attention_ref, flash_attention, packed_qkv_attention, packed_qkv_ok
 from ..ops.linear import dead_outputs, linear as fused_linear
 from ..parallel import mappings as M
@@ -260,6 +261,16 @@ class ParallelSelfAttention(nn.Module):
         relative position bias, block-sparse layouts, attention dropout and fp32 softmax."""
         sq, b, np_, hn = q.shape
         sk = k.shape[0]
+        if (self.sparse and sq == sk and attention_mask is None and self.rpe is None and self.pos_emb != "alibi"
+                and self.sliding_window_width is None):
+            # block-sparse layouts: only the kept tiles of the score matrix are computed (ops/sparse_attention.py)
+            drop = None
+            if self.dropout_p > 0 and self.training:
+                def drop(p):
+                    with get_cuda_rng_tracker().fork():
+                        return self.attention_dropout(p)
+            scale = (float(self.coeff) if self.coeff is not None else 1.0) / self.norm_factor
+            return block_sparse_attention(q, k, v, self.attention_type, self.sparsity_config, scale, dropout=drop)
         if k.shape[2] != np_:
             rep = np_ // k.shape[2]
             k = k.repeat_interleave(rep, dim=2)

@@ -1,3 +1,8 @@
+"""Operator-level checks that run on CPU (eager statements of the kernels' math)."""
+import pytest
+import torch
+
+
 
 
 def test_fp8_linear_gelu_split_matches_plain_composition():
@@ -63,3 +68,37 @@ def test_pair_kernel_selection(monkeypatch):
     assert not G.use_pair_kernel(8192, 6144, 6144)
     monkeypatch.setattr(G, "_PAIR", "1")
     assert G.use_pair_kernel(64, 64, 64)
+
+
+@pytest.mark.parametrize("kind,cfg", [
+    ("local", {"block": 16, "num_sliding_window_blocks": 3}),
+    ("sparse_fixed", {"block": 8, "num_local_blocks": 4, "num_global_blocks": 1}),
+    ("sparse_variable", {"block": 16, "num_local_blocks": 2}),
+    ("bigbird", {"block": 16, "num_sliding_window_blocks": 3, "num_global_blocks": 1, "num_random_blocks": 2}),
+    ("bslongformer", {"block": 16, "num_sliding_window_blocks": 3, "global_block_indices": [0, 2]}),
+])
+def test_block_sparse_attention_matches_the_dense_masked_statement(kind, cfg):
+    """Gathering only the kept tiles gives the same output and gradients as masking a dense score matrix."""
+    from gpt_neox_b200.models.transformer import sparse_layout_mask
+    from gpt_neox_b200.ops.sparse_attention import block_sparse_attention
+    torch.manual_seed(0)
+    s, b, h, hkv, d = 100, 2, 4, 2, 8                      # s is not a multiple of the block; grouped-query heads
+    q = torch.randn(s, b, h, d, requires_grad=True)
+    k = torch.randn(s, b, hkv, d, requires_grad=True)
+    v = torch.randn(s, b, hkv, d, requires_grad=True)
+    scale = d ** -0.5
+    out = block_sparse_attention(q, k, v, kind, cfg, scale)
+    g = torch.randn_like(out)
+    out.backward(g)
+    got = (out.detach(), q.grad.clone(), k.grad.clone(), v.grad.clone())
+    for t in (q, k, v):
+        t.grad = None
+    mask = sparse_layout_mask(kind, s, s, cfg, q.device) | (torch.arange(s)[None, :] > torch.arange(s)[:, None])
+    kf = k.repeat_interleave(h // hkv, dim=2)
+    vf = v.repeat_interleave(h // hkv, dim=2)
+    scores = torch.einsum("sbhd,tbhd->bhst", q, kf) * scale
+    probs = torch.softmax(scores.masked_fill(mask[None, None], float("-inf")), dim=-1)
+    ref = torch.einsum("bhst,tbhd->sbhd", probs, vf)
+    ref.backward(g)
+    for a, r in zip(got, (ref.detach(), q.grad, k.grad, v.grad)):
+        torch.testing.assert_close(a, r, atol=2e-5, rtol=1e-4)
