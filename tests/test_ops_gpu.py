@@ -922,3 +922,25 @@ def test_norm_fan_out_adds_all_gradient_contributions_in_the_kernels(kinds):
     xd = x.clone().requires_grad_(True)
     mods[0](xd).backward(gs[0])
     _close(xc.grad, xd.grad, 1e-6, rtol=0)
+
+
+def test_block_sparse_attention_on_device_bf16():
+    from gpt_neox_b200.models.transformer import sparse_layout_mask
+    from gpt_neox_b200.ops.sparse_attention import block_sparse_attention
+    torch.manual_seed(0)
+    s, b, h, d = 1000, 2, 8, 64
+    cfg = {"block": 16, "num_sliding_window_blocks": 5, "num_global_blocks": 2, "num_random_blocks": 2}
+    q, k, v = [torch.randn(s, b, h, d, device=DEV).to(torch.bfloat16).requires_grad_(True) for _ in range(3)]
+    out = block_sparse_attention(q, k, v, "bigbird", cfg, d ** -0.5)
+    g = torch.randn_like(out)
+    out.backward(g)
+    mask = sparse_layout_mask("bigbird", s, s, cfg, q.device) | \
+        (torch.arange(s, device=DEV)[None, :] > torch.arange(s, device=DEV)[:, None])
+    qf, kf, vf = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    probs = torch.softmax((torch.einsum("sbhd,tbhd->bhst", qf, kf) * d ** -0.5).masked_fill(mask[None, None],
+                                                                                           float("-inf")), dim=-1)
+    ref = torch.einsum("bhst,tbhd->sbhd", probs, vf)
+    ref.backward(g.float())
+    _close(out, ref, 2e-2, rtol=2e-2)
+    for a, r in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        _close(a, r, 6e-2, rtol=5e-2)
