@@ -13,7 +13,6 @@ formula (``megatron/logging.py:83-237``):
 from __future__ import annotations
 
 import math
-import sys
 
 import torch
 import torch.distributed as dist

@@ -4,7 +4,6 @@ applied to half of the channels, optionally helped by a tiny single-head attenti
 channel projection, with a pre-norm residual."""
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn as nn

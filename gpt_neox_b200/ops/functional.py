@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import ctypes
 import os
-import math
 
 import torch
 import torch.nn.functional as F

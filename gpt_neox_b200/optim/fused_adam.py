@@ -10,7 +10,6 @@ folded in), updates ``m``, ``v`` and the fp32 master weight and, when the parame
 from __future__ import annotations
 
 import ctypes
-import math
 
 import torch
 

@@ -14,7 +14,6 @@ and the backward are single-pass kernels (the ``ce_*`` kernels of
 """
 from __future__ import annotations
 
-import ctypes
 
 import torch
 import torch.distributed as dist

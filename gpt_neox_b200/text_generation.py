@@ -12,7 +12,6 @@ from __future__ import annotations
 
 import copy
 import json
-import os
 import time
 from typing import List, Union
 

@@ -16,8 +16,6 @@ from __future__ import annotations
 
 import argparse
 import os
-import re
-import sys
 
 import torch
 import yaml
