@@ -285,6 +285,7 @@ mup_rp_embedding_mult : float = 1.0
 mup_width_scale : int = 2
 
 [textgen]
+cuda_graph_decode : bool = False                   # decode against fixed-capacity key/value caches and replay each step from a CUDA graph (single GPU, rotary / learned positions)
 text_gen_type : str = None
 precompute_model_name : str = None
 temperature : float = 0.0

@@ -232,6 +232,8 @@ class ParallelSelfAttention(nn.Module):
         else:
             self.rotary_emb = None
 
+        # fixed-capacity key/value cache for graph-replayed decoding (text_generation.GraphDecoder sets these)
+        self.static_kv, self.static_pos, self.static_filled = None, None, False
         self.attention_type = neox_args.attention_config[layer_number]
         self.sparse = self.attention_type not in ("global", "flash")
         self.sparsity_config = neox_args.sparsity_config or {}
@@ -305,6 +307,28 @@ class ParallelSelfAttention(nn.Module):
         ctx = torch.matmul(probs, v.permute(1, 2, 0, 3))                  # [b, np, sq, hn]
         return ctx.permute(2, 0, 1, 3).contiguous()
 
+    def static_cache_supported(self):
+        """Static-cache decoding covers rotary / learned / no positional scheme with plain causal attention."""
+        return (self.rpe is None and not self.sparse and self.pos_emb != "alibi" and self.sliding_window_width is None
+                and not self.use_qk_layernorm)
+
+    def _static_decode(self, q, k, v):
+        """One new token against the fixed-capacity cache: write its key / value at ``static_pos``, attend to every
+        slot up to that position (a mask computed on the device), all shapes independent of the position."""
+        buf, pos = self.static_kv, self.static_pos
+        buf[0].index_copy_(0, pos, k.to(buf.dtype))
+        buf[1].index_copy_(0, pos, v.to(buf.dtype))
+        keys, vals = buf[0], buf[1]
+        np_ = q.shape[2]
+        if keys.shape[2] != np_:
+            rep = np_ // keys.shape[2]
+            keys, vals = keys.repeat_interleave(rep, dim=2), vals.repeat_interleave(rep, dim=2)
+        scale = (float(self.coeff) if self.coeff is not None else 1.0) / self.norm_factor
+        scores = torch.einsum("qbhd,kbhd->bhqk", q, keys).float() * scale
+        future = torch.arange(keys.shape[0], device=q.device)[None, None, None, :] > pos
+        probs = torch.softmax(scores.masked_fill(future, float("-inf")), dim=-1).to(q.dtype)
+        return torch.einsum("bhqk,kbhd->qbhd", probs, vals)
+
     def _packed_path(self, hidden_states, layer_past):
         """rotary + flash attention on the packed QKV projection, in place (training / no kv-cache)."""
         if self.gqa or self.use_qk_layernorm or self.use_cache or self.rpe is not None or self.sparse or \
@@ -337,7 +361,14 @@ class ParallelSelfAttention(nn.Module):
             q, k, v = self._project(hidden_states)
         if self.use_qk_layernorm:
             q, k = self.qk_layernorm(q), self.qk_layernorm(k)
-        if self.rotary_emb is not None:
+        static_step = self.static_kv is not None and self.use_cache and k.shape[0] == 1 and self.static_filled
+        if self.rotary_emb is not None and static_step:
+            # decoding against the fixed-capacity cache: the position lives on the device (``static_pos``), so the
+            # same launch sequence serves every step and can be replayed from a CUDA graph
+            cos, sin = self.rotary_emb(v, seq_len=self.static_kv.shape[1])
+            cos_q, sin_q = cos.index_select(0, self.static_pos), sin.index_select(0, self.static_pos)
+            q, k = OF.rope(q, cos_q, sin_q), OF.rope(k, cos_q, sin_q)
+        elif self.rotary_emb is not None:
             offset = layer_past[0].shape[0] if layer_past is not None and layer_past[0].numel() > 0 else 0
             seq_len = k.shape[0] + offset
             cos, sin = self.rotary_emb(v, seq_len=seq_len)
@@ -348,7 +379,20 @@ class ParallelSelfAttention(nn.Module):
                 k = OF.rope(k, cos_q, sin_q)
             else:
                 q, k = apply_rotary_pos_emb(q, k, cos, sin, offset=offset)
-        if self.use_cache:
+        if static_step:
+            ctx = self._static_decode(q, k, v)
+            ctx = ctx.reshape(ctx.shape[0], ctx.shape[1], self.hidden_size_per_partition)
+            out, bias = self.dense(ctx, residual=residual, fuse_bias=fuse_bias)
+            return [out, self.static_kv], bias
+        if self.use_cache and self.static_kv is not None:
+            # prompt pass of a static-cache generation: the usual causal attention over the prompt, whose keys and
+            # values also go into the fixed-capacity buffer
+            n = k.shape[0]
+            self.static_kv[0, :n].copy_(k)
+            self.static_kv[1, :n].copy_(v)
+            self.static_filled = True
+            present = self.static_kv
+        elif self.use_cache:
             # keys and values live in one buffer with spare rows behind the filled part: a decoding step writes its
             # new rows in place and hands out views, instead of re-copying the whole cache with cat + stack
             present = _extend_kv_cache(layer_past, k, v)

@@ -123,6 +123,72 @@ def stop_tokens_in_completion(stop_tokens, context_tokens, batch_index, current_
     return False
 
 
+class GraphDecoder:
+    """Token-by-token decoding with a fixed-capacity key/value cache, replayed from a CUDA graph.
+
+    A decoding step of the ordinary cached path launches a few dozen small kernels per layer whose shapes change with
+    the position (the cache grows), so it is bound by launch overhead and cannot be captured.  Here every attention
+    layer owns a ``[2, capacity, batch, heads, d]`` buffer and reads the current position from a device scalar: the
+    step's launch sequence is identical for every token, is captured once after the prompt pass and replayed.  On a
+    machine without CUDA (or with ``capture=False``) the same static-cache step runs eagerly, which is how its
+    numerics are tested.  The reference decodes with ``torch.cat`` caches and eager launches
+    (``megatron/text_generation_utils.py:198-405``)."""
+
+    def __init__(self, neox_args, model, batch_size, capacity, capture=None):
+        self.model = model
+        dev = _dev()
+        self.attn = [m for m in model.module.modules() if hasattr(m, "static_kv") and hasattr(m, "static_cache_supported")]
+        self.supported = bool(self.attn) and all(m.static_cache_supported() and m.use_cache for m in self.attn)
+        self.capture = (torch.cuda.is_available() if capture is None else capture) and self.supported
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.tokens = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
+        self.position_ids = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
+        self.graph, self.logits, self.steps = None, None, 0
+        if self.supported:
+            dt = neox_args.params_dtype
+            for m in self.attn:
+                m.static_kv = torch.zeros(2, capacity, batch_size, m.num_kv_heads_per_partition,
+                                          m.hidden_size_per_attention_head, dtype=dt, device=dev)
+                m.static_pos, m.static_filled = self.pos, False
+
+    def close(self):
+        for m in self.attn:
+            m.static_kv, m.static_pos, m.static_filled = None, None, False
+        self.graph = None
+
+    def prefill(self, tokens, position_ids):
+        """The prompt pass (eager): fills the caches; returns the logits of the prompt."""
+        out = self.model.module((tokens, position_ids, None))
+        return out[0] if isinstance(out, tuple) else out
+
+    def _forward(self):
+        out = self.model.module((self.tokens, self.position_ids, None))
+        return out[0] if isinstance(out, tuple) else out
+
+    def step(self, tokens, position_ids, index):
+        """Logits ``[b, 1, V]`` for the token at sequence position ``index`` given everything before it."""
+        self.tokens.copy_(tokens)
+        self.position_ids.copy_(position_ids)
+        self.pos.fill_(index)
+        self.steps += 1
+        if not self.capture:
+            return self._forward()
+        if self.graph is None:
+            # warm up on a side stream (lazy allocations, descriptor caches), then capture the very same step:
+            # re-running a step is harmless, it rewrites the same cache slot with the same values
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._forward()
+            torch.cuda.current_stream().wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = self._forward()
+        self.graph.replay()
+        return self.logits
+
+
 def stream_tokens(neox_args, model, context_tokens: List[List[int]], eos_token_id: int = None,
                   maximum_tokens: int = None, recompute: bool = False, temperature: float = 0.0, top_k: int = 0,
                   top_p: float = 0.0, stop_tokens=None):
@@ -151,6 +217,27 @@ def stream_tokens(neox_args, model, context_tokens: List[List[int]], eos_token_i
     last_index = min(total_len - 1, index + budget - 1)
     if hasattr(model.module, "clear_cache"):
         model.module.clear_cache()
+    decoder = None
+    if (getattr(neox_args, "cuda_graph_decode", False) and not recompute and not neox_args.is_pipe_parallel
+            and mpu.get_model_parallel_world_size() == 1):
+        decoder = GraphDecoder(neox_args, model, batch_size, total_len)
+        if not decoder.supported:
+            decoder.close()
+            decoder = None
+    try:
+        yield from _decode_loop(neox_args, model, decoder, context_tokens, position_ids, attention_mask, start_index,
+                                index, first_index, last_index, budget, batch_size, eos_token_id, stop_tokens,
+                                recompute, temperature, top_k, top_p, dev)
+    finally:
+        if decoder is not None:
+            decoder.close()
+            if hasattr(model.module, "clear_cache"):
+                model.module.clear_cache()
+
+
+def _decode_loop(neox_args, model, decoder, context_tokens, position_ids, attention_mask, start_index, index,
+                 first_index, last_index, budget, batch_size, eos_token_id, stop_tokens, recompute, temperature, top_k,
+                 top_p, dev):
     with torch.no_grad():
         is_done = torch.zeros(batch_size, dtype=torch.bool, device=dev)
         end_index = torch.full((batch_size,), -1, dtype=torch.long, device=dev)
@@ -167,7 +254,11 @@ def stream_tokens(neox_args, model, context_tokens: List[List[int]], eos_token_i
                 else:
                     use_t = context_tokens[:, index - 1].view(batch_size, -1)
                     use_p = position_ids[:, index - 1].view(batch_size, -1)
-                logits = forward_model(model, (use_t, use_p, attention_mask), neox_args.is_pipe_parallel)
+                if decoder is not None:
+                    logits = decoder.prefill(use_t, use_p) if index == first_index else \
+                        decoder.step(use_t, use_p, index - 1)
+                else:
+                    logits = forward_model(model, (use_t, use_p, attention_mask), neox_args.is_pipe_parallel)
                 tok_logits = logits[:, -1].view(batch_size, -1).contiguous() if logits is not None else None
             if tok_logits is not None:
                 tok_logits = tok_logits[:, : neox_args.padded_vocab_size]

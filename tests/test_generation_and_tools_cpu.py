@@ -241,3 +241,37 @@ def test_kv_cache_appends_in_place_and_survives_branching():
     # a plain tensor pair (no buffer attached) is accepted as the past
     q = _extend_kv_cache(torch.stack((k0, v0)), k1, v1)
     assert torch.equal(q[0], torch.cat([k0, k1]))
+
+
+def _static_cache_generation(rank, world, cfg):
+    """Decoding against the fixed-capacity cache (the step a CUDA graph replays; run eagerly here) produces the
+    tokens and logits of the ordinary growing-cache path, for prompts of different lengths."""
+    from gpt_neox_b200.text_generation import stream_tokens
+    args, model = _native_model({"optimizer": None, "no_load_optim": True, "seq_length": 48,
+                                 "max_position_embeddings": 48, "return_logits": True, **cfg})
+    model.module.inference_mode(use_cache=True)
+    prompts = [[5, 6, 7, 8, 9], [9, 10]]
+    outs = {}
+    for static in (False, True):
+        args.update_value("cuda_graph_decode", static)
+        last = None
+        for last in stream_tokens(args, model, prompts, eos_token_id=-1, maximum_tokens=10):
+            pass
+        outs[static] = (last[0].clone(), last[3].clone())
+    assert torch.equal(outs[False][0], outs[True][0]), (outs[False][0], outs[True][0])
+    torch.testing.assert_close(outs[False][1], outs[True][1], atol=2e-4, rtol=1e-4)
+    # the caches were handed back: the ordinary path works again afterwards
+    args.update_value("cuda_graph_decode", False)
+    for last in stream_tokens(args, model, prompts, eos_token_id=-1, maximum_tokens=4):
+        pass
+    assert torch.equal(last[0][:, :6], outs[False][0][:, :6])
+
+
+@pytest.mark.parametrize("cfg", [
+    {},                                                                       # rotary 25 %, parallel residual
+    {"rotary_pct": 1.0, "gpt_j_residual": False, "num_kv_heads": 2, "norm": "rmsnorm", "activation": "swiglu",
+     "use_bias_in_mlp": False},                                               # Llama-style, grouped-query
+    {"pos_emb": "learned"},
+])
+def test_static_cache_decoding_matches_the_growing_cache(cfg):
+    run_distributed(_static_cache_generation, 1, cfg)

@@ -29,3 +29,9 @@ def test_moe_grouped_kernels_match_the_per_expert_loop_and_train():
     """Fused router, dispatch, grouped tcgen05 GEMMs (forward, dgrad, wgrad) and combine against the per-expert loop
     (dropless and with a capacity limit), then a small MoE model trains through them."""
     _run("moe_grouped_worker.py", "MOE_GROUPED_OK")
+
+
+@pytest.mark.gpu
+def test_cuda_graph_decoding_matches_eager_decoding_and_is_faster():
+    """Fixed-capacity key/value caches + one captured decoding step replayed per token (``cuda_graph_decode``)."""
+    _run("graph_decode_worker.py", "GRAPH_DECODE_OK")
