@@ -24,7 +24,10 @@ def main():
     initialize_megatron(args)
     model, _, _, _ = setup_model_and_optimizer(args, use_cache=True)
     model.module.inference_mode(use_cache=True)
-    prompts = [[5, 6, 7, 8, 9, 10, 11, 12], [9, 10, 11]]
+    # sample 0 is a long prompt: its tokens are forced at every step, so both runs feed it identical inputs and its
+    # recorded logits can be compared position by position; sample 1 generates freely from a short prompt
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 500, (124,), generator=g).tolist(), [9, 10, 11]]
     seen = []
     orig = TG.GraphDecoder.step
 
@@ -45,15 +48,13 @@ def main():
         ms[graph] = (time.perf_counter() - t0) * 1e3
         res[graph] = (last[0].clone(), last[3].clone())
     assert seen and all(g for g, _ in seen) and max(n for _, n in seen) >= 100, seen[:3]
-    # the first generated positions see identical inputs in both runs: their logits agree to bf16 accuracy
-    a, b = res[False][1][:3], res[True][1][:3]
+    a, b = res[False][1][:118], res[True][1][:118]
     err = (a - b).abs().max().item()
-    assert err < 0.06 * max(a.abs().max().item(), 1.0), err
-    same = (res[False][0] == res[True][0]).float().mean().item()
-    assert same > 0.5, same
+    assert err < 0.06 * max(a.abs().max().item(), 1.0), (err, a.abs().max().item())
+    assert torch.equal(res[False][0][0], res[True][0][0])
     assert ms[True] < ms[False], ms
-    print(f"GRAPH_DECODE_OK eager {ms[False]:.0f} ms, graph {ms[True]:.0f} ms for 120 tokens; "
-          f"{same * 100:.0f}% of the tokens identical", flush=True)
+    print(f"GRAPH_DECODE_OK eager {ms[False]:.0f} ms, graph {ms[True]:.0f} ms for 120 tokens; max logit difference "
+          f"{err:.4f}", flush=True)
 
 
 if __name__ == "__main__":
