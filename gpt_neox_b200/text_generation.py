@@ -144,17 +144,32 @@ class GraphDecoder:
         self.tokens = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
         self.position_ids = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
         self.graph, self.logits, self.steps = None, None, 0
+        self.caches = []
         if self.supported:
             dt = neox_args.params_dtype
-            for m in self.attn:
-                m.static_kv = torch.zeros(2, capacity, batch_size, m.num_kv_heads_per_partition,
-                                          m.hidden_size_per_attention_head, dtype=dt, device=dev)
-                m.static_pos, m.static_filled = self.pos, False
+            self.caches = [torch.zeros(2, capacity, batch_size, m.num_kv_heads_per_partition,
+                                       m.hidden_size_per_attention_head, dtype=dt, device=dev) for m in self.attn]
+
+    @classmethod
+    def for_model(cls, neox_args, model, batch_size):
+        """The decoder of ``model`` for this batch size, kept on the model between generation calls so the captured
+        graph (which holds the addresses of the caches and of the static inputs) is reused.  Capacity is the model's
+        sequence length: every request fits."""
+        pool = model.__dict__.setdefault("_graph_decoders", {})
+        dec = pool.get(batch_size)
+        if dec is None:
+            dec = pool[batch_size] = cls(neox_args, model, batch_size, neox_args.seq_length)
+        return dec
+
+    def attach(self):
+        """Hand the caches to the attention layers for one generation call (an empty cache: the prompt pass fills it)."""
+        for m, buf in zip(self.attn, self.caches):
+            m.static_kv, m.static_pos, m.static_filled = buf, self.pos, False
 
     def close(self):
+        """Take the caches back (the layers return to the growing-cache path); the graph stays valid for the next call."""
         for m in self.attn:
             m.static_kv, m.static_pos, m.static_filled = None, None, False
-        self.graph = None
 
     def prefill(self, tokens, position_ids):
         """The prompt pass (eager): fills the caches; returns the logits of the prompt."""
@@ -220,9 +235,10 @@ def stream_tokens(neox_args, model, context_tokens: List[List[int]], eos_token_i
     decoder = None
     if (getattr(neox_args, "cuda_graph_decode", False) and not recompute and not neox_args.is_pipe_parallel
             and mpu.get_model_parallel_world_size() == 1):
-        decoder = GraphDecoder(neox_args, model, batch_size, total_len)
-        if not decoder.supported:
-            decoder.close()
+        decoder = GraphDecoder.for_model(neox_args, model, batch_size)
+        if decoder.supported:
+            decoder.attach()
+        else:
             decoder = None
     try:
         yield from _decode_loop(neox_args, model, decoder, context_tokens, position_ids, attention_mask, start_index,
