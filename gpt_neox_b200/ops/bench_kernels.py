@@ -40,6 +40,10 @@ def main():
                     help="only the mixture-of-experts kernels: router, dispatch / combine, and the grouped expert "
                          "GEMMs (forward, dgrad, wgrad) against the per-expert loop over the plain GEMM; "
                          "--tokens rows x top-2 of --experts experts, hidden --hidden, expert hidden --ffn")
+    ap.add_argument("--small-kernels", action="store_true",
+                    help="only the remaining element-wise / recurrent / optimizer kernels, each against its eager "
+                         "torch statement: bias-dropout-residual, RoPE, embedding fwd/bwd, bias-gradient column sum, "
+                         "wkv6, selective scan, top-k/top-p filter, Lion, block-wise 8-bit Adam, squared norm")
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--ffn", type=int, default=0, help="expert hidden size (default 4 x hidden)")
     a = ap.parse_args()
@@ -81,6 +85,8 @@ def main():
         return ab_gemm(a, dev, bf, flush)
     if a.moe:
         return moe_kernels(a, dev, bf, flush)
+    if a.small_kernels:
+        return small_kernels(a, dev, bf, flush)
     x = bf(T, h)
     w_qkv, w_fc1, w_fc2 = bf(3 * h, h), bf(4 * h, h), bf(h, 4 * h)
     y4 = bf(T, 4 * h)
@@ -257,6 +263,128 @@ def ab_gemm(a, dev, bf, flush):
         results.append(rec)
         print(json.dumps(rec), flush=True)
     return results
+
+
+def _ab(name, fns, iters, flush, nbytes=0.0, extra=None):
+    """Median time of every callable in ``fns`` (name -> fn), taking turns call by call, L2 flushed before each.
+    A case whose set-up or first call raises is reported and skipped, so the remaining cases still run."""
+    try:
+        return _ab_run(name, fns, iters, flush, nbytes, extra)
+    except Exception as exc:      # noqa: BLE001 -- a benchmark driver: report and go on
+        rec = {"kernel": name, "error": f"{type(exc).__name__}: {exc}"[:300]}
+        print(json.dumps(rec), flush=True)
+        return rec
+
+
+def _ab_run(name, fns, iters, flush, nbytes, extra):
+    hbm, _, kind = peaks()
+    for f in fns.values():
+        for _ in range(3):
+            f()
+    torch.cuda.synchronize()
+    ts = {k: [] for k in fns}
+    for _ in range(iters):
+        for k, f in fns.items():
+            flush.add_(1.0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts[k].append(e0.elapsed_time(e1))
+    med = {k: sorted(v)[len(v) // 2] for k, v in ts.items()}
+    keys = list(med)
+    rec = {"kernel": name, **{f"{k}_ms": round(v, 4) for k, v in med.items()}}
+    if len(keys) == 2:
+        rec["speedup"] = round(med[keys[0]] / med[keys[1]], 2)
+    if nbytes:
+        rec["gbs"] = round(nbytes / med[keys[-1]] / 1e6, 1)
+        rec[f"frac_of_{kind}_copy_bw"] = round(nbytes / med[keys[-1]] / 1e6 / hbm, 3)
+    rec.update(extra or {})
+    print(json.dumps(rec), flush=True)
+    return rec
+
+
+def small_kernels(a, dev, bf, flush):
+    """The kernels that the other modes do not time, each against the eager torch statement of the same operation."""
+    import torch.nn.functional as F
+    from ..optim.adam8bit import Adam8bit
+    from ..optim.lion import Lion
+    from ..text_generation import filter_logits
+    from . import embedding as E
+    from . import selective_scan as SS
+    from . import wkv6 as W
+    T, h, it = a.tokens, a.hidden, a.iters
+    out = []
+    x, res, bias = bf(T, h), bf(T, h), bf(h)
+    out.append(_ab("bias_dropout_residual_fwd",
+                   {"torch": lambda: res + F.dropout(x + bias, 0.1, True),
+                    "kernel": lambda: OF.bias_dropout_add(x, bias, res, 0.1, True)}, it, flush, 3.0 * T * h * 2))
+    q = bf(2048, 4, 64, 96)
+    t = torch.arange(2048, device=dev).float()
+    inv = 1.0 / (10000 ** (torch.arange(0, 24, 2, device=dev).float() / 24))
+    emb = torch.cat([torch.outer(t, inv)] * 2, -1)
+    cos, sin = emb.cos()[:, None, None, :], emb.sin()[:, None, None, :]
+    out.append(_ab("rope_partial_24_of_96", {"torch": lambda: OF.rope_ref(q, cos, sin), "kernel": lambda: OF.rope(q, cos, sin)},
+                   it, flush, 2.0 * q.numel() * 2))
+    V = 50432
+    table = torch.nn.Parameter(bf(V, h))
+    ids = torch.randint(0, V, (4, 2048), device=dev)
+    out.append(_ab("embedding_fwd", {"torch": lambda: F.embedding(ids, table), "kernel": lambda: E.embedding(ids, table)},
+                   it, flush, 2.0 * ids.numel() * h * 2))
+    ge = bf(4, 2048, h)
+
+    def emb_bwd(fn):
+        def f():
+            table.grad = None
+            fn(ids, table).backward(ge)
+        return f
+    out.append(_ab("embedding_fwd_bwd", {"torch": emb_bwd(F.embedding), "kernel": emb_bwd(E.embedding)}, it, flush))
+    g4 = bf(T, 4 * h)
+    out.append(_ab("bias_grad_column_sum", {"torch": lambda: g4.sum(0), "kernel": lambda: OF.bias_grad(g4)}, it, flush,
+                   T * 4 * h * 2.0))
+    B_, T_, H_, N_ = 4, 1024, 32, 64
+    r, k, v, w = (bf(B_, T_, H_ * N_) for _ in range(4))
+    u = bf(H_, N_)
+    out.append(_ab("wkv6_fwd", {"kernel": lambda: W.wkv6(r, k, v, w, u)}, it, flush, 5.0 * r.numel() * 2,
+                   {"shape": [B_, T_, H_, N_]}))
+    b_, l_, d_, n_ = 4, 2048, 4096, 16
+    us, dts, zs = bf(b_, l_, d_), bf(b_, l_, d_), bf(b_, l_, d_)
+    A = -torch.rand(d_, n_, device=dev) - 0.5
+    Bm, Cm = bf(b_, l_, n_), bf(b_, l_, n_)
+    D, dtb = torch.ones(d_, device=dev), torch.zeros(d_, device=dev)
+    out.append(_ab("selective_scan_fwd", {"kernel": lambda: SS.selective_scan(us, dts, A, Bm, Cm, D, zs, dtb)}, it, flush,
+                   4.0 * us.numel() * 2, {"shape": [b_, l_, d_, n_]}))
+    lg = torch.randn(64, V, device=dev)
+
+    def eager_filter():
+        kth = torch.topk(lg, 50)[0][..., -1, None]
+        x2 = lg.masked_fill(lg < kth, -float("inf"))
+        sl, si = torch.sort(x2, descending=True, dim=-1)
+        rm = torch.cumsum(F.softmax(sl, dim=-1), dim=-1) > 0.9
+        rm[..., 1:] = rm[..., :-1].clone()
+        rm[..., 0] = False
+        return x2.masked_fill(torch.zeros_like(rm).scatter(-1, si, rm), -float("inf"))
+    out.append(_ab("top_k_50_top_p_0.9_filter", {"torch": eager_filter, "kernel": lambda: filter_logits(lg, 50, 0.9)},
+                   it, flush))
+    n = 100 * 1000 * 1000
+    p1, p2 = torch.nn.Parameter(torch.zeros(n, device=dev)), torch.nn.Parameter(torch.zeros(n, device=dev))
+    p1.grad, p2.grad = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    lion, a8 = Lion([p1], lr=1e-4), Adam8bit([p2], lr=1e-4)
+    out.append(_ab("lion_step_100M", {"kernel": lion.step}, it, flush, n * 4 * 5.0))
+    out.append(_ab("adam8bit_step_100M", {"kernel": a8.step}, it, flush, n * (4 * 3 + 2 * 2.0)))
+    tot = torch.zeros((), device=dev)
+    import ctypes
+    from . import native
+
+    def sumsq():
+        rc = native.lib().neox_sumsq_f32(native.ptr(p1.grad), ctypes.c_longlong(n), native.ptr(tot),
+                                         ctypes.c_void_p(native.stream_ptr()))
+        native.check(rc, "neox_sumsq_f32")
+    out.append(_ab("squared_norm_100M", {"torch": lambda: torch.linalg.vector_norm(p1.grad) ** 2, "kernel": sumsq}, it,
+                   flush, n * 4.0))
+    print(json.dumps({"status_word": native.read_status()}), flush=True)
+    return out
 
 
 def moe_kernels(a, dev, bf, flush):
