@@ -422,14 +422,25 @@ __global__ void __launch_bounds__(256) lion_kernel(float* __restrict__ p, float*
     }
 }
 
+// 16-byte loads over the aligned body (two independent accumulators per thread), scalar loads for the ragged
+// head / tail; one atomic per CTA.
 __global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
     __shared__ float red[33];
-    float s = 0.f;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float v = x[i];
-        s += v * v;
+    const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    long long head = (4 - ((reinterpret_cast<uintptr_t>(x) >> 2) & 3)) & 3;      // floats before a 16-byte boundary
+    if (head > n) head = n;
+    const long long nvec = (n - head) >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x + head);
+    float s0 = 0.f, s1 = 0.f;
+    for (long long i = tid; i < nvec; i += nthreads) {
+        const float4 v = x4[i];
+        s0 += v.x * v.x + v.y * v.y;
+        s1 += v.z * v.z + v.w * v.w;
     }
-    s = block_reduce<false>(s, red);
+    for (long long i = tid; i < head; i += nthreads) s0 += x[i] * x[i];
+    for (long long i = head + (nvec << 2) + tid; i < n; i += nthreads) s1 += x[i] * x[i];
+    const float s = block_reduce<false>(s0 + s1, red);
     if (threadIdx.x == 0) atomicAdd(out, s);
 }
 
@@ -580,7 +591,7 @@ int neox_lion_step(float* p, float* m, const float* g, void* out, int out_dtype,
 // out += sum(x^2); the caller zeroes `out` first.
 int neox_sumsq_f32(const float* x, long long n, float* out, void* stream) {
     if (n <= 0) return 0;
-    sumsq_kernel<<<grid_for(n, 4), 256, 0, (cudaStream_t)stream>>>(x, n, out);
+    sumsq_kernel<<<grid_for((n + 3) / 4, 8), 256, 0, (cudaStream_t)stream>>>(x, n, out);
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
 }
 

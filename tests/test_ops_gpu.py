@@ -944,3 +944,17 @@ def test_block_sparse_attention_on_device_bf16():
     _close(out, ref, 2e-2, rtol=2e-2)
     for a, r in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
         _close(a, r, 6e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("n,offset", [(1, 0), (7, 1), (1000003, 0), (1000003, 3), (4096, 2)])
+def test_squared_norm_kernel_any_alignment(n, offset):
+    import ctypes
+    torch.manual_seed(6)
+    base = torch.randn(n + offset + 8, device=DEV)
+    x = base[offset:offset + n]
+    out = torch.zeros((), device=DEV)
+    rc = native.lib().neox_sumsq_f32(native.ptr(x), ctypes.c_longlong(n), native.ptr(out),
+                                     ctypes.c_void_p(native.stream_ptr()))
+    native.check(rc, "neox_sumsq_f32")
+    ref = (x.double() ** 2).sum().item()
+    assert abs(out.item() - ref) <= 2e-5 * max(ref, 1.0), (out.item(), ref)
