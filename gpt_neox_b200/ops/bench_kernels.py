@@ -327,6 +327,12 @@ def small_kernels(a, dev, bf, flush):
     cos, sin = emb.cos()[:, None, None, :], emb.sin()[:, None, None, :]
     out.append(_ab("rope_partial_24_of_96", {"torch": lambda: OF.rope_ref(q, cos, sin), "kernel": lambda: OF.rope(q, cos, sin)},
                    it, flush, 2.0 * q.numel() * 2))
+    q2 = bf(2048, 4, 32, 128)
+    inv2 = 1.0 / (10000 ** (torch.arange(0, 128, 2, device=dev).float() / 128))
+    emb2 = torch.cat([torch.outer(t, inv2)] * 2, -1)
+    cos2, sin2 = emb2.cos()[:, None, None, :], emb2.sin()[:, None, None, :]
+    out.append(_ab("rope_full_128", {"torch": lambda: OF.rope_ref(q2, cos2, sin2), "kernel": lambda: OF.rope(q2, cos2, sin2)},
+                   it, flush, 2.0 * q2.numel() * 2))
     V = 50432
     table = torch.nn.Parameter(bf(V, h))
     ids = torch.randint(0, V, (4, 2048), device=dev)

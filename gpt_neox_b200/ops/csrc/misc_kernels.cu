@@ -160,6 +160,71 @@ __global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, T* _
     }
 }
 
+// Same operation with vector accesses of BYTES (16 or 8) bytes: one work item is the pair of chunks (e, e + rot/2) of
+// one head -- it reads both once and writes both -- or one chunk of the unrotated tail.  Needs rot/2, d - rot and the
+// strides to be multiples of the chunk (BYTES / sizeof(T) elements) and BYTES-aligned bases; the caller checks.
+template <int BYTES> struct RopeVec;
+template <> struct RopeVec<16> { using type = uint4; };
+template <> struct RopeVec<8> { using type = uint2; };
+
+template <typename T, int BYTES>
+__global__ void __launch_bounds__(256) rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                       const float* __restrict__ cs, const float* __restrict__ sn,
+                                                       int s, int b, int h, int d, int rot, long long ss, long long sb,
+                                                       long long sh, int inverse) {
+    using VT = typename RopeVec<BYTES>::type;
+    constexpr int V = BYTES / (int)sizeof(T);
+    const int half = rot >> 1;
+    const int npair = half / V;
+    const int items = npair + (d - rot) / V;
+    const long long total = (long long)s * b * h * items;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int it = (int)(i % items);
+        long long r = i / items;
+        const int hh = (int)(r % h);
+        r /= h;
+        const int bb = (int)(r % b);
+        const int sI = (int)(r / b);
+        const T* xp = x + sI * ss + bb * sb + hh * sh;
+        T* op = out + (((long long)sI * b + bb) * h + hh) * d;
+        if (it >= npair) {
+            const int e0 = rot + (it - npair) * V;
+            *reinterpret_cast<VT*>(op + e0) = __ldg(reinterpret_cast<const VT*>(xp + e0));
+            continue;
+        }
+        const int e0 = it * V;
+        const VT ulo = __ldg(reinterpret_cast<const VT*>(xp + e0));
+        const VT uhi = __ldg(reinterpret_cast<const VT*>(xp + e0 + half));
+        const T* lo = reinterpret_cast<const T*>(&ulo);
+        const T* hi = reinterpret_cast<const T*>(&uhi);
+        const float* cp = cs + (long long)sI * rot + e0;
+        const float* sp = sn + (long long)sI * rot + e0;
+        VT olo, ohi;
+        T* ol = reinterpret_cast<T*>(&olo);
+        T* oh = reinterpret_cast<T*>(&ohi);
+#pragma unroll
+        for (int j = 0; j < V; j += 2) {                       // V is even; the tables are read 8 bytes at a time
+            const float2 c0 = __ldg(reinterpret_cast<const float2*>(cp + j));
+            const float2 c1 = __ldg(reinterpret_cast<const float2*>(cp + half + j));
+            float2 s0 = __ldg(reinterpret_cast<const float2*>(sp + j));
+            float2 s1 = __ldg(reinterpret_cast<const float2*>(sp + half + j));
+            if (inverse) {
+                s0 = make_float2(-s0.x, -s0.y);
+                s1 = make_float2(-s1.x, -s1.y);
+            }
+            const float a0 = to_f<T>(lo[j]), b0 = to_f<T>(hi[j]);
+            const float a1 = to_f<T>(lo[j + 1]), b1 = to_f<T>(hi[j + 1]);
+            ol[j] = from_f<T>(a0 * c0.x - b0 * s0.x);
+            ol[j + 1] = from_f<T>(a1 * c0.y - b1 * s0.y);
+            oh[j] = from_f<T>(b0 * c1.x + a0 * s1.x);
+            oh[j + 1] = from_f<T>(b1 * c1.y + a1 * s1.y);
+        }
+        *reinterpret_cast<VT*>(op + e0) = olo;
+        *reinterpret_cast<VT*>(op + e0 + half) = ohi;
+    }
+}
+
 // In-place rotary embedding of the first `rot` dims of every head of q and k (views of one packed QKV tensor): one
 // thread owns the pair (e, e + rot/2), so nothing is read after it was overwritten.  cs / sn: [s, rot] fp32.
 template <typename T>
@@ -489,6 +554,23 @@ int neox_rope(const void* x, void* out, const float* cs, const float* sn, int s,
     if (total <= 0) return 0;
     if (rot % 2 || rot > d) return NEOX_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
+    for (int bytes = 16; bytes >= 8; bytes >>= 1) {            // widest vector access the shape allows
+        const int vec = bytes / (dtype == 1 ? 4 : 2);
+        const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                               reinterpret_cast<uintptr_t>(cs) | reinterpret_cast<uintptr_t>(sn)) &
+                              (uintptr_t)(bytes - 1)) == 0;
+        if (!aligned || rot == 0 || (rot / 2) % vec || (d - rot) % vec || d % vec || ss % vec || sb % vec || sh % vec)
+            continue;
+        const long long items = (long long)s * b * h * ((rot / 2 + d - rot) / vec);
+        if (bytes == 16) {
+            DISPATCH(dtype, (rope_vec_kernel<T, 16><<<grid_for(items, 16), 256, 0, st>>>(
+                                (const T*)x, (T*)out, cs, sn, s, b, h, d, rot, ss, sb, sh, inverse)));
+        } else {
+            DISPATCH(dtype, (rope_vec_kernel<T, 8><<<grid_for(items, 16), 256, 0, st>>>(
+                                (const T*)x, (T*)out, cs, sn, s, b, h, d, rot, ss, sb, sh, inverse)));
+        }
+        return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    }
     DISPATCH(dtype, (rope_kernel<T><<<grid_for(total, 16), 256, 0, st>>>((const T*)x, (T*)out, cs, sn, s, b, h, d, rot,
                                                                          ss, sb, sh, inverse)));
     return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;

@@ -118,6 +118,52 @@ def test_moe_grouped_data_flow_matches_per_expert_loop(cfg):
     run_distributed(_moe_grouped_matches_loop, 1, cfg)
 
 
+def _moe_capacity_edges(rank, world):
+    """``moe_min_capacity`` is a floor under the capacity formula; assignments beyond an expert's capacity are
+    dropped in token order; a token with every assignment dropped contributes nothing (and gets no gradient)."""
+    import torch
+    from common import make_args
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.models.init_functions import get_init_methods
+    from gpt_neox_b200.models.moe import ParallelMoE
+    from gpt_neox_b200.ops import moe_ops as MO
+    args = make_args(global_num_gpus=world, moe_num_experts=8, moe_top_k=1, moe_token_dropping=True,
+                     moe_train_capacity_factor=0.01, moe_eval_capacity_factor=2.0, moe_min_capacity=3)
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    init, out_init = get_init_methods(args)
+    moe = ParallelMoE(args, init, out_init, 8).float()
+    moe.train()
+    assert moe._capacity(16) == 3                      # ceil(0.01 * 16 / 8) = 1 < the floor
+    assert moe._capacity(100000) == 125                # the formula once it exceeds the floor
+    moe.eval()
+    assert moe._capacity(16) == 4                      # the evaluation factor: ceil(2.0 * 16 / 8)
+    moe.train()
+
+    idx = torch.tensor([[0], [0], [1], [0], [0], [0], [1]])
+    counts = torch.bincount(idx.reshape(-1), minlength=8)
+    row_of, kept = MO.plan_rows(idx, counts, capacity=3)
+    assert kept.tolist() == [3, 2, 0, 0, 0, 0, 0, 0]
+    assert row_of.reshape(-1).tolist() == [0, 1, MO.PAD, 2, -1, -1, MO.PAD + 1]      # tokens 4 and 5 overflow expert 0
+
+    # route every token to expert 0: only the first three survive
+    with torch.no_grad():
+        moe.router.layer.weight.zero_()
+        moe.router.layer.weight[0].fill_(1.0)
+    x = torch.rand(6, 1, args.hidden_size) + 0.5       # positive features: expert 0 has the largest logit
+    for grouped in (False, True):
+        moe.grouped = grouped
+        xi = x.clone().requires_grad_(True)
+        y, _ = moe(xi)
+        assert bool((y[3:] == 0).all()) and bool((y[:3].abs().sum(-1) > 0).all())
+        y.sum().backward()
+        assert bool((xi.grad[3:] == 0).all())
+
+
+def test_moe_min_capacity_and_overflow():
+    run_distributed(_moe_capacity_edges, 1)
+
+
 def _expert_tensor_parallel(rank, world):
     """Experts sharded over the tensor-parallel group against a dense statement with the full weights: outputs,
     input gradient, router gradient (replicated) and expert-weight gradients (the matching slices) agree."""

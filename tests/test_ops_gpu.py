@@ -170,6 +170,28 @@ def test_rope_strided(d, rot):
     _close(qkv.grad, qr.grad, 3e-2)
 
 
+@pytest.mark.parametrize("dtype,d,rot", [(torch.float32, 64, 64), (torch.float32, 80, 20), (torch.float32, 66, 6),
+                                         (torch.float16, 96, 24), (torch.float16, 128, 64), (torch.float16, 80, 20)])
+def test_rope_every_vector_width(dtype, d, rot):
+    """16-byte, 8-byte and scalar accesses (chosen from rot / 2, d - rot and the strides) give the same rotation."""
+    torch.manual_seed(0)
+    s, b, h = 17, 3, 5
+    x = torch.randn(s, b, h, d, device=DEV, dtype=dtype, requires_grad=True)
+    t = torch.arange(s, device=DEV).float()
+    inv = 1.0 / (10000 ** (torch.arange(0, rot, 2, device=DEV).float() / rot))
+    emb = torch.cat([torch.outer(t, inv)] * 2, dim=-1)
+    cos, sin = emb.cos()[:, None, None, :], emb.sin()[:, None, None, :]
+    y = OF.rope(x, cos, sin)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = OF.rope_ref(xr, cos, sin)
+    yr.backward(g.float())
+    tol = 1e-5 if dtype == torch.float32 else 4e-3
+    _close(y, yr, tol)
+    _close(x.grad, xr.grad, tol)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_cross_entropy(dtype):
     from gpt_neox_b200.parallel.cross_entropy import vocab_parallel_cross_entropy
