@@ -471,6 +471,98 @@ __global__ void __launch_bounds__(256) adam8bit_kernel(float* __restrict__ p, in
     }
 }
 
+// The same update with one WARP per block of 256 elements: a lane owns 8 consecutive elements (16-byte accesses to the
+// fp32 arrays, 8-byte accesses to the quantised states), the two maxima are warp shuffles, nothing goes through shared
+// memory.  Needs 16-byte aligned p / g / out and 8-byte aligned qm / qv; the caller checks.
+template <typename OUT>
+__global__ void __launch_bounds__(256) adam8bit_warp_kernel(float* __restrict__ p, int8_t* __restrict__ qm,
+                                                            uint8_t* __restrict__ qv, float* __restrict__ sm,
+                                                            float* __restrict__ sv, const float* __restrict__ g,
+                                                            OUT* __restrict__ out, long long n, long long nblocks,
+                                                            float lr, float b1, float b2, float eps, float wd, float bc1,
+                                                            float bc2, float gs, int adamw) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long blk = warp; blk < nblocks; blk += nwarps) {
+        const long long i0 = blk * 256 + lane * 8;
+        const bool full = i0 + 8 <= n;
+        float pv[8], gv[8];
+        if (full) {
+            const float4 p0 = *reinterpret_cast<const float4*>(p + i0), p1 = *reinterpret_cast<const float4*>(p + i0 + 4);
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(g + i0));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(g + i0 + 4));
+            pv[0] = p0.x, pv[1] = p0.y, pv[2] = p0.z, pv[3] = p0.w, pv[4] = p1.x, pv[5] = p1.y, pv[6] = p1.z, pv[7] = p1.w;
+            gv[0] = g0.x, gv[1] = g0.y, gv[2] = g0.z, gv[3] = g0.w, gv[4] = g1.x, gv[5] = g1.y, gv[6] = g1.z, gv[7] = g1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool live = i0 + j < n;
+                pv[j] = live ? p[i0 + j] : 0.f;
+                gv[j] = live ? g[i0 + j] : 0.f;
+            }
+        }
+        const uint2 um = *reinterpret_cast<const uint2*>(qm + i0);          // the states are padded to whole blocks
+        const uint2 uv = *reinterpret_cast<const uint2*>(qv + i0);
+        const int8_t* m8 = reinterpret_cast<const int8_t*>(&um);
+        const uint8_t* v8 = reinterpret_cast<const uint8_t*>(&uv);
+        const float smb = sm[blk] * (1.0f / 127.0f), svb = sv[blk];
+        float mi[8], vi[8], am = 0.f, vm = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float gi = gv[j] * gs;
+            if (!adamw && wd != 0.f) gi += wd * pv[j];
+            const float r = (float)v8[j] * (1.0f / 255.0f);
+            mi[j] = b1 * ((float)m8[j] * smb) + (1.f - b1) * gi;
+            vi[j] = b2 * (r * r * svb) + (1.f - b2) * gi * gi;
+            am = fmaxf(am, fabsf(mi[j]));
+            vm = fmaxf(vm, vi[j]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, o));
+        }
+        const float amax = fmaxf(am, 1e-30f), vmax = fmaxf(vm, 1e-38f);
+        uint2 om, ov;
+        int8_t* om8 = reinterpret_cast<int8_t*>(&om);
+        uint8_t* ov8 = reinterpret_cast<uint8_t*>(&ov);
+        __align__(16) OUT o16[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            om8[j] = (int8_t)__float2int_rn(mi[j] / amax * 127.0f);
+            ov8[j] = (uint8_t)__float2int_rn(sqrtf(vi[j] / vmax) * 255.0f);
+            float upd = (mi[j] / bc1) / (sqrtf(vi[j] / bc2) + eps);
+            if (adamw && wd != 0.f) upd += wd * pv[j];
+            pv[j] -= lr * upd;
+            o16[j] = from_f<OUT>(pv[j]);
+        }
+        *reinterpret_cast<uint2*>(qm + i0) = om;
+        *reinterpret_cast<uint2*>(qv + i0) = ov;
+        if (lane == 0) {
+            sm[blk] = amax;
+            sv[blk] = vmax;
+        }
+        if (full) {
+            *reinterpret_cast<float4*>(p + i0) = make_float4(pv[0], pv[1], pv[2], pv[3]);
+            *reinterpret_cast<float4*>(p + i0 + 4) = make_float4(pv[4], pv[5], pv[6], pv[7]);
+            if (out) {
+                constexpr int NV = 8 * (int)sizeof(OUT) / 16;
+#pragma unroll
+                for (int q = 0; q < NV; ++q)
+                    reinterpret_cast<uint4*>(out + i0)[q] = reinterpret_cast<const uint4*>(o16)[q];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + j < n) {
+                    p[i0 + j] = pv[j];
+                    if (out) out[i0 + j] = o16[j];
+                }
+        }
+    }
+}
+
 template <typename OUT>
 __global__ void __launch_bounds__(256) lion_kernel(float* __restrict__ p, float* __restrict__ m,
                                                    const float* __restrict__ g, OUT* __restrict__ out, long long n,
@@ -648,6 +740,20 @@ int neox_adam8bit_step(float* p, void* qm, void* qv, float* sm, float* sv, const
     const unsigned grid = (unsigned)blocks;
     int8_t* m8 = static_cast<int8_t*>(qm);
     uint8_t* v8 = static_cast<uint8_t*>(qv);
+    if (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+        ((reinterpret_cast<uintptr_t>(qm) | reinterpret_cast<uintptr_t>(qv)) & 7) == 0) {
+        const unsigned wgrid = (unsigned)((blocks + 7) / 8);             // one warp per block of 256 elements
+        if (!out || out_dtype == 1)
+            adam8bit_warp_kernel<float><<<wgrid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (float*)out, n, blocks, lr, b1, b2,
+                                                               eps, wd, bc1, bc2, gs, adamw);
+        else if (out_dtype == 0)
+            adam8bit_warp_kernel<__nv_bfloat16><<<wgrid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (__nv_bfloat16*)out, n, blocks,
+                                                                       lr, b1, b2, eps, wd, bc1, bc2, gs, adamw);
+        else
+            adam8bit_warp_kernel<__half><<<wgrid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (__half*)out, n, blocks, lr, b1, b2,
+                                                                eps, wd, bc1, bc2, gs, adamw);
+        return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    }
     if (!out || out_dtype == 1)
         adam8bit_kernel<float><<<grid, 256, 0, st>>>(p, m8, v8, sm, sv, g, (float*)out, n, lr, b1, b2, eps, wd, bc1, bc2,
                                                      gs, adamw);

@@ -742,6 +742,14 @@ def test_adam8bit_tracks_fp32_adam():
         og.step()
     _close(pg.detach().cpu(), pc.detach(), 2e-3, rtol=1e-3)
     assert (og.state[pg]["qm"].cpu().int() - oc.state[pc]["qm"].int()).abs().max().item() <= 1
+    # the 16-bit model copy written by the same kernel is the rounded fp32 parameter, tail block included
+    pm = torch.nn.Parameter(torch.zeros(n, device=DEV))
+    pm.model_out = torch.full((n,), 7.0, device=DEV, dtype=torch.bfloat16)
+    om = Adam8bit([pm], lr=5e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    for _ in range(3):
+        pm.grad = torch.randn(n, device=DEV)
+        om.step()
+    assert torch.equal(pm.model_out, pm.detach().bfloat16())
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
