@@ -186,6 +186,10 @@ def main():
     sc = bf(4, 16, 2048, 2048)
     run("causal_softmax_fwd", lambda: OF.scaled_upper_triang_masked_softmax(sc.view(-1, 2048, 2048), 1.0),
         nbytes=2.0 * sc.numel() * 2)
+    scg = sc.view(-1, 2048, 2048).detach().requires_grad_(True)
+    ysm = OF.scaled_upper_triang_masked_softmax(scg, 1.0)
+    gsm = torch.randn_like(ysm)
+    run("causal_softmax_bwd", lambda: torch.autograd.grad(ysm, scg, gsm, retain_graph=True), nbytes=3.0 * sc.numel() * 2)
     V = 50432
     logits = bf(T, V)
     tgt = torch.randint(0, V, (T,), device=dev)

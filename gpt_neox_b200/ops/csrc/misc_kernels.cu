@@ -129,6 +129,126 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const T* __restrict__ 
     }
 }
 
+// Rows of up to 2048 16-bit elements: one WARP per row, the row held in registers as NC chunks of 8 elements per lane
+// (16-byte accesses, all of a lane's loads issued before the first use), maxima and sums by shuffles.  Chunks that lie
+// wholly behind the causal limit are never read.  Needs sk % 8 == 0, sk <= 256 * NC, 16-byte aligned x / y and an
+// 8-byte aligned mask; the caller checks.  Same arithmetic as softmax_fwd_kernel.
+template <typename T, int NC>
+__global__ void __launch_bounds__(256) softmax_fwd_warp_kernel(const T* __restrict__ x, const uint8_t* __restrict__ mask,
+                                                               T* __restrict__ y, long long rows, int sq, int sk,
+                                                               int heads, int mask_batches, float scale, int causal) {
+    const int lane = threadIdx.x & 31;
+    const int nchunk = sk >> 3;
+    const int wpc = blockDim.x >> 5;                                     // warps (= rows in flight) per CTA
+    const long long wstride = (long long)gridDim.x * wpc;
+    for (long long row = (long long)blockIdx.x * wpc + (threadIdx.x >> 5); row < rows; row += wstride) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + row * sk);
+        uint4* yr = reinterpret_cast<uint4*>(y + row * sk);
+        const int q = (int)(row % sq);
+        const uint2* mr = nullptr;
+        if (mask) {
+            const long long b = row / ((long long)heads * sq);
+            mr = reinterpret_cast<const uint2*>(mask + ((mask_batches == 1 ? 0 : b) * sq + q) * (long long)sk);
+        }
+        const int limit = causal ? q + 1 : sk;
+        uint4 raw[NC];
+        uint2 mraw[NC];
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int ch = lane + j * 32;
+            const bool live = ch < nchunk && ch * 8 < limit;
+            raw[j] = live ? __ldg(xr + ch) : make_uint4(0, 0, 0, 0);
+            mraw[j] = (live && mr) ? __ldg(mr + ch) : make_uint2(0, 0);
+        }
+        float v[NC][8];
+        float mx = -FLT_MAX;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int c0 = (lane + j * 32) * 8;
+            const T* e = reinterpret_cast<const T*>(&raw[j]);
+            const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mraw[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float t = to_f<T>(e[i]) * scale;
+                if (mb[i]) t = -10000.0f;
+                v[j][i] = (c0 + i < limit) ? t : -FLT_MAX;        // limit <= sk, so dead chunks land here too
+                mx = fmaxf(mx, v[j][i]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int c0 = (lane + j * 32) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[j][i] = (c0 + i < limit) ? __expf(v[j][i] - mx) : 0.f;
+                s += v[j][i];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float inv = 1.0f / s;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int ch = lane + j * 32;
+            if (ch < nchunk) {
+                uint4 o;
+                T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) oe[i] = from_f<T>(v[j][i] * inv);
+                yr[ch] = o;
+            }
+        }
+    }
+}
+
+// Backward of the same rows: dx = scale * y * (g - sum(g * y)); g and y stay packed in registers between the passes.
+template <typename T, int NC>
+__global__ void __launch_bounds__(256) softmax_bwd_warp_kernel(const T* __restrict__ g, const T* __restrict__ y,
+                                                               T* __restrict__ dx, long long rows, int sk, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int nchunk = sk >> 3;
+    const int wpc = blockDim.x >> 5;                                     // warps (= rows in flight) per CTA
+    const long long wstride = (long long)gridDim.x * wpc;
+    for (long long row = (long long)blockIdx.x * wpc + (threadIdx.x >> 5); row < rows; row += wstride) {
+        const uint4* gr = reinterpret_cast<const uint4*>(g + row * sk);
+        const uint4* yr = reinterpret_cast<const uint4*>(y + row * sk);
+        uint4* dr = reinterpret_cast<uint4*>(dx + row * sk);
+        uint4 graw[NC], yraw[NC];
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int ch = lane + j * 32;
+            graw[j] = ch < nchunk ? __ldg(gr + ch) : make_uint4(0, 0, 0, 0);
+            yraw[j] = ch < nchunk ? __ldg(yr + ch) : make_uint4(0, 0, 0, 0);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const T* ge = reinterpret_cast<const T*>(&graw[j]);
+            const T* ye = reinterpret_cast<const T*>(&yraw[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s += to_f<T>(ge[i]) * to_f<T>(ye[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int ch = lane + j * 32;
+            if (ch < nchunk) {
+                const T* ge = reinterpret_cast<const T*>(&graw[j]);
+                const T* ye = reinterpret_cast<const T*>(&yraw[j]);
+                uint4 o;
+                T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) oe[i] = from_f<T>(scale * to_f<T>(ye[i]) * (to_f<T>(ge[i]) - s));
+                dr[ch] = o;
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ rotary
 // x: [s, b, h, d] with element strides (ss, sb, sh) and unit stride on d; out: contiguous [s, b, h, d].
 // First `rot` dims rotated with cos/sin [s, rot] (fp32), remaining dims copied.
@@ -618,6 +738,13 @@ int row_grid(long long rows) {
         else { using T = __half; CALL; }                   \
     } while (0)
 
+// 16-bit types only (dtype 0 = bf16, 2 = fp16)
+#define DISPATCH16(dtype, CALL)                            \
+    do {                                                   \
+        if (dtype == 0) { using T = __nv_bfloat16; CALL; } \
+        else { using T = __half; CALL; }                   \
+    } while (0)
+
 }  // namespace
 
 extern "C" {
@@ -626,6 +753,23 @@ int neox_softmax_fwd(const void* x, const void* mask, void* y, long long rows, i
                      int mask_batches, float scale, int causal, int dtype, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != 1 && sk % 8 == 0 && sk <= 2048 &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(mask) & 7) == 0) {
+        // the 8-chunk variant needs ~160 registers: 128-thread CTAs keep 12 warps per SM resident instead of 8
+        const int threads = sk <= 1024 ? 256 : 128;
+        const long long ctas = (rows + threads / 32 - 1) / (threads / 32);      // one pass: a warp per row
+        const unsigned grid = (unsigned)(ctas < 2147483647LL ? ctas : 2147483647LL);
+#define NEOX_SOFTMAX_FWD_WARP(NC)                                                                                      \
+    DISPATCH16(dtype, (softmax_fwd_warp_kernel<T, NC><<<grid, threads, 0, st>>>(                                           \
+                          (const T*)x, (const uint8_t*)mask, (T*)y, rows, sq, sk, heads, mask_batches, scale, causal)))
+        if (sk <= 256) NEOX_SOFTMAX_FWD_WARP(1);
+        else if (sk <= 512) NEOX_SOFTMAX_FWD_WARP(2);
+        else if (sk <= 1024) NEOX_SOFTMAX_FWD_WARP(4);
+        else NEOX_SOFTMAX_FWD_WARP(8);
+#undef NEOX_SOFTMAX_FWD_WARP
+        return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    }
     const int threads = sk <= 512 ? 64 : 256;
     DISPATCH(dtype, (softmax_fwd_kernel<T><<<row_grid(rows), threads, 0, st>>>(
                         (const T*)x, (const uint8_t*)mask, (T*)y, rows, sq, sk, heads, mask_batches, scale, causal)));
@@ -635,6 +779,21 @@ int neox_softmax_bwd(const void* g, const void* y, void* dx, long long rows, int
                      void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != 1 && sk % 8 == 0 && sk <= 2048 &&
+        ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0) {
+        const int threads = sk <= 1024 ? 256 : 128;
+        const long long ctas = (rows + threads / 32 - 1) / (threads / 32);      // one pass: a warp per row
+        const unsigned grid = (unsigned)(ctas < 2147483647LL ? ctas : 2147483647LL);
+#define NEOX_SOFTMAX_BWD_WARP(NC)                                                                                      \
+    DISPATCH16(dtype, (softmax_bwd_warp_kernel<T, NC><<<grid, threads, 0, st>>>((const T*)g, (const T*)y, (T*)dx, rows,   \
+                                                                                sk, scale)))
+        if (sk <= 256) NEOX_SOFTMAX_BWD_WARP(1);
+        else if (sk <= 512) NEOX_SOFTMAX_BWD_WARP(2);
+        else if (sk <= 1024) NEOX_SOFTMAX_BWD_WARP(4);
+        else NEOX_SOFTMAX_BWD_WARP(8);
+#undef NEOX_SOFTMAX_BWD_WARP
+        return cudaGetLastError() == cudaSuccess ? 0 : NEOX_ERR_LAUNCH;
+    }
     const int threads = sk <= 512 ? 64 : 256;
     DISPATCH(dtype, (softmax_bwd_kernel<T><<<row_grid(rows), threads, 0, st>>>((const T*)g, (const T*)y, (T*)dx, rows,
                                                                               sk, scale)));

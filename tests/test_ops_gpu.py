@@ -135,10 +135,11 @@ def test_softmax(sk):
     _close(x.grad, xr.grad, 2e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("s", [16, 129, 2048])
-def test_causal_softmax(s):
+def test_causal_softmax(s, dtype):
     torch.manual_seed(0)
-    x = torch.randn(4, s, s, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    x = torch.randn(4, s, s, device=DEV, dtype=dtype, requires_grad=True)
     y = OF.scaled_upper_triang_masked_softmax(x, 0.5)
     g = torch.randn_like(y)
     y.backward(g)
