@@ -2,13 +2,39 @@
 document *i* of the ``pos`` corpus is paired with document *i* of the ``neg`` corpus; optional label and
 precomputed reference-log-probability side datasets.  Samples are one pair per item (``unpacked``) or pairs
 packed until the longer side would overflow (``pack_until_overflow``); ``packed`` is rejected because a pair
-must stay aligned."""
+must stay aligned.  The sample index (which documents make up sample *i*) is cached as ``.npy`` files next to the
+``pos`` corpus, like the index maps of the language-model dataset."""
 from __future__ import annotations
+
+import os
+import time
 
 import numpy as np
 import torch
+import torch.distributed as dist
 
 from ..utils import print_rank_0
+from .gpt2_dataset import _is_builder
+
+
+def _build_groups(docs, pos_sizes, neg_sizes, n, seq_length, pack_impl, rng):
+    """Documents of every sample as a flat array plus sample boundaries (sample i = doc_idx[start[i]:start[i + 1]])."""
+    if pack_impl == "unpacked":
+        reps = int(np.ceil(n / max(len(docs), 1)))
+        order = np.concatenate([rng.permutation(docs) for _ in range(max(reps, 1))])[:n]
+        return order.astype(np.int64), np.arange(len(order) + 1, dtype=np.int64)
+    doc_idx, starts, used = [], [0], 0
+    while len(starts) <= n:
+        for d in rng.permutation(docs):
+            need = int(max(pos_sizes[d], neg_sizes[d]))
+            if len(doc_idx) > starts[-1] and used + need > seq_length + 1:
+                starts.append(len(doc_idx))
+                used = 0
+                if len(starts) > n:
+                    break
+            doc_idx.append(int(d))
+            used += need
+    return np.asarray(doc_idx[:starts[n]], dtype=np.int64), np.asarray(starts[:n + 1], dtype=np.int64)
 
 
 class PairwiseDataset(torch.utils.data.Dataset):
@@ -19,34 +45,48 @@ class PairwiseDataset(torch.utils.data.Dataset):
         assert pack_impl != "packed", "Pairwise data cannot be 'packed': pairs must stay aligned"
         self.name, self.seq_length, self.pack_impl, self.allow_chopped = name, seq_length, pack_impl, allow_chopped
         self.pos, self.neg = pos_indexed_dataset, neg_indexed_dataset
+        self.indexed_dataset = self.pos            # what the weighting by number of documents counts
         self.pos_label, self.neg_label = pos_label_dataset, neg_label_dataset
         self.pos_ref, self.neg_ref = pos_ref_dataset, neg_ref_dataset
         assert np.min(documents) >= 0 and np.max(documents) < self.pos.sizes.shape[0]
         assert self.pos.sizes.shape[0] == self.neg.sizes.shape[0], "pos and neg corpora must have the same documents"
-        rng = np.random.RandomState(seed)
+        self.doc_idx, self.starts = np.zeros(0, dtype=np.int64), np.zeros(1, dtype=np.int64)
+        if not build_index_mappings:               # a first pass that only wants the document counts
+            return
         docs = [d for d in documents if allow_chopped or max(self.pos.sizes[d], self.neg.sizes[d]) <= seq_length + 1]
         n = num_samples if num_samples is not None else len(docs)
-        if pack_impl == "unpacked":
-            reps = int(np.ceil(n / max(len(docs), 1)))
-            order = np.concatenate([rng.permutation(docs) for _ in range(max(reps, 1))])[:n]
-            self.groups = [[int(d)] for d in order]
+        # the index is cached next to the data, keyed by everything it depends on; one rank builds, all load
+        base = f"{pos_data_prefix}_{name}_pairmap_{n}ns_{seq_length}sl_{seed}s_{pack_impl}pi" + \
+            ("_ac" if allow_chopped else "")
+        f_doc, f_start = base + "_doc_idx.npy", base + "_sample_idx.npy"
+        cache = os.path.isdir(os.path.dirname(os.path.abspath(str(pos_data_prefix)))) and \
+            os.path.isfile(str(pos_data_prefix) + ".idx")
+        if not cache:                              # in-memory corpora (tests, synthetic pairs): nothing to put it beside
+            self.doc_idx, self.starts = _build_groups(docs, self.pos.sizes, self.neg.sizes, n, seq_length, pack_impl,
+                                                      np.random.RandomState(seed))
         else:
-            self.groups, cur, used = [], [], 0
-            while len(self.groups) < n:
-                for d in rng.permutation(docs):
-                    need = int(max(self.pos.sizes[d], self.neg.sizes[d]))
-                    if cur and used + need > seq_length + 1:
-                        self.groups.append(cur)
-                        cur, used = [], 0
-                        if len(self.groups) >= n:
-                            break
-                    cur.append(int(d))
-                    used += need
-            self.groups = self.groups[:n]
-        print_rank_0(f"    {name}: {len(self.groups)} pairwise samples")
+            if _is_builder(use_shared_fs) and not (os.path.isfile(f_doc) and os.path.isfile(f_start)):
+                print_rank_0(" > WARNING: could not find pairwise index map files, building the indices ...")
+                t0 = time.time()
+                doc_idx, starts = _build_groups(docs, self.pos.sizes, self.neg.sizes, n, seq_length, pack_impl,
+                                                np.random.RandomState(seed))
+                np.save(f_doc, doc_idx, allow_pickle=True)
+                np.save(f_start, starts, allow_pickle=True)
+                print_rank_0(f" > elapsed time to build and save pairwise index mappings (seconds): "
+                             f"{time.time() - t0:4f}")
+            if dist.is_available() and dist.is_initialized():
+                dist.barrier()
+            self.doc_idx = np.load(f_doc, allow_pickle=True, mmap_mode="r")
+            self.starts = np.load(f_start, allow_pickle=True, mmap_mode="r")
+        print_rank_0(f"    {name}: {len(self)} pairwise samples")
+
+    @property
+    def groups(self):
+        """The documents of every sample, as lists."""
+        return [[int(d) for d in self.doc_idx[self.starts[i]:self.starts[i + 1]]] for i in range(len(self))]
 
     def __len__(self):
-        return len(self.groups)
+        return len(self.starts) - 1
 
     def _cat(self, ds, docs, pad, dtype):
         if ds is None:
@@ -58,7 +98,8 @@ class PairwiseDataset(torch.utils.data.Dataset):
         return arr[:L]
 
     def __getitem__(self, idx):
-        docs = self.groups[idx % len(self.groups)]
+        i = idx % len(self)
+        docs = [int(d) for d in self.doc_idx[self.starts[i]:self.starts[i + 1]]]
         out = {"pos": self._cat(self.pos, docs, 0, np.int64), "neg": self._cat(self.neg, docs, 0, np.int64)}
         if self.pos_label is not None:
             out["pos_label"] = self._cat(self.pos_label, docs, -100, np.int64)

@@ -50,6 +50,41 @@ def test_pairwise_dataset_keeps_pairs_aligned():
         PairwiseDataset("t", "p", np.arange(6), pos, neg, 4, 15, 1, pack_impl="packed")
 
 
+def test_pairwise_dataset_caches_its_index_beside_the_corpus(tmp_path):
+    """With corpora on disk the sample index is written once as ``.npy`` files and loaded afterwards; a dataset built
+    only for its document count (the weighting-by-documents first pass) builds no index."""
+    import glob
+    from gpt_neox_b200.data.indexed_dataset import MMapIndexedDatasetBuilder, make_dataset
+    from gpt_neox_b200.data.pairwise_dataset import PairwiseDataset
+    rng = np.random.default_rng(0)
+    docs = [rng.integers(1, 99, size=n) for n in (5, 9, 3, 12, 7, 4)]
+    for side, shift in (("pos", 0), ("neg", 100)):
+        b = MMapIndexedDatasetBuilder(str(tmp_path / side) + ".bin", dtype=np.uint16)
+        for d in docs:
+            b.add_item(np.asarray(d + shift, dtype=np.uint16))
+            b.end_document()
+        b.finalize(str(tmp_path / side) + ".idx")
+    pos, neg = make_dataset(str(tmp_path / "pos"), "mmap"), make_dataset(str(tmp_path / "neg"), "mmap")
+    mk = lambda **kw: PairwiseDataset("train_0", str(tmp_path / "pos"), np.arange(6), pos, neg, num_samples=5,
+                                      seq_length=15, seed=3, pack_impl="pack_until_overflow", **kw)
+    count_only = mk(build_index_mappings=False)
+    assert len(count_only) == 0 and count_only.indexed_dataset.sizes.shape[0] == 6
+    assert not glob.glob(str(tmp_path / "*pairmap*"))
+    first = mk()
+    files = sorted(glob.glob(str(tmp_path / "*pairmap*")))
+    assert len(files) == 2 and len(first) == 5
+    groups = first.groups
+    s = first[0]
+    live = s["pos"] > 0
+    assert np.array_equal(s["neg"][live], s["pos"][live] + 100)
+    # the second construction reads the files: swap two samples in the cached boundaries' documents and see it
+    doc_file = [f for f in files if f.endswith("_doc_idx.npy")][0]
+    saved = np.load(doc_file)
+    np.save(doc_file, saved[::-1].copy())
+    again = mk()
+    assert [d for g in again.groups for d in g] == [d for g in groups for d in g][::-1]
+
+
 def test_online_dataset_consumes_a_sampling_server():
     from gpt_neox_b200.data.online_dataset import OnlineDataset
     batch = {"prefix": [5, 6, 7], "completions": [[8, 9], [10], [11, 12, 13]], "rewards": [1.0, 0.0, 2.0]}
