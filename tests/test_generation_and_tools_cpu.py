@@ -102,6 +102,65 @@ def test_hf_conversion_round_trip(arch, tmp_path):
     run_distributed(_hf_round_trip, 1, arch, str(tmp_path))
 
 
+def _hf_export_variants(rank, world, tmp):
+    """Legacy MLP key spellings, a reward model, zero-filled biases, the tied-layernorm refusal and precision
+    detection of the native -> Hugging Face converter."""
+    import glob
+    from gpt_neox_b200.checkpointing import save_checkpoint
+    from gpt_neox_b200.tools.ckpts import convert_neox_to_hf as C
+    keys = ("num_layers", "hidden_size", "num_attention_heads", "max_position_embeddings", "rotary_pct",
+            "rotary_emb_base", "layernorm_epsilon", "rms_norm_epsilon", "gpt_j_residual", "no_weight_tying",
+            "padded_vocab_size", "model_parallel_size", "intermediate_size", "expansion_factor", "activation",
+            "mlp_multiple_of", "num_kv_heads", "use_bias_in_attn_linear", "init_method_std", "train_impl")
+    # ---- a reward model without MLP biases
+    args, model = _native_model({"save": tmp, "optimizer": None, "no_load_optim": True, "train_impl": "rm",
+                                 "use_bias_in_mlp": False, "no_weight_tying": True})
+    model.module.train_mode()
+    save_checkpoint(args, 1, model, None, None)
+    ckpt = os.path.join(tmp, "global_step1")
+    conf = {k: getattr(args, k) for k in keys}
+    tokens = torch.randint(1, args.padded_vocab_size, (2, args.seq_length))
+    pos = torch.arange(args.seq_length).unsqueeze(0).expand_as(tokens)
+    with torch.no_grad():
+        out = model.module((tokens, pos, None))
+        native = (out[0] if isinstance(out, tuple) else out).float()
+    hf = C.convert(ckpt, conf, architecture="neox", is_rm=True, pad_token_id=0)
+    hf.eval()
+    assert type(hf).__name__ == "GPTNeoXForSequenceClassification" and hf.config.num_labels == 1
+    assert float(hf.gpt_neox.layers[0].mlp.dense_h_to_4h.bias.abs().max()) == 0.0      # absent in training: zeros
+    with torch.no_grad():
+        score = hf(tokens).logits                          # the reward at the last token that is not padding
+    assert torch.allclose(score.reshape(-1), native.reshape(2, -1)[:, -1], atol=2e-4, rtol=1e-3)
+    # ---- the same checkpoint with the MLP keys spelt the old way converts to the same model
+    for f in glob.glob(os.path.join(ckpt, "*model_states.pt")):
+        sd = torch.load(f, map_location="cpu", weights_only=False)
+        inner = sd["module"] if "module" in sd else sd
+        for k in list(inner):
+            for new_name, old_name in (("mlp.linear1.", "mlp.dense_h_to_4h."), ("mlp.linear2.", "mlp.dense_4h_to_h.")):
+                if new_name in k:
+                    inner[k.replace(new_name, old_name)] = inner.pop(k)
+        torch.save(sd, f)
+    sequential = not os.path.exists(os.path.join(ckpt, "layer_00-model_00-model_states.pt"))
+    assert C.get_mlp_naming_convention(C.load_partitions(ckpt, 1, 2, sequential)) == "legacy"
+    hf_old = C.convert(ckpt, conf, architecture="neox", is_rm=True, pad_token_id=0)
+    for (k, a), (_, b) in zip(hf.state_dict().items(), hf_old.state_dict().items()):
+        assert torch.equal(a, b), k
+    # ---- refusals and detection
+    with pytest.raises(NotImplementedError):
+        C.create_config({**conf, "gpt_j_tied": True})
+    assert C.detect_precision({"fp16": {"enabled": True}}) == "fp16"
+    assert C.detect_precision({"bf16": {"enabled": True}}) == "bf16"
+    assert C.detect_precision({"precision": "bfloat16"}) == "bf16"
+    assert C.detect_precision({"fp16": {"enabled": True, "type": "bfloat16"}}) == "bf16"
+    assert C.detect_precision({}) == "fp32"
+    assert next(C.convert(ckpt, {**conf, "precision": "bfloat16"}, architecture="neox", is_rm=True, pad_token_id=0,
+                          precision="auto").parameters()).dtype == torch.bfloat16
+
+
+def test_hf_export_legacy_keys_reward_model_and_precision(tmp_path):
+    run_distributed(_hf_export_variants, 1, str(tmp_path))
+
+
 def test_annealing_lr_shapes():
     from gpt_neox_b200.learning_rates import AnnealingLR
 
