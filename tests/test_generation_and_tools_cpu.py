@@ -161,6 +161,35 @@ def test_hf_export_legacy_keys_reward_model_and_precision(tmp_path):
     run_distributed(_hf_export_variants, 1, str(tmp_path))
 
 
+def test_inspect_checkpoints_lists_selects_and_compares(tmp_path, capsys):
+    from argparse import Namespace
+    from gpt_neox_b200.tools.ckpts import inspect_checkpoints as I
+    a = {"module": {"sequential.2.w": torch.ones(2, 3), "sequential.10.w": torch.zeros(4)},
+         "args": Namespace(hidden_size=8), "iteration": 7, "lr": [0.1, 0.2]}
+    b = {"module": {"sequential.2.w": torch.ones(2, 3), "sequential.10.w": torch.full((4,), 0.5)},
+         "args": Namespace(hidden_size=8), "iteration": 9, "extra": "x"}
+    for d, obj in (("A", a), ("B", b)):
+        os.makedirs(tmp_path / d)
+        torch.save(obj, tmp_path / d / "mp_rank_00_model_states.pt")
+        torch.save({"k": torch.arange(3)}, tmp_path / d / "layer_10-model_00-model_states.pt")
+        torch.save({"k": torch.arange(3)}, tmp_path / d / "layer_2-model_00-model_states.pt")
+    files = [os.path.basename(f) for f in I.checkpoint_files(str(tmp_path / "A"))]
+    assert files.index("layer_2-model_00-model_states.pt") < files.index("layer_10-model_00-model_states.pt")
+    lines = I.describe(a)
+    assert "module/sequential.2.w: tensor (2, 3) float32" in lines and "args/hidden_size: int 8" in lines
+    assert I.describe(a, ["module/sequential.10.w"], stats=True)[0].startswith(
+        "module/sequential.10.w: tensor (4,) float32 min=0")
+    assert I.select(a, "lr/1") == 0.2
+    out, diffs = I.compare_objects(a, b, only_diffs=True)
+    assert diffs == 4 and any(l.startswith("! module/sequential.10.w: max |a - b| = 0.5") for l in out)
+    assert any(l.startswith("- lr") for l in out) and any(l.startswith("+ extra") for l in out)
+    assert I.main(["-c", f"{tmp_path / 'A'},{tmp_path / 'B'}", "-d"]) == 4
+    text = capsys.readouterr().out
+    assert "3 file(s) compared, 4 difference(s)" in text and "layer_2" not in text     # equal files stay silent with -d
+    I.main([str(tmp_path / "A" / "mp_rank_00_model_states.pt"), "--attributes", "iteration"])
+    assert "iteration: int 7" in capsys.readouterr().out
+
+
 def test_annealing_lr_shapes():
     from gpt_neox_b200.learning_rates import AnnealingLR
 
