@@ -53,6 +53,16 @@ class NeoXEngine:
         self.timers = None
         self.training = True
         self.is_pipe_parallel = False
+        # ``wall_clock_breakdown``: per-phase times of the engine, averaged over ``steps_per_print`` optimizer steps,
+        # printed by rank 0 and left in ``timer_values`` (milliseconds per step) for the training log.  The timers
+        # record CUDA events and are only resolved when they are printed, so they do not serialise the step.
+        self._breakdown = bool(getattr(neox_args, "wall_clock_breakdown", False))
+        self._steps_per_print = max(1, int(getattr(neox_args, "steps_per_print", None) or 10))
+        self._clock = None
+        self.timer_values = None
+        if self._breakdown:
+            from ..utils import Timers
+            self._clock = Timers()
 
     # ------------------------------------------------------------------ mode helpers
     def train(self, mode=True):
@@ -64,7 +74,29 @@ class NeoXEngine:
         return self.train(False)
 
     def __call__(self, *args, **kwargs):
-        return self.module(*args, **kwargs)
+        with self._timed("forward" if self.training else None):
+            return self.module(*args, **kwargs)
+
+    # ------------------------------------------------------------------ wall-clock breakdown
+    def wall_clock_breakdown(self):
+        return self._breakdown
+
+    def steps_per_print(self):
+        return self._steps_per_print
+
+    def _timed(self, name):
+        """Context manager that accumulates the enclosed region into timer ``name`` (no-op when disabled)."""
+        return _Region(self._clock(name) if (self._clock is not None and name) else None)
+
+    def _publish_breakdown(self):
+        """Called after every optimizer step: every ``steps_per_print`` steps resolve the timers."""
+        if self._clock is None or self.global_steps % self._steps_per_print:
+            return
+        self.timer_values = {name: t.elapsed(reset=True) * 1000.0 / self._steps_per_print
+                             for name, t in self._clock.timers.items()}
+        if not _dist_on() or dist.get_rank() == 0:
+            print("time (ms) per step | " + " | ".join(f"{k}: {v:.2f}" for k, v in self.timer_values.items()),
+                  flush=True)
 
     def parameters(self):
         return self.module.parameters()
@@ -95,7 +127,8 @@ class NeoXEngine:
         if self.optimizer is not None and self.is_gradient_accumulation_boundary() and \
                 hasattr(self.optimizer, "arm_overlap"):
             self.optimizer.arm_overlap()     # last micro-batch: reduce each bucket as soon as its gradients exist
-        scaled.backward(retain_graph=retain_graph)
+        with self._timed("backward"):
+            scaled.backward(retain_graph=retain_graph)
         if self.optimizer is not None and getattr(self.optimizer, "partition_grads", False):
             # ZeRO stage 2: gradients leave their transient full-size buffers after every micro-batch, so the
             # fix-ups that rewrite them (sequence-parallel norm gradients) run now, not at the step
@@ -116,11 +149,13 @@ class NeoXEngine:
         self._take_step()
 
     def _take_step(self):
-        self._pre_step_grad_sync()
+        with self._timed("backward_allreduce"):
+            self._pre_step_grad_sync()
         if self.store_gradients:
             self.stored_gradients = [p.main_grad.detach().clone() for b in self.optimizer.buckets for p in b.params
                                      if getattr(p, "main_grad", None) is not None]
-        ok = self.optimizer.step(grad_divisor=float(self.gas * self.dp_world_size))
+        with self._timed("step"):
+            ok = self.optimizer.step(grad_divisor=float(self.gas * self.dp_world_size))
         fp8.invalidate_weight_cache()          # the fused optimizer rewrites parameters through raw pointers
         if ok:
             if self.lr_scheduler is not None:
@@ -129,6 +164,7 @@ class NeoXEngine:
             self.skipped_steps += 1
         self.global_steps += 1
         self.global_samples += self.neox_args.train_batch_size
+        self._publish_breakdown()
 
     def zero_grad(self):
         if self.optimizer is not None:
@@ -145,6 +181,22 @@ class NeoXEngine:
         fp8.invalidate_weight_cache()
         return engine_load_checkpoint(self, load_dir, tag, load_optimizer_states, load_lr_scheduler_states,
                                       load_module_only, load_module_strict)
+
+
+class _Region:
+    """``with`` block around one timed phase; ``timer`` is a ``utils.Timer`` or None."""
+
+    def __init__(self, timer):
+        self.timer = timer
+
+    def __enter__(self):
+        if self.timer is not None:
+            self.timer.start()
+
+    def __exit__(self, *exc):
+        if self.timer is not None:
+            self.timer.stop()
+        return False
 
 
 # ============================================================================================== pipeline
@@ -454,7 +506,12 @@ class PipelineEngine(NeoXEngine):
                           -1)
 
         def fwd(recv):
-            inputs, labels = self._load_micro_batch(data_iter)
+            with self._timed("batch_input" if train else None):
+                inputs, labels = self._load_micro_batch(data_iter)
+            with self._timed("forward_microstep" if train else None):
+                return fwd_compute(inputs, labels, recv)
+
+        def fwd_compute(inputs, labels, recv):
             out = self._forward_micro(inputs, recv, state["tuple"])
             loss = None
             if last:
@@ -468,6 +525,10 @@ class PipelineEngine(NeoXEngine):
         bwd_count = [0]
 
         def bwd(out, loss, grads):
+            with self._timed("backward_microstep"):
+                bwd_compute(out, loss, grads)
+
+        def bwd_compute(out, loss, grads):
             bwd_count[0] += 1
             if bwd_count[0] == M and self.optimizer is not None and hasattr(self.optimizer, "arm_overlap"):
                 self.optimizer.arm_overlap()     # last micro-batch of the step on this stage
@@ -545,9 +606,11 @@ class PipelineEngine(NeoXEngine):
     # ------------------------------------------------------------------ public API
     def train_batch(self, data_iter=None):
         self.module.train()
-        loss, _ = self._exec(data_iter, train=True)
+        with self._timed("train_batch"):
+            loss, _ = self._exec(data_iter, train=True)
         if hasattr(self.module, "allreduce_tied_weight_gradients"):
-            self.module.allreduce_tied_weight_gradients()
+            with self._timed("backward_tied_allreduce"):
+                self.module.allreduce_tied_weight_gradients()
         self.micro_steps += self.gas
         if self.optimizer is not None:
             self._take_step()

@@ -110,9 +110,14 @@ def training_log(neox_args, timers, loss_dict, total_loss_dict, learning_rate, i
 
     log = lambda k, v: tb_wandb_log(k, v, iteration, neox_args.use_wandb, neox_args.tensorboard_writer,
                                     neox_args.comet_experiment)
+    # per-phase engine times (``wall_clock_breakdown``): fresh every ``steps_per_print`` optimizer steps
+    if getattr(model, "timer_values", None) and model.wall_clock_breakdown() and \
+            model.global_steps % model.steps_per_print() == 0:
+        for key, val in model.timer_values.items():
+            log(f"timers/{key}", val)
     log("train/learning_rate", learning_rate)
     for key, val in loss_dict.items():
-        log(f"train/{key}", float(val))
+        log(f"train/{key.replace(' ', '_')}", float(val))
     if neox_args.precision == "fp16":
         log("train/loss_scale", loss_scale)
     if noise_scale_logger is not None and getattr(noise_scale_logger, "noise_scale", None) is not None:
@@ -172,8 +177,12 @@ def training_log(neox_args, timers, loss_dict, total_loss_dict, learning_rate, i
             report_memory("after {} iterations".format(iteration))
             report_memory_flag = False
         if timers is not None:
-            names = [n for n in ("forward", "backward", "optimizer", "batch generator", "data loader")
-                     if n in timers.timers]
+            names = [n for n in ("forward", "backward", "backward-backward", "backward-allreduce",
+                                 "backward-master-grad", "backward-clip-grad", "optimizer", "batch generator",
+                                 "data loader") if n in timers.timers]
             if names:
+                # the timers hold CUDA events that are resolved here, once per interval, not at every step
+                if not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0:
+                    timers.write(names, iteration, normalizer=neox_args.log_interval)
                 timers.log(names, normalizer=neox_args.log_interval)
     return report_memory_flag

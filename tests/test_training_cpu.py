@@ -165,6 +165,44 @@ def test_pipeline_with_tied_embeddings_and_tp():
                                          "no_weight_tying": False}, None)
 
 
+def _wall_clock_breakdown(rank, world, cfg):
+    """``wall_clock_breakdown``: the engine publishes per-phase milliseconds every ``steps_per_print`` steps."""
+    args, model, opt, sched = _setup({**cfg, "global_num_gpus": world, "wall_clock_breakdown": True,
+                                      "steps_per_print": 2})
+    assert model.wall_clock_breakdown() and model.steps_per_print() == 2 and model.timer_values is None
+    _train(args, model, opt, sched, 1)
+    assert model.timer_values is None                         # published at multiples of steps_per_print only
+    _train(args, model, opt, sched, 1)
+    vals = model.timer_values
+    want = ({"train_batch", "forward_microstep", "backward_microstep", "batch_input", "step"}
+            if args.is_pipe_parallel else {"forward", "backward", "step"})
+    assert want <= set(vals), vals
+    assert all(v >= 0.0 for v in vals.values()) and vals["step"] > 0.0
+    if args.is_pipe_parallel:
+        assert vals["train_batch"] >= vals["forward_microstep"]
+    # the training log forwards them to the metric sinks as timers/<phase>
+    from gpt_neox_b200 import logging as L
+    from gpt_neox_b200.utils import Timers
+    seen = {}
+
+    class Writer:
+        def add_scalar(self, key, value, it):
+            seen[key] = value
+    args.tensorboard_writer = Writer()
+    timers = Timers()
+    timers("interval time").start()
+    L.training_log(args, timers, {"lm_loss": torch.tensor(1.0)}, {}, 1e-4, model.global_steps, 1.0, False, 0, model,
+                   opt, None)
+    if rank == 0:
+        assert "timers/step" in seen and "train/lm_loss" in seen
+
+
+@pytest.mark.parametrize("world,cfg", [(1, {}), (2, {"pipe_parallel_size": 2, "gradient_accumulation_steps": 2,
+                                                      "num_layers": 4})])
+def test_wall_clock_breakdown(world, cfg):
+    run_distributed(_wall_clock_breakdown, world, cfg)
+
+
 def _checkpoint(rank, world, cfg, save_dir):
     from gpt_neox_b200.checkpointing import load_checkpoint, save_checkpoint
     from gpt_neox_b200.parallel import mpu
