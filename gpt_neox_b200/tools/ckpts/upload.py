@@ -1,6 +1,6 @@
 #!/usr/bin/env python
-"""Upload a converted model directory to the Hugging Face hub (``tools/upload.py`` of the reference).
-Needs network access and ``huggingface_hub``; ``python -m gpt_neox_b200.tools.upload <repo> <branch> <dir>``."""
+"""Upload a converted model directory to the Hugging Face hub (``tools/ckpts/upload.py`` of the reference).
+Needs network access and ``huggingface_hub``; ``python -m gpt_neox_b200.tools.ckpts.upload <repo> <branch> <dir>``."""
 import os
 import sys
 
