@@ -109,7 +109,7 @@ class Bucket:
     """One contiguous (param, grad, master-shard) triple."""
 
     def __init__(self, params, group_opts, comm_group, comm_world, comm_rank, model_dtype, device, sharded,
-                 grad_dtype=torch.float32, partition_grads=False):
+                 grad_dtype=torch.float32, partition_grads=False, offload=False):
         # tensor-parallel-replicated parameters first: their squared norm is counted on TP rank 0 only
         rep = [p for p in params if not getattr(p, "model_parallel", False)]
         shd = [p for p in params if getattr(p, "model_parallel", False)]
@@ -164,11 +164,27 @@ class Bucket:
         self.lo = shard * self.rank if self.sharded else 0
         self.hi = self.lo + shard
         self.mixed = model_dtype != torch.float32
-        if self.mixed:
+        # optimizer-state offload (ZeRO-Offload): the fp32 master shard and the optimizer states live in host memory
+        # (pinned when the model is on a GPU); each step copies the reduced gradient shard down, runs the host
+        # optimizer, and copies the updated shard -- already rounded to bf16 by the host kernel when the model is
+        # bf16 -- back up into the parameter buffer
+        self.offload = bool(offload)
+        self.host_grad = self.host_out = None
+        if self.offload:
+            pin = torch.device(device).type == "cuda"
+            host = lambda dtype: torch.empty(shard, dtype=dtype, device="cpu", pin_memory=pin)
+            m = host(torch.float32)
+            m.copy_(self.flat_param[self.lo:self.hi])
+            self.master = torch.nn.Parameter(m)
+            self.host_grad = host(torch.float32)
+            self.host_out = host(torch.bfloat16) if model_dtype == torch.bfloat16 else None
+            self.master.model_out = self.host_out
+        elif self.mixed:
             self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi].float().clone())
+            self.master.model_out = self.flat_param[self.lo:self.hi]
         else:
             self.master = torch.nn.Parameter(self.flat_param[self.lo:self.hi])   # a view: updated in place
-        self.master.model_out = self.flat_param[self.lo:self.hi] if self.mixed else None
+            self.master.model_out = None
         self.grad_acc = torch.zeros(shard, dtype=torch.float32, device=device) if self.partition_grads else None
         self.partition_params = False      # ZeRO stage 3 (engine/zero3.py): flat_param is transient, param_shard persistent
         self.param_shard = None
@@ -401,14 +417,17 @@ class FlatMixedPrecisionOptimizer:
 
     def __init__(self, param_groups, inner_cls, inner_defaults, model_dtype, zero_stage=0, clip_grad=0.0,
                  fp16_cfg=None, gradient_predivide_factor=1.0, prescale_gradients=False, device=None,
-                 overlap_comm=False, reduce_bucket_size=None):
+                 overlap_comm=False, reduce_bucket_size=None, offload_optimizer=False):
         """``overlap_comm``: split every parameter group into buckets of at most ``reduce_bucket_size`` elements (in
         model order), start each bucket's data-parallel gradient reduction on a side stream as soon as the LAST
         micro-batch's backward has produced all of its gradients, and all-gather the updated parameter shards
         asynchronously, each layer waiting for its own bucket in a forward pre-hook
         (``zero_optimization.overlap_comm`` / ``reduce_bucket_size`` of the DeepSpeed ZeRO-1/2 config the reference
-        passes through)."""
+        passes through).  ``offload_optimizer``: keep the fp32 masters and the optimizer states in host memory and
+        run ``inner_cls`` there (``zero_optimization.cpu_offload`` / ``offload_optimizer.device: cpu``); ``inner_cls``
+        must accept host tensors (``optim.cpu_adam.CPUAdam``, ``torch.optim.Adam`` ...)."""
         self.zero_stage = int(zero_stage or 0)
+        self.offload_optimizer = bool(offload_optimizer)
         self.overlap_comm = bool(overlap_comm)
         self._armed = False
         self._comm_stream = None
@@ -454,7 +473,7 @@ class FlatMixedPrecisionOptimizer:
                         chunks.append(cur)
                 for chunk in chunks:
                     b = Bucket(chunk, opts, cg, cw, cr, model_dtype, dev, sharded=self.zero_stage >= 1,
-                               partition_grads=self.zero_stage >= 2)
+                               partition_grads=self.zero_stage >= 2, offload=self.offload_optimizer)
                     self.buckets.append(b)
                     inner_groups.append({"params": [b.master], **opts})
         self.optimizer = inner_cls(inner_groups, **inner_defaults)
@@ -654,8 +673,14 @@ class FlatMixedPrecisionOptimizer:
                 combined = scale * clip
         inv = 1.0 / combined
         for b, g in zip(self.buckets, self.optimizer.param_groups):
-            b.master.grad = b.grad_of_shard()
+            shard_grad = b.grad_of_shard()
+            if b.offload:
+                b.host_grad.copy_(shard_grad, non_blocking=True)
+                shard_grad = b.host_grad
+            b.master.grad = shard_grad
             g["grad_scale"] = inv
+        if self.offload_optimizer and torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()      # the gradient shards have landed in host memory
         if getattr(self.optimizer, "supports_grad_scale", False):
             self.optimizer.step()
         else:
@@ -664,7 +689,11 @@ class FlatMixedPrecisionOptimizer:
                     b.master.grad.mul_(inv)
             self.optimizer.step()
         for b in self.buckets:
-            if b.mixed and not getattr(self.optimizer, "writes_model_out", False):
+            if b.offload:
+                wrote_out = b.host_out is not None and getattr(self.optimizer, "writes_host_out", False)
+                (b.param_shard if b.partition_params else b.flat_param[b.lo:b.hi]).copy_(
+                    b.host_out if wrote_out else b.master.data, non_blocking=True)
+            elif b.mixed and not getattr(self.optimizer, "writes_model_out", False):
                 (b.param_shard if b.partition_params else b.flat_param[b.lo:b.hi]).copy_(b.master.data)
             b.master.grad = None
             if self.overlap_comm:
@@ -716,10 +745,10 @@ class FlatMixedPrecisionOptimizer:
                 # stage 3: called with the parameters resident (checkpointing wraps the load in all_resident())
                 assert b.flat_param is not None, "refresh_master_from_params under ZeRO stage 3 needs resident parameters"
                 b.param_shard.copy_(b.flat_param[b.lo:b.hi])
-                if b.mixed:
+                if b.mixed or b.offload:
                     b.master.data.copy_(b.param_shard.float())
                 continue
-            if b.mixed:
+            if b.mixed or b.offload:
                 b.master.data.copy_(b.flat_param[b.lo:b.hi].float())
 
 

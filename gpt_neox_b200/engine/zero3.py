@@ -43,7 +43,9 @@ class ParamPartitioner:
         self.gathers = 0
         for b in self.buckets:
             b.param_shard = b.flat_param[b.lo:b.hi].clone()
-            if b.mixed:
+            if getattr(b, "offload", False):
+                pass                                # host masters: the step copies the updated shard up itself
+            elif b.mixed:
                 b.master.model_out = b.param_shard
             else:
                 b.master.data = b.param_shard       # fp32 training: the shard IS the master (same Parameter object,

@@ -299,13 +299,25 @@ def get_model(neox_args, use_cache=False):
     return model
 
 
+def optimizer_offload(neox_args) -> bool:
+    """Whether the fp32 masters and optimizer states live in host memory: a host optimizer type, or the ZeRO
+    configuration asks for it (``cpu_offload: true``, or ``offload_optimizer: {device: cpu}``)."""
+    z = neox_args.zero_optimization or {}
+    off = z.get("offload_optimizer") or {}
+    return bool(z.get("cpu_offload")) or str(off.get("device", "none")).lower() == "cpu" or \
+        neox_args.optimizer_type.lower() in ("cpu_adam", "cpu_torch_adam")
+
+
 def _inner_optimizer(neox_args):
     """(class, kwargs) of the element-wise optimizer that updates the flat fp32 shards."""
     name = neox_args.optimizer_type.lower()
     params = dict(neox_args.optimizer.get("params", {}))
     params.pop("freeze_step", None) if name != "onebitadam" else None
     if name in ("adam", "cpu_adam", "cpu_torch_adam", "onebitadam"):
-        if name == "cpu_adam":
+        if name == "cpu_torch_adam":
+            params.pop("cuda_aware", None)
+            return torch.optim.Adam, dict(weight_decay=neox_args.weight_decay, **params)
+        if name == "cpu_adam" or (name == "adam" and optimizer_offload(neox_args)):
             from .optim.cpu_adam import CPUAdam
             return CPUAdam, dict(weight_decay=neox_args.weight_decay, **params)
         if name == "onebitadam":
@@ -372,7 +384,8 @@ def get_optimizer(model, neox_args, dummy=False):
                                             zero_stage=neox_args.zero_stage if isinstance(neox_args.zero_stage, int) else 0,
                                             clip_grad=neox_args.gradient_clipping, fp16_cfg=fp16_cfg,
                                             overlap_comm=bool((neox_args.zero_optimization or {}).get("overlap_comm", False)),
-                                            reduce_bucket_size=neox_args.zero_reduce_bucket_size)
+                                            reduce_bucket_size=neox_args.zero_reduce_bucket_size,
+                                            offload_optimizer=optimizer_offload(neox_args))
     if getattr(optimizer, "overlap_comm", False):
         # each layer waits only for the all-gather of its own parameters
         optimizer.install_param_wait_hooks(model)

@@ -102,3 +102,28 @@ def test_block_sparse_attention_matches_the_dense_masked_statement(kind, cfg):
     ref.backward(g)
     for a, r in zip(got, (ref.detach(), q.grad, k.grad, v.grad)):
         torch.testing.assert_close(a, r, atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("adamw", [True, False])
+def test_cpu_adam_host_kernel_matches_torch(adamw):
+    """The OpenMP / AVX2 host kernel against torch's Adam / AdamW: host parameters are updated in place, the bf16
+    copy is the rounded parameter, a gradient scale is folded in."""
+    from gpt_neox_b200.optim.cpu_adam import CPUAdam
+    torch.manual_seed(0)
+    n = 1000 + 37
+    p = torch.nn.Parameter(torch.randn(n))
+    q = torch.nn.Parameter(p.detach().clone())
+    p.model_out = torch.zeros(n, dtype=torch.bfloat16)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ours = CPUAdam([p], adamw_mode=adamw, **kw)
+    ref = (torch.optim.AdamW if adamw else torch.optim.Adam)([q], **kw)
+    ours.param_groups[0]["grad_scale"] = 0.5
+    storage = p.data_ptr()
+    for _ in range(5):
+        g = torch.randn(n)
+        p.grad, q.grad = g * 2.0, g.clone()               # the scale of 0.5 undoes the factor
+        ours.step()
+        ref.step()
+    assert p.data_ptr() == storage and "host_param" not in ours.state[p]
+    torch.testing.assert_close(p.detach(), q.detach(), atol=2e-6, rtol=1e-5)
+    assert torch.equal(p.model_out, p.detach().bfloat16())

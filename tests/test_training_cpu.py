@@ -80,6 +80,51 @@ def test_zero1_matches_zero0(tmp_path):
     assert all(abs(x - y) < 1e-4 for x, y in zip(l0, l1)), (l0, l1)
 
 
+@pytest.mark.parametrize("extra", [
+    {"zero_optimization": {"stage": 1, "cpu_offload": True}},
+    {"zero_optimization": {"stage": 2, "offload_optimizer": {"device": "cpu", "pin_memory": True},
+                           "reduce_bucket_size": 20000}, "precision": "bfloat16"},
+    {"zero_optimization": {"stage": 3, "cpu_offload": True, "reduce_bucket_size": 20000}},
+    {"zero_optimization": {"stage": 1}, "weight_decay": 0.0,
+     "optimizer": {"type": "cpu_torch_adam", "params": {"lr": 1e-3, "betas": [0.9, 0.95], "eps": 1e-8}}},
+])
+def test_optimizer_state_offload_matches_device_states(extra, tmp_path):
+    """Masters and Adam states in host memory, updated by the C++ host kernel (or torch's Adam): the same losses as
+    the device-resident optimizer at every ZeRO stage, in fp32 and bf16 (where the host kernel also produces the
+    rounded 16-bit shard that is copied back)."""
+    a, b = str(tmp_path / "dev.json"), str(tmp_path / "host.json")
+    base = {k: v for k, v in extra.items() if k != "optimizer"}
+    zero = dict(base.get("zero_optimization", {}))
+    zero.pop("cpu_offload", None)
+    zero.pop("offload_optimizer", None)
+    if "optimizer" in extra:              # torch's Adam on host masters against the device Adam, same settings
+        base["optimizer"] = {"type": "Adam", "params": extra["optimizer"]["params"]}
+    run_distributed(_loss_decreases, 2, {**base, "zero_optimization": zero}, a)
+    run_distributed(_loss_decreases, 2, extra, b)
+    l0, l1 = json.load(open(a)), json.load(open(b))
+    tol = 2e-2 if extra.get("precision") == "bfloat16" else 1e-4
+    assert all(abs(x - y) < tol for x, y in zip(l0, l1)), (l0, l1)
+
+
+def _offload_layout(rank, world):
+    """Where things live with offload on: masters, gradients-for-the-step and optimizer states on the host."""
+    args, model, opt, sched = _setup({"global_num_gpus": world, "precision": "bfloat16",
+                                      "zero_optimization": {"stage": 1, "cpu_offload": True}})
+    from gpt_neox_b200.optim.cpu_adam import CPUAdam
+    assert opt.offload_optimizer and isinstance(opt.optimizer, CPUAdam)
+    _train(args, model, opt, sched, 2)
+    for b in opt.buckets:
+        assert b.offload and b.master.device.type == "cpu" and b.host_out.dtype == torch.bfloat16
+        st = opt.optimizer.state[b.master]
+        assert st["exp_avg"].device.type == "cpu" and "host_param" not in st     # updated in place
+        # the parameter buffer holds exactly the bf16 rounding of the host master shard
+        assert torch.equal(b.flat_param[b.lo:b.hi].cpu(), b.master.data.bfloat16())
+
+
+def test_optimizer_state_offload_layout():
+    run_distributed(_offload_layout, 2)
+
+
 def _overlap_losses(rank, world, cfg, out):
     args, model, opt, sched = _setup({**cfg, "global_num_gpus": world})
     losses = _train(args, model, opt, sched, 8)
