@@ -375,6 +375,16 @@ class NeoXArgs:
                                                             project_name=self.comet_project)
             except ModuleNotFoundError:
                 print("comet_ml is not installed; continuing without Comet logging", flush=True)
+                return
+            exp = self.comet_experiment
+            if hasattr(exp, "log_parameters"):
+                exp.log_parameters(self._values(FIELDS.keys(), only_non_defaults=True))
+            if self.comet_experiment_name:
+                exp.set_name(self.comet_experiment_name)
+            if self.comet_tags:
+                exp.add_tags(self.comet_tags)
+            if self.comet_others:
+                exp.log_others(self.comet_others)
 
     # ------------------------------------------------------------------ logging
     def enable_logging(self):

@@ -13,6 +13,7 @@ formula (``megatron/logging.py:83-237``):
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -63,12 +64,53 @@ def human_readable_flops(num) -> str:
     return "%.1f%s" % (num, "Yi")
 
 
+class CsvMonitor:
+    """The ``csv_monitor`` block of the DeepSpeed configuration (``{"enabled": true, "output_path": ..., "job_name":
+    ...}``): every scalar goes to ``<output_path>/<job_name>/<key with / as _>.csv`` as ``step,value`` lines."""
+
+    def __init__(self, cfg):
+        cfg = cfg or {}
+        self.enabled = bool(cfg.get("enabled", False))
+        self.dir = os.path.join(cfg.get("output_path") or "csv_monitor", cfg.get("job_name") or "DeepSpeedJobName")
+        self._files = {}
+
+    def log(self, key, value, step):
+        if not self.enabled:
+            return
+        fh = self._files.get(key)
+        if fh is None:
+            os.makedirs(self.dir, exist_ok=True)
+            path = os.path.join(self.dir, key.replace("/", "_").replace(" ", "_") + ".csv")
+            new = not os.path.exists(path)
+            fh = self._files[key] = open(path, "a", buffering=1)
+            if new:
+                fh.write(f"step,{key}\n")
+        fh.write(f"{int(step)},{float(value)}\n")
+
+    def close(self):
+        for fh in self._files.values():
+            fh.close()
+        self._files = {}
+
+
+_csv_monitor = CsvMonitor(None)
+
+
+def configure_csv_monitor(cfg):
+    """Install the CSV sink that ``tb_wandb_log`` also writes to (rank 0); returns it."""
+    global _csv_monitor
+    _csv_monitor.close()
+    _csv_monitor = CsvMonitor(cfg)
+    return _csv_monitor
+
+
 def tb_wandb_log(key, value, iteration_no, use_wandb, tensorboard_writer=None, comet_experiment=None,
                  all_ranks=False):
     """Send one scalar to every enabled sink (rank 0 only unless ``all_ranks``)."""
     do_log = (dist.get_rank() == 0 if dist.is_available() and dist.is_initialized() else True) or all_ranks
     if not do_log or value is None:
         return
+    _csv_monitor.log(key, value, iteration_no)
     if tensorboard_writer:
         tensorboard_writer.add_scalar(key, value, iteration_no)
     if use_wandb:

@@ -410,6 +410,36 @@ def get_learning_rate_scheduler(optimizer, neox_args):
                        override_lr_scheduler=neox_args.override_lr_scheduler, use_mup=neox_args.use_mup)
 
 
+def dump_engine_state(engine, neox_args):
+    """``dump_state``: what the engine was built with, printed once by rank 0 after initialisation."""
+    opt = engine.optimizer
+    rows = {
+        "engine": type(engine).__name__,
+        "world (data x pipe x model)": f"{mpu.get_data_parallel_world_size()} x {mpu.get_pipe_parallel_world_size()} "
+                                       f"x {mpu.get_model_parallel_world_size()}",
+        "train_batch_size": neox_args.train_batch_size,
+        "train_micro_batch_size_per_gpu": neox_args.train_micro_batch_size_per_gpu,
+        "gradient_accumulation_steps": neox_args.gradient_accumulation_steps,
+        "precision": neox_args.precision,
+        "gradient_clipping": neox_args.gradient_clipping,
+        "total_params": getattr(engine, "total_params", None),
+        "optimizer": type(getattr(opt, "optimizer", opt)).__name__ if opt is not None else None,
+        "zero_stage": getattr(opt, "zero_stage", None),
+        "overlap_comm": getattr(opt, "overlap_comm", None),
+        "offload_optimizer": getattr(opt, "offload_optimizer", None),
+        "buckets": len(getattr(opt, "buckets", []) or []),
+        "bucket elements (largest)": max((b.padded for b in getattr(opt, "buckets", []) or []), default=0),
+        "loss_scale": opt.cur_scale if opt is not None and hasattr(opt, "cur_scale") else None,
+        "lr_scheduler": type(engine.lr_scheduler).__name__ if engine.lr_scheduler is not None else None,
+        "wall_clock_breakdown": engine.wall_clock_breakdown(),
+        "steps_per_print": engine.steps_per_print(),
+    }
+    print_rank_0("engine state:")
+    for k, v in rows.items():
+        print_rank_0(f"  {k} {'.' * max(1, 34 - len(k))} {v}")
+    return rows
+
+
 def setup_model_and_optimizer(neox_args, use_cache=False, iteration=None):
     """Model, optimizer, scheduler, engine and (optionally) checkpoint restore.
     Returns ``(engine, optimizer, lr_scheduler, reference_model)``."""
@@ -438,8 +468,8 @@ def setup_model_and_optimizer(neox_args, use_cache=False, iteration=None):
             if iteration is not None and iteration > 0:
                 curr.update_difficulty(iteration)
         engine.set_batch_fn(partial(get_batch_pipe, neox_args=neox_args, curr_scheduler=curr))
-    else:
-        model.set_batch_fn(partial(get_batch_sequential, neox_args=neox_args)) if False else None
+    if neox_args.dump_state:
+        dump_engine_state(engine, neox_args)
     if neox_args.load is not None:
         neox_args.iteration = load_checkpoint(neox_args=neox_args, model=engine, optimizer=optimizer,
                                               lr_scheduler=lr_scheduler, iteration=iteration)
@@ -549,6 +579,8 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
     overflow_monitor = OverflowMonitor(optimizer)
     ds_cfg = neox_args.deepspeed_config
     comms = comms_logger.configure(neox_args.comms_logger or ds_cfg.get("comms_logger"))
+    from .logging import configure_csv_monitor
+    configure_csv_monitor(neox_args.csv_monitor or ds_cfg.get("csv_monitor"))
     flops_prof = FlopsProfiler.from_config(getattr(model, "module", model),
                                            neox_args.flops_profiler or ds_cfg.get("flops_profiler"))
     prof = None

@@ -391,3 +391,66 @@ def test_autotuner_runs_a_real_trial_through_the_launcher(tmp_path):
     best = Autotuner(args).tune()
     assert best is not None and best["exit_code"] == 0 and best["throughput"] > 0 and best["latency"] > 0
     assert json.load(open(tmp_path / "exps" / "z0_mbs1" / "metric.json"))["tokens_per_sec"] > 0
+
+
+def test_csv_monitor_sink_and_comet_settings(tmp_path, monkeypatch):
+    """``csv_monitor`` writes one ``step,value`` file per metric; the Comet experiment gets its name, tags, other
+    fields and the non-default configuration (against a stand-in ``comet_ml``)."""
+    from gpt_neox_b200 import logging as L
+    mon = L.configure_csv_monitor({"enabled": True, "output_path": str(tmp_path), "job_name": "job"})
+    try:
+        for it, v in ((1, 2.5), (2, 2.25)):
+            L.tb_wandb_log("train/lm_loss", v, it, use_wandb=False)
+        L.tb_wandb_log("runtime/tokens_per_sec", 1000.0, 2, use_wandb=False)
+    finally:
+        mon.close()
+        L.configure_csv_monitor(None)
+    rows = open(tmp_path / "job" / "train_lm_loss.csv").read().split()
+    assert rows == ["step,train/lm_loss", "1,2.5", "2,2.25"]
+    assert os.path.exists(tmp_path / "job" / "runtime_tokens_per_sec.csv")
+    L.tb_wandb_log("train/lm_loss", 1.0, 3, use_wandb=False)                 # disabled again: nothing is appended
+    assert len(open(tmp_path / "job" / "train_lm_loss.csv").read().split()) == 3
+
+    calls = {}
+
+    class Experiment:
+        def __init__(self, **kw):
+            calls["init"] = kw
+
+        def log_parameters(self, d):
+            calls["params"] = d
+
+        def set_name(self, n):
+            calls["name"] = n
+
+        def add_tags(self, t):
+            calls["tags"] = t
+
+        def log_others(self, o):
+            calls["others"] = o
+    monkeypatch.setitem(sys.modules, "comet_ml", types.SimpleNamespace(Experiment=Experiment))
+    args = make_args(use_comet=True, comet_workspace="ws", comet_project="proj", comet_experiment_name="run-7",
+                     comet_tags=["b200", "125M"], comet_others={"note": "x"})
+    args.rank = 0
+    args.initialize_comet()
+    assert calls["init"] == {"workspace": "ws", "project_name": "proj"} and calls["name"] == "run-7"
+    assert calls["tags"] == ["b200", "125M"] and calls["others"] == {"note": "x"}
+    assert calls["params"]["comet_project"] == "proj"
+
+
+def _dump_state(rank, world):
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.training import setup_model_and_optimizer
+    args = make_args(global_num_gpus=world, dump_state=True, zero_optimization={"stage": 1})
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    engine, *_ = setup_model_and_optimizer(args)
+    from gpt_neox_b200.training import dump_engine_state
+    rows = dump_engine_state(engine, args)
+    assert rows["engine"] == "NeoXEngine" and rows["zero_stage"] == 1 and rows["buckets"] >= 1
+    assert rows["optimizer"] == "FusedAdam" and rows["total_params"] == engine.total_params
+
+
+def test_dump_state_prints_the_engine_configuration(capfd):
+    run_distributed(_dump_state, 1)
+    assert "engine state:" in capfd.readouterr().out
