@@ -549,11 +549,11 @@ class FlatMixedPrecisionOptimizer:
 
     param_partitioner = None
 
-    def enable_param_partitioning(self, model):
+    def enable_param_partitioning(self, model, offload_param=False):
         """ZeRO stage 3: keep only this rank's shard of every parameter bucket between uses (engine/zero3.py)."""
         from .zero3 import ParamPartitioner
         if self.param_partitioner is None and self.partition_grads:
-            self.param_partitioner = ParamPartitioner(self).install(model)
+            self.param_partitioner = ParamPartitioner(self, offload_param=offload_param).install(model)
         return self.param_partitioner
 
     def end_micro_batch(self):

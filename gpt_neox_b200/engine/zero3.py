@@ -34,8 +34,13 @@ def _layers(module):
 
 
 class ParamPartitioner:
-    def __init__(self, optimizer):
+    def __init__(self, optimizer, offload_param=False):
+        """``offload_param``: keep the persistent 16-bit shards in (pinned) host memory as well -- the
+        ``zero_optimization.offload_param`` of the reference's DeepSpeed configuration; a gather then starts with a
+        host-to-device copy of the shard.  Needs the optimizer states offloaded too (the host optimizer is what
+        writes the updated shard)."""
         self.opt = optimizer
+        self.offload_param = bool(offload_param)
         self.buckets = [b for b in optimizer.buckets if b.partition_grads]     # the data-parallel sharded ones
         self.resident = []          # buckets whose full buffer exists, least recently used first
         self.pinned = False         # True inside all_resident(): nothing is released
@@ -43,6 +48,14 @@ class ParamPartitioner:
         self.gathers = 0
         for b in self.buckets:
             b.param_shard = b.flat_param[b.lo:b.hi].clone()
+            if self.offload_param:
+                assert getattr(b, "offload", False), \
+                    "offload_param needs the optimizer states offloaded as well (zero_optimization.cpu_offload / " \
+                    "offload_optimizer.device: cpu)"
+                host = torch.empty(b.param_shard.shape, dtype=b.param_shard.dtype, device="cpu",
+                                   pin_memory=b.param_shard.is_cuda)
+                host.copy_(b.param_shard)
+                b.param_shard = host
             if getattr(b, "offload", False):
                 pass                                # host masters: the step copies the updated shard up itself
             elif b.mixed:
@@ -60,8 +73,10 @@ class ParamPartitioner:
         return torch.empty(1, dtype=p.dtype, device=p.device).expand(p.shape)
 
     def _gather(self, b):
-        full = torch.empty(b.padded, dtype=b.param_shard.dtype, device=b.param_shard.device)
-        dist.all_gather_into_tensor(full, b.param_shard, group=b.comm_group)
+        dev = torch.device(b.device)
+        shard = b.param_shard if b.param_shard.device.type == dev.type else b.param_shard.to(dev, non_blocking=True)
+        full = torch.empty(b.padded, dtype=shard.dtype, device=dev)
+        dist.all_gather_into_tensor(full, shard, group=b.comm_group)
         b.flat_param = full
         for p, o in zip(b.params, b.offsets):
             p.data = full[o:o + p.numel()].view(p.shape)

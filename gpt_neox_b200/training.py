@@ -390,7 +390,8 @@ def get_optimizer(model, neox_args, dummy=False):
         # each layer waits only for the all-gather of its own parameters
         optimizer.install_param_wait_hooks(model)
     if optimizer.zero_stage >= 3:
-        optimizer.enable_param_partitioning(model)
+        off = (neox_args.zero_optimization or {}).get("offload_param") or {}
+        optimizer.enable_param_partitioning(model, offload_param=str(off.get("device", "none")).lower() == "cpu")
     return optimizer, groups
 
 

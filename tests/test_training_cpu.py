@@ -85,6 +85,8 @@ def test_zero1_matches_zero0(tmp_path):
     {"zero_optimization": {"stage": 2, "offload_optimizer": {"device": "cpu", "pin_memory": True},
                            "reduce_bucket_size": 20000}, "precision": "bfloat16"},
     {"zero_optimization": {"stage": 3, "cpu_offload": True, "reduce_bucket_size": 20000}},
+    {"zero_optimization": {"stage": 3, "cpu_offload": True, "offload_param": {"device": "cpu"},
+                           "reduce_bucket_size": 20000}, "precision": "bfloat16"},
     {"zero_optimization": {"stage": 1}, "weight_decay": 0.0,
      "optimizer": {"type": "cpu_torch_adam", "params": {"lr": 1e-3, "betas": [0.9, 0.95], "eps": 1e-8}}},
 ])
@@ -97,6 +99,7 @@ def test_optimizer_state_offload_matches_device_states(extra, tmp_path):
     zero = dict(base.get("zero_optimization", {}))
     zero.pop("cpu_offload", None)
     zero.pop("offload_optimizer", None)
+    zero.pop("offload_param", None)
     if "optimizer" in extra:              # torch's Adam on host masters against the device Adam, same settings
         base["optimizer"] = {"type": "Adam", "params": extra["optimizer"]["params"]}
     run_distributed(_loss_decreases, 2, {**base, "zero_optimization": zero}, a)
