@@ -46,6 +46,9 @@ def _worker(rank, world, port, fn, fn_args, errq):
                       MASTER_PORT=str(port))
     sys.path.insert(0, ROOT)
     try:
+        # the models are tiny and several ranks (often several jobs) share the host: a full-width intra-op thread
+        # pool per rank only makes them fight for the cores
+        torch.set_num_threads(2)
         torch.manual_seed(0)
         fn(rank, world, *fn_args)
     except Exception:
@@ -78,3 +81,14 @@ def run_distributed(fn, world_size, *fn_args, timeout=300):
     assert not hung, f"{len(hung)} rank(s) did not finish within {timeout}s"
     assert not errs, "\n".join(f"[rank {r}]\n{tb}" for r, tb in errs)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+def run_distributed_many(*calls, timeout=300):
+    """Several independent ``run_distributed(fn, world, *args)`` jobs side by side (each with its own processes and
+    port): the baseline and the variant of a comparison do not have to wait for one another."""
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=len(calls)) as pool:
+        futures = [pool.submit(run_distributed, *c, timeout=timeout) for c in calls]
+        for f in futures:
+            f.result()
+

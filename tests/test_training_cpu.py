@@ -7,7 +7,7 @@ import os
 import pytest
 import torch
 
-from common import make_args, run_distributed
+from common import make_args, run_distributed, run_distributed_many
 
 
 def _setup(cfg):
@@ -74,8 +74,8 @@ def test_loss_decreases_single_process(cfg):
 
 def test_zero1_matches_zero0(tmp_path):
     a, b = str(tmp_path / "z0.json"), str(tmp_path / "z1.json")
-    run_distributed(_loss_decreases, 2, {"zero_optimization": {"stage": 0}}, a)
-    run_distributed(_loss_decreases, 2, {"zero_optimization": {"stage": 1}}, b)
+    run_distributed_many((_loss_decreases, 2, {"zero_optimization": {"stage": 0}}, a),
+                         (_loss_decreases, 2, {"zero_optimization": {"stage": 1}}, b))
     l0, l1 = json.load(open(a)), json.load(open(b))
     assert all(abs(x - y) < 1e-4 for x, y in zip(l0, l1)), (l0, l1)
 
@@ -102,8 +102,8 @@ def test_optimizer_state_offload_matches_device_states(extra, tmp_path):
     zero.pop("offload_param", None)
     if "optimizer" in extra:              # torch's Adam on host masters against the device Adam, same settings
         base["optimizer"] = {"type": "Adam", "params": extra["optimizer"]["params"]}
-    run_distributed(_loss_decreases, 2, {**base, "zero_optimization": zero}, a)
-    run_distributed(_loss_decreases, 2, extra, b)
+    run_distributed_many((_loss_decreases, 2, {**base, "zero_optimization": zero}, a),
+                         (_loss_decreases, 2, extra, b))
     l0, l1 = json.load(open(a)), json.load(open(b))
     tol = 2e-2 if extra.get("precision") == "bfloat16" else 1e-4
     assert all(abs(x - y) < tol for x, y in zip(l0, l1)), (l0, l1)
@@ -142,9 +142,9 @@ def test_zero1_overlapped_reduction_matches_plain(tmp_path):
     same losses as the reduce-at-step form, and the early path is really taken."""
     a, b = str(tmp_path / "plain.json"), str(tmp_path / "overlap.json")
     base = {"gradient_accumulation_steps": 2}
-    run_distributed(_overlap_losses, 2, {**base, "zero_optimization": {"stage": 1}}, a)
-    run_distributed(_overlap_losses, 2, {**base, "zero_optimization": {"stage": 1, "overlap_comm": True,
-                                                                       "reduce_bucket_size": 20000}}, b)
+    run_distributed_many((_overlap_losses, 2, {**base, "zero_optimization": {"stage": 1}}, a),
+                         (_overlap_losses, 2, {**base, "zero_optimization": {"stage": 1, "overlap_comm": True,
+                                                                             "reduce_bucket_size": 20000}}, b))
     ra, rb = json.load(open(a)), json.load(open(b))
     assert all(abs(x - y) < 1e-4 for x, y in zip(ra["losses"], rb["losses"])), (ra, rb)
     assert rb["buckets"] > ra["buckets"] and rb["overlapped"] > 0, rb
@@ -161,9 +161,9 @@ def test_overlapped_reduction_leaves_late_gradients_alone(tmp_path, world, cfg):
     the losses of the run without it, and other buckets are still reduced early."""
     a, b = str(tmp_path / "plain.json"), str(tmp_path / "overlap.json")
     base = {"gradient_accumulation_steps": 2, **cfg}
-    run_distributed(_overlap_losses, world, {**base, "zero_optimization": {"stage": 1}}, a)
-    run_distributed(_overlap_losses, world, {**base, "zero_optimization": {"stage": 1, "overlap_comm": True,
-                                                                           "reduce_bucket_size": 20000}}, b)
+    run_distributed_many((_overlap_losses, world, {**base, "zero_optimization": {"stage": 1}}, a),
+                         (_overlap_losses, world, {**base, "zero_optimization": {"stage": 1, "overlap_comm": True,
+                                                                                 "reduce_bucket_size": 20000}}, b))
     ra, rb = json.load(open(a)), json.load(open(b))
     assert all(abs(x - y) < 1e-5 for x, y in zip(ra["losses"], rb["losses"])), (ra, rb)
     assert rb["overlapped"] > 0, rb
@@ -190,8 +190,8 @@ def test_recomputation_skips_the_block_tail_without_changing_the_training(tmp_pa
     """When a checkpointed block is re-run in backward the output of its last layer is never read; the GEMMs (and
     the reduction) that only produce it are skipped.  Losses must be identical to the full recomputation."""
     a, b = str(tmp_path / "full.json"), str(tmp_path / "skip.json")
-    run_distributed(_recompute_losses, world, cfg, False, a)
-    run_distributed(_recompute_losses, world, cfg, True, b)
+    run_distributed_many((_recompute_losses, world, cfg, False, a),
+                         (_recompute_losses, world, cfg, True, b))
     la, lb = json.load(open(a)), json.load(open(b))
     assert la == lb, (la, lb)
     assert lb[-1] < lb[0]
@@ -407,8 +407,8 @@ def test_zero2_gradient_partitioning_matches_zero1(tmp_path, extra):
     world = 4 if extra else 2
     base = {"gradient_accumulation_steps": 2, "train_micro_batch_size_per_gpu": 2, **extra}
     a, b = str(tmp_path / "z1.json"), str(tmp_path / "z2.json")
-    run_distributed(_zero2_losses, world, {**base, "zero_optimization": {"stage": 1}}, a)
-    run_distributed(_zero2_losses, world, {**base, "zero_optimization": {"stage": 2, "reduce_bucket_size": 40000}}, b)
+    run_distributed_many((_zero2_losses, world, {**base, "zero_optimization": {"stage": 1}}, a),
+                         (_zero2_losses, world, {**base, "zero_optimization": {"stage": 2, "reduce_bucket_size": 40000}}, b))
     ra, rb = json.load(open(a)), json.load(open(b))
     assert rb["buckets"] > ra["buckets"]                    # stage 2 bounds its transient memory by bucketing
     for x, y in zip(ra["losses"], rb["losses"]):
@@ -467,9 +467,9 @@ def _zero3_worker(rank, world, cfg, out, ckpt_dir):
 def test_zero3_parameter_partitioning_matches_zero1(tmp_path, extra):
     base = {"gradient_accumulation_steps": 2, "train_micro_batch_size_per_gpu": 2, **extra}
     a, b = str(tmp_path / "z1.json"), str(tmp_path / "z3.json")
-    run_distributed(_zero3_worker, 2, {**base, "zero_optimization": {"stage": 1}}, a, None)
-    run_distributed(_zero3_worker, 2, {**base, "zero_optimization": {"stage": 3, "reduce_bucket_size": 40000}}, b,
-                    str(tmp_path / "ckpt"))
+    run_distributed_many((_zero3_worker, 2, {**base, "zero_optimization": {"stage": 1}}, a, None),
+                         (_zero3_worker, 2, {**base, "zero_optimization": {"stage": 3, "reduce_bucket_size": 40000}}, b,
+                          str(tmp_path / "ckpt")))
     la, lb = json.load(open(a)), json.load(open(b))
     tol = 2e-4 if extra.get("precision") != "bfloat16" else 3e-2
     for x, y in zip(la, lb):
@@ -481,7 +481,7 @@ def test_zero3_with_tensor_and_sequence_parallelism(tmp_path):
     base = {"gradient_accumulation_steps": 2, "train_micro_batch_size_per_gpu": 2, "model_parallel_size": 2,
             "sequence_parallel": True}
     a, b = str(tmp_path / "z1.json"), str(tmp_path / "z3.json")
-    run_distributed(_zero3_worker, 4, {**base, "zero_optimization": {"stage": 1}}, a, None)
-    run_distributed(_zero3_worker, 4, {**base, "zero_optimization": {"stage": 3, "reduce_bucket_size": 40000}}, b, None)
+    run_distributed_many((_zero3_worker, 4, {**base, "zero_optimization": {"stage": 1}}, a, None),
+                         (_zero3_worker, 4, {**base, "zero_optimization": {"stage": 3, "reduce_bucket_size": 40000}}, b, None))
     for x, y in zip(json.load(open(a)), json.load(open(b))):
         assert abs(x - y) < 2e-4
