@@ -417,7 +417,8 @@ class FlatMixedPrecisionOptimizer:
 
     def __init__(self, param_groups, inner_cls, inner_defaults, model_dtype, zero_stage=0, clip_grad=0.0,
                  fp16_cfg=None, gradient_predivide_factor=1.0, prescale_gradients=False, device=None,
-                 overlap_comm=False, reduce_bucket_size=None, offload_optimizer=False):
+                 overlap_comm=False, reduce_bucket_size=None, offload_optimizer=False,
+                 partition_params_at_build=False, offload_param=False):
         """``overlap_comm``: split every parameter group into buckets of at most ``reduce_bucket_size`` elements (in
         model order), start each bucket's data-parallel gradient reduction on a side stream as soon as the LAST
         micro-batch's backward has produced all of its gradients, and all-gather the updated parameter shards
@@ -425,7 +426,11 @@ class FlatMixedPrecisionOptimizer:
         (``zero_optimization.overlap_comm`` / ``reduce_bucket_size`` of the DeepSpeed ZeRO-1/2 config the reference
         passes through).  ``offload_optimizer``: keep the fp32 masters and the optimizer states in host memory and
         run ``inner_cls`` there (``zero_optimization.cpu_offload`` / ``offload_optimizer.device: cpu``); ``inner_cls``
-        must accept host tensors (``optim.cpu_adam.CPUAdam``, ``torch.optim.Adam`` ...)."""
+        must accept host tensors (``optim.cpu_adam.CPUAdam``, ``torch.optim.Adam`` ...).
+        ``partition_params_at_build`` (stage 3): every bucket is reduced to this rank's shard as soon as it has been
+        laid out, before the next one is built, so a model whose layers were parked in host memory while it was
+        constructed (``engine.pipe_module.built_through``) never exists in full on the device: the peak is the
+        shards plus one bucket.  ``device``: where the buckets live when the parameters are still elsewhere."""
         self.zero_stage = int(zero_stage or 0)
         self.offload_optimizer = bool(offload_optimizer)
         self.overlap_comm = bool(overlap_comm)
@@ -438,6 +443,7 @@ class FlatMixedPrecisionOptimizer:
         self.skipped_steps = 0
         self._global_grad_norm = 0.0
         self.buckets: list[Bucket] = []
+        self.max_resident_at_build = 0      # full-size sharded buckets alive at once while the buckets were laid out
         dp_group, dp_world, dp_rank = mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(), \
             mpu.get_data_parallel_rank()
         inner_groups = []
@@ -476,6 +482,12 @@ class FlatMixedPrecisionOptimizer:
                                partition_grads=self.zero_stage >= 2, offload=self.offload_optimizer)
                     self.buckets.append(b)
                     inner_groups.append({"params": [b.master], **opts})
+                    if partition_params_at_build and b.partition_grads:
+                        from .zero3 import partition_bucket
+                        self.max_resident_at_build = max(self.max_resident_at_build,
+                                                         sum(x.flat_param is not None and x.partition_grads
+                                                             for x in self.buckets))
+                        partition_bucket(b, offload_param)
         self.optimizer = inner_cls(inner_groups, **inner_defaults)
         self.param_groups = self.optimizer.param_groups
         self.dp_world = dp_world

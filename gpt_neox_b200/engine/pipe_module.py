@@ -16,6 +16,7 @@ instantiates only the layers owned by the local pipeline stage.  This file provi
 """
 from __future__ import annotations
 
+import contextlib
 import re
 from collections import OrderedDict
 
@@ -36,8 +37,15 @@ class LayerSpec:
             raise RuntimeError("LayerSpec only supports torch.nn.Module types.")
         self.typename, self.module_args, self.module_kwargs = typename, module_args, module_kwargs
 
+    # set by ``built_through``: called on every freshly built layer (e.g. to park it in host memory)
+    _post_build = None
+
     def build(self):
-        return self.typename(*self.module_args, **self.module_kwargs)
+        module = self.typename(*self.module_args, **self.module_kwargs)
+        hook = LayerSpec._post_build
+        if hook is not None and not any(p.is_meta for p in module.parameters()):
+            module = hook(module) or module
+        return module
 
     def __repr__(self):
         return f"LayerSpec({self.typename.__name__})"
@@ -47,6 +55,18 @@ class TiedLayerSpec(LayerSpec):
     def __init__(self, key, typename, *module_args, forward_fn=None, tied_weight_attr="weight", **module_kwargs):
         super().__init__(typename, *module_args, **module_kwargs)
         self.key, self.forward_fn, self.tied_weight_attr = key, forward_fn, tied_weight_attr
+
+
+@contextlib.contextmanager
+def built_through(hook):
+    """Inside the block every layer built from a ``LayerSpec`` is passed through ``hook(module)`` as soon as it
+    exists, before the next one is built."""
+    prev = LayerSpec._post_build
+    LayerSpec._post_build = hook
+    try:
+        yield
+    finally:
+        LayerSpec._post_build = prev
 
 
 def partition_uniform(num_items, num_parts):

@@ -33,6 +33,39 @@ def _layers(module):
             yield child
 
 
+def _placeholder(p):
+    """Stand-in for a released parameter: keeps shape / dtype / device, owns one element."""
+    return torch.empty(1, dtype=p.dtype, device=p.device).expand(p.shape)
+
+
+def partition_bucket(b, offload_param=False):
+    """Turn a freshly built bucket into its stage-3 form: keep this rank's shard (in host memory with
+    ``offload_param``), hand it to the optimizer as the place the updated 16-bit copy goes, release the full
+    buffer.  Idempotent."""
+    if b.partition_params:
+        return
+    b.param_shard = b.flat_param[b.lo:b.hi].clone()
+    if offload_param:
+        assert getattr(b, "offload", False), \
+            "offload_param needs the optimizer states offloaded as well (zero_optimization.cpu_offload / " \
+            "offload_optimizer.device: cpu)"
+        host = torch.empty(b.param_shard.shape, dtype=b.param_shard.dtype, device="cpu",
+                           pin_memory=b.param_shard.is_cuda)
+        host.copy_(b.param_shard)
+        b.param_shard = host
+    if getattr(b, "offload", False):
+        pass                                # host masters: the step copies the updated shard up itself
+    elif b.mixed:
+        b.master.model_out = b.param_shard
+    else:
+        b.master.data = b.param_shard       # fp32 training: the shard IS the master (same Parameter object,
+        #                                     which the inner optimizer already holds)
+    b.partition_params = True
+    for p in b.params:
+        p.data = _placeholder(p)
+    b.flat_param = None
+
+
 class ParamPartitioner:
     def __init__(self, optimizer, offload_param=False):
         """``offload_param``: keep the persistent 16-bit shards in (pinned) host memory as well -- the
@@ -47,31 +80,9 @@ class ParamPartitioner:
         self._prev = ()
         self.gathers = 0
         for b in self.buckets:
-            b.param_shard = b.flat_param[b.lo:b.hi].clone()
-            if self.offload_param:
-                assert getattr(b, "offload", False), \
-                    "offload_param needs the optimizer states offloaded as well (zero_optimization.cpu_offload / " \
-                    "offload_optimizer.device: cpu)"
-                host = torch.empty(b.param_shard.shape, dtype=b.param_shard.dtype, device="cpu",
-                                   pin_memory=b.param_shard.is_cuda)
-                host.copy_(b.param_shard)
-                b.param_shard = host
-            if getattr(b, "offload", False):
-                pass                                # host masters: the step copies the updated shard up itself
-            elif b.mixed:
-                b.master.model_out = b.param_shard
-            else:
-                b.master.data = b.param_shard       # fp32 training: the shard IS the master (same Parameter object,
-                #                                     which the inner optimizer already holds)
-            b.partition_params = True
-        for b in self.buckets:
-            self._release(b)
+            partition_bucket(b, self.offload_param)      # no-op for buckets partitioned while they were built
 
     # ------------------------------------------------------------------ gather / release
-    @staticmethod
-    def _placeholder(p):
-        return torch.empty(1, dtype=p.dtype, device=p.device).expand(p.shape)
-
     def _gather(self, b):
         dev = torch.device(b.device)
         shard = b.param_shard if b.param_shard.device.type == dev.type else b.param_shard.to(dev, non_blocking=True)
@@ -86,7 +97,7 @@ class ParamPartitioner:
         if b.flat_param is None:
             return
         for p in b.params:
-            p.data = self._placeholder(p)
+            p.data = _placeholder(p)
         b.flat_param = None
 
     def acquire(self, buckets):

@@ -7,6 +7,7 @@ Public surface kept from the reference: ``pretrain``, ``setup_model_and_optimize
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import sys
 from contextlib import nullcontext
@@ -267,8 +268,8 @@ def forward_step(data_iterator, model, neox_args, timers, return_logits=False, i
 
 
 # ------------------------------------------------------------------------------------ model / optimizer
-def get_model(neox_args, use_cache=False):
-    """Build the model on this rank (``megatron/training.py:947-1033``)."""
+def get_model(neox_args, use_cache=False, park_on_host=False):
+    """Build the model on this rank (``megatron/training.py:947-1033``).  ``park_on_host``: see below."""
     print_rank_0("building GPT2 model ...")
     if neox_args.zero_stage in (2, 3):
         if neox_args.pipe_parallel_size == 1:
@@ -279,8 +280,17 @@ def get_model(neox_args, use_cache=False):
             sys.exit(1)
         # (the reference also refuses model parallelism here, ``megatron/training.py:968-973``; this engine's
         # gradient partitioning works per data-parallel group and composes with tensor / sequence parallelism)
-    model = GPT2ModelPipe(neox_args=neox_args, num_tokentypes=0, parallel_output=neox_args.train_impl != "rm",
-                          topology=mpu.get_topology(), use_cache=use_cache)
+    # stage 3 with parameter offload: every layer is parked in host memory as soon as it has been built and
+    # initialised, and the optimizer later brings it to the device one bucket at a time, keeping only this rank's
+    # shard -- the model never exists in full on the device (the role of ``deepspeed.zero.Init(remote_device="cpu")``,
+    # ``megatron/training.py:958-977``)
+    through_host = contextlib.nullcontext()
+    if park_on_host:
+        from .engine.pipe_module import built_through
+        through_host = built_through(lambda layer: layer.to("cpu"))
+    with through_host:
+        model = GPT2ModelPipe(neox_args=neox_args, num_tokentypes=0, parallel_output=neox_args.train_impl != "rm",
+                              topology=mpu.get_topology(), use_cache=use_cache)
     if neox_args.soft_prompt_tuning is not None and neox_args.soft_prompt_tuning.get("enabled", False):
         spt = neox_args.soft_prompt_tuning
         soft = SoftEmbedding(neox_args, wte=getattr(model, "0").word_embeddings if hasattr(model, "0")
@@ -299,6 +309,10 @@ def get_model(neox_args, use_cache=False):
     return model
 
 
+def _train_device():
+    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+
+
 def optimizer_offload(neox_args) -> bool:
     """Whether the fp32 masters and optimizer states live in host memory: a host optimizer type, or the ZeRO
     configuration asks for it (``cpu_offload: true``, or ``offload_optimizer: {device: cpu}``)."""
@@ -306,6 +320,13 @@ def optimizer_offload(neox_args) -> bool:
     off = z.get("offload_optimizer") or {}
     return bool(z.get("cpu_offload")) or str(off.get("device", "none")).lower() == "cpu" or \
         neox_args.optimizer_type.lower() in ("cpu_adam", "cpu_torch_adam")
+
+
+def param_offload(neox_args) -> bool:
+    """ZeRO stage 3 with the persistent parameter shards in host memory (``offload_param: {device: cpu}``)."""
+    z = neox_args.zero_optimization or {}
+    off = z.get("offload_param") or {}
+    return neox_args.zero_stage == 3 and str(off.get("device", "none")).lower() == "cpu"
 
 
 def _inner_optimizer(neox_args):
@@ -385,13 +406,17 @@ def get_optimizer(model, neox_args, dummy=False):
                                             clip_grad=neox_args.gradient_clipping, fp16_cfg=fp16_cfg,
                                             overlap_comm=bool((neox_args.zero_optimization or {}).get("overlap_comm", False)),
                                             reduce_bucket_size=neox_args.zero_reduce_bucket_size,
-                                            offload_optimizer=optimizer_offload(neox_args))
+                                            offload_optimizer=optimizer_offload(neox_args),
+                                            partition_params_at_build=param_offload(neox_args),
+                                            offload_param=param_offload(neox_args),
+                                            device=_train_device() if param_offload(neox_args) else None)
+    if param_offload(neox_args):
+        model.to(_train_device())      # buffers and parameters outside the optimizer follow; released ones are there
     if getattr(optimizer, "overlap_comm", False):
         # each layer waits only for the all-gather of its own parameters
         optimizer.install_param_wait_hooks(model)
     if optimizer.zero_stage >= 3:
-        off = (neox_args.zero_optimization or {}).get("offload_param") or {}
-        optimizer.enable_param_partitioning(model, offload_param=str(off.get("device", "none")).lower() == "cpu")
+        optimizer.enable_param_partitioning(model, offload_param=param_offload(neox_args))
     return optimizer, groups
 
 
@@ -446,7 +471,8 @@ def setup_model_and_optimizer(neox_args, use_cache=False, iteration=None):
     Returns ``(engine, optimizer, lr_scheduler, reference_model)``."""
     if neox_args.memory_profiling and torch.cuda.is_available():
         torch.cuda.memory._record_memory_history(True, trace_alloc_max_entries=100000, trace_alloc_record_context=True)
-    model = get_model(neox_args=neox_args, use_cache=use_cache)
+    will_train = neox_args.optimizer is not None and not neox_args.no_load_optim
+    model = get_model(neox_args=neox_args, use_cache=use_cache, park_on_host=param_offload(neox_args) and will_train)
     needs_reference = (neox_args.train_impl == "dpo" and neox_args.precompute_model_name is None
                        and not neox_args.dpo_reference_free) or \
                       (neox_args.train_impl == "kto" and neox_args.precompute_model_name is None)

@@ -128,6 +128,38 @@ def test_optimizer_state_offload_layout():
     run_distributed(_offload_layout, 2)
 
 
+def _host_staged_construction(rank, world):
+    """Stage 3 with parameter offload: layers are parked on the host as they are built, and the optimizer reduces
+    every bucket to this rank's shard before it lays out the next one."""
+    from gpt_neox_b200.engine import pipe_module
+    parked = []
+    real_to = torch.nn.Module.to
+
+    def spy(self, *a, **kw):
+        if pipe_module.LayerSpec._post_build is not None and a and a[0] == "cpu":
+            parked.append(type(self).__name__)
+        return real_to(self, *a, **kw)
+    torch.nn.Module.to = spy
+    try:
+        args, model, opt, sched = _setup({"global_num_gpus": world, "precision": "bfloat16",
+                                          "zero_optimization": {"stage": 3, "cpu_offload": True,
+                                                                "offload_param": {"device": "cpu"},
+                                                                "reduce_bucket_size": 20000}})
+    finally:
+        torch.nn.Module.to = real_to
+    assert pipe_module.LayerSpec._post_build is None                 # the hook does not outlive the construction
+    assert len(parked) >= args.num_layers + 2, parked               # embedding, every block, the final layers
+    sharded = [b for b in opt.buckets if b.partition_grads]
+    assert len(sharded) > 2 and opt.max_resident_at_build == 1
+    assert all(b.flat_param is None and b.partition_params and b.param_shard.device.type == "cpu" for b in sharded)
+    losses = _train(args, model, opt, sched, 6)
+    assert min(losses) < losses[0]
+
+
+def test_zero3_param_offload_builds_the_model_through_the_host():
+    run_distributed(_host_staged_construction, 2)
+
+
 def _overlap_losses(rank, world, cfg, out):
     args, model, opt, sched = _setup({**cfg, "global_num_gpus": world})
     losses = _train(args, model, opt, sched, 8)
