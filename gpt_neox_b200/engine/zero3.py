@@ -132,7 +132,7 @@ class ParamPartitioner:
             if write_back:
                 for b in self.buckets:
                     b.param_shard.copy_(b.flat_param[b.lo:b.hi])
-                    if b.mixed:
+                    if b.mixed or getattr(b, "offload", False):
                         b.master.data.copy_(b.param_shard.float())
         finally:
             self.pinned = False

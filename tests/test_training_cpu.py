@@ -509,6 +509,19 @@ def test_zero3_parameter_partitioning_matches_zero1(tmp_path, extra):
     assert lb[6] < lb[0]                      # training continues after the checkpoint round trip
 
 
+@pytest.mark.parametrize("precision", ["fp32", "bfloat16"])
+def test_zero3_offload_checkpoint_round_trip(tmp_path, precision):
+    """Stage 3 with optimizer states and parameter shards in host memory: save, wipe, load gives the same
+    parameters back and training continues (the worker asserts it)."""
+    cfg = {"gradient_accumulation_steps": 2, "train_micro_batch_size_per_gpu": 2, "precision": precision,
+           "zero_optimization": {"stage": 3, "reduce_bucket_size": 40000, "cpu_offload": True,
+                                 "offload_param": {"device": "cpu"}}}
+    out = str(tmp_path / "z3.json")
+    run_distributed(_zero3_worker, 2, cfg, out, str(tmp_path / "ckpt"))
+    losses = json.load(open(out))
+    assert len(losses) == 7 and losses[6] < losses[0]
+
+
 def test_zero3_with_tensor_and_sequence_parallelism(tmp_path):
     base = {"gradient_accumulation_steps": 2, "train_micro_batch_size_per_gpu": 2, "model_parallel_size": 2,
             "sequence_parallel": True}
