@@ -31,7 +31,7 @@ from socket import gethostname
 import torch
 import yaml
 
-from .schema import (ATTENTION_TYPE_CHOICES, ENGINE_KEYS, FIELDS, GROUPS, OPT_DEFAULT, OPT_PARAMS_DEFAULTS,
+from .schema import (ATTENTION_TYPE_CHOICES, ENGINE_KEYS, FIELDS, OPT_DEFAULT, OPT_PARAMS_DEFAULTS,
                      RUNNER_KEYS, ZERO_DEFAULTS)
 
 DLTS_HOSTFILE = "/job/hostfile"

@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import math
 from functools import partial
-from itertools import cycle, zip_longest
 
 import numpy as np
 import torch

@@ -14,7 +14,6 @@ from __future__ import annotations
 
 import os
 import struct
-from functools import lru_cache
 
 import numpy as np
 import torch

@@ -18,7 +18,6 @@ from __future__ import annotations
 
 import contextlib
 import re
-from collections import OrderedDict
 
 import torch
 import torch.distributed as dist

@@ -198,7 +198,7 @@ class EvalHarnessAdapter:
     # ------------------------------------------------------------------ harness driver
     def run_eval(self, eval_tasks=None, num_fewshot=0, bootstrap_iters=2, use_cache=False, name="neox", limit=None):
         try:
-            from lm_eval import evaluator, tasks, utils
+            from lm_eval import evaluator, tasks
             from lm_eval.api.model import LM
         except ModuleNotFoundError as exc:
             raise ModuleNotFoundError("lm_eval (lm-evaluation-harness >= 0.4) is required for eval.py / `eval_tasks`") from exc

@@ -18,7 +18,6 @@ import os
 import torch
 import torch.distributed as dist
 
-from .parallel import mpu
 from .utils import print_rank_0, report_memory
 
 

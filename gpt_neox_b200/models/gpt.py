@@ -13,7 +13,6 @@ Mamba according to ``attention_config``), ``L+2`` ``_post_transformer_block`` (d
 from __future__ import annotations
 
 import math
-from collections import defaultdict
 from functools import partial
 
 import torch
@@ -24,8 +23,7 @@ from ..parallel import mpu
 from ..parallel.rng import set_block_tail
 from ..parallel.cross_entropy import vocab_parallel_cross_entropy
 from ..parallel.layers import ParallelRelativePositionBias
-from ..parallel.rng import checkpoint as ckpt_fn
-from .embeddings import EmbeddingPipe, SoftEmbedding
+from .embeddings import EmbeddingPipe
 from .init_functions import get_init_methods
 from .norms import get_norm
 from .transformer import NormPipe, ParallelLinearPipe, ParallelTransformerLayerPipe, parallel_lm_logits

@@ -36,7 +36,6 @@ from ..ops import moe_ops as MO
 from ..ops.linear import linear as fused_linear
 from ..parallel import mappings as M
 from ..parallel import moe_comm, mpu
-from ..parallel.rng import get_cuda_rng_tracker
 from ..ops.linear import main_grad_of
 
 

@@ -22,11 +22,11 @@ import torch.nn.functional as F
 
 from ..ops import functional as OF
 from ..ops.sparse_attention import block_sparse_attention
-from ..ops.attention import attention_ref, flash_attention, packed_qkv_attention, packed_qkv_ok
+from ..ops.attention import flash_attention, packed_qkv_attention, packed_qkv_ok
 from ..ops.linear import dead_outputs, linear as fused_linear
 from ..parallel import mappings as M
 from ..parallel import mpu
-from ..parallel.layers import ColumnParallelLinear, ParallelRelativePositionBias, RowParallelLinear
+from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
 from ..parallel.rng import get_cuda_rng_tracker, recompute_tail
 from .norms import LayerNorm, get_norm
 from .positional import AliBi, RotaryEmbedding, apply_rotary_pos_emb

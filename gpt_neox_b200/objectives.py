@@ -10,7 +10,6 @@ import torch
 import torch.nn.functional as F
 
 from .parallel import mappings as M
-from .parallel import mpu
 from .parallel.cross_entropy import vocab_parallel_cross_entropy
 
 

@@ -466,7 +466,6 @@ def precompute_logits(neox_args, model):
                 inp, lab = t[:, :-1].contiguous(), t[:, 1:].contiguous()
                 pos = torch.arange(inp.shape[1], device=_dev()).unsqueeze(0)
                 with torch.no_grad():
-                    from .objectives import get_logp as vp_logp
                     out = model.module((inp, pos, None))
                     logits = out[0] if isinstance(out, tuple) else out
                     from .parallel import mappings as M

@@ -15,10 +15,8 @@ import gzip
 import io
 import json
 import multiprocessing
-import os
 import sys
 import time
-from types import SimpleNamespace
 
 import numpy as np
 
