@@ -132,11 +132,12 @@ class SequentialWrapper(nn.Module):
                     attention_mask = attention_mask[:, :, :curriculum_seqlen, :curriculum_seqlen].contiguous()
             forward_input = (tokens, position_ids, attention_mask)
         moe_losses = []
+        layers = list(self.sequential)      # slicing the container itself would build a new nn.Sequential each time
 
         def exec_range(start, end):
             def run(*inputs):
                 x = inputs[0] if len(inputs) == 1 else inputs
-                block = self.sequential[start:end]
+                block = layers[start:end]
                 for i, layer in enumerate(block):
                     set_block_tail(i == len(block) - 1)
                     x = layer(x)
@@ -145,7 +146,7 @@ class SequentialWrapper(nn.Module):
                 return x
             return run
 
-        n = len(self.sequential)
+        n = len(layers)
         if self.activation_checkpoint_interval == 0 or not torch.is_grad_enabled():
             x = exec_range(0, n)(forward_input)
         else:
@@ -154,7 +155,7 @@ class SequentialWrapper(nn.Module):
                 end = min(start + self.activation_checkpoint_interval, n)
                 if not isinstance(x, tuple):
                     x = (x,)
-                if self._is_checkpointable(self.sequential[start:end]):
+                if self._is_checkpointable(layers[start:end]):
                     x = self.activation_checkpoint_func(exec_range(start, end), *x)
                 else:
                     x = exec_range(start, end)(*x)
