@@ -195,6 +195,28 @@ def get_model_parallel_ranks():
     return list(_S.model_ranks)
 
 
+# the Megatron-LM spellings of the same four (``megatron/mpu/initialize.py:274-298``)
+def get_tensor_model_parallel_group():
+    return get_model_parallel_group()
+
+
+def get_tensor_model_parallel_src_rank() -> int:
+    return get_model_parallel_src_rank()
+
+
+def get_tensor_model_parallel_world_size() -> int:
+    return get_model_parallel_world_size()
+
+
+def get_tensor_model_parallel_rank() -> int:
+    return get_model_parallel_rank()
+
+
+def is_unitialized() -> bool:
+    """For code that may run with or without the groups set up (the reference's spelling)."""
+    return not _S.initialized
+
+
 # ---------------------------------------------------------------- data parallel
 def get_data_parallel_group():
     return _S.data_group

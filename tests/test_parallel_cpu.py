@@ -49,7 +49,12 @@ def _vocab_ce(rank, world):
     from gpt_neox_b200.parallel import mpu
     from gpt_neox_b200.parallel.cross_entropy import vocab_parallel_cross_entropy
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    assert mpu.is_unitialized()
     mpu.initialize_model_parallel(world)
+    # the Megatron-LM spellings name the same group
+    assert not mpu.is_unitialized() and mpu.get_tensor_model_parallel_group() is mpu.get_model_parallel_group()
+    assert mpu.get_tensor_model_parallel_rank() == rank and mpu.get_tensor_model_parallel_world_size() == world
+    assert mpu.get_tensor_model_parallel_src_rank() == 0
     torch.manual_seed(0)
     V = 64
     logits = torch.randn(3, 5, V) * 2
