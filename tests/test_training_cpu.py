@@ -283,6 +283,15 @@ def test_wall_clock_breakdown(world, cfg):
     run_distributed(_wall_clock_breakdown, world, cfg)
 
 
+def test_tensor4_pipeline2_layout_trains():
+    """The 8-rank layout of the headline benchmark (tensor parallel 4 x pipeline 2, activation checkpointing,
+    ZeRO-1, bf16) through the host-side code paths: grouping, 1F1B schedule, tied / late gradients."""
+    run_distributed(_loss_decreases, 8, {"pipe_parallel_size": 2, "model_parallel_size": 4,
+                                         "gradient_accumulation_steps": 4, "num_layers": 4, "num_attention_heads": 8,
+                                         "checkpoint_activations": True, "zero_optimization": {"stage": 1},
+                                         "precision": "bfloat16"}, None, timeout=600)
+
+
 def _checkpoint(rank, world, cfg, save_dir):
     from gpt_neox_b200.checkpointing import load_checkpoint, save_checkpoint
     from gpt_neox_b200.parallel import mpu
