@@ -378,7 +378,8 @@ class ParallelMoE(nn.Module):
                     out_e = self._expert(e, seg)
                     o2 = 0
                     for o, n, _ in pieces[e]:
-                        res_parts[o] = out_e[o2:o2 + n]
+                        if n:                  # an empty piece shares its offset with the piece that follows it
+                            res_parts[o] = out_e[o2:o2 + n]
                         o2 += n
                 outs = torch.cat([res_parts[o] for o in sorted(res_parts)]) if res_parts else xr
                 if peer:

@@ -36,6 +36,35 @@ def test_moe_expert_parallel_two_ranks():
                                          "moe_expert_parallel_size": 2, "gpt_j_residual": False}, None)
 
 
+def _ep4_loop_vs_grouped(rank, world):
+    """Four expert-parallel ranks with two local experts each: with few tokens many (source rank, expert) segments
+    are empty, which the receive-side bookkeeping has to survive; the per-expert loop and the grouped form give the
+    same training."""
+    import torch
+    from test_training_cpu import _setup, _train
+    from gpt_neox_b200.models.moe import ParallelMoE
+    from gpt_neox_b200.parallel import mpu
+    runs = []
+    for grouped in (False, True):
+        torch.manual_seed(0)
+        args, model, opt, sched = _setup({"global_num_gpus": world, "moe_num_experts": 8, "moe_top_k": 2,
+                                          "expert_interval": 2, "moe_expert_parallel_size": 4,
+                                          "gpt_j_residual": False, "moe_token_dropping": False})
+        moes = [m for m in model.module.modules() if isinstance(m, ParallelMoE)]
+        assert moes and all(m.ep == 4 and m.local_experts == 2 for m in moes)
+        for m in moes:
+            m.grouped = grouped
+        runs.append(_train(args, model, opt, sched, 8))
+        mpu.destroy_model_parallel()
+    assert min(runs[0]) < runs[0][0]
+    for a, b in zip(*runs):
+        assert abs(a - b) < 1e-4, runs
+
+
+def test_moe_expert_parallel_four_ranks_two_local_experts():
+    run_distributed(_ep4_loop_vs_grouped, 4)
+
+
 def test_wkv6_reference_gradients_are_consistent():
     """The closed form used for the decay gradient (reverse cumulative sums of r*grS and k*gkG) equals autograd
     through the plain recurrence."""
