@@ -467,7 +467,7 @@ class PipelineEngine(NeoXEngine):
                 return None
 
             def post():
-                metas, is_tuple = p2p._recv_meta(p2p.peer(-1), "act")
+                metas, is_tuple = p2p._recv_meta(p2p.peer(-1), "act_in")      # (a middle stage also SENDS a header)
                 state["tuple"] = is_tuple
                 return p2p.post_recv(metas, -1)
             return post() if ahead else post
@@ -481,7 +481,7 @@ class PipelineEngine(NeoXEngine):
             if last:
                 return
             ts, is_tuple = self._tensors_of(out)
-            p2p._send_meta(ts, p2p.peer(+1), "act", is_tuple)
+            p2p._send_meta(ts, p2p.peer(+1), "act_out", is_tuple)
             p2p.post_send(ts, +1)
 
         def grad_metas(out):

@@ -283,6 +283,27 @@ def test_wall_clock_breakdown(world, cfg):
     run_distributed(_wall_clock_breakdown, world, cfg)
 
 
+def _pipeline_with_middle_stages(rank, world, cfg):
+    """More than two stages: a middle stage both receives and sends the one-time shape header; training and
+    evaluation run through every stage."""
+    args, model, opt, sched = _setup({**cfg, "global_num_gpus": world})
+    it = _fixed_batches(args)
+    losses = _train(args, model, opt, sched, 8, it)
+    assert min(losses) < losses[0], losses
+    ev = model.eval_batch(it)
+    assert torch.isfinite(ev).all() and abs(float(ev) - losses[-1]) < 1.0
+    losses += _train(args, model, opt, sched, 2, it)          # and back to training
+    assert all(l == l for l in losses)
+
+
+@pytest.mark.parametrize("world,cfg", [
+    (4, {"pipe_parallel_size": 4, "num_layers": 6, "gradient_accumulation_steps": 6, "no_weight_tying": False}),
+    (3, {"pipe_parallel_size": 3, "num_layers": 5, "gradient_accumulation_steps": 2}),       # fewer micro-batches than stages
+])
+def test_pipeline_with_middle_stages(world, cfg):
+    run_distributed(_pipeline_with_middle_stages, world, cfg)
+
+
 def test_tensor4_pipeline2_layout_trains():
     """The 8-rank layout of the headline benchmark (tensor parallel 4 x pipeline 2, activation checkpointing,
     ZeRO-1, bf16) through the host-side code paths: grouping, 1F1B schedule, tied / late gradients."""
