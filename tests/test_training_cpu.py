@@ -283,6 +283,65 @@ def test_wall_clock_breakdown(world, cfg):
     run_distributed(_wall_clock_breakdown, world, cfg)
 
 
+def _post_training(rank, world, cfg):
+    """``train_step`` with a post-training objective: batches of the shape that objective's data loader yields, a
+    reference model where one is needed, finite metrics, and a loss that moves."""
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.parallel import mpu
+    from gpt_neox_b200.training import setup_model_and_optimizer, train_step
+    from gpt_neox_b200.utils import Timers
+    args = make_args(**{**cfg, "global_num_gpus": world})
+    args.configure_distributed_args()
+    initialize_megatron(args)
+    model, opt, sched, ref = setup_model_and_optimizer(args)
+    impl = args.train_impl
+    assert (ref is not None) == (impl in ("dpo", "kto") and not args.dpo_reference_free
+                                 and args.precompute_model_name is None)
+    g = torch.Generator().manual_seed(100 + mpu.get_data_parallel_rank())
+    mb, L, V = args.train_micro_batch_size_per_gpu, args.seq_length + 1, args.padded_vocab_size
+    tok = lambda: torch.randint(1, V, (mb, L), generator=g)
+
+    def batch():
+        if impl == "rm":                       # one labelled position per sequence: where the reward is read
+            lab = torch.full((mb, L), -100)
+            lab[:, -1] = 5
+            return {"pos": tok(), "neg": tok(), "pos_label": lab.clone(), "neg_label": lab.clone()}
+        if impl == "dpo":
+            return {"pos": tok(), "neg": tok()}
+        if impl == "kto":
+            return {"text": tok(), "reward": (torch.rand(mb, L, generator=g) > 0.5).float() * 2 - 1,
+                    "ref": torch.zeros(mb, L)}
+        return {"text": tok(), "reward": torch.rand(mb, generator=g), "raw_reward": torch.rand(mb, generator=g)}
+    fixed = [batch() for _ in range(2)]
+
+    def it():
+        i = 0
+        while True:
+            yield fixed[i % 2]
+            i += 1
+    itr, losses = it(), []
+    for _ in range(6):
+        d, _ = train_step(args, Timers(), itr, model, opt, sched, reference_model=ref)
+        assert all(float(v) == float(v) for v in d.values()), d
+        losses.append(float(d["lm_loss"]))
+    assert min(losses[2:]) < max(losses[:2]), losses
+    return losses
+
+
+@pytest.mark.parametrize("world,cfg", [
+    (2, {"train_impl": "dpo", "model_parallel_size": 2, "dpo_beta": 0.1}),                       # with a reference model
+    (4, {"train_impl": "dpo", "dpo_reference_free": True, "model_parallel_size": 2, "sequence_parallel": True,
+         "zero_optimization": {"stage": 2, "reduce_bucket_size": 30000}}),
+    (2, {"train_impl": "rm", "model_parallel_size": 2, "no_weight_tying": True,
+         "pos_train_label_data_paths": ["x"], "neg_train_label_data_paths": ["x"]}),
+    (2, {"train_impl": "kto", "model_parallel_size": 2}),                                        # reference model
+    (2, {"train_impl": "kto", "precompute_model_name": "ref"}),                                  # stored reference log-probs
+    (2, {"train_impl": "reinforce", "model_parallel_size": 2}),
+])
+def test_post_training_objectives_train_end_to_end(world, cfg):
+    run_distributed(_post_training, world, {"train_micro_batch_size_per_gpu": 2, **cfg})
+
+
 def _pipeline_with_middle_stages(rank, world, cfg):
     """More than two stages: a middle stage both receives and sends the one-time shape header; training and
     evaluation run through every stage."""
