@@ -53,6 +53,12 @@ class NeoXEngine:
         self.timers = None
         self.training = True
         self.is_pipe_parallel = False
+        self.curriculum_scheduler = None
+        cl = getattr(neox_args, "curriculum_learning", None)
+        if cl and cl.get("enabled", True) and optimizer is not None and not getattr(neox_args, "is_pipe_parallel", False) \
+                and cl.get("curriculum_type", "seqlen") == "seqlen":
+            from .curriculum import CurriculumScheduler
+            self.curriculum_scheduler = CurriculumScheduler(cl)
         # ``wall_clock_breakdown``: per-phase times of the engine, averaged over ``steps_per_print`` optimizer steps,
         # printed by rank 0 and left in ``timer_values`` (milliseconds per step) for the training log.  The timers
         # record CUDA events and are only resolved when they are printed, so they do not serialise the step.
@@ -74,6 +80,11 @@ class NeoXEngine:
         return self.train(False)
 
     def __call__(self, *args, **kwargs):
+        if self.training and self.curriculum_scheduler is not None:
+            # sequence-length curriculum of the sequential model: the module truncates its inputs to the current
+            # difficulty and records it in ``neox_args.curriculum_seqlen`` for the loss (the pipeline engine gets the
+            # same through its batch function)
+            kwargs["curriculum_seqlen"] = self.curriculum_scheduler.update_difficulty(self.global_steps + 1)
         with self._timed("forward" if self.training else None):
             return self.module(*args, **kwargs)
 
@@ -604,8 +615,21 @@ class PipelineEngine(NeoXEngine):
         return agg, logits_out
 
     # ------------------------------------------------------------------ public API
+    def set_curriculum_scheduler(self, scheduler):
+        """The scheduler the batch function truncates sequences with: every stage follows it, so that the cached
+        message shapes are dropped whenever the sequence length is about to change."""
+        self._pipe_curriculum, self._pipe_difficulty = scheduler, None
+
     def train_batch(self, data_iter=None):
         self.module.train()
+        sched = getattr(self, "_pipe_curriculum", None)
+        if sched is not None:
+            it = getattr(self.neox_args, "iteration", None)
+            step = (it if it is not None else self.global_steps) + 1
+            now = min(sched.get_difficulty(step), sched.state["max_difficulty"])
+            if now != self._pipe_difficulty:
+                self.reset_activation_shape()
+                self._pipe_difficulty = now
         with self._timed("train_batch"):
             loss, _ = self._exec(data_iter, train=True)
         if hasattr(self.module, "allreduce_tied_weight_gradients"):

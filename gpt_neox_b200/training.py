@@ -495,6 +495,8 @@ def setup_model_and_optimizer(neox_args, use_cache=False, iteration=None):
             if iteration is not None and iteration > 0:
                 curr.update_difficulty(iteration)
         engine.set_batch_fn(partial(get_batch_pipe, neox_args=neox_args, curr_scheduler=curr))
+        if curr is not None:
+            engine.set_curriculum_scheduler(curr)
     if neox_args.dump_state:
         dump_engine_state(engine, neox_args)
     if neox_args.load is not None:

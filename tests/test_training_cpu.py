@@ -283,6 +283,41 @@ def test_wall_clock_breakdown(world, cfg):
     run_distributed(_wall_clock_breakdown, world, cfg)
 
 
+def _curriculum(rank, world, cfg):
+    """Sequence-length curriculum: the length the model actually sees ramps from min to max difficulty, on the
+    sequential engine (driven by the engine's forward) and on the pipeline engine (driven by its batch function)."""
+    from gpt_neox_b200.models import gpt as G
+    cl = {"enabled": True, "curriculum_type": "seqlen", "min_difficulty": 8, "max_difficulty": 32,
+          "schedule_type": "fixed_linear", "schedule_config": {"total_curriculum_step": 6, "difficulty_step": 8}}
+    args, model, opt, sched = _setup({**cfg, "global_num_gpus": world, "curriculum_learning": cl})
+    seen = []
+    if not args.is_pipe_parallel:
+        inner = model.module.sequential[0]
+        inner.register_forward_pre_hook(lambda m, a: seen.append(a[0][0].shape[1]) if m.training else None)
+    it = _fixed_batches(args)
+    losses = []
+    if args.is_pipe_parallel and rank == 0:
+        first = model.module.forward_funcs[0]
+        first.register_forward_pre_hook(lambda m, a: seen.append(a[0][0].shape[1]) if m.training else None)
+    for step in range(8):
+        args.iteration = step                               # what the training loop maintains
+        losses += _train(args, model, opt, sched, 1, it)
+    assert all(l == l for l in losses)
+    if seen and (not args.is_pipe_parallel or rank == 0):
+        assert seen[0] == 8 and seen[-1] == 32 and sorted(seen) == seen, seen
+    model.eval()                                            # evaluation always sees whole sequences
+    if not args.is_pipe_parallel:
+        from gpt_neox_b200.training import forward_step
+        loss, _ = forward_step(it, model, args, None)
+        assert loss == loss
+
+
+@pytest.mark.parametrize("world,cfg", [(1, {}), (2, {"pipe_parallel_size": 2, "num_layers": 4,
+                                                      "gradient_accumulation_steps": 2})])
+def test_sequence_length_curriculum(world, cfg):
+    run_distributed(_curriculum, world, cfg)
+
+
 def _post_training(rank, world, cfg):
     """``train_step`` with a post-training objective: batches of the shape that objective's data loader yields, a
     reference model where one is needed, finite metrics, and a loss that moves."""
