@@ -96,10 +96,27 @@ def check_forward_pass(neox_args, model, checkpoint_logits, inference):
 
 
 # ------------------------------------------------------------------------------------ engine-level writer
-def _optim_file(save_dir, tag, bf16):
+def _optim_file(save_dir, tag, bf16, dp_rank=None):
     prefix = "bf16_" if bf16 else ""
-    return os.path.join(save_dir, tag, f"{prefix}zero_pp_rank_{mpu.get_data_parallel_rank()}_mp_rank_"
-                                       f"{_mp_file_rank():02d}_optim_states.pt")
+    dp_rank = mpu.get_data_parallel_rank() if dp_rank is None else dp_rank
+    return os.path.join(save_dir, tag, f"{prefix}zero_pp_rank_{dp_rank}_mp_rank_{_mp_file_rank():02d}_optim_states.pt")
+
+
+def _expert_params(module):
+    """``{name: parameter}`` of the parameters that differ between expert-parallel ranks."""
+    return {n: p for n, p in module.named_parameters() if getattr(p, "expert_parallel", False)}
+
+
+def _expert_file(d):
+    """Experts are split over the expert-parallel ranks of a data-parallel group, so the shared model files (written
+    by data-parallel rank 0) hold only that rank's experts; every expert-parallel rank keeps its own in this file."""
+    return os.path.join(d, f"expert_ep_rank_{mpu.get_expert_parallel_rank():02d}_mp_rank_{_mp_file_rank():02d}"
+                           "_model_states.pt")
+
+
+def _per_rank_optimizer_state(engine) -> bool:
+    """Whether every data-parallel rank holds optimizer state of its own: ZeRO shards, or experts of its own."""
+    return getattr(engine.optimizer, "zero_stage", 0) >= 1 or mpu.get_expert_parallel_world_size() > 1
 
 
 def _atomic_save(obj, path):
@@ -196,9 +213,12 @@ def _engine_save_checkpoint(engine, save_dir, tag, client_state):
     elif writer:
         sd = {k: v.detach().cpu() for k, v in module.state_dict().items()}
         _atomic_save({"module": sd, **common}, os.path.join(d, f"mp_rank_{tp:02d}_model_states.pt"))
+    if mpu.get_expert_parallel_world_size() > 1 and mpu.get_expert_data_parallel_rank() == 0:
+        experts = _expert_params(module)
+        if experts:
+            _atomic_save({n: p.detach().cpu() for n, p in experts.items()}, _expert_file(d))
     if engine.optimizer is not None and not engine.neox_args.no_save_optim:
-        zero = getattr(engine.optimizer, "zero_stage", 0) >= 1
-        if zero or writer:
+        if _per_rank_optimizer_state(engine) or writer:
             _atomic_save({"optimizer_state_dict": engine.optimizer.state_dict(),
                           "ds_config": engine.neox_args.deepspeed_config, "ds_version": "neox-b200"},
                          _optim_file(save_dir, tag, engine.neox_args.precision == "bfloat16"))
@@ -315,6 +335,20 @@ def _load_tag_impl(engine, load_dir, tag, load_optimizer_states, load_lr_schedul
                 if os.path.isfile(f) and any(True for _ in layer.state_dict()):
                     _load_module_sequential(layer, _read(f),
                                             load_module_strict)
+    if mpu.get_expert_parallel_world_size() > 1:
+        experts = _expert_params(module)
+        f = _expert_file(d)
+        if experts and os.path.isfile(f):
+            saved = _read(f)
+            with torch.no_grad():
+                for n, p in experts.items():
+                    if n in saved:
+                        p.copy_(saved[n].to(p.device))
+                    elif load_module_strict:
+                        raise KeyError(f"{f} has no entry for expert parameter {n}")
+        elif experts and load_module_strict:
+            raise FileNotFoundError(f"{f}: this run splits the experts over {mpu.get_expert_parallel_world_size()} "
+                                    "ranks, but the checkpoint has no expert file for this rank")
     if engine.optimizer is not None and hasattr(engine.optimizer, "refresh_master_from_params"):
         engine.optimizer.refresh_master_from_params()
     if not load_module_only:
@@ -324,10 +358,12 @@ def _load_tag_impl(engine, load_dir, tag, load_optimizer_states, load_lr_schedul
         if load_lr_scheduler_states and engine.lr_scheduler is not None and state.get("lr_scheduler") is not None:
             engine.lr_scheduler.load_state_dict(state["lr_scheduler"])
         if load_optimizer_states and engine.optimizer is not None:
-            f = _optim_file(load_dir, tag, engine.neox_args.precision == "bfloat16")
-            if not os.path.isfile(f):
-                f2 = _optim_file(load_dir, tag, not (engine.neox_args.precision == "bfloat16"))
-                f = f2 if os.path.isfile(f2) else f
+            bf16 = engine.neox_args.precision == "bfloat16"
+            # without ZeRO (and without experts of its own) every data-parallel rank holds the same optimizer
+            # state and only rank 0 wrote it
+            ranks = [None] if _per_rank_optimizer_state(engine) else [None, 0]
+            cands = [_optim_file(load_dir, tag, b, r) for r in ranks for b in (bf16, not bf16)]
+            f = next((c for c in cands if os.path.isfile(c)), cands[0])
             if os.path.isfile(f):
                 osd = _read(f)
                 engine.optimizer.load_state_dict(osd["optimizer_state_dict"])

@@ -304,6 +304,10 @@ def get_expert_data_parallel_world_size() -> int:
     return len(_S.expert_data_ranks)
 
 
+def get_expert_data_parallel_rank() -> int:
+    return _S.expert_data_ranks.index(_S.rank) if _S.rank in _S.expert_data_ranks else 0
+
+
 # ---------------------------------------------------------------- small helpers
 def divide(numerator: int, denominator: int) -> int:
     assert numerator % denominator == 0, f"{numerator} is not divisible by {denominator}"

@@ -446,6 +446,29 @@ def test_checkpoint_round_trip_sequential(tmp_path):
     assert sd["iteration"] == 42 and "args" in sd
 
 
+def test_checkpoint_round_trip_data_parallel_without_zero(tmp_path):
+    """ZeRO stage 0 on two data-parallel ranks: only rank 0 writes the (replicated) optimizer state and both read it."""
+    run_distributed(_checkpoint, 2, {"zero_optimization": {"stage": 0}}, str(tmp_path))
+    files = os.listdir(tmp_path / "global_step42")
+    assert "zero_pp_rank_0_mp_rank_00_optim_states.pt" in files
+    assert "zero_pp_rank_1_mp_rank_00_optim_states.pt" not in files
+
+
+@pytest.mark.parametrize("world,zero", [(2, 0), (4, 1)])
+def test_checkpoint_round_trip_expert_parallel(tmp_path, world, zero):
+    """Experts split over two expert-parallel ranks (times two expert-data-parallel ranks in the second case): every
+    expert-parallel rank writes its own experts and optimizer state, and gets them back."""
+    run_distributed(_checkpoint, world, {"moe_num_experts": 4, "moe_top_k": 2, "expert_interval": 2,
+                                         "moe_expert_parallel_size": 2, "gpt_j_residual": False,
+                                         "zero_optimization": {"stage": zero}}, str(tmp_path))
+    files = os.listdir(tmp_path / "global_step42")
+    assert {"expert_ep_rank_00_mp_rank_00_model_states.pt", "expert_ep_rank_01_mp_rank_00_model_states.pt"} <= set(files)
+    a = torch.load(tmp_path / "global_step42" / "expert_ep_rank_00_mp_rank_00_model_states.pt", weights_only=False)
+    b = torch.load(tmp_path / "global_step42" / "expert_ep_rank_01_mp_rank_00_model_states.pt", weights_only=False)
+    assert set(a) == set(b) and a and any(not torch.equal(a[k], b[k]) for k in a)      # different experts
+    assert sum(f.endswith("optim_states.pt") for f in files) == world
+
+
 def test_checkpoint_round_trip_zero1_two_ranks(tmp_path):
     run_distributed(_checkpoint, 2, {"zero_optimization": {"stage": 1}, "precision": "bfloat16"}, str(tmp_path))
     files = os.listdir(tmp_path / "global_step42")
