@@ -115,8 +115,11 @@ def _expert_file(d):
 
 
 def _per_rank_optimizer_state(engine) -> bool:
-    """Whether every data-parallel rank holds optimizer state of its own: ZeRO shards, or experts of its own."""
-    return getattr(engine.optimizer, "zero_stage", 0) >= 1 or mpu.get_expert_parallel_world_size() > 1
+    """Whether every data-parallel rank holds optimizer state of its own: ZeRO shards, experts of its own, or an
+    optimizer that says so (the error-feedback buffers of compressed communication)."""
+    inner = getattr(engine.optimizer, "optimizer", engine.optimizer)
+    return getattr(engine.optimizer, "zero_stage", 0) >= 1 or mpu.get_expert_parallel_world_size() > 1 or \
+        bool(getattr(inner, "rank_local_state", False))
 
 
 def _atomic_save(obj, path):

@@ -81,6 +81,7 @@ def compressed_allreduce(buf, worker_error, server_error, group=None):
 
 class OneBitAdam(torch.optim.Optimizer):
     supports_grad_scale = False
+    rank_local_state = True         # the error-feedback buffers differ per rank: every rank checkpoints its own state
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, freeze_step=400,
                  bias_correction=True, comm_group=None, **_ignored):

@@ -454,6 +454,16 @@ def test_checkpoint_round_trip_data_parallel_without_zero(tmp_path):
     assert "zero_pp_rank_1_mp_rank_00_optim_states.pt" not in files
 
 
+def test_checkpoint_round_trip_onebit_adam_compression_phase(tmp_path):
+    """Saved while the momentum is already exchanged as sign bits: the per-rank error-feedback buffers are part of
+    every rank's own optimizer file, so the continuation is exact."""
+    run_distributed(_checkpoint, 2, {"zero_optimization": {"stage": 0},
+                                     "optimizer": {"type": "OneBitAdam", "params": {"lr": 1e-3, "freeze_step": 2}}},
+                    str(tmp_path))
+    files = os.listdir(tmp_path / "global_step42")
+    assert sum(f.endswith("optim_states.pt") for f in files) == 2
+
+
 @pytest.mark.parametrize("world,zero", [(2, 0), (4, 1)])
 def test_checkpoint_round_trip_expert_parallel(tmp_path, world, zero):
     """Experts split over two expert-parallel ranks (times two expert-data-parallel ranks in the second case): every
