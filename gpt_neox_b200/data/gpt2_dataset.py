@@ -141,6 +141,20 @@ def _build_shuffle_idx(size, np_rng):
     return shuffle_idx
 
 
+def _io_barrier():
+    """Wait for the rank that builds the index files.  Only the ranks that load data come here (tensor-parallel rank
+    0 of the first and last pipeline stages), so the barrier runs over their group, not over the world."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    from ..parallel import mpu
+    if mpu.model_parallel_is_initialized():
+        group = mpu.get_io_parallel_group()
+        if group is not None:
+            dist.barrier(group=group)
+        return
+    dist.barrier()
+
+
 def _is_builder(use_shared_fs):
     if not (dist.is_available() and dist.is_initialized()):
         return True
@@ -212,8 +226,7 @@ def _build_index_mappings(name, data_prefix, documents, sizes, label_dataset, nu
         np.save(f_sample, sample_idx, allow_pickle=True)
         np.save(f_shuffle, shuffle_idx, allow_pickle=True)
         print_rank_0(f" > elapsed time to build and save index mappings (seconds): {time.time() - t0:4f}")
-    if dist.is_available() and dist.is_initialized():
-        dist.barrier()
+    _io_barrier()
     doc_idx = np.load(f_doc, allow_pickle=True, mmap_mode="r")
     sample_idx = np.load(f_sample, allow_pickle=True, mmap_mode="r")
     shuffle_idx = np.load(f_shuffle, allow_pickle=True, mmap_mode="r")

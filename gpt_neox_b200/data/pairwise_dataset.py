@@ -11,10 +11,9 @@ import time
 
 import numpy as np
 import torch
-import torch.distributed as dist
 
 from ..utils import print_rank_0
-from .gpt2_dataset import _is_builder
+from .gpt2_dataset import _io_barrier, _is_builder
 
 
 def _build_groups(docs, pos_sizes, neg_sizes, n, seq_length, pack_impl, rng):
@@ -74,8 +73,7 @@ class PairwiseDataset(torch.utils.data.Dataset):
                 np.save(f_start, starts, allow_pickle=True)
                 print_rank_0(f" > elapsed time to build and save pairwise index mappings (seconds): "
                              f"{time.time() - t0:4f}")
-            if dist.is_available() and dist.is_initialized():
-                dist.barrier()
+            _io_barrier()
             self.doc_idx = np.load(f_doc, allow_pickle=True, mmap_mode="r")
             self.starts = np.load(f_start, allow_pickle=True, mmap_mode="r")
         print_rank_0(f"    {name}: {len(self)} pairwise samples")
