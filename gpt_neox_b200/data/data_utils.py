@@ -148,7 +148,7 @@ def build_weighted_datasets(neox_args, train_num_samples, valid_num_samples, tes
                             valid_epochs, test_epochs, build_index_mappings=True):
     train_ds, valid_ds, test_ds = [], [], []
     a = neox_args
-    g = lambda lst, i: lst[i] if lst else None
+    g = lambda lst, i: lst[i] if lst and i < len(lst) else None      # the three splits may list different numbers of corpora
     n = max(len(x) for x in (a.train_data_paths or a.pos_train_data_paths or [],
                              a.valid_data_paths or a.pos_valid_data_paths or [],
                              a.test_data_paths or a.pos_test_data_paths or []))
