@@ -134,6 +134,8 @@ def get_normalized_weights_and_num_samples(weights, num_samples):
 def weights_by_num_docs(l, alpha=0.3):
     """Multinomial sampling weights from document counts, smoothed by ``alpha`` (as used for
     multilingual corpora): p_i ~ (n_i / N)^alpha, then scaled by (1 - p_i) and renormalised."""
+    if len(l) == 1:                 # a single corpus: (1 - p) would be zero
+        return [1.0]
     total = sum(l)
     unbiased = [i / total for i in l]
     probs = [p ** alpha for p in unbiased]
