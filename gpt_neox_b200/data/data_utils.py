@@ -268,6 +268,10 @@ def build_train_valid_test_data_loaders(neox_args):
 
 
 def shift_and_wrap_data_loaders(neox_args, train_dl, valid_dl, test_dl, loop=True):
+    for name, dl in (("training", train_dl), ("validation", valid_dl), ("test", test_dl)):
+        if dl is not None and len(dl) == 0:
+            raise ValueError(f"the {name} split holds fewer samples than one batch per data-parallel rank "
+                             "(check `split` / the data paths / train_micro_batch_size_per_gpu)")
     if train_dl is not None:
         train_dl.batch_sampler.start_iter = (neox_args.iteration * neox_args.gradient_accumulation_steps) % len(train_dl)
         print_rank_0(f"setting training data start iteration to {train_dl.batch_sampler.start_iter}")
