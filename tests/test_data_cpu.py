@@ -158,3 +158,41 @@ def test_tokenizers(tmp_path):
         for s in ["Hello, world!", "The quick brown fox's 123 jumps\n over  lazy dogs."]:
             assert mine.tokenize(s) == t.tokenize(s)
             assert mine.detokenize(mine.tokenize(s)) == s
+
+
+def _pretrain_on_disk(rank, world, cfg):
+    from common import make_args
+    from gpt_neox_b200.training import pretrain
+    args = make_args(**{**cfg, "global_num_gpus": world})
+    args.configure_distributed_args()
+    pretrain(args)
+    assert args.iteration == (cfg.get("train_iters") or args.train_iters) and args.iteration > 0
+
+
+@pytest.mark.parametrize("world,extra", [
+    (2, {"model_parallel_size": 2, "split": "80,10,10"}),                     # only tensor-parallel rank 0 loads data
+    (2, {"pipe_parallel_size": 2, "num_layers": 4, "gradient_accumulation_steps": 2, "weight_by_num_documents": True,
+         "weighted_sampler_alpha": 0.5, "paths": True}),                      # first and last stage load; 2 / 1 / 1 corpora
+    (2, {"train_iters": None, "train_epochs": 1, "split": "60,20,20", "lr_decay_fraction": 0.9}),
+])
+def test_pretrain_reads_indexed_datasets_from_disk(tmp_path, world, extra):
+    """``pretrain`` end to end on memory-mapped corpora: index files are built once by rank 0 while the other
+    data-loading ranks (not the whole world) wait; blended corpora; epochs instead of iterations."""
+    from common import run_distributed
+    rng = np.random.default_rng(0)
+    for name in ("a", "b"):
+        _write_corpus(str(tmp_path / name), [rng.integers(1, 500, size=rng.integers(20, 90)) for _ in range(60)])
+    extra = dict(extra)
+    cfg = {"save": str(tmp_path / "ckpt"), "train_iters": 6, "lr_decay_iters": 6, "eval_interval": 3, "eval_iters": 2,
+           "log_interval": 2, "checkpoint_factor": 3, "num_workers": 0}
+    if extra.pop("paths", False):
+        cfg.update({"data_path": None, "train_data_paths": [str(tmp_path / "a"), str(tmp_path / "b")],
+                    "valid_data_paths": [str(tmp_path / "a")], "test_data_paths": [str(tmp_path / "b")]})
+    else:
+        cfg["data_path"] = str(tmp_path / "a")
+    if extra.get("train_epochs"):
+        cfg.pop("lr_decay_iters")
+    cfg.update(extra)
+    run_distributed(_pretrain_on_disk, world, cfg, timeout=240)
+    assert os.path.exists(tmp_path / "ckpt" / "latest")
+    assert any("indexmap" in f for f in os.listdir(tmp_path))
