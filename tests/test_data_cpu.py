@@ -196,3 +196,38 @@ def test_pretrain_reads_indexed_datasets_from_disk(tmp_path, world, extra):
     run_distributed(_pretrain_on_disk, world, cfg, timeout=240)
     assert os.path.exists(tmp_path / "ckpt" / "latest")
     assert any("indexmap" in f for f in os.listdir(tmp_path))
+
+
+@pytest.mark.parametrize("kind", ["labels", "pairwise", "reward"])
+def test_pretrain_with_label_pairwise_and_reward_corpora(tmp_path, kind):
+    """The side corpora of fine-tuning and preference training through ``pretrain``: per-token labels (SFT masks),
+    chosen / rejected pairs (DPO, ``dataset_impl: pairwise``) and per-token rewards (KTO)."""
+    from common import run_distributed
+    rng = np.random.default_rng(0)
+    docs = [rng.integers(1, 500, size=rng.integers(20, 60)) for _ in range(60)]
+    p = lambda n: [str(tmp_path / n)]
+    cfg = {"save": str(tmp_path / "ckpt"), "train_iters": 4, "lr_decay_iters": 4, "eval_interval": 2, "eval_iters": 1,
+           "log_interval": 2, "checkpoint_factor": 4, "num_workers": 0, "data_path": None, "pack_impl": "unpacked"}
+    three = lambda key, n: {f"train_{key}": p(n), f"valid_{key}": p(n), f"test_{key}": p(n)}
+    if kind == "pairwise":
+        _write_corpus(str(tmp_path / "pos"), docs)
+        _write_corpus(str(tmp_path / "neg"), [d[::-1] for d in docs])
+        cfg.update({"train_impl": "dpo", "dataset_impl": "pairwise", "dpo_reference_free": True,
+                    "train_micro_batch_size_per_gpu": 2})
+        for split in ("train", "valid", "test"):
+            cfg[f"pos_{split}_data_paths"], cfg[f"neg_{split}_data_paths"] = p("pos"), p("neg")
+    else:
+        _write_corpus(str(tmp_path / "a"), docs)
+        cfg.update({**three("data_paths", "a"), "model_parallel_size": 2})
+        if kind == "labels":
+            _write_corpus(str(tmp_path / "a_label"), [np.where(np.arange(len(d)) < 3, -100, d) for d in docs],
+                          dtype=np.int32)
+            cfg.update(three("label_data_paths", "a_label"))
+        else:
+            _write_corpus(str(tmp_path / "a_reward"),
+                          [np.full(len(d), 1.0 if i % 2 else -1.0, dtype=np.float32) for i, d in enumerate(docs)],
+                          dtype=np.float32)
+            cfg.update({**three("reward_data_paths", "a_reward"), "train_impl": "kto",
+                        "train_micro_batch_size_per_gpu": 2})
+    run_distributed(_pretrain_on_disk, 2, cfg, timeout=240)
+    assert os.path.exists(tmp_path / "ckpt" / "latest")
