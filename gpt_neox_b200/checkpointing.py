@@ -318,11 +318,18 @@ def _load_tag_impl(engine, load_dir, tag, load_optimizer_states, load_lr_schedul
             if layer is None or not any(True for _ in layer.state_dict()):
                 continue
             f = os.path.join(d, f"layer_{idx:02d}-model_{tp:02d}-model_states.pt")
-            if not os.path.isfile(f):
-                if load_module_strict:
-                    raise FileNotFoundError(f)
+            if os.path.isfile(f):
+                sd = _read(f)
+            elif state.get("module") is not None:
+                # a sequential-layout checkpoint read into a pipeline module: this layer's entries of the one state dict
+                pre = f"sequential.{idx}."
+                sd = {k[len(pre):]: v for k, v in state["module"].items() if k.startswith(pre)}
+                if not sd and load_module_strict:
+                    raise KeyError(f"{state_file} has no parameters of layer {idx}")
+            elif load_module_strict:
+                raise FileNotFoundError(f)
+            else:
                 continue
-            sd = _read(f)
             _load_module_sequential(layer, sd, load_module_strict)
     else:
         state_file = os.path.join(d, f"mp_rank_{tp:02d}_model_states.pt")

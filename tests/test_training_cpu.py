@@ -446,6 +446,30 @@ def test_checkpoint_round_trip_sequential(tmp_path):
     assert sd["iteration"] == 42 and "args" in sd
 
 
+def _cross_layout(rank, world, cfg_save, cfg_load, d):
+    from gpt_neox_b200.checkpointing import save_checkpoint
+    from gpt_neox_b200.parallel import mpu
+    args, model, opt, sched = _setup({**cfg_save, "global_num_gpus": world, "save": d, "load": None})
+    _train(args, model, opt, sched, 2, _fixed_batches(args))
+    save_checkpoint(args, 7, model, opt, sched)
+    strip = lambda k: k.split(".", 1)[-1] if k.startswith("sequential.") else k
+    want = {strip(k): v.detach().clone() for k, v in model.module.state_dict().items()}
+    mpu.destroy_model_parallel()
+    args2, model2, opt2, sched2 = _setup({**cfg_load, "global_num_gpus": world, "save": d, "load": d})
+    assert args2.iteration == 7
+    got = {strip(k): v for k, v in model2.module.state_dict().items()}
+    shared = set(got) & set(want)
+    assert len(shared) > 10 and all(torch.equal(got[k], want[k]) for k in shared)
+    _train(args2, model2, opt2, sched2, 1, _fixed_batches(args2))
+
+
+@pytest.mark.parametrize("save,load", [(1, 0), (0, 1)])
+def test_checkpoint_moves_between_the_pipeline_and_the_sequential_layout(tmp_path, save, load):
+    """Per-layer files (a pipeline engine with one stage) load into the sequential model and the sequential state
+    dict loads into a pipeline module: same weights, training continues."""
+    run_distributed(_cross_layout, 1, {"pipe_parallel_size": save}, {"pipe_parallel_size": load}, str(tmp_path))
+
+
 def test_checkpoint_round_trip_data_parallel_without_zero(tmp_path):
     """ZeRO stage 0 on two data-parallel ranks: only rank 0 writes the (replicated) optimizer state and both read it."""
     run_distributed(_checkpoint, 2, {"zero_optimization": {"stage": 0}}, str(tmp_path))
