@@ -541,6 +541,8 @@ class NeoXArgs:
         opt = self.optimizer or {"type": OPT_DEFAULT, "params": OPT_PARAMS_DEFAULTS}
         self.optimizer_type = opt.get("type", OPT_DEFAULT)
         self.lr = opt.get("params", {}).get("lr", OPT_PARAMS_DEFAULTS["lr"])
+        if isinstance(self.lr, str):            # YAML 1.1 reads "1e-4" (no dot) as a string
+            self.lr = float(self.lr)
         if self.optimizer_type.lower() == "onebitadam":
             assert self.train_iters is not None, "OneBitAdam requires train_iters to be specified"
             self.scheduler = {"type": "WarmupDecayLR",

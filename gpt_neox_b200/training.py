@@ -329,10 +329,22 @@ def param_offload(neox_args) -> bool:
     return neox_args.zero_stage == 3 and str(off.get("device", "none")).lower() == "cpu"
 
 
+def _numeric(v):
+    """YAML 1.1 reads ``1e-8`` (no dot) as a string: give optimizer hyper-parameters written that way their value."""
+    if isinstance(v, str):
+        try:
+            return float(v)
+        except ValueError:
+            return v
+    if isinstance(v, (list, tuple)):
+        return type(v)(_numeric(x) for x in v)
+    return v
+
+
 def _inner_optimizer(neox_args):
     """(class, kwargs) of the element-wise optimizer that updates the flat fp32 shards."""
     name = neox_args.optimizer_type.lower()
-    params = dict(neox_args.optimizer.get("params", {}))
+    params = {k: _numeric(v) for k, v in dict(neox_args.optimizer.get("params", {})).items()}
     params.pop("freeze_step", None) if name != "onebitadam" else None
     if name in ("adam", "cpu_adam", "cpu_torch_adam", "onebitadam"):
         if name == "cpu_torch_adam":

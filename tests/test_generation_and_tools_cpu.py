@@ -396,3 +396,32 @@ def _static_cache_generation(rank, world, cfg):
 ])
 def test_static_cache_decoding_matches_the_growing_cache(cfg):
     run_distributed(_static_cache_generation, 1, cfg)
+
+
+def test_deepy_train_then_generate_from_the_checkpoint(tmp_path):
+    """The command-line surface end to end on one CPU rank: ``deepy.py train.py cfg.yml`` writes a checkpoint and
+    ``deepy.py generate.py cfg.yml gen.yml`` loads it and writes samples."""
+    import json
+    import subprocess
+    import sys
+    from common import ROOT
+    cfg = {"num_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "seq_length": 32,
+           "max_position_embeddings": 32, "pos_emb": "rotary", "no_weight_tying": True,
+           "tokenizer_type": "CharLevelTokenizer", "make_vocab_size_divisible_by": 64, "precision": "fp32",
+           "optimizer": {"type": "Adam", "params": {"lr": 0.001, "betas": [0.9, 0.95], "eps": 1.0e-8}},
+           "train_micro_batch_size_per_gpu": 2, "gradient_accumulation_steps": 1, "train_iters": 4, "lr_decay_iters": 4,
+           "eval_interval": 100, "eval_iters": 1, "log_interval": 2, "checkpoint_factor": 4, "data_path": "synthetic",
+           "save": str(tmp_path / "ckpt"), "load": str(tmp_path / "ckpt"), "num_workers": 0, "global_num_gpus": 1}
+    gen = {"text_gen_type": "unconditional", "maximum_tokens": 8, "temperature": 0.8, "top_k": 5, "num_samples": 3,
+           "sample_output_file": str(tmp_path / "samples.txt")}
+    (tmp_path / "cfg.yml").write_text(json.dumps(cfg))
+    (tmp_path / "gen.yml").write_text(json.dumps(gen))
+    env = {**os.environ, "CUDA_VISIBLE_DEVICES": "", "MASTER_ADDR": "127.0.0.1"}
+    for script, extra in (("train.py", []), ("generate.py", [str(tmp_path / "gen.yml")])):
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "deepy.py"), os.path.join(ROOT, script),
+                            str(tmp_path / "cfg.yml"), *extra], cwd=ROOT, env=env, capture_output=True, text=True,
+                           timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert (tmp_path / "ckpt" / "latest").read_text().strip() == "global_step4"
+    samples = [json.loads(l) for l in open(tmp_path / "samples.txt")]
+    assert len(samples) == 3 and all(s["length"] > 0 for s in samples)
