@@ -169,16 +169,31 @@ def _pretrain_on_disk(rank, world, cfg):
     assert args.iteration == (cfg.get("train_iters") or args.train_iters) and args.iteration > 0
 
 
-@pytest.mark.parametrize("world,extra", [
+_ON_DISK_CASES = [
     (2, {"model_parallel_size": 2, "split": "80,10,10"}),                     # only tensor-parallel rank 0 loads data
     (2, {"pipe_parallel_size": 2, "num_layers": 4, "gradient_accumulation_steps": 2, "weight_by_num_documents": True,
          "weighted_sampler_alpha": 0.5, "paths": True}),                      # first and last stage load; 2 / 1 / 1 corpora
     (2, {"train_iters": None, "train_epochs": 1, "split": "60,20,20", "lr_decay_fraction": 0.9}),
-])
-def test_pretrain_reads_indexed_datasets_from_disk(tmp_path, world, extra):
+]
+
+
+def test_pretrain_reads_indexed_datasets_from_disk(tmp_path):
     """``pretrain`` end to end on memory-mapped corpora: index files are built once by rank 0 while the other
     data-loading ranks (not the whole world) wait; blended corpora; epochs instead of iterations."""
-    from common import run_distributed
+    from common import run_distributed_many
+    jobs = []
+    for i, (world, extra) in enumerate(_ON_DISK_CASES):
+        d = tmp_path / f"case{i}"
+        os.makedirs(d)
+        jobs.append((_pretrain_on_disk, world, _on_disk_config(d, extra)))
+    run_distributed_many(*jobs, timeout=240)
+    for i in range(len(jobs)):
+        d = tmp_path / f"case{i}"
+        assert os.path.exists(d / "ckpt" / "latest")
+        assert any("indexmap" in f for f in os.listdir(d))
+
+
+def _on_disk_config(tmp_path, extra):
     rng = np.random.default_rng(0)
     for name in ("a", "b"):
         _write_corpus(str(tmp_path / name), [rng.integers(1, 500, size=rng.integers(20, 90)) for _ in range(60)])
@@ -193,16 +208,23 @@ def test_pretrain_reads_indexed_datasets_from_disk(tmp_path, world, extra):
     if extra.get("train_epochs"):
         cfg.pop("lr_decay_iters")
     cfg.update(extra)
-    run_distributed(_pretrain_on_disk, world, cfg, timeout=240)
-    assert os.path.exists(tmp_path / "ckpt" / "latest")
-    assert any("indexmap" in f for f in os.listdir(tmp_path))
+    return cfg
 
 
-@pytest.mark.parametrize("kind", ["labels", "pairwise", "reward"])
-def test_pretrain_with_label_pairwise_and_reward_corpora(tmp_path, kind):
+def test_pretrain_with_label_pairwise_and_reward_corpora(tmp_path):
     """The side corpora of fine-tuning and preference training through ``pretrain``: per-token labels (SFT masks),
     chosen / rejected pairs (DPO, ``dataset_impl: pairwise``) and per-token rewards (KTO)."""
-    from common import run_distributed
+    from common import run_distributed_many
+    jobs = []
+    for kind in ("labels", "pairwise", "reward"):
+        os.makedirs(tmp_path / kind)
+        jobs.append((_pretrain_on_disk, 2, _side_corpora_config(tmp_path / kind, kind)))
+    run_distributed_many(*jobs, timeout=240)
+    for kind in ("labels", "pairwise", "reward"):
+        assert os.path.exists(tmp_path / kind / "ckpt" / "latest")
+
+
+def _side_corpora_config(tmp_path, kind):
     rng = np.random.default_rng(0)
     docs = [rng.integers(1, 500, size=rng.integers(20, 60)) for _ in range(60)]
     p = lambda n: [str(tmp_path / n)]
@@ -229,5 +251,4 @@ def test_pretrain_with_label_pairwise_and_reward_corpora(tmp_path, kind):
                           dtype=np.float32)
             cfg.update({**three("reward_data_paths", "a_reward"), "train_impl": "kto",
                         "train_micro_batch_size_per_gpu": 2})
-    run_distributed(_pretrain_on_disk, 2, cfg, timeout=240)
-    assert os.path.exists(tmp_path / "ckpt" / "latest")
+    return cfg

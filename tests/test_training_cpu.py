@@ -363,7 +363,7 @@ def _post_training(rank, world, cfg):
     return losses
 
 
-@pytest.mark.parametrize("world,cfg", [
+_POST_TRAINING_CASES = [
     (2, {"train_impl": "dpo", "model_parallel_size": 2, "dpo_beta": 0.1}),                       # with a reference model
     (4, {"train_impl": "dpo", "dpo_reference_free": True, "model_parallel_size": 2, "sequence_parallel": True,
          "zero_optimization": {"stage": 2, "reduce_bucket_size": 30000}}),
@@ -372,9 +372,14 @@ def _post_training(rank, world, cfg):
     (2, {"train_impl": "kto", "model_parallel_size": 2}),                                        # reference model
     (2, {"train_impl": "kto", "precompute_model_name": "ref"}),                                  # stored reference log-probs
     (2, {"train_impl": "reinforce", "model_parallel_size": 2}),
-])
-def test_post_training_objectives_train_end_to_end(world, cfg):
-    run_distributed(_post_training, world, {"train_micro_batch_size_per_gpu": 2, **cfg})
+]
+
+
+def test_post_training_objectives_train_end_to_end():
+    # the six jobs are independent: side by side, three at a time
+    jobs = [(_post_training, world, {"train_micro_batch_size_per_gpu": 2, **cfg}) for world, cfg in _POST_TRAINING_CASES]
+    run_distributed_many(*jobs[:3])
+    run_distributed_many(*jobs[3:])
 
 
 def _pipeline_with_middle_stages(rank, world, cfg):
