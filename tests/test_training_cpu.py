@@ -312,10 +312,9 @@ def _curriculum(rank, world, cfg):
         assert loss == loss
 
 
-@pytest.mark.parametrize("world,cfg", [(1, {}), (2, {"pipe_parallel_size": 2, "num_layers": 4,
-                                                      "gradient_accumulation_steps": 2})])
-def test_sequence_length_curriculum(world, cfg):
-    run_distributed(_curriculum, world, cfg)
+def test_sequence_length_curriculum():
+    run_distributed_many((_curriculum, 1, {}),
+                         (_curriculum, 2, {"pipe_parallel_size": 2, "num_layers": 4, "gradient_accumulation_steps": 2}))
 
 
 def _post_training(rank, world, cfg):
@@ -395,12 +394,12 @@ def _pipeline_with_middle_stages(rank, world, cfg):
     assert all(l == l for l in losses)
 
 
-@pytest.mark.parametrize("world,cfg", [
-    (4, {"pipe_parallel_size": 4, "num_layers": 6, "gradient_accumulation_steps": 6, "no_weight_tying": False}),
-    (3, {"pipe_parallel_size": 3, "num_layers": 5, "gradient_accumulation_steps": 2}),       # fewer micro-batches than stages
-])
-def test_pipeline_with_middle_stages(world, cfg):
-    run_distributed(_pipeline_with_middle_stages, world, cfg)
+def test_pipeline_with_middle_stages():
+    run_distributed_many(
+        (_pipeline_with_middle_stages, 4, {"pipe_parallel_size": 4, "num_layers": 6, "gradient_accumulation_steps": 6,
+                                           "no_weight_tying": False}),
+        (_pipeline_with_middle_stages, 3, {"pipe_parallel_size": 3, "num_layers": 5,
+                                           "gradient_accumulation_steps": 2}))      # fewer micro-batches than stages
 
 
 def test_tensor4_pipeline2_layout_trains():
